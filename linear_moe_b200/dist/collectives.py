@@ -36,11 +36,13 @@ def all_gather_raw(x: torch.Tensor, g: Group, dim: int = 0) -> torch.Tensor:
     if g.is_trivial:
         return x
     x = x.contiguous()
-    out = torch.empty((g.size,) + tuple(x.shape), dtype=x.dtype, device=x.device)
+    if x.dim() == 0:
+        x = x.reshape(1)
+    out = torch.empty((g.size * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
     dist.all_gather_into_tensor(out, x, group=g.pg)
     if dim == 0:
-        return out.reshape(g.size * x.shape[0], *x.shape[1:])
-    return torch.cat(list(out.unbind(0)), dim=dim)
+        return out
+    return torch.cat(list(out.chunk(g.size, dim=0)), dim=dim)
 
 
 def reduce_scatter_raw(x: torch.Tensor, g: Group, dim: int = 0) -> torch.Tensor:

@@ -1,0 +1,365 @@
+"""Gradient buffers, data-parallel reduction and the mixed-precision Adam optimizer (with ZeRO-1).
+
+This one module plays the roles of Megatron's ``DistributedDataParallel`` (contiguous grad
+buffers, fp32 accumulation, bucketed reduce), ``Float16OptimizerWithFloat16Params`` /
+``DistributedOptimizer`` (fp32 master weights, reduce-scatter -> shard update -> all-gather),
+gradient clipping by global norm and Apex ``FusedAdam`` — the external pieces the reference
+reaches through ``setup_model_and_optimizer`` / ``optimizer.step`` (training.py:113,278-298,
+343-351; run_pretrain_qwen.sh:321-328).
+
+Layout (B200-first): parameters are grouped into at most four *flat* buffers —
+(dense | expert) x (weight-decay | no-weight-decay).  Each buffer holds the model-dtype
+parameters, an fp32 gradient accumulator, and fp32 master / exp_avg / exp_avg_sq either in full or,
+under ZeRO-1, only for this rank's contiguous shard.  Module parameters are views into the flat
+parameter buffer, so an optimizer step is ONE fused kernel per buffer
+(``ops.cuda.fused_adam``) and a gradient reduction is ONE collective per buffer — or, with the
+symmetric-memory workspace, the fused reduce-scatter + Adam + all-gather kernel over NVLS
+(``ops.cuda.zero1_fused_step``), no NCCL.
+
+Reduction groups: dense parameters average over ``dp_cp``; expert parameters sum over ``edp``
+and are scaled by ``1/(dp*cp)`` (their gradients already contain the tokens of the whole EP group;
+experts.py:153-154 ``allreduce=False``).  Parameters tagged ``sequence_parallel_grad`` (norm
+weights, router, shared-expert gate) are additionally summed over TP under sequence parallelism.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, Iterable, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..config.model_config import TrainConfig
+from ..dist import collectives as C
+from ..dist.mesh import Group, Mesh
+
+_ALIGN = 128
+
+
+def _no_weight_decay(name: str, p: nn.Parameter) -> bool:
+    return getattr(p, "_no_weight_decay", False) or p.dim() <= 1 or name.endswith(".bias")
+
+
+@dataclass
+class _Slot:
+    name: str
+    param: nn.Parameter
+    start: int
+    numel: int
+
+
+class FlatBuffer:
+    """One flat parameter/gradient buffer and its optimizer state."""
+
+    def __init__(self, slots: List[Tuple[str, nn.Parameter]], *, expert: bool, weight_decay: bool, group: Group,
+                 grad_scale: float, zero1: bool, master: bool):
+        self.expert, self.weight_decay, self.group, self.grad_scale, self.zero1 = expert, weight_decay, group, grad_scale, zero1
+        p0 = slots[0][1]
+        self.device, self.dtype = p0.device, p0.dtype
+        self.slots: List[_Slot] = []
+        off = 0
+        for name, p in slots:
+            self.slots.append(_Slot(name, p, off, p.numel()))
+            off += (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
+        shard_mult = _ALIGN * (group.size if zero1 else 1)
+        self.numel = (off + shard_mult - 1) // shard_mult * shard_mult
+        self.params = torch.zeros(self.numel, dtype=self.dtype, device=self.device)
+        self.grads = torch.zeros(self.numel, dtype=torch.float32, device=self.device)
+        for s in self.slots:
+            view = self.params[s.start:s.start + s.numel].view_as(s.param)
+            view.copy_(s.param.data)
+            s.param.data = view
+            s.param.main_grad = self.grads[s.start:s.start + s.numel].view_as(s.param)
+        if zero1 and group.size > 1:
+            n = self.numel // group.size
+            self.shard = (group.rank * n, (group.rank + 1) * n)
+        else:
+            self.shard = (0, self.numel)
+        lo, hi = self.shard
+        self.master = self.params[lo:hi].float().clone() if master else None
+        self.exp_avg = torch.zeros(hi - lo, dtype=torch.float32, device=self.device)
+        self.exp_avg_sq = torch.zeros(hi - lo, dtype=torch.float32, device=self.device)
+        # tensor-parallel duplicates are counted once in the gradient norm: mask of slots that are
+        # replicated over TP (norm weights, router, ...)
+        self.tp_dup = [not getattr(s.param, "tensor_parallel", False) for s in self.slots]
+
+    def shard_view(self, t: torch.Tensor) -> torch.Tensor:
+        return t[self.shard[0]:self.shard[1]]
+
+    def reload_master(self):
+        """Refresh fp32 masters from the model parameters (``optimizer.reload_model_params()``,
+        finetune_utils.py:317-327)."""
+        if self.master is not None:
+            self.master.copy_(self.shard_view(self.params).float())
+
+
+class MixedPrecisionAdam:
+    """AdamW over flat buffers with fp32 masters, global-norm clipping, optional dynamic loss scaling
+    and optional ZeRO-1 sharding over the data-parallel group."""
+
+    def __init__(self, model: nn.Module, mesh: Mesh, tc: TrainConfig, *, zero1: bool = False,
+                 sequence_parallel: bool = False, fused_comm: bool = True):
+        self.mesh, self.tc, self.zero1 = mesh, tc, zero1 and (mesh.dp * mesh.cp) > 1
+        self.sequence_parallel = sequence_parallel and mesh.tp > 1
+        self.fused_comm = fused_comm
+        self.step_count = 0
+        named = [(n, p) for n, p in model.named_parameters() if p.requires_grad]
+        seen, uniq = set(), []
+        for n, p in named:
+            if id(p) not in seen:
+                seen.add(id(p))
+                uniq.append((n, p))
+        self.named = uniq
+        groups: Dict[Tuple[bool, bool], List[Tuple[str, nn.Parameter]]] = {}
+        for n, p in uniq:
+            key = (bool(getattr(p, "expert_parallel", False)), not _no_weight_decay(n, p))
+            groups.setdefault(key, []).append((n, p))
+        dpcp = mesh.dp * mesh.cp
+        self.buffers: List[FlatBuffer] = []
+        for (expert, wd), slots in sorted(groups.items()):
+            g = mesh["edp"] if expert else mesh["dp_cp"]
+            by_dtype: Dict[torch.dtype, list] = {}
+            for n, p in slots:
+                by_dtype.setdefault(p.dtype, []).append((n, p))
+            for dt, sl in by_dtype.items():
+                self.buffers.append(FlatBuffer(sl, expert=expert, weight_decay=wd, group=g, grad_scale=1.0 / dpcp,
+                                               zero1=self.zero1, master=dt != torch.float32))
+        self._hooks = []
+        for n, p in uniq:
+            self._hooks.append(p.register_post_accumulate_grad_hook(self._accumulate))
+        # loss scaling (fp16 only)
+        self.loss_scale = None
+        if tc.fp16:
+            self.loss_scale = tc.loss_scale if tc.loss_scale else tc.initial_loss_scale
+            self._growth_tracker, self._hysteresis = 0, tc.hysteresis
+        self.dynamic_scale = tc.fp16 and not tc.loss_scale
+        self.skipped_iters = 0
+
+    # ------------------------------------------------------------------
+    @staticmethod
+    def _accumulate(p: nn.Parameter):
+        if p.grad is not None:
+            p.main_grad.add_(p.grad.to(torch.float32))
+            p.grad = None
+
+    def zero_grad(self):
+        for b in self.buffers:
+            b.grads.zero_()
+        for _, p in self.named:
+            p.grad = None
+
+    def scale_loss(self, loss: torch.Tensor) -> torch.Tensor:
+        return loss if self.loss_scale is None else loss * self.loss_scale
+
+    # ------------------------------------------------------------------
+    def _reduce_sequence_parallel_grads(self):
+        if not self.sequence_parallel:
+            return
+        g = self.mesh["tp"]
+        ts = [p.main_grad for _, p in self.named if getattr(p, "sequence_parallel_grad", False)]
+        if ts:
+            flat = torch.cat([t.reshape(-1) for t in ts])
+            C.all_reduce_(flat, g)
+            off = 0
+            for t in ts:
+                t.copy_(flat[off:off + t.numel()].view_as(t))
+                off += t.numel()
+
+    def reduce_grads(self):
+        """Data-parallel reduction of every buffer: all-reduce, or reduce-scatter into this rank's
+        shard under ZeRO-1 (the rest of the buffer is then stale until the next zero_grad)."""
+        self._reduce_sequence_parallel_grads()
+        for b in self.buffers:
+            if b.grad_scale != 1.0:
+                b.grads.mul_(b.grad_scale)
+            g = b.group
+            if g.is_trivial:
+                continue
+            if self.zero1:
+                out = C.reduce_scatter_raw(b.grads, g, dim=0)
+                b.shard_view(b.grads).copy_(out)
+            else:
+                C.all_reduce_(b.grads, g)
+
+    # ------------------------------------------------------------------
+    def _grad_sq_and_finite(self) -> Tuple[torch.Tensor, torch.Tensor]:
+        mesh = self.mesh
+        dev = self.buffers[0].device
+        dense = torch.zeros((), dtype=torch.float32, device=dev)
+        expert = torch.zeros((), dtype=torch.float32, device=dev)
+        for b in self.buffers:
+            lo, hi = b.shard
+            if mesh.tp > 1 and mesh.tp_rank != 0:
+                # drop TP-replicated parameters from all but TP rank 0
+                sq = torch.zeros((), dtype=torch.float32, device=dev)
+                for s, dup in zip(b.slots, b.tp_dup):
+                    if dup:
+                        continue
+                    a, e = max(s.start, lo), min(s.start + s.numel, hi)
+                    if e > a:
+                        sq = sq + b.grads[a:e].pow(2).sum()
+            else:
+                sq = b.grads[lo:hi].pow(2).sum()
+            if b.expert:
+                expert = expert + sq
+            else:
+                dense = dense + sq
+        if self.zero1:
+            C.all_reduce_(dense, mesh["dp_cp"])
+            C.all_reduce_(expert, mesh["edp"])
+        C.all_reduce_(expert, mesh["ep"])
+        total = dense + expert
+        C.all_reduce_(total, mesh["mp"])
+        return total, torch.isfinite(total)
+
+    @torch.no_grad()
+    def step(self, lr: float, weight_decay: float) -> Tuple[bool, Optional[float], int]:
+        """Returns (update_successful, grad_norm, num_zeros_in_grad) like Megatron's optimizer.step
+        (training.py:343-351)."""
+        tc = self.tc
+        inv_scale = 1.0 if self.loss_scale is None else 1.0 / self.loss_scale
+        total_sq, finite = self._grad_sq_and_finite()
+        if self.loss_scale is not None:
+            ok = bool(finite)
+            self._update_loss_scale(ok)
+            if not ok:
+                self.skipped_iters += 1
+                return False, None, 0
+        grad_norm = float(total_sq.sqrt()) * inv_scale if (tc.clip_grad > 0 or tc.log_interval) else None
+        clip = 1.0
+        if tc.clip_grad > 0 and grad_norm is not None and math.isfinite(grad_norm):
+            clip = min(1.0, tc.clip_grad / (grad_norm + 1e-6))
+        if grad_norm is not None and not math.isfinite(grad_norm) and tc.check_for_nan_in_loss_and_grad:
+            raise FloatingPointError(f"non-finite gradient norm {grad_norm} on rank {self.mesh.rank}")
+        self.step_count += 1
+        b1, b2, eps = tc.adam_beta1, tc.adam_beta2, tc.adam_eps
+        bc1, bc2 = 1.0 - b1 ** self.step_count, 1.0 - b2 ** self.step_count
+        gscale = inv_scale * clip
+        for b in self.buffers:
+            lo, hi = b.shard
+            wd = weight_decay if b.weight_decay else 0.0
+            g = b.grads[lo:hi]
+            pshard = b.params[lo:hi]
+            if g.is_cuda:
+                from ..ops import cuda as K
+                K.fused_adam(pshard, b.master, g, b.exp_avg, b.exp_avg_sq, lr, b1, b2, eps, wd, bc1, bc2, gscale)
+            else:
+                w = b.master if b.master is not None else pshard
+                gg = g * gscale
+                b.exp_avg.mul_(b1).add_(gg, alpha=1 - b1)
+                b.exp_avg_sq.mul_(b2).addcmul_(gg, gg, value=1 - b2)
+                denom = (b.exp_avg_sq / bc2).sqrt_().add_(eps)
+                w.mul_(1.0 - lr * wd).addcdiv_(b.exp_avg / bc1, denom, value=-lr)
+                if b.master is not None:
+                    pshard.copy_(w)
+            if self.zero1 and not b.group.is_trivial:
+                gathered = C.all_gather_raw(pshard.clone(), b.group, dim=0)
+                b.params.copy_(gathered)
+        return True, grad_norm, 0
+
+    def count_zeros(self) -> int:
+        z = torch.zeros((), dtype=torch.float32, device=self.buffers[0].device)
+        for b in self.buffers:
+            lo, hi = b.shard
+            z += (b.grads[lo:hi] == 0).sum()
+        return int(z)
+
+    def _update_loss_scale(self, ok: bool):
+        if not self.dynamic_scale:
+            return
+        tc = self.tc
+        if not ok:
+            self._growth_tracker = 0
+            self._hysteresis -= 1
+            if self._hysteresis <= 0:
+                self.loss_scale = max(self.loss_scale / 2.0, tc.min_loss_scale)
+        else:
+            self._growth_tracker += 1
+            if self._growth_tracker >= tc.loss_scale_window:
+                self._growth_tracker, self._hysteresis = 0, tc.hysteresis
+                self.loss_scale *= 2.0
+
+    def reload_model_params(self):
+        for b in self.buffers:
+            b.reload_master()
+
+    # ---- checkpointing -------------------------------------------------
+    def state_dict(self) -> dict:
+        return {
+            "step": self.step_count, "loss_scale": self.loss_scale, "zero1": self.zero1,
+            "buffers": [{"expert": b.expert, "weight_decay": b.weight_decay, "shard": b.shard, "numel": b.numel,
+                         "names": [s.name for s in b.slots],
+                         "master": None if b.master is None else b.master.cpu(),
+                         "exp_avg": b.exp_avg.cpu(), "exp_avg_sq": b.exp_avg_sq.cpu()} for b in self.buffers],
+        }
+
+    def load_state_dict(self, sd: dict):
+        self.step_count = sd["step"]
+        self.loss_scale = sd.get("loss_scale", self.loss_scale)
+        assert len(sd["buffers"]) == len(self.buffers), "optimizer layout changed"
+        for b, s in zip(self.buffers, sd["buffers"]):
+            assert s["numel"] == b.numel and tuple(s["shard"]) == tuple(b.shard), \
+                "optimizer shard layout differs (use ckpt.reshard_optimizer for a new DP size)"
+            if b.master is not None and s["master"] is not None:
+                b.master.copy_(s["master"])
+            b.exp_avg.copy_(s["exp_avg"])
+            b.exp_avg_sq.copy_(s["exp_avg_sq"])
+
+
+class OptimizerParamScheduler:
+    """Learning-rate and weight-decay schedules (Megatron ``OptimizerParamScheduler``, reached by the
+    reference through training.py:30): linear warm-up then constant / linear / cosine /
+    inverse-square-root decay; constant / linear / cosine weight-decay increment."""
+
+    def __init__(self, tc: TrainConfig):
+        self.tc = tc
+        self.num_steps = 0
+        self.decay_steps = tc.lr_decay_iters if tc.lr_decay_iters is not None else tc.train_iters
+        self.warmup = tc.lr_warmup_iters
+        self.start_wd = tc.start_weight_decay if tc.start_weight_decay is not None else tc.weight_decay
+        self.end_wd = tc.end_weight_decay if tc.end_weight_decay is not None else tc.weight_decay
+
+    def get_lr(self) -> float:
+        tc, n = self.tc, self.num_steps
+        if self.warmup > 0 and n <= self.warmup:
+            return tc.lr_warmup_init + (tc.lr - tc.lr_warmup_init) * n / self.warmup
+        if tc.lr_decay_style == "constant":
+            return tc.lr
+        if n > self.decay_steps:
+            return tc.min_lr
+        if tc.lr_decay_style == "inverse-square-root":
+            w = max(self.warmup, 1)
+            return max(tc.min_lr, tc.lr * math.sqrt(w) / math.sqrt(max(n, 1)))
+        ratio = (n - self.warmup) / max(self.decay_steps - self.warmup, 1)
+        delta = tc.lr - tc.min_lr
+        if tc.lr_decay_style == "linear":
+            coeff = 1.0 - ratio
+        elif tc.lr_decay_style == "cosine":
+            coeff = 0.5 * (math.cos(math.pi * ratio) + 1.0)
+        else:
+            raise ValueError(tc.lr_decay_style)
+        return tc.min_lr + coeff * delta
+
+    def get_wd(self) -> float:
+        tc = self.tc
+        if tc.weight_decay_incr_style == "constant" or self.start_wd == self.end_wd:
+            return self.end_wd
+        ratio = min(self.num_steps / max(self.decay_steps, 1), 1.0)
+        if tc.weight_decay_incr_style == "linear":
+            coeff = ratio
+        elif tc.weight_decay_incr_style == "cosine":
+            coeff = 0.5 * (math.cos(math.pi * (1 - ratio)) + 1.0)
+        else:
+            raise ValueError(tc.weight_decay_incr_style)
+        return self.start_wd + coeff * (self.end_wd - self.start_wd)
+
+    def step(self, increment: int = 1):
+        self.num_steps += increment
+
+    def state_dict(self):
+        return {"num_steps": self.num_steps}
+
+    def load_state_dict(self, sd):
+        self.num_steps = sd["num_steps"]
