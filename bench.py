@@ -1,0 +1,205 @@
+"""Headline benchmark: training tokens/s of the LASP-2 Linear-Llama3-1B configuration.
+
+Model (benchmark configuration "LASP-2 long-sequence Linear-Llama3 1B dense"): 16 layers of lightning
+attention (per-head decay, chunk 64), hidden 2048, 16 heads x 128, SwiGLU ffn 8192, vocab 128256, bf16,
+micro-batch 1, sequence parallel over all N GPUs of the node with LASP-2.  Per-GPU work is fixed at
+16384 tokens (weak scaling): the sequence is 16384 x N, i.e. the named 131072-token sequence at N = 8.
+Synthetic uniform token ids, N(0, 0.02) random-init weights.  One step = forward + backward + gradient
+reduction over the sequence-parallel ranks + clip + Adam on fp32 masters.
+
+  python bench.py --gpus 1 --steps K --warmup W
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+      bench.py --gpus N --steps K --warmup W
+
+Rank 0 prints ONE JSON line.  ``value`` is device-timed (CUDA events, max over ranks) with the batch already
+on the device; ``e2e`` repeats the measurement through ``Trainer.train_step`` with, every step, the host->device
+copy of that step's tokens/labels/mask from pinned memory and a device->host read of the loss.
+``--impl reference`` would run the unmodified reference; it cannot be installed offline, so that arm prints why.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+TOKENS_PER_GPU = 16384
+METRIC = "train tokens/s per 8xB200 box (LASP-2 Linear-Llama3-1B, lightning attention, 16384 tokens per GPU, seq 131072 at 8 GPUs)"
+
+
+def parse():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=8)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
+    p.add_argument("--config", type=str, default="bench-lasp2-llama3-1b")
+    p.add_argument("--tokens-per-gpu", type=int, default=TOKENS_PER_GPU)
+    p.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (marks the result invalid)")
+    p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--zero1", action="store_true")
+    return p.parse_args()
+
+
+def reference_arm():
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "the reference is not installable offline: /root/reference has no setup.py/pyproject.toml and its "
+                       "engines (megatron-core, transformer_engine, flash-linear-attention submodules, mamba_ssm, "
+                       "grouped_gemm) are empty git links or absent from the image"}))
+    return 0
+
+
+class ClockSampler:
+    """nvidia-smi sampled every 200 ms while the timed region runs (read-only query)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc, self.idx = None, gpu_index
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(gpu_index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        return reference_arm()
+    import torch
+    import torch.distributed as dist
+    from linear_moe_b200.config.model_config import ParallelConfig, TrainConfig
+    from linear_moe_b200.config.presets import get_preset
+    from linear_moe_b200.dist.mesh import init_distributed
+    from linear_moe_b200.ops import cuda as K
+    from linear_moe_b200.parallel import fused_comm
+    from linear_moe_b200.train.loop import Trainer
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
+    par = ParallelConfig(context_parallel_size=world, use_distributed_optimizer=args.zero1, distributed_backend="nccl")
+    mesh = init_distributed(par)
+    dev = torch.device("cuda", torch.cuda.current_device())
+    overrides = {} if args.layers is None else {"num_layers": args.layers, "layer_type_list": "L" * args.layers}
+    cfg = get_preset(args.config, **overrides)
+    seq = args.tokens_per_gpu * world
+    tc = TrainConfig(micro_batch_size=1, global_batch_size=1, seq_length=seq, train_iters=10 ** 9, lr=1e-4, min_lr=1e-5,
+                     lr_decay_style="cosine", lr_decay_iters=100000, lr_warmup_iters=100, weight_decay=0.1,
+                     adam_beta1=0.9, adam_beta2=0.95, clip_grad=1.0, bf16=True, log_interval=10 ** 9, seed=1234,
+                     check_for_nan_in_loss_and_grad=False)
+    if world > 1:
+        fused_comm.init_workspaces(mesh, cfg, tc)
+    trainer = Trainer(cfg, par, tc, mesh, device=dev)
+    n_params = sum(p.numel() for p in trainer.model.parameters())
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(step_fn, steps):
+        sync()
+        K.reset_launch_count()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            step_fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            dist.barrier()
+        return float(ms) / steps, K.reset_launch_count() // max(steps, 1)
+
+    # ---- device-resident batches (kernel-side number) ---------------------------------------
+    resident = [next(trainer.data_iter) for _ in range(4)]
+    torch.cuda.synchronize()
+
+    class Cycle:
+        def __init__(self, items):
+            self.items, self.i = items, 0
+
+        def __iter__(self):
+            return self
+
+        def __next__(self):
+            self.i += 1
+            return self.items[self.i % len(self.items)]
+    real_iter = trainer.data_iter
+    trainer.data_iter = Cycle(resident)
+    for _ in range(max(args.warmup, 3)):
+        trainer.train_step()
+    sampler = ClockSampler(torch.cuda.current_device()) if mesh.rank == 0 else None
+    ms_dev, launches = timed(trainer.train_step, args.steps)
+    clocks = sampler.stop() if sampler is not None else None
+
+    # ---- end to end: pinned host batch -> device every step, loss read back every step ----------
+    e2e = None
+    if not args.no_e2e:
+        trainer.data_iter = real_iter
+        h2d = sum(v.numel() * v.element_size() for v in resident[0].values())
+        last = {}
+
+        def e2e_step():
+            st = trainer.train_step()                       # BatchIterator pins + copies this step's batch
+            last["loss"] = float(st["lm loss"]) if "lm loss" in st else 0.0   # device -> host read
+        for _ in range(2):
+            e2e_step()
+        ms_e2e, _ = timed(e2e_step, args.steps)
+        e2e = {"value": seq / (ms_e2e / 1000.0), "unit": "tokens/s", "ms_per_step": ms_e2e,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "last_loss": last.get("loss")}
+
+    if mesh.rank == 0:
+        out = {
+            "metric": METRIC, "value": seq / (ms_dev / 1000.0), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_dev, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
+            "impl": "ours",
+            "config": {"model": args.config, "global_batch": 1, "seq_len": seq, "tokens_per_gpu": args.tokens_per_gpu,
+                       "parallelism": f"sp{world} (LASP-2)" + (" zero1" if args.zero1 else ""), "params": n_params,
+                       "layers": cfg.num_layers, "l2": "inputs larger than L2 (16384x2048 bf16 activations, 3.3 GB weights)",
+                       "optimizer": "AdamW fp32 masters, clip 1.0", "valid": args.layers is None},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

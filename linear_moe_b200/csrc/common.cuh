@@ -1,0 +1,93 @@
+// Shared device helpers for the sm_100a kernels of linear_moe_b200.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define LMOE_API extern "C" __attribute__((visibility("default")))
+
+namespace lmoe {
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f(float x) { return x; }
+__device__ __forceinline__ float to_f(bf16 x) { return __bfloat162float(x); }
+template <typename T> __device__ __forceinline__ T from_f(float x);
+template <> __device__ __forceinline__ float from_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ bf16 from_f<bf16>(float x) { return __float2bfloat16(x); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum for blocks of up to 1024 threads; `red` is 32 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    int nw = (blockDim.x + 31) >> 5;
+    float r = (threadIdx.x < nw) ? red[threadIdx.x] : 0.f;
+    if (w == 0) r = warp_sum(r);
+    if (threadIdx.x == 0) red[0] = r;
+    __syncthreads();
+    r = red[0];
+    return r;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+    v = warp_max(v);
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) red[w] = v;
+    __syncthreads();
+    int nw = (blockDim.x + 31) >> 5;
+    float r = (threadIdx.x < nw) ? red[threadIdx.x] : -INFINITY;
+    if (w == 0) r = warp_max(r);
+    if (threadIdx.x == 0) red[0] = r;
+    __syncthreads();
+    r = red[0];
+    return r;
+}
+
+// 16-byte vector of 8 bf16 or 4 fp32, loaded/stored as one transaction.
+template <typename T> struct Vec;
+template <> struct Vec<bf16> {
+    static constexpr int N = 8;
+    uint4 raw;
+    __device__ __forceinline__ void load(const bf16* p) { raw = *reinterpret_cast<const uint4*>(p); }
+    __device__ __forceinline__ void store(bf16* p) const { *reinterpret_cast<uint4*>(p) = raw; }
+    __device__ __forceinline__ float get(int i) const {
+        const bf16* h = reinterpret_cast<const bf16*>(&raw);
+        return __bfloat162float(h[i]);
+    }
+    __device__ __forceinline__ void set(int i, float v) {
+        bf16* h = reinterpret_cast<bf16*>(&raw);
+        h[i] = __float2bfloat16(v);
+    }
+};
+template <> struct Vec<float> {
+    static constexpr int N = 4;
+    float4 raw;
+    __device__ __forceinline__ void load(const float* p) { raw = *reinterpret_cast<const float4*>(p); }
+    __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = raw; }
+    __device__ __forceinline__ float get(int i) const { return reinterpret_cast<const float*>(&raw)[i]; }
+    __device__ __forceinline__ void set(int i, float v) { reinterpret_cast<float*>(&raw)[i] = v; }
+};
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
+// d/dx [x * sigmoid(x)]
+__device__ __forceinline__ float dsilu_f(float x) {
+    float s = sigmoid_f(x);
+    return s * (1.f + x * (1.f - s));
+}
+
+}  // namespace lmoe

@@ -1,0 +1,636 @@
+"""CUDA back end of :mod:`linear_moe_b200.ops`: ctypes bindings of ``lib/liblmoe.so`` wrapped in
+``torch.autograd.Function``s.
+
+The library is plain C ABI (no torch headers): every entry point takes raw device pointers, sizes and
+the CUDA stream, so a call costs one ctypes dispatch and launches on torch's current stream.  A missing
+library is an error on a machine with a GPU (no silent fallback to eager).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+from ..ref import ops as R
+from . import lsm_torch as LT
+
+_LIB: Optional[ctypes.CDLL] = None
+NUM_SMS = 148
+launch_count = 0          # kernels of this library launched since the last reset (bench.py reports it)
+
+
+def lib_path() -> str:
+    return os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "lib", "liblmoe.so")
+
+
+def lib() -> ctypes.CDLL:
+    global _LIB
+    if _LIB is None:
+        p = lib_path()
+        if not os.path.exists(p):
+            raise RuntimeError(f"{p} is missing: run `python -m linear_moe_b200.build` (nvcc, sm_100a) first")
+        _LIB = ctypes.CDLL(p)
+    return _LIB
+
+
+def reset_launch_count() -> int:
+    global launch_count
+    n, launch_count = launch_count, 0
+    return n
+
+
+def _p(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _st():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.bfloat16:
+        return 1
+    if t.dtype == torch.float32:
+        return 0
+    raise TypeError(f"unsupported dtype {t.dtype} (bf16 and fp32 kernels only)")
+
+
+def _check(rc: int, name: str, n: int = 1):
+    global launch_count
+    if rc != 0:
+        raise RuntimeError(f"{name} failed with code {rc}")
+    launch_count += n
+
+
+_i64, _i32, _f32 = ctypes.c_int64, ctypes.c_int, ctypes.c_float
+
+
+def _same_dtype(x, *ts):
+    return [None if t is None else (t if t.dtype == x.dtype else t.to(x.dtype)) for t in ts]
+
+
+# =====================================================================================
+# GEMM-shaped (cuBLAS for the plain ones; the fused tcgen05 variants live in gemm.py)
+# =====================================================================================
+def linear(x, weight, bias=None):
+    return F.linear(x, weight if weight.dtype == x.dtype else weight.to(x.dtype),
+                    None if bias is None else bias.to(x.dtype))
+
+
+def linear_swiglu(x, weight):
+    from . import gemm
+    if gemm.available() and gemm.supports_swiglu(x, weight):
+        return gemm.LinearSwiGLU.apply(x, weight)
+    return swiglu(F.linear(x, weight))
+
+
+def fused_tp_available(group) -> bool:
+    from ..parallel import fused_comm
+    return fused_comm.tp_workspace(group) is not None
+
+
+def fused_lasp_available(group, q, k, v, g) -> bool:
+    from ..parallel import fused_comm
+    if fused_comm.lasp_workspace(group) is None:
+        return False
+    D = q.shape[-1]
+    return (q.dtype == torch.bfloat16 and D == v.shape[-1] and D in (64, 128)
+            and (g is None or g.dim() == 1))
+
+
+def fused_moe_available(mesh) -> bool:
+    return False
+
+
+def lasp2_scalar(q, k, v, g, scale, group, chunk_size):
+    from ..parallel import fused_comm
+    return fused_comm.lasp2_scalar(q, k, v, g, scale, group)
+
+
+def allgather_linear(x, weight, bias, group, dim):
+    from ..parallel import fused_comm
+    return fused_comm.allgather_linear(x, weight, bias, group, dim)
+
+
+def linear_reducescatter(x, weight, group, dim):
+    from ..parallel import fused_comm
+    return fused_comm.linear_reducescatter(x, weight, group, dim)
+
+
+# =====================================================================================
+# RMSNorm (+ residual add)
+# =====================================================================================
+_PARTIAL_BLOCKS = NUM_SMS * 4
+
+
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, residual, weight, eps, want_residual):
+        N = x.shape[-1]
+        xc = x.contiguous()
+        rc = None if residual is None else residual.contiguous()
+        (w,) = _same_dtype(xc, weight)
+        rows = xc.numel() // N
+        y = torch.empty_like(xc)
+        res_out = torch.empty_like(xc) if rc is not None else None
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        _check(lib().lmoe_rms_norm_fwd(_p(xc), _p(rc), _p(w), _p(y), _p(res_out), _p(rstd), _i64(rows), _i32(N),
+                                       _f32(eps), _i32(_dt(xc)), _st()), "rms_norm_fwd")
+        xin = res_out if rc is not None else xc
+        ctx.save_for_backward(xin, w, rstd)
+        ctx.has_res, ctx.wdtype = rc is not None, None if weight is None else weight.dtype
+        if want_residual:
+            return y, xin
+        return y
+
+    @staticmethod
+    def backward(ctx, dy, dres=None):
+        xin, w, rstd = ctx.saved_tensors
+        N = xin.shape[-1]
+        rows = xin.numel() // N
+        dy = dy.contiguous()
+        dres = None if dres is None else dres.contiguous()
+        dx = torch.empty_like(xin)
+        P = min(rows, _PARTIAL_BLOCKS)
+        partial = torch.empty(P, N, dtype=torch.float32, device=xin.device) if w is not None else None
+        dw = torch.empty(N, dtype=xin.dtype, device=xin.device) if w is not None else None
+        _check(lib().lmoe_rms_norm_bwd(_p(dy), _p(xin), _p(w), _p(rstd), _p(dres), _p(dx), _p(partial), _p(dw),
+                                       _i64(rows), _i32(N), _i32(P), _i32(_dt(xin)), _st()), "rms_norm_bwd", 2)
+        if dw is not None and ctx.wdtype != dw.dtype:
+            dw = dw.to(ctx.wdtype)
+        return dx, (dx if ctx.has_res else None), dw, None, None
+
+
+def _rms_ok(x):
+    N = x.shape[-1]
+    vn = 8 if x.dtype == torch.bfloat16 else 4
+    return x.dtype in (torch.bfloat16, torch.float32) and N % vn == 0 and N // vn <= 2048
+
+
+def rms_norm(x, weight=None, eps: float = 1e-6):
+    if not _rms_ok(x):
+        return R.rms_norm(x, weight, eps)
+    return _RMSNorm.apply(x, None, weight, eps, False)
+
+
+def add_rms_norm(x, residual, weight, eps: float = 1e-6):
+    if not _rms_ok(x):
+        r = x + residual
+        return R.rms_norm(r, weight, eps), r
+    return _RMSNorm.apply(x, residual, weight, eps, True)
+
+
+# =====================================================================================
+# per-head norm + swish gate
+# =====================================================================================
+class _HeadNormGate(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, o, weight, gate, eps, do_norm):
+        B, T, H, D = o.shape
+        oc, gc = o.contiguous(), gate.contiguous()
+        (w,) = _same_dtype(oc, weight)
+        rows = B * T * H
+        y = torch.empty(B, T, H * D, dtype=o.dtype, device=o.device)
+        rstd = torch.empty(rows if do_norm else 1, dtype=torch.float32, device=o.device)
+        _check(lib().lmoe_head_norm_gate_fwd(_p(oc), _p(w), _p(gc), _p(y), _p(rstd), _i64(rows), _i32(D), _f32(eps),
+                                             _i32(int(do_norm)), _i32(_dt(oc)), _st()), "head_norm_gate_fwd")
+        ctx.save_for_backward(oc, w, gc, rstd)
+        ctx.do_norm, ctx.wdtype = do_norm, None if weight is None else weight.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        oc, w, gc, rstd = ctx.saved_tensors
+        B, T, H, D = oc.shape
+        rows = B * T * H
+        dy = dy.contiguous()
+        d_o, dgate = torch.empty_like(oc), torch.empty_like(gc)
+        need_dw = w is not None and ctx.do_norm
+        P = min((rows + 7) // 8, NUM_SMS * 2)
+        partial = torch.empty(P, D, dtype=torch.float32, device=oc.device) if need_dw else None
+        dw = torch.empty(D, dtype=oc.dtype, device=oc.device) if need_dw else None
+        _check(lib().lmoe_head_norm_gate_bwd(_p(dy), _p(oc), _p(w), _p(gc), _p(rstd), _p(d_o), _p(dgate), _p(partial),
+                                             _p(dw), _i64(rows), _i32(D), _i32(int(ctx.do_norm)), _i32(P),
+                                             _i32(_dt(oc)), _st()), "head_norm_gate_bwd", 2)
+        if dw is not None and ctx.wdtype != dw.dtype:
+            dw = dw.to(ctx.wdtype)
+        return d_o, dw, dgate, None, None
+
+
+def head_norm_gate(o, weight, gate, eps, do_norm: bool):
+    if o.shape[-1] > 512 or o.dtype not in (torch.bfloat16, torch.float32) or gate.dtype != o.dtype:
+        y = R.rms_norm(o, weight, eps) if do_norm else o
+        B, T = o.shape[:2]
+        return (y.reshape(B, T, -1).float() * F.silu(gate.float())).to(o.dtype)
+    return _HeadNormGate.apply(o, weight if do_norm else None, gate, eps, do_norm)
+
+
+# =====================================================================================
+# gated RMSNorm (Mamba2)
+# =====================================================================================
+class _GatedRMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, z, weight, eps, G):
+        N = x.shape[-1]
+        xc, zc = x.contiguous(), z.contiguous()
+        (w,) = _same_dtype(xc, weight)
+        rows = xc.numel() // N
+        y = torch.empty_like(xc)
+        rstd = torch.empty(rows * (N // G), dtype=torch.float32, device=x.device)
+        _check(lib().lmoe_gated_rms_norm_fwd(_p(xc), _p(zc), _p(w), _p(y), _p(rstd), _i64(rows), _i32(N), _i32(G),
+                                             _f32(eps), _i32(_dt(xc)), _st()), "gated_rms_norm_fwd")
+        ctx.save_for_backward(xc, zc, w, rstd)
+        ctx.G, ctx.wdtype = G, weight.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xc, zc, w, rstd = ctx.saved_tensors
+        N = xc.shape[-1]
+        rows = xc.numel() // N
+        dx, dz = torch.empty_like(xc), torch.empty_like(zc)
+        dw = torch.zeros(N, dtype=torch.float32, device=xc.device)
+        _check(lib().lmoe_gated_rms_norm_bwd(_p(dy.contiguous()), _p(xc), _p(zc), _p(w), _p(rstd), _p(dx), _p(dz),
+                                             _p(dw), _i64(rows), _i32(N), _i32(ctx.G), _i32(_dt(xc)), _st()),
+               "gated_rms_norm_bwd")
+        return dx, dz, dw.to(ctx.wdtype), None, None
+
+
+def gated_rms_norm(x, z, weight, eps=1e-5, group_size=None):
+    if x.dtype not in (torch.bfloat16, torch.float32) or z.dtype != x.dtype:
+        return R.gated_rms_norm(x, z, weight, eps, group_size)
+    return _GatedRMSNorm.apply(x, z, weight, eps, group_size or x.shape[-1])
+
+
+# =====================================================================================
+# SwiGLU, l2norm, rotary
+# =====================================================================================
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x):
+        F2 = x.shape[-1]
+        xc = x.contiguous()
+        rows = xc.numel() // F2
+        y = torch.empty(*x.shape[:-1], F2 // 2, dtype=x.dtype, device=x.device)
+        _check(lib().lmoe_swiglu_fwd(_p(xc), _p(y), _i64(rows), _i32(F2 // 2), _i32(_dt(xc)), _st()), "swiglu_fwd")
+        ctx.save_for_backward(xc)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (xc,) = ctx.saved_tensors
+        F2 = xc.shape[-1]
+        dx = torch.empty_like(xc)
+        _check(lib().lmoe_swiglu_bwd(_p(dy.contiguous()), _p(xc), _p(dx), _i64(xc.numel() // F2), _i32(F2 // 2),
+                                     _i32(_dt(xc)), _st()), "swiglu_bwd")
+        return dx
+
+
+def swiglu(x):
+    vn = 8 if x.dtype == torch.bfloat16 else 4
+    if x.dtype not in (torch.bfloat16, torch.float32) or (x.shape[-1] // 2) % vn != 0:
+        return R.swiglu(x)
+    return _SwiGLU.apply(x)
+
+
+class _L2Norm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, eps):
+        D = x.shape[-1]
+        xc = x.contiguous()
+        rows = xc.numel() // D
+        y = torch.empty_like(xc)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        _check(lib().lmoe_l2norm_fwd(_p(xc), _p(y), _p(rstd), _i64(rows), _i32(D), _f32(eps), _i32(_dt(xc)), _st()),
+               "l2norm_fwd")
+        ctx.save_for_backward(xc, rstd)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xc, rstd = ctx.saved_tensors
+        D = xc.shape[-1]
+        dx = torch.empty_like(xc)
+        _check(lib().lmoe_l2norm_bwd(_p(dy.contiguous()), _p(xc), _p(rstd), _p(dx), _i64(xc.numel() // D), _i32(D),
+                                     _i32(_dt(xc)), _st()), "l2norm_bwd")
+        return dx, None
+
+
+def l2_norm(x, eps: float = 1e-6):
+    if x.shape[-1] > 512 or x.dtype not in (torch.bfloat16, torch.float32):
+        return R.l2_norm(x, eps)
+    return _L2Norm.apply(x, eps)
+
+
+class _Rope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin, interleaved):
+        B, T, H, D = x.shape
+        xc = x.contiguous()
+        cs, sn = cos.float().contiguous(), sin.float().contiguous()
+        y = torch.empty_like(xc)
+        Rr = cs.shape[-1] * 2
+        _check(lib().lmoe_rope(_p(xc), _p(cs), _p(sn), _p(y), _i64(B * T), _i32(T), _i32(H), _i32(D), _i32(Rr),
+                               _i32(int(interleaved)), _i32(0), _i32(_dt(xc)), _st()), "rope_fwd")
+        ctx.save_for_backward(cs, sn)
+        ctx.interleaved = interleaved
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        cs, sn = ctx.saved_tensors
+        B, T, H, D = dy.shape
+        dyc = dy.contiguous()
+        dx = torch.empty_like(dyc)
+        _check(lib().lmoe_rope(_p(dyc), _p(cs), _p(sn), _p(dx), _i64(B * T), _i32(T), _i32(H), _i32(D),
+                               _i32(cs.shape[-1] * 2), _i32(int(ctx.interleaved)), _i32(1), _i32(_dt(dyc)), _st()),
+               "rope_bwd")
+        return dx, None, None, None
+
+
+def apply_rope(x, cos, sin, interleaved=False):
+    if x.dtype not in (torch.bfloat16, torch.float32):
+        return R.apply_rope(x, cos, sin, interleaved)
+    return _Rope.apply(x, cos, sin, interleaved)
+
+
+# =====================================================================================
+# softmax cross entropy on a chunk of logits
+# =====================================================================================
+def softmax_ce_fwd(logits, labels, loss_out, lse_out, ignore_index):
+    rows, V = logits.shape
+    logits = logits.contiguous()
+    _check(lib().lmoe_softmax_ce_fwd(_p(logits), _p(labels.contiguous()), _p(loss_out), _p(lse_out), _i64(rows), _i32(V),
+                                     _i64(ignore_index), _i32(_dt(logits)), _st()), "softmax_ce_fwd")
+
+
+def softmax_ce_bwd(logits, labels, lse, gloss, ignore_index):
+    """Overwrites ``logits`` with the gradient and returns it."""
+    rows, V = logits.shape
+    _check(lib().lmoe_softmax_ce_bwd(_p(logits), _p(labels.contiguous()), _p(lse), _p(gloss), _p(logits), _i64(rows),
+                                     _i32(V), _i64(ignore_index), _i32(_dt(logits)), _st()), "softmax_ce_bwd")
+    return logits
+
+
+# =====================================================================================
+# causal conv1d
+# =====================================================================================
+class _CausalConv1d(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, init, act):
+        B, T, D = x.shape
+        K = weight.shape[-1]
+        xc = x.contiguous()
+        w, b, ini = _same_dtype(xc, weight.contiguous(), bias, None if init is None else init.contiguous())
+        y = torch.empty_like(xc)
+        _check(lib().lmoe_causal_conv1d_fwd(_p(xc), _p(w), _p(b), _p(ini), _p(y), _i32(B), _i32(T), _i32(D), _i32(K),
+                                            _i32(int(act)), _i32(_dt(xc)), _st()), "causal_conv1d_fwd")
+        ctx.save_for_backward(xc, w, b, ini)
+        ctx.act, ctx.wdtype, ctx.bdtype = act, weight.dtype, None if bias is None else bias.dtype
+        # final state: the last K-1 inputs (including the entering state when T < K-1)
+        if ini is not None:
+            tail = torch.cat([ini, xc], dim=1)[:, -(K - 1):]
+        else:
+            tail = F.pad(xc, (0, 0, max(K - 1 - T, 0), 0))[:, -(K - 1):]
+        ctx.mark_non_differentiable(tail)
+        return y, tail
+
+    @staticmethod
+    def backward(ctx, dy, _dtail):
+        xc, w, b, ini = ctx.saved_tensors
+        B, T, D = xc.shape
+        K = w.shape[-1]
+        dx = torch.empty_like(xc)
+        dw = torch.zeros(D, K, dtype=torch.float32, device=xc.device)
+        db = torch.zeros(D, dtype=torch.float32, device=xc.device) if b is not None else None
+        dini = torch.empty_like(ini) if ini is not None else None
+        _check(lib().lmoe_causal_conv1d_bwd(_p(dy.contiguous()), _p(xc), _p(w), _p(b), _p(ini), _p(dx), _p(dw), _p(db),
+                                            _p(dini), _i32(B), _i32(T), _i32(D), _i32(K), _i32(int(ctx.act)),
+                                            _i32(_dt(xc)), _st()), "causal_conv1d_bwd")
+        return dx, dw.to(ctx.wdtype), None if db is None else db.to(ctx.bdtype), dini, None
+
+
+def causal_conv1d(x, weight, bias=None, activation="silu", initial_state=None):
+    K = weight.shape[-1]
+    if x.dtype not in (torch.bfloat16, torch.float32) or K not in (2, 3, 4):
+        return R.causal_conv1d(x, weight, bias, activation, initial_state)
+    return _CausalConv1d.apply(x, weight, bias, initial_state, activation in ("silu", "swish"))
+
+
+# =====================================================================================
+# router
+# =====================================================================================
+class _RouterTopK(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, k, order):
+        T, E = logits.shape
+        lf = logits.float().contiguous()
+        full = torch.empty_like(lf)
+        probs = torch.empty(T, k, dtype=torch.float32, device=lf.device)
+        idx = torch.empty(T, k, dtype=torch.int64, device=lf.device)
+        _check(lib().lmoe_router_topk(_p(lf), _p(full), _p(probs), _p(idx), _p(None), _i64(T), _i32(E), _i32(k),
+                                      _i32(1 if order == "topk_softmax" else 0), _st()), "router_topk")
+        ctx.save_for_backward(full, probs, idx)
+        ctx.order, ctx.dtype = order, logits.dtype
+        ctx.mark_non_differentiable(idx)
+        return probs, idx, full
+
+    @staticmethod
+    def backward(ctx, dprobs, _didx, dfull):
+        full, probs, idx = ctx.saved_tensors
+        if ctx.order == "softmax_topk":
+            g = dfull.clone() if dfull is not None else torch.zeros_like(full)
+            if dprobs is not None:
+                g.scatter_add_(1, idx, dprobs)
+            dl = full * (g - (g * full).sum(-1, keepdim=True))
+        else:
+            dl = torch.zeros_like(full)
+            if dfull is not None:
+                dl = full * (dfull - (dfull * full).sum(-1, keepdim=True))
+            if dprobs is not None:
+                dsel = probs * (dprobs - (dprobs * probs).sum(-1, keepdim=True))
+                dl.scatter_add_(1, idx, dsel)
+        return dl.to(ctx.dtype), None, None
+
+
+def router_topk(logits, k, order="softmax_topk"):
+    if logits.shape[-1] > 256 or k > 16:
+        return R.router_topk(logits, k, order)
+    return _RouterTopK.apply(logits, k, order)
+
+
+def grouped_mlp(x_sorted, tokens_per_expert, w1, w2):
+    from . import gemm
+    if gemm.available() and gemm.supports_grouped(x_sorted, w1, w2):
+        return gemm.grouped_mlp(x_sorted, tokens_per_expert, w1, w2)
+    outs, start = [], 0
+    counts = tokens_per_expert.tolist()
+    for e, n in enumerate(counts):
+        xe = x_sorted[start:start + n]
+        outs.append(swiglu(xe @ w1[e]) @ w2[e])
+        start += n
+    return torch.cat(outs, 0)
+
+
+# =====================================================================================
+# attention
+# =====================================================================================
+def flash_attention(q, k, v, scale, causal, q_offset, window):
+    from . import attention
+    return attention.flash_attention(q, k, v, scale, causal, q_offset, window)
+
+
+# =====================================================================================
+# fused Adam
+# =====================================================================================
+def fused_adam(p, master, g, m, v, lr, b1, b2, eps, wd, bc1, bc2, gscale):
+    n = p.numel()
+    _check(lib().lmoe_fused_adam(_p(p), _p(master), _p(g), _p(m), _p(v), _i64(n), _f32(lr), _f32(b1), _f32(b2), _f32(eps),
+                                 _f32(wd), _f32(bc1), _f32(bc2), _f32(gscale), _i32(_dt(p)), _st()), "fused_adam")
+
+
+def accumulate_grad(acc, g):
+    _check(lib().lmoe_accumulate_grad(_p(acc), _p(g), _i64(g.numel()), _i32(_dt(g)), _st()), "accumulate_grad")
+
+
+# =====================================================================================
+# linear sequence models
+# =====================================================================================
+class _LsmArgs(ctypes.Structure):
+    _fields_ = ([(n, ctypes.c_void_p) for n in ("q", "k", "v", "d_o")] +
+                [(n, ctypes.c_int64) for n in ("qs_b", "qs_t", "qs_h", "ks_b", "ks_t", "ks_h", "vs_b", "vs_t", "vs_h")] +
+                [(n, ctypes.c_void_p) for n in ("o", "dq", "dk", "dv")] +
+                [(n, ctypes.c_int64) for n in ("dqs_b", "dqs_t", "dqs_h", "dks_b", "dks_t", "dks_h", "dvs_b", "dvs_t", "dvs_h")] +
+                [("g", ctypes.c_void_p), ("gmode", ctypes.c_int), ("scale", ctypes.c_float)] +
+                [(n, ctypes.c_int) for n in ("B", "T", "H", "G", "cpg")] +
+                [("states", ctypes.c_void_p), ("gdecay", ctypes.c_void_p)])
+
+
+def _inner_contig(t):
+    """Kernels need unit stride in the last dim and 16-byte aligned rows; other strides are free."""
+    if t.stride(-1) != 1 or any(s % 8 for s in t.stride()[:-1]) or t.data_ptr() % 16:
+        return t.contiguous()
+    return t
+
+
+def lsm_groups(B, H, T):
+    nchunks = (T + 63) // 64
+    G = max(1, min(nchunks, NUM_SMS // max(B * H, 1)))
+    cpg = (nchunks + G - 1) // G
+    G = (nchunks + cpg - 1) // cpg
+    return G, cpg
+
+
+def _lsm_args(q, k, v, g, gmode, scale, B, T, H, G, cpg, states, gdecay, d_o=None, o=None, dq=None, dk=None, dv=None):
+    a = _LsmArgs()
+    a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    a.d_o = 0 if d_o is None else d_o.data_ptr()
+    a.qs_b, a.qs_t, a.qs_h = q.stride(0), q.stride(1), q.stride(2)
+    a.ks_b, a.ks_t, a.ks_h = k.stride(0), k.stride(1), k.stride(2)
+    a.vs_b, a.vs_t, a.vs_h = v.stride(0), v.stride(1), v.stride(2)
+    a.o = 0 if o is None else o.data_ptr()
+    for name, t in (("dq", dq), ("dk", dk), ("dv", dv)):
+        setattr(a, name, 0 if t is None else t.data_ptr())
+        if t is not None:
+            setattr(a, name + "s_b", t.stride(0)), setattr(a, name + "s_t", t.stride(1)), setattr(a, name + "s_h", t.stride(2))
+    a.g = 0 if g is None else g.data_ptr()
+    a.gmode, a.scale = gmode, float(scale)
+    a.B, a.T, a.H, a.G, a.cpg = B, T, H, G, cpg
+    a.states = states.data_ptr()
+    a.gdecay = 0 if gdecay is None else gdecay.data_ptr()
+    return a
+
+
+def _lsm_launch(which, D, args):
+    _check(lib().lmoe_lsm_scalar_launch(_i32(which), _i32(D), ctypes.byref(args), _st()), f"lsm_scalar[{which}]")
+
+
+def _lsm_combine(rev, states, gdecay, gconst, seed, final_out, BH, H, G, cpg, T, D):
+    _check(lib().lmoe_lsm_scalar_combine(_i32(rev), _p(states), _p(gdecay), _p(gconst), _p(seed), _p(final_out), _i32(BH),
+                                         _i32(H), _i32(G), _i32(cpg), _i32(T), _i32(D), _st()), "lsm_scalar_combine")
+
+
+class _LsmScalar(torch.autograd.Function):
+    """o, S_T = scalar-decay linear attention.  q,k,v bf16 [B,T,H,D]; g None | [H] | [B,T,H] fp32."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, scale, init):
+        B, T, H, D = q.shape
+        q, k, v = _inner_contig(q), _inner_contig(k), _inner_contig(v)
+        gmode = 0 if g is None else (1 if g.dim() == 1 else 2)
+        gf = None if g is None else g.float().contiguous()
+        G, cpg = lsm_groups(B, H, T)
+        states = torch.empty(B, H, G, D, D, dtype=torch.float32, device=q.device)
+        gdecay = torch.empty(B, H, G, dtype=torch.float32, device=q.device) if gmode == 2 else None
+        o = torch.empty(B, T, H, D, dtype=q.dtype, device=q.device)
+        final = torch.empty(B, H, D, D, dtype=torch.float32, device=q.device)
+        seed = None if init is None else init.float().contiguous()
+        a = _lsm_args(q, k, v, gf, gmode, scale, B, T, H, G, cpg, states, gdecay, o=o)
+        _lsm_launch(0, D, a)
+        _lsm_combine(0, states, gdecay, gf if gmode == 1 else None, seed, final, B * H, H, G, cpg, T, D)
+        _lsm_launch(2, D, a)
+        ctx.save_for_backward(q, k, v, gf, states, gdecay, final)
+        ctx.scale, ctx.gmode, ctx.grid, ctx.has_init = scale, gmode, (G, cpg), init is not None
+        ctx.g_dtype = None if g is None else g.dtype
+        return o, final
+
+    @staticmethod
+    def backward(ctx, d_o, dfinal):
+        q, k, v, gf, states, gdecay, final = ctx.saved_tensors
+        B, T, H, D = q.shape
+        G, cpg = ctx.grid
+        d_o = d_o.contiguous()
+        if d_o.dtype != q.dtype:
+            d_o = d_o.to(q.dtype)
+        # dq | dk | dv are written straight into one [B,T,H,3D] buffer: when q,k,v were views of a fused
+        # projection, autograd's concatenation of the three gradients becomes a no-op copy
+        dqkv = torch.empty(B, T, H, 3 * D, dtype=q.dtype, device=q.device)
+        dq, dk, dv = dqkv[..., :D], dqkv[..., D:2 * D], dqkv[..., 2 * D:]
+        dstates = torch.empty_like(states)
+        dinit = torch.empty(B, H, D, D, dtype=torch.float32, device=q.device) if ctx.has_init else None
+        # forward-direction sweep: dq (entering states of every group are still in `states`)
+        a = _lsm_args(q, k, v, gf, ctx.gmode, ctx.scale, B, T, H, G, cpg, states, gdecay, d_o=d_o, dq=dq)
+        _lsm_launch(3, D, a)
+        # reverse-direction: group summaries of dS, suffix combine, dk/dv sweep
+        a2 = _lsm_args(q, k, v, gf, ctx.gmode, ctx.scale, B, T, H, G, cpg, dstates, None, d_o=d_o, dk=dk, dv=dv)
+        _lsm_launch(1, D, a2)
+        seed = None if dfinal is None else dfinal.float().contiguous()
+        _lsm_combine(1, dstates, gdecay, gf if ctx.gmode == 1 else None, seed, dinit, B * H, H, G, cpg, T, D)
+        _lsm_launch(4, D, a2)
+        dg = None
+        if ctx.gmode == 2:
+            # dg_t = sum_{i>=t} q_i.dq_i - sum_{j>=t} k_j.dk_j (+ <S_T, dS_T> when the final state has a gradient)
+            s = (q.float() * dq.float()).sum(-1) - (k.float() * dk.float()).sum(-1)
+            dg = s.flip(1).cumsum(1).flip(1)
+            if dfinal is not None:
+                dg = dg + (final * dfinal.float()).sum((-1, -2))[:, None, :]
+            dg = dg.to(ctx.g_dtype)
+        elif ctx.gmode == 1 and ctx.needs_input_grad[3]:
+            s = (q.float() * dq.float()).sum(-1) - (k.float() * dk.float()).sum(-1)
+            dgt = s.flip(1).cumsum(1).flip(1)
+            if dfinal is not None:
+                dgt = dgt + (final * dfinal.float()).sum((-1, -2))[:, None, :]
+            dg = dgt.sum((0, 1)).to(ctx.g_dtype)
+        return dq, dk, dv, dg, None, dinit
+
+
+def lsm_scalar(q, k, v, g, scale, initial_state, chunk_size):
+    D = q.shape[-1]
+    ok = (q.dtype == torch.bfloat16 and k.dtype == q.dtype and v.dtype == q.dtype and v.shape[-1] == D
+          and k.shape[-1] == D and D in (64, 128))
+    if not ok:
+        return LT.chunk_scalar_gated(q, k, v, g, scale, initial_state, chunk_size)
+    scale = D ** -0.5 if scale is None else scale
+    return _LsmScalar.apply(q, k, v, g, scale, initial_state)
+
+
+def lsm_vector(q, k, v, gk, scale, initial_state, bonus, chunk_size):
+    return LT.chunk_vector_gated(q, k, v, gk, scale, initial_state, 16, bonus)
+
+
+def lsm_delta(q, k, v, beta, g, scale, initial_state, chunk_size):
+    return LT.chunk_delta_rule(q, k, v, beta, g, scale, initial_state, chunk_size)

@@ -1,0 +1,227 @@
+"""CUDA kernels against the plain fp32 PyTorch definition of the same operator."""
+import math
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+from linear_moe_b200 import ops
+from linear_moe_b200.ops import lsm_torch as LT
+from linear_moe_b200.ref import ops as R
+
+
+def dev():
+    return torch.device("cuda", 0)
+
+
+def close(a, b, rtol, atol, name=""):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    ref = b.abs().max().item()
+    assert torch.allclose(a, b, rtol=rtol, atol=atol), f"{name}: max abs err {err:.4e} (ref max {ref:.4e})"
+
+
+def grads(fn, inputs, gout):
+    ins = [t.detach().clone().requires_grad_(True) for t in inputs]
+    out = fn(*ins)
+    outs = out if isinstance(out, (tuple, list)) else (out,)
+    g = gout if isinstance(gout, (tuple, list)) else (gout,)
+    torch.autograd.backward([o for o, gg in zip(outs, g) if gg is not None], [gg for gg in g if gg is not None])
+    return outs, [t.grad for t in ins]
+
+
+@pytest.mark.parametrize("N,rows", [(2048, 300), (128, 1000), (4096, 64), (1024, 33)])
+@pytest.mark.parametrize("residual", [False, True])
+def test_rms_norm(N, rows, residual):
+    torch.manual_seed(0)
+    x = torch.randn(rows, N, device=dev(), dtype=torch.bfloat16)
+    r = torch.randn(rows, N, device=dev(), dtype=torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(N, device=dev())).to(torch.bfloat16)
+    gy = torch.randn(rows, N, device=dev(), dtype=torch.bfloat16)
+    gr = torch.randn(rows, N, device=dev(), dtype=torch.bfloat16)
+    if residual:
+        f_k = lambda x, r, w: ops.add_rms_norm(x, r, w, 1e-6)
+        f_r = lambda x, r, w: (R.rms_norm(x + r, w, 1e-6), x + r)
+        (y, ro), gk = grads(f_k, [x, r, w], (gy, gr))
+        (y2, ro2), gr_ = grads(f_r, [x.float(), r.float(), w.float()], (gy.float(), gr.float()))
+        close(ro, ro2, 1e-2, 1e-2, "residual out")
+    else:
+        f_k = lambda x, w: ops.rms_norm(x, w, 1e-6)
+        f_r = lambda x, w: R.rms_norm(x, w, 1e-6)
+        (y,), gk = grads(f_k, [x, w], gy)
+        (y2,), gr_ = grads(f_r, [x.float(), w.float()], gy.float())
+    close(y, y2, 2e-2, 2e-2, "y")
+    close(gk[0], gr_[0], 3e-2, 3e-2, "dx")
+    close(gk[-1], gr_[-1], 3e-2, 0.02 * math.sqrt(rows), "dw")
+
+
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("norm", [True, False])
+def test_head_norm_gate(D, norm):
+    torch.manual_seed(1)
+    B, T, H = 2, 100, 4
+    o = torch.randn(B, T, H, D, device=dev(), dtype=torch.bfloat16)
+    g = torch.randn(B, T, H * D, device=dev(), dtype=torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(D, device=dev())).to(torch.bfloat16)
+    gy = torch.randn(B, T, H * D, device=dev(), dtype=torch.bfloat16)
+
+    def ref(o, w, g):
+        y = R.rms_norm(o, w, 1e-5) if norm else o
+        return y.reshape(B, T, -1) * F.silu(g)
+    (y,), gk = grads(lambda o, w, g: ops.head_norm_gate(o, w, g, 1e-5, "swish", "rmsnorm" if norm else "identity"),
+                     [o, w, g], gy)
+    (y2,), gr = grads(ref, [o.float(), w.float(), g.float()], gy.float())
+    close(y, y2, 2e-2, 2e-2, "y")
+    close(gk[0], gr[0], 3e-2, 3e-2, "do")
+    close(gk[2], gr[2], 3e-2, 3e-2, "dgate")
+    if norm:
+        close(gk[1], gr[1], 3e-2, 0.5, "dw")
+
+
+def test_gated_rms_norm():
+    torch.manual_seed(2)
+    rows, N, G = 200, 512, 128
+    x = torch.randn(rows, N, device=dev(), dtype=torch.bfloat16)
+    z = torch.randn(rows, N, device=dev(), dtype=torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(N, device=dev())).to(torch.bfloat16)
+    gy = torch.randn(rows, N, device=dev(), dtype=torch.bfloat16)
+    (y,), gk = grads(lambda x, z, w: ops.gated_rms_norm(x, z, w, 1e-5, G), [x, z, w], gy)
+    (y2,), gr = grads(lambda x, z, w: R.gated_rms_norm(x, z, w, 1e-5, G), [x.float(), z.float(), w.float()], gy.float())
+    close(y, y2, 2e-2, 2e-2, "y")
+    close(gk[0], gr[0], 3e-2, 3e-2, "dx")
+    close(gk[1], gr[1], 3e-2, 3e-2, "dz")
+    close(gk[2], gr[2], 3e-2, 0.3, "dw")
+
+
+def test_swiglu_l2norm_rope():
+    torch.manual_seed(3)
+    x = torch.randn(300, 2 * 1408, device=dev(), dtype=torch.bfloat16)
+    gy = torch.randn(300, 1408, device=dev(), dtype=torch.bfloat16)
+    (y,), gk = grads(ops.swiglu, [x], gy)
+    (y2,), gr = grads(R.swiglu, [x.float()], gy.float())
+    close(y, y2, 2e-2, 2e-2, "swiglu")
+    close(gk[0], gr[0], 3e-2, 3e-2, "dswiglu")
+    x = torch.randn(2, 50, 4, 128, device=dev(), dtype=torch.bfloat16)
+    gy = torch.randn_like(x)
+    (y,), gk = grads(lambda t: ops.l2_norm(t), [x], gy)
+    (y2,), gr = grads(lambda t: R.l2_norm(t), [x.float()], gy.float())
+    close(y, y2, 2e-2, 2e-2, "l2norm")
+    close(gk[0], gr[0], 3e-2, 3e-2, "dl2norm")
+    for inter in (False, True):
+        for rot in (128, 64):
+            cos, sin = R.rope_freqs(50, rot, 10000.0, 7, dev())
+            (y,), gk = grads(lambda t: ops.apply_rope(t, cos, sin, inter), [x], gy)
+            (y2,), gr = grads(lambda t: R.apply_rope(t, cos, sin, inter), [x.float()], gy.float())
+            close(y, y2, 2e-2, 2e-2, "rope")
+            close(gk[0], gr[0], 3e-2, 3e-2, "drope")
+
+
+def test_linear_cross_entropy():
+    torch.manual_seed(4)
+    T, h, V = 700, 256, 32000
+    x = (0.5 * torch.randn(T, h, device=dev())).to(torch.bfloat16)
+    w = (0.05 * torch.randn(V, h, device=dev())).to(torch.bfloat16)
+    lab = torch.randint(0, V, (T,), device=dev())
+    lab[::7] = -100
+    gl = torch.rand(T, device=dev())
+    (l,), gk = grads(lambda x, w: ops.linear_cross_entropy(x, w, lab, -100, 256), [x, w], gl)
+    (l2,), gr = grads(lambda x, w: R.linear_cross_entropy(x, w, lab), [x.float(), w.float()], gl)
+    close(l, l2, 2e-2, 2e-2, "loss")
+    close(gk[0], gr[0], 5e-2, 2e-3, "dh")
+    close(gk[1], gr[1], 5e-2, 2e-3, "dw")
+
+
+@pytest.mark.parametrize("init", [False, True])
+def test_causal_conv1d(init):
+    torch.manual_seed(5)
+    B, T, D, K = 2, 300, 384, 4
+    x = torch.randn(B, T, D, device=dev(), dtype=torch.bfloat16)
+    w = (0.5 * torch.randn(D, K, device=dev())).to(torch.bfloat16)
+    b = (0.1 * torch.randn(D, device=dev())).to(torch.bfloat16)
+    s = torch.randn(B, K - 1, D, device=dev(), dtype=torch.bfloat16) if init else None
+    gy = torch.randn(B, T, D, device=dev(), dtype=torch.bfloat16)
+    ins = [x, w, b] + ([s] if init else [])
+    f_k = lambda x, w, b, s=None: ops.causal_conv1d(x, w, b, "silu", s)[0]
+    f_r = lambda x, w, b, s=None: R.causal_conv1d(x, w, b, "silu", s)[0]
+    (y,), gk = grads(f_k, ins, gy)
+    (y2,), gr = grads(f_r, [t.float() for t in ins], gy.float())
+    close(y, y2, 2e-2, 2e-2, "y")
+    close(gk[0], gr[0], 3e-2, 3e-2, "dx")
+    close(gk[1], gr[1], 3e-2, 0.5, "dw")
+    close(gk[2], gr[2], 3e-2, 0.5, "db")
+    if init:
+        close(gk[3], gr[3], 3e-2, 3e-2, "dinit")
+        close(ops.causal_conv1d(x, w, b, "silu", s)[1], R.causal_conv1d(x, w, b, "silu", s)[1], 0, 0, "tail")
+
+
+@pytest.mark.parametrize("order", ["softmax_topk", "topk_softmax"])
+def test_router(order):
+    torch.manual_seed(6)
+    T, E, k = 500, 64, 8
+    logits = torch.randn(T, E, device=dev())
+    gp, gf = torch.randn(T, k, device=dev()), torch.randn(T, E, device=dev())
+    (p, i, f), gk = grads(lambda l: ops.router_topk(l, k, order), [logits], (gp, None, gf))
+    (p2, i2, f2), gr = grads(lambda l: R.router_topk(l, k, order), [logits], (gp, None, gf))
+    assert torch.equal(i, i2)
+    close(p, p2, 1e-4, 1e-5, "probs")
+    close(f, f2, 1e-4, 1e-5, "full")
+    close(gk[0], gr[0], 1e-3, 1e-5, "dlogits")
+
+
+def test_fused_adam():
+    torch.manual_seed(7)
+    from linear_moe_b200.ops import cuda as K
+    n = 4096 * 3
+    p = torch.randn(n, device=dev()).to(torch.bfloat16)
+    master = p.float().clone()
+    g = torch.randn(n, device=dev())
+    m, v = torch.zeros(n, device=dev()), torch.zeros(n, device=dev())
+    w2, m2, v2 = master.clone(), m.clone(), v.clone()
+    lr, b1, b2, eps, wd = 1e-3, 0.9, 0.95, 1e-8, 0.1
+    for step in range(1, 4):
+        bc1, bc2 = 1 - b1 ** step, 1 - b2 ** step
+        K.fused_adam(p, master, g, m, v, lr, b1, b2, eps, wd, bc1, bc2, 0.5)
+        gg = g * 0.5
+        m2.mul_(b1).add_(gg, alpha=1 - b1)
+        v2.mul_(b2).addcmul_(gg, gg, value=1 - b2)
+        w2.mul_(1 - lr * wd).addcdiv_(m2 / bc1, (v2 / bc2).sqrt() + eps, value=-lr)
+    close(master, w2, 1e-5, 1e-6, "master")
+    close(p, w2.to(torch.bfloat16), 0, 0, "bf16 copy")
+
+
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("gmode", ["none", "const", "token"])
+@pytest.mark.parametrize("T,with_state", [(1000, False), (256, True), (70, True)])
+def test_lsm_scalar(D, gmode, T, with_state):
+    torch.manual_seed(8)
+    B, H = 2, 3
+    qkv = (0.5 * torch.randn(B, T, H, 3 * D, device=dev())).to(torch.bfloat16)
+    q, k, v = qkv.split(D, dim=-1)                    # strided views, as in the model
+    g = None
+    if gmode == "const":
+        g = -torch.tensor([0.02, 0.1, 0.5], device=dev())
+    elif gmode == "token":
+        g = -0.2 * torch.rand(B, T, H, device=dev())
+    S0 = 0.3 * torch.randn(B, H, D, D, device=dev()) if with_state else None
+    go = torch.randn(B, T, H, D, device=dev(), dtype=torch.bfloat16)
+    gS = 0.1 * torch.randn(B, H, D, D, device=dev()) if with_state else None
+    ins = [q, k, v] + ([g] if gmode == "token" else []) + ([S0] if with_state else [])
+
+    def unpack(args):
+        args = list(args)
+        qq, kk, vv = args[:3]
+        rest = args[3:]
+        gg = rest.pop(0) if gmode == "token" else g
+        ss = rest.pop(0) if with_state else None
+        return qq, kk, vv, gg, ss
+    f_k = lambda *a: ops.lsm_scalar(*unpack(a)[:4], None, unpack(a)[4], 64)
+    f_r = lambda *a: LT.chunk_scalar_gated(*unpack(a)[:4], None, unpack(a)[4], 64)
+    (o, S), gk = grads(f_k, ins, (go, gS))
+    (o2, S2), gr = grads(f_r, [t.float() for t in ins], (go.float(), gS))
+    scale_o = o2.abs().max().item()
+    close(o, o2, 3e-2, 2e-2 * scale_o, "o")
+    close(S, S2, 3e-2, 2e-2 * S2.abs().max().item(), "final state")
+    for name, a, b in zip(["dq", "dk", "dv", "d3", "d4"], gk, gr):
+        close(a, b, 5e-2, 3e-2 * b.abs().max().item(), name)
