@@ -102,7 +102,10 @@ class _ChunkedLinearCE(torch.autograd.Function):
                 p.scatter_add_(-1, lab.clamp(min=0)[:, None], -torch.ones_like(p[:, :1]))
                 g = (p * (gl[s:e] * valid)[:, None]).to(h.dtype)
             dh[s:e] = g @ wd
-            dw.addmm_(g.t().float() if not _cuda(h) else g.t(), h[s:e].float() if not _cuda(h) else h[s:e])
+            if _cuda(h) and g.dtype != torch.float32:
+                dw += torch.mm(g.t(), h[s:e], out_dtype=torch.float32)     # bf16 operands, fp32 accumulate + output
+            else:
+                dw.addmm_(g.t().float(), h[s:e].float())
         return dh, dw.to(weight.dtype), None, None, None
 
 
