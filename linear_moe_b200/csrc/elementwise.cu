@@ -153,35 +153,66 @@ __global__ void reduce_partials_kernel(const float* __restrict__ partial, T* __r
 // Per-head RMSNorm + swish gate (LSM epilogue).  rows = B*T*H, D = head value dim, one warp per row.
 //   y = (norm ? o * rstd * w : o) * silu(gate)
 // ---------------------------------------------------------------------------------------------
+// Lane l owns the 4 contiguous channels [4l + 128j, 4l + 128j + 4) of the row: one 8-byte (bf16) or 16-byte
+// (fp32) access per lane and j.
+template <typename T> struct Quad;
+template <> struct Quad<bf16> {
+    uint2 raw;
+    __device__ __forceinline__ void load(const bf16* p) { raw = *reinterpret_cast<const uint2*>(p); }
+    __device__ __forceinline__ void store(bf16* p) const { *reinterpret_cast<uint2*>(p) = raw; }
+    __device__ __forceinline__ float get(int i) const { return __bfloat162float(reinterpret_cast<const bf16*>(&raw)[i]); }
+    __device__ __forceinline__ void set(int i, float v) { reinterpret_cast<bf16*>(&raw)[i] = __float2bfloat16(v); }
+};
+template <> struct Quad<float> {
+    float4 raw;
+    __device__ __forceinline__ void load(const float* p) { raw = *reinterpret_cast<const float4*>(p); }
+    __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = raw; }
+    __device__ __forceinline__ float get(int i) const { return reinterpret_cast<const float*>(&raw)[i]; }
+    __device__ __forceinline__ void set(int i, float v) { reinterpret_cast<float*>(&raw)[i] = v; }
+};
+
 template <typename T, int DMAX>
 __global__ void head_norm_gate_fwd_kernel(const T* __restrict__ o, const T* __restrict__ w, const T* __restrict__ gate,
                                           T* __restrict__ y, float* __restrict__ rstd_out, int64_t rows, int D,
                                           float eps, int do_norm) {
     const int lane = threadIdx.x & 31;
-    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= rows) return;
-    constexpr int PER = DMAX / 32;
-    float v[PER];
-    float ss = 0.f;
+    constexpr int PER = DMAX / 128;
+    const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+    float wv[PER][4];
 #pragma unroll
     for (int j = 0; j < PER; ++j) {
-        int c = lane + j * 32;
-        v[j] = c < D ? to_f(o[row * D + c]) : 0.f;
-        ss += v[j] * v[j];
-    }
-    float rs = 1.f;
-    if (do_norm) {
-        ss = warp_sum(ss);
-        rs = rsqrtf(ss / (float)D + eps);
-        if (lane == 0) rstd_out[row] = rs;
-    }
+        int c = lane * 4 + j * 128;
 #pragma unroll
-    for (int j = 0; j < PER; ++j) {
-        int c = lane + j * 32;
-        if (c < D) {
-            float n = v[j] * rs;
-            if (do_norm && w != nullptr) n *= to_f(w[c]);
-            y[row * D + c] = from_f<T>(n * silu_f(to_f(gate[row * D + c])));
+        for (int e = 0; e < 4; ++e) wv[j][e] = (do_norm && w != nullptr && c + e < D) ? to_f(w[c + e]) : 1.f;
+    }
+    for (int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); row < rows; row += nwarps) {
+        Quad<T> v[PER], g[PER];
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            int c = lane * 4 + j * 128;
+            if (c < D) {
+                v[j].load(o + row * D + c);
+                g[j].load(gate + row * D + c);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { float f = v[j].get(e); ss += f * f; }
+            }
+        }
+        float rs = 1.f;
+        if (do_norm) {
+            ss = warp_sum(ss);
+            rs = rsqrtf(ss / (float)D + eps);
+            if (lane == 0) rstd_out[row] = rs;
+        }
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            int c = lane * 4 + j * 128;
+            if (c < D) {
+                Quad<T> out;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) out.set(e, v[j].get(e) * rs * wv[j][e] * silu_f(g[j].get(e)));
+                out.store(y + row * D + c);
+            }
         }
     }
 }
@@ -192,51 +223,61 @@ __global__ void head_norm_gate_bwd_kernel(const T* __restrict__ dy, const T* __r
                                           T* __restrict__ d_o, T* __restrict__ dgate, float* __restrict__ dw_partial,
                                           int64_t rows, int D, int do_norm) {
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    constexpr int PER = DMAX / 32;
-    float dwacc[PER];
+    constexpr int PER = DMAX / 128;
+    float dwacc[PER][4], wv[PER][4];
 #pragma unroll
-    for (int j = 0; j < PER; ++j) dwacc[j] = 0.f;
+    for (int j = 0; j < PER; ++j) {
+        int c = lane * 4 + j * 128;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            dwacc[j][e] = 0.f;
+            wv[j][e] = (do_norm && w != nullptr && c + e < D) ? to_f(w[c + e]) : 1.f;
+        }
+    }
     for (int64_t row = (int64_t)blockIdx.x * nw + wid; row < rows; row += (int64_t)gridDim.x * nw) {
         const float rs = do_norm ? rstd[row] : 1.f;
-        float xh[PER], gn[PER];
+        Quad<T> ov[PER], gv[PER], gy[PER];
+        float xh[PER][4], gn[PER][4];
         float dot = 0.f;
 #pragma unroll
         for (int j = 0; j < PER; ++j) {
-            int c = lane + j * 32;
-            xh[j] = 0.f; gn[j] = 0.f;
+            int c = lane * 4 + j * 128;
             if (c < D) {
-                float ov = to_f(o[row * D + c]);
-                float gv = to_f(gate[row * D + c]);
-                float g = to_f(dy[row * D + c]);
-                float wv = (do_norm && w != nullptr) ? to_f(w[c]) : 1.f;
-                xh[j] = ov * rs;
-                float n = xh[j] * wv;
-                dgate[row * D + c] = from_f<T>(g * n * dsilu_f(gv));
-                float gnorm = g * silu_f(gv);          // grad wrt normalised*w output
-                dwacc[j] += gnorm * xh[j];
-                gn[j] = gnorm * wv;
-                dot += gn[j] * xh[j];
+                ov[j].load(o + row * D + c);
+                gv[j].load(gate + row * D + c);
+                gy[j].load(dy + row * D + c);
+                Quad<T> dg;
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    float gt = gv[j].get(e), g = gy[j].get(e);
+                    xh[j][e] = ov[j].get(e) * rs;
+                    dg.set(e, g * xh[j][e] * wv[j][e] * dsilu_f(gt));
+                    float gnorm = g * silu_f(gt);
+                    dwacc[j][e] += gnorm * xh[j][e];
+                    gn[j][e] = gnorm * wv[j][e];
+                    dot += gn[j][e] * xh[j][e];
+                }
+                dg.store(dgate + row * D + c);
             }
         }
-        if (do_norm) {
-            dot = warp_sum(dot) / (float)D;
+        if (do_norm) dot = warp_sum(dot) / (float)D;
 #pragma unroll
-            for (int j = 0; j < PER; ++j) {
-                int c = lane + j * 32;
-                if (c < D) d_o[row * D + c] = from_f<T>(rs * (gn[j] - xh[j] * dot));
-            }
-        } else {
+        for (int j = 0; j < PER; ++j) {
+            int c = lane * 4 + j * 128;
+            if (c < D) {
+                Quad<T> out;
 #pragma unroll
-            for (int j = 0; j < PER; ++j) {
-                int c = lane + j * 32;
-                if (c < D) d_o[row * D + c] = from_f<T>(gn[j]);
+                for (int e = 0; e < 4; ++e) out.set(e, do_norm ? rs * (gn[j][e] - xh[j][e] * dot) : gn[j][e]);
+                out.store(d_o + row * D + c);
             }
         }
     }
     if (dw_partial != nullptr) {
         extern __shared__ float sm[];                  // [nw, DMAX]
 #pragma unroll
-        for (int j = 0; j < PER; ++j) sm[wid * DMAX + lane + j * 32] = dwacc[j];
+        for (int j = 0; j < PER; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) sm[wid * DMAX + lane * 4 + j * 128 + e] = dwacc[j][e];
         __syncthreads();
         for (int c = threadIdx.x; c < D; c += blockDim.x) {
             float s = 0.f;
@@ -758,9 +799,10 @@ LMOE_API int lmoe_rms_norm_bwd(const void* dy, const void* xin, const void* w, c
 
 LMOE_API int lmoe_head_norm_gate_fwd(const void* o, const void* w, const void* gate, void* y, float* rstd, int64_t rows,
                                      int D, float eps, int do_norm, int dtype, cudaStream_t st) {
-    if (D > 512) return -1;
+    if (D > 512 || D % 4 != 0) return -1;
     const int wpb = 8;
-    int blocks = (int)((rows + wpb - 1) / wpb);
+    int64_t need = (rows + wpb - 1) / wpb;
+    int blocks = (int)(need < 148 * 8 ? need : 148 * 8);
     DISPATCH_T(dtype, {
         if (D <= 128) head_norm_gate_fwd_kernel<T, 128><<<blocks, wpb * 32, 0, st>>>((const T*)o, (const T*)w, (const T*)gate, (T*)y, rstd, rows, D, eps, do_norm);
         else if (D <= 256) head_norm_gate_fwd_kernel<T, 256><<<blocks, wpb * 32, 0, st>>>((const T*)o, (const T*)w, (const T*)gate, (T*)y, rstd, rows, D, eps, do_norm);
@@ -772,7 +814,7 @@ LMOE_API int lmoe_head_norm_gate_fwd(const void* o, const void* w, const void* g
 LMOE_API int lmoe_head_norm_gate_bwd(const void* dy, const void* o, const void* w, const void* gate, const float* rstd,
                                      void* d_o, void* dgate, float* dw_partial, void* dw, int64_t rows, int D,
                                      int do_norm, int P, int dtype, cudaStream_t st) {
-    if (D > 512) return -1;
+    if (D > 512 || D % 4 != 0) return -1;
     const int wpb = 8;
     int64_t need = (rows + wpb - 1) / wpb;
     int blocks = (int)(need < P ? need : P);

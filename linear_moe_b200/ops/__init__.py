@@ -109,8 +109,43 @@ class _ChunkedLinearCE(torch.autograd.Function):
         return dh, dw.to(weight.dtype), None, None, None
 
 
+class _CachedLinearCE(torch.autograd.Function):
+    """LM head + cross entropy that keeps ``Z = softmax(logits) - onehot(label)`` in bf16 instead of
+    recomputing the logits in the backward: forward = one GEMM + two passes over the logits (log-sum-exp,
+    then in-place conversion to Z); backward = ``dh = g * (Z W)`` and ``dW = Z^T (g * h)``, two GEMMs.
+    Costs ``T*V*2`` bytes; used when that fits the budget of :func:`linear_cross_entropy`."""
+
+    @staticmethod
+    def forward(ctx, h, weight, labels, ignore_index):
+        T = h.shape[0]
+        wd = weight if weight.dtype == h.dtype else weight.to(h.dtype)
+        Z = torch.mm(h, wd.t())
+        loss = torch.empty(T, dtype=torch.float32, device=h.device)
+        lse = torch.empty(T, dtype=torch.float32, device=h.device)
+        K = _K()
+        K.softmax_ce_fwd(Z, labels, loss, lse, ignore_index)
+        K.softmax_ce_bwd(Z, labels, lse, torch.ones(T, dtype=torch.float32, device=h.device), ignore_index)
+        ctx.save_for_backward(h, wd, Z)
+        ctx.wdtype = weight.dtype
+        return loss
+
+    @staticmethod
+    def backward(ctx, gl):
+        h, wd, Z = ctx.saved_tensors
+        g = gl.to(h.dtype)[:, None]
+        dh = torch.mm(Z, wd) * g
+        dw = torch.mm(Z.t(), h * g)
+        return dh, dw.to(ctx.wdtype), None, None
+
+
+_CE_CACHE_BYTES = 8 << 30
+
+
 def linear_cross_entropy(h, weight, labels, ignore_index: int = -100, chunk: int = 4096):
     """Per-token loss ``[T]`` of ``softmax(h W^T)`` vs ``labels``; h ``[T,hid]``, W ``[V,hid]``."""
+    if (_cuda(h) and h.dtype == torch.bfloat16 and torch.is_grad_enabled()
+            and h.shape[0] * weight.shape[0] * 2 <= _CE_CACHE_BYTES):
+        return _CachedLinearCE.apply(h, weight, labels.contiguous(), ignore_index)
     return _ChunkedLinearCE.apply(h, weight, labels, ignore_index, chunk)
 
 

@@ -210,7 +210,7 @@ class _HeadNormGate(torch.autograd.Function):
         dy = dy.contiguous()
         d_o, dgate = torch.empty_like(oc), torch.empty_like(gc)
         need_dw = w is not None and ctx.do_norm
-        P = min((rows + 7) // 8, NUM_SMS * 2)
+        P = min((rows + 7) // 8, NUM_SMS * 8)
         partial = torch.empty(P, D, dtype=torch.float32, device=oc.device) if need_dw else None
         dw = torch.empty(D, dtype=oc.dtype, device=oc.device) if need_dw else None
         _check(lib().lmoe_head_norm_gate_bwd(_p(dy), _p(oc), _p(w), _p(gc), _p(rstd), _p(d_o), _p(dgate), _p(partial),
@@ -554,6 +554,9 @@ def _lsm_combine(rev, states, gdecay, gconst, seed, final_out, BH, H, G, cpg, T,
                                          _i32(H), _i32(G), _i32(cpg), _i32(T), _i32(D), _st()), "lsm_scalar_combine")
 
 
+_LASP_CTX = None          # set by parallel.fused_comm.lasp2_scalar while a sequence-parallel call is running
+
+
 class _LsmScalar(torch.autograd.Function):
     """o, S_T = scalar-decay linear attention.  q,k,v bf16 [B,T,H,D]; g None | [H] | [B,T,H] fp32."""
 
@@ -571,8 +574,13 @@ class _LsmScalar(torch.autograd.Function):
         seed = None if init is None else init.float().contiguous()
         a = _lsm_args(q, k, v, gf, gmode, scale, B, T, H, G, cpg, states, gdecay, o=o)
         _lsm_launch(0, D, a)
-        _lsm_combine(0, states, gdecay, gf if gmode == 1 else None, seed, final, B * H, H, G, cpg, T, D)
+        lasp = _LASP_CTX if (gmode != 2 and init is None) else None
+        if lasp is not None:       # sequence split over ranks: exchange fused into the combine kernel
+            lasp.combine(0, states, gf if gmode == 1 else None, final, B * H, H, G, cpg, T, D)
+        else:
+            _lsm_combine(0, states, gdecay, gf if gmode == 1 else None, seed, final, B * H, H, G, cpg, T, D)
         _lsm_launch(2, D, a)
+        ctx.lasp = lasp
         ctx.save_for_backward(q, k, v, gf, states, gdecay, final)
         ctx.scale, ctx.gmode, ctx.grid, ctx.has_init = scale, gmode, (G, cpg), init is not None
         ctx.g_dtype = None if g is None else g.dtype
@@ -599,7 +607,10 @@ class _LsmScalar(torch.autograd.Function):
         a2 = _lsm_args(q, k, v, gf, ctx.gmode, ctx.scale, B, T, H, G, cpg, dstates, None, d_o=d_o, dk=dk, dv=dv)
         _lsm_launch(1, D, a2)
         seed = None if dfinal is None else dfinal.float().contiguous()
-        _lsm_combine(1, dstates, gdecay, gf if ctx.gmode == 1 else None, seed, dinit, B * H, H, G, cpg, T, D)
+        if ctx.lasp is not None:
+            ctx.lasp.combine(1, dstates, gf if ctx.gmode == 1 else None, None, B * H, H, G, cpg, T, D)
+        else:
+            _lsm_combine(1, dstates, gdecay, gf if ctx.gmode == 1 else None, seed, dinit, B * H, H, G, cpg, T, D)
         _lsm_launch(4, D, a2)
         dg = None
         if ctx.gmode == 2:
@@ -609,13 +620,47 @@ class _LsmScalar(torch.autograd.Function):
             if dfinal is not None:
                 dg = dg + (final * dfinal.float()).sum((-1, -2))[:, None, :]
             dg = dg.to(ctx.g_dtype)
-        elif ctx.gmode == 1 and ctx.needs_input_grad[3]:
+        elif ctx.gmode == 1 and len(ctx.needs_input_grad) > 3 and ctx.needs_input_grad[3]:
             s = (q.float() * dq.float()).sum(-1) - (k.float() * dk.float()).sum(-1)
             dgt = s.flip(1).cumsum(1).flip(1)
             if dfinal is not None:
                 dgt = dgt + (final * dfinal.float()).sum((-1, -2))[:, None, :]
             dg = dgt.sum((0, 1)).to(ctx.g_dtype)
         return dq, dk, dv, dg, None, dinit
+
+
+def _fused_base(q, k, v):
+    """If q, k, v are the three slices of one [B,T,H,3D] tensor (a fused projection), return that tensor."""
+    base = q._base                                   # root of the view chain, e.g. the projection output [B,T,H*3D]
+    if base is None or k._base is not base or v._base is not base or not base.is_contiguous():
+        return None
+    B, T, H, D = q.shape
+    if base.numel() != B * T * H * 3 * D:
+        return None
+    e = base.element_size()
+    if (q.data_ptr() != base.data_ptr() or k.data_ptr() != base.data_ptr() + D * e
+            or v.data_ptr() != base.data_ptr() + 2 * D * e):
+        return None
+    want = (T * H * 3 * D, H * 3 * D, 3 * D, 1)
+    if q.stride() != want or k.stride() != want or v.stride() != want:
+        return None
+    return base.view(B, T, H, 3 * D)
+
+
+class _LsmScalarFused(torch.autograd.Function):
+    """Same as ``_LsmScalar`` with q|k|v given as one fused ``[B,T,H,3D]`` tensor, so that the backward hands
+    autograd one gradient tensor instead of three slices it would have to concatenate."""
+
+    @staticmethod
+    def forward(ctx, qkv, g, scale, init):
+        D = qkv.shape[-1] // 3
+        q, k, v = qkv[..., :D], qkv[..., D:2 * D], qkv[..., 2 * D:]
+        return _LsmScalar.forward(ctx, q, k, v, g, scale, init)
+
+    @staticmethod
+    def backward(ctx, d_o, dfinal):
+        dq, dk, dv, dg, _, dinit = _LsmScalar.backward(ctx, d_o, dfinal)
+        return dq._base, dg, None, dinit
 
 
 def lsm_scalar(q, k, v, g, scale, initial_state, chunk_size):
@@ -625,6 +670,9 @@ def lsm_scalar(q, k, v, g, scale, initial_state, chunk_size):
     if not ok:
         return LT.chunk_scalar_gated(q, k, v, g, scale, initial_state, chunk_size)
     scale = D ** -0.5 if scale is None else scale
+    base = _fused_base(q, k, v)
+    if base is not None:
+        return _LsmScalarFused.apply(base, g, scale, initial_state)
     return _LsmScalar.apply(q, k, v, g, scale, initial_state)
 
 

@@ -141,7 +141,11 @@ class MixedPrecisionAdam:
     @staticmethod
     def _accumulate(p: nn.Parameter):
         if p.grad is not None:
-            p.main_grad.add_(p.grad.to(torch.float32))
+            if p.grad.is_cuda and p.grad.dtype in (torch.bfloat16, torch.float32) and p.grad.is_contiguous():
+                from ..ops import cuda as K
+                K.accumulate_grad(p.main_grad, p.grad)      # one pass: fp32 accumulator += bf16 gradient
+            else:
+                p.main_grad.add_(p.grad.to(torch.float32))
             p.grad = None
 
     def zero_grad(self):

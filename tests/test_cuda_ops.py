@@ -118,7 +118,9 @@ def test_swiglu_l2norm_rope():
             close(gk[0], gr[0], 3e-2, 3e-2, "drope")
 
 
-def test_linear_cross_entropy():
+@pytest.mark.parametrize("cached", [True, False])
+def test_linear_cross_entropy(cached, monkeypatch):
+    monkeypatch.setattr(ops, "_CE_CACHE_BYTES", (8 << 30) if cached else 0)
     torch.manual_seed(4)
     T, h, V = 700, 256, 32000
     x = (0.5 * torch.randn(T, h, device=dev())).to(torch.bfloat16)
