@@ -967,3 +967,54 @@ LMOE_API int lmoe_accumulate_grad(float* acc, const void* g, int64_t n, int dtyp
     })
     return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------------
+// RMSNorm backward without any allocation: the dw partials go to a fixed array in the library image.
+// See lmoe_noalloc.h for the contract.
+// ---------------------------------------------------------------------------------------------
+#include "lmoe_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_partials[LMOE_NOALLOC_MAX_BLOCKS * LMOE_NOALLOC_MAX_N];
+
+// Device address of g_noalloc_partials per device ordinal.  In host code the array's name is only a handle for
+// the runtime, not a device pointer: the address a kernel can use comes from cudaGetSymbolAddress, looked up
+// once per device with that device current.
+static float* g_noalloc_addr[64] = {nullptr};
+
+static int noalloc_scratch(float** out) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return LMOE_NOALLOC_ERR_SETUP;
+    if (g_noalloc_addr[dev] == nullptr) {
+        float* p = nullptr;
+        if (cudaGetSymbolAddress((void**)&p, g_noalloc_partials) != cudaSuccess || p == nullptr)
+            return LMOE_NOALLOC_ERR_SETUP;
+        g_noalloc_addr[dev] = p;
+    }
+    *out = g_noalloc_addr[dev];
+    return 0;
+}
+
+LMOE_API const char* lmoe_noalloc_strerror(int code) {
+    switch (code) {
+        case 0: return "ok";
+        case LMOE_NOALLOC_ERR_SIZE:
+            return "lmoe_rms_norm_bwd_noalloc: N exceeds LMOE_NOALLOC_MAX_N (4096) or is not a multiple of the "
+                   "vector width (8 for bf16, 4 for fp32)";
+        case LMOE_NOALLOC_ERR_SETUP:
+            return "lmoe_rms_norm_bwd_noalloc: could not obtain the device address of the built-in scratch array";
+        default: return "lmoe_rms_norm_bwd_noalloc: CUDA launch error (code is a cudaError_t)";
+    }
+}
+
+LMOE_API int lmoe_rms_norm_bwd_noalloc(const void* dy, const void* xin, const void* w, const float* rstd,
+                                       const void* dres, void* dx, void* dw, int64_t rows, int N, int dtype,
+                                       cudaStream_t st) {
+    const int vn = dtype == 1 ? 8 : 4;
+    if (N <= 0 || N > LMOE_NOALLOC_MAX_N || N % vn != 0) return LMOE_NOALLOC_ERR_SIZE;
+    float* scratch = nullptr;
+    int rc = noalloc_scratch(&scratch);
+    if (rc != 0) return rc;
+    // same kernels as lmoe_rms_norm_bwd, with the built-in array as the partials buffer
+    return lmoe_rms_norm_bwd(dy, xin, w, rstd, dres, dx, w != nullptr ? scratch : nullptr, dw, rows, N,
+                             LMOE_NOALLOC_MAX_BLOCKS, dtype, st);
+}
