@@ -103,7 +103,8 @@ class SelfAttention(nn.Module):
             k = ops.rms_norm(k.contiguous(), self.k_layernorm.weight, cfg.norm_eps)
         cp = self.mesh["cp"]
         past = cache["k"].shape[1] if (cache is not None and "k" in cache) else 0
-        pos0 = position_offset + past + (cp.rank * T if not cp.is_trivial else 0)
+        # position_offset is the absolute position of this call's first token (the cache length when decoding)
+        pos0 = position_offset + (cp.rank * T if not cp.is_trivial else 0)
         if self.rope is not None:
             cos, sin = self.rope.get(T, pos0, x.device)
             q = ops.apply_rope(q.contiguous(), cos, sin, cfg.rotary_interleaved)
@@ -194,7 +195,8 @@ class MLASelfAttention(nn.Module):
         k_nope, v = kv.split([self.dn, self.dvh], dim=-1)
         cp = self.mesh["cp"]
         past = cache["k"].shape[1] if (cache is not None and "k" in cache) else 0
-        pos0 = position_offset + past + (cp.rank * T if not cp.is_trivial else 0)
+        # position_offset is the absolute position of this call's first token (the cache length when decoding)
+        pos0 = position_offset + (cp.rank * T if not cp.is_trivial else 0)
         cos, sin = self.rope.get(T, pos0, x.device)
         # HF DeepSeek stores the rope dims interleaved; the reference permutes them to half layout
         # before rotating (yarn_rotary_pos_embedding.py:198-202): same as rotating interleaved pairs.

@@ -1,0 +1,200 @@
+"""Checkpoint layout, resharding rules, HF conversion, generation caches, datasets (all CPU)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from linear_moe_b200.ckpt import hf_convert, legacy, reshard
+from linear_moe_b200.config.model_config import ModelConfig, ParallelConfig, TrainConfig
+from linear_moe_b200.dist.mesh import Mesh
+from linear_moe_b200.models.transformer import CausalLM
+
+
+def _cfg(**kw):
+    base = dict(num_layers=2, hidden_size=64, num_attention_heads=4, ffn_hidden_size=128, vocab_size=512)
+    base.update(kw)
+    return ModelConfig(**base)
+
+
+CASES = {
+    "qwen2_moe_gqa": dict(base_model="qwen2", num_query_groups=2, add_qkv_bias=True, num_experts=4, moe_topk=2,
+                          moe_ffn_hidden_size=64, enable_shared_expert=True, shared_moe_ffn_hidden_size=128),
+    "hybrid_gla": dict(use_la_module=True, la_module="gla", layer_type_list="LN", num_experts=4, moe_ffn_hidden_size=64),
+    "hybrid_gdn_conv": dict(use_la_module=True, la_module="gated_deltanet", layer_type_list="LN", use_short_conv=True),
+    "mamba2": dict(use_la_module=True, la_module="mamba2", hybrid_override_pattern="M*", mamba_head_dim=16,
+                   mamba_d_state=16, mamba_ngroups=2, base_model="mixtral", num_experts=4, moe_ffn_hidden_size=64),
+    "deepseek_mla": dict(base_model="deepseek_v2", num_experts=4, moe_topk=2, moe_ffn_hidden_size=32,
+                         enable_shared_expert=True, shared_moe_ffn_hidden_size=64, kv_lora_rank=32, qk_nope_head_dim=16,
+                         qk_rope_head_dim=8, v_head_dim=16, q_lora_rank=24, moe_layer_freq=1),
+}
+
+
+@pytest.mark.parametrize("name", list(CASES))
+def test_reshard_rules_match_model_sharding(name):
+    """A model built on TP rank r of 2 must hold exactly ``shard_state_dict(full, tp=2, tp_rank=r)``; same for EP."""
+    cfg = _cfg(**CASES[name])
+    full = CausalLM(cfg).state_dict()
+    for tp, ep in ((2, 1), (1, 2)):
+        if ep > 1 and not cfg.is_moe:
+            continue
+        par = ParallelConfig(tensor_model_parallel_size=tp, expert_model_parallel_size=ep)
+        shards = {}
+        for r in range(2):
+            mesh = Mesh(par, world_size=2, rank=r, create_groups=False)
+            sd = CausalLM(cfg, mesh, sequence_parallel=tp > 1).state_dict()
+            t_r, e_r = (r, 0) if tp == 2 else (0, r)
+            want = reshard.shard_state_dict(full, cfg, tp, 1, ep, t_r, 0, e_r)
+            assert set(sd) == set(want)
+            for k in sd:
+                assert sd[k].shape == want[k].shape, (k, sd[k].shape, want[k].shape)
+                assert torch.equal(sd[k], want[k]), k
+            shards[(t_r, 0, e_r)] = sd
+        merged = reshard.merge_state_dicts(shards, cfg, tp, 1, ep)
+        for k in full:
+            assert torch.equal(merged[k], full[k]), k
+
+
+def test_pipeline_split_and_reshard_roundtrip():
+    cfg = _cfg(num_layers=4, use_la_module=True, la_module="retention", layer_type_list="LLNL")
+    full = CausalLM(cfg).state_dict()
+    shards = {(t, p, 0): reshard.shard_state_dict(full, cfg, 2, 2, 1, t, p, 0) for t in range(2) for p in range(2)}
+    assert "embedding.word_embeddings.weight" not in shards[(0, 1, 0)]
+    assert "output_layer.weight" not in shards[(0, 0, 0)]
+    again = reshard.reshard(shards, cfg, (2, 2, 1), (1, 4, 1))
+    back = reshard.merge_state_dicts(again, cfg, 1, 4, 1)
+    assert all(torch.equal(back[k], full[k]) for k in full)
+
+
+@pytest.mark.parametrize("name", ["qwen2_moe_gqa", "deepseek_mla"])
+def test_hf_roundtrip(name):
+    cfg = _cfg(**CASES[name])
+    sd = {k: v for k, v in CausalLM(cfg).state_dict().items()}
+    hf = hf_convert.mcore_to_hf(sd, cfg)
+    assert "model.layers.0.self_attn.o_proj.weight" in hf
+    back = hf_convert.hf_to_mcore(hf, cfg)
+    assert set(back) == set(sd)
+    assert all(torch.equal(back[k], sd[k]) for k in sd)
+
+
+def test_qkv_packing_is_group_major():
+    H, G, hd, h = 4, 2, 3, 5
+    q, k, v = torch.randn(H * hd, h), torch.randn(G * hd, h), torch.randn(G * hd, h)
+    w = hf_convert.pack_qkv(q, k, v, G, hd)
+    assert torch.equal(w[: 2 * hd], q[: 2 * hd]) and torch.equal(w[2 * hd:3 * hd], k[:hd])
+    q2, k2, v2 = hf_convert.unpack_qkv(w, H, G, hd)
+    assert torch.equal(q2, q) and torch.equal(k2, k) and torch.equal(v2, v)
+
+
+def test_legacy_checkpoint_roundtrip(tmp_path):
+    from linear_moe_b200.train.loop import Trainer
+    cfg = _cfg(use_la_module=True, la_module="gla", layer_type_list="LN", num_experts=4, moe_ffn_hidden_size=64)
+    tc = TrainConfig(micro_batch_size=2, global_batch_size=2, seq_length=32, train_iters=3, log_interval=100,
+                     save=str(tmp_path), lr=1e-3)
+    tr = Trainer(cfg, ParallelConfig(), tc, device=torch.device("cpu"))
+    for _ in range(2):
+        tr.train_step()
+    tr.save()
+    assert open(tmp_path / legacy.TRACKER).read() == "2"
+    path = legacy.checkpoint_name(str(tmp_path), 2, False, 0, 0, 0, 1, 1)
+    assert path.endswith("iter_0000002/mp_rank_00/model_optim_rng.pt")
+    ck = torch.load(path, weights_only=False)
+    assert ck["checkpoint_version"] == 3.0 and ck["iteration"] == 2
+    keys = set(ck["model"])
+    assert "decoder.layers.0.mlp.experts.local_experts.3.linear_fc1.weight" in keys
+    assert "decoder.layers.0.self_attention.gk_proj.gk_proj.1.bias" in keys
+    assert "embedding.word_embeddings.weight" in keys and "decoder.final_layernorm.weight" in keys
+    tc2 = TrainConfig(micro_batch_size=2, global_batch_size=2, seq_length=32, train_iters=3, log_interval=100,
+                      load=str(tmp_path), lr=1e-3)
+    tr2 = Trainer(cfg, ParallelConfig(), tc2, device=torch.device("cpu"))
+    assert tr2.iteration == 2
+    a, b = tr.model.state_dict(), tr2.model.state_dict()
+    assert all(torch.equal(a[k], b[k]) for k in a)
+    s1, s2 = tr.train_step(), tr2.train_step()
+    assert abs(float(s1["lm loss"]) - float(s2["lm loss"])) < 1e-5      # optimizer + data position restored
+
+
+def test_zero1_optimizer_reshard():
+    states = []
+    for r in range(2):
+        n = 256
+        states.append({"step": 3, "loss_scale": None, "zero1": True, "buffers": [{
+            "expert": False, "weight_decay": True, "shard": (r * n, (r + 1) * n), "numel": 512, "names": ["w"],
+            "master": torch.arange(r * n, (r + 1) * n, dtype=torch.float32), "exp_avg": torch.ones(n) * r,
+            "exp_avg_sq": torch.zeros(n)}]})
+    new = reshard.reshard_optimizer_shards(states, 4)
+    assert len(new) == 4 and new[3]["buffers"][0]["shard"] == (384, 512)
+    assert torch.equal(torch.cat([s["buffers"][0]["master"] for s in new]), torch.arange(512, dtype=torch.float32))
+
+
+@pytest.mark.parametrize("la", [None, "lightning_attention", "gla", "gated_deltanet", "hgrn2", "rwkv6", "mamba2"])
+def test_incremental_decoding_matches_full_forward(la):
+    """Prefill + token-by-token decoding with the recurrent / KV caches gives the logits of one full forward."""
+    torch.manual_seed(0)
+    kw = dict(num_layers=2, hidden_size=64, num_attention_heads=4, ffn_hidden_size=128, vocab_size=128, init_method_std=0.1)
+    if la == "mamba2":
+        kw.update(use_la_module=True, la_module=la, hybrid_override_pattern="M*", mamba_head_dim=16, mamba_d_state=16,
+                  mamba_ngroups=2)
+    elif la is not None:
+        kw.update(use_la_module=True, la_module=la, layer_type_list="LN", use_short_conv=la == "gated_deltanet")
+    model = CausalLM(ModelConfig(**kw)).eval()
+    ids = torch.randint(0, 128, (2, 12))
+    with torch.no_grad():
+        full = model(ids)
+        caches = model.new_cache()
+        parts = [model(ids[:, :5], caches=caches, position_offset=0)]
+        for t in range(5, 12):
+            parts.append(model(ids[:, t:t + 1], caches=caches, position_offset=t))
+        inc = torch.cat(parts, dim=1)
+    assert torch.allclose(full, inc, atol=2e-4, rtol=1e-3), (full - inc).abs().max()
+
+
+def test_generation_api():
+    from linear_moe_b200.data.tokenizer import NullTokenizer
+    from linear_moe_b200.infer import generation as G
+    torch.manual_seed(0)
+    model = CausalLM(_cfg(vocab_size=64, use_la_module=True, la_module="retention", layer_type_list="LN")).eval()
+    tok = NullTokenizer(64)
+    texts, toks, lp = G.generate_and_post_process(model, tok, ["1 2 3", "4 5"], tokens_to_generate=6, top_k_sampling=1,
+                                                  return_output_log_probs=True, use_eod_token_for_early_termination=False)
+    assert len(toks[0]) == 9 and toks[0][:3] == [1, 2, 3] and toks[1][:2] == [4, 5]
+    # greedy continuation equals argmax of a full forward on the generated prefix
+    seq = torch.tensor([toks[1]])
+    with torch.no_grad():
+        nxt = model(seq[:, :-1])[0, -1].argmax().item()
+    assert nxt == toks[1][-1]
+    assert lp.shape == (2, 8) and torch.isfinite(lp).all()
+    out, scores = G.beam_search(model, torch.tensor([[1, 2, 3]]), beam_size=3, max_new_tokens=4, eod=63)
+    assert out.shape[0] == 1 and out[0, :3].tolist() == [1, 2, 3]
+    logits = torch.tensor([[0.0, 1.0, 2.0, 3.0]])
+    assert G.sample(logits, top_k=1).item() == 3
+    assert set(G.modify_logits_for_top_k(logits, 2)[0].isinf().tolist()) == {True, False}
+    assert G.modify_logits_for_top_p(logits, 0.5)[0, 0].isinf()
+
+
+def test_indexed_dataset_and_index_builder(tmp_path):
+    from linear_moe_b200.data import datasets as D
+    from linear_moe_b200.utils import hostlib
+    rng = np.random.RandomState(0)
+    docs = [rng.randint(0, 1000, size=rng.randint(5, 40)).astype(np.int32) for _ in range(50)]
+    prefix = str(tmp_path / "corpus")
+    D.IndexedDataset.write(prefix, docs)
+    ds = D.IndexedDataset(prefix)
+    assert len(ds) == 50 and np.array_equal(ds.get(7), docs[7]) and np.array_equal(ds.get(7, 2, 3), docs[7][2:5])
+    g = D.GPTDataset(ds, seq_length=16, num_samples=40, seed=1)
+    flat = np.concatenate([docs[i] for i in g.doc_idx])
+    for i in range(10):
+        s = g.shuffle_idx[i]
+        want = flat[s * 16: s * 16 + 17]
+        assert np.array_equal(g[i]["text"].numpy(), want)
+    lib = hostlib.load()
+    if lib is not None:     # C++ builder equals the numpy definition
+        sizes, doc_idx = np.asarray(ds.sizes), g.doc_idx
+        a = hostlib.build_sample_idx(lib, sizes, doc_idx, 16, 30)
+        hostlib._LIB, keep = None, hostlib._LIB
+        hostlib._TRIED = True
+        b = D.build_sample_idx(sizes, doc_idx, 16, 1, 16 * 30 + 1)
+        hostlib._LIB = keep
+        assert np.array_equal(a, b[: len(a)])
+    batch = D.make_batch({"text": torch.arange(18)[None]}, eod_token=5, eod_mask_loss=True)
+    assert batch["tokens"].shape == (1, 17) and batch["labels"][0, 5] == -100 and batch["loss_mask"][0, 5] == 0
