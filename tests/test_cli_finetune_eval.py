@@ -1,0 +1,131 @@
+"""Argument surface, fine-tuning loop, lm-eval adaptor, preprocessing, layer patterns, failure detection (CPU)."""
+import json
+import os
+import time
+
+import pytest
+import torch
+
+from linear_moe_b200.config.arguments import build_parser, parse_args
+from linear_moe_b200.config.model_config import ModelConfig, ParallelConfig, TrainConfig
+from linear_moe_b200.config.presets import PRESETS, get_preset
+from linear_moe_b200.models.layout import allocate_mamba_pattern, expand_layer_pattern, split_for_pipeline
+
+
+def test_reference_flags_are_accepted():
+    argv = ("--num-layers 4 --hidden-size 64 --num-attention-heads 4 --ffn-hidden-size 128 --seq-length 128 "
+            "--max-position-embeddings 128 --micro-batch-size 1 --global-batch-size 8 --lr 1e-4 --min-lr 1e-5 "
+            "--lr-decay-style cosine --weight-decay 0.1 --adam-beta1 0.9 --adam-beta2 0.95 --clip-grad 1.0 "
+            "--init-method-std 0.008 --attention-dropout 0.0 --hidden-dropout 0.0 --train-iters 10 --lr-warmup-iters 2 "
+            "--log-interval 10 --eval-interval 100000 --eval-iters 10 --save-interval 100 --tensorboard-queue-size 1000 "
+            "--log-timers-to-tensorboard --log-batch-size-to-tensorboard --log-validation-ppl-to-tensorboard "
+            "--tensor-model-parallel-size 2 --pipeline-model-parallel-size 1 --context-parallel-size 1 --no-load-optim "
+            "--no-load-rng --num-workers 8 --extra-vocab-size 293 --patch-tokenizer-type Qwen2Tokenizer "
+            "--dataset LLama-Pretrain-Idxmap --swiglu --normalization RMSNorm --norm-epsilon 1e-6 "
+            "--use-rotary-position-embeddings --no-rope-fusion --position-embedding-type rope "
+            "--untie-embeddings-and-output-weights --disable-bias-linear --add-qkv-bias --group-query-attention "
+            "--num-query-groups 4 --rotary-percent 1.0 --rotary-base 1000000 --rotary-seq-len-interpolation-factor 1 "
+            "--no-create-attention-mask-in-dataloader --bf16 --use-distributed-optimizer --sequence-parallel "
+            "--recompute-activations --moe-router-topk 2 --num-experts 8 --moe-aux-loss-coeff 1e-2 "
+            "--expert-model-parallel-size 2 --moe-router-load-balancing-type aux_loss --moe-ffn-hidden-size 64 "
+            "--enable-shared-expert --shared-moe-ffn-hidden-size 128 --use-la-module --la-module gated_deltanet "
+            "--la-mode chunk --base-model qwen2 --la-feature-map elu --la-output-norm rmsnorm --la-gate-fn swish "
+            "--layer-type-list LLLN --transformer-impl transformer_engine --use-mcore-models --use-flash-attn "
+            "--fp8-hybrid --fp8-amax-history-len 1024 --fp8-amax-compute-algo max --moe-token-dropping "
+            "--moe-train-capacity-factor 1.25 --top-k 5 --temperature 0.7 --out-seq-length 32").split()
+    args, cfg, par, tc = parse_args(argv)
+    assert cfg.la_module == "gated_deltanet" and cfg.layer_type_list == "LLLN" and cfg.num_experts == 8
+    assert cfg.vocab_size % (128 * 2) == 0 and not cfg.add_bias_linear and cfg.add_qkv_bias and not cfg.tie_embeddings
+    assert par.tp == 2 and par.ep == 2 and par.sequence_parallel and par.use_distributed_optimizer
+    assert cfg.recompute_granularity == "selective" and cfg.fp8 == "block" and tc.bf16
+    assert cfg.params_dtype == torch.bfloat16 and cfg.moe_token_dropping and cfg.moe_train_capacity_factor == 1.25
+    names = {a.dest for a in build_parser()._actions}
+    for flag in ("la_tie_feature_map_qk", "gla_la_gate_low_rank_dim", "rwkv6_la_proj_low_rank_dim", "expand_k", "a_num",
+                 "megatron_hybrid_mamba_method", "hybrid_override_pattern", "kv_lora_rank", "text_generate_input_file",
+                 "repetition_penalty", "max_padding_length", "keep_last", "sliding_window", "mom_num_memories"):
+        assert flag in names, flag
+
+
+def test_presets_build():
+    for name in PRESETS:
+        cfg = get_preset(name)
+        specs = cfg.layer_types()
+        assert len(specs) >= cfg.num_layers
+
+
+def test_layer_patterns():
+    cfg = ModelConfig(num_layers=4, use_la_module=True, la_module="gla", layer_type_list="LLLN", num_experts=4)
+    s = expand_layer_pattern(cfg)
+    assert [x.mixer for x in s] == ["lsm", "lsm", "lsm", "attn"] and all(x.ffn == "moe" for x in s)
+    assert [x.index for x in split_for_pipeline(s, 2, 1)] == [2, 3]            # hybrid patterns are PP-sliced
+    m = ModelConfig(num_layers=4, use_la_module=True, la_module="mamba2", hybrid_override_pattern="MM*M")
+    assert "".join(x.symbol for x in expand_layer_pattern(m)) == "M-M-*-M-"     # default: an FFN block after each mixer
+    lit = m.replace(megatron_hybrid_mamba_method=True, hybrid_override_pattern="M-*-")
+    assert "".join(x.symbol for x in expand_layer_pattern(lit)) == "M-*-"
+    auto = allocate_mamba_pattern(8, 0.25, 0.25)
+    assert auto.count("*") == 2 and auto.count("-") == 2
+    ds = ModelConfig(num_layers=3, base_model="deepseek_v2", num_experts=4, moe_layer_freq=1)
+    assert [x.ffn for x in expand_layer_pattern(ds)] == ["mlp", "moe", "moe"] and expand_layer_pattern(ds)[0].mixer == "mla"
+
+
+def test_finetune_and_eval_adaptor(tmp_path):
+    from linear_moe_b200.data.datasets import RawJsonDataset
+    from linear_moe_b200.data.tokenizer import NullTokenizer
+    from linear_moe_b200.infer.lm_eval_adaptor import EvalHarnessAdaptor, LinearMoeOpenCompassModel
+    from linear_moe_b200.train.finetune import finetune
+    rows = [{"instruction": " ".join(str((i * 7 + j) % 50) for j in range(5)), "input": "",
+             "output": " ".join(str((i + j) % 50) for j in range(4))} for i in range(16)]
+    path = tmp_path / "sft.json"
+    path.write_text(json.dumps(rows))
+    tok = NullTokenizer(64)
+    ds = RawJsonDataset([str(path)], tok, max_padding_length=16, sft=True)
+    item = ds[0]
+    assert item["text"].shape == (17,) and (item["labels_full"][:5] == -100).all() and item["labels_full"][5] >= 0
+    cfg = ModelConfig(num_layers=2, hidden_size=32, num_attention_heads=2, ffn_hidden_size=64, vocab_size=64,
+                      use_la_module=True, la_module="linear_attention", layer_type_list="LN")
+    tc = TrainConfig(micro_batch_size=4, global_batch_size=4, seq_length=16, epochs=3, lr=3e-3, min_lr=3e-3,
+                     lr_decay_style="constant", log_interval=1000, weight_decay=0.0)
+    first = {}
+    tr = finetune(cfg, ParallelConfig(), tc, ds, end_of_epoch_callback=lambda t, e: first.setdefault(e, t.iteration))
+    assert tr.iteration == 12 and first[0] == 4
+    ad = EvalHarnessAdaptor(tr.model, tok, max_length=32)
+    res = ad.loglikelihood([("1 2 3", "4 5"), ("", "7")])
+    assert len(res) == 2 and all(r[0] < 0 for r in res)
+    assert len(ad.loglikelihood_rolling([("1 2 3 4 5 6 7 8",)])) == 1
+    assert isinstance(ad.generate_until([("1 2 3", {"max_gen_toks": 4, "until": []})])[0], str)
+    assert LinearMoeOpenCompassModel(tr.model, tok).get_ppl(["1 2 3 4"])[0] > 0
+
+
+def test_preprocess(tmp_path):
+    from linear_moe_b200.data import preprocess
+    from linear_moe_b200.data.datasets import IndexedDataset
+    src = tmp_path / "in.jsonl"
+    src.write_text("\n".join(json.dumps({"text": " ".join(str(i + j) for j in range(6))}) for i in range(10)))
+    preprocess.main(["--input", str(src), "--output-prefix", str(tmp_path / "out"), "--append-eod", "--vocab-size", "100"])
+    ds = IndexedDataset(str(tmp_path / "out_text_document"))
+    assert len(ds) == 10 and ds.get(3).tolist() == [3, 4, 5, 6, 7, 8, 99]
+
+
+def test_heartbeat_detects_a_silent_rank():
+    """Host-side failure detection: a rank that stops beating is reported; nothing touches a GPU."""
+    from linear_moe_b200.train.watchdog import CommTimeout, Heartbeat, raise_on_comm_status
+
+    class Store(dict):
+        def set(self, k, v): self[k] = v.encode()
+        def check(self, ks): return all(k in self for k in ks)
+
+    class M:
+        world_size = 3
+        def __init__(self, r): self.rank = r
+    store, now = Store(), [100.0]
+    hb = [Heartbeat(M(r), 0.0, 5.0, store=store, clock=lambda: now[0]) for r in range(3)]
+    for h in hb:
+        h.beat(1)
+    assert hb[0].check() == []
+    now[0] = 104.0
+    hb[0].beat(2), hb[1].beat(2)            # rank 2 went silent
+    now[0] = 107.0
+    assert hb[0].check() == [2] and hb[1].check() == [2]
+    with pytest.raises(CommTimeout):
+        raise_on_comm_status(torch.tensor([(7 << 24) | (3 << 16) | 1]), "lasp")
+    raise_on_comm_status(torch.tensor([0]), "ok")
