@@ -1,0 +1,170 @@
+"""Per-kernel timing and roofline harness.
+
+  python -m linear_moe_b200.bench.kernels [--kernel all|gemm|lsm|norm|headnorm|swiglu|ce|adam|conv] [--size small|full]
+
+Each kernel is timed with CUDA events on the launching stream after warm-up, with an L2 flush (a 256 MiB write)
+between iterations; the median is reported together with the algorithmic bytes / FLOPs and the fraction of the
+measured peaks (``MEASURED_PEAKS.json`` at the repository root: STREAM-style copy bandwidth and cuBLAS bf16
+throughput; fallback 6650 GB/s and 1590 TFLOPS when the file is absent).  ``--size small`` keeps the working set
+at a few hundred MB (larger than L2), which is the case to run under ``ncu``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+
+import torch
+
+
+def peaks():
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    p = os.path.join(root, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"], d["bf16_tflops"], "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def timeit(fn, iters=10, warmup=3):
+    dev = torch.device("cuda", 0)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for _ in range(warmup):
+        fn()
+    ts = []
+    for _ in range(iters):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ts.append(e0.elapsed_time(e1))
+    return statistics.median(ts)
+
+
+def report(name, ms, bytes_=None, flops=None):
+    bw, tf, kind = peaks()
+    line = f"{name:38s} {ms * 1e3:9.1f} us"
+    if bytes_ is not None:
+        g = bytes_ / ms / 1e6
+        line += f" | {g:7.0f} GB/s = {g / bw:5.2f} of {kind} copy bw"
+    if flops is not None:
+        t = flops / ms / 1e9
+        line += f" | {t:7.0f} TFLOPS = {t / tf:5.2f} of {kind} cuBLAS bf16"
+    print(line, flush=True)
+
+
+def bench_gemm(size):
+    from ..ops import gemm
+    dev = torch.device("cuda", 0)
+    shapes = [(4096, 4096, 2048)] if size == "small" else [(16384, 8192, 2048), (16384, 16384, 2048), (16384, 2048, 8192)]
+    for M, N, K in shapes:
+        a = torch.randn(M, K, device=dev).bfloat16()
+        b = torch.randn(N, K, device=dev).bfloat16()
+        c = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        report(f"gemm tcgen05 {M}x{N}x{K}", timeit(lambda: gemm.gemm_nt(a, b, out=c)), flops=2.0 * M * N * K)
+        report(f"gemm cuBLAS  {M}x{N}x{K}", timeit(lambda: torch.mm(a, b.t(), out=c)), flops=2.0 * M * N * K)
+    gemm.check_error()
+
+
+def bench_lsm(size):
+    from .. import ops
+    dev = torch.device("cuda", 0)
+    B, H, D = 1, 16, 128
+    T = 4096 if size == "small" else 16384
+    qkv = (0.5 * torch.randn(B, T, H, 3 * D, device=dev)).bfloat16().requires_grad_(True)
+    g = -torch.linspace(0.01, 0.3, H, device=dev)
+    go = torch.randn(B, T, H, D, device=dev).bfloat16()
+    elt = B * T * H * D * 2
+
+    def fwd():
+        q, k, v = qkv.split(D, dim=-1)
+        return ops.lsm_scalar(q, k, v, g, 1.0, None, 64)[0]
+    intra = 2.0 * B * H * T * (2 * 64 * D + 2 * D * D)          # per token: QK^T, PV (64-wide) + QS, K^T V
+    with torch.no_grad():
+        report(f"lsm_scalar fwd T={T} H={H} D={D}", timeit(fwd), bytes_=6 * elt, flops=1.5 * intra)
+    o = fwd()
+
+    def bwd():
+        qkv.grad = None
+        o.backward(go, retain_graph=True)
+    report(f"lsm_scalar bwd T={T} H={H} D={D}", timeit(bwd), bytes_=15 * elt, flops=3.5 * intra)
+
+
+def bench_elementwise(which, size):
+    from .. import ops
+    from ..ops import cuda as K
+    dev = torch.device("cuda", 0)
+    T = 8192 if size == "small" else 16384
+    h, f, H, D = 2048, 8192, 16, 128
+    if which in ("norm", "all"):
+        x = torch.randn(T, h, device=dev).bfloat16().requires_grad_(True)
+        r = torch.randn(T, h, device=dev).bfloat16().requires_grad_(True)
+        w = torch.ones(h, device=dev).bfloat16().requires_grad_(True)
+        with torch.no_grad():
+            report("add_rms_norm fwd", timeit(lambda: ops.add_rms_norm(x, r, w, 1e-6)), bytes_=4 * T * h * 2)
+        y, ro = ops.add_rms_norm(x, r, w, 1e-6)
+        gy = torch.randn_like(y)
+        report("add_rms_norm bwd", timeit(lambda: torch.autograd.grad([y, ro], [x, w], [gy, gy], retain_graph=True)),
+               bytes_=4 * T * h * 2)
+    if which in ("headnorm", "all"):
+        o = torch.randn(1, T, H, D, device=dev).bfloat16().requires_grad_(True)
+        gt = torch.randn(1, T, H * D, device=dev).bfloat16().requires_grad_(True)
+        w = torch.ones(D, device=dev).bfloat16().requires_grad_(True)
+        with torch.no_grad():
+            report("head_norm_gate fwd", timeit(lambda: ops.head_norm_gate(o, w, gt, 1e-5)), bytes_=3 * T * h * 2)
+        y = ops.head_norm_gate(o, w, gt, 1e-5)
+        gy = torch.randn_like(y)
+        report("head_norm_gate bwd", timeit(lambda: torch.autograd.grad(y, [o, gt, w], gy, retain_graph=True)),
+               bytes_=5 * T * h * 2)
+    if which in ("swiglu", "all"):
+        x = torch.randn(T, 2 * f, device=dev).bfloat16().requires_grad_(True)
+        with torch.no_grad():
+            report("swiglu fwd", timeit(lambda: ops.swiglu(x)), bytes_=3 * T * f * 2)
+        y = ops.swiglu(x)
+        gy = torch.randn_like(y)
+        report("swiglu bwd", timeit(lambda: torch.autograd.grad(y, x, gy, retain_graph=True)), bytes_=5 * T * f * 2)
+    if which in ("ce", "all"):
+        V, Tc = 128256, 2048 if size == "small" else 4096
+        logits = torch.randn(Tc, V, device=dev).bfloat16()
+        lab = torch.randint(0, V, (Tc,), device=dev)
+        loss, lse = torch.empty(Tc, device=dev), torch.empty(Tc, device=dev)
+        report("softmax_ce fwd", timeit(lambda: K.softmax_ce_fwd(logits, lab, loss, lse, -100)), bytes_=Tc * V * 2)
+        gl = torch.ones(Tc, device=dev)
+        report("softmax_ce bwd (in place)", timeit(lambda: K.softmax_ce_bwd(logits, lab, lse, gl, -100)), bytes_=2 * Tc * V * 2)
+    if which in ("adam", "all"):
+        n = (64 << 20) if size == "small" else (512 << 20)
+        p = torch.zeros(n, device=dev, dtype=torch.bfloat16)
+        m32, g, m, v = (torch.zeros(n, device=dev) for _ in range(4))
+        report(f"fused_adam n={n >> 20}Mi", timeit(lambda: K.fused_adam(p, m32, g, m, v, 1e-4, 0.9, 0.95, 1e-8, 0.1, 0.1, 0.05, 1.0)),
+               bytes_=n * 30)
+    if which in ("conv", "all"):
+        Dc = 6144
+        x = torch.randn(1, T, Dc, device=dev).bfloat16().requires_grad_(True)
+        w = torch.randn(Dc, 4, device=dev).bfloat16().requires_grad_(True)
+        with torch.no_grad():
+            report("causal_conv1d fwd", timeit(lambda: ops.causal_conv1d(x, w)), bytes_=2 * T * Dc * 2)
+        y = ops.causal_conv1d(x, w)[0]
+        gy = torch.randn_like(y)
+        report("causal_conv1d bwd", timeit(lambda: torch.autograd.grad(y, [x, w], gy, retain_graph=True)), bytes_=3 * T * Dc * 2)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", default="all")
+    ap.add_argument("--size", default="full", choices=["small", "full"])
+    a = ap.parse_args()
+    torch.cuda.set_device(0)
+    print(f"peaks: {peaks()}")
+    if a.kernel in ("gemm", "all"):
+        bench_gemm(a.size)
+    if a.kernel in ("lsm", "all"):
+        bench_lsm(a.size)
+    if a.kernel in ("norm", "headnorm", "swiglu", "ce", "adam", "conv", "all"):
+        bench_elementwise(a.kernel, a.size)
+
+
+if __name__ == "__main__":
+    main()
