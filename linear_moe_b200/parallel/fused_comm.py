@@ -151,3 +151,69 @@ def init_workspaces(mesh, cfg=None, tc=None):
         dk, dv = cfg.key_dim // cfg.num_attention_heads, cfg.value_dim // cfg.num_attention_heads
         mb = tc.micro_batch_size if tc is not None else 1
         _LASP[cp.name] = LaspWorkspace(cp, mb * H * dk * dv, device)
+
+
+# ---------------------------------------------------------------------------------------------
+# ZeRO-1: fused reduce-scatter + Adam + all-gather over NVLS (csrc/zero_comm.cu)
+# ---------------------------------------------------------------------------------------------
+class _ZeroArgs(ctypes.Structure):
+    _fields_ = [("grads", ctypes.c_void_p), ("grads_mc", ctypes.c_void_p), ("peer_grads", ctypes.c_void_p),
+                ("params", ctypes.c_void_p), ("params_mc", ctypes.c_void_p), ("peer_params", ctypes.c_void_p),
+                ("peer_flags", ctypes.c_void_p), ("status", ctypes.c_void_p), ("sumsq", ctypes.c_void_p),
+                ("done_ctr", ctypes.c_void_p), ("master", ctypes.c_void_p), ("exp_avg", ctypes.c_void_p),
+                ("exp_avg_sq", ctypes.c_void_p), ("lo", ctypes.c_longlong), ("hi", ctypes.c_longlong),
+                ("rank", ctypes.c_int), ("world", ctypes.c_int), ("epoch", ctypes.c_int), ("grad_scale", ctypes.c_float),
+                ("lr", ctypes.c_float), ("b1", ctypes.c_float), ("b2", ctypes.c_float), ("eps", ctypes.c_float),
+                ("wd", ctypes.c_float), ("bc1", ctypes.c_float), ("bc2", ctypes.c_float), ("gscale", ctypes.c_float),
+                ("spin_limit", ctypes.c_longlong)]
+
+
+class ZeroBufferWorkspace:
+    """Symmetric parameter (bf16) and gradient (fp32) storage of one flat optimizer buffer plus the flags of its two
+    barriers.  ``reduce`` and ``adam_broadcast`` are the two kernel launches of a fused ZeRO-1 step."""
+
+    def __init__(self, group, numel: int, device, spin_limit: int = 4_000_000, use_multicast: bool = True):
+        self.group, self.device, self.numel = group, device, numel
+        self.W, self.rank = group.size, group.rank
+        self.params, self.p_hdl = _symm_empty(numel, torch.bfloat16, device, group)
+        self.grads, self.g_hdl = _symm_empty(numel, torch.float32, device, group)
+        self.flags, self.f_hdl = _symm_empty(2 * self.W + 64, torch.int32, device, group)
+        self.flags.zero_()
+        mc_p = int(getattr(self.p_hdl, "multicast_ptr", 0) or 0)
+        mc_g = int(getattr(self.g_hdl, "multicast_ptr", 0) or 0)
+        self.mc_params, self.mc_grads = (mc_p, mc_g) if (use_multicast and mc_p and mc_g) else (0, 0)
+        self.peer_params = torch.tensor(list(self.p_hdl.buffer_ptrs), dtype=torch.int64, device=device)
+        self.peer_grads = torch.tensor(list(self.g_hdl.buffer_ptrs), dtype=torch.int64, device=device)
+        self.peer_flags = torch.tensor(list(self.f_hdl.buffer_ptrs), dtype=torch.int64, device=device)
+        self.sumsq = torch.zeros(1, dtype=torch.float32, device=device)
+        self.done_ctr = torch.zeros(1, dtype=torch.int32, device=device)
+        self.epoch = 0
+        self.spin_limit = spin_limit
+        torch.cuda.synchronize()
+        dist.barrier(group=group.pg)
+
+    def _args(self, shard) -> _ZeroArgs:
+        a = _ZeroArgs()
+        a.grads, a.grads_mc, a.peer_grads = self.grads.data_ptr(), self.mc_grads, self.peer_grads.data_ptr()
+        a.params, a.params_mc, a.peer_params = self.params.data_ptr(), self.mc_params, self.peer_params.data_ptr()
+        a.peer_flags, a.status = self.peer_flags.data_ptr(), status_word(self.device).data_ptr()
+        a.sumsq, a.done_ctr = self.sumsq.data_ptr(), self.done_ctr.data_ptr()
+        a.lo, a.hi = shard
+        a.rank, a.world, a.epoch = self.rank, self.W, self.epoch
+        a.spin_limit = self.spin_limit
+        return a
+
+    def reduce(self, shard, grad_scale: float):
+        from ..ops import cuda as K
+        self.epoch += 1
+        self.sumsq.zero_()
+        a = self._args(shard)
+        a.grad_scale = grad_scale
+        K._check(K.lib().lmoe_zero_reduce(ctypes.byref(a), ctypes.c_int(K.NUM_SMS * 4), K._st()), "zero_reduce")
+
+    def adam_broadcast(self, shard, master, exp_avg, exp_avg_sq, lr, b1, b2, eps, wd, bc1, bc2, gscale):
+        from ..ops import cuda as K
+        a = self._args(shard)
+        a.master, a.exp_avg, a.exp_avg_sq = master.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr()
+        a.lr, a.b1, a.b2, a.eps, a.wd, a.bc1, a.bc2, a.gscale = lr, b1, b2, eps, wd, bc1, bc2, gscale
+        K._check(K.lib().lmoe_zero_adam_bcast(ctypes.byref(a), ctypes.c_int(K.NUM_SMS * 4), K._st()), "zero_adam_bcast")

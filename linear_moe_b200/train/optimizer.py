@@ -54,7 +54,7 @@ class FlatBuffer:
     """One flat parameter/gradient buffer and its optimizer state."""
 
     def __init__(self, slots: List[Tuple[str, nn.Parameter]], *, expert: bool, weight_decay: bool, group: Group,
-                 grad_scale: float, zero1: bool, master: bool):
+                 grad_scale: float, zero1: bool, master: bool, symmetric: bool = False):
         self.expert, self.weight_decay, self.group, self.grad_scale, self.zero1 = expert, weight_decay, group, grad_scale, zero1
         p0 = slots[0][1]
         self.device, self.dtype = p0.device, p0.dtype
@@ -65,8 +65,17 @@ class FlatBuffer:
             off += (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
         shard_mult = _ALIGN * (group.size if zero1 else 1)
         self.numel = (off + shard_mult - 1) // shard_mult * shard_mult
-        self.params = torch.zeros(self.numel, dtype=self.dtype, device=self.device)
-        self.grads = torch.zeros(self.numel, dtype=torch.float32, device=self.device)
+        self.fused = None
+        if symmetric and self.dtype == torch.bfloat16:
+            # parameters and gradients live in symmetric memory so that the fused ZeRO-1 kernels can reduce the
+            # gradients and broadcast the parameters through NVSwitch without NCCL
+            from ..parallel.fused_comm import ZeroBufferWorkspace
+            self.fused = ZeroBufferWorkspace(group, self.numel, self.device)
+            self.params, self.grads = self.fused.params, self.fused.grads
+            self.params.zero_(), self.grads.zero_()
+        else:
+            self.params = torch.zeros(self.numel, dtype=self.dtype, device=self.device)
+            self.grads = torch.zeros(self.numel, dtype=torch.float32, device=self.device)
         for s in self.slots:
             view = self.params[s.start:s.start + s.numel].view_as(s.param)
             view.copy_(s.param.data)
@@ -125,7 +134,8 @@ class MixedPrecisionAdam:
                 by_dtype.setdefault(p.dtype, []).append((n, p))
             for dt, sl in by_dtype.items():
                 self.buffers.append(FlatBuffer(sl, expert=expert, weight_decay=wd, group=g, grad_scale=1.0 / dpcp,
-                                               zero1=self.zero1, master=dt != torch.float32))
+                                               zero1=self.zero1, master=dt != torch.float32,
+                                               symmetric=self._want_fused(g, dt)))
         self._hooks = []
         for n, p in uniq:
             self._hooks.append(p.register_post_accumulate_grad_hook(self._accumulate))
@@ -136,6 +146,12 @@ class MixedPrecisionAdam:
             self._growth_tracker, self._hysteresis = 0, tc.hysteresis
         self.dynamic_scale = tc.fp16 and not tc.loss_scale
         self.skipped_iters = 0
+
+    def _want_fused(self, group: Group, dtype) -> bool:
+        """Symmetric-memory buffers + fused NVLS kernels: ZeRO-1 on a multi-GPU NCCL group with bf16 parameters."""
+        if not (self.zero1 and self.fused_comm and not group.is_trivial and dtype == torch.bfloat16):
+            return False
+        return torch.cuda.is_available() and dist.is_initialized() and dist.get_backend() == "nccl"
 
     # ------------------------------------------------------------------
     @staticmethod
@@ -176,6 +192,10 @@ class MixedPrecisionAdam:
         shard under ZeRO-1 (the rest of the buffer is then stale until the next zero_grad)."""
         self._reduce_sequence_parallel_grads()
         for b in self.buffers:
+            if b.fused is not None:
+                # barrier + in-switch reduce-scatter + scale + partial sum of squares, one kernel, no NCCL
+                b.fused.reduce(b.shard, b.grad_scale)
+                continue
             if b.grad_scale != 1.0:
                 b.grads.mul_(b.grad_scale)
             g = b.group
@@ -246,6 +266,10 @@ class MixedPrecisionAdam:
             wd = weight_decay if b.weight_decay else 0.0
             g = b.grads[lo:hi]
             pshard = b.params[lo:hi]
+            if b.fused is not None:
+                # Adam on the shard + multicast store of the bf16 parameters to every rank + barrier, one kernel
+                b.fused.adam_broadcast(b.shard, b.master, b.exp_avg, b.exp_avg_sq, lr, b1, b2, eps, wd, bc1, bc2, gscale)
+                continue
             if g.is_cuda:
                 from ..ops import cuda as K
                 K.fused_adam(pshard, b.master, g, b.exp_avg, b.exp_avg_sq, lr, b1, b2, eps, wd, bc1, bc2, gscale)

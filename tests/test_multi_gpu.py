@@ -62,3 +62,43 @@ def test_lasp2_fused_matches_single_gpu(D, decay, T):
         for eo, eg in errs:
             assert eo < 3e-2 * so, (errs, so)
             assert eg < 4e-2 * sg, (errs, sg)
+
+
+def _zero_worker(rank, world, multicast):
+    from linear_moe_b200.config.model_config import ParallelConfig, TrainConfig
+    from linear_moe_b200.config.presets import get_preset
+    from linear_moe_b200.dist.mesh import Mesh
+    from linear_moe_b200.parallel import fused_comm
+    from linear_moe_b200.train.loop import Trainer
+    dev = torch.device("cuda", rank)
+    if not multicast:
+        orig = fused_comm.ZeroBufferWorkspace.__init__
+        fused_comm.ZeroBufferWorkspace.__init__ = lambda self, g, n, d, **kw: orig(self, g, n, d, use_multicast=False)
+    cfg = get_preset("bench-lasp2-llama3-1b", num_layers=2, layer_type_list="LL", vocab_size=2048, hidden_size=256,
+                     num_attention_heads=2, ffn_hidden_size=512)
+    outs = {}
+    for fused in (True, False):
+        par = ParallelConfig(use_distributed_optimizer=True, fused_comm=fused)
+        mesh = Mesh(par)
+        tc = TrainConfig(micro_batch_size=1, global_batch_size=world, seq_length=256, train_iters=4, bf16=True,
+                         log_interval=1000, lr=1e-3, min_lr=1e-3, lr_decay_style="constant", seed=7)
+        tr = Trainer(cfg, par, tc, mesh, device=dev)
+        assert (tr.optimizer.buffers[0].fused is not None) == fused
+        losses = [float(tr.train_step()["lm loss"]) for _ in range(4)]
+        torch.cuda.synchronize()
+        fused_comm.check_status("zero test")
+        outs[fused] = (losses, torch.cat([b.params.float().cpu() for b in tr.optimizer.buffers]))
+    mc = tr.optimizer.buffers[0].fused is None and None
+    return outs[True][0], outs[False][0], (outs[True][1] - outs[False][1]).abs().max().item(), outs[False][1].abs().max().item()
+
+
+@pytest.mark.parametrize("multicast", [True, False])
+def test_zero1_fused_matches_nccl(multicast):
+    """ZeRO-1 step through the fused NVLS kernels (multimem reduce / multimem store) or their peer-pointer variant
+    equals the reduce-scatter / Adam / all-gather path on NCCL."""
+    _need_gpus(2)
+    outs = run_distributed(_zero_worker, 2, backend="nccl", multicast=multicast)
+    for lf, ln, dmax, pmax in outs:
+        assert all(abs(a - b) < 2e-2 for a, b in zip(lf, ln)), (lf, ln)
+        assert dmax < 2e-2 * pmax + 4e-3, (dmax, pmax)
+    assert outs[0][0][-1] < outs[0][0][0]
