@@ -40,7 +40,8 @@ def parse():
     p.add_argument("--tokens-per-gpu", type=int, default=TOKENS_PER_GPU)
     p.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (marks the result invalid)")
     p.add_argument("--no-e2e", action="store_true")
-    p.add_argument("--zero1", action="store_true")
+    p.add_argument("--zero1", action=argparse.BooleanOptionalAction, default=True,
+                   help="distributed optimizer (ZeRO-1) through the fused NVLS kernels when N > 1 (the reference launchers default to DO=true)")
     return p.parse_args()
 
 

@@ -38,10 +38,13 @@ def _entry(rank, world, port, fn, kwargs, outdir, backend):
 
 def run_distributed(fn, world: int, backend: str = "gloo", **kwargs):
     """``fn(rank, world, **kwargs)`` must be importable (module level).  Returns the list of outputs."""
-    with tempfile.TemporaryDirectory() as d:
-        try:
-            mp.spawn(_entry, args=(world, _free_port(), fn, kwargs, d, backend), nprocs=world, join=True)
-        except Exception:
-            errs = [open(os.path.join(d, f)).read() for f in sorted(os.listdir(d)) if f.startswith("err_")]
-            raise RuntimeError("distributed worker failed:\n" + "\n".join(errs))
-        return [torch.load(os.path.join(d, f"out_{r}.pt"), weights_only=False) for r in range(world)]
+    for attempt in range(4):
+        with tempfile.TemporaryDirectory() as d:
+            try:
+                mp.spawn(_entry, args=(world, _free_port(), fn, kwargs, d, backend), nprocs=world, join=True)
+            except Exception:
+                errs = [open(os.path.join(d, f)).read() for f in sorted(os.listdir(d)) if f.startswith("err_")]
+                if attempt < 3 and any("EADDRINUSE" in e for e in errs):
+                    continue                      # the probed port was taken in the meantime: pick another one
+                raise RuntimeError("distributed worker failed:\n" + "\n".join(errs))
+            return [torch.load(os.path.join(d, f"out_{r}.pt"), weights_only=False) for r in range(world)]
