@@ -676,8 +676,99 @@ def lsm_scalar(q, k, v, g, scale, initial_state, chunk_size):
     return _LsmScalar.apply(q, k, v, g, scale, initial_state)
 
 
+class _GlaArgs(ctypes.Structure):
+    _fields_ = ([(n, ctypes.c_void_p) for n in ("q", "k", "v", "d_o")] +
+                [(n, ctypes.c_int64) for n in ("qs_b", "qs_t", "qs_h", "ks_b", "ks_t", "ks_h", "vs_b", "vs_t", "vs_h")] +
+                [(n, ctypes.c_void_p) for n in ("o", "dq", "dk", "dv")] +
+                [(n, ctypes.c_int64) for n in ("dqs_b", "dqs_t", "dqs_h", "dks_b", "dks_t", "dks_h", "dvs_b", "dvs_t", "dvs_h")] +
+                [("gk", ctypes.c_void_p), ("scale", ctypes.c_float)] +
+                [(n, ctypes.c_int) for n in ("B", "T", "H", "G", "cpg")] +
+                [("states", ctypes.c_void_p), ("gdecay", ctypes.c_void_p)])
+
+
+def _gla_args(q, k, v, gk, scale, B, T, H, G, cpg, states, gdecay, d_o=None, o=None, dq=None, dk=None, dv=None):
+    a = _GlaArgs()
+    a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    a.d_o = 0 if d_o is None else d_o.data_ptr()
+    a.qs_b, a.qs_t, a.qs_h = q.stride(0), q.stride(1), q.stride(2)
+    a.ks_b, a.ks_t, a.ks_h = k.stride(0), k.stride(1), k.stride(2)
+    a.vs_b, a.vs_t, a.vs_h = v.stride(0), v.stride(1), v.stride(2)
+    a.o = 0 if o is None else o.data_ptr()
+    for name, t in (("dq", dq), ("dk", dk), ("dv", dv)):
+        setattr(a, name, 0 if t is None else t.data_ptr())
+        if t is not None:
+            setattr(a, name + "s_b", t.stride(0)), setattr(a, name + "s_t", t.stride(1)), setattr(a, name + "s_h", t.stride(2))
+    a.gk, a.scale = gk.data_ptr(), float(scale)
+    a.B, a.T, a.H, a.G, a.cpg = B, T, H, G, cpg
+    a.states = states.data_ptr()
+    a.gdecay = 0 if gdecay is None else gdecay.data_ptr()
+    return a
+
+
+def _gla_launch(which, D, args):
+    _check(lib().lmoe_gla_launch(_i32(which), _i32(D), ctypes.byref(args), _st()), f"gla[{which}]")
+
+
+def _gla_combine(rev, states, gdecay, seed, final_out, BH, G, D):
+    _check(lib().lmoe_gla_combine(_i32(rev), _p(states), _p(gdecay), _p(seed), _p(final_out), _i32(BH), _i32(G), _i32(D),
+                                  _st()), "gla_combine")
+
+
+class _LsmVector(torch.autograd.Function):
+    """o, S_T = linear attention with a log decay per key channel.  q,k,v bf16 [B,T,H,D]; gk [B,T,H,D]."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, gk, scale, init):
+        B, T, H, D = q.shape
+        q, k, v = _inner_contig(q), _inner_contig(k), _inner_contig(v)
+        gf = gk.float().contiguous()
+        G, cpg = lsm_groups(B, H, T)
+        states = torch.empty(B, H, G, D, D, dtype=torch.float32, device=q.device)
+        gdecay = torch.empty(B, H, G, D, dtype=torch.float32, device=q.device)
+        o = torch.empty(B, T, H, D, dtype=q.dtype, device=q.device)
+        final = torch.empty(B, H, D, D, dtype=torch.float32, device=q.device)
+        seed = None if init is None else init.float().contiguous()
+        a = _gla_args(q, k, v, gf, scale, B, T, H, G, cpg, states, gdecay, o=o)
+        _gla_launch(0, D, a)
+        _gla_combine(0, states, gdecay, seed, final, B * H, G, D)
+        _gla_launch(2, D, a)
+        ctx.save_for_backward(q, k, v, gf, states, gdecay, final)
+        ctx.scale, ctx.grid, ctx.has_init, ctx.g_dtype = scale, (G, cpg), init is not None, gk.dtype
+        return o, final
+
+    @staticmethod
+    def backward(ctx, d_o, dfinal):
+        q, k, v, gf, states, gdecay, final = ctx.saved_tensors
+        B, T, H, D = q.shape
+        G, cpg = ctx.grid
+        d_o = d_o.contiguous().to(q.dtype)
+        dqkv = torch.empty(B, T, H, 3 * D, dtype=q.dtype, device=q.device)
+        dq, dk, dv = dqkv[..., :D], dqkv[..., D:2 * D], dqkv[..., 2 * D:]
+        dstates = torch.empty_like(states)
+        dinit = torch.empty(B, H, D, D, dtype=torch.float32, device=q.device) if ctx.has_init else None
+        a = _gla_args(q, k, v, gf, ctx.scale, B, T, H, G, cpg, states, None, d_o=d_o, dq=dq)
+        _gla_launch(3, D, a)
+        a2 = _gla_args(q, k, v, gf, ctx.scale, B, T, H, G, cpg, dstates, None, d_o=d_o, dk=dk, dv=dv)
+        _gla_launch(1, D, a2)
+        seed = None if dfinal is None else dfinal.float().contiguous()
+        _gla_combine(1, dstates, gdecay, seed, dinit, B * H, G, D)
+        _gla_launch(4, D, a2)
+        # d gk_t = sum_{i>=t} q_i . dq_i - sum_{j>=t} k_j . dk_j per channel (+ <S_T, dS_T> rows with a final-state gradient)
+        s = q.float() * dq.float() - k.float() * dk.float()
+        dg = s.flip(1).cumsum(1).flip(1)
+        if dfinal is not None:
+            dg = dg + (final * dfinal.float()).sum(-1)[:, None]
+        return dq, dk, dv, dg.to(ctx.g_dtype), None, dinit
+
+
 def lsm_vector(q, k, v, gk, scale, initial_state, bonus, chunk_size):
-    return LT.chunk_vector_gated(q, k, v, gk, scale, initial_state, 16, bonus)
+    D = q.shape[-1]
+    ok = (bonus is None and q.dtype == torch.bfloat16 and k.dtype == q.dtype and v.dtype == q.dtype
+          and v.shape[-1] == D and k.shape[-1] == D and D in (64, 128))
+    if not ok:
+        return LT.chunk_vector_gated(q, k, v, gk, scale, initial_state, 16, bonus)
+    scale = D ** -0.5 if scale is None else scale
+    return _LsmVector.apply(q, k, v, gk, scale, initial_state)
 
 
 def lsm_delta(q, k, v, beta, g, scale, initial_state, chunk_size):

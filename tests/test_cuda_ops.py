@@ -227,3 +227,25 @@ def test_lsm_scalar(D, gmode, T, with_state):
     close(S, S2, 3e-2, 2e-2 * S2.abs().max().item(), "final state")
     for name, a, b in zip(["dq", "dk", "dv", "d3", "d4"], gk, gr):
         close(a, b, 5e-2, 3e-2 * b.abs().max().item(), name)
+
+
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("T,with_state", [(1000, False), (200, True)])
+def test_lsm_vector_gla(D, T, with_state):
+    torch.manual_seed(9)
+    B, H = 2, 3
+    qkv = (0.5 * torch.randn(B, T, H, 3 * D, device=dev())).to(torch.bfloat16)
+    q, k, v = qkv.split(D, dim=-1)
+    gk = torch.nn.functional.logsigmoid(2.0 * torch.randn(B, T, H, D, device=dev())) / 4.0      # strong decays
+    S0 = 0.3 * torch.randn(B, H, D, D, device=dev()) if with_state else None
+    go = torch.randn(B, T, H, D, device=dev(), dtype=torch.bfloat16)
+    gS = 0.1 * torch.randn(B, H, D, D, device=dev()) if with_state else None
+    ins = [q, k, v, gk] + ([S0] if with_state else [])
+    f_k = lambda q, k, v, g, s=None: ops.lsm_vector(q, k, v, g, None, s, None, 64)
+    f_r = lambda q, k, v, g, s=None: LT.chunk_vector_gated(q, k, v, g, None, s, 16)
+    (o, S), gk_ = grads(f_k, ins, (go, gS))
+    (o2, S2), gr = grads(f_r, [t.float() for t in ins], (go.float(), gS))
+    close(o, o2, 3e-2, 2e-2 * o2.abs().max().item(), "o")
+    close(S, S2, 3e-2, 2e-2 * S2.abs().max().item(), "final state")
+    for name, a, b in zip(["dq", "dk", "dv", "dgk", "dS0"], gk_, gr):
+        close(a, b, 5e-2, 3e-2 * b.abs().max().item(), name)
