@@ -79,3 +79,83 @@ def supports_swiglu(x, w) -> bool:
 
 def supports_grouped(x, w1, w2) -> bool:
     return False
+
+
+# ---------------------------------------------------------------------------------------------
+# grouped / layout-general GEMMs (csrc/gemm_grouped.cu)
+# ---------------------------------------------------------------------------------------------
+def _gg(A, a_mn, B, b_mn, C, mode, M, N, Kd, groups, offs, c_stride):
+    from . import cuda as K
+    rc = K.lib().lmoe_gemm_grouped(
+        K._p(A), ctypes.c_int(A.shape[0]), ctypes.c_int(A.shape[1]), ctypes.c_int(A.stride(0)), ctypes.c_int(int(a_mn)),
+        K._p(B), ctypes.c_int(B.shape[0]), ctypes.c_int(B.shape[1]), ctypes.c_int(B.stride(0)), ctypes.c_int(int(b_mn)),
+        K._p(C), ctypes.c_int(C.stride(-2)), ctypes.c_int(mode), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(Kd),
+        ctypes.c_int(groups), K._p(offs), ctypes.c_longlong(c_stride), K._p(_err(A.device)), ctypes.c_int(K.NUM_SMS), K._st())
+    K._check(rc, "gemm_grouped")
+    return C
+
+
+def gemm_general(a: torch.Tensor, b: torch.Tensor, a_mn: bool = False, b_mn: bool = False) -> torch.Tensor:
+    """Dense ``C[M,N]``.  ``a`` is ``[M,K]`` (or ``[K,M]`` if ``a_mn``); ``b`` is ``[N,K]`` (or ``[K,N]`` if ``b_mn``)."""
+    M, Kd = (a.shape[1], a.shape[0]) if a_mn else a.shape
+    N = b.shape[1] if b_mn else b.shape[0]
+    C = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    return _gg(a, a_mn, b, b_mn, C, 0, M, N, Kd, 0, None, 0)
+
+
+def padded_offsets(counts: torch.Tensor, align: int = 128) -> torch.Tensor:
+    """Per-expert token counts -> int32 row offsets ``[E+1]`` with every segment padded to ``align`` rows (device op)."""
+    padded = (counts + align - 1) // align * align
+    offs = torch.zeros(counts.numel() + 1, dtype=torch.int32, device=counts.device)
+    offs[1:] = torch.cumsum(padded, 0).to(torch.int32)
+    return offs
+
+
+class GroupedLinear(torch.autograd.Function):
+    """``y[rows of expert e] = x[rows of expert e] @ w[e]`` for ``w [E, K, N]`` over a padded expert-sorted buffer.
+    Forward, dgrad and wgrad are three launches of the grouped tcgen05 kernel; the expert offsets never leave the device."""
+
+    @staticmethod
+    def forward(ctx, x, w, offs):
+        E, Kd, N = w.shape
+        y = torch.empty(x.shape[0], N, dtype=torch.bfloat16, device=x.device)
+        _gg(x, False, w.view(E * Kd, N), True, y, 1, 0, N, Kd, E, offs, 0)
+        ctx.save_for_backward(x, w, offs)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, offs = ctx.saved_tensors
+        E, Kd, N = w.shape
+        dy = dy.contiguous()
+        dx = torch.empty_like(x)
+        _gg(dy, False, w.view(E * Kd, N), False, dx, 1, 0, Kd, N, E, offs, 0)              # dy @ w[e]^T
+        dw = torch.empty_like(w)
+        _gg(x, True, dy, True, dw, 2, Kd, N, 0, E, offs, Kd * N)                           # x_e^T @ dy_e
+        return dx, dw, None
+
+
+def supports_grouped(x, w1, w2) -> bool:
+    h, f2 = w1.shape[1], w1.shape[2]
+    return (available() and x.dtype == torch.bfloat16 and w1.dtype == torch.bfloat16 and w2.dtype == torch.bfloat16
+            and h % 8 == 0 and f2 % 16 == 0 and x.is_contiguous())
+
+
+def grouped_mlp(x_sorted: torch.Tensor, tokens_per_expert: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor) -> torch.Tensor:
+    """Expert-sorted tokens ``[T, h]`` through per-expert SwiGLU MLPs (``w1 [E,h,2f]``, ``w2 [E,f,h]``).  Tokens are
+    scattered into a 128-row-padded buffer (index arithmetic on the device only), run through two grouped GEMMs with the
+    SwiGLU kernel in between, and gathered back."""
+    from . import cuda as K
+    E = w1.shape[0]
+    T, h = x_sorted.shape
+    counts = tokens_per_expert.to(torch.int64)
+    offs = padded_offsets(counts)
+    start = torch.cumsum(counts, 0) - counts                                   # unpadded start of each expert
+    eid = torch.repeat_interleave(torch.arange(E, device=x_sorted.device), counts, output_size=T)
+    dest = offs[:-1].to(torch.int64)[eid] + (torch.arange(T, device=x_sorted.device) - start[eid])
+    Tp = (T + E * 127 + 127) // 128 * 128
+    xp = torch.zeros(Tp, h, dtype=x_sorted.dtype, device=x_sorted.device).index_copy(0, dest, x_sorted)
+    y1 = GroupedLinear.apply(xp, w1, offs)
+    act = K.swiglu(y1)
+    y2 = GroupedLinear.apply(act, w2, offs)
+    return y2.index_select(0, dest)
