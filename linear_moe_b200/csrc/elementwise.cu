@@ -139,14 +139,23 @@ __global__ void rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __restric
     }
 }
 
-// out[c] = sum_p partial[p, c]
+// out[c] = sum_p partial[p, c].  Block = 32 columns x 8 row-slices; the slices are summed through shared memory.
 template <typename T>
 __global__ void reduce_partials_kernel(const float* __restrict__ partial, T* __restrict__ out, int P, int N) {
-    int c = blockIdx.x * blockDim.x + threadIdx.x;
-    if (c >= N) return;
+    __shared__ float sm[8][33];
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int c = blockIdx.x * 32 + tx;
     float s = 0.f;
-    for (int p = 0; p < P; ++p) s += partial[(int64_t)p * N + c];
-    out[c] = from_f<T>(s);
+    if (c < N)
+        for (int p = ty; p < P; p += 8) s += partial[(int64_t)p * N + c];
+    sm[ty][tx] = s;
+    __syncthreads();
+    if (ty == 0 && c < N) {
+        float t = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) t += sm[j][tx];
+        out[c] = from_f<T>(t);
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -568,6 +577,55 @@ __global__ void causal_conv1d_fwd_kernel(const T* __restrict__ x, const T* __res
     }
 }
 
+// Vectorised forward: a thread owns VN consecutive channels (one 16-byte access per token) and walks a run of
+// `trun` tokens with the last K-1 rows kept in registers, so every input row is read once per thread.
+template <typename T, int K>
+__global__ void causal_conv1d_fwd_vec_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ bias,
+                                             const T* __restrict__ init, T* __restrict__ y, int B, int Tlen, int D,
+                                             int act, int trun) {
+    constexpr int VN = Vec<T>::N;
+    const int dv = blockIdx.x * blockDim.x + threadIdx.x;
+    if (dv * VN >= D) return;
+    const int d0 = dv * VN, b = blockIdx.z;
+    const int t0 = blockIdx.y * trun, t1 = min(Tlen, t0 + trun);
+    float wk[VN][K], bv[VN];
+#pragma unroll
+    for (int e = 0; e < VN; ++e) {
+        bv[e] = bias != nullptr ? to_f(bias[d0 + e]) : 0.f;
+#pragma unroll
+        for (int k = 0; k < K; ++k) wk[e][k] = to_f(w[(d0 + e) * K + k]);
+    }
+    float hist[K - 1][VN];                                   // rows t-(K-1) .. t-1
+#pragma unroll
+    for (int j = 0; j < K - 1; ++j) {
+        const int ts = t0 - (K - 1) + j;
+        Vec<T> v;
+        bool have = false;
+        if (ts >= 0) { v.load(x + ((int64_t)b * Tlen + ts) * D + d0); have = true; }
+        else if (init != nullptr) { v.load(init + ((int64_t)b * (K - 1) + (K - 1 + ts)) * D + d0); have = true; }
+#pragma unroll
+        for (int e = 0; e < VN; ++e) hist[j][e] = have ? v.get(e) : 0.f;
+    }
+    for (int t = t0; t < t1; ++t) {
+        Vec<T> cur, out;
+        cur.load(x + ((int64_t)b * Tlen + t) * D + d0);
+#pragma unroll
+        for (int e = 0; e < VN; ++e) {
+            float acc = bv[e] + cur.get(e) * wk[e][K - 1];
+#pragma unroll
+            for (int j = 0; j < K - 1; ++j) acc += hist[j][e] * wk[e][j];
+            out.set(e, act ? silu_f(acc) : acc);
+        }
+        out.store(y + ((int64_t)b * Tlen + t) * D + d0);
+#pragma unroll
+        for (int j = 0; j + 1 < K - 1; ++j)
+#pragma unroll
+            for (int e = 0; e < VN; ++e) hist[j][e] = hist[j + 1][e];
+#pragma unroll
+        for (int e = 0; e < VN; ++e) hist[K - 2][e] = cur.get(e);
+    }
+}
+
 // Backward: dx[b,t,d] = sum_k dpre[b, t + (K-1-k), d] * w[d,k]; dw[d,k] = sum dpre[b,t,d] * x[b, t-(K-1)+k, d];
 // dpre = dy * dsilu(pre) is recomputed.  Blocks tile (b, time-chunk) x channel; dw/dbias via atomics.
 template <typename T, int K>
@@ -632,6 +690,123 @@ __global__ void causal_conv1d_bwd_kernel(const T* __restrict__ dy, const T* __re
 #pragma unroll
     for (int k = 0; k < K; ++k) atomicAdd(&dw[d * K + k], dwacc[k]);
     if (dbias != nullptr) atomicAdd(&dbias[d], dbacc);
+}
+
+// Vectorised backward: a thread owns VN channels and a run of tokens [t0, t1); it walks t0 .. t1+K-2 recomputing the
+// pre-activation from a K-row window of x, keeps the last K values of dpre = dy * dsilu(pre), emits dx[t-(K-1)] as soon as
+// its K contributions are known, and accumulates dw / dbias for its own tokens in registers (atomics once per thread).
+template <typename T, int K>
+__global__ void causal_conv1d_bwd_vec_kernel(const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
+                                             const T* __restrict__ bias, const T* __restrict__ init, T* __restrict__ dx,
+                                             float* __restrict__ dw, float* __restrict__ dbias, T* __restrict__ dinit,
+                                             int B, int Tlen, int D, int act, int trun) {
+    constexpr int VN = Vec<T>::N;
+    const int dvec = blockIdx.x * blockDim.x + threadIdx.x;
+    if (dvec * VN >= D) return;
+    const int d0 = dvec * VN, b = blockIdx.z;
+    const int t0 = blockIdx.y * trun, t1 = min(Tlen, t0 + trun);
+    float wk[VN][K], bv[VN], dwacc[VN][K], dbacc[VN];
+#pragma unroll
+    for (int e = 0; e < VN; ++e) {
+        bv[e] = bias != nullptr ? to_f(bias[d0 + e]) : 0.f;
+        dbacc[e] = 0.f;
+#pragma unroll
+        for (int k = 0; k < K; ++k) { wk[e][k] = to_f(w[(d0 + e) * K + k]); dwacc[e][k] = 0.f; }
+    }
+    float xw[K][VN];                                         // xw[k] = x[t-(K-1)+k]
+    float dp[K][VN];                                         // dp[k] = dpre[t-(K-1)+k]
+#pragma unroll
+    for (int k = 0; k < K; ++k)
+#pragma unroll
+        for (int e = 0; e < VN; ++e) { xw[k][e] = 0.f; dp[k][e] = 0.f; }
+    // preload the K-1 rows before t0 into xw[1..K-1] (they shift down by one at the first step)
+#pragma unroll
+    for (int j = 0; j < K - 1; ++j) {
+        const int ts = t0 - (K - 1) + j;
+        Vec<T> v;
+        bool have = false;
+        if (ts >= 0) { v.load(x + ((int64_t)b * Tlen + ts) * D + d0); have = true; }
+        else if (init != nullptr) { v.load(init + ((int64_t)b * (K - 1) + (K - 1 + ts)) * D + d0); have = true; }
+#pragma unroll
+        for (int e = 0; e < VN; ++e) xw[j + 1][e] = have ? v.get(e) : 0.f;
+    }
+    float first_dp[K - 1][VN];                               // dpre[0..K-2] of the sequence (for dinit)
+#pragma unroll
+    for (int j = 0; j < K - 1; ++j)
+#pragma unroll
+        for (int e = 0; e < VN; ++e) first_dp[j][e] = 0.f;
+    for (int t = t0; t < t1 + K - 1; ++t) {
+        // shift windows
+#pragma unroll
+        for (int k = 0; k + 1 < K; ++k)
+#pragma unroll
+            for (int e = 0; e < VN; ++e) { xw[k][e] = xw[k + 1][e]; dp[k][e] = dp[k + 1][e]; }
+        if (t < Tlen) {
+            Vec<T> cur, g;
+            cur.load(x + ((int64_t)b * Tlen + t) * D + d0);
+            g.load(dy + ((int64_t)b * Tlen + t) * D + d0);
+#pragma unroll
+            for (int e = 0; e < VN; ++e) {
+                xw[K - 1][e] = cur.get(e);
+                float gv = g.get(e);
+                if (act) {
+                    float pre = bv[e];
+#pragma unroll
+                    for (int k = 0; k < K; ++k) pre += xw[k][e] * wk[e][k];
+                    gv *= dsilu_f(pre);
+                }
+                dp[K - 1][e] = gv;
+                if (t < t1) {
+                    dbacc[e] += gv;
+#pragma unroll
+                    for (int k = 0; k < K; ++k) dwacc[e][k] += gv * xw[k][e];
+                }
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < VN; ++e) { xw[K - 1][e] = 0.f; dp[K - 1][e] = 0.f; }
+        }
+        if (t0 == 0 && t < K - 1) {
+#pragma unroll
+            for (int j = 0; j < K - 1; ++j)
+                if (j == t)
+#pragma unroll
+                    for (int e = 0; e < VN; ++e) first_dp[j][e] = dp[K - 1][e];
+        }
+        const int tout = t - (K - 1);
+        if (tout >= t0 && tout < t1) {
+            Vec<T> o;
+#pragma unroll
+            for (int e = 0; e < VN; ++e) {
+                float acc = 0.f;
+#pragma unroll
+                for (int k = 0; k < K; ++k) acc += dp[K - 1 - k][e] * wk[e][k];       // dpre[tout + K-1-k] * w[k]
+                o.set(e, acc);
+            }
+            o.store(dx + ((int64_t)b * Tlen + tout) * D + d0);
+        }
+    }
+    if (dinit != nullptr && t0 == 0) {
+#pragma unroll
+        for (int j = 0; j < K - 1; ++j) {
+            Vec<T> o;
+#pragma unroll
+            for (int e = 0; e < VN; ++e) {
+                float acc = 0.f;
+#pragma unroll
+                for (int k = 0; k < K; ++k)
+                    if (k <= j) acc += first_dp[j - k][e] * wk[e][k];
+                o.set(e, acc);
+            }
+            o.store(dinit + ((int64_t)b * (K - 1) + j) * D + d0);
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < VN; ++e) {
+#pragma unroll
+        for (int k = 0; k < K; ++k) atomicAdd(&dw[(d0 + e) * K + k], dwacc[e][k]);
+        if (dbias != nullptr) atomicAdd(&dbias[d0 + e], dbacc[e]);
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -792,7 +967,7 @@ LMOE_API int lmoe_rms_norm_bwd(const void* dy, const void* xin, const void* w, c
         else
             rms_norm_bwd_kernel<T, 8><<<blocks, threads, 0, st>>>((const T*)dy, (const T*)xin, (const T*)w, rstd, (const T*)dres, (T*)dx, dw_partial, (int)rows, N);
         if (dw != nullptr && dw_partial != nullptr)
-            reduce_partials_kernel<T><<<(N + 255) / 256, 256, 0, st>>>(dw_partial, (T*)dw, blocks, N);
+            reduce_partials_kernel<T><<<(N + 31) / 32, 256, 0, st>>>(dw_partial, (T*)dw, blocks, N);
     })
     return (int)cudaGetLastError();
 }
@@ -823,7 +998,7 @@ LMOE_API int lmoe_head_norm_gate_bwd(const void* dy, const void* o, const void* 
         else if (D <= 256) head_norm_gate_bwd_kernel<T, 256><<<blocks, wpb * 32, wpb * 256 * 4, st>>>((const T*)dy, (const T*)o, (const T*)w, (const T*)gate, rstd, (T*)d_o, (T*)dgate, dw_partial, rows, D, do_norm);
         else head_norm_gate_bwd_kernel<T, 512><<<blocks, wpb * 32, wpb * 512 * 4, st>>>((const T*)dy, (const T*)o, (const T*)w, (const T*)gate, rstd, (T*)d_o, (T*)dgate, dw_partial, rows, D, do_norm);
         if (dw != nullptr && dw_partial != nullptr)
-            reduce_partials_kernel<T><<<(D + 255) / 256, 256, 0, st>>>(dw_partial, (T*)dw, blocks, D);
+            reduce_partials_kernel<T><<<(D + 31) / 32, 256, 0, st>>>(dw_partial, (T*)dw, blocks, D);
     })
     return (int)cudaGetLastError();
 }
@@ -920,6 +1095,15 @@ LMOE_API int lmoe_causal_conv1d_fwd(const void* x, const void* w, const void* bi
                                     int Tlen, int D, int K, int act, int dtype, cudaStream_t st) {
     int64_t total = (int64_t)B * Tlen * D;
     DISPATCH_T(dtype, {
+        constexpr int VN = Vec<T>::N;
+        if (D % VN == 0 && K >= 2 && K <= 4) {
+            const int trun = 32;
+            dim3 vgrid((D / VN + 127) / 128, (Tlen + trun - 1) / trun, B);
+            if (K == 4) causal_conv1d_fwd_vec_kernel<T, 4><<<vgrid, 128, 0, st>>>((const T*)x, (const T*)w, (const T*)bias, (const T*)init, (T*)y, B, Tlen, D, act, trun);
+            else if (K == 3) causal_conv1d_fwd_vec_kernel<T, 3><<<vgrid, 128, 0, st>>>((const T*)x, (const T*)w, (const T*)bias, (const T*)init, (T*)y, B, Tlen, D, act, trun);
+            else causal_conv1d_fwd_vec_kernel<T, 2><<<vgrid, 128, 0, st>>>((const T*)x, (const T*)w, (const T*)bias, (const T*)init, (T*)y, B, Tlen, D, act, trun);
+            return (int)cudaGetLastError();
+        }
         int g = grid_for(total, 256);
         if (K == 4) causal_conv1d_fwd_kernel<T, 4><<<g, 256, 0, st>>>((const T*)x, (const T*)w, (const T*)bias, (const T*)init, (T*)y, B, Tlen, D, act);
         else if (K == 3) causal_conv1d_fwd_kernel<T, 3><<<g, 256, 0, st>>>((const T*)x, (const T*)w, (const T*)bias, (const T*)init, (T*)y, B, Tlen, D, act);
@@ -935,6 +1119,15 @@ LMOE_API int lmoe_causal_conv1d_bwd(const void* dy, const void* x, const void* w
     const int tchunk = 128;
     dim3 grid((D + 127) / 128, (Tlen + tchunk - 1) / tchunk, B);
     DISPATCH_T(dtype, {
+        constexpr int VN = Vec<T>::N;
+        if (D % VN == 0 && K >= 2 && K <= 4) {
+            const int trun = 64;
+            dim3 vgrid((D / VN + 63) / 64, (Tlen + trun - 1) / trun, B);
+            if (K == 4) causal_conv1d_bwd_vec_kernel<T, 4><<<vgrid, 64, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, (const T*)bias, (const T*)init, (T*)dx, dw, dbias, (T*)dinit, B, Tlen, D, act, trun);
+            else if (K == 3) causal_conv1d_bwd_vec_kernel<T, 3><<<vgrid, 64, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, (const T*)bias, (const T*)init, (T*)dx, dw, dbias, (T*)dinit, B, Tlen, D, act, trun);
+            else causal_conv1d_bwd_vec_kernel<T, 2><<<vgrid, 64, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, (const T*)bias, (const T*)init, (T*)dx, dw, dbias, (T*)dinit, B, Tlen, D, act, trun);
+            return (int)cudaGetLastError();
+        }
         if (K == 4) causal_conv1d_bwd_kernel<T, 4><<<grid, 128, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, (const T*)bias, (const T*)init, (T*)dx, dw, dbias, (T*)dinit, B, Tlen, D, act, tchunk);
         else if (K == 3) causal_conv1d_bwd_kernel<T, 3><<<grid, 128, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, (const T*)bias, (const T*)init, (T*)dx, dw, dbias, (T*)dinit, B, Tlen, D, act, tchunk);
         else if (K == 2) causal_conv1d_bwd_kernel<T, 2><<<grid, 128, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, (const T*)bias, (const T*)init, (T*)dx, dw, dbias, (T*)dinit, B, Tlen, D, act, tchunk);
