@@ -35,7 +35,7 @@ def sdpa_reference(q, k, v, scale, causal, q_offset, window):
 def flash_attention(q, k, v, scale: Optional[float], causal: bool, q_offset: int, window: Optional[int]):
     from . import flash
     if flash.supported(q, k, v, causal, window):
-        return flash.FlashAttention.apply(q, k, v, scale if scale is not None else q.shape[-1] ** -0.5, q_offset)
+        return flash.FlashAttention.apply(q, k, v, scale if scale is not None else q.shape[-1] ** -0.5, q_offset, window)
     if q.dtype in (torch.bfloat16, torch.float16) and v.shape[-1] == q.shape[-1]:
         return sdpa_reference(q, k, v, scale, causal, q_offset, window)
     return R.softmax_attention(q, k, v, scale, causal, q_offset, window)

@@ -392,10 +392,12 @@ class _CausalConv1d(torch.autograd.Function):
         ctx.save_for_backward(xc, w, b, ini)
         ctx.act, ctx.wdtype, ctx.bdtype = act, weight.dtype, None if bias is None else bias.dtype
         # final state: the last K-1 inputs (including the entering state when T < K-1)
-        if ini is not None:
+        if T >= K - 1:
+            tail = xc[:, T - (K - 1):].clone()
+        elif ini is not None:
             tail = torch.cat([ini, xc], dim=1)[:, -(K - 1):]
         else:
-            tail = F.pad(xc, (0, 0, max(K - 1 - T, 0), 0))[:, -(K - 1):]
+            tail = F.pad(xc, (0, 0, K - 1 - T, 0))
         ctx.mark_non_differentiable(tail)
         return y, tail
 

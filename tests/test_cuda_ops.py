@@ -249,3 +249,28 @@ def test_lsm_vector_gla(D, T, with_state):
     close(S, S2, 3e-2, 2e-2 * S2.abs().max().item(), "final state")
     for name, a, b in zip(["dq", "dk", "dv", "dgk", "dS0"], gk_, gr):
         close(a, b, 5e-2, 3e-2 * b.abs().max().item(), name)
+
+
+@pytest.mark.parametrize("D", [128, 64])
+@pytest.mark.parametrize("Tq,Tk,q_offset,window,Hq,Hkv", [
+    (300, 300, 0, None, 4, 2),           # ragged tiles, grouped-query heads
+    (128, 384, 256, None, 2, 2),         # sequence-parallel rank: suffix of the positions against gathered keys
+    (1, 200, 199, None, 4, 1),           # decoding against a cache
+    (257, 257, 0, 100, 2, 1),            # sliding window
+])
+def test_flash_attention(D, Tq, Tk, q_offset, window, Hq, Hkv):
+    from linear_moe_b200.ops import flash
+    torch.manual_seed(11)
+    B = 2
+    q = torch.randn(B, Tq, Hq, D, device=dev()).to(torch.bfloat16)
+    kv = torch.randn(B, Tk, Hkv, 2 * D, device=dev()).to(torch.bfloat16)
+    k, v = kv.split(D, dim=-1)                                   # strided views, as out of a fused projection
+    go = torch.randn(B, Tq, Hq, D, device=dev()).to(torch.bfloat16)
+    assert flash.supported(q, k, v, True, window)
+    f_k = lambda q, k, v: flash.FlashAttention.apply(q, k, v, D ** -0.5, q_offset, window)
+    f_r = lambda q, k, v: R.softmax_attention(q, k, v, D ** -0.5, True, q_offset, window)
+    (o,), gk = grads(f_k, [q, k, v], go)
+    (o2,), gr = grads(f_r, [q.float(), k.float(), v.float()], go.float())
+    close(o, o2, 2e-2, 2e-2, "o")
+    for name, a, b in zip(["dq", "dk", "dv"], gk, gr):
+        close(a, b, 3e-2, 2e-2 * b.abs().max().item(), name)
