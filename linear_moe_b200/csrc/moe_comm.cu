@@ -1,0 +1,299 @@
+// Expert-parallel token exchange of the MoE layer over NVLink peer memory: no NCCL all-to-all, no host sync.
+//
+// Replaces the reference's permute -> all_to_all -> permute ... unpermute -> all_to_all -> unpermute chain
+// (moe/token_dispatcher.py:412-548, whose split sizes are read back by the host with .tolist()) with
+//
+//   moe_exchange_kernel   every rank stores its per-expert token counts into every peer's count matrix, releases a
+//                         flag, waits (bounded) for the peers' rows and derives, on the device: the padded row
+//                         offsets of its local experts in its receive buffer (the grouped GEMM's problem sizes) and,
+//                         for every global expert, the row in the owner's receive buffer where THIS rank's tokens
+//                         for that expert start.
+//   moe_map_kernel        (sorted assignment -> destination rank, destination row) for every (token, slot) pair.
+//   moe_push_kernel       dispatch: every (token, slot) row is written straight into the owner rank's receive buffer
+//                         with 16-byte peer stores (optionally scaled, which is the backward of the combine); the
+//                         last CTA to finish releases a flag on every peer and waits for theirs.
+//   moe_zero_pads_kernel  clears the <128 padding rows behind every expert segment so that the weight-gradient GEMMs,
+//                         which contract over the padded rows, see zeros.
+//   moe_signal_kernel     "my expert outputs are complete" flag to every peer.
+//   moe_pull_kernel       combine: waits for the owners' flags, then every token gathers its k expert outputs from
+//                         the owners' result buffers with 16-byte peer loads, weights them by the routing
+//                         probabilities and sums them in fp32 (un-permute + weighted sum + all-to-all in one pass).
+//
+// Buffers are symmetric allocations shared by all MoE layers; a push/pull pair of one layer is ordered against the
+// next layer's by the flags themselves (a rank starts its next push only after its pull, which waited for every owner's
+// compute; an owner overwrites its result buffer only after every peer's next push).  Flags carry monotonically
+// increasing epochs.  Every spin is bounded: on expiry the kernel records {kernel, peer} in the status word and goes
+// on (results are then wrong but finite, every address stays in bounds) and the host raises after the step.
+#include "common.cuh"
+
+namespace lmoe {
+
+__device__ __forceinline__ void moe_st_rel(int* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;\n" :: "l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int moe_ld_acq(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+struct MoeArgs {
+    int* const* peer_cnt;       // [W] count matrices, int32 [W(src)][E]
+    int* const* peer_flags;     // [W] flag arrays, int32 [3][W(src)]: counts ready / push done / outputs ready
+    bf16* const* peer_x;        // [W] receive buffers [cap][h]
+    bf16* const* peer_y;        // [W] result buffers [cap][h]
+    int* status;
+    unsigned int* done_ctr;
+    int rank, world, E, El, cap, h;
+    int epoch;
+    long long spin_limit;
+    // exchange
+    const int* counts;          // [E] tokens of this rank per global expert
+    int* offs;                  // [El+1] out: padded row offsets of the local experts
+    int* real;                  // [El]   out: tokens received per local expert
+    int* send_base;             // [E]    out: first row of this rank's tokens in the owner's buffer, -1 = do not send
+    int* starts;                // [E]    out: exclusive prefix of counts (start of each expert in the sorted order)
+    // map
+    const long long* order;     // [n_sorted] sorted position -> flat (token, slot) index
+    const long long* sorted_e;  // [n_sorted] expert id of the sorted position (E = dropped)
+    int* dest_rank;             // [n_assign]
+    int* dest_row;              // [n_assign]
+    // push / pull
+    const bf16* src;            // [T][h]
+    const float* w;             // [n_assign] or null
+    bf16* out;                  // [T][h]
+    bf16* rows;                 // [n_assign][h] or null: the gathered rows, unweighted
+    int n_assign, k;
+};
+
+// wait until flags[phase][j] >= epoch for every peer j; one thread per peer.  Returns through smem `fail`.
+__device__ __forceinline__ void moe_wait_all(const MoeArgs& a, int phase, int code, int* fail) {
+    if ((int)threadIdx.x < a.world) {
+        const int* f = a.peer_flags[a.rank] + phase * a.world + threadIdx.x;
+        long long spins = 0;
+        while (moe_ld_acq(f) < a.epoch) {
+            if (++spins > a.spin_limit) {
+                atomicCAS(a.status, 0, (9 << 24) | ((int)threadIdx.x << 16) | code);
+                *fail = 1;
+                break;
+            }
+            __nanosleep(64);
+        }
+    }
+}
+
+__global__ void moe_exchange_kernel(MoeArgs a) {
+    extern __shared__ int sm[];
+    int* tot = sm;                 // [E]
+    int* prior = sm + a.E;         // [E]
+    int* over = sm + 2 * a.E;      // [W]
+    __shared__ int fail;
+    if (threadIdx.x == 0) fail = 0;
+    for (int e = threadIdx.x; e < a.E; e += blockDim.x) {
+        const int c = a.counts[e];
+        for (int j = 0; j < a.world; ++j) a.peer_cnt[j][a.rank * a.E + e] = c;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if ((int)threadIdx.x < a.world) moe_st_rel(a.peer_flags[threadIdx.x] + 0 * a.world + a.rank, a.epoch);
+    moe_wait_all(a, 0, 1, &fail);
+    __syncthreads();
+    const int* cnt = a.peer_cnt[a.rank];
+    for (int e = threadIdx.x; e < a.E; e += blockDim.x) {
+        int t = 0, p = 0;
+        for (int s = 0; s < a.world; ++s) {
+            const int c = fail ? 0 : max(__ldcg(cnt + s * a.E + e), 0);
+            if (s < a.rank) p += c;
+            t += c;
+        }
+        tot[e] = t;
+        prior[e] = p;
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < a.world) {
+        const int d = threadIdx.x;
+        long long run = 0;
+        for (int el = 0; el < a.El; ++el) run += (tot[d * a.El + el] + 127) / 128 * 128;
+        over[d] = run > a.cap;
+        if (run > a.cap) atomicCAS(a.status, 0, (9 << 24) | (d << 16) | 7);        // receive buffer of rank d too small
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < a.world) {
+        const int d = threadIdx.x;
+        int run = 0;
+        for (int el = 0; el < a.El; ++el) {
+            const int e = d * a.El + el;
+            a.send_base[e] = over[d] ? -1 : run + prior[e];
+            if (d == a.rank) { a.offs[el] = over[d] ? 0 : run; a.real[el] = over[d] ? 0 : tot[e]; }
+            run += (tot[e] + 127) / 128 * 128;
+        }
+        if (d == a.rank) a.offs[a.El] = over[d] ? 0 : run;
+    }
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < a.E; ++e) { a.starts[e] = run; run += a.counts[e]; }
+    }
+}
+
+__global__ void moe_map_kernel(MoeArgs a) {
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= a.n_assign) return;
+    const long long e = a.sorted_e[p];
+    const long long f = a.order[p];
+    int dr = -1, row = -1;
+    if (e >= 0 && e < a.E) {
+        const int sb = a.send_base[e];
+        if (sb >= 0) { dr = (int)e / a.El; row = sb + (p - a.starts[e]); }
+        if (row >= a.cap) { dr = -1; row = -1; }
+    }
+    a.dest_rank[f] = dr;
+    a.dest_row[f] = row;
+}
+
+__global__ void moe_push_kernel(MoeArgs a) {
+    __shared__ int fail, last;
+    const int wpb = blockDim.x >> 5, l = threadIdx.x & 31;
+    const int vecs = a.h / 8;
+    for (long long as = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); as < a.n_assign; as += (long long)gridDim.x * wpb) {
+        const int dr = a.dest_rank[as];
+        if (dr < 0) continue;
+        const uint4* s = reinterpret_cast<const uint4*>(a.src + (as / a.k) * a.h);
+        uint4* d = reinterpret_cast<uint4*>(a.peer_x[dr] + (long long)a.dest_row[as] * a.h);
+        if (a.w == nullptr) {
+            for (int c = l; c < vecs; c += 32) d[c] = s[c];
+        } else {
+            const float wt = a.w[as];
+            for (int c = l; c < vecs; c += 32) {
+                uint4 v = s[c];
+                __nv_bfloat162* hv = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float2 f = __bfloat1622float2(hv[i]);
+                    hv[i] = __floats2bfloat162_rn(f.x * wt, f.y * wt);
+                }
+                d[c] = v;
+            }
+        }
+    }
+    // grid-wide completion -> flag to every peer -> wait for every peer's flag
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        fail = 0;
+        last = atomicAdd(a.done_ctr, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!last) return;
+    __threadfence_system();
+    if ((int)threadIdx.x < a.world) moe_st_rel(a.peer_flags[threadIdx.x] + 1 * a.world + a.rank, a.epoch);
+    moe_wait_all(a, 1, 2, &fail);
+    if (threadIdx.x == 0) *a.done_ctr = 0;
+}
+
+// grid (El, chunks): zero rows [offs[el] + real[el], offs[el+1]) of the local receive buffer
+__global__ void moe_zero_pads_kernel(MoeArgs a) {
+    const int el = blockIdx.x;
+    const int lo = a.offs[el] + a.real[el], hi = min(a.offs[el + 1], a.cap);
+    const int vecs = a.h / 8;
+    uint4* x = reinterpret_cast<uint4*>(a.peer_x[a.rank]);
+    const long long n = (long long)max(hi - lo, 0) * vecs;
+    for (long long i = (long long)blockIdx.y * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.y * blockDim.x)
+        x[(long long)lo * vecs + i] = make_uint4(0, 0, 0, 0);
+}
+
+__global__ void moe_signal_kernel(MoeArgs a) {
+    __threadfence_system();
+    if ((int)threadIdx.x < a.world) moe_st_rel(a.peer_flags[threadIdx.x] + 2 * a.world + a.rank, a.epoch);
+}
+
+template <int KMAX>
+__global__ void moe_pull_kernel(MoeArgs a) {
+    __shared__ int fail;
+    if (threadIdx.x == 0) fail = 0;
+    __syncthreads();
+    moe_wait_all(a, 2, 3, &fail);
+    __syncthreads();
+    const int wpb = blockDim.x >> 5, l = threadIdx.x & 31;
+    const int vecs = a.h / 8;
+    const int T = a.n_assign / a.k;
+    for (long long t = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); t < T; t += (long long)gridDim.x * wpb) {
+        const uint4* rp[KMAX];
+        float wt[KMAX];
+#pragma unroll
+        for (int j = 0; j < KMAX; ++j) {
+            rp[j] = nullptr;
+            wt[j] = 0.f;
+            if (j < a.k) {
+                const int dr = a.dest_rank[t * a.k + j];
+                if (dr >= 0) {
+                    rp[j] = reinterpret_cast<const uint4*>(a.peer_y[dr] + (long long)a.dest_row[t * a.k + j] * a.h);
+                    wt[j] = a.w != nullptr ? a.w[t * a.k + j] : 1.f;
+                }
+            }
+        }
+        for (int c = l; c < vecs; c += 32) {
+            uint4 v[KMAX];
+#pragma unroll
+            for (int j = 0; j < KMAX; ++j) v[j] = rp[j] != nullptr ? __ldcg(rp[j] + c) : make_uint4(0, 0, 0, 0);
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < KMAX; ++j) {
+                const __nv_bfloat162* hv = reinterpret_cast<const __nv_bfloat162*>(&v[j]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float2 f = __bfloat1622float2(hv[i]);
+                    acc[2 * i] += wt[j] * f.x;
+                    acc[2 * i + 1] += wt[j] * f.y;
+                }
+                if (a.rows != nullptr && j < a.k)
+                    reinterpret_cast<uint4*>(a.rows + (t * a.k + j) * a.h)[c] = v[j];
+            }
+            uint4 o;
+            __nv_bfloat162* ho = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) ho[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+            reinterpret_cast<uint4*>(a.out + t * a.h)[c] = o;
+        }
+    }
+}
+
+}  // namespace lmoe
+
+using namespace lmoe;
+
+// which: 0 exchange, 1 map, 2 push, 3 zero pads, 4 signal, 5 pull
+LMOE_API int lmoe_moe_comm(int which, const MoeArgs* ap, int num_sms, cudaStream_t st) {
+    const MoeArgs a = *ap;
+    if (a.h % 8 != 0 || a.world > 32) return -2;
+    const int T = a.k > 0 ? a.n_assign / a.k : 0;
+    switch (which) {
+    case 0:
+        moe_exchange_kernel<<<1, 256, (2 * a.E + a.world) * sizeof(int), st>>>(a);
+        break;
+    case 1:
+        if (a.n_assign > 0) moe_map_kernel<<<(a.n_assign + 255) / 256, 256, 0, st>>>(a);
+        break;
+    case 2: {
+        int grid = (int)std::min<long long>(std::max<long long>((a.n_assign + 7) / 8, 1), (long long)num_sms * 8);
+        moe_push_kernel<<<grid, 256, 0, st>>>(a);
+        break;
+    }
+    case 3:
+        moe_zero_pads_kernel<<<dim3(a.El, 8), 256, 0, st>>>(a);
+        break;
+    case 4:
+        moe_signal_kernel<<<1, 32, 0, st>>>(a);
+        break;
+    case 5: {
+        int grid = (int)std::min<long long>(std::max<long long>((T + 7) / 8, 1), (long long)num_sms * 8);
+        if (a.k <= 2) moe_pull_kernel<2><<<grid, 256, 0, st>>>(a);
+        else if (a.k <= 4) moe_pull_kernel<4><<<grid, 256, 0, st>>>(a);
+        else if (a.k <= 8) moe_pull_kernel<8><<<grid, 256, 0, st>>>(a);
+        else return -3;
+        break;
+    }
+    default:
+        return -1;
+    }
+    return (int)cudaGetLastError();
+}

@@ -273,14 +273,24 @@ class MoELayer(nn.Module):
             self.shared_expert = None
 
     # ------------------------------------------------------------------
+    def _fused_workspace(self, h: torch.Tensor):
+        """The peer-memory exchange applies to bf16 CUDA tokens on an expert-parallel group without expert TP."""
+        mesh = self.mesh
+        if not (h.is_cuda and h.dtype == torch.bfloat16) or mesh["ep"].is_trivial or not mesh["tp"].is_trivial:
+            return None
+        from ..parallel import fused_comm
+        ws = fused_comm.moe_workspace(mesh["ep"])
+        if ws is None or ws.h != h.shape[-1] or ws.E != self.E or self.k > 8:
+            return None
+        from ..ops import gemm
+        return ws if gemm.supports_grouped(h, self.experts.weight1, self.experts.weight2) else None
+
     def _experts_with_ep(self, permuted: torch.Tensor, counts: torch.Tensor) -> torch.Tensor:
         """Expert computation on expert-sorted tokens, exchanging them over the EP group."""
         mesh = self.mesh
         ep, tpg = mesh["ep"], mesh["tp"]
         if ep.is_trivial and tpg.is_trivial:
             return self.experts(permuted, counts)
-        if x_fused := (permuted.is_cuda and ops._K().fused_moe_available(mesh)):
-            return ops._K().moe_dispatch_experts_combine(permuted, counts, self.experts, mesh)
         W, El = ep.size, self.El
         if not ep.is_trivial:
             # counts[e] tokens for global expert e; rank r owns experts [r*El, (r+1)*El)
@@ -333,9 +343,14 @@ class MoELayer(nn.Module):
         h = x.reshape(-1, shape[-1])
         T = h.shape[0]
         probs, idx = self.router(h)
-        permuted, order, counts = permute(h, idx, self.E)
-        y = self._experts_with_ep(permuted, counts)
-        out = unpermute(y, order, probs, T, self.k).reshape(shape)
+        ws = self._fused_workspace(h)
+        if ws is not None:
+            from ..ops.moe_fused import fused_moe
+            out = fused_moe(h, probs, idx, self.experts.weight1, self.experts.weight2, ws).reshape(shape)
+        else:
+            permuted, order, counts = permute(h, idx, self.E)
+            y = self._experts_with_ep(permuted, counts)
+            out = unpermute(y, order, probs, T, self.k).reshape(shape)
         if self.shared_expert is not None:
             s = self.shared_expert(x)
             if self.shared_expert_gate is not None:

@@ -17,6 +17,7 @@ step synchronises all ranks), i.e. by ``2 x layers`` calls, which NSLOT must exc
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, Optional
 
 import torch
@@ -151,6 +152,15 @@ def init_workspaces(mesh, cfg=None, tc=None):
         dk, dv = cfg.key_dim // cfg.num_attention_heads, cfg.value_dim // cfg.num_attention_heads
         mb = tc.micro_batch_size if tc is not None else 1
         _LASP[cp.name] = LaspWorkspace(cp, mb * H * dk * dv, device)
+    ep = mesh["ep"]
+    if (not ep.is_trivial and mesh["tp"].is_trivial and cfg is not None and cfg.num_experts and ep.name not in _MOE
+            and os.environ.get("LMOE_FUSED_MOE", "1") != "0"):
+        mb = tc.micro_batch_size if tc is not None else 1
+        seq = (tc.seq_length if tc is not None else cfg.max_position_embeddings) // max(mesh.cp, 1)
+        tokens = mb * seq * cfg.moe_topk
+        factor = float(os.environ.get("LMOE_MOE_RECV_FACTOR", "2.0"))         # receive rows per rank / average
+        cap = int(tokens * factor) + 128 * (cfg.num_experts // ep.size)
+        _MOE[ep.name] = MoeWorkspace(ep, cfg.num_experts, cfg.hidden_size, cap, device)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -217,3 +227,137 @@ class ZeroBufferWorkspace:
         a.master, a.exp_avg, a.exp_avg_sq = master.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr()
         a.lr, a.b1, a.b2, a.eps, a.wd, a.bc1, a.bc2, a.gscale = lr, b1, b2, eps, wd, bc1, bc2, gscale
         K._check(K.lib().lmoe_zero_adam_bcast(ctypes.byref(a), ctypes.c_int(K.NUM_SMS * 4), K._st()), "zero_adam_bcast")
+
+
+# ---------------------------------------------------------------------------------------------
+# MoE dispatch / combine over peer memory (csrc/moe_comm.cu)
+# ---------------------------------------------------------------------------------------------
+_MOE: Dict[str, "MoeWorkspace"] = {}
+
+
+def moe_workspace(group) -> Optional["MoeWorkspace"]:
+    return _MOE.get(group.name)
+
+
+class _MoeArgs(ctypes.Structure):
+    _fields_ = ([(n, ctypes.c_void_p) for n in ("peer_cnt", "peer_flags", "peer_x", "peer_y", "status", "done_ctr")] +
+                [(n, ctypes.c_int) for n in ("rank", "world", "E", "El", "cap", "h", "epoch")] +
+                [("spin_limit", ctypes.c_longlong)] +
+                [(n, ctypes.c_void_p) for n in ("counts", "offs", "real", "send_base", "starts", "order", "sorted_e",
+                                                "dest_rank", "dest_row", "src", "w", "out", "rows")] +
+                [("n_assign", ctypes.c_int), ("k", ctypes.c_int)])
+
+
+class MoeWorkspace:
+    """Receive buffer ``x [cap, h]``, result buffer ``y [cap, h]``, count matrix and flags of one expert-parallel group.
+    ``group=None`` builds a one-rank workspace out of ordinary tensors (single-GPU use and tests)."""
+
+    def __init__(self, group, num_experts: int, hidden: int, cap_rows: int, device, spin_limit: int = 4_000_000):
+        self.group, self.device = group, device
+        self.W, self.rank = (group.size, group.rank) if group is not None else (1, 0)
+        W = self.W
+        assert num_experts % W == 0 and hidden % 8 == 0
+        self.E, self.El, self.h = num_experts, num_experts // W, hidden
+        self.cap = (cap_rows + 127) // 128 * 128
+        if group is not None:
+            self.x, hx = _symm_empty(self.cap * hidden, torch.bfloat16, device, group)
+            self.y, hy = _symm_empty(self.cap * hidden, torch.bfloat16, device, group)
+            self.cnt, hc = _symm_empty(W * num_experts, torch.int32, device, group)
+            self.flags, hf = _symm_empty(3 * W + 64, torch.int32, device, group)
+            self._hdls = (hx, hy, hc, hf)
+            ptrs = [list(hd.buffer_ptrs) for hd in self._hdls]
+        else:
+            self.x = torch.empty(self.cap * hidden, dtype=torch.bfloat16, device=device)
+            self.y = torch.empty(self.cap * hidden, dtype=torch.bfloat16, device=device)
+            self.cnt = torch.empty(W * num_experts, dtype=torch.int32, device=device)
+            self.flags = torch.empty(3 * W + 64, dtype=torch.int32, device=device)
+            ptrs = [[t.data_ptr()] for t in (self.x, self.y, self.cnt, self.flags)]
+        for t in (self.x, self.y, self.cnt, self.flags):
+            t.zero_()
+        self.x, self.y = self.x.view(self.cap, hidden), self.y.view(self.cap, hidden)
+        self.peer_x, self.peer_y, self.peer_cnt, self.peer_flags = [
+            torch.tensor(p, dtype=torch.int64, device=device) for p in ptrs]
+        self.done_ctr = torch.zeros(1, dtype=torch.int32, device=device)
+        self.ep_exchange = self.ep_push = self.ep_pull = 0
+        self.spin_limit = spin_limit
+        torch.cuda.synchronize()
+        if group is not None:
+            dist.barrier(group=group.pg)
+
+    def _args(self) -> _MoeArgs:
+        a = _MoeArgs()
+        a.peer_cnt, a.peer_flags = self.peer_cnt.data_ptr(), self.peer_flags.data_ptr()
+        a.peer_x, a.peer_y = self.peer_x.data_ptr(), self.peer_y.data_ptr()
+        a.status, a.done_ctr = status_word(self.device).data_ptr(), self.done_ctr.data_ptr()
+        a.rank, a.world, a.E, a.El, a.cap, a.h = self.rank, self.W, self.E, self.El, self.cap, self.h
+        a.spin_limit = self.spin_limit
+        return a
+
+    def _run(self, which: int, a: _MoeArgs, name: str):
+        from ..ops import cuda as K
+        K._check(K.lib().lmoe_moe_comm(ctypes.c_int(which), ctypes.byref(a), ctypes.c_int(K.NUM_SMS), K._st()), name)
+
+    def route(self, idx: torch.Tensor):
+        """Top-k expert indices ``[T, k]`` (``-1`` = dropped) -> routing record: destination (rank, row) of every
+        (token, slot) pair, padded offsets and real sizes of the local expert segments.  No host synchronisation."""
+        T, k = idx.shape
+        dev = idx.device
+        flat = idx.reshape(-1)
+        key = torch.where(flat >= 0, flat, torch.full_like(flat, self.E))
+        sorted_e, order = torch.sort(key, stable=True)
+        counts = torch.bincount(key, minlength=self.E + 1)[: self.E].to(torch.int32)
+        offs = torch.empty(self.El + 1, dtype=torch.int32, device=dev)
+        real = torch.empty(self.El, dtype=torch.int32, device=dev)
+        send_base = torch.empty(self.E, dtype=torch.int32, device=dev)
+        starts = torch.empty(self.E, dtype=torch.int32, device=dev)
+        dest_rank = torch.empty(T * k, dtype=torch.int32, device=dev)
+        dest_row = torch.empty(T * k, dtype=torch.int32, device=dev)
+        self.ep_exchange += 1
+        a = self._args()
+        a.epoch = self.ep_exchange
+        a.counts, a.offs, a.real, a.send_base, a.starts = (counts.data_ptr(), offs.data_ptr(), real.data_ptr(),
+                                                           send_base.data_ptr(), starts.data_ptr())
+        a.order, a.sorted_e = order.data_ptr(), sorted_e.data_ptr()
+        a.dest_rank, a.dest_row = dest_rank.data_ptr(), dest_row.data_ptr()
+        a.n_assign, a.k = T * k, k
+        self._run(0, a, "moe_exchange")
+        self._run(1, a, "moe_map")
+        return MoeRoute(T, k, dest_rank, dest_row, offs, real)
+
+    def push(self, src: torch.Tensor, route: "MoeRoute", weights: Optional[torch.Tensor]) -> torch.Tensor:
+        """Send every (token, slot) row of ``src [T, h]`` (times ``weights [T*k]``) to its expert's rank; returns a copy
+        of this rank's receive buffer ``[cap, h]`` with zeroed padding rows."""
+        assert src.is_contiguous() and src.dtype == torch.bfloat16 and src.shape == (route.T, self.h)
+        self.ep_push += 1
+        a = self._args()
+        a.epoch = self.ep_push
+        a.src = src.data_ptr()
+        a.w = 0 if weights is None else weights.data_ptr()
+        a.dest_rank, a.dest_row = route.dest_rank.data_ptr(), route.dest_row.data_ptr()
+        a.offs, a.real = route.offs.data_ptr(), route.real.data_ptr()
+        a.n_assign, a.k = route.T * route.k, route.k
+        self._run(2, a, "moe_push")
+        self._run(3, a, "moe_zero_pads")
+        return self.x.clone()
+
+    def pull(self, y_local: torch.Tensor, route: "MoeRoute", weights: Optional[torch.Tensor], save_rows: bool):
+        """Publish this rank's expert results ``[cap, h]`` and gather, weight and sum every token's ``k`` rows from their
+        owners.  Returns ``(out [T, h], rows [T*k, h] or None)``."""
+        self.ep_pull += 1
+        self.y.copy_(y_local)
+        a = self._args()
+        a.epoch = self.ep_pull
+        out = torch.empty(route.T, self.h, dtype=torch.bfloat16, device=self.device)
+        rows = torch.empty(route.T * route.k, self.h, dtype=torch.bfloat16, device=self.device) if save_rows else None
+        a.w = 0 if weights is None else weights.data_ptr()
+        a.out, a.rows = out.data_ptr(), 0 if rows is None else rows.data_ptr()
+        a.dest_rank, a.dest_row = route.dest_rank.data_ptr(), route.dest_row.data_ptr()
+        a.n_assign, a.k = route.T * route.k, route.k
+        self._run(4, a, "moe_signal")
+        self._run(5, a, "moe_pull")
+        return out, rows
+
+
+class MoeRoute:
+    def __init__(self, T, k, dest_rank, dest_row, offs, real):
+        self.T, self.k, self.dest_rank, self.dest_row, self.offs, self.real = T, k, dest_rank, dest_row, offs, real

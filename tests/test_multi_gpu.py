@@ -102,3 +102,49 @@ def test_zero1_fused_matches_nccl(multicast):
         assert all(abs(a - b) < 2e-2 for a, b in zip(lf, ln)), (lf, ln)
         assert dmax < 2e-2 * pmax + 4e-3, (dmax, pmax)
     assert outs[0][0][-1] < outs[0][0][0]
+
+
+def _moe_worker(rank, world):
+    from linear_moe_b200.config.model_config import ModelConfig, ParallelConfig
+    from linear_moe_b200.dist.mesh import Mesh
+    from linear_moe_b200.models.moe import MoELayer
+    from linear_moe_b200.ops import gemm
+    from linear_moe_b200.parallel import fused_comm
+    dev = torch.device("cuda", rank)
+    mesh = Mesh(ParallelConfig(expert_model_parallel_size=world))
+    cfg = ModelConfig(num_layers=2, hidden_size=256, num_attention_heads=2, ffn_hidden_size=512, vocab_size=1024,
+                      num_experts=8, moe_topk=2, moe_ffn_hidden_size=128, params_dtype=torch.bfloat16)
+    layer = MoELayer(cfg, mesh, 1, "layers.0.mlp", device=dev).to(dev)
+    torch.manual_seed(100 + rank)                       # every rank routes its own tokens
+    T = 700 + 40 * rank
+    x = torch.randn(1, T, 256, device=dev).to(torch.bfloat16)
+    go = torch.randn(1, T, 256, device=dev).to(torch.bfloat16)
+
+    def run():
+        xx = x.clone().requires_grad_(True)
+        for p in layer.parameters():
+            p.grad = None
+        out = layer(xx)
+        out.backward(go)
+        torch.cuda.synchronize()
+        return [out.float(), xx.grad.float()] + [p.grad.float() for p in layer.parameters()]
+
+    ref = run()                                          # NCCL all-to-all path (no workspace yet)
+    fused_comm._MOE[mesh["ep"].name] = fused_comm.MoeWorkspace(mesh["ep"], 8, 256, 4 * 800 * 2, dev)
+    assert layer._fused_workspace(x.view(-1, 256)) is not None
+    errs = []
+    for it in range(3):
+        got = run()
+        fused_comm.check_status("moe fused test")
+        gemm.check_error()
+        errs.append([((a - b).abs().max().item(), b.abs().max().item()) for a, b in zip(got, ref)])
+    return errs
+
+
+def test_moe_fused_dispatch_combine_matches_nccl_path():
+    _need_gpus(2)
+    outs = run_distributed(_moe_worker, 2, backend="nccl")
+    for errs in outs:
+        for it in errs:
+            for err, scale in it:
+                assert err <= 3e-2 * scale + 1e-3, (err, scale)
