@@ -152,6 +152,12 @@ def init_workspaces(mesh, cfg=None, tc=None):
         dk, dv = cfg.key_dim // cfg.num_attention_heads, cfg.value_dim // cfg.num_attention_heads
         mb = tc.micro_batch_size if tc is not None else 1
         _LASP[cp.name] = LaspWorkspace(cp, mb * H * dk * dv, device)
+    tpg = mesh["tp"]
+    if (not tpg.is_trivial and tpg.size <= 8 and cfg is not None and tpg.name not in _TP
+            and os.environ.get("LMOE_FUSED_TP", "1") != "0"):
+        mb = tc.micro_batch_size if tc is not None else 1
+        seq = (tc.seq_length if tc is not None else cfg.max_position_embeddings) // max(mesh.cp, 1) // tpg.size
+        _TP[tpg.name] = TpWorkspace(tpg, mb * seq * cfg.hidden_size, device)
     ep = mesh["ep"]
     if (not ep.is_trivial and mesh["tp"].is_trivial and cfg is not None and cfg.num_experts and ep.name not in _MOE
             and os.environ.get("LMOE_FUSED_MOE", "1") != "0"):
@@ -361,3 +367,200 @@ class MoeWorkspace:
 class MoeRoute:
     def __init__(self, T, k, dest_rank, dest_row, offs, real):
         self.T, self.k, self.dest_rank, self.dest_row, self.offs, self.real = T, k, dest_rank, dest_row, offs, real
+
+
+# ---------------------------------------------------------------------------------------------
+# Sequence-parallel linear layers: all-gather -> GEMM and GEMM -> reduce-scatter in one kernel (csrc/gemm_tp.cu)
+# ---------------------------------------------------------------------------------------------
+class _TpParams(ctypes.Structure):
+    _fields_ = ([(n, ctypes.c_int) for n in ("mode", "rank", "world", "M_loc", "T_loc", "N", "K", "ldc")] +
+                [("C", ctypes.c_void_p), ("peer_inbox", ctypes.c_void_p), ("inbox_off", ctypes.c_longlong),
+                 ("peer_flags", ctypes.c_void_p), ("epoch", ctypes.c_int), ("done_ctr", ctypes.c_void_p),
+                 ("status", ctypes.c_void_p), ("err", ctypes.c_void_p), ("spin_cycles", ctypes.c_longlong)])
+
+
+class _TpCommArgs(ctypes.Structure):
+    _fields_ = [("peer_flags", ctypes.c_void_p), ("peer_x", ctypes.c_void_p), ("peer_inbox", ctypes.c_void_p),
+                ("x_off", ctypes.c_longlong), ("inbox_off", ctypes.c_longlong), ("status", ctypes.c_void_p),
+                ("rank", ctypes.c_int), ("world", ctypes.c_int), ("epoch", ctypes.c_int), ("M_loc", ctypes.c_int),
+                ("T_loc", ctypes.c_int), ("cols", ctypes.c_int), ("out", ctypes.c_void_p), ("spin_limit", ctypes.c_longlong)]
+
+
+class TpWorkspace:
+    """Symmetric buffers of one tensor-parallel group: ``NSLOT`` published activation shards, ``NSLOT`` inboxes of
+    ``W`` partial results, and the flags.  Two consecutive calls never share a slot, and a rank can be at most one call
+    ahead of a peer (every call needs data of every rank), so a slot is never overwritten while a peer still reads it."""
+    NSLOT = 4
+
+    def __init__(self, group, max_shard_elems: int, device, spin_limit: int = 4_000_000):
+        self.group, self.device = group, device
+        self.W, self.rank = group.size, group.rank
+        assert self.W <= 8
+        self.max_elems = (max_shard_elems + 127) // 128 * 128
+        self.xs, hx = _symm_empty(self.NSLOT * self.max_elems, torch.bfloat16, device, group)
+        self.inbox, hi = _symm_empty(self.NSLOT * self.W * self.max_elems, torch.bfloat16, device, group)
+        self.flags, hf = _symm_empty(2 * self.W + 64, torch.int32, device, group)
+        self._hdls = (hx, hi, hf)
+        self.flags.zero_()
+        self.x_ptrs = list(hx.buffer_ptrs)
+        self.peer_x = torch.tensor(self.x_ptrs, dtype=torch.int64, device=device)
+        self.peer_inbox = torch.tensor(list(hi.buffer_ptrs), dtype=torch.int64, device=device)
+        self.peer_flags = torch.tensor(list(hf.buffer_ptrs), dtype=torch.int64, device=device)
+        self.done_ctr = torch.zeros(1, dtype=torch.int32, device=device)
+        self.ag_calls = self.rs_calls = 0
+        self.spin_limit = spin_limit
+        self.spin_cycles = 4_000_000_000                      # ~2 s of SM clock
+        torch.cuda.synchronize()
+        dist.barrier(group=group.pg)
+
+    def supports(self, m_loc: int, t_loc: int, cols_shard: int, n: int, k: int) -> bool:
+        return (t_loc % 128 == 0 and m_loc % t_loc == 0 and n % 8 == 0 and k % 8 == 0 and cols_shard % 8 == 0
+                and m_loc * cols_shard <= self.max_elems)
+
+    def _comm(self) -> _TpCommArgs:
+        a = _TpCommArgs()
+        a.peer_flags, a.peer_x, a.peer_inbox = self.peer_flags.data_ptr(), self.peer_x.data_ptr(), self.peer_inbox.data_ptr()
+        a.status = status_word(self.device).data_ptr()
+        a.rank, a.world, a.spin_limit = self.rank, self.W, self.spin_limit
+        return a
+
+    def publish(self, x2d: torch.Tensor):
+        """Copy this rank's shard ``[M_loc, cols]`` into the next slot and raise the flag on every peer."""
+        from ..ops import cuda as K
+        self.ag_calls += 1
+        epoch, slot = self.ag_calls, self.ag_calls % self.NSLOT
+        off = slot * self.max_elems
+        self.xs[off: off + x2d.numel()].view_as(x2d).copy_(x2d)
+        a = self._comm()
+        a.epoch = epoch
+        K._check(K.lib().lmoe_tp_comm(ctypes.c_int(0), ctypes.byref(a), ctypes.c_int(K.NUM_SMS), K._st()), "tp_signal")
+        return epoch, off
+
+    def _params(self, m_loc, t_loc, n, k) -> _TpParams:
+        from ..ops import gemm
+        p = _TpParams()
+        p.rank, p.world, p.M_loc, p.T_loc, p.N, p.K = self.rank, self.W, m_loc, t_loc, n, k
+        p.peer_inbox, p.peer_flags = self.peer_inbox.data_ptr(), self.peer_flags.data_ptr()
+        p.done_ctr, p.status = self.done_ctr.data_ptr(), status_word(self.device).data_ptr()
+        p.err = gemm._err(self.device).data_ptr()
+        p.spin_cycles = self.spin_cycles
+        return p
+
+    def ag_gemm(self, pub, m_loc: int, t_loc: int, k: int, w: torch.Tensor, b_mn: bool) -> torch.Tensor:
+        """``gather(shards)[M_full, k] @ (w^T if not b_mn else w)`` reading the shards published as ``pub``."""
+        from ..ops import cuda as K
+        epoch, off = pub
+        n = w.shape[1] if b_mn else w.shape[0]
+        out = torch.empty(m_loc * self.W, n, dtype=torch.bfloat16, device=self.device)
+        p = self._params(m_loc, t_loc, n, k)
+        p.C, p.ldc, p.epoch = out.data_ptr(), n, epoch
+        ptrs = (ctypes.c_void_p * 8)(*[self.x_ptrs[i % self.W] + 2 * off for i in range(8)])
+        K._check(K.lib().lmoe_gemm_tp(ctypes.c_int(0), ptrs, K._p(w), ctypes.c_int(w.shape[0]), ctypes.c_int(w.shape[1]),
+                                      ctypes.c_int(int(b_mn)), ctypes.byref(p), ctypes.c_int(K.NUM_SMS), K._st()), "gemm_tp_ag")
+        return out
+
+    def gemm_rs(self, x2d: torch.Tensor, t_loc: int, w: torch.Tensor, b_mn: bool) -> torch.Tensor:
+        """``reduce_scatter(x2d[M_full, k] @ (w^T if not b_mn else w))`` -> ``[M_loc, n]``."""
+        from ..ops import cuda as K
+        m_full, k = x2d.shape
+        m_loc = m_full // self.W
+        n = w.shape[1] if b_mn else w.shape[0]
+        self.rs_calls += 1
+        epoch, slot = self.rs_calls, self.rs_calls % self.NSLOT
+        p = self._params(m_loc, t_loc, n, k)
+        p.inbox_off, p.epoch, p.ldc = slot * self.W * self.max_elems, epoch, n
+        ptrs = (ctypes.c_void_p * 8)(*[x2d.data_ptr()] * 8)
+        K._check(K.lib().lmoe_gemm_tp(ctypes.c_int(1), ptrs, K._p(w), ctypes.c_int(w.shape[0]), ctypes.c_int(w.shape[1]),
+                                      ctypes.c_int(int(b_mn)), ctypes.byref(p), ctypes.c_int(K.NUM_SMS), K._st()), "gemm_tp_rs")
+        out = torch.empty(m_loc, n, dtype=torch.bfloat16, device=self.device)
+        a = self._comm()
+        a.inbox_off, a.epoch, a.M_loc, a.T_loc, a.cols, a.out = p.inbox_off, epoch, m_loc, t_loc, n, out.data_ptr()
+        K._check(K.lib().lmoe_tp_comm(ctypes.c_int(1), ctypes.byref(a), ctypes.c_int(K.NUM_SMS), K._st()), "tp_reduce")
+        return out
+
+    def gather(self, pub, m_loc: int, t_loc: int, cols: int) -> torch.Tensor:
+        from ..ops import cuda as K
+        epoch, off = pub
+        out = torch.empty(m_loc * self.W, cols, dtype=torch.bfloat16, device=self.device)
+        a = self._comm()
+        a.x_off, a.epoch, a.M_loc, a.T_loc, a.cols, a.out = off, epoch, m_loc, t_loc, cols, out.data_ptr()
+        K._check(K.lib().lmoe_tp_comm(ctypes.c_int(2), ctypes.byref(a), ctypes.c_int(K.NUM_SMS), K._st()), "tp_gather")
+        return out
+
+
+class _AGLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias, ws):
+        B, T_loc, Kd = x.shape
+        x2d = x.reshape(B * T_loc, Kd)
+        wb = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
+        y = ws.ag_gemm(ws.publish(x2d), B * T_loc, T_loc, Kd, wb, False)
+        if bias is not None:
+            y = y + bias.to(y.dtype)
+        ctx.save_for_backward(x2d, w)
+        ctx.ws, ctx.dims, ctx.has_bias = ws, (B, T_loc, Kd), bias is not None
+        return y.view(B, ws.W * T_loc, -1)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2d, w = ctx.saved_tensors
+        ws, (B, T_loc, Kd) = ctx.ws, ctx.dims
+        dy2d = dy.reshape(-1, dy.shape[-1])
+        dy2d = dy2d if dy2d.is_contiguous() else dy2d.contiguous()
+        wb = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
+        dx = ws.gemm_rs(dy2d, T_loc, wb, True)                               # (dy W) reduce-scattered
+        xfull = ws.gather(ws.publish(x2d), B * T_loc, T_loc, Kd)             # re-gathered, not saved
+        dw = torch.mm(dy2d.t(), xfull).to(w.dtype)
+        db = dy2d.sum(0) if ctx.has_bias else None
+        return dx.view(B, T_loc, Kd), dw, db, None
+
+
+class _LinearRS(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, ws):
+        B, T_full, Kd = x.shape
+        T_loc = T_full // ws.W
+        x2d = x.reshape(B * T_full, Kd)
+        x2d = x2d if x2d.is_contiguous() else x2d.contiguous()
+        wb = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
+        y = ws.gemm_rs(x2d, T_loc, wb, False)
+        ctx.save_for_backward(x2d, w)
+        ctx.ws, ctx.dims = ws, (B, T_loc, Kd)
+        return y.view(B, T_loc, -1)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2d, w = ctx.saved_tensors
+        ws, (B, T_loc, Kd) = ctx.ws, ctx.dims
+        N = dy.shape[-1]
+        dy2d = dy.reshape(B * T_loc, N)
+        wb = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
+        pub = ws.publish(dy2d)
+        dx = ws.ag_gemm(pub, B * T_loc, T_loc, N, wb, True)                  # gather(dy) W
+        dyfull = ws.gather(pub, B * T_loc, T_loc, N)
+        dw = torch.mm(dyfull.t(), x2d).to(w.dtype)
+        return dx.view(B, ws.W * T_loc, Kd), dw, None
+
+
+def _tp_ok(ws, x, weight, t_loc, cols_shard) -> bool:
+    return (ws is not None and x.dim() == 3 and x.dtype == torch.bfloat16 and weight.dim() == 2
+            and ws.supports(x.shape[0] * t_loc, t_loc, cols_shard, weight.shape[0], weight.shape[1]))
+
+
+def allgather_linear(x, weight, bias, group, dim):
+    from ..dist import collectives as C
+    import torch.nn.functional as F
+    ws = tp_workspace(group)
+    if dim == 1 and _tp_ok(ws, x, weight, x.shape[1], x.shape[2]):
+        return _AGLinear.apply(x, weight, bias, ws)
+    return F.linear(C.all_gather(x, group, dim=dim), weight.to(x.dtype), None if bias is None else bias.to(x.dtype))
+
+
+def linear_reducescatter(x, weight, group, dim):
+    from ..dist import collectives as C
+    import torch.nn.functional as F
+    ws = tp_workspace(group)
+    if dim == 1 and x.dim() == 3 and x.shape[1] % group.size == 0 and \
+            _tp_ok(ws, x, weight, x.shape[1] // group.size, weight.shape[0]):
+        return _LinearRS.apply(x, weight, ws)
+    return C.reduce_scatter(F.linear(x, weight.to(x.dtype)), group, dim=dim)

@@ -148,3 +148,49 @@ def test_moe_fused_dispatch_combine_matches_nccl_path():
         for it in errs:
             for err, scale in it:
                 assert err <= 3e-2 * scale + 1e-3, (err, scale)
+
+
+def _tp_worker(rank, world, B, T_loc, h, f):
+    from linear_moe_b200 import ops
+    from linear_moe_b200.config.model_config import ParallelConfig
+    from linear_moe_b200.dist.mesh import Mesh
+    from linear_moe_b200.ops import gemm
+    from linear_moe_b200.parallel import fused_comm
+    dev = torch.device("cuda", rank)
+    mesh = Mesh(ParallelConfig(tensor_model_parallel_size=world, sequence_parallel=True))
+    g = mesh["tp"]
+    torch.manual_seed(5 + rank)
+    x = torch.randn(B, T_loc, h, device=dev).to(torch.bfloat16)
+    w1 = (0.05 * torch.randn(f, h, device=dev)).to(torch.bfloat16)          # column-parallel shard [f_loc, h]
+    b1 = (0.1 * torch.randn(f, device=dev)).to(torch.bfloat16)
+    w2 = (0.05 * torch.randn(h, f, device=dev)).to(torch.bfloat16)          # row-parallel shard [h, f_loc]
+    go = torch.randn(B, T_loc, h, device=dev).to(torch.bfloat16)
+
+    def run():
+        ins = [t.clone().requires_grad_(True) for t in (x, w1, b1, w2)]
+        y = ops.allgather_linear(ins[0], ins[1], ins[2], g, dim=1)         # [B, W*T_loc, f]
+        z = ops.linear_reducescatter(torch.nn.functional.silu(y), ins[3], g, dim=1)
+        z.backward(go)
+        torch.cuda.synchronize()
+        return [z.float(), y.float()] + [t.grad.float() for t in ins]
+
+    ref = run()                                                             # NCCL collectives + cuBLAS
+    fused_comm._TP[g.name] = fused_comm.TpWorkspace(g, B * T_loc * max(h, f), dev)
+    errs = []
+    for it in range(3):
+        got = run()
+        fused_comm.check_status("tp fused test")
+        gemm.check_error()
+        errs.append([((a - b).abs().max().item(), b.abs().max().item()) for a, b in zip(got, ref)])
+    assert fused_comm._TP[g.name].ag_calls == 9 and fused_comm._TP[g.name].rs_calls == 6
+    return errs
+
+
+@pytest.mark.parametrize("B,T_loc,h,f", [(1, 512, 512, 1024), (2, 128, 256, 328)])
+def test_tp_fused_allgather_gemm_and_gemm_reducescatter(B, T_loc, h, f):
+    _need_gpus(2)
+    outs = run_distributed(_tp_worker, 2, backend="nccl", B=B, T_loc=T_loc, h=h, f=f)
+    for errs in outs:
+        for it in errs:
+            for err, scale in it:
+                assert err <= 2e-2 * scale + 1e-3, (err, scale)
