@@ -282,5 +282,5 @@ class BatchIterator:
         batch = make_batch(sample, **self.kw)
         batch = slice_for_context_parallel(batch, mesh)
         if self.pin:
-            batch = {k: v.pin_memory() for k, v in batch.items()}
+            batch = {k: v.contiguous().pin_memory() for k, v in batch.items()}
         return {k: v.to(self.device, non_blocking=True) for k, v in batch.items()}

@@ -81,6 +81,9 @@ class Trainer:
         self.device = device or (torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available()
                                  else torch.device("cpu"))
         set_init_seed(tc.seed)
+        if par.fused_comm and self.device.type == "cuda" and self.mesh.world_size > 1:
+            from ..parallel import fused_comm
+            fused_comm.init_workspaces(self.mesh, cfg, tc)
         torch.manual_seed(tc.seed + 100 * self.mesh.pp_rank + 10 * self.mesh.dp_rank + self.mesh.cp_rank)
         sp = par.sequence_parallel and par.tp > 1
         self.models = model_provider(cfg, self.mesh, self.device) if model_provider else \
@@ -181,6 +184,9 @@ class Trainer:
             self.scheduler.step(1)
         self.iteration += 1
         self.consumed_samples += tc.global_batch_size
+        if self.device.type == "cuda" and self.iteration % max(tc.log_interval, 1) == 0:
+            from ..parallel import fused_comm
+            fused_comm.check_status(f"iteration {self.iteration}")         # a bounded wait of a fused kernel expired
         out = {"lr": lr, "grad_norm": grad_norm, "skipped": 0 if ok else 1}
         if mesh.is_last_stage and logs:
             keys = logs[0].keys()

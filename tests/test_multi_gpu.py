@@ -194,3 +194,52 @@ def test_tp_fused_allgather_gemm_and_gemm_reducescatter(B, T_loc, h, f):
         for it in errs:
             for err, scale in it:
                 assert err <= 2e-2 * scale + 1e-3, (err, scale)
+
+
+def _model_worker(rank, world, par_kw, overrides, steps):
+    from linear_moe_b200.config.model_config import ParallelConfig, TrainConfig
+    from linear_moe_b200.config.presets import get_preset
+    from linear_moe_b200.data.datasets import SyntheticTokenDataset
+    from linear_moe_b200.dist.mesh import Mesh, single_process_mesh
+    from linear_moe_b200.ops import gemm
+    from linear_moe_b200.parallel import fused_comm
+    from linear_moe_b200.train.loop import Trainer
+    dev = torch.device("cuda", rank)
+    seq, gbs = 512, 2
+    cfg = get_preset("bench-cpu-plumbing", params_dtype=torch.bfloat16, **overrides)
+    ds = SyntheticTokenDataset(cfg.vocab_size, seq, num_samples=gbs, seed=0)
+
+    def train(mesh, par):
+        tc = TrainConfig(micro_batch_size=2 if mesh.dp == 1 else 1, global_batch_size=gbs, seq_length=seq, train_iters=steps,
+                         lr=1e-3, min_lr=1e-3, lr_decay_style="constant", weight_decay=0.0, clip_grad=0.0,
+                         log_interval=1, seed=0, bf16=True)
+        tr = Trainer(cfg, par, tc, mesh, device=dev, dataset=ds)
+        out = []
+        for _ in range(steps):
+            st = tr.train_step()
+            out.append((float(st["lm loss"]), float(st["grad_norm"])))
+        gemm.check_error()
+        return out
+
+    multi = train(Mesh(ParallelConfig(**par_kw)), ParallelConfig(**par_kw))
+    used = dict(tp=sum(w.ag_calls for w in fused_comm._TP.values()), moe=sum(w.ep_push for w in fused_comm._MOE.values()),
+                lasp=sum(w.calls for w in fused_comm._LASP.values()))
+    single = train(single_process_mesh(), ParallelConfig()) if rank == 0 else None
+    return multi, single, used
+
+
+@pytest.mark.parametrize("name,par_kw,overrides,expect", [
+    ("tp2_sp", dict(tensor_model_parallel_size=2, sequence_parallel=True), dict(layer_type_list="LN"), "tp"),
+    ("ep2", dict(expert_model_parallel_size=2), dict(), "moe"),
+    ("cp2_zero1", dict(context_parallel_size=2, use_distributed_optimizer=True),
+     dict(la_module="lightning_attention", kv_channels=64), "lasp"),
+])
+def test_two_gpu_training_matches_one_gpu(name, par_kw, overrides, expect):
+    """bf16 training steps of the small MoE model split over 2 GPUs (fused communication kernels on) against 1 GPU."""
+    _need_gpus(2)
+    outs = run_distributed(_model_worker, 2, backend="nccl", par_kw=par_kw, overrides=overrides, steps=3)
+    multi, single, used = outs[0]
+    assert used[expect] > 0, f"the fused {expect} path was not used: {used}"
+    for (l, g), (l0, g0) in zip(multi, single):
+        assert abs(l - l0) < 5e-2, (multi, single)
+    assert abs(multi[0][1] - single[0][1]) < 0.1 * single[0][1], (multi, single)
