@@ -126,7 +126,7 @@ class _CachedLinearCE(torch.autograd.Function):
         K.softmax_ce_fwd(Z, labels, loss, lse, ignore_index)
         K.softmax_ce_bwd(Z, labels, lse, torch.ones(T, dtype=torch.float32, device=h.device), ignore_index)
         ctx.save_for_backward(h, wd, Z)
-        ctx.wdtype = weight.dtype
+        ctx.wdtype, ctx.weight = weight.dtype, weight
         return loss
 
     @staticmethod
@@ -134,6 +134,8 @@ class _CachedLinearCE(torch.autograd.Function):
         h, wd, Z = ctx.saved_tensors
         g = gl.to(h.dtype)[:, None]
         dh = torch.mm(Z, wd) * g
+        if _K().wgrad_into_main_grad(ctx.weight, Z.t(), h * g):
+            return dh, None, None, None
         dw = torch.mm(Z.t(), h * g)
         return dh, dw.to(ctx.wdtype), None, None
 

@@ -76,7 +76,61 @@ def _same_dtype(x, *ts):
 # =====================================================================================
 # GEMM-shaped (cuBLAS for the plain ones; the fused tcgen05 variants live in gemm.py)
 # =====================================================================================
+_MM_OUT_F32 = None        # does torch.mm(bf16, bf16, out_dtype=fp32, out=...) work in this build?
+
+
+def wgrad_into_main_grad(weight, a_t: torch.Tensor, b: torch.Tensor) -> bool:
+    """``weight.main_grad (+)= a_t @ b`` straight from the GEMM (fp32 output), skipping the bf16 gradient tensor and
+    the separate accumulation pass (the counterpart of Megatron's gradient-accumulation fusion).  The first write
+    after ``zero_grad`` overwrites, later ones add.  Returns False when the parameter has no fp32 accumulator."""
+    global _MM_OUT_F32
+    mg = getattr(weight, "main_grad", None)
+    if os.environ.get("LMOE_DIRECT_WGRAD", "1") == "0":
+        return False
+    if mg is None or mg.dtype != torch.float32 or a_t.dtype != torch.bfloat16 or not mg.is_contiguous():
+        return False
+    if _MM_OUT_F32 is None:
+        try:
+            t = torch.zeros(8, 8, dtype=torch.float32, device=a_t.device)
+            torch.mm(torch.ones(8, 16, dtype=torch.bfloat16, device=a_t.device),
+                     torch.ones(16, 8, dtype=torch.bfloat16, device=a_t.device), out_dtype=torch.float32, out=t)
+            _MM_OUT_F32 = bool((t == 16).all())
+        except Exception:
+            _MM_OUT_F32 = False
+    if not _MM_OUT_F32:
+        return False
+    if getattr(weight, "_main_grad_fresh", False):
+        torch.mm(a_t, b, out_dtype=torch.float32, out=mg.view(a_t.shape[0], b.shape[1]))
+        weight._main_grad_fresh = False
+    else:
+        mg.view(a_t.shape[0], b.shape[1]).add_(torch.mm(a_t, b, out_dtype=torch.float32))
+    return True
+
+
+class _LinearMainGrad(torch.autograd.Function):
+    """``x W^T`` whose weight gradient goes directly into ``W.main_grad``."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        ctx.save_for_backward(x, weight)
+        return F.linear(x, weight)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        dx = torch.matmul(dy, weight) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            dy2, x2 = dy.reshape(-1, dy.shape[-1]), x.reshape(-1, x.shape[-1])
+            if not wgrad_into_main_grad(weight, dy2.t(), x2):
+                dw = torch.mm(dy2.t(), x2)
+        return dx, dw
+
+
 def linear(x, weight, bias=None):
+    if (bias is None and weight.dtype == x.dtype == torch.bfloat16 and weight.requires_grad and torch.is_grad_enabled()
+            and getattr(weight, "main_grad", None) is not None):
+        return _LinearMainGrad.apply(x, weight)
     return F.linear(x, weight if weight.dtype == x.dtype else weight.to(x.dtype),
                     None if bias is None else bias.to(x.dtype))
 

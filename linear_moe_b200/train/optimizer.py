@@ -163,12 +163,14 @@ class MixedPrecisionAdam:
             else:
                 p.main_grad.add_(p.grad.to(torch.float32))
             p.grad = None
+            p._main_grad_fresh = False
 
     def zero_grad(self):
         for b in self.buffers:
             b.grads.zero_()
         for _, p in self.named:
             p.grad = None
+            p._main_grad_fresh = True          # the next direct weight-gradient GEMM may overwrite instead of add
 
     def scale_loss(self, loss: torch.Tensor) -> torch.Tensor:
         return loss if self.loss_scale is None else loss * self.loss_scale
@@ -223,9 +225,9 @@ class MixedPrecisionAdam:
                         continue
                     a, e = max(s.start, lo), min(s.start + s.numel, hi)
                     if e > a:
-                        sq = sq + b.grads[a:e].pow(2).sum()
+                        sq = sq + torch.linalg.vector_norm(b.grads[a:e]).square()
             else:
-                sq = b.grads[lo:hi].pow(2).sum()
+                sq = torch.linalg.vector_norm(b.grads[lo:hi]).square()
             if b.expert:
                 expert = expert + sq
             else:

@@ -47,3 +47,29 @@ def test_gpu_model_matches_cpu_model(name):
             assert torch.isfinite(p.grad).all(), n
     from linear_moe_b200.ops import gemm
     gemm.check_error()
+
+
+def test_direct_weight_gradient_accumulation(monkeypatch):
+    """Weight-gradient GEMMs that write the fp32 accumulators directly against the bf16 gradient + accumulation pass,
+    over two micro-batches (first write overwrites, second adds)."""
+    from linear_moe_b200.config.model_config import ParallelConfig, TrainConfig
+    from linear_moe_b200.data.datasets import SyntheticTokenDataset
+    from linear_moe_b200.train.loop import Trainer
+    dev = torch.device("cuda", 0)
+    cfg = ModelConfig(params_dtype=torch.bfloat16, use_la_module=True, la_module="lightning_attention", layer_type_list="LN", **BASE)
+    ds = SyntheticTokenDataset(cfg.vocab_size, 256, num_samples=4, seed=0)
+
+    def run(direct):
+        monkeypatch.setenv("LMOE_DIRECT_WGRAD", "1" if direct else "0")
+        tc = TrainConfig(micro_batch_size=1, global_batch_size=2, seq_length=256, train_iters=2, lr=1e-3, min_lr=1e-3,
+                         lr_decay_style="constant", clip_grad=1.0, log_interval=1, seed=0, bf16=True)
+        tr = Trainer(cfg, ParallelConfig(), tc, device=dev, dataset=ds)
+        K.reset_launch_count()
+        out = [tr.train_step() for _ in range(2)]
+        return [(float(o["lm loss"]), float(o["grad_norm"])) for o in out], K.reset_launch_count()
+
+    a, n_direct = run(True)
+    b, n_plain = run(False)
+    assert n_direct < n_plain, "the direct path must save the accumulation launches"
+    for (l1, g1), (l2, g2) in zip(a, b):
+        assert abs(l1 - l2) < 2e-2 and abs(g1 - g2) < 3e-2 * g2, (a, b)
