@@ -723,6 +723,14 @@ def lsm_scalar(q, k, v, g, scale, initial_state, chunk_size):
     D = q.shape[-1]
     ok = (q.dtype == torch.bfloat16 and k.dtype == q.dtype and v.dtype == q.dtype and v.shape[-1] == D
           and k.shape[-1] == D and D in (64, 128))
+    Dv = v.shape[-1]
+    if (not ok and q.dtype == torch.bfloat16 and k.dtype == q.dtype and v.dtype == q.dtype and k.shape[-1] == D
+            and D in (64, 128) and Dv < D):
+        # value heads narrower than the key/state width (Mamba2: head dim 64, state 128): zero-pad the values
+        scale = D ** -0.5 if scale is None else scale
+        s0 = None if initial_state is None else F.pad(initial_state, (0, D - Dv))
+        o, S = lsm_scalar(q, k, F.pad(v, (0, D - Dv)), g, scale, s0, chunk_size)
+        return o[..., :Dv], (None if S is None else S[..., :Dv])
     if not ok:
         return LT.chunk_scalar_gated(q, k, v, g, scale, initial_state, chunk_size)
     scale = D ** -0.5 if scale is None else scale

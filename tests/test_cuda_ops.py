@@ -9,7 +9,9 @@ pytestmark = pytest.mark.gpu
 
 from linear_moe_b200 import ops
 from linear_moe_b200.ops import lsm_torch as LT
+from linear_moe_b200.ref import lsm as RL
 from linear_moe_b200.ref import ops as R
+from linear_moe_b200.ops import cuda as K
 
 
 def dev():
@@ -274,3 +276,27 @@ def test_flash_attention(D, Tq, Tk, q_offset, window, Hq, Hkv):
     close(o, o2, 2e-2, 2e-2, "o")
     for name, a, b in zip(["dq", "dk", "dv"], gk, gr):
         close(a, b, 3e-2, 2e-2 * b.abs().max().item(), name)
+
+
+def test_ssd_mamba2_on_scalar_kernels():
+    """Mamba2 SSD (state 128, head dim 64, heads sharing B/C per group, per-token decay) through the scalar-decay
+    kernels against the recurrent fp32 definition."""
+    torch.manual_seed(2)
+    B, T, H, P, N, G = 2, 300, 4, 64, 128, 2
+    x = torch.randn(B, T, H, P, device=dev()).to(torch.bfloat16)
+    dt = torch.nn.functional.softplus(torch.randn(B, T, H, device=dev()) - 1.0)
+    A = -torch.exp(torch.randn(H, device=dev()) * 0.5)
+    Bm = (0.3 * torch.randn(B, T, G, N, device=dev())).to(torch.bfloat16)
+    Cm = (0.3 * torch.randn(B, T, G, N, device=dev())).to(torch.bfloat16)
+    Dskip = torch.randn(H, device=dev())
+    go = torch.randn(B, T, H, P, device=dev()).to(torch.bfloat16)
+    K.reset_launch_count()
+    f_k = lambda x, dt, Bm, Cm: ops.ssd(x, dt, A, Bm, Cm, Dskip, None, 64)[0]
+    (o,), gk = grads(f_k, [x, dt, Bm, Cm], go)
+    assert K.reset_launch_count() > 0
+
+    f_r = lambda x, dt, Bm, Cm: RL.recurrent_ssd(x, dt, A, Bm, Cm, Dskip)[0]
+    (o2,), gr = grads(f_r, [x.float(), dt, Bm.float(), Cm.float()], go.float())
+    close(o, o2, 3e-2, 2e-2 * o2.abs().max().item(), "y")
+    for name, a, b in zip(["dx", "ddt", "dB", "dC"], gk, gr):
+        close(a, b, 5e-2, 3e-2 * b.abs().max().item(), name)
