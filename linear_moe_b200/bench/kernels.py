@@ -1,6 +1,6 @@
 """Per-kernel timing and roofline harness.
 
-  python -m linear_moe_b200.bench.kernels [--kernel all|gemm|lsm|norm|headnorm|swiglu|ce|adam|conv] [--size small|full]
+  python -m linear_moe_b200.bench.kernels [--kernel all|gemm|lsm|flash|families|moe|norm|headnorm|swiglu|ce|adam|conv] [--size small|full]
 
 Each kernel is timed with CUDA events on the launching stream after warm-up, with an L2 flush (a 256 MiB write)
 between iterations; the median is reported together with the algorithmic bytes / FLOPs and the fraction of the
@@ -151,6 +151,92 @@ def bench_elementwise(which, size):
         report("causal_conv1d bwd", timeit(lambda: torch.autograd.grad(y, [x, w], gy, retain_graph=True)), bytes_=3 * T * Dc * 2)
 
 
+def bench_flash(size):
+    from ..ops import flash, attention
+    dev = torch.device("cuda", 0)
+    B, Hq, Hkv, D = 1, 16, 4, 128
+    T = 4096 if size == "small" else 16384
+    q = torch.randn(B, T, Hq, D, device=dev).bfloat16().requires_grad_(True)
+    kv = torch.randn(B, T, Hkv, 2 * D, device=dev).bfloat16().requires_grad_(True)
+    go = torch.randn(B, T, Hq, D, device=dev).bfloat16()
+    fl = 4.0 * B * Hq * T * T * D / 2                      # causal: half of QK^T + PV
+
+    def fwd(fn):
+        k, v = kv.split(D, dim=-1)
+        return fn(q, k, v)
+    mine = lambda q, k, v: flash.FlashAttention.apply(q, k, v, D ** -0.5, 0, None)
+    lib = lambda q, k, v: attention.sdpa_reference(q, k, v, D ** -0.5, True, 0, None)
+    for name, fn in (("flash_attn (own)", mine), ("sdpa (library)", lib)):
+        with torch.no_grad():
+            report(f"{name} fwd T={T} {Hq}q/{Hkv}kv D={D}", timeit(lambda: fwd(fn)), flops=fl)
+        o = fwd(fn)
+
+        def bwd():
+            q.grad = kv.grad = None
+            o.backward(go, retain_graph=True)
+        report(f"{name} bwd T={T} {Hq}q/{Hkv}kv D={D}", timeit(bwd), flops=2.5 * fl)
+
+
+def bench_lsm_families(size):
+    from .. import ops
+    dev = torch.device("cuda", 0)
+    B, H, D = 1, 8, 128
+    T = 4096
+    q, k, v = [(0.5 * torch.randn(B, T, H, D, device=dev)).bfloat16().requires_grad_(True) for _ in range(3)]
+    gk = (torch.nn.functional.logsigmoid(torch.randn(B, T, H, D, device=dev)) / 16).requires_grad_(True)
+    g = (torch.nn.functional.logsigmoid(torch.randn(B, T, H, device=dev)) / 16).requires_grad_(True)
+    beta = torch.rand(B, T, H, device=dev).requires_grad_(True)
+    go = torch.randn(B, T, H, D, device=dev).bfloat16()
+    kn = torch.nn.functional.normalize(k.detach().float(), dim=-1).bfloat16().requires_grad_(True)
+    cases = {
+        "gla (lsm_vector.cu)": lambda: ops.lsm_vector(q, k, v, gk, None, None, None, 64)[0],
+        "gated delta rule (torch WY)": lambda: ops.lsm_delta(q, kn, v, beta, g, None, None, 64)[0],
+    }
+    for name, fn in cases.items():
+        with torch.no_grad():
+            report(f"{name} fwd T={T} H={H} D={D}", timeit(fn, iters=5))
+        o = fn()
+
+        def bwd():
+            for t in (q, k, v, gk, g, beta, kn):
+                t.grad = None
+            o.backward(go, retain_graph=True)
+        report(f"{name} bwd T={T} H={H} D={D}", timeit(bwd, iters=5))
+
+
+def bench_moe(size):
+    """Expert MLPs of BASELINE config #2 on one rank: 8 local experts, hidden 1024, ffn 896, top-8."""
+    from ..ops import gemm
+    from ..ops.moe_fused import fused_moe
+    from ..parallel import fused_comm
+    dev = torch.device("cuda", 0)
+    T, k, E, hid, f = (2048, 8, 8, 1024, 896) if size == "small" else (8192, 8, 8, 1024, 896)
+    ws = fused_comm.MoeWorkspace(None, E, hid, T * k + 128 * E, dev)
+    h = torch.randn(T, hid, device=dev).bfloat16().requires_grad_(True)
+    probs, idx = torch.topk(torch.softmax(torch.randn(T, E, device=dev), -1), k, dim=-1)
+    probs = probs.requires_grad_(True)
+    w1 = (0.05 * torch.randn(E, hid, 2 * f, device=dev)).bfloat16().requires_grad_(True)
+    w2 = (0.05 * torch.randn(E, f, hid, device=dev)).bfloat16().requires_grad_(True)
+    go = torch.randn(T, hid, device=dev).bfloat16()
+    fl = 2.0 * T * k * hid * 3 * f
+    fn = lambda: fused_moe(h, probs, idx, w1, w2, ws)
+    with torch.no_grad():
+        report(f"fused moe fwd T={T} k={k} E={E} h={hid} f={f}", timeit(fn), flops=fl)
+    o = fn()
+
+    def bwd():
+        h.grad = probs.grad = w1.grad = w2.grad = None
+        o.backward(go, retain_graph=True)
+    report(f"fused moe bwd T={T} k={k} E={E} h={hid} f={f}", timeit(bwd), flops=2 * fl)
+    # the grouped GEMM alone (fc1 of all experts)
+    x = torch.randn(T * k, hid, device=dev).bfloat16()
+    offs = torch.arange(0, E + 1, device=dev, dtype=torch.int32) * (T * k // E)
+    with torch.no_grad():
+        report(f"grouped gemm fc1 rows={T * k} E={E}", timeit(lambda: gemm.GroupedLinear.apply(x, w1, offs)), flops=2.0 * T * k * hid * 2 * f)
+    gemm.check_error()
+    fused_comm.check_status("bench")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", default="all")
@@ -162,6 +248,12 @@ def main():
         bench_gemm(a.size)
     if a.kernel in ("lsm", "all"):
         bench_lsm(a.size)
+    if a.kernel in ("flash", "all"):
+        bench_flash(a.size)
+    if a.kernel in ("families", "all"):
+        bench_lsm_families(a.size)
+    if a.kernel in ("moe", "all"):
+        bench_moe(a.size)
     if a.kernel in ("norm", "headnorm", "swiglu", "ce", "adam", "conv", "all"):
         bench_elementwise(a.kernel, a.size)
 

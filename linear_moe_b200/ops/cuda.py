@@ -835,5 +835,47 @@ def lsm_vector(q, k, v, gk, scale, initial_state, bonus, chunk_size):
     return _LsmVector.apply(q, k, v, gk, scale, initial_state)
 
 
+class _tf32:
+    """fp32 matmuls on the tensor cores (TF32) inside the block."""
+
+    def __enter__(self):
+        self.prev = torch.backends.cuda.matmul.allow_tf32
+        torch.backends.cuda.matmul.allow_tf32 = True
+
+    def __exit__(self, *exc):
+        torch.backends.cuda.matmul.allow_tf32 = self.prev
+
+
+class _DeltaRuleScan(torch.autograd.Function):
+    """(Gated) delta rule as batched tensor-core matmuls: WY/UT transform per chunk, a parallel scan over the chunks'
+    affine state maps, then all chunk outputs at once.  The backward recomputes the forward (nothing but the inputs
+    is kept) and differentiates it."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, beta, g, initial_state, scale, chunk_size):
+        with torch.no_grad(), _tf32():
+            o, S = LT.chunk_delta_rule(q, k, v, beta, g, scale, initial_state, chunk_size, parallel_scan=True)
+        ctx.save_for_backward(q, k, v, beta, g, initial_state)
+        ctx.cfg = (scale, chunk_size)
+        return o.to(q.dtype), S
+
+    @staticmethod
+    def backward(ctx, do, dS):
+        saved = ctx.saved_tensors
+        ins = [None if t is None else t.detach().requires_grad_(t.is_floating_point()) for t in saved]
+        with torch.enable_grad(), _tf32():
+            o, S = LT.chunk_delta_rule(*ins[:5], ctx.cfg[0], ins[5], ctx.cfg[1], parallel_scan=True)
+            outs, gouts = [o], [do.to(o.dtype)]
+            if dS is not None:
+                outs.append(S)
+                gouts.append(dS)
+            need = [t for t in ins if t is not None]
+            grads = torch.autograd.grad(outs, need, gouts, allow_unused=True)
+        it = iter(grads)
+        full = [None if t is None else next(it) for t in ins]
+        full = [None if gr is None else gr.to(t.dtype) for gr, t in zip(full, ins)]
+        return (*full, None, None)
+
+
 def lsm_delta(q, k, v, beta, g, scale, initial_state, chunk_size):
-    return LT.chunk_delta_rule(q, k, v, beta, g, scale, initial_state, chunk_size)
+    return _DeltaRuleScan.apply(q, k, v, beta, g, initial_state, scale, chunk_size)

@@ -124,7 +124,7 @@ def chunk_vector_gated(q, k, v, gk, scale: Optional[float] = None, initial_state
 
 
 def chunk_delta_rule(q, k, v, beta, g: Optional[torch.Tensor] = None, scale: Optional[float] = None,
-                     initial_state=None, chunk_size: int = 64) -> Tuple[torch.Tensor, torch.Tensor]:
+                     initial_state=None, chunk_size: int = 64, parallel_scan: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
     """(Gated) delta rule: ``S_t = e^{g_t} S_{t-1}``, ``S_t += beta_t k_t^T (v_t - k_t S_t)``."""
     B, T, H, dk = q.shape
     dv = v.shape[-1]
@@ -157,6 +157,26 @@ def chunk_delta_rule(q, k, v, beta, g: Optional[torch.Tensor] = None, scale: Opt
     kd = kc * (btot[..., None] - b).exp()[..., None]
     gam = btot.exp()
     S = torch.zeros(B, H, dk, dv, dtype=f, device=q.device) if initial_state is None else initial_state.to(f)
+    if parallel_scan:
+        # Every chunk is an affine map of its entering state, S' = M S + Nb with M = gamma I - kd^T W and
+        # Nb = kd^T U; a Hillis-Steele scan over the chunks composes them in log2(N) batched matmuls, after which
+        # outputs of all chunks are computed at once (no Python loop over chunks, no per-chunk launches).
+        kdT = kd.transpose(-1, -2)
+        M = gam[..., None, None] * torch.eye(dk, dtype=f, device=q.device) - kdT @ W          # [B,N,H,dk,dk]
+        P = torch.cat([M, kdT @ U], dim=-1)                                                   # [B,N,H,dk,dk+dv]
+        d = 1
+        while d < N:
+            hi, lo = P[:, d:], P[:, :-d]
+            comp = hi[..., :dk] @ lo
+            comp = torch.cat([comp[..., :dk], comp[..., dk:] + hi[..., dk:]], dim=-1)
+            P = torch.cat([P[:, :d], comp], dim=1)
+            d *= 2
+        after = P[..., :dk] @ S[:, None] + P[..., dk:]                                        # state after chunk n
+        enter = torch.cat([S[:, None], after[:, :-1]], dim=1)                                 # state entering chunk n
+        vn = U - W @ enter
+        o = qd @ enter + QK @ vn
+        o = o.permute(0, 1, 3, 2, 4).reshape(B, N * C, H, dv)[:, :T]
+        return o, after[:, -1]
     outs = []
     for n in range(N):
         vn = U[:, n] - W[:, n] @ S

@@ -300,3 +300,33 @@ def test_ssd_mamba2_on_scalar_kernels():
     close(o, o2, 3e-2, 2e-2 * o2.abs().max().item(), "y")
     for name, a, b in zip(["dx", "ddt", "dB", "dC"], gk, gr):
         close(a, b, 5e-2, 3e-2 * b.abs().max().item(), name)
+
+
+@pytest.mark.parametrize("gated,with_state", [(True, False), (False, True)])
+def test_lsm_delta_rule_scan(gated, with_state):
+    """(Gated) delta rule on the GPU (WY transform + parallel scan over chunk maps, TF32) against the token-by-token
+    fp32 recurrence."""
+    torch.manual_seed(4)
+    B, T, H, D = 2, 300, 2, 64
+    q, v = [(0.5 * torch.randn(B, T, H, D, device=dev())).to(torch.bfloat16) for _ in range(2)]
+    k = torch.nn.functional.normalize(torch.randn(B, T, H, D, device=dev()), dim=-1).to(torch.bfloat16)
+    beta = torch.rand(B, T, H, device=dev())
+    g = torch.nn.functional.logsigmoid(torch.randn(B, T, H, device=dev()) + 2.0) if gated else None
+    S0 = 0.2 * torch.randn(B, H, D, D, device=dev()) if with_state else None
+    go = torch.randn(B, T, H, D, device=dev()).to(torch.bfloat16)
+    ins = [q, k, v, beta] + ([g] if gated else []) + ([S0] if with_state else [])
+
+    def unpack(a):
+        a = list(a)
+        q, k, v, beta = a[:4]
+        gg = a[4] if gated else None
+        s = a[-1] if with_state else None
+        return q, k, v, beta, gg, s
+    f_k = lambda *a: ops.lsm_delta(*unpack(a)[:5], None, unpack(a)[5], 64)[0]
+    f_r = lambda *a: RL.recurrent_lsm(unpack(a)[0], unpack(a)[1], unpack(a)[2], beta=unpack(a)[3], g=unpack(a)[4],
+                                      initial_state=unpack(a)[5])[0]
+    (o,), gk = grads(f_k, ins, go)
+    (o2,), gr = grads(f_r, [t.float() for t in ins], go.float())
+    close(o, o2, 3e-2, 2e-2 * o2.abs().max().item(), "o")
+    for name, a, b in zip(["dq", "dk", "dv", "dbeta", "dg/dS0", "dS0"], gk, gr):
+        close(a, b, 5e-2, 3e-2 * b.abs().max().item(), name)
