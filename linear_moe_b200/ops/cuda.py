@@ -128,6 +128,9 @@ class _LinearMainGrad(torch.autograd.Function):
 
 
 def linear(x, weight, bias=None):
+    from . import fp8
+    if fp8.enabled() and bias is None and fp8.supported(x, weight):
+        return fp8.Fp8Linear.apply(x, weight)
     if (bias is None and weight.dtype == x.dtype == torch.bfloat16 and weight.requires_grad and torch.is_grad_enabled()
             and getattr(weight, "main_grad", None) is not None):
         return _LinearMainGrad.apply(x, weight)

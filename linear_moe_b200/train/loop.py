@@ -47,6 +47,8 @@ def print_rank_0(*a, **kw):
 def build_model(cfg: ModelConfig, mesh: Mesh, device, sequence_parallel: bool = False) -> List[CausalLM]:
     """One model chunk per virtual pipeline stage of this rank (training.py:184-305 ``get_model``)."""
     vpp = mesh.par.virtual_pipeline_model_parallel_size or 1
+    from ..ops import fp8
+    fp8.set_enabled(bool(cfg.fp8) and torch.device(device).type == "cuda")
     chunks = []
     for v in range(vpp):
         vs = v * mesh.pp + mesh.pp_rank

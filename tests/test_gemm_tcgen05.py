@@ -75,3 +75,47 @@ def test_grouped_mlp_matches_loop():
         err = (a.float() - b).abs().max().item()
         assert err <= 3e-2 * b.abs().max().item() + 1e-3, (name, err, b.abs().max().item())
     assert w1.grad[1].abs().max().item() == 0.0          # expert without tokens: exact zero gradient
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 1024), (1000 // 16 * 16, 328 // 8 * 8, 272), (128, 256, 128)])
+def test_fp8_gemm_and_quantisation(M, N, K):
+    """e4m3 tcgen05 GEMM with per-row scales against the fp32 product of the de-quantised operands (exact up to
+    accumulation order and the bf16 output), and the quantisers against torch's float8 cast."""
+    from linear_moe_b200.ops import fp8, gemm
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(1)
+    a = (torch.randn(M, K, device=dev) * torch.rand(M, 1, device=dev) * 3).to(torch.bfloat16)
+    b = torch.randn(N, K, device=dev).to(torch.bfloat16)
+    aq, sa = fp8.quant_rows(a)
+    bq, sb = fp8.quant_rows(b)
+    # quantiser: scale = amax / 448 and round-to-nearest e4m3
+    assert torch.allclose(sa, a.float().abs().amax(1) / 448.0, rtol=1e-6)
+    want = (a.float() / sa[:, None]).to(torch.float8_e4m3fn).view(torch.uint8)
+    assert (aq != want).float().mean().item() < 1e-3          # ties may round differently
+    c = fp8.gemm_nt(aq, sa, bq, sb)
+    gemm.check_error()
+    ref = fp8.dequant_rows(aq, sa) @ fp8.dequant_rows(bq, sb).t()
+    err = (c.float() - ref).abs().max().item()
+    assert err <= 1e-2 * ref.abs().max().item(), (err, ref.abs().max().item())
+    # transposed column-wise quantisation = row-wise quantisation of the transpose
+    tq, ts = fp8.quant_cols_t(a)
+    tq2, ts2 = fp8.quant_rows(a.t().contiguous())
+    assert torch.allclose(ts, ts2, rtol=1e-6) and (tq != tq2).float().mean().item() < 1e-3
+
+
+def test_fp8_linear_close_to_bf16():
+    from linear_moe_b200.ops import fp8
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(2)
+    x = torch.randn(4, 256, 512, device=dev).to(torch.bfloat16).requires_grad_(True)
+    w = (0.05 * torch.randn(768, 512, device=dev)).to(torch.bfloat16).requires_grad_(True)
+    go = torch.randn(4, 256, 768, device=dev).to(torch.bfloat16)
+    y = fp8.Fp8Linear.apply(x, w)
+    y.backward(go)
+    g1 = (x.grad.clone(), w.grad.clone())
+    x.grad = w.grad = None
+    y2 = torch.nn.functional.linear(x, w)
+    y2.backward(go)
+    for name, p, q in (("y", y, y2), ("dx", g1[0], x.grad), ("dw", g1[1], w.grad)):
+        rel = (p.float() - q.float()).norm() / q.float().norm()
+        assert rel < 6e-2, (name, rel.item())           # e4m3 has 3 mantissa bits: ~4 % relative error per GEMM
