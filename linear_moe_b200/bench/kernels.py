@@ -66,6 +66,15 @@ def bench_gemm(size):
         c = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
         report(f"gemm tcgen05 {M}x{N}x{K}", timeit(lambda: gemm.gemm_nt(a, b, out=c)), flops=2.0 * M * N * K)
         report(f"gemm cuBLAS  {M}x{N}x{K}", timeit(lambda: torch.mm(a, b.t(), out=c)), flops=2.0 * M * N * K)
+    from ..ops import fp8
+    for M, N, K in shapes:
+        a = torch.randn(M, K, device=dev).bfloat16()
+        b = torch.randn(N, K, device=dev).bfloat16()
+        aq, sa = fp8.quant_rows(a)
+        bq, sb = fp8.quant_rows(b)
+        report(f"gemm fp8 tcgen05 {M}x{N}x{K}", timeit(lambda: fp8.gemm_nt(aq, sa, bq, sb)), flops=2.0 * M * N * K)
+        report(f"fp8 quant rows {M}x{K}", timeit(lambda: fp8.quant_rows(a)), bytes_=3.0 * M * K)
+        report(f"fp8 quant cols^T {M}x{K}", timeit(lambda: fp8.quant_cols_t(a)), bytes_=5.0 * M * K)
     gemm.check_error()
 
 

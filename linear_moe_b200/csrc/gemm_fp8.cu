@@ -131,6 +131,12 @@ gemm_fp8_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
             const int cols_valid = N - tn * BN;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
+                // column scales first, so that their latency overlaps the tensor-memory load
+                float4 sc[8];
+#pragma unroll
+                for (int g = 0; g < 8; ++g)
+                    sc[g] = (c + g * 4 + 4 <= cols_valid) ? __ldg(reinterpret_cast<const float4*>(sb + tn * BN + c + g * 4))
+                                                           : make_float4(0.f, 0.f, 0.f, 0.f);
                 uint32_t v[32];
                 tmem_ld32(taddr + c, v);
                 tmem_ld_wait();
@@ -139,8 +145,7 @@ gemm_fp8_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
                     for (int g = 0; g < 4; ++g) {
                         const int col = c + g * 8;
                         if (col + 8 <= cols_valid) {
-                            const float4 s0 = *reinterpret_cast<const float4*>(sb + tn * BN + col);
-                            const float4 s1 = *reinterpret_cast<const float4*>(sb + tn * BN + col + 4);
+                            const float4 s0 = sc[2 * g], s1 = sc[2 * g + 1];
                             uint4 o;
                             o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]) * ra * s0.x, __uint_as_float(v[g * 8 + 1]) * ra * s0.y);
                             o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]) * ra * s0.z, __uint_as_float(v[g * 8 + 3]) * ra * s0.w);

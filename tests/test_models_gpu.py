@@ -73,3 +73,31 @@ def test_direct_weight_gradient_accumulation(monkeypatch):
     assert n_direct < n_plain, "the direct path must save the accumulation launches"
     for (l1, g1), (l2, g2) in zip(a, b):
         assert abs(l1 - l2) < 2e-2 and abs(g1 - g2) < 3e-2 * g2, (a, b)
+
+
+def test_fp8_model_close_to_bf16_model():
+    """The Mamba2 + attention + MoE hybrid with e4m3 projections against the same model in bf16."""
+    from linear_moe_b200.ops import fp8
+    kw = dict(BASE)
+    kw.update(CASES["mamba2_mixtral"])
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    ids = torch.randint(0, 1024, (2, 256), device=dev)
+    labels = torch.roll(ids, -1, 1)
+    model = CausalLM(ModelConfig(params_dtype=torch.bfloat16, **kw)).to(dev)
+    losses = []
+    for flag in (False, True):
+        fp8.set_enabled(flag)
+        try:
+            K.reset_launch_count()
+            loss = model(ids, labels).mean()
+            model.zero_grad()
+            loss.backward()
+            losses.append((loss.item(), K.reset_launch_count()))
+        finally:
+            fp8.set_enabled(False)
+    assert losses[1][1] > losses[0][1], "fp8 path did not launch its quantisers / GEMMs"
+    assert abs(losses[0][0] - losses[1][0]) < 3e-2, losses
+    for n, p in model.named_parameters():
+        if p.grad is not None:
+            assert torch.isfinite(p.grad).all(), n
