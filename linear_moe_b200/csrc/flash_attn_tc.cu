@@ -1,0 +1,334 @@
+// Flash-attention forward on the 5th-generation tensor cores: S = Q K^T and O_j = P_j V_j are tcgen05.mma instructions
+// with accumulators in tensor memory, operands staged by TMA (4-D tensor maps over [B, T, H, D], 128-byte swizzle).
+//
+// One CTA = 128 queries of one head.  192 threads:
+//   warp 0      TMA producer: Q once, then K_j / V_j tiles of 128 keys through two 2-stage rings
+//   warp 1      MMA issuer:   S_{j+1} = Q K_{j+1}^T is issued before P_j V_j, so the tensor core works on the next
+//               score tile while the softmax warps are busy with the current one
+//   warps 2-5   softmax: thread r owns query row r (TMEM lane r): two passes over the 128 scores in tensor memory
+//               (row max, then exp2 / sum / bf16 pack), P_j written to shared memory in the K-major 128-byte-swizzle
+//               layout the MMA reads, then O += P_j V_j is folded into registers (o = o * corr + O_j) one iteration
+//               later, so that it overlaps the next tile's math.  No tensor-memory stores, no cross-thread shuffles.
+// Tensor memory: 2 x 128 columns of scores + 2 x D columns of partial outputs.
+// Masking (causal with a query offset, sliding window, key length) is applied only on tiles that cross a boundary.
+// Every mbarrier wait is bounded (clock64 budget); on expiry the error word is set and the CTA drains and frees its
+// tensor memory.  Writes O (bf16) and the natural-log row log-sum-exp, which the backward kernels of flash_attn.cu use.
+//
+// Replaces dot_product_attention.py:139-183 (baddbmm + softmax + bmm) and the flash_attn / TransformerEngine back ends
+// of the reference (llama3/transformer_legacy.py:446-505).
+#include "tcgen05_utils.cuh"
+
+namespace lmoe {
+namespace fatc {
+using namespace lmoe::tc;
+
+constexpr int BM = 128, BN = 128, THREADS = 192, UMMA_K = 16;
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct Args {
+    bf16* out;            // [B, Tq, Hq, D]
+    float* lse;           // [B, Hq, Tq]
+    int B, Tq, Tk, Hq, Hkv;
+    int q_offset, window; // window <= 0: none
+    float scale;
+    int* err;
+};
+
+template <int D>
+struct __align__(1024) Smem {
+    uint8_t q[BM * D * 2];
+    uint8_t k[2][BN * D * 2];
+    uint8_t v[2][BN * D * 2];
+    uint8_t p[BM * BN * 2];
+    uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], o_full[2], p_ready;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2, int c3) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 :: "r"(s32(dst)), "l"(map), "r"(s32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+template <bool B_MN, int N>
+__host__ __device__ constexpr uint32_t idesc_bf16() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+template <int D>
+__global__ void __launch_bounds__(THREADS, 1)
+fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    Smem<D>& sm = *reinterpret_cast<Smem<D>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int DK = D / 64;                              // 64-element blocks along the head dimension
+    constexpr uint32_t TMEM_COLS = 512;
+    constexpr uint32_t O_COL = 2 * BN;                      // partial outputs behind the two score buffers
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qb = gridDim.x - 1 - blockIdx.x;              // long (late) query tiles first
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int hk = h / (a.Hq / a.Hkv);
+    const int q0 = qb * BM;
+    volatile int* abort_flag = &sm.abort_flag;
+    int* err = a.err;
+
+    // visible key range of this query tile -> key tiles [nb_lo, nb_hi)
+    const int last_q = min(a.Tq, q0 + BM) - 1;
+    const int k_hi = min(a.Tk, a.q_offset + last_q + 1);
+    const int k_lo = a.window > 0 ? max(0, a.q_offset + q0 - a.window + 1) : 0;
+    const int nb_lo = k_lo / BN, nb_hi = (k_hi + BN - 1) / BN;
+    const int n_it = max(nb_hi - nb_lo, 0);
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sm.q_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&sm.k_full[s], 1); mbar_init(&sm.k_empty[s], 1);
+            mbar_init(&sm.v_full[s], 1); mbar_init(&sm.v_empty[s], 1);
+            mbar_init(&sm.s_full[s], 1); mbar_init(&sm.o_full[s], 1);
+        }
+        mbar_init(&sm.p_ready, 4);
+        sm.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(s32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = sm.tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0 && n_it > 0) {
+            mbar_expect_tx(&sm.q_full, BM * D * 2);
+#pragma unroll
+            for (int kb = 0; kb < DK; ++kb) tma_load_4d(sm.q + kb * BM * 128, &tmQ, &sm.q_full, kb * 64, h, q0, b);
+            for (int j = 0; j < n_it; ++j) {
+                const int s = j & 1;
+                const uint32_t ph = (j >> 1) & 1;
+                const int key0 = (nb_lo + j) * BN;
+                if (!mbar_wait(&sm.k_empty[s], ph ^ 1, abort_flag, err, 0x1100 | s)) break;
+                mbar_expect_tx(&sm.k_full[s], BN * D * 2);
+#pragma unroll
+                for (int kb = 0; kb < DK; ++kb) tma_load_4d(sm.k[s] + kb * BN * 128, &tmK, &sm.k_full[s], kb * 64, hk, key0, b);
+                if (!mbar_wait(&sm.v_empty[s], ph ^ 1, abort_flag, err, 0x1200 | s)) break;
+                mbar_expect_tx(&sm.v_full[s], BN * D * 2);
+                // MN-major operand: per 64 keys, D/64 boxes of {64 d, 64 keys} (8 KiB each)
+#pragma unroll
+                for (int kk = 0; kk < BN / 64; ++kk)
+#pragma unroll
+                    for (int nb = 0; nb < DK; ++nb)
+                        tma_load_4d(sm.v[s] + (kk * DK + nb) * 8192, &tmV, &sm.v_full[s], nb * 64, hk, key0 + kk * 64, b);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && n_it > 0) {
+            constexpr uint32_t idesc_s = idesc_bf16<false, BN>();
+            constexpr uint32_t idesc_o = idesc_bf16<true, D>();
+            bool ok = mbar_wait(&sm.q_full, 0, abort_flag, err, 0x2000);
+            auto issue_s = [&](int j) -> bool {
+                const int s = j & 1;
+                if (!mbar_wait(&sm.k_full[s], (j >> 1) & 1, abort_flag, err, 0x2100 | s)) return false;
+                tc_fence_after();
+                const uint32_t qa = s32(sm.q), ka = s32(sm.k[s]);
+#pragma unroll
+                for (int kk = 0; kk < D / UMMA_K; ++kk) {
+                    const uint32_t off = (kk / 4) * (BM * 128) + (kk % 4) * 32;
+                    umma_f16(tmem_base + s * BN, make_desc<false>(qa + off), make_desc<false>(ka + off), idesc_s, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(&sm.k_empty[s]);
+                umma_commit(&sm.s_full[s]);
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            for (int j = 0; ok && j < n_it; ++j) {
+                if (j + 1 < n_it) { ok = issue_s(j + 1); if (!ok) break; }
+                const int s = j & 1;
+                if (!mbar_wait(&sm.v_full[s], (j >> 1) & 1, abort_flag, err, 0x2200 | s)) break;
+                if (!mbar_wait(&sm.p_ready, j & 1, abort_flag, err, 0x2300)) break;
+                tc_fence_after();
+                const uint32_t pa = s32(sm.p), va = s32(sm.v[s]);
+#pragma unroll
+                for (int kk = 0; kk < BN / UMMA_K; ++kk) {
+                    const uint32_t aoff = (kk / 4) * (BM * 128) + (kk % 4) * 32;
+                    const uint32_t boff = (kk / 4) * (DK * 8192) + (kk % 4) * 2048;
+                    umma_f16(tmem_base + O_COL + s * D, make_desc<false>(pa + aoff), make_desc<true>(va + boff), idesc_o, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(&sm.v_empty[s]);
+                umma_commit(&sm.o_full[s]);
+            }
+        }
+    } else {
+        const int qd = warp & 3;                              // TMEM lane quarter of this warp
+        const int r = qd * 32 + lane;                         // query row inside the tile
+        const int qi = a.q_offset + q0 + r;                   // absolute position of this query
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
+        const float sc = a.scale * LOG2E;
+        float o[D];
+#pragma unroll
+        for (int i = 0; i < D; ++i) o[i] = 0.f;
+        float m = -INFINITY, l = 0.f, corr_prev = 1.f;
+        uint8_t* prow = sm.p + (r >> 3) * 1024 + (r & 7) * 128;
+        bool alive = n_it > 0;
+        for (int j = 0; alive && j < n_it; ++j) {
+            const int s = j & 1;
+            const int key0 = (nb_lo + j) * BN;
+            if (!mbar_wait(&sm.s_full[s], (j >> 1) & 1, abort_flag, err, 0x3100 | s)) { alive = false; break; }
+            tc_fence_after();
+            const bool need_mask = (key0 + BN - 1 > a.q_offset + q0) || (key0 + BN > a.Tk) ||
+                                   (a.window > 0 && key0 <= a.q_offset + q0 + BM - 1 - a.window);
+            // pass 1: row maximum
+            float mx = m;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(lane_addr + s * BN + c, v);
+                tmem_ld_wait();
+                if (need_mask) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const int key = key0 + c + i;
+                        const bool vis = key <= qi && key < a.Tk && (a.window <= 0 || key > qi - a.window);
+                        mx = fmaxf(mx, vis ? __uint_as_float(v[i]) : -INFINITY);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+                }
+            }
+            const float corr = (m == -INFINITY) ? 1.f : exp2f((m - mx) * sc);
+            const float msc = (mx == -INFINITY) ? 0.f : mx * sc;
+            m = mx;
+            // the P buffer and the partial output of the previous tile are free once P_{j-1} V_{j-1} has completed
+            if (j > 0 && !mbar_wait(&sm.o_full[s ^ 1], ((j - 1) >> 1) & 1, abort_flag, err, 0x3200 | s)) { alive = false; break; }
+            // pass 2: p = exp2(s * sc - m * sc), row sum, bf16 pack, swizzled store
+            float ps = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(lane_addr + s * BN + c, v);
+                tmem_ld_wait();
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    float x0 = __uint_as_float(v[i]), x1 = __uint_as_float(v[i + 1]);
+                    if (need_mask) {
+                        const int key = key0 + c + i;
+                        const bool v0 = key <= qi && key < a.Tk && (a.window <= 0 || key > qi - a.window);
+                        const bool v1 = key + 1 <= qi && key + 1 < a.Tk && (a.window <= 0 || key + 1 > qi - a.window);
+                        x0 = v0 ? x0 : -INFINITY;
+                        x1 = v1 ? x1 : -INFINITY;
+                    }
+                    const float p0 = exp2f(fmaf(x0, sc, -msc)), p1 = exp2f(fmaf(x1, sc, -msc));
+                    ps += p0 + p1;
+                    pk[i >> 1] = pack_bf16(p0, p1);
+                }
+                // 32 keys = 64 bytes = 4 chunks of 16 bytes inside the 128-byte row of key block c / 64
+                uint8_t* pb = prow + (c >> 6) * (BM * 128);
+                const int ch0 = (c & 63) >> 3;
+#pragma unroll
+                for (int g = 0; g < 4; ++g)
+                    *reinterpret_cast<uint4*>(pb + (((ch0 + g) ^ (r & 7)) << 4)) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+            }
+            l = l * corr + ps;
+            // hand P_j to the MMA warp
+            tc_fence_before();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.p_ready);
+            // fold the previous tile's partial output while the tensor core runs P_j V_j
+            if (j > 0) {
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < D; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(lane_addr + O_COL + (s ^ 1) * D + c, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], corr_prev, __uint_as_float(v[i]));
+                }
+            }
+            corr_prev = corr;
+        }
+        if (alive && n_it > 0) {
+            const int s = (n_it - 1) & 1;
+            if (mbar_wait(&sm.o_full[s], ((n_it - 1) >> 1) & 1, abort_flag, err, 0x3300 | s)) {
+                tc_fence_after();
+#pragma unroll
+                for (int c = 0; c < D; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(lane_addr + O_COL + s * D + c, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], corr_prev, __uint_as_float(v[i]));
+                }
+            }
+        }
+        const int row = q0 + r;
+        if (row < a.Tq) {
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            bf16* og = a.out + (((long long)b * a.Tq + row) * a.Hq + h) * D;
+#pragma unroll
+            for (int c = 0; c < D; c += 8) {
+                uint4 w;
+                w.x = pack_bf16(o[c] * inv, o[c + 1] * inv);
+                w.y = pack_bf16(o[c + 2] * inv, o[c + 3] * inv);
+                w.z = pack_bf16(o[c + 4] * inv, o[c + 5] * inv);
+                w.w = pack_bf16(o[c + 6] * inv, o[c + 7] * inv);
+                *reinterpret_cast<uint4*>(og + c) = w;
+            }
+            a.lse[((long long)b * a.Hq + h) * a.Tq + row] = l > 0.f ? m * a.scale + logf(l) : -INFINITY;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// [B, T, H, D] bf16 with element strides (sb, st, sh), unit stride along D; box = {64, 1, box_t, 1}
+static int make_map_4d(CUtensorMap* map, const void* ptr, int B, int T, int H, int D, long long sb, long long st, long long sh,
+                       uint32_t box_t) {
+    EncodeTiledFn enc = get_encode();
+    if (enc == nullptr) return -10;
+    cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)H, (cuuint64_t)T, (cuuint64_t)B};
+    cuuint64_t strides[3] = {(cuuint64_t)sh * 2, (cuuint64_t)st * 2, (cuuint64_t)sb * 2};
+    cuuint32_t box[4] = {64, 1, box_t, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -11;
+}
+
+}  // namespace fatc
+}  // namespace lmoe
+
+using namespace lmoe;
+using namespace lmoe::fatc;
+
+// q [B,Tq,Hq,D], k/v [B,Tk,Hkv,D] bf16 with element strides (batch, token, head); 16-byte aligned bases, strides % 8 == 0.
+LMOE_API int lmoe_flash_attn_fwd_tc(const void* q, const long long* qs, const void* k, const long long* ks, const void* v,
+                                    const long long* vs, const Args* ap, int D, cudaStream_t st) {
+    const Args a = *ap;
+    CUtensorMap mq, mk, mv;
+    int rc = make_map_4d(&mq, q, a.B, a.Tq, a.Hq, D, qs[0], qs[1], qs[2], BM);
+    if (rc) return rc;
+    rc = make_map_4d(&mk, k, a.B, a.Tk, a.Hkv, D, ks[0], ks[1], ks[2], BN);
+    if (rc) return rc;
+    rc = make_map_4d(&mv, v, a.B, a.Tk, a.Hkv, D, vs[0], vs[1], vs[2], 64);
+    if (rc) return rc;
+    dim3 grid((a.Tq + BM - 1) / BM, a.Hq, a.B);
+    if (D == 128) {
+        const size_t smem = sizeof(Smem<128>) + 1024;
+        cudaFuncSetAttribute(fa_fwd_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        fa_fwd_tc_kernel<128><<<grid, THREADS, smem, st>>>(mq, mk, mv, a);
+    } else if (D == 64) {
+        const size_t smem = sizeof(Smem<64>) + 1024;
+        cudaFuncSetAttribute(fa_fwd_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        fa_fwd_tc_kernel<64><<<grid, THREADS, smem, st>>>(mq, mk, mv, a);
+    } else return -1;
+    return (int)cudaGetLastError();
+}

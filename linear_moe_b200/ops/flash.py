@@ -12,6 +12,27 @@ import os
 import torch
 
 _ENABLED = os.environ.get("LMOE_FLASH_ATTN", "1") != "0"
+_TCGEN05_FWD = os.environ.get("LMOE_FLASH_TCGEN05", "1") != "0"      # forward on tcgen05/TMEM (csrc/flash_attn_tc.cu)
+
+
+class _FaTcArgs(ctypes.Structure):
+    _fields_ = ([("out", ctypes.c_void_p), ("lse", ctypes.c_void_p)] +
+                [(n, ctypes.c_int) for n in ("B", "Tq", "Tk", "Hq", "Hkv", "q_offset", "window")] +
+                [("scale", ctypes.c_float), ("err", ctypes.c_void_p)])
+
+
+def _forward_tcgen05(q, k, v, out, lse, scale, q_offset, window):
+    from . import cuda as K
+    from . import gemm
+    a = _FaTcArgs()
+    a.out, a.lse = out.data_ptr(), lse.data_ptr()
+    a.B, a.Tq, a.Hq = q.shape[0], q.shape[1], q.shape[2]
+    a.Tk, a.Hkv = k.shape[1], k.shape[2]
+    a.q_offset, a.window, a.scale = int(q_offset), int(window or 0), float(scale)
+    a.err = gemm._err(q.device).data_ptr()
+    st = lambda t: (ctypes.c_longlong * 3)(t.stride(0), t.stride(1), t.stride(2))
+    K._check(K.lib().lmoe_flash_attn_fwd_tc(K._p(q), st(q), K._p(k), st(k), K._p(v), st(v), ctypes.byref(a),
+                                            ctypes.c_int(q.shape[-1]), K._st()), "flash_attn_fwd_tc")
 
 
 class _FaArgs(ctypes.Structure):
@@ -59,9 +80,12 @@ class FlashAttention(torch.autograd.Function):
         B, Tq, Hq, D = q.shape
         out = torch.empty(B, Tq, Hq, D, dtype=q.dtype, device=q.device)
         lse = torch.empty(B, Hq, Tq, dtype=torch.float32, device=q.device)
-        a = _args(q, k, v, scale, q_offset, window)
-        a.out, a.lse = out.data_ptr(), lse.data_ptr()
-        K._check(K.lib().lmoe_flash_attn_fwd(ctypes.byref(a), ctypes.c_int(D), K._st()), "flash_attn_fwd")
+        if _TCGEN05_FWD:
+            _forward_tcgen05(q, k, v, out, lse, scale, q_offset, window)
+        else:
+            a = _args(q, k, v, scale, q_offset, window)
+            a.out, a.lse = out.data_ptr(), lse.data_ptr()
+            K._check(K.lib().lmoe_flash_attn_fwd(ctypes.byref(a), ctypes.c_int(D), K._st()), "flash_attn_fwd")
         ctx.save_for_backward(q, k, v, out, lse)
         ctx.cfg = (scale, q_offset, window)
         return out

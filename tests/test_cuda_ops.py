@@ -259,9 +259,12 @@ def test_lsm_vector_gla(D, T, with_state):
     (128, 384, 256, None, 2, 2),         # sequence-parallel rank: suffix of the positions against gathered keys
     (1, 200, 199, None, 4, 1),           # decoding against a cache
     (257, 257, 0, 100, 2, 1),            # sliding window
+    (1024, 1024, 0, None, 2, 2),         # several key tiles per query tile
 ])
-def test_flash_attention(D, Tq, Tk, q_offset, window, Hq, Hkv):
-    from linear_moe_b200.ops import flash
+@pytest.mark.parametrize("tcgen05", [True, False])
+def test_flash_attention(D, Tq, Tk, q_offset, window, Hq, Hkv, tcgen05, monkeypatch):
+    from linear_moe_b200.ops import flash, gemm
+    monkeypatch.setattr(flash, "_TCGEN05_FWD", tcgen05)
     torch.manual_seed(11)
     B = 2
     q = torch.randn(B, Tq, Hq, D, device=dev()).to(torch.bfloat16)
@@ -272,6 +275,7 @@ def test_flash_attention(D, Tq, Tk, q_offset, window, Hq, Hkv):
     f_k = lambda q, k, v: flash.FlashAttention.apply(q, k, v, D ** -0.5, q_offset, window)
     f_r = lambda q, k, v: R.softmax_attention(q, k, v, D ** -0.5, True, q_offset, window)
     (o,), gk = grads(f_k, [q, k, v], go)
+    gemm.check_error()
     (o2,), gr = grads(f_r, [q.float(), k.float(), v.float()], go.float())
     close(o, o2, 2e-2, 2e-2, "o")
     for name, a, b in zip(["dq", "dk", "dv"], gk, gr):
