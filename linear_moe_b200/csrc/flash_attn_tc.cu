@@ -1,14 +1,16 @@
 // Flash-attention forward on the 5th-generation tensor cores: S = Q K^T and O_j = P_j V_j are tcgen05.mma instructions
 // with accumulators in tensor memory, operands staged by TMA (4-D tensor maps over [B, T, H, D], 128-byte swizzle).
 //
-// One CTA = 128 queries of one head.  192 threads:
+// One CTA = 128 queries of one head.  128 + 128 * SPLIT threads (warps 0-1: TMA / MMA, warps 2-3 idle, warps 4.. softmax):
 //   warp 0      TMA producer: Q once, then K_j / V_j tiles of 128 keys through two 2-stage rings
 //   warp 1      MMA issuer:   S_{j+1} = Q K_{j+1}^T is issued before P_j V_j, so the tensor core works on the next
 //               score tile while the softmax warps are busy with the current one
-//   warps 2-5   softmax: thread r owns query row r (TMEM lane r): two passes over the 128 scores in tensor memory
-//               (row max, then exp2 / sum / bf16 pack), P_j written to shared memory in the K-major 128-byte-swizzle
-//               layout the MMA reads, then O += P_j V_j is folded into registers (o = o * corr + O_j) one iteration
-//               later, so that it overlaps the next tile's math.  No tensor-memory stores, no cross-thread shuffles.
+//   warps 4..   softmax: the SPLIT warps with equal (w & 3) own the 32 query rows of that TMEM lane quarter and split
+//               the columns: one tensor-memory load of the scores, row max (exchanged between the parts through
+//               shared memory and a named barrier), exp2 / sum / bf16 pack, P_j written to shared memory in
+//               the K-major 128-byte-swizzle layout the MMA reads; O += P_j V_j is folded into registers
+//               (o = o * corr + O_j) one iteration later, so that it overlaps the next tile's math.  SPLIT warps per
+//               scheduler hide the tensor-memory latency; no tensor-memory stores, no shuffles.
 // Tensor memory: 2 x 128 columns of scores + 2 x D columns of partial outputs.
 // Masking (causal with a query offset, sliding window, key length) is applied only on tiles that cross a boundary.
 // Every mbarrier wait is bounded (clock64 budget); on expiry the error word is set and the CTA drains and frees its
@@ -22,7 +24,7 @@ namespace lmoe {
 namespace fatc {
 using namespace lmoe::tc;
 
-constexpr int BM = 128, BN = 128, THREADS = 192, UMMA_K = 16;
+constexpr int BM = 128, BN = 128, SPLIT = 4, THREADS = 128 + 128 * SPLIT, UMMA_K = 16;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct Args {
@@ -41,6 +43,7 @@ struct __align__(1024) Smem {
     uint8_t v[2][BN * D * 2];
     uint8_t p[BM * BN * 2];
     uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], o_full[2], p_ready;
+    float mx[2][SPLIT][BM], ls[SPLIT][BM];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -49,9 +52,62 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, u
     asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
                  :: "r"(s32(dst)), "l"(map), "r"(s32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
+// Bounded wait that sleeps between polls: for the producer and MMA threads, whose spinning would otherwise take issue
+// slots from the softmax warps on the same scheduler.
+__device__ __forceinline__ bool mbar_wait_sleep(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
+    const long long t0 = clock64();
+    for (int i = 0;; ++i) {
+        if (mbar_test(bar, parity)) return true;
+        __nanosleep(40);
+        if ((i & 63) == 63) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > WAIT_CYCLES) break;
+        }
+    }
+    *abort_flag = 1;
+    atomicCAS(err, 0, code);
+    return false;
+}
 template <bool B_MN, int N>
 __host__ __device__ constexpr uint32_t idesc_bf16() {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&r)[64]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,"
+                 "%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]),
+                   "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]),
+                   "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]),
+                   "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]),
+                   "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+}
+template <int N>
+__device__ __forceinline__ void tmem_ld(uint32_t taddr, uint32_t (&r)[N]) {
+    static_assert(N == 16 || N == 32 || N == 64, "tensor-memory load width");
+    if constexpr (N == 64) tmem_ld64(taddr, r);
+    else if constexpr (N == 32) tmem_ld32(taddr, r);
+    else tmem_ld16(taddr, r);
+}
+// o[i] = o[i] * corr + partial[i] for this thread's OW columns of the partial output in tensor memory
+template <int OW>
+__device__ __forceinline__ void fold_o(float (&o)[OW], uint32_t taddr, float corr) {
+    uint32_t v[OW];
+    tmem_ld<OW>(taddr, v);
+    tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < OW; ++i) o[i] = fmaf(o[i], corr, __uint_as_float(v[i]));
 }
 
 template <int D>
@@ -85,7 +141,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             mbar_init(&sm.v_full[s], 1); mbar_init(&sm.v_empty[s], 1);
             mbar_init(&sm.s_full[s], 1); mbar_init(&sm.o_full[s], 1);
         }
-        mbar_init(&sm.p_ready, 4);
+        mbar_init(&sm.p_ready, 4 * SPLIT);
         sm.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -107,11 +163,11 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 const int s = j & 1;
                 const uint32_t ph = (j >> 1) & 1;
                 const int key0 = (nb_lo + j) * BN;
-                if (!mbar_wait(&sm.k_empty[s], ph ^ 1, abort_flag, err, 0x1100 | s)) break;
+                if (!mbar_wait_sleep(&sm.k_empty[s], ph ^ 1, abort_flag, err, 0x1100 | s)) break;
                 mbar_expect_tx(&sm.k_full[s], BN * D * 2);
 #pragma unroll
                 for (int kb = 0; kb < DK; ++kb) tma_load_4d(sm.k[s] + kb * BN * 128, &tmK, &sm.k_full[s], kb * 64, hk, key0, b);
-                if (!mbar_wait(&sm.v_empty[s], ph ^ 1, abort_flag, err, 0x1200 | s)) break;
+                if (!mbar_wait_sleep(&sm.v_empty[s], ph ^ 1, abort_flag, err, 0x1200 | s)) break;
                 mbar_expect_tx(&sm.v_full[s], BN * D * 2);
                 // MN-major operand: per 64 keys, D/64 boxes of {64 d, 64 keys} (8 KiB each)
 #pragma unroll
@@ -125,10 +181,10 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (lane == 0 && n_it > 0) {
             constexpr uint32_t idesc_s = idesc_bf16<false, BN>();
             constexpr uint32_t idesc_o = idesc_bf16<true, D>();
-            bool ok = mbar_wait(&sm.q_full, 0, abort_flag, err, 0x2000);
+            bool ok = mbar_wait_sleep(&sm.q_full, 0, abort_flag, err, 0x2000);
             auto issue_s = [&](int j) -> bool {
                 const int s = j & 1;
-                if (!mbar_wait(&sm.k_full[s], (j >> 1) & 1, abort_flag, err, 0x2100 | s)) return false;
+                if (!mbar_wait_sleep(&sm.k_full[s], (j >> 1) & 1, abort_flag, err, 0x2100 | s)) return false;
                 tc_fence_after();
                 const uint32_t qa = s32(sm.q), ka = s32(sm.k[s]);
 #pragma unroll
@@ -144,8 +200,8 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             for (int j = 0; ok && j < n_it; ++j) {
                 if (j + 1 < n_it) { ok = issue_s(j + 1); if (!ok) break; }
                 const int s = j & 1;
-                if (!mbar_wait(&sm.v_full[s], (j >> 1) & 1, abort_flag, err, 0x2200 | s)) break;
-                if (!mbar_wait(&sm.p_ready, j & 1, abort_flag, err, 0x2300)) break;
+                if (!mbar_wait_sleep(&sm.v_full[s], (j >> 1) & 1, abort_flag, err, 0x2200 | s)) break;
+                if (!mbar_wait_sleep(&sm.p_ready, j & 1, abort_flag, err, 0x2300)) break;
                 tc_fence_after();
                 const uint32_t pa = s32(sm.p), va = s32(sm.v[s]);
 #pragma unroll
@@ -158,79 +214,94 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 umma_commit(&sm.o_full[s]);
             }
         }
-    } else {
-        const int qd = warp & 3;                              // TMEM lane quarter of this warp
+    } else if (warp >= 4) {
+        // 4*SPLIT softmax warps: the SPLIT warps with the same (warp & 3) own the 32 query rows of that TMEM lane
+        // quarter and split the score / output columns between them
+        const int qd = warp & 3;
+        const int part = (warp - 4) >> 2;
         const int r = qd * 32 + lane;                         // query row inside the tile
         const int qi = a.q_offset + q0 + r;                   // absolute position of this query
         const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
         const float sc = a.scale * LOG2E;
-        float o[D];
+        constexpr int CW = BN / SPLIT;                        // score columns of this thread
+        constexpr int OW = D / SPLIT;                         // output columns of this thread
+        float o[OW];
 #pragma unroll
-        for (int i = 0; i < D; ++i) o[i] = 0.f;
+        for (int i = 0; i < OW; ++i) o[i] = 0.f;
         float m = -INFINITY, l = 0.f, corr_prev = 1.f;
-        uint8_t* prow = sm.p + (r >> 3) * 1024 + (r & 7) * 128;
+        // CW keys = CW * 2 bytes inside the 128-byte row of key block (part * CW) / 64
+        uint8_t* prow = sm.p + ((part * CW) >> 6) * (BM * 128) + (r >> 3) * 1024 + (r & 7) * 128;
+        const int ch0 = ((part * CW) & 63) >> 3;
         bool alive = n_it > 0;
         for (int j = 0; alive && j < n_it; ++j) {
             const int s = j & 1;
-            const int key0 = (nb_lo + j) * BN;
+            const int tile_key0 = (nb_lo + j) * BN;
+            const int key0 = tile_key0 + part * CW;           // first key of this thread's columns
             if (!mbar_wait(&sm.s_full[s], (j >> 1) & 1, abort_flag, err, 0x3100 | s)) { alive = false; break; }
             tc_fence_after();
-            const bool need_mask = (key0 + BN - 1 > a.q_offset + q0) || (key0 + BN > a.Tk) ||
-                                   (a.window > 0 && key0 <= a.q_offset + q0 + BM - 1 - a.window);
-            // pass 1: row maximum
-            float mx = m;
-#pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                uint32_t v[32];
-                tmem_ld32(lane_addr + s * BN + c, v);
+            const bool need_mask = (tile_key0 + BN - 1 > a.q_offset + q0) || (tile_key0 + BN > a.Tk) ||
+                                   (a.window > 0 && tile_key0 <= a.q_offset + q0 + BM - 1 - a.window);
+            // pass 1: row maximum, 16 columns at a time (keeps the live register set small)
+            float mx4[4] = {m, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int c = 0; c < CW; c += 16) {
+                uint32_t v[16];
+                tmem_ld16(lane_addr + s * BN + part * CW + c, v);
                 tmem_ld_wait();
                 if (need_mask) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
+                    for (int i = 0; i < 16; ++i) {
                         const int key = key0 + c + i;
                         const bool vis = key <= qi && key < a.Tk && (a.window <= 0 || key > qi - a.window);
-                        mx = fmaxf(mx, vis ? __uint_as_float(v[i]) : -INFINITY);
+                        if (!vis) v[i] = 0xff800000u;         // -inf
                     }
-                } else {
+                }
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(v[i]));
+                for (int i = 0; i < 16; i += 4) {
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], __uint_as_float(v[i + e]));
                 }
             }
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            // row maximum over the SPLIT parts (buffers alternate so that a fast thread cannot overwrite a value a slow
+            // one still has to read)
+            sm.mx[s][part][r] = mx;
+            asm volatile("bar.sync %0, %1;" :: "r"(1 + qd), "n"(32 * SPLIT) : "memory");
+#pragma unroll
+            for (int q2 = 0; q2 < SPLIT; ++q2) mx = fmaxf(mx, sm.mx[s][q2][r]);
             const float corr = (m == -INFINITY) ? 1.f : exp2f((m - mx) * sc);
             const float msc = (mx == -INFINITY) ? 0.f : mx * sc;
             m = mx;
             // the P buffer and the partial output of the previous tile are free once P_{j-1} V_{j-1} has completed
             if (j > 0 && !mbar_wait(&sm.o_full[s ^ 1], ((j - 1) >> 1) & 1, abort_flag, err, 0x3200 | s)) { alive = false; break; }
-            // pass 2: p = exp2(s * sc - m * sc), row sum, bf16 pack, swizzled store
-            float ps = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                uint32_t v[32];
-                tmem_ld32(lane_addr + s * BN + c, v);
+            // pass 2: p = exp2(s * sc - m * sc), row sum, bf16 pack, swizzled 16-byte stores
+            float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < CW; c += 16) {
+                uint32_t v[16];
+                tmem_ld16(lane_addr + s * BN + part * CW + c, v);
                 tmem_ld_wait();
-                uint32_t pk[16];
+                if (need_mask) {
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float x0 = __uint_as_float(v[i]), x1 = __uint_as_float(v[i + 1]);
-                    if (need_mask) {
+                    for (int i = 0; i < 16; ++i) {
                         const int key = key0 + c + i;
-                        const bool v0 = key <= qi && key < a.Tk && (a.window <= 0 || key > qi - a.window);
-                        const bool v1 = key + 1 <= qi && key + 1 < a.Tk && (a.window <= 0 || key + 1 > qi - a.window);
-                        x0 = v0 ? x0 : -INFINITY;
-                        x1 = v1 ? x1 : -INFINITY;
+                        const bool vis = key <= qi && key < a.Tk && (a.window <= 0 || key > qi - a.window);
+                        if (!vis) v[i] = 0xff800000u;
                     }
-                    const float p0 = exp2f(fmaf(x0, sc, -msc)), p1 = exp2f(fmaf(x1, sc, -msc));
-                    ps += p0 + p1;
-                    pk[i >> 1] = pack_bf16(p0, p1);
                 }
-                // 32 keys = 64 bytes = 4 chunks of 16 bytes inside the 128-byte row of key block c / 64
-                uint8_t* pb = prow + (c >> 6) * (BM * 128);
-                const int ch0 = (c & 63) >> 3;
 #pragma unroll
-                for (int g = 0; g < 4; ++g)
-                    *reinterpret_cast<uint4*>(pb + (((ch0 + g) ^ (r & 7)) << 4)) = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+                for (int i = 0; i < 16; i += 4) {
+                    const float p0 = exp2f(fmaf(__uint_as_float(v[i]), sc, -msc)), p1 = exp2f(fmaf(__uint_as_float(v[i + 1]), sc, -msc));
+                    const float p2 = exp2f(fmaf(__uint_as_float(v[i + 2]), sc, -msc)), p3 = exp2f(fmaf(__uint_as_float(v[i + 3]), sc, -msc));
+                    ps4[0] += p0; ps4[1] += p1; ps4[2] += p2; ps4[3] += p3;
+                    v[i >> 1] = pack_bf16(p0, p1);
+                    v[(i >> 1) + 1] = pack_bf16(p2, p3);
+                }
+                const int ch = ch0 + (c >> 3);
+                *reinterpret_cast<uint4*>(prow + ((ch ^ (r & 7)) << 4)) = make_uint4(v[0], v[1], v[2], v[3]);
+                *reinterpret_cast<uint4*>(prow + (((ch + 1) ^ (r & 7)) << 4)) = make_uint4(v[4], v[5], v[6], v[7]);
             }
-            l = l * corr + ps;
+            l = l * corr + ((ps4[0] + ps4[1]) + (ps4[2] + ps4[3]));
             // hand P_j to the MMA warp
             tc_fence_before();
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -239,14 +310,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             // fold the previous tile's partial output while the tensor core runs P_j V_j
             if (j > 0) {
                 tc_fence_after();
-#pragma unroll
-                for (int c = 0; c < D; c += 32) {
-                    uint32_t v[32];
-                    tmem_ld32(lane_addr + O_COL + (s ^ 1) * D + c, v);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], corr_prev, __uint_as_float(v[i]));
-                }
+                fold_o<OW>(o, lane_addr + O_COL + (s ^ 1) * D + part * OW, corr_prev);
             }
             corr_prev = corr;
         }
@@ -254,22 +318,21 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const int s = (n_it - 1) & 1;
             if (mbar_wait(&sm.o_full[s], ((n_it - 1) >> 1) & 1, abort_flag, err, 0x3300 | s)) {
                 tc_fence_after();
-#pragma unroll
-                for (int c = 0; c < D; c += 32) {
-                    uint32_t v[32];
-                    tmem_ld32(lane_addr + O_COL + s * D + c, v);
-                    tmem_ld_wait();
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], corr_prev, __uint_as_float(v[i]));
-                }
+                fold_o<OW>(o, lane_addr + O_COL + s * D + part * OW, corr_prev);
             }
         }
+        // total row sum over the parts
+        sm.ls[part][r] = l;
+        asm volatile("bar.sync %0, %1;" :: "r"(1 + qd), "n"(32 * SPLIT) : "memory");
+        l = 0.f;
+#pragma unroll
+        for (int q2 = 0; q2 < SPLIT; ++q2) l += sm.ls[q2][r];
         const int row = q0 + r;
         if (row < a.Tq) {
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            bf16* og = a.out + (((long long)b * a.Tq + row) * a.Hq + h) * D;
+            bf16* og = a.out + (((long long)b * a.Tq + row) * a.Hq + h) * D + part * OW;
 #pragma unroll
-            for (int c = 0; c < D; c += 8) {
+            for (int c = 0; c < OW; c += 8) {
                 uint4 w;
                 w.x = pack_bf16(o[c] * inv, o[c + 1] * inv);
                 w.y = pack_bf16(o[c + 2] * inv, o[c + 3] * inv);
@@ -277,7 +340,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 w.w = pack_bf16(o[c + 6] * inv, o[c + 7] * inv);
                 *reinterpret_cast<uint4*>(og + c) = w;
             }
-            a.lse[((long long)b * a.Hq + h) * a.Tq + row] = l > 0.f ? m * a.scale + logf(l) : -INFINITY;
+            if (part == 0) a.lse[((long long)b * a.Hq + h) * a.Tq + row] = l > 0.f ? m * a.scale + logf(l) : -INFINITY;
         }
     }
     tc_fence_before();
