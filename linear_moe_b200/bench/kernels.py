@@ -65,6 +65,7 @@ def bench_gemm(size):
         b = torch.randn(N, K, device=dev).bfloat16()
         c = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
         report(f"gemm tcgen05 {M}x{N}x{K}", timeit(lambda: gemm.gemm_nt(a, b, out=c)), flops=2.0 * M * N * K)
+        report(f"gemm tcgen05 2-CTA {M}x{N}x{K}", timeit(lambda: gemm.gemm_nt_2cta(a, b, out=c)), flops=2.0 * M * N * K)
         report(f"gemm cuBLAS  {M}x{N}x{K}", timeit(lambda: torch.mm(a, b.t(), out=c)), flops=2.0 * M * N * K)
     from ..ops import fp8
     for M, N, K in shapes:

@@ -1,0 +1,217 @@
+// bf16 GEMM C[M,N] = A[M,K] * B[N,K]^T on CTA pairs: tcgen05.mma.cta_group::2 computes a 256 x 256 tile per pair of
+// SMs, each CTA staging only its own 128 rows of A and its own 128 rows of B.
+//
+// Why pairs: the single-CTA kernel (gemm_tcgen05.cu, 128 x 256 tile) moves 96 KiB through one SM's shared memory per
+// 64-wide k-block (48 KiB written by TMA, 48 KiB read by the MMA) for 512 clk of tensor work, more than the ~128 B/clk
+// the shared memory delivers, and stalls at ~68 % tensor-pipe activity.  In a pair each CTA writes 32 KiB and the MMA
+// reads 32 KiB per CTA for the same 512 clk: 64 KiB per SM, inside the budget.
+//
+// Structure per CTA (192 threads, one CTA per SM, clusters of 2 along x):
+//   warp 0   TMA producer: own A rows [tm*256 + rank*128, +128) and own B rows [tn*256 + rank*128, +128) of every
+//            k-block into a 6-stage ring; the loads carry .cta_group::2 and complete on the LEADER CTA's `full`
+//            barrier (no multicast: every CTA fetches only what it stages itself).
+//   warp 1   (leader CTA only) MMA issuer: M=256, N=256, K=16 instructions on both CTAs' operands, accumulators in
+//            both CTAs' tensor memory (each holds its 128 rows x 256 columns, double buffered); tcgen05.commit with a
+//            2-CTA mask releases the stage in both CTAs and publishes the accumulator to both epilogues.
+//   warps 2-5  epilogue: TMEM -> registers -> bf16 -> global, then an arrive on the leader's `tmem_empty` barrier
+//            (remote arrive from the peer CTA).
+// Every wait is bounded by a clock64 budget; on expiry the error word is set, the CTA leaves its loops, the pair meets
+// at the final cluster barrier and tensor memory is released.
+#include <cooperative_groups.h>
+#include "tcgen05_utils.cuh"
+
+namespace lmoe {
+namespace g2 {
+using namespace lmoe::tc;
+
+constexpr int BM = 128, BN_HALF = 128, BN = 256, BK = 64, STAGES = 6, UMMA_K = 16;
+constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN_HALF * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int THREADS = 192;
+constexpr uint32_t TMEM_COLS = 512;
+
+struct __align__(1024) Smem {
+    uint8_t tiles[STAGES][STAGE_BYTES];
+    uint64_t full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `p` (a shared::cta address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t rank) {
+    uint32_t out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(s32(p)), "r"(rank));
+    return out;
+}
+// TMA load into this CTA's shared memory whose completion is signalled on an mbarrier that may live in the peer CTA
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 :: "r"(s32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+                 :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrive on the mbarrier at the same shared-memory offset in both CTAs of the pair once the MMAs issued so far are done
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 :: "r"(s32(bar)), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(bar_cluster_addr) : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm_bf16_nt_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, bf16* __restrict__ C,
+                         int M, int N, int K, int ldc, int* err) {
+    extern __shared__ uint8_t smem_raw[];
+    Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();                    // 0 = leader of the pair
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + BN - 1) / BN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int kblocks = (K + BK - 1) / BK;
+    volatile int* abort_flag = &sm.abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&sm.tmem_full[b], 1); mbar_init(&sm.tmem_empty[b], 8); }   // 4 warps x 2 CTAs
+        sm.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(s32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();                                          // both CTAs' barriers are initialised before any remote use
+    tc_fence_after();
+    const uint32_t tmem_base = sm.tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            for (int tile = pair; tile < num_tiles && !*abort_flag; tile += num_pairs) {
+                const int tm = tile % tiles_m, tn = tile / tiles_m;
+                const int a_row = tm * 2 * BM + (int)rank * BM, b_row = tn * BN + (int)rank * BN_HALF;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(&sm.empty[s], ph ^ 1, abort_flag, err, 0x5100 | s)) goto producer_done;
+                    if (rank == 0) mbar_expect_tx(&sm.full[s], 2 * STAGE_BYTES);       // both CTAs' loads land on this barrier
+                    const uint32_t full_leader = map_to_cta(&sm.full[s], 0);
+                    tma_load_2d_pair(sm.tiles[s], &tmA, full_leader, kb * BK, a_row);
+                    tma_load_2d_pair(sm.tiles[s] + A_BYTES, &tmB, full_leader, kb * BK, b_row);
+                }
+            }
+        }
+    producer_done:;
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // M = 256 (128 per CTA), N = 256, bf16 x bf16 -> fp32, both operands K-major
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+            int it = 0, lt = 0;
+            for (int tile = pair; tile < num_tiles && !*abort_flag; tile += num_pairs, ++lt) {
+                const int buf = lt & 1;
+                const uint32_t aph = (lt >> 1) & 1;
+                if (!mbar_wait(&sm.tmem_empty[buf], aph ^ 1, abort_flag, err, 0x5200 | buf)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                bool dead = false;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(&sm.full[s], ph, abort_flag, err, 0x5300 | s)) { dead = true; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = s32(sm.tiles[s]), b_addr = a_addr + A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k)
+                        umma_f16_pair(d_tmem, make_desc<false>(a_addr + k * UMMA_K * 2), make_desc<false>(b_addr + k * UMMA_K * 2), idesc,
+                                      (kb > 0 || k > 0) ? 1u : 0u);
+                    umma_commit_pair(&sm.empty[s]);
+                }
+                if (dead) break;
+                umma_commit_pair(&sm.tmem_full[buf]);
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        int lt = 0;
+        for (int tile = pair; tile < num_tiles; tile += num_pairs, ++lt) {
+            const int tm = tile % tiles_m, tn = tile / tiles_m;
+            const int buf = lt & 1;
+            const uint32_t aph = (lt >> 1) & 1;
+            if (!mbar_wait(&sm.tmem_full[buf], aph, abort_flag, err, 0x5400 | buf)) break;
+            tc_fence_after();
+            const int r = q * 32 + lane;
+            const int row = tm * 2 * BM + (int)rank * BM + r;
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+            bf16* crow = C + (long long)row * ldc + (long long)tn * BN;
+            const int cols_valid = N - tn * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(taddr + c, v);
+                tmem_ld_wait();
+                if (row < M) {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const int col = c + g * 8;
+                        if (col + 8 <= cols_valid) {
+                            uint4 o;
+                            o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
+                            o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
+                            o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
+                            o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
+                            *reinterpret_cast<uint4*>(crow + col) = o;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(&sm.tmem_empty[buf], 0));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();                                          // nobody leaves while the peer may still signal its barriers
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+}  // namespace g2
+}  // namespace lmoe
+
+using namespace lmoe;
+using namespace lmoe::g2;
+
+// A [M,K], B [N,K] bf16 (pitches lda, ldb), C [M,N] bf16 (pitch ldc).  K % 8 == 0, N % 8 == 0.
+LMOE_API int lmoe_gemm_bf16_nt_2cta(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int* err,
+                                    int num_sms, cudaStream_t st) {
+    if (K % 8 || N % 8 || lda % 8 || ldb % 8 || ldc % 8) return -1;
+    CUtensorMap ma, mb;
+    int rc = make_map(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)lda, BM);
+    if (rc) return rc;
+    rc = make_map(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN_HALF);
+    if (rc) return rc;
+    const size_t smem = sizeof(Smem) + 1024;
+    cudaFuncSetAttribute(gemm_bf16_nt_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+    int pairs = num_sms / 2;
+    if (tiles < pairs) pairs = tiles;
+    gemm_bf16_nt_2cta_kernel<<<2 * pairs, THREADS, smem, st>>>(ma, mb, (bf16*)C, M, N, K, ldc, err);
+    return (int)cudaGetLastError();
+}

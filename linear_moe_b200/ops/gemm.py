@@ -65,6 +65,20 @@ def gemm_nt(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None
     return out
 
 
+def gemm_nt_2cta(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``a @ b.T`` on CTA pairs (``tcgen05.mma.cta_group::2``, 256 x 256 tile per pair; ``csrc/gemm_2cta.cu``)."""
+    from . import cuda as K
+    M, Kd = a.shape
+    N = b.shape[0]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
+    rc = K.lib().lmoe_gemm_bf16_nt_2cta(K._p(a), K._p(b), K._p(out), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(Kd),
+                                        ctypes.c_int(a.stride(0)), ctypes.c_int(b.stride(0)), ctypes.c_int(out.stride(0)),
+                                        K._p(_err(a.device)), ctypes.c_int(K.NUM_SMS), K._st())
+    K._check(rc, "gemm_bf16_nt_2cta")
+    return out
+
+
 def tile_swiglu_weight(w: torch.Tensor) -> torch.Tensor:
     """``[2f, h]`` = [gate; up]  ->  per 128 output columns: 128 gate rows followed by the 128 up rows."""
     f = w.shape[0] // 2

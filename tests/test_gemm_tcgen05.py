@@ -119,3 +119,20 @@ def test_fp8_linear_close_to_bf16():
     for name, p, q in (("y", y, y2), ("dx", g1[0], x.grad), ("dw", g1[1], w.grad)):
         rel = (p.float() - q.float()).norm() / q.float().norm()
         assert rel < 6e-2, (name, rel.item())           # e4m3 has 3 mantissa bits: ~4 % relative error per GEMM
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 512), (1000, 328, 200), (4096, 2048, 1024), (128, 256, 2048)])
+def test_gemm_2cta_pairs(M, N, K):
+    """tcgen05.mma.cta_group::2 GEMM (256 x 256 tile per CTA pair) against the fp32 product."""
+    from linear_moe_b200.ops import gemm
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(M + N + K)
+    a = torch.randn(M, K, device=dev).to(torch.bfloat16)
+    b = torch.randn(N, K, device=dev).to(torch.bfloat16)
+    for _ in range(2):
+        c = gemm.gemm_nt_2cta(a, b)
+    torch.cuda.synchronize()
+    gemm.check_error()
+    ref = a.float() @ b.float().t()
+    err = (c.float() - ref).abs().max().item()
+    assert err <= 2e-2 * ref.abs().max().item() + 1e-2, (err, ref.abs().max().item())
