@@ -73,7 +73,8 @@ def bench_gemm(size):
         b = torch.randn(N, K, device=dev).bfloat16()
         aq, sa = fp8.quant_rows(a)
         bq, sb = fp8.quant_rows(b)
-        report(f"gemm fp8 tcgen05 {M}x{N}x{K}", timeit(lambda: fp8.gemm_nt(aq, sa, bq, sb)), flops=2.0 * M * N * K)
+        report(f"gemm fp8 tcgen05 {M}x{N}x{K}", timeit(lambda: fp8.gemm_nt(aq, sa, bq, sb, pairs=False)), flops=2.0 * M * N * K)
+        report(f"gemm fp8 tcgen05 2-CTA {M}x{N}x{K}", timeit(lambda: fp8.gemm_nt(aq, sa, bq, sb, pairs=True)), flops=2.0 * M * N * K)
         report(f"fp8 quant rows {M}x{K}", timeit(lambda: fp8.quant_rows(a)), bytes_=3.0 * M * K)
         report(f"fp8 quant cols^T {M}x{K}", timeit(lambda: fp8.quant_cols_t(a)), bytes_=5.0 * M * K)
     gemm.check_error()

@@ -24,8 +24,8 @@ namespace lmoe {
 namespace g2 {
 using namespace lmoe::tc;
 
-constexpr int BM = 128, BN_HALF = 128, BN = 256, BK = 64, STAGES = 6, UMMA_K = 16;
-constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN_HALF * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int BM = 128, BN_HALF = 128, BN = 256, BK_BYTES = 128, STAGES = 6;     // 64 bf16 or 128 e4m3 per k-block
+constexpr int A_BYTES = BM * BK_BYTES, B_BYTES = BN_HALF * BK_BYTES, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;
 
@@ -55,10 +55,16 @@ __device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* m
     asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  :: "r"(s32(dst)), "l"(map), "r"(bar_cluster_addr), "r"(c0), "r"(c1) : "memory");
 }
-__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
-                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
-                 :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+template <bool FP8>
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    if (FP8)
+        asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                     "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n}"
+                     :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+    else
+        asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\n"
+                     "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}"
+                     :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 // arrive on the mbarrier at the same shared-memory offset in both CTAs of the pair once the MMAs issued so far are done
 __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
@@ -69,9 +75,13 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(bar_cluster_addr) : "memory");
 }
 
+// FP8 = false: bf16 operands.  FP8 = true: e4m3 operands, C = diag(sa) acc diag(sb) (per-row scales of A and B).
+template <bool FP8>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
-gemm_bf16_nt_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, bf16* __restrict__ C,
-                         int M, int N, int K, int ldc, int* err) {
+gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, bf16* __restrict__ C,
+                    const float* __restrict__ sa, const float* __restrict__ sb, int M, int N, int K, int ldc, int* err) {
+    constexpr int BK = FP8 ? 128 : 64;                       // elements per k-block
+    constexpr int UMMA_K = FP8 ? 32 : 16;                    // 32 bytes of K per instruction
     extern __shared__ uint8_t smem_raw[];
     Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -119,7 +129,8 @@ gemm_bf16_nt_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
             // M = 256 (128 per CTA), N = 256, bf16 x bf16 -> fp32, both operands K-major
-            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+            constexpr uint32_t idesc = (1u << 4) | (FP8 ? 0u : ((1u << 7) | (1u << 10))) | ((uint32_t)(BN >> 3) << 17) |
+                                       ((uint32_t)((2 * BM) >> 4) << 24);
             int it = 0, lt = 0;
             for (int tile = pair; tile < num_tiles && !*abort_flag; tile += num_pairs, ++lt) {
                 const int buf = lt & 1;
@@ -136,8 +147,8 @@ gemm_bf16_nt_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                     const uint32_t a_addr = s32(sm.tiles[s]), b_addr = a_addr + A_BYTES;
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma_f16_pair(d_tmem, make_desc<false>(a_addr + k * UMMA_K * 2), make_desc<false>(b_addr + k * UMMA_K * 2), idesc,
-                                      (kb > 0 || k > 0) ? 1u : 0u);
+                        umma_pair<FP8>(d_tmem, make_desc<false>(a_addr + k * 32), make_desc<false>(b_addr + k * 32), idesc,
+                                       (kb > 0 || k > 0) ? 1u : 0u);
                     umma_commit_pair(&sm.empty[s]);
                 }
                 if (dead) break;
@@ -158,11 +169,28 @@ gemm_bf16_nt_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
             bf16* crow = C + (long long)row * ldc + (long long)tn * BN;
             const int cols_valid = N - tn * BN;
+            const float ra = (FP8 && row < M) ? sa[row] : 1.f;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 32) {
+                float4 sc[8];
+                if (FP8) {
+#pragma unroll
+                    for (int g = 0; g < 8; ++g)
+                        sc[g] = (c + g * 4 + 4 <= cols_valid) ? __ldg(reinterpret_cast<const float4*>(sb + tn * BN + c + g * 4))
+                                                               : make_float4(0.f, 0.f, 0.f, 0.f);
+                }
                 uint32_t v[32];
                 tmem_ld32(taddr + c, v);
                 tmem_ld_wait();
+                if (FP8) {
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        v[g * 4 + 0] = __float_as_uint(__uint_as_float(v[g * 4 + 0]) * ra * sc[g].x);
+                        v[g * 4 + 1] = __float_as_uint(__uint_as_float(v[g * 4 + 1]) * ra * sc[g].y);
+                        v[g * 4 + 2] = __float_as_uint(__uint_as_float(v[g * 4 + 2]) * ra * sc[g].z);
+                        v[g * 4 + 3] = __float_as_uint(__uint_as_float(v[g * 4 + 3]) * ra * sc[g].w);
+                    }
+                }
                 if (row < M) {
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
@@ -198,6 +226,31 @@ gemm_bf16_nt_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 using namespace lmoe;
 using namespace lmoe::g2;
 
+static int make_map_u8(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+    EncodeTiledFn enc = get_encode();
+    if (enc == nullptr) return -10;
+    cuuint64_t dims[2] = {cols, rows};
+    cuuint64_t strides[1] = {ld};
+    cuuint32_t box[2] = {128, box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -11;
+}
+
+template <bool FP8>
+static int launch_2cta(const CUtensorMap& ma, const CUtensorMap& mb, void* C, const float* sa, const float* sb, int M, int N, int K,
+                       int ldc, int* err, int num_sms, cudaStream_t st) {
+    const size_t smem = sizeof(Smem) + 1024;
+    cudaFuncSetAttribute(gemm_nt_2cta_kernel<FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+    int pairs = num_sms / 2;
+    if (tiles < pairs) pairs = tiles;
+    gemm_nt_2cta_kernel<FP8><<<2 * pairs, THREADS, smem, st>>>(ma, mb, (bf16*)C, sa, sb, M, N, K, ldc, err);
+    return (int)cudaGetLastError();
+}
+
 // A [M,K], B [N,K] bf16 (pitches lda, ldb), C [M,N] bf16 (pitch ldc).  K % 8 == 0, N % 8 == 0.
 LMOE_API int lmoe_gemm_bf16_nt_2cta(const void* A, const void* B, void* C, int M, int N, int K, int lda, int ldb, int ldc, int* err,
                                     int num_sms, cudaStream_t st) {
@@ -207,11 +260,17 @@ LMOE_API int lmoe_gemm_bf16_nt_2cta(const void* A, const void* B, void* C, int M
     if (rc) return rc;
     rc = make_map(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)ldb, BN_HALF);
     if (rc) return rc;
-    const size_t smem = sizeof(Smem) + 1024;
-    cudaFuncSetAttribute(gemm_bf16_nt_2cta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    const int tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
-    int pairs = num_sms / 2;
-    if (tiles < pairs) pairs = tiles;
-    gemm_bf16_nt_2cta_kernel<<<2 * pairs, THREADS, smem, st>>>(ma, mb, (bf16*)C, M, N, K, ldc, err);
-    return (int)cudaGetLastError();
+    return launch_2cta<false>(ma, mb, C, nullptr, nullptr, M, N, K, ldc, err, num_sms, st);
+}
+
+// A8 [M,K], B8 [N,K] e4m3 contiguous, sa [M], sb [N] fp32 row scales, C [M,N] bf16.  K % 16 == 0, N % 8 == 0.
+LMOE_API int lmoe_gemm_fp8_nt_2cta(const void* A, const void* B, void* C, const float* sa, const float* sb, int M, int N, int K,
+                                   int ldc, int* err, int num_sms, cudaStream_t st) {
+    if (K % 16 || N % 8 || ldc % 8) return -1;
+    CUtensorMap ma, mb;
+    int rc = make_map_u8(&ma, A, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM);
+    if (rc) return rc;
+    rc = make_map_u8(&mb, B, (uint64_t)N, (uint64_t)K, (uint64_t)K, BN_HALF);
+    if (rc) return rc;
+    return launch_2cta<true>(ma, mb, C, sa, sb, M, N, K, ldc, err, num_sms, st);
 }

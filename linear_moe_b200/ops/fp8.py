@@ -62,13 +62,19 @@ def quant_cols_t(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     return q, s
 
 
-def gemm_nt(a8: torch.Tensor, sa: torch.Tensor, b8: torch.Tensor, sb: torch.Tensor) -> torch.Tensor:
-    """``diag(sa) (a8 [M,K] @ b8 [N,K]^T) diag(sb)`` -> bf16 ``[M, N]``."""
+def gemm_nt(a8: torch.Tensor, sa: torch.Tensor, b8: torch.Tensor, sb: torch.Tensor, pairs: bool = True) -> torch.Tensor:
+    """``diag(sa) (a8 [M,K] @ b8 [N,K]^T) diag(sb)`` -> bf16 ``[M, N]``.  ``pairs`` selects the CTA-pair kernel
+    (``tcgen05.mma.cta_group::2``, ``csrc/gemm_2cta.cu``), which halves the shared-memory traffic per SM."""
     from . import cuda as K
     from . import gemm
     M, Kd = a8.shape
     N = b8.shape[0]
     out = torch.empty(M, N, dtype=torch.bfloat16, device=a8.device)
+    if pairs:
+        K._check(K.lib().lmoe_gemm_fp8_nt_2cta(K._p(a8), K._p(b8), K._p(out), K._p(sa), K._p(sb), ctypes.c_int(M), ctypes.c_int(N),
+                                               ctypes.c_int(Kd), ctypes.c_int(N), K._p(gemm._err(a8.device)),
+                                               ctypes.c_int(K.NUM_SMS), K._st()), "gemm_fp8_nt_2cta")
+        return out
     K._check(K.lib().lmoe_gemm_fp8_nt(K._p(a8), K._p(b8), K._p(out), K._p(sa), K._p(sb), ctypes.c_int(M), ctypes.c_int(N),
                                       ctypes.c_int(Kd), ctypes.c_int(N), K._p(gemm._err(a8.device)), ctypes.c_int(K.NUM_SMS),
                                       K._st()), "gemm_fp8_nt")

@@ -92,11 +92,12 @@ def test_fp8_gemm_and_quantisation(M, N, K):
     assert torch.allclose(sa, a.float().abs().amax(1) / 448.0, rtol=1e-6)
     want = (a.float() / sa[:, None]).to(torch.float8_e4m3fn).view(torch.uint8)
     assert (aq != want).float().mean().item() < 1e-3          # ties may round differently
-    c = fp8.gemm_nt(aq, sa, bq, sb)
-    gemm.check_error()
     ref = fp8.dequant_rows(aq, sa) @ fp8.dequant_rows(bq, sb).t()
-    err = (c.float() - ref).abs().max().item()
-    assert err <= 1e-2 * ref.abs().max().item(), (err, ref.abs().max().item())
+    for pairs in (False, True):                              # single-CTA and CTA-pair kernels
+        c = fp8.gemm_nt(aq, sa, bq, sb, pairs=pairs)
+        gemm.check_error()
+        err = (c.float() - ref).abs().max().item()
+        assert err <= 1e-2 * ref.abs().max().item(), (pairs, err, ref.abs().max().item())
     # transposed column-wise quantisation = row-wise quantisation of the transpose
     tq, ts = fp8.quant_cols_t(a)
     tq2, ts2 = fp8.quant_rows(a.t().contiguous())
