@@ -222,7 +222,7 @@ def bench_moe(size):
     from ..parallel import fused_comm
     dev = torch.device("cuda", 0)
     T, k, E, hid, f = (2048, 8, 8, 1024, 896) if size == "small" else (8192, 8, 8, 1024, 896)
-    ws = fused_comm.MoeWorkspace(None, E, hid, T * k + 128 * E, dev)
+    ws = fused_comm.MoeWorkspace(None, E, hid, T * k + 256 * E, dev)
     h = torch.randn(T, hid, device=dev).bfloat16().requires_grad_(True)
     probs, idx = torch.topk(torch.softmax(torch.randn(T, E, device=dev), -1), k, dim=-1)
     probs = probs.requires_grad_(True)

@@ -56,35 +56,36 @@ struct Tile {
     int rows_valid, cols_valid;
 };
 
-__device__ __forceinline__ bool decode_tile(const Params& p, int t, Tile& o) {
+// `bm` = rows of one output tile: 128 for one CTA, 256 for a CTA pair
+__device__ __forceinline__ bool decode_tile(const Params& p, int t, Tile& o, const int bm = BM) {
     const int tiles_n = (p.N + BN - 1) / BN;
     if (p.mode == 0) {
-        const int tiles_m = (p.M + BM - 1) / BM;
+        const int tiles_m = (p.M + bm - 1) / bm;
         if (t >= tiles_m * tiles_n) return false;
         const int tm = t % tiles_m, tn = t / tiles_m;
-        o.a_row = tm * BM; o.b_row = tn * BN; o.a_k0 = 0; o.b_k0 = 0;
+        o.a_row = tm * bm; o.b_row = tn * BN; o.a_k0 = 0; o.b_k0 = 0;
         o.kblocks = (p.K + BK - 1) / BK;
-        o.c_off = (long long)tm * BM * p.ldc + (long long)tn * BN;
-        o.rows_valid = p.M - tm * BM; o.cols_valid = p.N - tn * BN;
+        o.c_off = (long long)tm * bm * p.ldc + (long long)tn * BN;
+        o.rows_valid = p.M - tm * bm; o.cols_valid = p.N - tn * BN;
         return true;
     }
     if (p.mode == 1) {
         int base = 0;
         for (int e = 0; e < p.num_groups; ++e) {
             const int r0 = p.offs[e], r1 = p.offs[e + 1];
-            const int tm_e = (r1 - r0) / BM;
+            const int tm_e = (r1 - r0) / bm;
             const int n_e = tm_e * tiles_n;
             if (t < base + n_e) {
                 const int lt = t - base;
                 const int tm = lt % tm_e, tn = lt / tm_e;
-                o.a_row = r0 + tm * BM;
+                o.a_row = r0 + tm * bm;
                 o.a_k0 = 0;
                 // B map: K-major -> rows [e*N + tn*BN), k from 0.  MN-major -> mn column tn*BN, k rows from e*K
                 o.b_row = tn * BN;
                 o.b_k0 = e * p.b_group_rows;              // used as a row offset (K-major: added to b_row) or k offset (MN-major)
                 o.kblocks = (p.K + BK - 1) / BK;
-                o.c_off = (long long)(r0 + tm * BM) * p.ldc + (long long)tn * BN;
-                o.rows_valid = BM; o.cols_valid = p.N - tn * BN;
+                o.c_off = (long long)(r0 + tm * bm) * p.ldc + (long long)tn * BN;
+                o.rows_valid = bm; o.cols_valid = p.N - tn * BN;
                 return true;
             }
             base += n_e;
@@ -92,17 +93,17 @@ __device__ __forceinline__ bool decode_tile(const Params& p, int t, Tile& o) {
         return false;
     }
     // mode 2: per expert an (M x N) output, K = the expert's rows
-    const int tiles_m = (p.M + BM - 1) / BM;
+    const int tiles_m = (p.M + bm - 1) / bm;
     const int per = tiles_m * tiles_n;
     const int e = t / per;
     if (e >= p.num_groups) return false;
     const int lt = t - e * per;
     const int tm = lt % tiles_m, tn = lt / tiles_m;
     const int r0 = p.offs[e], r1 = p.offs[e + 1];
-    o.a_row = tm * BM; o.b_row = tn * BN; o.a_k0 = r0; o.b_k0 = r0;
+    o.a_row = tm * bm; o.b_row = tn * BN; o.a_k0 = r0; o.b_k0 = r0;
     o.kblocks = (r1 - r0) / BK;
-    o.c_off = (long long)e * p.c_group_stride + (long long)tm * BM * p.ldc + (long long)tn * BN;
-    o.rows_valid = p.M - tm * BM; o.cols_valid = p.N - tn * BN;
+    o.c_off = (long long)e * p.c_group_stride + (long long)tm * bm * p.ldc + (long long)tn * BN;
+    o.rows_valid = p.M - tm * bm; o.cols_valid = p.N - tn * BN;
     return true;
 }
 
@@ -252,6 +253,170 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, bf16* C, const P
     return (int)cudaGetLastError();
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// CTA-pair variant: tcgen05.mma.cta_group::2 on 256-row tiles (expert offsets must then be multiples of 256).  Each
+// CTA of the pair stages its own 128 rows (or 128 mn columns) of A and of B, the leader issues M = 256, N = 256 MMAs,
+// both CTAs drain their half of the accumulator.  Same protocol as gemm_2cta.cu.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int P_STAGES = 6, P_A_BYTES = 128 * BK * 2, P_B_BYTES = 128 * BK * 2, P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
+struct __align__(1024) SmemPair {
+    uint8_t tiles[P_STAGES][P_STAGE_BYTES];
+    uint64_t full[P_STAGES], empty[P_STAGES], tmem_full[2], tmem_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm_grouped_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, bf16* __restrict__ C, Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    SmemPair& sm = *reinterpret_cast<SmemPair*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    volatile int* abort_flag = &sm.abort_flag;
+    int* err = p.err;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < P_STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&sm.tmem_full[b], 1); mbar_init(&sm.tmem_empty[b], 8); }
+        sm.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(s32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();
+    tc_fence_after();
+    const uint32_t tmem_base = sm.tmem_base;
+    const int half = (int)rank * 128;                        // this CTA's rows of A (M) and of B (N) inside the pair tile
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            Tile t;
+            for (int tile = pair; !*abort_flag && decode_tile(p, tile, t, 256); tile += num_pairs) {
+                for (int kb = 0; kb < t.kblocks; ++kb, ++it) {
+                    const int s = it % P_STAGES;
+                    const uint32_t ph = (it / P_STAGES) & 1;
+                    if (!mbar_wait(&sm.empty[s], ph ^ 1, abort_flag, err, 0x6100 | s)) goto producer_done;
+                    if (rank == 0) mbar_expect_tx(&sm.full[s], 2 * P_STAGE_BYTES);
+                    const uint32_t fl = map_to_cta(&sm.full[s], 0);
+                    uint8_t* sa = sm.tiles[s];
+                    uint8_t* sb = sa + P_A_BYTES;
+                    if (!A_MN) {
+                        tma_load_2d_pair(sa, &tmA, fl, t.a_k0 + kb * BK, t.a_row + half);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) tma_load_2d_pair(sa + j * 8192, &tmA, fl, t.a_row + half + j * 64, t.a_k0 + kb * BK);
+                    }
+                    if (!B_MN) {
+                        const int brow = t.b_row + half + (p.mode == 1 ? t.b_k0 : 0);
+                        tma_load_2d_pair(sb, &tmB, fl, (p.mode == 1 ? 0 : t.b_k0) + kb * BK, brow);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) tma_load_2d_pair(sb + j * 8192, &tmB, fl, t.b_row + half + j * 64, t.b_k0 + kb * BK);
+                    }
+                }
+            }
+        }
+    producer_done:;
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) |
+                                       ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+            int it = 0, lt = 0;
+            Tile t;
+            for (int tile = pair; !*abort_flag && decode_tile(p, tile, t, 256); tile += num_pairs, ++lt) {
+                const int buf = lt & 1;
+                const uint32_t aph = (lt >> 1) & 1;
+                if (!mbar_wait(&sm.tmem_empty[buf], aph ^ 1, abort_flag, err, 0x6200 | buf)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                bool dead = false;
+                for (int kb = 0; kb < t.kblocks; ++kb, ++it) {
+                    const int s = it % P_STAGES;
+                    const uint32_t ph = (it / P_STAGES) & 1;
+                    if (!mbar_wait(&sm.full[s], ph, abort_flag, err, 0x6300 | s)) { dead = true; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = s32(sm.tiles[s]), b_addr = a_addr + P_A_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t ad = make_desc<A_MN>(a_addr + (A_MN ? k * 2048 : k * UMMA_K * 2));
+                        const uint64_t bd = make_desc<B_MN>(b_addr + (B_MN ? k * 2048 : k * UMMA_K * 2));
+                        umma_pair<false>(d_tmem, ad, bd, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit_pair(&sm.empty[s]);
+                }
+                if (dead) break;
+                umma_commit_pair(&sm.tmem_full[buf]);              // also for kblocks == 0: completes at once
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        int lt = 0;
+        Tile t;
+        for (int tile = pair; decode_tile(p, tile, t, 256); tile += num_pairs, ++lt) {
+            const int buf = lt & 1;
+            const uint32_t aph = (lt >> 1) & 1;
+            if (!mbar_wait(&sm.tmem_full[buf], aph, abort_flag, err, 0x6400 | buf)) break;
+            tc_fence_after();
+            const int r = half + q * 32 + lane;                  // row inside the 256-row tile
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+            bf16* crow = C + t.c_off + (long long)r * p.ldc;
+            const bool zero = t.kblocks == 0;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t v[32];
+                tmem_ld32(taddr + c, v);
+                tmem_ld_wait();
+                if (r < t.rows_valid) {
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        const int col = c + g * 8;
+                        if (col + 8 <= t.cols_valid) {
+                            uint4 o;
+                            if (zero) o = make_uint4(0, 0, 0, 0);
+                            else {
+                                o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
+                                o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
+                                o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
+                                o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
+                            }
+                            *reinterpret_cast<uint4*>(crow + col) = o;
+                        } else {
+                            for (int e = 0; e < 8; ++e)
+                                if (col + e < t.cols_valid) crow[col + e] = __float2bfloat16(zero ? 0.f : __uint_as_float(v[g * 8 + e]));
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(&sm.tmem_empty[buf], 0));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+template <bool A_MN, bool B_MN>
+static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mb, bf16* C, const Params& p, int grid, cudaStream_t st) {
+    const size_t smem = sizeof(SmemPair) + 1024;
+    cudaFuncSetAttribute(gemm_grouped_pair_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    gemm_grouped_pair_kernel<A_MN, B_MN><<<grid & ~1, THREADS, smem, st>>>(ma, mb, C, p);
+    return (int)cudaGetLastError();
+}
+
 }  // namespace gg
 }  // namespace lmoe
 
@@ -262,18 +427,25 @@ using namespace lmoe::gg;
 //   a_mn = 0: A is [rows, K] (K-major).   a_mn = 1: A is [K rows, M cols] (MN-major).   Same for B with N.
 // mode 0: dense (M, N, K).  mode 1: grouped along M by offs (A rows), B holds num_groups matrices stacked along its rows.
 // mode 2: grouped along K by offs (rows of A and B), C holds num_groups outputs c_group_stride elements apart.
+// pairs != 0: CTA-pair kernel (256-row tiles; in mode 1 every offset must be a multiple of 256).
 LMOE_API int lmoe_gemm_grouped(const void* A, int a_rows, int a_cols, int lda, int a_mn, const void* B, int b_rows, int b_cols,
                                int ldb, int b_mn, void* C, int ldc, int mode, int M, int N, int K, int num_groups,
-                               const int* offs, long long c_group_stride, int* err, int num_sms, cudaStream_t st) {
+                               const int* offs, long long c_group_stride, int* err, int num_sms, int pairs, cudaStream_t st) {
     if (lda % 8 || ldb % 8 || ldc % 8 || a_cols % 8 || b_cols % 8) return -1;
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, (uint64_t)a_rows, (uint64_t)a_cols, (uint64_t)lda, a_mn ? 64 : BM);
     if (rc) return rc;
-    rc = make_map(&mb, B, (uint64_t)b_rows, (uint64_t)b_cols, (uint64_t)ldb, b_mn ? 64 : BN);
+    rc = make_map(&mb, B, (uint64_t)b_rows, (uint64_t)b_cols, (uint64_t)ldb, b_mn ? 64 : (pairs ? 128 : BN));
     if (rc) return rc;
     Params p;
     p.mode = mode; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.num_groups = num_groups; p.offs = offs;
     p.c_group_stride = c_group_stride; p.b_group_rows = b_mn ? K : N; p.err = err;
+    if (pairs) {
+        if (!a_mn && !b_mn) return launch_pair<false, false>(ma, mb, (bf16*)C, p, num_sms, st);
+        if (!a_mn && b_mn) return launch_pair<false, true>(ma, mb, (bf16*)C, p, num_sms, st);
+        if (a_mn && b_mn) return launch_pair<true, true>(ma, mb, (bf16*)C, p, num_sms, st);
+        return launch_pair<true, false>(ma, mb, (bf16*)C, p, num_sms, st);
+    }
     if (!a_mn && !b_mn) return launch<false, false>(ma, mb, (bf16*)C, p, num_sms, st);
     if (!a_mn && b_mn) return launch<false, true>(ma, mb, (bf16*)C, p, num_sms, st);
     if (a_mn && b_mn) return launch<true, true>(ma, mb, (bf16*)C, p, num_sms, st);

@@ -12,7 +12,7 @@
 //   moe_push_kernel       dispatch: every (token, slot) row is written straight into the owner rank's receive buffer
 //                         with 16-byte peer stores (optionally scaled, which is the backward of the combine); the
 //                         last CTA to finish releases a flag on every peer and waits for theirs.
-//   moe_zero_pads_kernel  clears the <128 padding rows behind every expert segment so that the weight-gradient GEMMs,
+//   moe_zero_pads_kernel  clears the padding rows behind every expert segment so that the weight-gradient GEMMs,
 //                         which contract over the padded rows, see zeros.
 //   moe_signal_kernel     "my expert outputs are complete" flag to every peer.
 //   moe_pull_kernel       combine: waits for the owners' flags, then every token gathers its k expert outputs from
@@ -64,6 +64,7 @@ struct MoeArgs {
     bf16* out;                  // [T][h]
     bf16* rows;                 // [n_assign][h] or null: the gathered rows, unweighted
     int n_assign, k;
+    int pad;                    // expert segments in the receive buffer start at multiples of `pad` rows
 };
 
 // wait until flags[phase][j] >= epoch for every peer j; one thread per peer.  Returns through smem `fail`.
@@ -113,7 +114,7 @@ __global__ void moe_exchange_kernel(MoeArgs a) {
     if ((int)threadIdx.x < a.world) {
         const int d = threadIdx.x;
         long long run = 0;
-        for (int el = 0; el < a.El; ++el) run += (tot[d * a.El + el] + 127) / 128 * 128;
+        for (int el = 0; el < a.El; ++el) run += (tot[d * a.El + el] + a.pad - 1) / a.pad * a.pad;
         over[d] = run > a.cap;
         if (run > a.cap) atomicCAS(a.status, 0, (9 << 24) | (d << 16) | 7);        // receive buffer of rank d too small
     }
@@ -125,7 +126,7 @@ __global__ void moe_exchange_kernel(MoeArgs a) {
             const int e = d * a.El + el;
             a.send_base[e] = over[d] ? -1 : run + prior[e];
             if (d == a.rank) { a.offs[el] = over[d] ? 0 : run; a.real[el] = over[d] ? 0 : tot[e]; }
-            run += (tot[e] + 127) / 128 * 128;
+            run += (tot[e] + a.pad - 1) / a.pad * a.pad;
         }
         if (d == a.rank) a.offs[a.El] = over[d] ? 0 : run;
     }

@@ -98,27 +98,35 @@ def supports_grouped(x, w1, w2) -> bool:
 # ---------------------------------------------------------------------------------------------
 # grouped / layout-general GEMMs (csrc/gemm_grouped.cu)
 # ---------------------------------------------------------------------------------------------
-def _gg(A, a_mn, B, b_mn, C, mode, M, N, Kd, groups, offs, c_stride):
+PAIRS = os.environ.get("LMOE_GEMM_PAIRS", "1") != "0"     # CTA-pair (cta_group::2) kernels for the grouped GEMMs
+ROW_ALIGN = 256 if PAIRS else 128                          # expert segments are padded to whole pair tiles
+
+
+def _gg(A, a_mn, B, b_mn, C, mode, M, N, Kd, groups, offs, c_stride, pairs=None):
     from . import cuda as K
+    pairs = PAIRS if pairs is None else pairs
     rc = K.lib().lmoe_gemm_grouped(
         K._p(A), ctypes.c_int(A.shape[0]), ctypes.c_int(A.shape[1]), ctypes.c_int(A.stride(0)), ctypes.c_int(int(a_mn)),
         K._p(B), ctypes.c_int(B.shape[0]), ctypes.c_int(B.shape[1]), ctypes.c_int(B.stride(0)), ctypes.c_int(int(b_mn)),
         K._p(C), ctypes.c_int(C.stride(-2)), ctypes.c_int(mode), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(Kd),
-        ctypes.c_int(groups), K._p(offs), ctypes.c_longlong(c_stride), K._p(_err(A.device)), ctypes.c_int(K.NUM_SMS), K._st())
+        ctypes.c_int(groups), K._p(offs), ctypes.c_longlong(c_stride), K._p(_err(A.device)), ctypes.c_int(K.NUM_SMS),
+        ctypes.c_int(int(pairs)), K._st())
     K._check(rc, "gemm_grouped")
     return C
 
 
-def gemm_general(a: torch.Tensor, b: torch.Tensor, a_mn: bool = False, b_mn: bool = False) -> torch.Tensor:
+def gemm_general(a: torch.Tensor, b: torch.Tensor, a_mn: bool = False, b_mn: bool = False, pairs=None) -> torch.Tensor:
     """Dense ``C[M,N]``.  ``a`` is ``[M,K]`` (or ``[K,M]`` if ``a_mn``); ``b`` is ``[N,K]`` (or ``[K,N]`` if ``b_mn``)."""
     M, Kd = (a.shape[1], a.shape[0]) if a_mn else a.shape
     N = b.shape[1] if b_mn else b.shape[0]
     C = torch.empty(M, N, dtype=torch.bfloat16, device=a.device)
-    return _gg(a, a_mn, b, b_mn, C, 0, M, N, Kd, 0, None, 0)
+    return _gg(a, a_mn, b, b_mn, C, 0, M, N, Kd, 0, None, 0, pairs)
 
 
-def padded_offsets(counts: torch.Tensor, align: int = 128) -> torch.Tensor:
-    """Per-expert token counts -> int32 row offsets ``[E+1]`` with every segment padded to ``align`` rows (device op)."""
+def padded_offsets(counts: torch.Tensor, align: int = 0) -> torch.Tensor:
+    """Per-expert token counts -> int32 row offsets ``[E+1]`` with every segment padded to ``align`` rows (device op);
+    the default is the tile height of the grouped kernels in use (:data:`ROW_ALIGN`)."""
+    align = align or ROW_ALIGN
     padded = (counts + align - 1) // align * align
     offs = torch.zeros(counts.numel() + 1, dtype=torch.int32, device=counts.device)
     offs[1:] = torch.cumsum(padded, 0).to(torch.int32)
@@ -127,7 +135,8 @@ def padded_offsets(counts: torch.Tensor, align: int = 128) -> torch.Tensor:
 
 class GroupedLinear(torch.autograd.Function):
     """``y[rows of expert e] = x[rows of expert e] @ w[e]`` for ``w [E, K, N]`` over a padded expert-sorted buffer.
-    Forward, dgrad and wgrad are three launches of the grouped tcgen05 kernel; the expert offsets never leave the device."""
+    Forward, dgrad and wgrad are three launches of the grouped tcgen05 kernel; the expert offsets never leave the device.
+    Every offset must be a multiple of :data:`ROW_ALIGN`."""
 
     @staticmethod
     def forward(ctx, x, w, offs):
@@ -167,7 +176,7 @@ def grouped_mlp(x_sorted: torch.Tensor, tokens_per_expert: torch.Tensor, w1: tor
     start = torch.cumsum(counts, 0) - counts                                   # unpadded start of each expert
     eid = torch.repeat_interleave(torch.arange(E, device=x_sorted.device), counts, output_size=T)
     dest = offs[:-1].to(torch.int64)[eid] + (torch.arange(T, device=x_sorted.device) - start[eid])
-    Tp = (T + E * 127 + 127) // 128 * 128
+    Tp = (T + E * (ROW_ALIGN - 1) + ROW_ALIGN - 1) // ROW_ALIGN * ROW_ALIGN
     xp = torch.zeros(Tp, h, dtype=x_sorted.dtype, device=x_sorted.device).index_copy(0, dest, x_sorted)
     y1 = GroupedLinear.apply(xp, w1, offs)
     act = K.swiglu(y1)

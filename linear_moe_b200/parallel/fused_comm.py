@@ -165,7 +165,7 @@ def init_workspaces(mesh, cfg=None, tc=None):
         seq = (tc.seq_length if tc is not None else cfg.max_position_embeddings) // max(mesh.cp, 1)
         tokens = mb * seq * cfg.moe_topk
         factor = float(os.environ.get("LMOE_MOE_RECV_FACTOR", "2.0"))         # receive rows per rank / average
-        cap = int(tokens * factor) + 128 * (cfg.num_experts // ep.size)
+        cap = int(tokens * factor) + 256 * (cfg.num_experts // ep.size)
         _MOE[ep.name] = MoeWorkspace(ep, cfg.num_experts, cfg.hidden_size, cap, device)
 
 
@@ -251,7 +251,7 @@ class _MoeArgs(ctypes.Structure):
                 [("spin_limit", ctypes.c_longlong)] +
                 [(n, ctypes.c_void_p) for n in ("counts", "offs", "real", "send_base", "starts", "order", "sorted_e",
                                                 "dest_rank", "dest_row", "src", "w", "out", "rows")] +
-                [("n_assign", ctypes.c_int), ("k", ctypes.c_int)])
+                [("n_assign", ctypes.c_int), ("k", ctypes.c_int), ("pad", ctypes.c_int)])
 
 
 class MoeWorkspace:
@@ -264,7 +264,7 @@ class MoeWorkspace:
         W = self.W
         assert num_experts % W == 0 and hidden % 8 == 0
         self.E, self.El, self.h = num_experts, num_experts // W, hidden
-        self.cap = (cap_rows + 127) // 128 * 128
+        self.cap = (cap_rows + 255) // 256 * 256
         if group is not None:
             self.x, hx = _symm_empty(self.cap * hidden, torch.bfloat16, device, group)
             self.y, hy = _symm_empty(self.cap * hidden, torch.bfloat16, device, group)
@@ -297,6 +297,8 @@ class MoeWorkspace:
         a.status, a.done_ctr = status_word(self.device).data_ptr(), self.done_ctr.data_ptr()
         a.rank, a.world, a.E, a.El, a.cap, a.h = self.rank, self.W, self.E, self.El, self.cap, self.h
         a.spin_limit = self.spin_limit
+        from ..ops import gemm
+        a.pad = gemm.ROW_ALIGN
         return a
 
     def _run(self, which: int, a: _MoeArgs, name: str):

@@ -36,15 +36,16 @@ def test_gemm_nt_swiglu():
     assert err <= 2e-2 * ref.abs().max().item() + 1e-3, err
 
 
-@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("pairs", [False, True])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
 @pytest.mark.parametrize("M,N,K", [(256, 512, 256), (384, 320, 200)])
-def test_gemm_layouts(a_mn, b_mn, M, N, K):
+def test_gemm_layouts(a_mn, b_mn, M, N, K, pairs):
     from linear_moe_b200.ops import gemm
     dev = torch.device("cuda", 0)
     torch.manual_seed(1)
     a = torch.randn(M, K, device=dev).to(torch.bfloat16)
     b = torch.randn(N, K, device=dev).to(torch.bfloat16)
-    c = gemm.gemm_general(a.t().contiguous() if a_mn else a, b.t().contiguous() if b_mn else b, a_mn, b_mn)
+    c = gemm.gemm_general(a.t().contiguous() if a_mn else a, b.t().contiguous() if b_mn else b, a_mn, b_mn, pairs=pairs)
     torch.cuda.synchronize()
     gemm.check_error()
     ref = a.float() @ b.float().t()
@@ -52,9 +53,12 @@ def test_gemm_layouts(a_mn, b_mn, M, N, K):
     assert err <= 2e-2 * ref.abs().max().item() + 1e-3, err
 
 
-def test_grouped_mlp_matches_loop():
+@pytest.mark.parametrize("pairs", [False, True])
+def test_grouped_mlp_matches_loop(pairs, monkeypatch):
     from linear_moe_b200.ops import gemm
     from linear_moe_b200.ref import ops as R
+    monkeypatch.setattr(gemm, "PAIRS", pairs)                # single-CTA kernels (128-row tiles) or CTA pairs (256)
+    monkeypatch.setattr(gemm, "ROW_ALIGN", 256 if pairs else 128)
     dev = torch.device("cuda", 0)
     torch.manual_seed(2)
     E, h, f = 6, 256, 192

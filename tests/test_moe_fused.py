@@ -16,7 +16,7 @@ def test_fused_moe_one_rank(T, k, E, hid, f, drop):
     from linear_moe_b200.parallel import fused_comm
     dev = torch.device("cuda", 0)
     torch.manual_seed(3)
-    ws = fused_comm.MoeWorkspace(None, E, hid, T * k + 128 * E, dev)
+    ws = fused_comm.MoeWorkspace(None, E, hid, T * k + 256 * E, dev)
     h = torch.randn(T, hid, device=dev).to(torch.bfloat16)
     logits = torch.randn(T, E, device=dev)
     probs, idx = torch.topk(torch.softmax(logits, -1), k, dim=-1)
