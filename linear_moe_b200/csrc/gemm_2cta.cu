@@ -13,8 +13,10 @@
 //   warp 1   (leader CTA only) MMA issuer: M=256, N=256, K=16 instructions on both CTAs' operands, accumulators in
 //            both CTAs' tensor memory (each holds its 128 rows x 256 columns, double buffered); tcgen05.commit with a
 //            2-CTA mask releases the stage in both CTAs and publishes the accumulator to both epilogues.
-//   warps 2-5  epilogue: TMEM -> registers -> bf16 -> global, then an arrive on the leader's `tmem_empty` barrier
-//            (remote arrive from the peer CTA).
+//   warps 2-5  epilogue: TMEM -> registers -> bf16 -> swizzled shared-memory staging -> global stores in which 8 lanes
+//            write one row's 128 contiguous bytes (whole lines; the row-per-lane stores of the single-CTA kernel
+//            write 32 partial lines per instruction), then an arrive on the leader's `tmem_empty` barrier (remote
+//            arrive from the peer CTA).
 // Every wait is bounded by a clock64 budget; on expiry the error word is set, the CTA leaves its loops, the pair meets
 // at the final cluster barrier and tensor memory is released.
 #include <cooperative_groups.h>
@@ -31,6 +33,7 @@ constexpr uint32_t TMEM_COLS = 512;
 
 struct __align__(1024) Smem {
     uint8_t tiles[STAGES][STAGE_BYTES];
+    uint8_t stage_out[4][32 * 128];            // epilogue staging, one per epilogue warp
     uint64_t full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
     int abort_flag;
@@ -125,47 +128,58 @@ gemm_nt_2cta_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const uint32_t aph = (lt >> 1) & 1;
             if (!mbar_wait(&sm.tmem_full[buf], aph, abort_flag, err, 0x5400 | buf)) break;
             tc_fence_after();
-            const int r = q * 32 + lane;
-            const int row = tm * 2 * BM + (int)rank * BM + r;
+            const int row0 = tm * 2 * BM + (int)rank * BM + q * 32;       // first of this warp's 32 rows
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
-            bf16* crow = C + (long long)row * ldc + (long long)tn * BN;
             const int cols_valid = N - tn * BN;
-            const float ra = (FP8 && row < M) ? sa[row] : 1.f;
+            const float ra = (FP8 && row0 + lane < M) ? sa[row0 + lane] : 1.f;
+            uint8_t* stg = sm.stage_out[warp - 2];                         // 32 rows x 128 bytes, 16-byte chunks xor-swizzled
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                float4 sc[8];
-                if (FP8) {
+            for (int c = 0; c < BN; c += 64) {
 #pragma unroll
-                    for (int g = 0; g < 8; ++g)
-                        sc[g] = (c + g * 4 + 4 <= cols_valid) ? __ldg(reinterpret_cast<const float4*>(sb + tn * BN + c + g * 4))
-                                                               : make_float4(0.f, 0.f, 0.f, 0.f);
-                }
-                uint32_t v[32];
-                tmem_ld32(taddr + c, v);
-                tmem_ld_wait();
-                if (FP8) {
+                for (int hc = 0; hc < 2; ++hc) {
+                    const int cc = c + hc * 32;
+                    float4 sc[8];
+                    if (FP8) {
 #pragma unroll
-                    for (int g = 0; g < 8; ++g) {
-                        v[g * 4 + 0] = __float_as_uint(__uint_as_float(v[g * 4 + 0]) * ra * sc[g].x);
-                        v[g * 4 + 1] = __float_as_uint(__uint_as_float(v[g * 4 + 1]) * ra * sc[g].y);
-                        v[g * 4 + 2] = __float_as_uint(__uint_as_float(v[g * 4 + 2]) * ra * sc[g].z);
-                        v[g * 4 + 3] = __float_as_uint(__uint_as_float(v[g * 4 + 3]) * ra * sc[g].w);
+                        for (int g = 0; g < 8; ++g)
+                            sc[g] = (cc + g * 4 + 4 <= cols_valid) ? __ldg(reinterpret_cast<const float4*>(sb + tn * BN + cc + g * 4))
+                                                                    : make_float4(0.f, 0.f, 0.f, 0.f);
                     }
-                }
-                if (row < M) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + cc, v);
+                    tmem_ld_wait();
+                    if (FP8) {
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        const int col = c + g * 8;
-                        if (col + 8 <= cols_valid) {
-                            uint4 o;
-                            o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
-                            o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
-                            o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
-                            o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
-                            *reinterpret_cast<uint4*>(crow + col) = o;
+                        for (int g = 0; g < 8; ++g) {
+                            v[g * 4 + 0] = __float_as_uint(__uint_as_float(v[g * 4 + 0]) * ra * sc[g].x);
+                            v[g * 4 + 1] = __float_as_uint(__uint_as_float(v[g * 4 + 1]) * ra * sc[g].y);
+                            v[g * 4 + 2] = __float_as_uint(__uint_as_float(v[g * 4 + 2]) * ra * sc[g].z);
+                            v[g * 4 + 3] = __float_as_uint(__uint_as_float(v[g * 4 + 3]) * ra * sc[g].w);
                         }
                     }
+                    // this lane's row: 32 columns = 4 chunks of 16 bytes
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
+                        uint4 o;
+                        o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
+                        o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
+                        o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
+                        o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
+                        *reinterpret_cast<uint4*>(stg + lane * 128 + (((hc * 4 + g) ^ (lane & 7)) << 4)) = o;
+                    }
                 }
+                __syncwarp();
+                // 8 lanes write one row's 128 contiguous bytes: 4 rows per instruction, whole lines only
+                const int chunk = lane & 7;
+                const int col = c + chunk * 8;
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                    const int rr = it * 4 + (lane >> 3);
+                    const uint4 o = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((chunk ^ (rr & 7)) << 4));
+                    if (row0 + rr < M && col + 8 <= cols_valid)
+                        *reinterpret_cast<uint4*>(C + (long long)(row0 + rr) * ldc + (long long)tn * BN + col) = o;
+                }
+                __syncwarp();
             }
             tc_fence_before();
             __syncwarp();

@@ -262,6 +262,7 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mb, bf16* C, const P
 constexpr int P_STAGES = 6, P_A_BYTES = 128 * BK * 2, P_B_BYTES = 128 * BK * 2, P_STAGE_BYTES = P_A_BYTES + P_B_BYTES;
 struct __align__(1024) SmemPair {
     uint8_t tiles[P_STAGES][P_STAGE_BYTES];
+    uint8_t stage_out[4][32 * 128];            // epilogue staging, one per epilogue warp
     uint64_t full[P_STAGES], empty[P_STAGES], tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
     int abort_flag;
@@ -365,35 +366,42 @@ gemm_grouped_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             const uint32_t aph = (lt >> 1) & 1;
             if (!mbar_wait(&sm.tmem_full[buf], aph, abort_flag, err, 0x6400 | buf)) break;
             tc_fence_after();
-            const int r = half + q * 32 + lane;                  // row inside the 256-row tile
+            const int r0 = half + q * 32;                            // first of this warp's 32 rows inside the 256-row tile
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
-            bf16* crow = C + t.c_off + (long long)r * p.ldc;
-            const bool zero = t.kblocks == 0;
+            const bool zero = t.kblocks == 0;                        // an expert without tokens: its weight gradient is zero
+            uint8_t* stg = sm.stage_out[warp - 2];                   // 32 rows x 128 bytes, 16-byte chunks xor-swizzled
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                uint32_t v[32];
-                tmem_ld32(taddr + c, v);
-                tmem_ld_wait();
-                if (r < t.rows_valid) {
+            for (int c = 0; c < BN; c += 64) {
+#pragma unroll
+                for (int hc = 0; hc < 2; ++hc) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + c + hc * 32, v);
+                    tmem_ld_wait();
 #pragma unroll
                     for (int g = 0; g < 4; ++g) {
-                        const int col = c + g * 8;
-                        if (col + 8 <= t.cols_valid) {
-                            uint4 o;
-                            if (zero) o = make_uint4(0, 0, 0, 0);
-                            else {
-                                o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
-                                o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
-                                o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
-                                o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
-                            }
-                            *reinterpret_cast<uint4*>(crow + col) = o;
-                        } else {
-                            for (int e = 0; e < 8; ++e)
-                                if (col + e < t.cols_valid) crow[col + e] = __float2bfloat16(zero ? 0.f : __uint_as_float(v[g * 8 + e]));
+                        uint4 o;
+                        if (zero) o = make_uint4(0, 0, 0, 0);
+                        else {
+                            o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
+                            o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
+                            o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
+                            o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
                         }
+                        *reinterpret_cast<uint4*>(stg + lane * 128 + (((hc * 4 + g) ^ (lane & 7)) << 4)) = o;
                     }
                 }
+                __syncwarp();
+                // 8 lanes write one row's 128 contiguous bytes: whole lines, 4 rows per instruction
+                const int chunk = lane & 7;
+                const int col = c + chunk * 8;
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                    const int rr = it * 4 + (lane >> 3);
+                    const uint4 o = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((chunk ^ (rr & 7)) << 4));
+                    if (r0 + rr < t.rows_valid && col + 8 <= t.cols_valid)
+                        *reinterpret_cast<uint4*>(C + t.c_off + (long long)(r0 + rr) * p.ldc + col) = o;
+                }
+                __syncwarp();
             }
             tc_fence_before();
             __syncwarp();
@@ -431,7 +439,7 @@ using namespace lmoe::gg;
 LMOE_API int lmoe_gemm_grouped(const void* A, int a_rows, int a_cols, int lda, int a_mn, const void* B, int b_rows, int b_cols,
                                int ldb, int b_mn, void* C, int ldc, int mode, int M, int N, int K, int num_groups,
                                const int* offs, long long c_group_stride, int* err, int num_sms, int pairs, cudaStream_t st) {
-    if (lda % 8 || ldb % 8 || ldc % 8 || a_cols % 8 || b_cols % 8) return -1;
+    if (lda % 8 || ldb % 8 || ldc % 8 || a_cols % 8 || b_cols % 8 || N % 8) return -1;
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, (uint64_t)a_rows, (uint64_t)a_cols, (uint64_t)lda, a_mn ? 64 : BM);
     if (rc) return rc;
