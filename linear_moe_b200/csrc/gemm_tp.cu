@@ -3,10 +3,14 @@
 //
 //   mode 0  all-gather -> GEMM   C[M_full, N] = gather_r(A_r)[M_full, K] * B      (column-parallel forward: QKV / FC1 /
 //           in_proj; row-parallel input gradient).  Every rank publishes its activation shard A_r [M_loc, K] in a
-//           symmetric buffer and raises a flag on its peers.  The TMA producer of this kernel reads the row tiles of
-//           rank r straight from rank r's buffer (one tensor map per peer, no multicast), after a bounded
-//           acquire-wait on r's flag.  Tiles of the local shard are scheduled first, so the remote shards arrive
-//           while the tensor cores work on local data; the gathered matrix is never materialised.
+//           symmetric buffer and raises a flag on its peers.  The first `n_copy` CTAs of this kernel are copiers: after
+//           a bounded acquire-wait on a peer's flag they pull that peer's shard over NVLink, 128 rows at a time, into
+//           the local gathered matrix (each remote byte crosses the link once) and release a per-row-block flag.  The
+//           other CTAs are GEMM workers: tiles of the local shard (read from the own symmetric buffer) are scheduled
+//           first, so the remote shards arrive while the tensor cores work on local data; the TMA producer of a tile
+//           on remote rows waits (bounded) for that row block's flag and reads it from local memory.  All CTAs of the
+//           launch are co-resident (grid <= number of SMs, one CTA per SM).  The gathered matrix also serves the
+//           weight-gradient GEMM of the backward pass.
 //   mode 1  GEMM -> reduce-scatter   each rank holds a K-slice and computes the partial C[M_full, N]; the epilogue
 //           stores every tile (bf16) into the owner rank's inbox slot [src = this rank] with 16-byte peer stores,
 //           tiles of the other ranks first.  The last CTA raises a flag on every peer.  tp_reduce_kernel on the owner
@@ -36,6 +40,7 @@ constexpr int MAX_W = 8;
 
 struct __align__(1024) Smem {
     uint8_t tiles[STAGES][STAGE_BYTES];
+    uint8_t stage_out[4][32 * 128];            // epilogue staging, one per epilogue warp
     uint64_t full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2];
     uint32_t tmem_base;
     int abort_flag;
@@ -59,6 +64,11 @@ struct Params {
     int* status;                // fused-communication status word (bounded flag waits)
     int* err;                   // GEMM error word (bounded mbarrier waits)
     long long spin_cycles;
+    // mode 0: gather by copier CTAs
+    const bf16* const* peer_x;  // [W] published shards of this call ([M_loc, K] each)
+    bf16* gathered;             // local [M_full, K]: remote rows are written here (the local rows too, by the host copy)
+    int* ready;                 // [W * M_loc / 128] epoch per (source rank, row block) of `gathered`
+    int n_copy;                 // number of copier CTAs (0 when world == 1)
 };
 
 __device__ __forceinline__ void st_rel_sys(int* p, int v) {
@@ -68,6 +78,79 @@ __device__ __forceinline__ int ld_acq_sys(const int* p) {
     int v;
     asm volatile("ld.acquire.sys.global.s32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
     return v;
+}
+__device__ __forceinline__ void st_rel_gpu(int* p, int v) {
+    asm volatile("st.release.gpu.global.s32 [%0], %1;\n" :: "l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acq_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Copier CTA: pull 128-row blocks of the peers' shards into the local gathered matrix.  One thread drives bulk copies
+// (peer global -> shared memory ring -> local global), which keeps 3 x 48 KiB in flight per CTA over NVLink without
+// spending registers or issue slots; a row block is contiguous on both sides.
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(s32(dst)), "l"(src), "r"(bytes), "r"(s32(bar)) : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void* dst, const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" :: "l"(dst), "r"(s32(src)), "r"(bytes) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <class SmemT>
+__device__ __forceinline__ void copier_loop(const Params& p, int copier, SmemT& sm) {
+    if (threadIdx.x != 0) return;
+    volatile int* abort_flag = &sm.abort_flag;
+    const int tpr = p.M_loc / BM;
+    const long long block_bytes = (long long)BM * p.K * 2;
+    unsigned ready_mask = 0;
+    int it = 0;                                                 // pieces issued so far (ring position)
+    for (int idx = copier; idx < (p.world - 1) * tpr; idx += p.n_copy) {
+        const int s = idx / tpr + 1, j = idx - (s - 1) * tpr;
+        const int src = (p.rank + s) % p.world;
+        if (!((ready_mask >> src) & 1u)) {
+            const int* f = p.peer_flags[p.rank] + src;
+            const long long t0 = clock64();
+            while (ld_acq_sys(f) < p.epoch) {
+                if (clock64() - t0 > p.spin_cycles) { atomicCAS(p.status, 0, (10 << 24) | (src << 16) | 4); return; }
+                __nanosleep(100);
+            }
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            ready_mask |= 1u << src;
+        }
+        const int local_row = j * BM;
+        const int b = local_row / p.T_loc, tt = local_row - b * p.T_loc;
+        const long long full_row = (long long)b * p.world * p.T_loc + (long long)src * p.T_loc + tt;
+        const uint8_t* in = reinterpret_cast<const uint8_t*>(p.peer_x[src]) + (long long)local_row * p.K * 2;
+        uint8_t* out = reinterpret_cast<uint8_t*>(p.gathered) + full_row * p.K * 2;
+        const int pieces = (int)((block_bytes + STAGE_BYTES - 1) / STAGE_BYTES);
+        const int lag = STAGES - 1;
+        const int it0 = it;
+        for (int i = 0; i < pieces + lag; ++i) {
+            if (i < pieces) {
+                const int st = (it0 + i) % STAGES;
+                // the store that last read this stage was committed in the previous iteration
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                const uint32_t bytes = (uint32_t)min((long long)STAGE_BYTES, block_bytes - (long long)i * STAGE_BYTES);
+                mbar_expect_tx(&sm.full[st], bytes);
+                bulk_g2s(sm.tiles[st], in + (long long)i * STAGE_BYTES, bytes, &sm.full[st]);
+            }
+            const int jj = i - lag;
+            if (jj >= 0) {
+                const int st = (it0 + jj) % STAGES;
+                const uint32_t ph = ((it0 + jj) / STAGES) & 1;
+                if (!mbar_wait(&sm.full[st], ph, abort_flag, p.err, 0x700 | st)) return;
+                const uint32_t bytes = (uint32_t)min((long long)STAGE_BYTES, block_bytes - (long long)jj * STAGE_BYTES);
+                bulk_s2g(out + (long long)jj * STAGE_BYTES, sm.tiles[st], bytes);
+            }
+        }
+        it = it0 + pieces;
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // the block is in local memory
+        __threadfence();
+        st_rel_gpu(p.ready + src * tpr + j, p.epoch);
+    }
 }
 
 struct Tile {
@@ -118,18 +201,24 @@ gemm_tp_kernel(const __grid_constant__ Maps mapsA, const __grid_constant__ CUten
     tc_fence_after();
     const uint32_t tmem_base = sm.tmem_base;
     const int kblocks = (p.K + BK - 1) / BK;
+    const int n_copy = p.mode == 0 ? p.n_copy : 0;
+    const int worker = (int)blockIdx.x - n_copy, workers = (int)gridDim.x - n_copy;
+    const int tpr = p.M_loc / BM;
 
-    if (warp == 0) {
+    if (worker < 0) {
+        // copier CTA (mode 0): no tensor-core work
+        copier_loop(p, (int)blockIdx.x, sm);
+    } else if (warp == 0) {
         if (lane == 0) {
             int it = 0;
-            unsigned ready = 1u << p.rank;                       // the own shard needs no flag
             Tile t;
-            for (int tile = blockIdx.x; !*abort_flag && decode_tile(p, tile, t); tile += gridDim.x) {
-                if (p.mode == 0 && !((ready >> t.peer) & 1u)) {
-                    const int* f = p.peer_flags[p.rank] + t.peer;
+            for (int tile = worker; !*abort_flag && decode_tile(p, tile, t); tile += workers) {
+                const bool remote = p.mode == 0 && t.peer != p.rank;
+                if (remote) {
+                    const int* f = p.ready + t.peer * tpr + t.local_row / BM;
                     const long long t0 = clock64();
                     bool ok = true;
-                    while (ld_acq_sys(f) < p.epoch) {
+                    while (ld_acq_gpu(f) < p.epoch) {
                         if (clock64() - t0 > p.spin_cycles) { ok = false; break; }
                         __nanosleep(100);
                     }
@@ -139,10 +228,10 @@ gemm_tp_kernel(const __grid_constant__ Maps mapsA, const __grid_constant__ CUten
                         break;
                     }
                     asm volatile("fence.proxy.async.global;" ::: "memory");
-                    ready |= 1u << t.peer;
                 }
-                const CUtensorMap* ma = p.mode == 0 ? &mapsA.m[t.peer] : &mapsA.m[0];
-                const int a_row = p.mode == 0 ? t.local_row : t.full_row;
+                // mode 0: own rows from the own published shard (map 0), remote rows from the gathered matrix (map 1)
+                const CUtensorMap* ma = remote ? &mapsA.m[1] : &mapsA.m[0];
+                const int a_row = (p.mode == 0 && !remote) ? t.local_row : t.full_row;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
@@ -167,7 +256,7 @@ gemm_tp_kernel(const __grid_constant__ Maps mapsA, const __grid_constant__ CUten
             constexpr uint32_t idesc = make_idesc<false, B_MN, BM, BN>();
             int it = 0, lt = 0;
             Tile t;
-            for (int tile = blockIdx.x; !*abort_flag && decode_tile(p, tile, t); tile += gridDim.x, ++lt) {
+            for (int tile = worker; !*abort_flag && decode_tile(p, tile, t); tile += workers, ++lt) {
                 const int buf = lt & 1;
                 const uint32_t aph = (lt >> 1) & 1;
                 if (!mbar_wait(&sm.tmem_empty[buf], aph ^ 1, abort_flag, err, 0x200 | buf)) break;
@@ -196,33 +285,46 @@ gemm_tp_kernel(const __grid_constant__ Maps mapsA, const __grid_constant__ CUten
         const int q = warp & 3;
         int lt = 0;
         Tile t;
-        for (int tile = blockIdx.x; decode_tile(p, tile, t); tile += gridDim.x, ++lt) {
+        for (int tile = worker; decode_tile(p, tile, t); tile += workers, ++lt) {
             const int buf = lt & 1;
             const uint32_t aph = (lt >> 1) & 1;
             if (!mbar_wait(&sm.tmem_full[buf], aph, abort_flag, err, 0x400 | buf)) break;
             tc_fence_after();
-            const int r = q * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
-            bf16* crow;
-            if (p.mode == 0) crow = p.C + (long long)(t.full_row + r) * p.ldc + (long long)t.tn * BN;
-            else crow = p.peer_inbox[t.peer] + p.inbox_off + ((long long)p.rank * p.M_loc + t.local_row + r) * p.N + (long long)t.tn * BN;
+            // first of this warp's 32 output rows; mode 1 writes into the owner rank's inbox slot [src = this rank]
+            bf16* cbase;
+            long long ld;
+            if (p.mode == 0) { cbase = p.C + (long long)(t.full_row + q * 32) * p.ldc + (long long)t.tn * BN; ld = p.ldc; }
+            else { cbase = p.peer_inbox[t.peer] + p.inbox_off + ((long long)p.rank * p.M_loc + t.local_row + q * 32) * p.N + (long long)t.tn * BN; ld = p.N; }
+            uint8_t* stg = sm.stage_out[warp - 2];                       // 32 rows x 128 bytes, 16-byte chunks xor-swizzled
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 32) {
-                uint32_t v[32];
-                tmem_ld32(taddr + c, v);
-                tmem_ld_wait();
+            for (int c = 0; c < BN; c += 64) {
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    const int col = c + g * 8;
-                    if (col + 8 <= t.cols_valid) {
+                for (int hc = 0; hc < 2; ++hc) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + c + hc * 32, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) {
                         uint4 o;
                         o.x = pack_bf16(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1]));
                         o.y = pack_bf16(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3]));
                         o.z = pack_bf16(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5]));
                         o.w = pack_bf16(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7]));
-                        *reinterpret_cast<uint4*>(crow + col) = o;
+                        *reinterpret_cast<uint4*>(stg + lane * 128 + (((hc * 4 + g) ^ (lane & 7)) << 4)) = o;
                     }
                 }
+                __syncwarp();
+                // 8 lanes write one row's 128 contiguous bytes (whole lines, also over NVLink in mode 1)
+                const int chunk = lane & 7;
+                const int col = c + chunk * 8;
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                    const int rr = it * 4 + (lane >> 3);
+                    const uint4 o = *reinterpret_cast<const uint4*>(stg + rr * 128 + ((chunk ^ (rr & 7)) << 4));
+                    if (col + 8 <= t.cols_valid) *reinterpret_cast<uint4*>(cbase + (long long)rr * ld + col) = o;
+                }
+                __syncwarp();
             }
             tc_fence_before();
             __syncwarp();
@@ -339,23 +441,28 @@ __global__ void tp_gather_kernel(CommArgs a) {
 using namespace lmoe;
 using namespace lmoe::tp;
 
-// a_ptrs: mode 0: W base pointers of the published shards ([M_loc, K], contiguous); mode 1: a_ptrs[0] = local A [M_full, K].
+// mode 0: a_ptrs[0] = this rank's published shard [M_loc, K], a_ptrs[1] = local gathered matrix [M_full, K] (scratch that the
+//         copier CTAs fill; also pp->gathered), pp->peer_x = device array of the W published shards, pp->n_copy copier CTAs.
+// mode 1: a_ptrs[0] = local A [M_full, K].
 LMOE_API int lmoe_gemm_tp(int mode, const void* const* a_ptrs, const void* B, int b_rows, int b_cols, int b_mn,
                           const Params* pp, int num_sms, cudaStream_t st) {
     Params p = *pp;
     p.mode = mode;
     if (p.world > MAX_W || p.M_loc % BM || p.T_loc % BM || p.K % 8 || p.N % 8 || b_cols % 8) return -1;
+    if (mode == 0 && p.world > 1 && (p.n_copy < 1 || p.n_copy >= num_sms)) return -2;
+    if (mode != 0 || p.world == 1) p.n_copy = 0;
     Maps maps;
-    const int nmaps = mode == 0 ? p.world : 1;
-    const uint64_t a_rows = mode == 0 ? (uint64_t)p.M_loc : (uint64_t)p.M_loc * p.world;
-    for (int i = 0; i < MAX_W; ++i) {
-        int rc = make_map(&maps.m[i], a_ptrs[i < nmaps ? i : 0], a_rows, (uint64_t)p.K, (uint64_t)p.K, BM);
-        if (rc) return rc;
-    }
+    const uint64_t m_full = (uint64_t)p.M_loc * p.world;
+    int rc = make_map(&maps.m[0], a_ptrs[0], mode == 0 ? (uint64_t)p.M_loc : m_full, (uint64_t)p.K, (uint64_t)p.K, BM);
+    if (rc) return rc;
+    rc = make_map(&maps.m[1], a_ptrs[mode == 0 ? 1 : 0], m_full, (uint64_t)p.K, (uint64_t)p.K, BM);
+    if (rc) return rc;
+    for (int i = 2; i < MAX_W; ++i) maps.m[i] = maps.m[0];
     CUtensorMap mb;
-    int rc = make_map(&mb, B, (uint64_t)b_rows, (uint64_t)b_cols, (uint64_t)b_cols, b_mn ? 64 : BN);
+    rc = make_map(&mb, B, (uint64_t)b_rows, (uint64_t)b_cols, (uint64_t)b_cols, b_mn ? 64 : BN);
     if (rc) return rc;
     const size_t smem = sizeof(Smem) + 1024;
+    // one CTA per SM and grid <= number of SMs: every CTA of the launch is resident, which the copier / worker hand-off needs
     if (b_mn) {
         cudaFuncSetAttribute(gemm_tp_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         gemm_tp_kernel<true><<<num_sms, THREADS, smem, st>>>(maps, mb, p);

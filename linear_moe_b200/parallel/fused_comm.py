@@ -378,7 +378,8 @@ class _TpParams(ctypes.Structure):
     _fields_ = ([(n, ctypes.c_int) for n in ("mode", "rank", "world", "M_loc", "T_loc", "N", "K", "ldc")] +
                 [("C", ctypes.c_void_p), ("peer_inbox", ctypes.c_void_p), ("inbox_off", ctypes.c_longlong),
                  ("peer_flags", ctypes.c_void_p), ("epoch", ctypes.c_int), ("done_ctr", ctypes.c_void_p),
-                 ("status", ctypes.c_void_p), ("err", ctypes.c_void_p), ("spin_cycles", ctypes.c_longlong)])
+                 ("status", ctypes.c_void_p), ("err", ctypes.c_void_p), ("spin_cycles", ctypes.c_longlong),
+                 ("peer_x", ctypes.c_void_p), ("gathered", ctypes.c_void_p), ("ready", ctypes.c_void_p), ("n_copy", ctypes.c_int)])
 
 
 class _TpCommArgs(ctypes.Structure):
@@ -412,6 +413,12 @@ class TpWorkspace:
         self.ag_calls = self.rs_calls = 0
         self.spin_limit = spin_limit
         self.spin_cycles = 4_000_000_000                      # ~2 s of SM clock
+        # all-gather -> GEMM: per-slot pointer tables of the published shards, scratch for the gathered matrix, row-block flags
+        self.peer_x_slot = [torch.tensor([p + 2 * s * self.max_elems for p in self.x_ptrs], dtype=torch.int64, device=device)
+                            for s in range(self.NSLOT)]
+        self.gathered = torch.empty(self.W * self.max_elems, dtype=torch.bfloat16, device=device)
+        self.ready = torch.zeros(self.W * (self.max_elems // 1024 + 1), dtype=torch.int32, device=device)
+        self.n_copy = int(os.environ.get("LMOE_TP_COPY_CTAS", "12"))
         torch.cuda.synchronize()
         dist.barrier(group=group.pg)
 
@@ -456,7 +463,10 @@ class TpWorkspace:
         out = torch.empty(m_loc * self.W, n, dtype=torch.bfloat16, device=self.device)
         p = self._params(m_loc, t_loc, n, k)
         p.C, p.ldc, p.epoch = out.data_ptr(), n, epoch
-        ptrs = (ctypes.c_void_p * 8)(*[self.x_ptrs[i % self.W] + 2 * off for i in range(8)])
+        slot = off // self.max_elems
+        p.peer_x, p.gathered, p.ready = self.peer_x_slot[slot].data_ptr(), self.gathered.data_ptr(), self.ready.data_ptr()
+        p.n_copy = self.n_copy
+        ptrs = (ctypes.c_void_p * 8)(self.x_ptrs[self.rank] + 2 * off, self.gathered.data_ptr(), 0, 0, 0, 0, 0, 0)
         K._check(K.lib().lmoe_gemm_tp(ctypes.c_int(0), ptrs, K._p(w), ctypes.c_int(w.shape[0]), ctypes.c_int(w.shape[1]),
                                       ctypes.c_int(int(b_mn)), ctypes.byref(p), ctypes.c_int(K.NUM_SMS), K._st()), "gemm_tp_ag")
         return out
