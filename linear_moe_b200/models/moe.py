@@ -22,6 +22,7 @@ Design notes
 from __future__ import annotations
 
 import math
+import os
 from typing import List, Optional, Tuple
 
 import torch
@@ -276,14 +277,21 @@ class MoELayer(nn.Module):
     def _fused_workspace(self, h: torch.Tensor):
         """The peer-memory exchange applies to bf16 CUDA tokens on an expert-parallel group without expert TP."""
         mesh = self.mesh
-        if not (h.is_cuda and h.dtype == torch.bfloat16) or mesh["ep"].is_trivial or not mesh["tp"].is_trivial:
-            return None
-        from ..parallel import fused_comm
-        ws = fused_comm.moe_workspace(mesh["ep"])
-        if ws is None or ws.h != h.shape[-1] or ws.E != self.E or self.k > 8:
+        if not (h.is_cuda and h.dtype == torch.bfloat16) or not mesh["tp"].is_trivial or self.k > 8:
             return None
         from ..ops import gemm
-        return ws if gemm.supports_grouped(h, self.experts.weight1, self.experts.weight2) else None
+        from ..parallel import fused_comm
+        if not gemm.supports_grouped(h, self.experts.weight1, self.experts.weight2) or h.shape[-1] % 8:
+            return None
+        if mesh["ep"].is_trivial:
+            if os.environ.get("LMOE_FUSED_MOE", "1") == "0":
+                return None
+            rows = h.shape[0] * self.k + gemm.ROW_ALIGN * self.E
+            return fused_comm.local_moe_workspace(self.E, h.shape[-1], rows, h.device)
+        ws = fused_comm.moe_workspace(mesh["ep"])
+        if ws is None or ws.h != h.shape[-1] or ws.E != self.E:
+            return None
+        return ws
 
     def _experts_with_ep(self, permuted: torch.Tensor, counts: torch.Tensor) -> torch.Tensor:
         """Expert computation on expert-sorted tokens, exchanging them over the EP group."""

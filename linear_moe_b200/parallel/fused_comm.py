@@ -245,6 +245,20 @@ def moe_workspace(group) -> Optional["MoeWorkspace"]:
     return _MOE.get(group.name)
 
 
+_MOE_LOCAL: Dict[tuple, "MoeWorkspace"] = {}
+
+
+def local_moe_workspace(num_experts: int, hidden: int, rows: int, device) -> "MoeWorkspace":
+    """One-rank workspace (ordinary tensors) for a MoE layer without expert parallelism: the same push / pull kernels
+    replace the index_select / index_add_ permutation, which is several times slower in both directions."""
+    key = (str(device), num_experts, hidden)
+    ws = _MOE_LOCAL.get(key)
+    if ws is None or ws.cap < rows:
+        ws = MoeWorkspace(None, num_experts, hidden, rows, device)
+        _MOE_LOCAL[key] = ws
+    return ws
+
+
 class _MoeArgs(ctypes.Structure):
     _fields_ = ([(n, ctypes.c_void_p) for n in ("peer_cnt", "peer_flags", "peer_x", "peer_y", "status", "done_ctr")] +
                 [(n, ctypes.c_int) for n in ("rank", "world", "E", "El", "cap", "h", "epoch")] +
