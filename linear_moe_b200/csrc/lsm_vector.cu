@@ -417,3 +417,55 @@ LMOE_API int lmoe_gla_combine(int rev, float* states, const float* gdecay, const
     else gla_combine_kernel<0><<<grid, 256, 0, st>>>(states, gdecay, seed, final_out, G, D);
     return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// Gradient of the vector log-gates: dg[b,t,h,d] = sum_{i >= t} (q . dq - k . dk)[b,i,h,d]  (reverse cumulative sum
+// over time per channel).  Two launches over segments of 256 tokens: per-segment channel sums, then every segment
+// walks its tokens backwards starting from the sum of the later segments.  20 bytes of traffic per element instead of
+// the ~70 of the elementwise + transpose + cumsum formulation.
+// ---------------------------------------------------------------------------------------------------------------
+namespace lmoe {
+constexpr int DG_SEG = 256;
+struct DgArgs {
+    const bf16 *q, *k, *dq, *dk;
+    int64_t qs_b, qs_t, qs_h, ks_b, ks_t, ks_h, dqs_b, dqs_t, dqs_h, dks_b, dks_t, dks_h;
+    float* dg;            // [B,T,H,D] contiguous
+    float* segsum;        // [B*H, nseg, D]
+    int B, T, H, D, nseg;
+};
+__device__ __forceinline__ float dg_term(const DgArgs& a, int b, int t, int h, int d) {
+    const float q = __bfloat162float(a.q[b * a.qs_b + (int64_t)t * a.qs_t + h * a.qs_h + d]);
+    const float k = __bfloat162float(a.k[b * a.ks_b + (int64_t)t * a.ks_t + h * a.ks_h + d]);
+    const float dq = __bfloat162float(a.dq[b * a.dqs_b + (int64_t)t * a.dqs_t + h * a.dqs_h + d]);
+    const float dk = __bfloat162float(a.dk[b * a.dks_b + (int64_t)t * a.dks_t + h * a.dks_h + d]);
+    return q * dq - k * dk;
+}
+// grid (nseg, B*H), D threads
+__global__ void gla_dg_segsum_kernel(DgArgs a) {
+    const int seg = blockIdx.x, bh = blockIdx.y, b = bh / a.H, h = bh % a.H, d = threadIdx.x;
+    const int t0 = seg * DG_SEG, t1 = min(a.T, t0 + DG_SEG);
+    float s = 0.f;
+    for (int t = t0; t < t1; ++t) s += dg_term(a, b, t, h, d);
+    a.segsum[((int64_t)bh * a.nseg + seg) * a.D + d] = s;
+}
+__global__ void gla_dg_scan_kernel(DgArgs a) {
+    const int seg = blockIdx.x, bh = blockIdx.y, b = bh / a.H, h = bh % a.H, d = threadIdx.x;
+    float run = 0.f;
+    for (int s2 = a.nseg - 1; s2 > seg; --s2) run += a.segsum[((int64_t)bh * a.nseg + s2) * a.D + d];
+    const int t0 = seg * DG_SEG, t1 = min(a.T, t0 + DG_SEG);
+    for (int t = t1 - 1; t >= t0; --t) {
+        run += dg_term(a, b, t, h, d);
+        a.dg[(((int64_t)b * a.T + t) * a.H + h) * a.D + d] = run;
+    }
+}
+}  // namespace lmoe
+
+LMOE_API int lmoe_gla_dg(const lmoe::DgArgs* ap, cudaStream_t st) {
+    lmoe::DgArgs a = *ap;
+    if (a.D > 1024 || a.T <= 0) return -1;
+    a.nseg = (a.T + lmoe::DG_SEG - 1) / lmoe::DG_SEG;
+    dim3 grid(a.nseg, a.B * a.H);
+    lmoe::gla_dg_segsum_kernel<<<grid, a.D, 0, st>>>(a);
+    lmoe::gla_dg_scan_kernel<<<grid, a.D, 0, st>>>(a);
+    return (int)cudaGetLastError();
+}

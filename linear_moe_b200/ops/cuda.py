@@ -823,12 +823,34 @@ class _LsmVector(torch.autograd.Function):
         _gla_launch(4, D, a2)
         # d gk_t = sum_{i>=t} q_i . dq_i - sum_{j>=t} k_j . dk_j per channel (+ <S_T, dS_T> rows with a final-state gradient)
         # (the scan runs along the innermost dimension of a [B,H,D,T] copy: a scan over an outer dimension is ~10x slower)
-        s = (q.float() * dq.float() - k.float() * dk.float()).permute(0, 2, 3, 1).contiguous()
-        c = s.cumsum(-1)
-        dg = (c[..., -1:] - c + s).permute(0, 3, 1, 2)
+        dg = _gla_dg(q, k, dq, dk)
         if dfinal is not None:
             dg = dg + (final * dfinal.float()).sum(-1)[:, None]
         return dq, dk, dv, dg.to(ctx.g_dtype), None, dinit
+
+
+class _DgArgs(ctypes.Structure):
+    _fields_ = ([(n, ctypes.c_void_p) for n in ("q", "k", "dq", "dk")] +
+                [(n, ctypes.c_int64) for n in ("qs_b", "qs_t", "qs_h", "ks_b", "ks_t", "ks_h", "dqs_b", "dqs_t", "dqs_h",
+                                               "dks_b", "dks_t", "dks_h")] +
+                [("dg", ctypes.c_void_p), ("segsum", ctypes.c_void_p)] +
+                [(n, ctypes.c_int) for n in ("B", "T", "H", "D", "nseg")])
+
+
+def _gla_dg(q, k, dq, dk):
+    """Reverse cumulative sum over time of ``q*dq - k*dk`` per channel -> fp32 ``[B,T,H,D]`` (two kernel launches)."""
+    B, T, H, D = q.shape
+    dg = torch.empty(B, T, H, D, dtype=torch.float32, device=q.device)
+    nseg = (T + 255) // 256
+    seg = torch.empty(B * H, nseg, D, dtype=torch.float32, device=q.device)
+    a = _DgArgs()
+    for name, t in (("q", q), ("k", k), ("dq", dq), ("dk", dk)):
+        setattr(a, name, t.data_ptr())
+        setattr(a, name + "s_b", t.stride(0)), setattr(a, name + "s_t", t.stride(1)), setattr(a, name + "s_h", t.stride(2))
+    a.dg, a.segsum = dg.data_ptr(), seg.data_ptr()
+    a.B, a.T, a.H, a.D, a.nseg = B, T, H, D, nseg
+    _check(lib().lmoe_gla_dg(ctypes.byref(a), _st()), "gla_dg", 2)
+    return dg
 
 
 def lsm_vector(q, k, v, gk, scale, initial_state, bonus, chunk_size):

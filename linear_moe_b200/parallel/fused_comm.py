@@ -358,6 +358,13 @@ class MoeWorkspace:
         a.dest_rank, a.dest_row = route.dest_rank.data_ptr(), route.dest_row.data_ptr()
         a.offs, a.real = route.offs.data_ptr(), route.real.data_ptr()
         a.n_assign, a.k = route.T * route.k, route.k
+        if self.group is None:
+            # one rank: the receive buffer is a fresh tensor that the caller keeps, no copy out of a shared buffer
+            x = torch.empty(self.cap, self.h, dtype=torch.bfloat16, device=self.device)
+            self.peer_x.fill_(x.data_ptr())
+            self._run(2, a, "moe_push")
+            self._run(3, a, "moe_zero_pads")
+            return x
         self._run(2, a, "moe_push")
         self._run(3, a, "moe_zero_pads")
         return self.x.clone()
@@ -366,7 +373,11 @@ class MoeWorkspace:
         """Publish this rank's expert results ``[cap, h]`` and gather, weight and sum every token's ``k`` rows from their
         owners.  Returns ``(out [T, h], rows [T*k, h] or None)``."""
         self.ep_pull += 1
-        self.y.copy_(y_local)
+        if self.group is None:
+            y_local = y_local.contiguous()
+            self.peer_y.fill_(y_local.data_ptr())                # one rank: read the results where they are
+        else:
+            self.y.copy_(y_local)
         a = self._args()
         a.epoch = self.ep_pull
         out = torch.empty(route.T, self.h, dtype=torch.bfloat16, device=self.device)
