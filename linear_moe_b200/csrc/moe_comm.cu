@@ -290,6 +290,7 @@ LMOE_API int lmoe_moe_comm(int which, const MoeArgs* ap, int num_sms, cudaStream
         if (a.k <= 2) moe_pull_kernel<2><<<grid, 256, 0, st>>>(a);
         else if (a.k <= 4) moe_pull_kernel<4><<<grid, 256, 0, st>>>(a);
         else if (a.k <= 8) moe_pull_kernel<8><<<grid, 256, 0, st>>>(a);
+        else if (a.k <= 16) moe_pull_kernel<16><<<grid, 256, 0, st>>>(a);
         else return -3;
         break;
     }

@@ -277,12 +277,18 @@ class MoELayer(nn.Module):
     def _fused_workspace(self, h: torch.Tensor):
         """The peer-memory exchange applies to bf16 CUDA tokens on an expert-parallel group without expert TP."""
         mesh = self.mesh
-        if not (h.is_cuda and h.dtype == torch.bfloat16) or not mesh["tp"].is_trivial or self.k > 8:
+        if not (h.is_cuda and h.dtype == torch.bfloat16) or self.k * mesh.tp > 16:
             return None
         from ..ops import gemm
         from ..parallel import fused_comm
         if not gemm.supports_grouped(h, self.experts.weight1, self.experts.weight2) or h.shape[-1] % 8:
             return None
+        if not mesh["tp"].is_trivial:
+            # experts are ffn-sharded over TP: every (expert, TP shard) pair is a virtual expert of the TP x EP group
+            ws = fused_comm.moe_workspace(mesh["tp_ep"])
+            if ws is None or ws.h != h.shape[-1] or ws.E != self.E * mesh.tp:
+                return None
+            return ws
         if mesh["ep"].is_trivial:
             if os.environ.get("LMOE_FUSED_MOE", "1") == "0":
                 return None
@@ -354,7 +360,18 @@ class MoELayer(nn.Module):
         ws = self._fused_workspace(h)
         if ws is not None:
             from ..ops.moe_fused import fused_moe
-            out = fused_moe(h, probs, idx, self.experts.weight1, self.experts.weight2, ws).reshape(shape)
+            tp = self.mesh.tp
+            if tp > 1:
+                # token -> all TP shards of its experts; the partial outputs of the shards are summed by the combine.
+                # Rank g = ep_rank * tp + tp_rank of the TP x EP group owns virtual experts [g * El, (g + 1) * El).
+                El = self.El
+                base = torch.div(idx, El, rounding_mode="floor") * (tp * El) + idx % El
+                idx_v = torch.stack([base + r * El for r in range(tp)], dim=-1)
+                idx_v = torch.where(idx[..., None] >= 0, idx_v, torch.full_like(idx_v, -1)).reshape(T, self.k * tp)
+                probs_v = probs.repeat_interleave(tp, dim=1)
+                out = fused_moe(h, probs_v, idx_v, self.experts.weight1, self.experts.weight2, ws).reshape(shape)
+            else:
+                out = fused_moe(h, probs, idx, self.experts.weight1, self.experts.weight2, ws).reshape(shape)
         else:
             permuted, order, counts = permute(h, idx, self.E)
             y = self._experts_with_ep(permuted, counts)

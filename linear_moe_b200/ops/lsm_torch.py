@@ -138,9 +138,10 @@ def chunk_delta_rule(q, k, v, beta, g: Optional[torch.Tensor] = None, scale: Opt
     v, _ = _pad_to_chunks(v.to(f), C)
     beta, _ = _pad_to_chunks(beta.to(f), C)
     g, _ = _pad_to_chunks(g.to(f), C)
-    qc, kc, vc = (_chunk(x, C).permute(0, 1, 3, 2, 4) for x in (q, k, v))   # [B,N,H,C,d]
-    bc = _chunk(beta, C).permute(0, 1, 3, 2)                                  # [B,N,H,C]
-    b = _chunk(g, C).cumsum(2).permute(0, 1, 3, 2)                            # [B,N,H,C]
+    # contiguous [B,N,H,C,d] copies: every later elementwise op then runs the vectorised kernels instead of strided ones
+    qc, kc, vc = (_chunk(x, C).permute(0, 1, 3, 2, 4).contiguous() for x in (q, k, v))
+    bc = _chunk(beta, C).permute(0, 1, 3, 2).contiguous()                     # [B,N,H,C]
+    b = _chunk(g, C).permute(0, 1, 3, 2).contiguous().cumsum(-1)              # [B,N,H,C], scan along the innermost dim
     N = qc.shape[1]
     diff = b[..., :, None] - b[..., None, :]
     tril = torch.ones(C, C, dtype=torch.bool, device=q.device).tril()

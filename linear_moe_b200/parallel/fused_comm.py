@@ -158,6 +158,16 @@ def init_workspaces(mesh, cfg=None, tc=None):
         mb = tc.micro_batch_size if tc is not None else 1
         seq = (tc.seq_length if tc is not None else cfg.max_position_embeddings) // max(mesh.cp, 1) // tpg.size
         _TP[tpg.name] = TpWorkspace(tpg, mb * seq * cfg.hidden_size, device)
+    tpep = mesh["tp_ep"]
+    if (not mesh["tp"].is_trivial and not tpep.is_trivial and cfg is not None and cfg.num_experts and tpep.name not in _MOE
+            and cfg.moe_topk * mesh.tp <= 16 and os.environ.get("LMOE_FUSED_MOE", "1") != "0"):
+        # tensor-parallel experts: (expert, TP shard) pairs are the virtual experts of the TP x EP group
+        mb = tc.micro_batch_size if tc is not None else 1
+        seq = (tc.seq_length if tc is not None else cfg.max_position_embeddings) // max(mesh.cp, 1) // mesh.tp
+        rows = mb * seq * cfg.moe_topk * mesh.tp
+        factor = float(os.environ.get("LMOE_MOE_RECV_FACTOR", "2.0"))
+        cap = int(rows * factor) + 256 * (cfg.num_experts // mesh.ep)
+        _MOE[tpep.name] = MoeWorkspace(tpep, cfg.num_experts * mesh.tp, cfg.hidden_size, cap, device)
     ep = mesh["ep"]
     if (not ep.is_trivial and mesh["tp"].is_trivial and cfg is not None and cfg.num_experts and ep.name not in _MOE
             and os.environ.get("LMOE_FUSED_MOE", "1") != "0"):
