@@ -43,6 +43,8 @@ struct Params {
     long long c_group_stride; // mode 2: elements between consecutive experts' outputs
     int b_group_rows;         // mode 1: rows of the B map per expert (N if B is K-major, K if MN-major)
     int* err;
+    int out_f32;              // pair kernel: C is fp32 (weight gradients straight into the fp32 accumulators)
+    int accumulate;           // with out_f32: C += result instead of C = result
 };
 
 
@@ -370,6 +372,35 @@ gemm_grouped_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
             const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
             const bool zero = t.kblocks == 0;                        // an expert without tokens: its weight gradient is zero
             uint8_t* stg = sm.stage_out[warp - 2];                   // 32 rows x 128 bytes, 16-byte chunks xor-swizzled
+            if (p.out_f32) {
+                // fp32 output (optionally accumulating): 32 columns = 128 bytes per row and pass through the staging buffer
+                float* C32 = reinterpret_cast<float*>(C);
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 32) {
+                    uint32_t v[32];
+                    tmem_ld32(taddr + c, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int g = 0; g < 8; ++g) {
+                        uint4 o = zero ? make_uint4(0, 0, 0, 0) : make_uint4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+                        *reinterpret_cast<uint4*>(stg + lane * 128 + ((g ^ (lane & 7)) << 4)) = o;
+                    }
+                    __syncwarp();
+                    const int chunk = lane & 7;
+                    const int col = c + chunk * 4;
+#pragma unroll
+                    for (int it = 0; it < 8; ++it) {
+                        const int rr = it * 4 + (lane >> 3);
+                        float4 o = *reinterpret_cast<const float4*>(stg + rr * 128 + ((chunk ^ (rr & 7)) << 4));
+                        if (r0 + rr < t.rows_valid && col + 4 <= t.cols_valid) {
+                            float4* dst = reinterpret_cast<float4*>(C32 + t.c_off + (long long)(r0 + rr) * p.ldc + col);
+                            if (p.accumulate) { const float4 old = *dst; o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w; }
+                            *dst = o;
+                        }
+                    }
+                    __syncwarp();
+                }
+            } else
 #pragma unroll 1
             for (int c = 0; c < BN; c += 64) {
 #pragma unroll
@@ -438,7 +469,8 @@ using namespace lmoe::gg;
 // pairs != 0: CTA-pair kernel (256-row tiles; in mode 1 every offset must be a multiple of 256).
 LMOE_API int lmoe_gemm_grouped(const void* A, int a_rows, int a_cols, int lda, int a_mn, const void* B, int b_rows, int b_cols,
                                int ldb, int b_mn, void* C, int ldc, int mode, int M, int N, int K, int num_groups,
-                               const int* offs, long long c_group_stride, int* err, int num_sms, int pairs, cudaStream_t st) {
+                               const int* offs, long long c_group_stride, int* err, int num_sms, int pairs, int out_f32, int accumulate,
+                               cudaStream_t st) {
     if (lda % 8 || ldb % 8 || ldc % 8 || a_cols % 8 || b_cols % 8 || N % 8) return -1;
     CUtensorMap ma, mb;
     int rc = make_map(&ma, A, (uint64_t)a_rows, (uint64_t)a_cols, (uint64_t)lda, a_mn ? 64 : BM);
@@ -448,6 +480,8 @@ LMOE_API int lmoe_gemm_grouped(const void* A, int a_rows, int a_cols, int lda, i
     Params p;
     p.mode = mode; p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.num_groups = num_groups; p.offs = offs;
     p.c_group_stride = c_group_stride; p.b_group_rows = b_mn ? K : N; p.err = err;
+    p.out_f32 = out_f32; p.accumulate = accumulate;
+    if (out_f32 && !pairs) return -3;
     if (pairs) {
         if (!a_mn && !b_mn) return launch_pair<false, false>(ma, mb, (bf16*)C, p, num_sms, st);
         if (!a_mn && b_mn) return launch_pair<false, true>(ma, mb, (bf16*)C, p, num_sms, st);

@@ -829,6 +829,20 @@ class _LsmVector(torch.autograd.Function):
         return dq, dk, dv, dg.to(ctx.g_dtype), None, dinit
 
 
+class _LsmVectorFused(torch.autograd.Function):
+    """``_LsmVector`` with q|k|v given as one fused ``[B,T,H,3D]`` tensor: one gradient tensor, no concatenation."""
+
+    @staticmethod
+    def forward(ctx, qkv, gk, scale, init):
+        D = qkv.shape[-1] // 3
+        return _LsmVector.forward(ctx, qkv[..., :D], qkv[..., D:2 * D], qkv[..., 2 * D:], gk, scale, init)
+
+    @staticmethod
+    def backward(ctx, d_o, dfinal):
+        dq, dk, dv, dg, _, dinit = _LsmVector.backward(ctx, d_o, dfinal)
+        return dq._base, dg, None, dinit
+
+
 class _DgArgs(ctypes.Structure):
     _fields_ = ([(n, ctypes.c_void_p) for n in ("q", "k", "dq", "dk")] +
                 [(n, ctypes.c_int64) for n in ("qs_b", "qs_t", "qs_h", "ks_b", "ks_t", "ks_h", "dqs_b", "dqs_t", "dqs_h",
@@ -860,6 +874,9 @@ def lsm_vector(q, k, v, gk, scale, initial_state, bonus, chunk_size):
     if not ok:
         return LT.chunk_vector_gated(q, k, v, gk, scale, initial_state, 16, bonus)
     scale = D ** -0.5 if scale is None else scale
+    base = _fused_base(q, k, v)
+    if base is not None:
+        return _LsmVectorFused.apply(base, gk, scale, initial_state)
     return _LsmVector.apply(q, k, v, gk, scale, initial_state)
 
 

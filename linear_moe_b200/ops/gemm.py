@@ -102,7 +102,7 @@ PAIRS = os.environ.get("LMOE_GEMM_PAIRS", "1") != "0"     # CTA-pair (cta_group:
 ROW_ALIGN = 256 if PAIRS else 128                          # expert segments are padded to whole pair tiles
 
 
-def _gg(A, a_mn, B, b_mn, C, mode, M, N, Kd, groups, offs, c_stride, pairs=None):
+def _gg(A, a_mn, B, b_mn, C, mode, M, N, Kd, groups, offs, c_stride, pairs=None, accumulate=False):
     from . import cuda as K
     pairs = PAIRS if pairs is None else pairs
     rc = K.lib().lmoe_gemm_grouped(
@@ -110,7 +110,7 @@ def _gg(A, a_mn, B, b_mn, C, mode, M, N, Kd, groups, offs, c_stride, pairs=None)
         K._p(B), ctypes.c_int(B.shape[0]), ctypes.c_int(B.shape[1]), ctypes.c_int(B.stride(0)), ctypes.c_int(int(b_mn)),
         K._p(C), ctypes.c_int(C.stride(-2)), ctypes.c_int(mode), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(Kd),
         ctypes.c_int(groups), K._p(offs), ctypes.c_longlong(c_stride), K._p(_err(A.device)), ctypes.c_int(K.NUM_SMS),
-        ctypes.c_int(int(pairs)), K._st())
+        ctypes.c_int(int(pairs)), ctypes.c_int(int(C.dtype == torch.float32)), ctypes.c_int(int(accumulate)), K._st())
     K._check(rc, "gemm_grouped")
     return C
 
@@ -153,6 +153,13 @@ class GroupedLinear(torch.autograd.Function):
         dy = dy.contiguous()
         dx = torch.empty_like(x)
         _gg(dy, False, w.view(E * Kd, N), False, dx, 1, 0, Kd, N, E, offs, 0)              # dy @ w[e]^T
+        mg = getattr(w, "main_grad", None)
+        if PAIRS and mg is not None and mg.dtype == torch.float32 and mg.is_contiguous() and mg.shape == w.shape:
+            # weight gradient straight into the fp32 accumulator (first write after zero_grad overwrites, later ones add)
+            fresh = getattr(w, "_main_grad_fresh", False)
+            _gg(x, True, dy, True, mg, 2, Kd, N, 0, E, offs, Kd * N, accumulate=not fresh)
+            w._main_grad_fresh = False
+            return dx, None, None
         dw = torch.empty_like(w)
         _gg(x, True, dy, True, dw, 2, Kd, N, 0, E, offs, Kd * N)                           # x_e^T @ dy_e
         return dx, dw, None

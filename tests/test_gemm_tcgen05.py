@@ -141,3 +141,29 @@ def test_gemm_2cta_pairs(M, N, K):
     ref = a.float() @ b.float().t()
     err = (c.float() - ref).abs().max().item()
     assert err <= 2e-2 * ref.abs().max().item() + 1e-2, (err, ref.abs().max().item())
+
+
+def test_grouped_wgrad_into_fp32_accumulator():
+    """The grouped weight-gradient GEMM writes (first call) and then accumulates (second call) into ``main_grad``."""
+    from linear_moe_b200.ops import gemm
+    if not gemm.PAIRS:
+        pytest.skip("needs the CTA-pair grouped kernels")
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(3)
+    E, h, f = 4, 256, 320
+    counts = torch.tensor([256, 0, 512, 256], device=dev)
+    offs = gemm.padded_offsets(counts)
+    rows = int(offs[-1])
+    x = (0.5 * torch.randn(rows, h, device=dev)).to(torch.bfloat16).requires_grad_(True)
+    w = (0.05 * torch.randn(E, h, f, device=dev)).to(torch.bfloat16).requires_grad_(True)
+    gy = torch.randn(rows, f, device=dev).to(torch.bfloat16)
+    ref = torch.autograd.grad(gemm.GroupedLinear.apply(x, w, offs), w, gy)[0].float()
+    w.main_grad = torch.full((E, h, f), 7.0, dtype=torch.float32, device=dev)     # stale content: the first write overwrites
+    w._main_grad_fresh = True
+    for n in (1, 2):
+        gemm.GroupedLinear.apply(x, w, offs).backward(gy)
+        torch.cuda.synchronize()
+        gemm.check_error()
+        assert w.grad is None
+        err = (w.main_grad - n * ref).abs().max().item()
+        assert err <= 2e-2 * ref.abs().max().item() * n + 1e-3, (n, err)
