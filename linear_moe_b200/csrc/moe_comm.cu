@@ -3,12 +3,14 @@
 // Replaces the reference's permute -> all_to_all -> permute ... unpermute -> all_to_all -> unpermute chain
 // (moe/token_dispatcher.py:412-548, whose split sizes are read back by the host with .tolist()) with
 //
-//   moe_exchange_kernel   every rank stores its per-expert token counts into every peer's count matrix, releases a
+//   moe_exchange_kernel   sums the chunk histograms; every rank stores its per-expert token counts into every peer's count matrix, releases a
 //                         flag, waits (bounded) for the peers' rows and derives, on the device: the padded row
 //                         offsets of its local experts in its receive buffer (the grouped GEMM's problem sizes) and,
 //                         for every global expert, the row in the owner's receive buffer where THIS rank's tokens
 //                         for that expert start.
-//   moe_map_kernel        (sorted assignment -> destination rank, destination row) for every (token, slot) pair.
+//   moe_count_kernel      per-chunk histograms of the (token, slot) -> expert assignments (chunks of 4096 assignments).
+//   moe_assign_kernel     destination (rank, row) of every (token, slot) pair: a counting sort that is stable in the
+//                         assignment index (deterministic row order), without any library sort.
 //   moe_push_kernel       dispatch: every (token, slot) row is written straight into the owner rank's receive buffer
 //                         with 16-byte peer stores (optionally scaled, which is the backward of the combine); the
 //                         last CTA to finish releases a flag on every peer and waits for theirs.
@@ -48,14 +50,14 @@ struct MoeArgs {
     int epoch;
     long long spin_limit;
     // exchange
-    const int* counts;          // [E] tokens of this rank per global expert
     int* offs;                  // [El+1] out: padded row offsets of the local experts
     int* real;                  // [El]   out: tokens received per local expert
     int* send_base;             // [E]    out: first row of this rank's tokens in the owner's buffer, -1 = do not send
-    int* starts;                // [E]    out: exclusive prefix of counts (start of each expert in the sorted order)
-    // map
-    const long long* order;     // [n_sorted] sorted position -> flat (token, slot) index
-    const long long* sorted_e;  // [n_sorted] expert id of the sorted position (E = dropped)
+    // count / assign
+    const long long* idx;       // [n_assign] expert id of every (token, slot) pair, -1 = dropped
+    int* blockhist;             // [nchunks][E] assignments per chunk and expert
+    int* blockbase;             // [nchunks][E] exclusive prefix of blockhist over the chunks
+    int nchunks;
     int* dest_rank;             // [n_assign]
     int* dest_row;              // [n_assign]
     // push / pull
@@ -91,7 +93,11 @@ __global__ void moe_exchange_kernel(MoeArgs a) {
     __shared__ int fail;
     if (threadIdx.x == 0) fail = 0;
     for (int e = threadIdx.x; e < a.E; e += blockDim.x) {
-        const int c = a.counts[e];
+        int c = 0;
+        for (int ch = 0; ch < a.nchunks; ++ch) {                     // exclusive prefix over the chunks, total = this rank's count
+            a.blockbase[ch * a.E + e] = c;
+            c += a.blockhist[ch * a.E + e];
+        }
         for (int j = 0; j < a.world; ++j) a.peer_cnt[j][a.rank * a.E + e] = c;
     }
     __threadfence_system();
@@ -130,25 +136,68 @@ __global__ void moe_exchange_kernel(MoeArgs a) {
         }
         if (d == a.rank) a.offs[a.El] = over[d] ? 0 : run;
     }
-    if (threadIdx.x == 0) {
-        int run = 0;
-        for (int e = 0; e < a.E; ++e) { a.starts[e] = run; run += a.counts[e]; }
-    }
 }
 
-__global__ void moe_map_kernel(MoeArgs a) {
-    const int p = blockIdx.x * blockDim.x + threadIdx.x;
-    if (p >= a.n_assign) return;
-    const long long e = a.sorted_e[p];
-    const long long f = a.order[p];
-    int dr = -1, row = -1;
-    if (e >= 0 && e < a.E) {
-        const int sb = a.send_base[e];
-        if (sb >= 0) { dr = (int)e / a.El; row = sb + (p - a.starts[e]); }
-        if (row >= a.cap) { dr = -1; row = -1; }
+constexpr int ASSIGN_CHUNK = 4096, ASSIGN_PER_THREAD = 16;          // 256 threads x 16 consecutive assignments
+
+// grid = nchunks: histogram of one chunk of assignments
+__global__ void moe_count_kernel(MoeArgs a) {
+    extern __shared__ int hist[];
+    for (int e = threadIdx.x; e < a.E; e += blockDim.x) hist[e] = 0;
+    __syncthreads();
+    const long long base = (long long)blockIdx.x * ASSIGN_CHUNK;
+    for (int i = threadIdx.x; i < ASSIGN_CHUNK; i += blockDim.x) {
+        const long long p = base + i;
+        if (p < a.n_assign) {
+            const long long e = a.idx[p];
+            if (e >= 0 && e < a.E) atomicAdd(&hist[e], 1);
+        }
     }
-    a.dest_rank[f] = dr;
-    a.dest_row[f] = row;
+    __syncthreads();
+    for (int e = threadIdx.x; e < a.E; e += blockDim.x) a.blockhist[blockIdx.x * a.E + e] = hist[e];
+}
+
+// grid = nchunks, 256 threads, dynamic smem 256 * E * 2 bytes: thread t owns assignments [16 t, 16 t + 16) of the chunk
+__global__ void moe_assign_kernel(MoeArgs a) {
+    extern __shared__ unsigned short cnt[];                          // [256][E] -> exclusive prefix over the threads
+    const int t = threadIdx.x;
+    unsigned short* mine = cnt + t * a.E;
+    for (int e = 0; e < a.E; ++e) mine[e] = 0;
+    const long long base = (long long)blockIdx.x * ASSIGN_CHUNK + (long long)t * ASSIGN_PER_THREAD;
+    long long ev[ASSIGN_PER_THREAD];
+#pragma unroll
+    for (int i = 0; i < ASSIGN_PER_THREAD; ++i) {
+        const long long p = base + i;
+        long long e = p < a.n_assign ? a.idx[p] : -1;
+        if (e >= a.E) e = -1;
+        ev[i] = e;
+        if (e >= 0) mine[e]++;
+    }
+    __syncthreads();
+    for (int e = t; e < a.E; e += blockDim.x) {
+        unsigned int run = 0;
+        for (int r = 0; r < (int)blockDim.x; ++r) {
+            const unsigned short c = cnt[r * a.E + e];
+            cnt[r * a.E + e] = (unsigned short)run;
+            run += c;
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < ASSIGN_PER_THREAD; ++i) {
+        const long long p = base + i;
+        if (p >= a.n_assign) break;
+        const long long e = ev[i];
+        int dr = -1, row = -1;
+        if (e >= 0) {
+            const int pos = mine[e]++;
+            const int sb = a.send_base[e];
+            if (sb >= 0) { dr = (int)e / a.El; row = sb + a.blockbase[blockIdx.x * a.E + e] + pos; }
+            if (row >= a.cap) { dr = -1; row = -1; }
+        }
+        a.dest_rank[p] = dr;
+        a.dest_row[p] = row;
+    }
 }
 
 __global__ void moe_push_kernel(MoeArgs a) {
@@ -262,7 +311,7 @@ __global__ void moe_pull_kernel(MoeArgs a) {
 
 using namespace lmoe;
 
-// which: 0 exchange, 1 map, 2 push, 3 zero pads, 4 signal, 5 pull
+// which: 0 exchange, 1 assign, 2 push, 3 zero pads, 4 signal, 5 pull, 6 count
 LMOE_API int lmoe_moe_comm(int which, const MoeArgs* ap, int num_sms, cudaStream_t st) {
     const MoeArgs a = *ap;
     if (a.h % 8 != 0 || a.world > 32) return -2;
@@ -272,7 +321,15 @@ LMOE_API int lmoe_moe_comm(int which, const MoeArgs* ap, int num_sms, cudaStream
         moe_exchange_kernel<<<1, 256, (2 * a.E + a.world) * sizeof(int), st>>>(a);
         break;
     case 1:
-        if (a.n_assign > 0) moe_map_kernel<<<(a.n_assign + 255) / 256, 256, 0, st>>>(a);
+        if (a.nchunks > 0) {
+            const size_t sm = (size_t)256 * a.E * sizeof(unsigned short);
+            if (sm > 200 * 1024) return -4;
+            cudaFuncSetAttribute(moe_assign_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+            moe_assign_kernel<<<a.nchunks, 256, sm, st>>>(a);
+        }
+        break;
+    case 6:
+        if (a.nchunks > 0) moe_count_kernel<<<a.nchunks, 256, a.E * sizeof(int), st>>>(a);
         break;
     case 2: {
         int grid = (int)std::min<long long>(std::max<long long>((a.n_assign + 7) / 8, 1), (long long)num_sms * 8);

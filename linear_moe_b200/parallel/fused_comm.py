@@ -273,8 +273,9 @@ class _MoeArgs(ctypes.Structure):
     _fields_ = ([(n, ctypes.c_void_p) for n in ("peer_cnt", "peer_flags", "peer_x", "peer_y", "status", "done_ctr")] +
                 [(n, ctypes.c_int) for n in ("rank", "world", "E", "El", "cap", "h", "epoch")] +
                 [("spin_limit", ctypes.c_longlong)] +
-                [(n, ctypes.c_void_p) for n in ("counts", "offs", "real", "send_base", "starts", "order", "sorted_e",
-                                                "dest_rank", "dest_row", "src", "w", "out", "rows")] +
+                [(n, ctypes.c_void_p) for n in ("offs", "real", "send_base", "idx", "blockhist", "blockbase")] +
+                [("nchunks", ctypes.c_int)] +
+                [(n, ctypes.c_void_p) for n in ("dest_rank", "dest_row", "src", "w", "out", "rows")] +
                 [("n_assign", ctypes.c_int), ("k", ctypes.c_int), ("pad", ctypes.c_int)])
 
 
@@ -334,26 +335,29 @@ class MoeWorkspace:
         (token, slot) pair, padded offsets and real sizes of the local expert segments.  No host synchronisation."""
         T, k = idx.shape
         dev = idx.device
-        flat = idx.reshape(-1)
-        key = torch.where(flat >= 0, flat, torch.full_like(flat, self.E))
-        sorted_e, order = torch.sort(key, stable=True)
-        counts = torch.bincount(key, minlength=self.E + 1)[: self.E].to(torch.int32)
-        offs = torch.empty(self.El + 1, dtype=torch.int32, device=dev)
-        real = torch.empty(self.El, dtype=torch.int32, device=dev)
-        send_base = torch.empty(self.E, dtype=torch.int32, device=dev)
-        starts = torch.empty(self.E, dtype=torch.int32, device=dev)
-        dest_rank = torch.empty(T * k, dtype=torch.int32, device=dev)
-        dest_row = torch.empty(T * k, dtype=torch.int32, device=dev)
+        flat = idx.reshape(-1).contiguous()
+        if flat.dtype != torch.int64:
+            flat = flat.to(torch.int64)
+        nch = (T * k + 4095) // 4096
+        scratch = torch.empty(2 * nch * self.E + self.El + 1 + self.El + self.E + 2 * T * k, dtype=torch.int32, device=dev)
+        o = 0
+        blockhist = scratch[o:o + nch * self.E]; o += nch * self.E
+        blockbase = scratch[o:o + nch * self.E]; o += nch * self.E
+        offs = scratch[o:o + self.El + 1]; o += self.El + 1
+        real = scratch[o:o + self.El]; o += self.El
+        send_base = scratch[o:o + self.E]; o += self.E
+        dest_rank = scratch[o:o + T * k]; o += T * k
+        dest_row = scratch[o:o + T * k]
         self.ep_exchange += 1
         a = self._args()
         a.epoch = self.ep_exchange
-        a.counts, a.offs, a.real, a.send_base, a.starts = (counts.data_ptr(), offs.data_ptr(), real.data_ptr(),
-                                                           send_base.data_ptr(), starts.data_ptr())
-        a.order, a.sorted_e = order.data_ptr(), sorted_e.data_ptr()
+        a.offs, a.real, a.send_base = offs.data_ptr(), real.data_ptr(), send_base.data_ptr()
+        a.idx, a.blockhist, a.blockbase, a.nchunks = flat.data_ptr(), blockhist.data_ptr(), blockbase.data_ptr(), nch
         a.dest_rank, a.dest_row = dest_rank.data_ptr(), dest_row.data_ptr()
         a.n_assign, a.k = T * k, k
+        self._run(6, a, "moe_count")
         self._run(0, a, "moe_exchange")
-        self._run(1, a, "moe_map")
+        self._run(1, a, "moe_assign")
         return MoeRoute(T, k, dest_rank, dest_row, offs, real)
 
     def push(self, src: torch.Tensor, route: "MoeRoute", weights: Optional[torch.Tensor]) -> torch.Tensor:
