@@ -139,10 +139,9 @@ def linear(x, weight, bias=None):
 
 
 def linear_swiglu(x, weight):
-    from . import gemm
-    if gemm.available() and gemm.supports_swiglu(x, weight):
-        return gemm.LinearSwiGLU.apply(x, weight)
-    return swiglu(F.linear(x, weight))
+    """fc1 + SwiGLU.  The GEMM goes through :func:`linear` (fp32 weight-gradient accumulation, fp8 when enabled); the
+    fused-epilogue tcgen05 kernel (``gemm.gemm_nt(..., swiglu=True)``) needs the tiled fc1 layout and is opt-in."""
+    return swiglu(linear(x, weight))
 
 
 def fused_tp_available(group) -> bool:
@@ -157,10 +156,6 @@ def fused_lasp_available(group, q, k, v, g) -> bool:
     D = q.shape[-1]
     return (q.dtype == torch.bfloat16 and D == v.shape[-1] and D in (64, 128)
             and (g is None or g.dim() == 1))
-
-
-def fused_moe_available(mesh) -> bool:
-    return False
 
 
 def lasp2_scalar(q, k, v, g, scale, group, chunk_size):

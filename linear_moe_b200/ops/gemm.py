@@ -87,14 +87,6 @@ def tile_swiglu_weight(w: torch.Tensor) -> torch.Tensor:
     return torch.cat([g, u], dim=1).reshape(2 * f, -1).contiguous()
 
 
-def supports_swiglu(x, w) -> bool:
-    return False          # the model keeps fc1 in [gate; up] order; the tiled layout is opt-in
-
-
-def supports_grouped(x, w1, w2) -> bool:
-    return False
-
-
 # ---------------------------------------------------------------------------------------------
 # grouped / layout-general GEMMs (csrc/gemm_grouped.cu)
 # ---------------------------------------------------------------------------------------------
