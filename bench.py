@@ -48,7 +48,7 @@ def parse():
 def reference_arm():
     print(json.dumps({
         "impl": "reference",
-        "unavailable": "the reference is not installable offline: /root/reference has no setup.py/pyproject.toml and its "
+        "unavailable": "the reference is not installable offline: its source tree has no setup.py/pyproject.toml and its "
                        "engines (megatron-core, transformer_engine, flash-linear-attention submodules, mamba_ssm, "
                        "grouped_gemm) are empty git links or absent from the image"}))
     return 0

@@ -60,7 +60,7 @@ def report(name, ms, flops=None, link_bytes=None):
 
 
 def bench_tp(mesh, iters):
-    """Sequence-parallel column layer (all-gather -> GEMM) and row layer (GEMM -> reduce-scatter), BASELINE config #3
+    """Sequence-parallel column layer (all-gather -> GEMM) and row layer (GEMM -> reduce-scatter), the A1B-7B hybrid preset
     sizes: hidden 2048, per-rank tokens 4096 * 2 / W, ffn shard 2 * 1408 * 16 / W."""
     from .. import ops
     from ..dist import collectives as C
@@ -92,7 +92,7 @@ def bench_tp(mesh, iters):
 
 
 def bench_moe(mesh, iters):
-    """Expert-parallel MoE layer core of BASELINE config #2: hidden 1024, expert ffn 896, 64 experts, top-8."""
+    """Expert-parallel MoE layer core of the A0.3B-2B GLA preset: hidden 1024, expert ffn 896, 64 experts, top-8."""
     from ..config.model_config import ModelConfig
     from ..models.moe import MoELayer
     from ..parallel import fused_comm
@@ -128,7 +128,7 @@ def bench_moe(mesh, iters):
 
 
 def bench_lasp(mesh, iters):
-    """LASP-2 lightning attention of BASELINE config #4: 16 heads x 128, 16384 tokens per rank."""
+    """LASP-2 lightning attention of the LASP-2 Linear-Llama3-1B preset: 16 heads x 128, 16384 tokens per rank."""
     from ..parallel import fused_comm
     from ..parallel.lasp2 import lasp2
     cp = mesh["cp"]

@@ -216,7 +216,7 @@ def bench_lsm_families(size):
 
 
 def bench_moe(size):
-    """Expert MLPs of BASELINE config #2 on one rank: 8 local experts, hidden 1024, ffn 896, top-8."""
+    """Expert MLPs of the A0.3B-2B GLA preset on one rank: 8 local experts, hidden 1024, ffn 896, top-8."""
     from ..ops import gemm
     from ..ops.moe_fused import fused_moe
     from ..parallel import fused_comm
