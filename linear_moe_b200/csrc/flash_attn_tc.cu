@@ -52,22 +52,6 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, u
     asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
                  :: "r"(s32(dst)), "l"(map), "r"(s32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
 }
-// Bounded wait that sleeps between polls: for the producer and MMA threads, whose spinning would otherwise take issue
-// slots from the softmax warps on the same scheduler.
-__device__ __forceinline__ bool mbar_wait_sleep(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
-    const long long t0 = clock64();
-    for (int i = 0;; ++i) {
-        if (mbar_test(bar, parity)) return true;
-        __nanosleep(40);
-        if ((i & 63) == 63) {
-            if (*abort_flag) return false;
-            if (clock64() - t0 > WAIT_CYCLES) break;
-        }
-    }
-    *abort_flag = 1;
-    atomicCAS(err, 0, code);
-    return false;
-}
 template <bool B_MN, int N>
 __host__ __device__ constexpr uint32_t idesc_bf16() {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
@@ -106,8 +90,34 @@ __device__ __forceinline__ void fold_o(float (&o)[OW], uint32_t taddr, float cor
     uint32_t v[OW];
     tmem_ld<OW>(taddr, v);
     tmem_ld_wait();
+    const float2 c2 = make_float2(corr, corr);
 #pragma unroll
-    for (int i = 0; i < OW; ++i) o[i] = fmaf(o[i], corr, __uint_as_float(v[i]));
+    for (int i = 0; i < OW; i += 2) {                            // packed fp32 FMAs: two columns per instruction
+        const float2 r = __ffma2_rn(make_float2(o[i], o[i + 1]), c2, make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])));
+        o[i] = r.x;
+        o[i + 1] = r.y;
+    }
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+// Bounded wait that lets the hardware suspend the warp (try_wait with a time hint) instead of spinning on test_wait:
+// the 16 softmax warps share 4 schedulers, a spinning warp takes issue slots from the others.
+__device__ __forceinline__ bool mbar_wait_suspend(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
+    const long long t0 = clock64();
+    for (;;) {
+        uint32_t ok;
+        asm volatile("{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\nselp.u32 %0, 1, 0, p;\n}"
+                     : "=r"(ok) : "r"(s32(bar)), "r"(parity), "r"(20000u) : "memory");
+        if (ok) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > WAIT_CYCLES) break;
+    }
+    *abort_flag = 1;
+    atomicCAS(err, 0, code);
+    return false;
 }
 
 template <int D>
@@ -163,11 +173,11 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 const int s = j & 1;
                 const uint32_t ph = (j >> 1) & 1;
                 const int key0 = (nb_lo + j) * BN;
-                if (!mbar_wait_sleep(&sm.k_empty[s], ph ^ 1, abort_flag, err, 0x1100 | s)) break;
+                if (!mbar_wait_suspend(&sm.k_empty[s], ph ^ 1, abort_flag, err, 0x1100 | s)) break;
                 mbar_expect_tx(&sm.k_full[s], BN * D * 2);
 #pragma unroll
                 for (int kb = 0; kb < DK; ++kb) tma_load_4d(sm.k[s] + kb * BN * 128, &tmK, &sm.k_full[s], kb * 64, hk, key0, b);
-                if (!mbar_wait_sleep(&sm.v_empty[s], ph ^ 1, abort_flag, err, 0x1200 | s)) break;
+                if (!mbar_wait_suspend(&sm.v_empty[s], ph ^ 1, abort_flag, err, 0x1200 | s)) break;
                 mbar_expect_tx(&sm.v_full[s], BN * D * 2);
                 // MN-major operand: per 64 keys, D/64 boxes of {64 d, 64 keys} (8 KiB each)
 #pragma unroll
@@ -181,10 +191,10 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (lane == 0 && n_it > 0) {
             constexpr uint32_t idesc_s = idesc_bf16<false, BN>();
             constexpr uint32_t idesc_o = idesc_bf16<true, D>();
-            bool ok = mbar_wait_sleep(&sm.q_full, 0, abort_flag, err, 0x2000);
+            bool ok = mbar_wait_suspend(&sm.q_full, 0, abort_flag, err, 0x2000);
             auto issue_s = [&](int j) -> bool {
                 const int s = j & 1;
-                if (!mbar_wait_sleep(&sm.k_full[s], (j >> 1) & 1, abort_flag, err, 0x2100 | s)) return false;
+                if (!mbar_wait_suspend(&sm.k_full[s], (j >> 1) & 1, abort_flag, err, 0x2100 | s)) return false;
                 tc_fence_after();
                 const uint32_t qa = s32(sm.q), ka = s32(sm.k[s]);
 #pragma unroll
@@ -200,8 +210,8 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             for (int j = 0; ok && j < n_it; ++j) {
                 if (j + 1 < n_it) { ok = issue_s(j + 1); if (!ok) break; }
                 const int s = j & 1;
-                if (!mbar_wait_sleep(&sm.v_full[s], (j >> 1) & 1, abort_flag, err, 0x2200 | s)) break;
-                if (!mbar_wait_sleep(&sm.p_ready, j & 1, abort_flag, err, 0x2300)) break;
+                if (!mbar_wait_suspend(&sm.v_full[s], (j >> 1) & 1, abort_flag, err, 0x2200 | s)) break;
+                if (!mbar_wait_suspend(&sm.p_ready, j & 1, abort_flag, err, 0x2300)) break;
                 tc_fence_after();
                 const uint32_t pa = s32(sm.p), va = s32(sm.v[s]);
 #pragma unroll
@@ -237,7 +247,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const int s = j & 1;
             const int tile_key0 = (nb_lo + j) * BN;
             const int key0 = tile_key0 + part * CW;           // first key of this thread's columns
-            if (!mbar_wait(&sm.s_full[s], (j >> 1) & 1, abort_flag, err, 0x3100 | s)) { alive = false; break; }
+            if (!mbar_wait_suspend(&sm.s_full[s], (j >> 1) & 1, abort_flag, err, 0x3100 | s)) { alive = false; break; }
             tc_fence_after();
             const bool need_mask = (tile_key0 + BN - 1 > a.q_offset + q0) || (tile_key0 + BN > a.Tk) ||
                                    (a.window > 0 && tile_key0 <= a.q_offset + q0 + BM - 1 - a.window);
@@ -257,10 +267,9 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                     }
                 }
 #pragma unroll
-                for (int i = 0; i < 16; i += 4) {
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], __uint_as_float(v[i + e]));
-                }
+                for (int e = 0; e < 4; ++e)                              // 3-input max: two scores per instruction
+                    mx4[e] = max3(max3(mx4[e], __uint_as_float(v[e]), __uint_as_float(v[e + 4])), __uint_as_float(v[e + 8]),
+                                  __uint_as_float(v[e + 12]));
             }
             float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // row maximum over the SPLIT parts (buffers alternate so that a fast thread cannot overwrite a value a slow
@@ -273,7 +282,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             const float msc = (mx == -INFINITY) ? 0.f : mx * sc;
             m = mx;
             // the P buffer and the partial output of the previous tile are free once P_{j-1} V_{j-1} has completed
-            if (j > 0 && !mbar_wait(&sm.o_full[s ^ 1], ((j - 1) >> 1) & 1, abort_flag, err, 0x3200 | s)) { alive = false; break; }
+            if (j > 0 && !mbar_wait_suspend(&sm.o_full[s ^ 1], ((j - 1) >> 1) & 1, abort_flag, err, 0x3200 | s)) { alive = false; break; }
             // pass 2: p = exp2(s * sc - m * sc), row sum, bf16 pack, swizzled 16-byte stores
             float ps4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -291,9 +300,13 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 }
 #pragma unroll
                 for (int i = 0; i < 16; i += 4) {
-                    const float p0 = exp2f(fmaf(__uint_as_float(v[i]), sc, -msc)), p1 = exp2f(fmaf(__uint_as_float(v[i + 1]), sc, -msc));
-                    const float p2 = exp2f(fmaf(__uint_as_float(v[i + 2]), sc, -msc)), p3 = exp2f(fmaf(__uint_as_float(v[i + 3]), sc, -msc));
-                    ps4[0] += p0; ps4[1] += p1; ps4[2] += p2; ps4[3] += p3;
+                    const float2 sc2 = make_float2(sc, sc), nm2 = make_float2(-msc, -msc);
+                    const float2 x01 = __ffma2_rn(make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])), sc2, nm2);
+                    const float2 x23 = __ffma2_rn(make_float2(__uint_as_float(v[i + 2]), __uint_as_float(v[i + 3])), sc2, nm2);
+                    const float p0 = exp2f(x01.x), p1 = exp2f(x01.y), p2 = exp2f(x23.x), p3 = exp2f(x23.y);
+                    const float2 s01 = __fadd2_rn(make_float2(ps4[0], ps4[1]), make_float2(p0, p1));
+                    const float2 s23 = __fadd2_rn(make_float2(ps4[2], ps4[3]), make_float2(p2, p3));
+                    ps4[0] = s01.x; ps4[1] = s01.y; ps4[2] = s23.x; ps4[3] = s23.y;
                     v[i >> 1] = pack_bf16(p0, p1);
                     v[(i >> 1) + 1] = pack_bf16(p2, p3);
                 }
@@ -316,7 +329,7 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         }
         if (alive && n_it > 0) {
             const int s = (n_it - 1) & 1;
-            if (mbar_wait(&sm.o_full[s], ((n_it - 1) >> 1) & 1, abort_flag, err, 0x3300 | s)) {
+            if (mbar_wait_suspend(&sm.o_full[s], ((n_it - 1) >> 1) & 1, abort_flag, err, 0x3300 | s)) {
                 tc_fence_after();
                 fold_o<OW>(o, lane_addr + O_COL + s * D + part * OW, corr_prev);
             }
