@@ -95,7 +95,7 @@ class LearnablePolySketch(nn.Module):
                                        [nn.Linear(s, s, bias=False) for _ in range(n_extra)])
 
     def forward(self, x):
-        x = F.layer_norm(x, (self.head_dim,), self.gamma, self.beta)
+        x = F.layer_norm(x.float(), (self.head_dim,), self.gamma.float(), self.beta.float()).to(x.dtype)
         x = self.sketches1[0](x) * self.sketches2[0](x) * self.head_dim ** -0.5
         for i in range(1, len(self.sketches1)):
             x = self.sketches1[i](x) * self.sketches2[i](x) * self.head_dim ** -0.5
@@ -127,7 +127,7 @@ class RebasedMap(nn.Module):
 
     def forward(self, x, flatten: bool = True):
         if self.normalize:
-            x = F.layer_norm(x, (self.head_dim,), self.gamma, self.beta)
+            x = F.layer_norm(x.float(), (self.head_dim,), self.gamma.float(), self.beta.float()).to(x.dtype)
         elif self.gamma is not None and self.beta is not None:
             x = torch.addcmul(self.beta, x, self.gamma)
         elif self.gamma is not None:

@@ -19,6 +19,15 @@ CASES = {
     "mamba2_mixtral": dict(base_model="mixtral", use_la_module=True, la_module="mamba2", hybrid_override_pattern="M*",
                            mamba_head_dim=64, mamba_d_state=128, mamba_ngroups=2, num_experts=4, moe_ffn_hidden_size=128),
     "retention_basic": dict(use_la_module=True, la_module="retention", layer_type_list="LN"),
+    "deltanet": dict(use_la_module=True, la_module="deltanet", layer_type_list="LL"),
+    "gsa": dict(use_la_module=True, la_module="gsa", layer_type_list="LL"),
+    "based": dict(use_la_module=True, la_module="based", layer_type_list="LL", kv_channels=16, num_attention_heads=4),
+    "rebased": dict(use_la_module=True, la_module="rebased", layer_type_list="LL", kv_channels=16, num_attention_heads=4),
+    "hgrn2": dict(use_la_module=True, la_module="hgrn2", layer_type_list="LL"),
+    "rwkv6": dict(use_la_module=True, la_module="rwkv6", layer_type_list="LL"),
+    "rwkv7": dict(use_la_module=True, la_module="rwkv7", layer_type_list="LL", kv_channels=64, num_attention_heads=4),
+    "mom_gla": dict(use_la_module=True, la_module="mom_gla", layer_type_list="LL"),
+    "lasp2_basic": dict(use_la_module=True, la_module="lasp2", layer_type_list="LL"),
     "deepseek_mla": dict(base_model="deepseek_v2", num_experts=4, moe_topk=2, moe_ffn_hidden_size=128, kv_lora_rank=64,
                          qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32, moe_layer_freq=1),
 }
