@@ -457,7 +457,7 @@ class TpWorkspace:
                             for s in range(self.NSLOT)]
         self.gathered = torch.empty(self.W * self.max_elems, dtype=torch.bfloat16, device=device)
         self.ready = torch.zeros(self.W * (self.max_elems // 1024 + 1), dtype=torch.int32, device=device)
-        self.n_copy = int(os.environ.get("LMOE_TP_COPY_CTAS", "12"))
+        self.n_copy = int(os.environ.get("LMOE_TP_COPY_CTAS", "16"))
         torch.cuda.synchronize()
         dist.barrier(group=group.pg)
 

@@ -244,3 +244,42 @@ def test_two_gpu_training_matches_one_gpu(name, par_kw, overrides, expect):
     for (l, g), (l0, g0) in zip(multi, single):
         assert abs(l - l0) < 5e-2, (multi, single)
     assert abs(multi[0][1] - single[0][1]) < 0.1 * single[0][1], (multi, single)
+
+
+def _resume_worker(rank, world, tmp):
+    """Train 2 steps, checkpoint, train 2 more; a fresh trainer that loads the checkpoint reproduces steps 3-4."""
+    from linear_moe_b200.config.model_config import ParallelConfig, TrainConfig
+    from linear_moe_b200.config.presets import get_preset
+    from linear_moe_b200.data.datasets import SyntheticTokenDataset
+    from linear_moe_b200.dist.mesh import Mesh
+    from linear_moe_b200.train.loop import Trainer
+    dev = torch.device("cuda", rank)
+    seq, gbs = 512, 4
+    cfg = get_preset("bench-cpu-plumbing", params_dtype=torch.bfloat16, la_module="lightning_attention", kv_channels=64)
+    ds = SyntheticTokenDataset(cfg.vocab_size, seq, num_samples=64, seed=0)
+    par = ParallelConfig(context_parallel_size=2, use_distributed_optimizer=True)     # fused LASP-2 + fused ZeRO-1
+    mesh = Mesh(par)
+
+    def make():
+        tc = TrainConfig(micro_batch_size=2, global_batch_size=gbs, seq_length=seq, train_iters=4, lr=1e-3, min_lr=1e-4,
+                         lr_decay_style="cosine", lr_decay_iters=100, weight_decay=0.01, clip_grad=1.0, log_interval=1,
+                         seed=0, bf16=True)
+        return Trainer(cfg, par, tc, mesh, device=dev, dataset=ds)
+    a = make()
+    for _ in range(2):
+        a.train_step()
+    a.save(tmp)
+    cont = [float(a.train_step()["lm loss"]) for _ in range(2)]
+    b = make()
+    b.load(tmp)
+    assert b.iteration == 2
+    resumed = [float(b.train_step()["lm loss"]) for _ in range(2)]
+    return cont, resumed
+
+
+def test_checkpoint_resume_with_fused_paths(tmp_path):
+    _need_gpus(2)
+    outs = run_distributed(_resume_worker, 2, backend="nccl", tmp=str(tmp_path / "ckpt"))
+    cont, resumed = outs[0]
+    for x, y in zip(cont, resumed):
+        assert abs(x - y) < 2e-3, (cont, resumed)
