@@ -129,3 +129,36 @@ def test_heartbeat_detects_a_silent_rank():
     with pytest.raises(CommTimeout):
         raise_on_comm_status(torch.tensor([(7 << 24) | (3 << 16) | 1]), "lasp")
     raise_on_comm_status(torch.tensor([0]), "ok")
+
+
+def test_convert_checkpoint_cli_roundtrip(tmp_path):
+    """HF -> Megatron layout split over TP2 x EP2 -> merged back to HF through the example CLI gives the same tensors."""
+    import subprocess
+    import sys
+    import torch
+    from linear_moe_b200.ckpt import hf_convert
+    from linear_moe_b200.config.model_config import ModelConfig
+    from linear_moe_b200.models.transformer import CausalLM
+    flags = ["--base-model", "qwen2", "--num-layers", "2", "--hidden-size", "64", "--num-attention-heads", "4", "--group-query-attention",
+             "--num-query-groups", "2", "--ffn-hidden-size", "128", "--num-experts", "4", "--moe-router-topk", "2",
+             "--moe-ffn-hidden-size", "32", "--vocab-size", "256", "--patch-tokenizer-type", "NullTokenizer", "--swiglu",
+             "--untie-embeddings-and-output-weights", "--disable-bias-linear", "--seq-length", "32", "--max-position-embeddings", "32",
+             "--micro-batch-size", "1", "--global-batch-size", "1", "--train-iters", "1"]
+    from linear_moe_b200.config.arguments import parse_args
+    _, cfg, _, _ = parse_args(flags)
+    model = CausalLM(cfg)
+    hf = hf_convert.mcore_to_hf({k: v.detach() for k, v in model.state_dict().items()}, cfg)
+    hf_dir, ck, back = tmp_path / "hf", tmp_path / "ck", tmp_path / "back"
+    hf_dir.mkdir()
+    torch.save(hf, hf_dir / "pytorch_model.bin")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cli = os.path.join(root, "examples", "convert_checkpoint.py")
+    subprocess.run([sys.executable, cli, "--direction", "hf2mcore", "--load", str(hf_dir), "--save", str(ck),
+                    "--target-tp", "2", "--target-ep", "2", *flags], check=True, capture_output=True)
+    assert (ck / "latest_checkpointed_iteration.txt").read_text() == "release"
+    subprocess.run([sys.executable, cli, "--direction", "mcore2hf", "--load", str(ck), "--save", str(back),
+                    "--source-tp", "2", "--source-ep", "2", *flags], check=True, capture_output=True)
+    out = torch.load(back / "pytorch_model.bin")
+    assert set(out) == set(hf)
+    for k in hf:
+        assert torch.equal(out[k], hf[k]), k
