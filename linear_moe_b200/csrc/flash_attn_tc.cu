@@ -364,6 +364,421 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
 }
 
+
+// =====================================================================================================================
+// Backward on tcgen05, two kernels that recompute the scores (7 GEMMs per tile pair instead of 5, no atomics):
+//   fa_bwd_dq_tc_kernel    one CTA = 128 queries of one head; loops over tiles of 64 keys:
+//                          S = Q K^T and dP = dO V^T into tensor memory -> dS = P (dP - delta) scale (softmax warps,
+//                          thread = query row) -> shared memory -> dQ += dS K accumulated in tensor memory.
+//   fa_bwd_dkv_tc_kernel   one CTA = 128 keys of one KV head; loops over the query heads of the group and tiles of 64
+//                          queries: S^T = K Q^T and dP^T = V dO^T -> P^T, dS^T (thread = key row) -> shared memory ->
+//                          dV += P^T dO and dK += dS^T Q accumulated in tensor memory.
+// A [64 x D] tile loaded as D/64 boxes of {64 d, 64 rows} serves both as a K-major operand (rows = N) of the score GEMMs
+// and as an MN-major operand (rows = K) of the gradient GEMMs.  Same warp roles, barriers and bounded waits as the forward.
+// =====================================================================================================================
+constexpr int BT = 64;                                       // tile of the looped dimension (keys for dQ, queries for dK/dV)
+
+struct BwdArgs {
+    const float* lse;     // [B, Hq, Tq] natural-log sum-exp from the forward
+    const float* delta;   // [B, Hq, Tq] rowsum(dO * O)
+    bf16* dq;             // [B, Tq, Hq, D]
+    bf16* dk;             // [B, Tk, Hkv, D]
+    bf16* dv;             // [B, Tk, Hkv, D]
+    int B, Tq, Tk, Hq, Hkv;
+    int q_offset, window;
+    float scale;
+    int* err;
+};
+
+template <int D>
+struct __align__(1024) SmemBwd {
+    uint8_t big0[BM * D * 2];          // dQ kernel: Q tile      | dK/dV kernel: K tile
+    uint8_t big1[BM * D * 2];          // dQ kernel: dO tile     | dK/dV kernel: V tile
+    uint8_t st0[2][BT * D * 2];        // dQ kernel: K stages    | dK/dV kernel: Q stages
+    uint8_t st1[2][BT * D * 2];        // dQ kernel: V stages    | dK/dV kernel: dO stages
+    uint8_t p[BM * BT * 2];            // dS (dQ kernel) | P^T (dK/dV kernel), K-major, 128 rows x 128 bytes
+    uint8_t ds[BM * BT * 2];           // dS^T (dK/dV kernel)
+    uint64_t big_full, st_full[2], st_empty[2], s_full[2], p_ready, acc_done;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ bool visible(int key, int qi, int Tk, int window) {
+    return key <= qi && key < Tk && (window <= 0 || key > qi - window);
+}
+
+template <int D>
+__global__ void __launch_bounds__(THREADS, 1)
+fa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmG,
+                    const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, BwdArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    SmemBwd<D>& sm = *reinterpret_cast<SmemBwd<D>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int DK = D / 64;
+    constexpr uint32_t TMEM_COLS = 512, ACC_COL = 256;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qb = gridDim.x - 1 - blockIdx.x;
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int hk = h / (a.Hq / a.Hkv);
+    const int q0 = qb * BM;
+    volatile int* abort_flag = &sm.abort_flag;
+    int* err = a.err;
+    const int last_q = min(a.Tq, q0 + BM) - 1;
+    const int k_hi = min(a.Tk, a.q_offset + last_q + 1);
+    const int k_lo = a.window > 0 ? max(0, a.q_offset + q0 - a.window + 1) : 0;
+    const int nb_lo = k_lo / BT, nb_hi = (k_hi + BT - 1) / BT;
+    const int n_it = max(nb_hi - nb_lo, 0);
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sm.big_full, 1);
+        for (int s = 0; s < 2; ++s) { mbar_init(&sm.st_full[s], 1); mbar_init(&sm.st_empty[s], 1); mbar_init(&sm.s_full[s], 1); }
+        mbar_init(&sm.p_ready, 4 * SPLIT);
+        mbar_init(&sm.acc_done, 1);
+        sm.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(s32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = sm.tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0 && n_it > 0) {
+            mbar_expect_tx(&sm.big_full, 2 * BM * D * 2);
+#pragma unroll
+            for (int kb = 0; kb < DK; ++kb) {
+                tma_load_4d(sm.big0 + kb * BM * 128, &tmQ, &sm.big_full, kb * 64, h, q0, b);
+                tma_load_4d(sm.big1 + kb * BM * 128, &tmG, &sm.big_full, kb * 64, h, q0, b);
+            }
+            for (int j = 0; j < n_it; ++j) {
+                const int s = j & 1;
+                const int key0 = (nb_lo + j) * BT;
+                if (!mbar_wait_suspend(&sm.st_empty[s], ((j >> 1) & 1) ^ 1, abort_flag, err, 0x4100 | s)) break;
+                mbar_expect_tx(&sm.st_full[s], 2 * BT * D * 2);
+#pragma unroll
+                for (int kb = 0; kb < DK; ++kb) {
+                    tma_load_4d(sm.st0[s] + kb * 8192, &tmK, &sm.st_full[s], kb * 64, hk, key0, b);
+                    tma_load_4d(sm.st1[s] + kb * 8192, &tmV, &sm.st_full[s], kb * 64, hk, key0, b);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && n_it > 0) {
+            constexpr uint32_t idesc_s = idesc_bf16<false, BT>();       // [128 q] x [64 keys], both K-major
+            constexpr uint32_t idesc_a = idesc_bf16<true, D>();         // dQ += dS K: B = K tile read MN-major
+            bool ok = mbar_wait_suspend(&sm.big_full, 0, abort_flag, err, 0x4200);
+            auto issue_sd = [&](int j) -> bool {
+                const int s = j & 1;
+                if (!mbar_wait_suspend(&sm.st_full[s], (j >> 1) & 1, abort_flag, err, 0x4300 | s)) return false;
+                tc_fence_after();
+                const uint32_t qa = s32(sm.big0), ga = s32(sm.big1), ka = s32(sm.st0[s]), va = s32(sm.st1[s]);
+#pragma unroll
+                for (int kk = 0; kk < D / UMMA_K; ++kk) {
+                    const uint32_t ao = (kk / 4) * (BM * 128) + (kk % 4) * 32, bo = (kk / 4) * 8192 + (kk % 4) * 32;
+                    umma_f16(tmem_base + s * 128, make_desc<false>(qa + ao), make_desc<false>(ka + bo), idesc_s, kk > 0 ? 1u : 0u);
+                }
+#pragma unroll
+                for (int kk = 0; kk < D / UMMA_K; ++kk) {
+                    const uint32_t ao = (kk / 4) * (BM * 128) + (kk % 4) * 32, bo = (kk / 4) * 8192 + (kk % 4) * 32;
+                    umma_f16(tmem_base + s * 128 + 64, make_desc<false>(ga + ao), make_desc<false>(va + bo), idesc_s, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(&sm.s_full[s]);
+                return true;
+            };
+            if (ok) ok = issue_sd(0);
+            for (int j = 0; ok && j < n_it; ++j) {
+                if (j + 1 < n_it) { ok = issue_sd(j + 1); if (!ok) break; }
+                const int s = j & 1;
+                if (!mbar_wait_suspend(&sm.p_ready, j & 1, abort_flag, err, 0x4400)) break;
+                tc_fence_after();
+                const uint32_t pa = s32(sm.p), ka = s32(sm.st0[s]);
+#pragma unroll
+                for (int kk = 0; kk < BT / UMMA_K; ++kk)
+                    umma_f16(tmem_base + ACC_COL, make_desc<false>(pa + kk * 32), make_desc<true>(ka + kk * 2048), idesc_a,
+                             (j > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(&sm.st_empty[s]);
+                umma_commit(&sm.acc_done);
+            }
+        }
+    } else if (warp >= 4) {
+        const int qd = warp & 3, part = (warp - 4) >> 2;
+        const int r = qd * 32 + lane;
+        const int row = q0 + r;
+        const int qi = a.q_offset + row;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
+        const float sc = a.scale * LOG2E;
+        constexpr int CW = BT / SPLIT;                           // 16 keys per thread
+        const long long stat = ((long long)b * a.Hq + h) * a.Tq + row;
+        const float lse2 = row < a.Tq ? a.lse[stat] * LOG2E : INFINITY;
+        const float dl = row < a.Tq ? a.delta[stat] : 0.f;
+        uint8_t* prow = sm.p + (r >> 3) * 1024 + (r & 7) * 128;
+        bool alive = n_it > 0;
+        for (int j = 0; alive && j < n_it; ++j) {
+            const int s = j & 1;
+            const int key0 = (nb_lo + j) * BT + part * CW;
+            if (!mbar_wait_suspend(&sm.s_full[s], (j >> 1) & 1, abort_flag, err, 0x4500 | s)) { alive = false; break; }
+            tc_fence_after();
+            uint32_t sv[CW], dv[CW];
+            tmem_ld16(lane_addr + s * 128 + part * CW, sv);
+            tmem_ld16(lane_addr + s * 128 + 64 + part * CW, dv);
+            tmem_ld_wait();
+            uint32_t pk[CW / 2];
+#pragma unroll
+            for (int i = 0; i < CW; i += 2) {
+                float d2[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const bool vis = visible(key0 + i + e, qi, a.Tk, a.window);
+                    const float p = vis ? exp2f(fmaf(__uint_as_float(sv[i + e]), sc, -lse2)) : 0.f;
+                    d2[e] = p * (__uint_as_float(dv[i + e]) - dl) * a.scale;
+                }
+                pk[i >> 1] = pack_bf16(d2[0], d2[1]);
+            }
+            if (j > 0 && !mbar_wait_suspend(&sm.acc_done, (j - 1) & 1, abort_flag, err, 0x4600)) { alive = false; break; }
+            *reinterpret_cast<uint4*>(prow + (((part * 2) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            *reinterpret_cast<uint4*>(prow + (((part * 2 + 1) ^ (r & 7)) << 4)) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            tc_fence_before();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.p_ready);
+        }
+        constexpr int OW = D / SPLIT;
+        uint32_t acc[OW];
+#pragma unroll
+        for (int i = 0; i < OW; ++i) acc[i] = 0u;
+        if (alive && n_it > 0 && mbar_wait_suspend(&sm.acc_done, (n_it - 1) & 1, abort_flag, err, 0x4700)) {
+            tc_fence_after();
+            tmem_ld<OW>(lane_addr + ACC_COL + part * OW, acc);
+            tmem_ld_wait();
+        }
+        if (row < a.Tq) {
+            bf16* og = a.dq + (((long long)b * a.Tq + row) * a.Hq + h) * D + part * OW;
+#pragma unroll
+            for (int c = 0; c < OW; c += 8)
+                *reinterpret_cast<uint4*>(og + c) = make_uint4(pack_bf16(__uint_as_float(acc[c]), __uint_as_float(acc[c + 1])),
+                                                               pack_bf16(__uint_as_float(acc[c + 2]), __uint_as_float(acc[c + 3])),
+                                                               pack_bf16(__uint_as_float(acc[c + 4]), __uint_as_float(acc[c + 5])),
+                                                               pack_bf16(__uint_as_float(acc[c + 6]), __uint_as_float(acc[c + 7])));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+
+template <int D>
+__global__ void __launch_bounds__(THREADS, 1)
+fa_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmG,
+                     const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV, BwdArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    SmemBwd<D>& sm = *reinterpret_cast<SmemBwd<D>*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int DK = D / 64;
+    constexpr uint32_t TMEM_COLS = 512, DV_COL = 256, DK_COL = 256 + D;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int kb_tile = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+    const int rep = a.Hq / a.Hkv;
+    const int k0 = kb_tile * BM;
+    volatile int* abort_flag = &sm.abort_flag;
+    int* err = a.err;
+    // query tiles (of 64) that can see a key of this tile: q >= k0 - q_offset, and with a window q < k0 + 127 + window - q_offset
+    const int i_lo = max(0, k0 - a.q_offset) / BT;
+    int q_end = a.Tq;
+    if (a.window > 0) q_end = min(a.Tq, max(0, k0 + BM - 1 + a.window - a.q_offset));
+    const int i_hi = (q_end + BT - 1) / BT;
+    const int ni = max(i_hi - i_lo, 0);
+    const int n_it = ni * rep;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sm.big_full, 1);
+        for (int s = 0; s < 2; ++s) { mbar_init(&sm.st_full[s], 1); mbar_init(&sm.st_empty[s], 1); mbar_init(&sm.s_full[s], 1); }
+        mbar_init(&sm.p_ready, 4 * SPLIT);
+        mbar_init(&sm.acc_done, 1);
+        sm.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(s32(&sm.tmem_base)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = sm.tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0 && n_it > 0) {
+            mbar_expect_tx(&sm.big_full, 2 * BM * D * 2);
+#pragma unroll
+            for (int kb = 0; kb < DK; ++kb) {
+                tma_load_4d(sm.big0 + kb * BM * 128, &tmK, &sm.big_full, kb * 64, hk, k0, b);
+                tma_load_4d(sm.big1 + kb * BM * 128, &tmV, &sm.big_full, kb * 64, hk, k0, b);
+            }
+            for (int it = 0; it < n_it; ++it) {
+                const int s = it & 1;
+                const int h = hk * rep + it / ni, q0 = (i_lo + it % ni) * BT;
+                if (!mbar_wait_suspend(&sm.st_empty[s], ((it >> 1) & 1) ^ 1, abort_flag, err, 0x5100 | s)) break;
+                mbar_expect_tx(&sm.st_full[s], 2 * BT * D * 2);
+#pragma unroll
+                for (int kb = 0; kb < DK; ++kb) {
+                    tma_load_4d(sm.st0[s] + kb * 8192, &tmQ, &sm.st_full[s], kb * 64, h, q0, b);
+                    tma_load_4d(sm.st1[s] + kb * 8192, &tmG, &sm.st_full[s], kb * 64, h, q0, b);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && n_it > 0) {
+            constexpr uint32_t idesc_s = idesc_bf16<false, BT>();       // [128 keys] x [64 queries], both K-major
+            constexpr uint32_t idesc_a = idesc_bf16<true, D>();         // B = dO / Q tile read MN-major
+            bool ok = mbar_wait_suspend(&sm.big_full, 0, abort_flag, err, 0x5200);
+            auto issue_sd = [&](int it) -> bool {
+                const int s = it & 1;
+                if (!mbar_wait_suspend(&sm.st_full[s], (it >> 1) & 1, abort_flag, err, 0x5300 | s)) return false;
+                tc_fence_after();
+                const uint32_t ka = s32(sm.big0), va = s32(sm.big1), qa = s32(sm.st0[s]), ga = s32(sm.st1[s]);
+#pragma unroll
+                for (int kk = 0; kk < D / UMMA_K; ++kk) {
+                    const uint32_t ao = (kk / 4) * (BM * 128) + (kk % 4) * 32, bo = (kk / 4) * 8192 + (kk % 4) * 32;
+                    umma_f16(tmem_base + s * 128, make_desc<false>(ka + ao), make_desc<false>(qa + bo), idesc_s, kk > 0 ? 1u : 0u);
+                }
+#pragma unroll
+                for (int kk = 0; kk < D / UMMA_K; ++kk) {
+                    const uint32_t ao = (kk / 4) * (BM * 128) + (kk % 4) * 32, bo = (kk / 4) * 8192 + (kk % 4) * 32;
+                    umma_f16(tmem_base + s * 128 + 64, make_desc<false>(va + ao), make_desc<false>(ga + bo), idesc_s, kk > 0 ? 1u : 0u);
+                }
+                umma_commit(&sm.s_full[s]);
+                return true;
+            };
+            if (ok) ok = issue_sd(0);
+            for (int it = 0; ok && it < n_it; ++it) {
+                if (it + 1 < n_it) { ok = issue_sd(it + 1); if (!ok) break; }
+                const int s = it & 1;
+                if (!mbar_wait_suspend(&sm.p_ready, it & 1, abort_flag, err, 0x5400)) break;
+                tc_fence_after();
+                const uint32_t pa = s32(sm.p), da = s32(sm.ds), qa = s32(sm.st0[s]), ga = s32(sm.st1[s]);
+#pragma unroll
+                for (int kk = 0; kk < BT / UMMA_K; ++kk)        // dV += P^T dO
+                    umma_f16(tmem_base + DV_COL, make_desc<false>(pa + kk * 32), make_desc<true>(ga + kk * 2048), idesc_a,
+                             (it > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+                for (int kk = 0; kk < BT / UMMA_K; ++kk)        // dK += dS^T Q
+                    umma_f16(tmem_base + DK_COL, make_desc<false>(da + kk * 32), make_desc<true>(qa + kk * 2048), idesc_a,
+                             (it > 0 || kk > 0) ? 1u : 0u);
+                umma_commit(&sm.st_empty[s]);
+                umma_commit(&sm.acc_done);
+            }
+        }
+    } else if (warp >= 4) {
+        const int qd = warp & 3, part = (warp - 4) >> 2;
+        const int r = qd * 32 + lane;                            // key row inside the tile
+        const int key = k0 + r;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(qd * 32) << 16);
+        const float sc = a.scale * LOG2E;
+        constexpr int CW = BT / SPLIT;                           // 16 queries per thread
+        uint8_t* prow = sm.p + (r >> 3) * 1024 + (r & 7) * 128;
+        uint8_t* drow = sm.ds + (r >> 3) * 1024 + (r & 7) * 128;
+        bool alive = n_it > 0;
+        for (int it = 0; alive && it < n_it; ++it) {
+            const int s = it & 1;
+            const int h = hk * rep + it / ni;
+            const int qbase = (i_lo + it % ni) * BT + part * CW;     // first query of this thread's columns
+            const float* lse_p = a.lse + ((long long)b * a.Hq + h) * a.Tq;
+            const float* del_p = a.delta + ((long long)b * a.Hq + h) * a.Tq;
+            float l2[CW], dl[CW];
+#pragma unroll
+            for (int i = 0; i < CW; ++i) {
+                const int q = qbase + i;
+                l2[i] = q < a.Tq ? __ldg(lse_p + q) * LOG2E : INFINITY;
+                dl[i] = q < a.Tq ? __ldg(del_p + q) : 0.f;
+            }
+            if (!mbar_wait_suspend(&sm.s_full[s], (it >> 1) & 1, abort_flag, err, 0x5500 | s)) { alive = false; break; }
+            tc_fence_after();
+            uint32_t sv[CW], dv[CW];
+            tmem_ld16(lane_addr + s * 128 + part * CW, sv);
+            tmem_ld16(lane_addr + s * 128 + 64 + part * CW, dv);
+            tmem_ld_wait();
+            uint32_t pk[CW / 2], dk2[CW / 2];
+#pragma unroll
+            for (int i = 0; i < CW; i += 2) {
+                float p2[2], d2[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const bool vis = visible(key, a.q_offset + qbase + i + e, a.Tk, a.window);
+                    p2[e] = vis ? exp2f(fmaf(__uint_as_float(sv[i + e]), sc, -l2[i + e])) : 0.f;
+                    d2[e] = p2[e] * (__uint_as_float(dv[i + e]) - dl[i + e]) * a.scale;
+                }
+                pk[i >> 1] = pack_bf16(p2[0], p2[1]);
+                dk2[i >> 1] = pack_bf16(d2[0], d2[1]);
+            }
+            if (it > 0 && !mbar_wait_suspend(&sm.acc_done, (it - 1) & 1, abort_flag, err, 0x5600)) { alive = false; break; }
+            const int c0 = ((part * 2) ^ (r & 7)) << 4, c1 = ((part * 2 + 1) ^ (r & 7)) << 4;
+            *reinterpret_cast<uint4*>(prow + c0) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            *reinterpret_cast<uint4*>(prow + c1) = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+            *reinterpret_cast<uint4*>(drow + c0) = make_uint4(dk2[0], dk2[1], dk2[2], dk2[3]);
+            *reinterpret_cast<uint4*>(drow + c1) = make_uint4(dk2[4], dk2[5], dk2[6], dk2[7]);
+            tc_fence_before();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.p_ready);
+        }
+        constexpr int OW = D / SPLIT;
+        uint32_t av[OW], ak[OW];
+#pragma unroll
+        for (int i = 0; i < OW; ++i) { av[i] = 0u; ak[i] = 0u; }
+        if (alive && n_it > 0 && mbar_wait_suspend(&sm.acc_done, (n_it - 1) & 1, abort_flag, err, 0x5700)) {
+            tc_fence_after();
+            tmem_ld<OW>(lane_addr + DV_COL + part * OW, av);
+            tmem_ld<OW>(lane_addr + DK_COL + part * OW, ak);
+            tmem_ld_wait();
+        }
+        if (key < a.Tk) {
+            const long long off = (((long long)b * a.Tk + key) * a.Hkv + hk) * D + part * OW;
+#pragma unroll
+            for (int c = 0; c < OW; c += 8) {
+                *reinterpret_cast<uint4*>(a.dv + off + c) = make_uint4(pack_bf16(__uint_as_float(av[c]), __uint_as_float(av[c + 1])),
+                                                                       pack_bf16(__uint_as_float(av[c + 2]), __uint_as_float(av[c + 3])),
+                                                                       pack_bf16(__uint_as_float(av[c + 4]), __uint_as_float(av[c + 5])),
+                                                                       pack_bf16(__uint_as_float(av[c + 6]), __uint_as_float(av[c + 7])));
+                *reinterpret_cast<uint4*>(a.dk + off + c) = make_uint4(pack_bf16(__uint_as_float(ak[c]), __uint_as_float(ak[c + 1])),
+                                                                       pack_bf16(__uint_as_float(ak[c + 2]), __uint_as_float(ak[c + 3])),
+                                                                       pack_bf16(__uint_as_float(ak[c + 4]), __uint_as_float(ak[c + 5])),
+                                                                       pack_bf16(__uint_as_float(ak[c + 6]), __uint_as_float(ak[c + 7])));
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+}
+
+// delta[b,h,t] = sum_d dO[b,t,h,d] * O[b,t,h,d]; one warp per (b,t,h)
+template <int D>
+__global__ void fa_delta_tc_kernel(const bf16* __restrict__ o, const bf16* __restrict__ d_o, float* __restrict__ delta, int B, int Tq, int Hq) {
+    const int l = threadIdx.x & 31;
+    const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (row >= (long long)B * Tq * Hq) return;
+    const int h = row % Hq;
+    const long long bt = row / Hq;
+    const int t = bt % Tq, b = bt / Tq;
+    float s = 0.f;
+    for (int c = l * 2; c < D; c += 64) {
+        const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + row * D + c));
+        const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(d_o + row * D + c));
+        s += x.x * y.x + x.y * y.y;
+    }
+    s = warp_sum(s);
+    if (l == 0) delta[((long long)b * Hq + h) * Tq + t] = s;
+}
+
 // [B, T, H, D] bf16 with element strides (sb, st, sh), unit stride along D; box = {64, 1, box_t, 1}
 static int make_map_4d(CUtensorMap* map, const void* ptr, int B, int T, int H, int D, long long sb, long long st, long long sh,
                        uint32_t box_t) {
@@ -407,4 +822,41 @@ LMOE_API int lmoe_flash_attn_fwd_tc(const void* q, const long long* qs, const vo
         fa_fwd_tc_kernel<64><<<grid, THREADS, smem, st>>>(mq, mk, mv, a);
     } else return -1;
     return (int)cudaGetLastError();
+}
+
+template <int D>
+static int launch_bwd_tc(const CUtensorMap& q128, const CUtensorMap& g128, const CUtensorMap& k64, const CUtensorMap& v64,
+                         const CUtensorMap& q64, const CUtensorMap& g64, const CUtensorMap& k128, const CUtensorMap& v128,
+                         const BwdArgs& a, const bf16* o, const bf16* d_o, float* delta, cudaStream_t st) {
+    const long long rows = (long long)a.B * a.Tq * a.Hq;
+    fa_delta_tc_kernel<D><<<(unsigned)((rows + 7) / 8), 256, 0, st>>>(o, d_o, delta, a.B, a.Tq, a.Hq);
+    const size_t smem = sizeof(SmemBwd<D>) + 1024;
+    cudaFuncSetAttribute(fa_bwd_dq_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(fa_bwd_dkv_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    fa_bwd_dq_tc_kernel<D><<<dim3((a.Tq + BM - 1) / BM, a.Hq, a.B), THREADS, smem, st>>>(q128, g128, k64, v64, a);
+    fa_bwd_dkv_tc_kernel<D><<<dim3((a.Tk + BM - 1) / BM, a.Hkv, a.B), THREADS, smem, st>>>(q64, g64, k128, v128, a);
+    return (int)cudaGetLastError();
+}
+
+// Backward of lmoe_flash_attn_fwd_tc.  o, d_o: contiguous [B,Tq,Hq,D]; ap->delta is scratch [B,Hq,Tq]; writes dq, dk, dv.
+LMOE_API int lmoe_flash_attn_bwd_tc(const void* q, const long long* qs, const void* k, const long long* ks, const void* v,
+                                    const long long* vs, const void* o, const void* d_o, float* delta, const BwdArgs* ap, int D,
+                                    cudaStream_t st) {
+    BwdArgs a = *ap;
+    a.delta = delta;
+    const long long gs[3] = {(long long)a.Tq * a.Hq * D, (long long)a.Hq * D, (long long)D};
+    CUtensorMap q128, g128, k64, v64, q64, g64, k128, v128;
+    int rc = 0;
+    rc |= make_map_4d(&q128, q, a.B, a.Tq, a.Hq, D, qs[0], qs[1], qs[2], BM);
+    rc |= make_map_4d(&g128, d_o, a.B, a.Tq, a.Hq, D, gs[0], gs[1], gs[2], BM);
+    rc |= make_map_4d(&k64, k, a.B, a.Tk, a.Hkv, D, ks[0], ks[1], ks[2], BT);
+    rc |= make_map_4d(&v64, v, a.B, a.Tk, a.Hkv, D, vs[0], vs[1], vs[2], BT);
+    rc |= make_map_4d(&q64, q, a.B, a.Tq, a.Hq, D, qs[0], qs[1], qs[2], BT);
+    rc |= make_map_4d(&g64, d_o, a.B, a.Tq, a.Hq, D, gs[0], gs[1], gs[2], BT);
+    rc |= make_map_4d(&k128, k, a.B, a.Tk, a.Hkv, D, ks[0], ks[1], ks[2], BM);
+    rc |= make_map_4d(&v128, v, a.B, a.Tk, a.Hkv, D, vs[0], vs[1], vs[2], BM);
+    if (rc) return -11;
+    if (D == 128) return launch_bwd_tc<128>(q128, g128, k64, v64, q64, g64, k128, v128, a, (const bf16*)o, (const bf16*)d_o, delta, st);
+    if (D == 64) return launch_bwd_tc<64>(q128, g128, k64, v64, q64, g64, k128, v128, a, (const bf16*)o, (const bf16*)d_o, delta, st);
+    return -1;
 }

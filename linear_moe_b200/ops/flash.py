@@ -13,6 +13,32 @@ import torch
 
 _ENABLED = os.environ.get("LMOE_FLASH_ATTN", "1") != "0"
 _TCGEN05_FWD = os.environ.get("LMOE_FLASH_TCGEN05", "1") != "0"      # forward on tcgen05/TMEM (csrc/flash_attn_tc.cu)
+_TCGEN05_BWD = os.environ.get("LMOE_FLASH_TCGEN05_BWD", "1") != "0"  # backward on tcgen05/TMEM (two kernels: dQ, dK/dV)
+
+
+class _FaTcBwdArgs(ctypes.Structure):
+    _fields_ = ([(n, ctypes.c_void_p) for n in ("lse", "delta", "dq", "dk", "dv")] +
+                [(n, ctypes.c_int) for n in ("B", "Tq", "Tk", "Hq", "Hkv", "q_offset", "window")] +
+                [("scale", ctypes.c_float), ("err", ctypes.c_void_p)])
+
+
+def _backward_tcgen05(q, k, v, out, d_out, lse, scale, q_offset, window):
+    from . import cuda as K
+    from . import gemm
+    B, Tq, Hq, D = q.shape
+    dq = torch.empty(B, Tq, Hq, D, dtype=q.dtype, device=q.device)
+    dk = torch.empty(B, k.shape[1], k.shape[2], D, dtype=q.dtype, device=q.device)
+    dv = torch.empty_like(dk)
+    delta = torch.empty_like(lse)
+    a = _FaTcBwdArgs()
+    a.lse, a.delta, a.dq, a.dk, a.dv = lse.data_ptr(), delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr()
+    a.B, a.Tq, a.Hq, a.Tk, a.Hkv = B, Tq, Hq, k.shape[1], k.shape[2]
+    a.q_offset, a.window, a.scale = int(q_offset), int(window or 0), float(scale)
+    a.err = gemm._err(q.device).data_ptr()
+    st = lambda t: (ctypes.c_longlong * 3)(t.stride(0), t.stride(1), t.stride(2))
+    K._check(K.lib().lmoe_flash_attn_bwd_tc(K._p(q), st(q), K._p(k), st(k), K._p(v), st(v), K._p(out), K._p(d_out), K._p(delta),
+                                            ctypes.byref(a), ctypes.c_int(D), K._st()), "flash_attn_bwd_tc", 3)
+    return dq, dk, dv
 
 
 class _FaTcArgs(ctypes.Structure):
@@ -97,6 +123,9 @@ class FlashAttention(torch.autograd.Function):
         scale, q_offset, window = ctx.cfg
         B, Tq, Hq, D = q.shape
         d_out = d_out.contiguous()
+        if _TCGEN05_BWD:
+            dq, dk, dv = _backward_tcgen05(q, k, v, out, d_out, lse, scale, q_offset, window)
+            return dq, dk, dv, None, None, None
         delta = torch.empty_like(lse)
         dq_acc = torch.zeros(B, Tq, Hq, D, dtype=torch.float32, device=q.device)
         dk = torch.empty(B, k.shape[1], k.shape[2], D, dtype=q.dtype, device=q.device)

@@ -265,6 +265,7 @@ def test_lsm_vector_gla(D, T, with_state):
 def test_flash_attention(D, Tq, Tk, q_offset, window, Hq, Hkv, tcgen05, monkeypatch):
     from linear_moe_b200.ops import flash, gemm
     monkeypatch.setattr(flash, "_TCGEN05_FWD", tcgen05)
+    monkeypatch.setattr(flash, "_TCGEN05_BWD", tcgen05)
     torch.manual_seed(11)
     B = 2
     q = torch.randn(B, Tq, Hq, D, device=dev()).to(torch.bfloat16)
