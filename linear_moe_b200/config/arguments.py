@@ -254,6 +254,7 @@ def build_parser() -> argparse.ArgumentParser:
     _flag(g, "--timing-log-level", type=int, default=0, choices=[0, 1, 2])
     _flag(g, "--barrier-with-L1-time", action=argparse.BooleanOptionalAction, default=True)
     _flag(g, "--transformer-timers", action="store_true")
+    _flag(g, "--preset", type=str, default=None)            # model architecture from config/presets.py instead of flags
     _flag(g, "--profile", action="store_true")
     _flag(g, "--profile-step-start", type=int, default=10)
     _flag(g, "--profile-step-end", type=int, default=12)
@@ -455,6 +456,10 @@ def configs_from_args(args: argparse.Namespace) -> Tuple[ModelConfig, ParallelCo
         keep_last=args.keep_last, eod_mask_loss=args.eod_mask_loss,
         heartbeat_interval_s=args.heartbeat_interval_s, heartbeat_timeout_s=args.heartbeat_timeout_s,
     )
+    if getattr(args, "preset", None):
+        # a named preset replaces the architecture flags (parallelism, precision and training flags still apply)
+        from .presets import get_preset
+        model = get_preset(args.preset, params_dtype=dtype, fp8=model.fp8 or None)
     return model, par, train
 
 
