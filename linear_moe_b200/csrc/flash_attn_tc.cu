@@ -377,6 +377,8 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 // and as an MN-major operand (rows = K) of the gradient GEMMs.  Same warp roles, barriers and bounded waits as the forward.
 // =====================================================================================================================
 constexpr int BT = 64;                                       // tile of the looped dimension (keys for dQ, queries for dK/dV)
+constexpr int NST = 3;                                       // TMA stages of the looped tiles: a stage is released only after the
+                                                             // gradient MMAs of its iteration, so two stages would expose the load latency
 
 struct BwdArgs {
     const float* lse;     // [B, Hq, Tq] natural-log sum-exp from the forward
@@ -394,11 +396,11 @@ template <int D>
 struct __align__(1024) SmemBwd {
     uint8_t big0[BM * D * 2];          // dQ kernel: Q tile      | dK/dV kernel: K tile
     uint8_t big1[BM * D * 2];          // dQ kernel: dO tile     | dK/dV kernel: V tile
-    uint8_t st0[2][BT * D * 2];        // dQ kernel: K stages    | dK/dV kernel: Q stages
-    uint8_t st1[2][BT * D * 2];        // dQ kernel: V stages    | dK/dV kernel: dO stages
+    uint8_t st0[NST][BT * D * 2];        // dQ kernel: K stages    | dK/dV kernel: Q stages
+    uint8_t st1[NST][BT * D * 2];        // dQ kernel: V stages    | dK/dV kernel: dO stages
     uint8_t p[BM * BT * 2];            // dS (dQ kernel) | P^T (dK/dV kernel), K-major, 128 rows x 128 bytes
     uint8_t ds[BM * BT * 2];           // dS^T (dK/dV kernel)
-    uint64_t big_full, st_full[2], st_empty[2], s_full[2], p_ready, acc_done;
+    uint64_t big_full, st_full[NST], st_empty[NST], s_full[2], p_ready, acc_done;
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -430,7 +432,8 @@ fa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.big_full, 1);
-        for (int s = 0; s < 2; ++s) { mbar_init(&sm.st_full[s], 1); mbar_init(&sm.st_empty[s], 1); mbar_init(&sm.s_full[s], 1); }
+        for (int s = 0; s < NST; ++s) { mbar_init(&sm.st_full[s], 1); mbar_init(&sm.st_empty[s], 1); }
+        for (int s = 0; s < 2; ++s) mbar_init(&sm.s_full[s], 1);
         mbar_init(&sm.p_ready, 4 * SPLIT);
         mbar_init(&sm.acc_done, 1);
         sm.abort_flag = 0;
@@ -454,9 +457,9 @@ fa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 tma_load_4d(sm.big1 + kb * BM * 128, &tmG, &sm.big_full, kb * 64, h, q0, b);
             }
             for (int j = 0; j < n_it; ++j) {
-                const int s = j & 1;
+                const int s = j % NST;
                 const int key0 = (nb_lo + j) * BT;
-                if (!mbar_wait_suspend(&sm.st_empty[s], ((j >> 1) & 1) ^ 1, abort_flag, err, 0x4100 | s)) break;
+                if (!mbar_wait_suspend(&sm.st_empty[s], ((j / NST) & 1) ^ 1, abort_flag, err, 0x4100 | s)) break;
                 mbar_expect_tx(&sm.st_full[s], 2 * BT * D * 2);
 #pragma unroll
                 for (int kb = 0; kb < DK; ++kb) {
@@ -471,10 +474,10 @@ fa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             constexpr uint32_t idesc_a = idesc_bf16<true, D>();         // dQ += dS K: B = K tile read MN-major
             bool ok = mbar_wait_suspend(&sm.big_full, 0, abort_flag, err, 0x4200);
             auto issue_sd = [&](int j) -> bool {
-                const int s = j & 1;
-                if (!mbar_wait_suspend(&sm.st_full[s], (j >> 1) & 1, abort_flag, err, 0x4300 | s)) return false;
+                const int s = j & 1, g = j % NST;                    // tensor-memory buffer, shared-memory stage
+                if (!mbar_wait_suspend(&sm.st_full[g], (j / NST) & 1, abort_flag, err, 0x4300 | g)) return false;
                 tc_fence_after();
-                const uint32_t qa = s32(sm.big0), ga = s32(sm.big1), ka = s32(sm.st0[s]), va = s32(sm.st1[s]);
+                const uint32_t qa = s32(sm.big0), ga = s32(sm.big1), ka = s32(sm.st0[g]), va = s32(sm.st1[g]);
 #pragma unroll
                 for (int kk = 0; kk < D / UMMA_K; ++kk) {
                     const uint32_t ao = (kk / 4) * (BM * 128) + (kk % 4) * 32, bo = (kk / 4) * 8192 + (kk % 4) * 32;
@@ -491,7 +494,7 @@ fa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             if (ok) ok = issue_sd(0);
             for (int j = 0; ok && j < n_it; ++j) {
                 if (j + 1 < n_it) { ok = issue_sd(j + 1); if (!ok) break; }
-                const int s = j & 1;
+                const int s = j % NST;
                 if (!mbar_wait_suspend(&sm.p_ready, j & 1, abort_flag, err, 0x4400)) break;
                 tc_fence_after();
                 const uint32_t pa = s32(sm.p), ka = s32(sm.st0[s]);
@@ -597,7 +600,8 @@ fa_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.big_full, 1);
-        for (int s = 0; s < 2; ++s) { mbar_init(&sm.st_full[s], 1); mbar_init(&sm.st_empty[s], 1); mbar_init(&sm.s_full[s], 1); }
+        for (int s = 0; s < NST; ++s) { mbar_init(&sm.st_full[s], 1); mbar_init(&sm.st_empty[s], 1); }
+        for (int s = 0; s < 2; ++s) mbar_init(&sm.s_full[s], 1);
         mbar_init(&sm.p_ready, 4 * SPLIT);
         mbar_init(&sm.acc_done, 1);
         sm.abort_flag = 0;
@@ -621,9 +625,9 @@ fa_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                 tma_load_4d(sm.big1 + kb * BM * 128, &tmV, &sm.big_full, kb * 64, hk, k0, b);
             }
             for (int it = 0; it < n_it; ++it) {
-                const int s = it & 1;
+                const int s = it % NST;
                 const int h = hk * rep + it / ni, q0 = (i_lo + it % ni) * BT;
-                if (!mbar_wait_suspend(&sm.st_empty[s], ((it >> 1) & 1) ^ 1, abort_flag, err, 0x5100 | s)) break;
+                if (!mbar_wait_suspend(&sm.st_empty[s], ((it / NST) & 1) ^ 1, abort_flag, err, 0x5100 | s)) break;
                 mbar_expect_tx(&sm.st_full[s], 2 * BT * D * 2);
 #pragma unroll
                 for (int kb = 0; kb < DK; ++kb) {
@@ -638,10 +642,10 @@ fa_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             constexpr uint32_t idesc_a = idesc_bf16<true, D>();         // B = dO / Q tile read MN-major
             bool ok = mbar_wait_suspend(&sm.big_full, 0, abort_flag, err, 0x5200);
             auto issue_sd = [&](int it) -> bool {
-                const int s = it & 1;
-                if (!mbar_wait_suspend(&sm.st_full[s], (it >> 1) & 1, abort_flag, err, 0x5300 | s)) return false;
+                const int s = it & 1, g = it % NST;                  // tensor-memory buffer, shared-memory stage
+                if (!mbar_wait_suspend(&sm.st_full[g], (it / NST) & 1, abort_flag, err, 0x5300 | g)) return false;
                 tc_fence_after();
-                const uint32_t ka = s32(sm.big0), va = s32(sm.big1), qa = s32(sm.st0[s]), ga = s32(sm.st1[s]);
+                const uint32_t ka = s32(sm.big0), va = s32(sm.big1), qa = s32(sm.st0[g]), ga = s32(sm.st1[g]);
 #pragma unroll
                 for (int kk = 0; kk < D / UMMA_K; ++kk) {
                     const uint32_t ao = (kk / 4) * (BM * 128) + (kk % 4) * 32, bo = (kk / 4) * 8192 + (kk % 4) * 32;
@@ -658,7 +662,7 @@ fa_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             if (ok) ok = issue_sd(0);
             for (int it = 0; ok && it < n_it; ++it) {
                 if (it + 1 < n_it) { ok = issue_sd(it + 1); if (!ok) break; }
-                const int s = it & 1;
+                const int s = it % NST;
                 if (!mbar_wait_suspend(&sm.p_ready, it & 1, abort_flag, err, 0x5400)) break;
                 tc_fence_after();
                 const uint32_t pa = s32(sm.p), da = s32(sm.ds), qa = s32(sm.st0[s]), ga = s32(sm.st1[s]);
