@@ -231,6 +231,8 @@ def build_parser() -> argparse.ArgumentParser:
     _flag(g, "--recompute-granularity", type=str, default=None, choices=["full", "selective"])
     _flag(g, "--recompute-method", type=str, default=None, choices=["uniform", "block"])
     _flag(g, "--recompute-num-layers", type=int, default=1)
+    _flag(g, "--cpu-offloading", action="store_true")
+    _flag(g, "--cpu-offloading-num-layers", type=int, default=0)
     _flag(g, "--train-mode", type=str, default="pretrain", choices=["pretrain", "finetune"])
     _flag(g, "--check-for-nan-in-loss-and-grad", action=argparse.BooleanOptionalAction, default=True)
     _flag(g, "--exit-interval", type=int, default=None)
@@ -407,6 +409,7 @@ def configs_from_args(args: argparse.Namespace) -> Tuple[ModelConfig, ParallelCo
         fp8="block" if (args.fp8_hybrid or args.fp8_format) else None,
         recompute_granularity=recompute, recompute_method=args.recompute_method,
         recompute_num_layers=args.recompute_num_layers, test_mode=args.test_mode,
+        cpu_offloading=args.cpu_offloading, cpu_offloading_num_layers=args.cpu_offloading_num_layers,
     )
     vpp = None
     if args.num_layers_per_virtual_pipeline_stage:

@@ -138,6 +138,8 @@ class ModelConfig:
     recompute_granularity: Optional[str] = None   # None | selective | full
     recompute_method: Optional[str] = None        # uniform | block
     recompute_num_layers: int = 1
+    cpu_offloading: bool = False                  # activations of the first cpu_offloading_num_layers blocks go to pinned host memory
+    cpu_offloading_num_layers: int = 0
     cross_entropy_chunk: int = 4096               # tokens per fused LM-head+CE chunk
     test_mode: bool = False
 

@@ -528,17 +528,20 @@ fa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             tmem_ld16(lane_addr + s * 128 + part * CW, sv);
             tmem_ld16(lane_addr + s * 128 + 64 + part * CW, dv);
             tmem_ld_wait();
+            // masking is needed only on tiles that cross the causal diagonal, the window edge or the key length
+            const int tile_key0 = (nb_lo + j) * BT;
+            const bool need_mask = (tile_key0 + BT - 1 > a.q_offset + q0) || (tile_key0 + BT > a.Tk) ||
+                                   (a.window > 0 && tile_key0 <= a.q_offset + q0 + BM - 1 - a.window);
+            if (need_mask) {
+#pragma unroll
+                for (int i = 0; i < CW; ++i)
+                    if (!visible(key0 + i, qi, a.Tk, a.window)) sv[i] = 0xff800000u;      // -inf -> p = 0
+            }
             uint32_t pk[CW / 2];
 #pragma unroll
             for (int i = 0; i < CW; i += 2) {
-                float d2[2];
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const bool vis = visible(key0 + i + e, qi, a.Tk, a.window);
-                    const float p = vis ? exp2f(fmaf(__uint_as_float(sv[i + e]), sc, -lse2)) : 0.f;
-                    d2[e] = p * (__uint_as_float(dv[i + e]) - dl) * a.scale;
-                }
-                pk[i >> 1] = pack_bf16(d2[0], d2[1]);
+                const float p0 = exp2f(fmaf(__uint_as_float(sv[i]), sc, -lse2)), p1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -lse2));
+                pk[i >> 1] = pack_bf16(p0 * (__uint_as_float(dv[i]) - dl) * a.scale, p1 * (__uint_as_float(dv[i + 1]) - dl) * a.scale);
             }
             if (j > 0 && !mbar_wait_suspend(&sm.acc_done, (j - 1) & 1, abort_flag, err, 0x4600)) { alive = false; break; }
             *reinterpret_cast<uint4*>(prow + (((part * 2) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
@@ -695,11 +698,21 @@ fa_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             const float* lse_p = a.lse + ((long long)b * a.Hq + h) * a.Tq;
             const float* del_p = a.delta + ((long long)b * a.Hq + h) * a.Tq;
             float l2[CW], dl[CW];
+            if ((a.Tq & 3) == 0 && qbase + CW <= a.Tq) {          // 16-byte aligned rows of lse / delta: 4 + 4 vector loads
 #pragma unroll
-            for (int i = 0; i < CW; ++i) {
-                const int q = qbase + i;
-                l2[i] = q < a.Tq ? __ldg(lse_p + q) * LOG2E : INFINITY;
-                dl[i] = q < a.Tq ? __ldg(del_p + q) : 0.f;
+                for (int i = 0; i < CW; i += 4) {
+                    const float4 x = __ldg(reinterpret_cast<const float4*>(lse_p + qbase + i));
+                    const float4 y = __ldg(reinterpret_cast<const float4*>(del_p + qbase + i));
+                    l2[i] = x.x * LOG2E; l2[i + 1] = x.y * LOG2E; l2[i + 2] = x.z * LOG2E; l2[i + 3] = x.w * LOG2E;
+                    dl[i] = y.x; dl[i + 1] = y.y; dl[i + 2] = y.z; dl[i + 3] = y.w;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < CW; ++i) {
+                    const int q = qbase + i;
+                    l2[i] = q < a.Tq ? __ldg(lse_p + q) * LOG2E : INFINITY;
+                    dl[i] = q < a.Tq ? __ldg(del_p + q) : 0.f;
+                }
             }
             if (!mbar_wait_suspend(&sm.s_full[s], (it >> 1) & 1, abort_flag, err, 0x5500 | s)) { alive = false; break; }
             tc_fence_after();
@@ -707,18 +720,20 @@ fa_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             tmem_ld16(lane_addr + s * 128 + part * CW, sv);
             tmem_ld16(lane_addr + s * 128 + 64 + part * CW, dv);
             tmem_ld_wait();
+            const int tile_q0 = (i_lo + it % ni) * BT;
+            const bool need_mask = (k0 + BM - 1 > a.q_offset + tile_q0) || (k0 + BM > a.Tk) ||
+                                   (a.window > 0 && k0 <= a.q_offset + tile_q0 + BT - 1 - a.window);
+            if (need_mask) {
+#pragma unroll
+                for (int i = 0; i < CW; ++i)
+                    if (!visible(key, a.q_offset + qbase + i, a.Tk, a.window)) sv[i] = 0xff800000u;
+            }
             uint32_t pk[CW / 2], dk2[CW / 2];
 #pragma unroll
             for (int i = 0; i < CW; i += 2) {
-                float p2[2], d2[2];
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const bool vis = visible(key, a.q_offset + qbase + i + e, a.Tk, a.window);
-                    p2[e] = vis ? exp2f(fmaf(__uint_as_float(sv[i + e]), sc, -l2[i + e])) : 0.f;
-                    d2[e] = p2[e] * (__uint_as_float(dv[i + e]) - dl[i + e]) * a.scale;
-                }
-                pk[i >> 1] = pack_bf16(p2[0], p2[1]);
-                dk2[i >> 1] = pack_bf16(d2[0], d2[1]);
+                const float p0 = exp2f(fmaf(__uint_as_float(sv[i]), sc, -l2[i])), p1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -l2[i + 1]));
+                pk[i >> 1] = pack_bf16(p0, p1);
+                dk2[i >> 1] = pack_bf16(p0 * (__uint_as_float(dv[i]) - dl[i]) * a.scale, p1 * (__uint_as_float(dv[i + 1]) - dl[i + 1]) * a.scale);
             }
             if (it > 0 && !mbar_wait_suspend(&sm.acc_done, (it - 1) & 1, abort_flag, err, 0x5600)) { alive = false; break; }
             const int c0 = ((part * 2) ^ (r & 7)) << 4, c1 = ((part * 2 + 1) ^ (r & 7)) << 4;

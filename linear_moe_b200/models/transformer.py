@@ -156,6 +156,10 @@ class CausalLM(nn.Module):
             tied = self.embedding.word_embeddings.weight if (cfg.tie_embeddings and pre_process) else None
             self.output_layer = LMHead(cfg.hidden_size, cfg.vocab_size, mesh=mesh, std=cfg.init_method_std, tied=tied,
                                        chunk=cfg.cross_entropy_chunk, sequence_parallel=sp, dtype=dt, device=device)
+        self.offload = None
+        if cfg.cpu_offloading and cfg.cpu_offloading_num_layers > 0:
+            from ..parallel.offload import ActivationOffload
+            self.offload = ActivationOffload(cfg.cpu_offloading_num_layers)
         if cfg.la_module == "hgrn2" and cfg.hgrn2_lower_bound:
             self.lower_bounds = nn.Parameter(torch.zeros(len(all_specs), cfg.key_dim, dtype=dt, device=device))
 
@@ -177,6 +181,9 @@ class CausalLM(nn.Module):
             lb_i = None if lbs is None else lbs[blk.spec.index]
             if full_recompute and self._should_recompute(i):
                 x, residual = ckpt.checkpoint(blk, x, residual, None, position_offset, lb_i, use_reentrant=False)
+            elif self.offload is not None and self.training and caches is None and torch.is_grad_enabled():
+                with self.offload.layer(i):
+                    x, residual = blk(x, residual, cache, position_offset, lb_i)
             else:
                 x, residual = blk(x, residual, cache, position_offset, lb_i)
         return x, residual

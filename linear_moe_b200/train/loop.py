@@ -175,6 +175,10 @@ class Trainer:
         timers("forward-backward").start(barrier=tc.barrier_with_L1_time and tc.timing_log_level > 0)
         logs = self._run_schedule()
         timers("forward-backward").stop()
+        for m in self.models:
+            inner = getattr(m, "module", m)
+            if getattr(inner, "offload", None) is not None:
+                inner.offload.step_done()
         timers("all-grads-sync", 1).start()
         self.optimizer.reduce_grads()
         timers("all-grads-sync", 1).stop()
