@@ -18,6 +18,7 @@
 //
 // Replaces dot_product_attention.py:139-183 (baddbmm + softmax + bmm) and the flash_attn / TransformerEngine back ends
 // of the reference (llama3/transformer_legacy.py:446-505).
+#include <cstdio>
 #include "tcgen05_utils.cuh"
 
 namespace lmoe {
@@ -541,7 +542,7 @@ fa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
             for (int i = 0; i < CW; i += 2) {
                 const float p0 = exp2f(fmaf(__uint_as_float(sv[i]), sc, -lse2)), p1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -lse2));
-                pk[i >> 1] = pack_bf16(p0 * (__uint_as_float(dv[i]) - dl) * a.scale, p1 * (__uint_as_float(dv[i + 1]) - dl) * a.scale);
+                pk[i >> 1] = pack_bf16(p0 * (__uint_as_float(dv[i]) - dl), p1 * (__uint_as_float(dv[i + 1]) - dl));   // the softmax scale is applied to dQ at the end
             }
             if (j > 0 && !mbar_wait_suspend(&sm.acc_done, (j - 1) & 1, abort_flag, err, 0x4600)) { alive = false; break; }
             *reinterpret_cast<uint4*>(prow + (((part * 2) ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
@@ -564,10 +565,10 @@ fa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             bf16* og = a.dq + (((long long)b * a.Tq + row) * a.Hq + h) * D + part * OW;
 #pragma unroll
             for (int c = 0; c < OW; c += 8)
-                *reinterpret_cast<uint4*>(og + c) = make_uint4(pack_bf16(__uint_as_float(acc[c]), __uint_as_float(acc[c + 1])),
-                                                               pack_bf16(__uint_as_float(acc[c + 2]), __uint_as_float(acc[c + 3])),
-                                                               pack_bf16(__uint_as_float(acc[c + 4]), __uint_as_float(acc[c + 5])),
-                                                               pack_bf16(__uint_as_float(acc[c + 6]), __uint_as_float(acc[c + 7])));
+                *reinterpret_cast<uint4*>(og + c) = make_uint4(pack_bf16(a.scale * __uint_as_float(acc[c]), a.scale * __uint_as_float(acc[c + 1])),
+                                                               pack_bf16(a.scale * __uint_as_float(acc[c + 2]), a.scale * __uint_as_float(acc[c + 3])),
+                                                               pack_bf16(a.scale * __uint_as_float(acc[c + 4]), a.scale * __uint_as_float(acc[c + 5])),
+                                                               pack_bf16(a.scale * __uint_as_float(acc[c + 6]), a.scale * __uint_as_float(acc[c + 7])));
         }
     }
     tc_fence_before();
@@ -733,7 +734,7 @@ fa_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             for (int i = 0; i < CW; i += 2) {
                 const float p0 = exp2f(fmaf(__uint_as_float(sv[i]), sc, -l2[i])), p1 = exp2f(fmaf(__uint_as_float(sv[i + 1]), sc, -l2[i + 1]));
                 pk[i >> 1] = pack_bf16(p0, p1);
-                dk2[i >> 1] = pack_bf16(p0 * (__uint_as_float(dv[i]) - dl[i]) * a.scale, p1 * (__uint_as_float(dv[i + 1]) - dl[i + 1]) * a.scale);
+                dk2[i >> 1] = pack_bf16(p0 * (__uint_as_float(dv[i]) - dl[i]), p1 * (__uint_as_float(dv[i + 1]) - dl[i + 1]));   // scale applied to dK at the end
             }
             if (it > 0 && !mbar_wait_suspend(&sm.acc_done, (it - 1) & 1, abort_flag, err, 0x5600)) { alive = false; break; }
             const int c0 = ((part * 2) ^ (r & 7)) << 4, c1 = ((part * 2 + 1) ^ (r & 7)) << 4;
@@ -764,10 +765,10 @@ fa_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                                                                        pack_bf16(__uint_as_float(av[c + 2]), __uint_as_float(av[c + 3])),
                                                                        pack_bf16(__uint_as_float(av[c + 4]), __uint_as_float(av[c + 5])),
                                                                        pack_bf16(__uint_as_float(av[c + 6]), __uint_as_float(av[c + 7])));
-                *reinterpret_cast<uint4*>(a.dk + off + c) = make_uint4(pack_bf16(__uint_as_float(ak[c]), __uint_as_float(ak[c + 1])),
-                                                                       pack_bf16(__uint_as_float(ak[c + 2]), __uint_as_float(ak[c + 3])),
-                                                                       pack_bf16(__uint_as_float(ak[c + 4]), __uint_as_float(ak[c + 5])),
-                                                                       pack_bf16(__uint_as_float(ak[c + 6]), __uint_as_float(ak[c + 7])));
+                *reinterpret_cast<uint4*>(a.dk + off + c) = make_uint4(pack_bf16(a.scale * __uint_as_float(ak[c]), a.scale * __uint_as_float(ak[c + 1])),
+                                                                       pack_bf16(a.scale * __uint_as_float(ak[c + 2]), a.scale * __uint_as_float(ak[c + 3])),
+                                                                       pack_bf16(a.scale * __uint_as_float(ak[c + 4]), a.scale * __uint_as_float(ak[c + 5])),
+                                                                       pack_bf16(a.scale * __uint_as_float(ak[c + 6]), a.scale * __uint_as_float(ak[c + 7])));
             }
         }
     }
@@ -810,6 +811,9 @@ static int make_map_4d(CUtensorMap* map, const void* ptr, int B, int T, int H, i
     CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        fprintf(stderr, "flash_attn_tc: tensor map rejected (CUresult %d): ptr %p dims {%d,%d,%d,%d} strides {%lld,%lld,%lld} box_t %u\n",
+                (int)r, ptr, D, H, T, B, sh, st, sb, box_t);
     return r == CUDA_SUCCESS ? 0 : -11;
 }
 

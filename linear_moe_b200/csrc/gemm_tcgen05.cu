@@ -278,6 +278,10 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 static EncodeTiledFn get_encode() {
+    // the encoder is a driver call: it wants the primary context current on this thread (an autograd worker that has
+    // made no runtime call yet has none)
+    static thread_local bool bound = false;
+    if (!bound) { cudaFree(0); bound = true; }
     static EncodeTiledFn fn = nullptr;
     if (fn == nullptr) {
         void* p = nullptr;

@@ -86,7 +86,15 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+// The tensor-map encoder is a driver call and wants the device's primary context current on the calling thread.  A
+// thread that has made no runtime call yet (the autograd engine's worker when the first backward node is one of these
+// kernels) has none and the encoder answers CUDA_ERROR_INVALID_CONTEXT, so bind it once per thread.
+static void bind_context() {
+    static thread_local bool bound = false;
+    if (!bound) { cudaFree(0); bound = true; }
+}
 static EncodeTiledFn get_encode() {
+    bind_context();
     static EncodeTiledFn fn = nullptr;
     if (fn == nullptr) {
         void* p = nullptr;

@@ -335,3 +335,23 @@ def test_lsm_delta_rule_scan(gated, with_state):
     close(o, o2, 3e-2, 2e-2 * o2.abs().max().item(), "o")
     for name, a, b in zip(["dq", "dk", "dv", "dbeta", "dg/dS0", "dS0"], gk, gr):
         close(a, b, 5e-2, 3e-2 * b.abs().max().item(), name)
+
+
+@pytest.mark.gpu
+def test_flash_backward_first_node_of_fresh_process():
+    """In a fresh process the autograd worker thread has made no runtime call when the flash backward (whose tensor maps
+    are encoded by a driver call) is its first node: the kernel wrapper has to bind the context itself."""
+    import subprocess
+    import sys
+    code = ("import torch\n"
+            "from linear_moe_b200.ops import flash\n"
+            "q = torch.randn(1, 256, 4, 128, device='cuda').bfloat16().requires_grad_(True)\n"
+            "kv = torch.randn(1, 256, 2, 256, device='cuda').bfloat16().requires_grad_(True)\n"
+            "k, v = kv.split(128, dim=-1)\n"
+            "o = flash.FlashAttention.apply(q, k, v, 128 ** -0.5, 0, None)\n"
+            "o.backward(torch.ones_like(o))\n"
+            "torch.cuda.synchronize()\n"
+            "assert torch.isfinite(q.grad.float()).all() and torch.isfinite(kv.grad.float()).all()\n"
+            "print('ok')\n")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]
