@@ -99,6 +99,26 @@ __device__ __forceinline__ void fold_o(float (&o)[OW], uint32_t taddr, float cor
         o[i + 1] = r.y;
     }
 }
+// The MMA warp runs its loop with all 32 lanes converged and only predicates the tcgen05 instructions on one lane: inside a
+// single-lane branch every operand lives in vector registers and each MMA pays for moving two 64-bit descriptors into
+// uniform registers, which at 64-column tiles costs more cycles than the MMA keeps the tensor core busy.  Descriptors are
+// built once per tile as a 32-bit low word (address / 16 and the leading-dimension offset); the high word is a constant and
+// stepping along K inside the swizzled tile is an add to the low word.
+constexpr uint32_t DESC_HI = (1024u >> 4) | (1u << 14) | (2u << 29);      // stride offset 1024 B, version 1, 128-byte swizzle
+template <bool MN>
+__device__ __forceinline__ uint32_t desc_lo(uint32_t saddr) {
+    return ((saddr >> 4) & 0x3FFFu) | ((MN ? (8192u >> 4) : 1u) << 16);
+}
+__device__ __forceinline__ void umma_lo(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t idesc, uint32_t accumulate, uint32_t issue) {
+    asm volatile("{\n.reg .pred p, q;\n.reg .b64 da, db;\nsetp.ne.b32 p, %4, 0;\nsetp.ne.b32 q, %5, 0;\n"
+                 "mov.b64 da, {%1, %6};\nmov.b64 db, {%2, %6};\n"
+                 "@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n}"
+                 :: "r"(tmem_d), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate), "r"(issue), "r"(DESC_HI) : "memory");
+}
+__device__ __forceinline__ void umma_commit_if(uint64_t* bar, uint32_t issue) {
+    asm volatile("{\n.reg .pred q;\nsetp.ne.b32 q, %1, 0;\n"
+                 "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n}" :: "r"(s32(bar)), "r"(issue) : "memory");
+}
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float r;
     asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
@@ -189,7 +209,8 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
         }
     } else if (warp == 1) {
-        if (lane == 0 && n_it > 0) {
+        if (n_it > 0) {
+            const uint32_t issue = lane == 0 ? 1u : 0u;
             constexpr uint32_t idesc_s = idesc_bf16<false, BN>();
             constexpr uint32_t idesc_o = idesc_bf16<true, D>();
             bool ok = mbar_wait_suspend(&sm.q_full, 0, abort_flag, err, 0x2000);
@@ -197,14 +218,14 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 const int s = j & 1;
                 if (!mbar_wait_suspend(&sm.k_full[s], (j >> 1) & 1, abort_flag, err, 0x2100 | s)) return false;
                 tc_fence_after();
-                const uint32_t qa = s32(sm.q), ka = s32(sm.k[s]);
+                const uint32_t ql = desc_lo<false>(s32(sm.q)), kl = desc_lo<false>(s32(sm.k[s]));
 #pragma unroll
                 for (int kk = 0; kk < D / UMMA_K; ++kk) {
-                    const uint32_t off = (kk / 4) * (BM * 128) + (kk % 4) * 32;
-                    umma_f16(tmem_base + s * BN, make_desc<false>(qa + off), make_desc<false>(ka + off), idesc_s, kk > 0 ? 1u : 0u);
+                    const uint32_t off = ((kk / 4) * (BM * 128) + (kk % 4) * 32) >> 4;
+                    umma_lo(tmem_base + s * BN, ql + off, kl + off, idesc_s, kk > 0 ? 1u : 0u, issue);
                 }
-                umma_commit(&sm.k_empty[s]);
-                umma_commit(&sm.s_full[s]);
+                umma_commit_if(&sm.k_empty[s], issue);
+                umma_commit_if(&sm.s_full[s], issue);
                 return true;
             };
             if (ok) ok = issue_s(0);
@@ -214,15 +235,15 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 if (!mbar_wait_suspend(&sm.v_full[s], (j >> 1) & 1, abort_flag, err, 0x2200 | s)) break;
                 if (!mbar_wait_suspend(&sm.p_ready, j & 1, abort_flag, err, 0x2300)) break;
                 tc_fence_after();
-                const uint32_t pa = s32(sm.p), va = s32(sm.v[s]);
+                const uint32_t pl = desc_lo<false>(s32(sm.p)), vl = desc_lo<true>(s32(sm.v[s]));
 #pragma unroll
                 for (int kk = 0; kk < BN / UMMA_K; ++kk) {
-                    const uint32_t aoff = (kk / 4) * (BM * 128) + (kk % 4) * 32;
-                    const uint32_t boff = (kk / 4) * (DK * 8192) + (kk % 4) * 2048;
-                    umma_f16(tmem_base + O_COL + s * D, make_desc<false>(pa + aoff), make_desc<true>(va + boff), idesc_o, kk > 0 ? 1u : 0u);
+                    const uint32_t aoff = ((kk / 4) * (BM * 128) + (kk % 4) * 32) >> 4;
+                    const uint32_t boff = ((kk / 4) * (DK * 8192) + (kk % 4) * 2048) >> 4;
+                    umma_lo(tmem_base + O_COL + s * D, pl + aoff, vl + boff, idesc_o, kk > 0 ? 1u : 0u, issue);
                 }
-                umma_commit(&sm.v_empty[s]);
-                umma_commit(&sm.o_full[s]);
+                umma_commit_if(&sm.v_empty[s], issue);
+                umma_commit_if(&sm.o_full[s], issue);
             }
         }
     } else if (warp >= 4) {
@@ -378,8 +399,11 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 // and as an MN-major operand (rows = K) of the gradient GEMMs.  Same warp roles, barriers and bounded waits as the forward.
 // =====================================================================================================================
 constexpr int BT = 64;                                       // tile of the looped dimension (keys for dQ, queries for dK/dV)
-constexpr int NST = 3;                                       // TMA stages of the looped tiles: a stage is released only after the
-                                                             // gradient MMAs of its iteration, so two stages would expose the load latency
+constexpr int NKS = 5, NVS = 4;                              // dQ kernel: K stages (held until the dQ MMAs of their tile) and V
+                                                             // stages (released right after the dP MMAs)
+constexpr int NQS = 4;                                       // dK/dV kernel: stages of a Q tile + a dO tile (both held until the
+                                                             // gradient MMAs).  The load latency is exposed when a stage's lifetime
+                                                             // (load + scores + softmax + gradient MMAs) exceeds stages x tile period
 
 struct BwdArgs {
     const float* lse;     // [B, Hq, Tq] natural-log sum-exp from the forward
@@ -397,11 +421,10 @@ template <int D>
 struct __align__(1024) SmemBwd {
     uint8_t big0[BM * D * 2];          // dQ kernel: Q tile      | dK/dV kernel: K tile
     uint8_t big1[BM * D * 2];          // dQ kernel: dO tile     | dK/dV kernel: V tile
-    uint8_t st0[NST][BT * D * 2];        // dQ kernel: K stages    | dK/dV kernel: Q stages
-    uint8_t st1[NST][BT * D * 2];        // dQ kernel: V stages    | dK/dV kernel: dO stages
     uint8_t p[BM * BT * 2];            // dS (dQ kernel) | P^T (dK/dV kernel), K-major, 128 rows x 128 bytes
-    uint8_t ds[BM * BT * 2];           // dS^T (dK/dV kernel)
-    uint64_t big_full, st_full[NST], st_empty[NST], s_full[2], p_ready, acc_done;
+    uint8_t ds[BM * BT * 2];           // dS^T (dK/dV kernel) | fifth K stage (dQ kernel)
+    uint8_t arena[8][BT * D * 2];      // dQ kernel: K stages 0-3, V stages 4-7 | dK/dV kernel: (Q, dO) of stage i in 2i, 2i+1
+    uint64_t big_full, a_full[NKS], a_empty[NKS], b_full[NVS], b_empty[NVS], s_full[2], p_ready, acc_done;
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -433,7 +456,8 @@ fa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.big_full, 1);
-        for (int s = 0; s < NST; ++s) { mbar_init(&sm.st_full[s], 1); mbar_init(&sm.st_empty[s], 1); }
+        for (int s = 0; s < NKS; ++s) { mbar_init(&sm.a_full[s], 1); mbar_init(&sm.a_empty[s], 1); }
+        for (int s = 0; s < NVS; ++s) { mbar_init(&sm.b_full[s], 1); mbar_init(&sm.b_empty[s], 1); }
         for (int s = 0; s < 2; ++s) mbar_init(&sm.s_full[s], 1);
         mbar_init(&sm.p_ready, 4 * SPLIT);
         mbar_init(&sm.acc_done, 1);
@@ -458,53 +482,58 @@ fa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 tma_load_4d(sm.big1 + kb * BM * 128, &tmG, &sm.big_full, kb * 64, h, q0, b);
             }
             for (int j = 0; j < n_it; ++j) {
-                const int s = j % NST;
+                const int ks = j % NKS, vs = j % NVS;
                 const int key0 = (nb_lo + j) * BT;
-                if (!mbar_wait_suspend(&sm.st_empty[s], ((j / NST) & 1) ^ 1, abort_flag, err, 0x4100 | s)) break;
-                mbar_expect_tx(&sm.st_full[s], 2 * BT * D * 2);
+                uint8_t* kst = ks < 4 ? sm.arena[ks] : sm.ds;
+                if (!mbar_wait_suspend(&sm.a_empty[ks], ((j / NKS) & 1) ^ 1, abort_flag, err, 0x4100 | ks)) break;
+                mbar_expect_tx(&sm.a_full[ks], BT * D * 2);
 #pragma unroll
-                for (int kb = 0; kb < DK; ++kb) {
-                    tma_load_4d(sm.st0[s] + kb * 8192, &tmK, &sm.st_full[s], kb * 64, hk, key0, b);
-                    tma_load_4d(sm.st1[s] + kb * 8192, &tmV, &sm.st_full[s], kb * 64, hk, key0, b);
-                }
+                for (int kb = 0; kb < DK; ++kb) tma_load_4d(kst + kb * 8192, &tmK, &sm.a_full[ks], kb * 64, hk, key0, b);
+                if (!mbar_wait_suspend(&sm.b_empty[vs], ((j / NVS) & 1) ^ 1, abort_flag, err, 0x4180 | vs)) break;
+                mbar_expect_tx(&sm.b_full[vs], BT * D * 2);
+#pragma unroll
+                for (int kb = 0; kb < DK; ++kb) tma_load_4d(sm.arena[4 + vs] + kb * 8192, &tmV, &sm.b_full[vs], kb * 64, hk, key0, b);
             }
         }
     } else if (warp == 1) {
-        if (lane == 0 && n_it > 0) {
+        if (n_it > 0) {
+            const uint32_t issue = lane == 0 ? 1u : 0u;
             constexpr uint32_t idesc_s = idesc_bf16<false, BT>();       // [128 q] x [64 keys], both K-major
             constexpr uint32_t idesc_a = idesc_bf16<true, D>();         // dQ += dS K: B = K tile read MN-major
             bool ok = mbar_wait_suspend(&sm.big_full, 0, abort_flag, err, 0x4200);
             auto issue_sd = [&](int j) -> bool {
-                const int s = j & 1, g = j % NST;                    // tensor-memory buffer, shared-memory stage
-                if (!mbar_wait_suspend(&sm.st_full[g], (j / NST) & 1, abort_flag, err, 0x4300 | g)) return false;
+                const int s = j & 1, ks = j % NKS, vs = j % NVS;     // tensor-memory buffer, shared-memory stages
+                if (!mbar_wait_suspend(&sm.a_full[ks], (j / NKS) & 1, abort_flag, err, 0x4300 | ks)) return false;
+                if (!mbar_wait_suspend(&sm.b_full[vs], (j / NVS) & 1, abort_flag, err, 0x4380 | vs)) return false;
                 tc_fence_after();
-                const uint32_t qa = s32(sm.big0), ga = s32(sm.big1), ka = s32(sm.st0[g]), va = s32(sm.st1[g]);
+                const uint32_t ql = desc_lo<false>(s32(sm.big0)), gl = desc_lo<false>(s32(sm.big1));
+                const uint32_t kl = desc_lo<false>(s32(ks < 4 ? sm.arena[ks] : sm.ds)), vl = desc_lo<false>(s32(sm.arena[4 + vs]));
 #pragma unroll
                 for (int kk = 0; kk < D / UMMA_K; ++kk) {
-                    const uint32_t ao = (kk / 4) * (BM * 128) + (kk % 4) * 32, bo = (kk / 4) * 8192 + (kk % 4) * 32;
-                    umma_f16(tmem_base + s * 128, make_desc<false>(qa + ao), make_desc<false>(ka + bo), idesc_s, kk > 0 ? 1u : 0u);
+                    const uint32_t ao = ((kk / 4) * (BM * 128) + (kk % 4) * 32) >> 4, bo = ((kk / 4) * 8192 + (kk % 4) * 32) >> 4;
+                    umma_lo(tmem_base + s * 128, ql + ao, kl + bo, idesc_s, kk > 0 ? 1u : 0u, issue);
                 }
 #pragma unroll
                 for (int kk = 0; kk < D / UMMA_K; ++kk) {
-                    const uint32_t ao = (kk / 4) * (BM * 128) + (kk % 4) * 32, bo = (kk / 4) * 8192 + (kk % 4) * 32;
-                    umma_f16(tmem_base + s * 128 + 64, make_desc<false>(ga + ao), make_desc<false>(va + bo), idesc_s, kk > 0 ? 1u : 0u);
+                    const uint32_t ao = ((kk / 4) * (BM * 128) + (kk % 4) * 32) >> 4, bo = ((kk / 4) * 8192 + (kk % 4) * 32) >> 4;
+                    umma_lo(tmem_base + s * 128 + 64, gl + ao, vl + bo, idesc_s, kk > 0 ? 1u : 0u, issue);
                 }
-                umma_commit(&sm.s_full[s]);
+                umma_commit_if(&sm.b_empty[vs], issue);              // V is not needed again
+                umma_commit_if(&sm.s_full[s], issue);
                 return true;
             };
             if (ok) ok = issue_sd(0);
             for (int j = 0; ok && j < n_it; ++j) {
                 if (j + 1 < n_it) { ok = issue_sd(j + 1); if (!ok) break; }
-                const int s = j % NST;
+                const int ks = j % NKS;
                 if (!mbar_wait_suspend(&sm.p_ready, j & 1, abort_flag, err, 0x4400)) break;
                 tc_fence_after();
-                const uint32_t pa = s32(sm.p), ka = s32(sm.st0[s]);
+                const uint32_t pl = desc_lo<false>(s32(sm.p)), kl = desc_lo<true>(s32(ks < 4 ? sm.arena[ks] : sm.ds));
 #pragma unroll
                 for (int kk = 0; kk < BT / UMMA_K; ++kk)
-                    umma_f16(tmem_base + ACC_COL, make_desc<false>(pa + kk * 32), make_desc<true>(ka + kk * 2048), idesc_a,
-                             (j > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(&sm.st_empty[s]);
-                umma_commit(&sm.acc_done);
+                    umma_lo(tmem_base + ACC_COL, pl + kk * 2, kl + kk * 128, idesc_a, (j > 0 || kk > 0) ? 1u : 0u, issue);
+                umma_commit_if(&sm.a_empty[ks], issue);
+                umma_commit_if(&sm.acc_done, issue);
             }
         }
     } else if (warp >= 4) {
@@ -604,7 +633,8 @@ fa_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.big_full, 1);
-        for (int s = 0; s < NST; ++s) { mbar_init(&sm.st_full[s], 1); mbar_init(&sm.st_empty[s], 1); }
+        for (int s = 0; s < NKS; ++s) { mbar_init(&sm.a_full[s], 1); mbar_init(&sm.a_empty[s], 1); }
+        for (int s = 0; s < NVS; ++s) { mbar_init(&sm.b_full[s], 1); mbar_init(&sm.b_empty[s], 1); }
         for (int s = 0; s < 2; ++s) mbar_init(&sm.s_full[s], 1);
         mbar_init(&sm.p_ready, 4 * SPLIT);
         mbar_init(&sm.acc_done, 1);
@@ -629,57 +659,58 @@ fa_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                 tma_load_4d(sm.big1 + kb * BM * 128, &tmV, &sm.big_full, kb * 64, hk, k0, b);
             }
             for (int it = 0; it < n_it; ++it) {
-                const int s = it % NST;
+                const int s = it % NQS;
                 const int h = hk * rep + it / ni, q0 = (i_lo + it % ni) * BT;
-                if (!mbar_wait_suspend(&sm.st_empty[s], ((it / NST) & 1) ^ 1, abort_flag, err, 0x5100 | s)) break;
-                mbar_expect_tx(&sm.st_full[s], 2 * BT * D * 2);
+                if (!mbar_wait_suspend(&sm.a_empty[s], ((it / NQS) & 1) ^ 1, abort_flag, err, 0x5100 | s)) break;
+                mbar_expect_tx(&sm.a_full[s], 2 * BT * D * 2);
 #pragma unroll
                 for (int kb = 0; kb < DK; ++kb) {
-                    tma_load_4d(sm.st0[s] + kb * 8192, &tmQ, &sm.st_full[s], kb * 64, h, q0, b);
-                    tma_load_4d(sm.st1[s] + kb * 8192, &tmG, &sm.st_full[s], kb * 64, h, q0, b);
+                    tma_load_4d(sm.arena[2 * s] + kb * 8192, &tmQ, &sm.a_full[s], kb * 64, h, q0, b);
+                    tma_load_4d(sm.arena[2 * s + 1] + kb * 8192, &tmG, &sm.a_full[s], kb * 64, h, q0, b);
                 }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0 && n_it > 0) {
+        if (n_it > 0) {
+            const uint32_t issue = lane == 0 ? 1u : 0u;
             constexpr uint32_t idesc_s = idesc_bf16<false, BT>();       // [128 keys] x [64 queries], both K-major
             constexpr uint32_t idesc_a = idesc_bf16<true, D>();         // B = dO / Q tile read MN-major
             bool ok = mbar_wait_suspend(&sm.big_full, 0, abort_flag, err, 0x5200);
             auto issue_sd = [&](int it) -> bool {
-                const int s = it & 1, g = it % NST;                  // tensor-memory buffer, shared-memory stage
-                if (!mbar_wait_suspend(&sm.st_full[g], (it / NST) & 1, abort_flag, err, 0x5300 | g)) return false;
+                const int s = it & 1, g = it % NQS;                  // tensor-memory buffer, shared-memory stage
+                if (!mbar_wait_suspend(&sm.a_full[g], (it / NQS) & 1, abort_flag, err, 0x5300 | g)) return false;
                 tc_fence_after();
-                const uint32_t ka = s32(sm.big0), va = s32(sm.big1), qa = s32(sm.st0[g]), ga = s32(sm.st1[g]);
+                const uint32_t kl = desc_lo<false>(s32(sm.big0)), vl = desc_lo<false>(s32(sm.big1));
+                const uint32_t ql = desc_lo<false>(s32(sm.arena[2 * g])), gl = desc_lo<false>(s32(sm.arena[2 * g + 1]));
 #pragma unroll
                 for (int kk = 0; kk < D / UMMA_K; ++kk) {
-                    const uint32_t ao = (kk / 4) * (BM * 128) + (kk % 4) * 32, bo = (kk / 4) * 8192 + (kk % 4) * 32;
-                    umma_f16(tmem_base + s * 128, make_desc<false>(ka + ao), make_desc<false>(qa + bo), idesc_s, kk > 0 ? 1u : 0u);
+                    const uint32_t ao = ((kk / 4) * (BM * 128) + (kk % 4) * 32) >> 4, bo = ((kk / 4) * 8192 + (kk % 4) * 32) >> 4;
+                    umma_lo(tmem_base + s * 128, kl + ao, ql + bo, idesc_s, kk > 0 ? 1u : 0u, issue);
                 }
 #pragma unroll
                 for (int kk = 0; kk < D / UMMA_K; ++kk) {
-                    const uint32_t ao = (kk / 4) * (BM * 128) + (kk % 4) * 32, bo = (kk / 4) * 8192 + (kk % 4) * 32;
-                    umma_f16(tmem_base + s * 128 + 64, make_desc<false>(va + ao), make_desc<false>(ga + bo), idesc_s, kk > 0 ? 1u : 0u);
+                    const uint32_t ao = ((kk / 4) * (BM * 128) + (kk % 4) * 32) >> 4, bo = ((kk / 4) * 8192 + (kk % 4) * 32) >> 4;
+                    umma_lo(tmem_base + s * 128 + 64, vl + ao, gl + bo, idesc_s, kk > 0 ? 1u : 0u, issue);
                 }
-                umma_commit(&sm.s_full[s]);
+                umma_commit_if(&sm.s_full[s], issue);
                 return true;
             };
             if (ok) ok = issue_sd(0);
             for (int it = 0; ok && it < n_it; ++it) {
                 if (it + 1 < n_it) { ok = issue_sd(it + 1); if (!ok) break; }
-                const int s = it % NST;
+                const int s = it % NQS;
                 if (!mbar_wait_suspend(&sm.p_ready, it & 1, abort_flag, err, 0x5400)) break;
                 tc_fence_after();
-                const uint32_t pa = s32(sm.p), da = s32(sm.ds), qa = s32(sm.st0[s]), ga = s32(sm.st1[s]);
+                const uint32_t pl = desc_lo<false>(s32(sm.p)), dl_ = desc_lo<false>(s32(sm.ds));
+                const uint32_t ql = desc_lo<true>(s32(sm.arena[2 * s])), gl = desc_lo<true>(s32(sm.arena[2 * s + 1]));
 #pragma unroll
                 for (int kk = 0; kk < BT / UMMA_K; ++kk)        // dV += P^T dO
-                    umma_f16(tmem_base + DV_COL, make_desc<false>(pa + kk * 32), make_desc<true>(ga + kk * 2048), idesc_a,
-                             (it > 0 || kk > 0) ? 1u : 0u);
+                    umma_lo(tmem_base + DV_COL, pl + kk * 2, gl + kk * 128, idesc_a, (it > 0 || kk > 0) ? 1u : 0u, issue);
 #pragma unroll
                 for (int kk = 0; kk < BT / UMMA_K; ++kk)        // dK += dS^T Q
-                    umma_f16(tmem_base + DK_COL, make_desc<false>(da + kk * 32), make_desc<true>(qa + kk * 2048), idesc_a,
-                             (it > 0 || kk > 0) ? 1u : 0u);
-                umma_commit(&sm.st_empty[s]);
-                umma_commit(&sm.acc_done);
+                    umma_lo(tmem_base + DK_COL, dl_ + kk * 2, ql + kk * 128, idesc_a, (it > 0 || kk > 0) ? 1u : 0u, issue);
+                umma_commit_if(&sm.a_empty[s], issue);
+                umma_commit_if(&sm.acc_done, issue);
             }
         }
     } else if (warp >= 4) {
