@@ -399,11 +399,8 @@ fa_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 // and as an MN-major operand (rows = K) of the gradient GEMMs.  Same warp roles, barriers and bounded waits as the forward.
 // =====================================================================================================================
 constexpr int BT = 64;                                       // tile of the looped dimension (keys for dQ, queries for dK/dV)
-constexpr int NKS = 5, NVS = 4;                              // dQ kernel: K stages (held until the dQ MMAs of their tile) and V
-                                                             // stages (released right after the dP MMAs)
-constexpr int NQS = 4;                                       // dK/dV kernel: stages of a Q tile + a dO tile (both held until the
-                                                             // gradient MMAs).  The load latency is exposed when a stage's lifetime
-                                                             // (load + scores + softmax + gradient MMAs) exceeds stages x tile period
+constexpr int NST = 3;                                       // TMA stages of the looped tiles: a stage is released only after the
+                                                             // gradient MMAs of its iteration, so two stages would expose the load latency
 
 struct BwdArgs {
     const float* lse;     // [B, Hq, Tq] natural-log sum-exp from the forward
@@ -421,10 +418,11 @@ template <int D>
 struct __align__(1024) SmemBwd {
     uint8_t big0[BM * D * 2];          // dQ kernel: Q tile      | dK/dV kernel: K tile
     uint8_t big1[BM * D * 2];          // dQ kernel: dO tile     | dK/dV kernel: V tile
+    uint8_t st0[NST][BT * D * 2];        // dQ kernel: K stages    | dK/dV kernel: Q stages
+    uint8_t st1[NST][BT * D * 2];        // dQ kernel: V stages    | dK/dV kernel: dO stages
     uint8_t p[BM * BT * 2];            // dS (dQ kernel) | P^T (dK/dV kernel), K-major, 128 rows x 128 bytes
-    uint8_t ds[BM * BT * 2];           // dS^T (dK/dV kernel) | fifth K stage (dQ kernel)
-    uint8_t arena[8][BT * D * 2];      // dQ kernel: K stages 0-3, V stages 4-7 | dK/dV kernel: (Q, dO) of stage i in 2i, 2i+1
-    uint64_t big_full, a_full[NKS], a_empty[NKS], b_full[NVS], b_empty[NVS], s_full[2], p_ready, acc_done;
+    uint8_t ds[BM * BT * 2];           // dS^T (dK/dV kernel)
+    uint64_t big_full, st_full[NST], st_empty[NST], s_full[2], p_ready, acc_done;
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -456,8 +454,7 @@ fa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.big_full, 1);
-        for (int s = 0; s < NKS; ++s) { mbar_init(&sm.a_full[s], 1); mbar_init(&sm.a_empty[s], 1); }
-        for (int s = 0; s < NVS; ++s) { mbar_init(&sm.b_full[s], 1); mbar_init(&sm.b_empty[s], 1); }
+        for (int s = 0; s < NST; ++s) { mbar_init(&sm.st_full[s], 1); mbar_init(&sm.st_empty[s], 1); }
         for (int s = 0; s < 2; ++s) mbar_init(&sm.s_full[s], 1);
         mbar_init(&sm.p_ready, 4 * SPLIT);
         mbar_init(&sm.acc_done, 1);
@@ -482,17 +479,15 @@ fa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                 tma_load_4d(sm.big1 + kb * BM * 128, &tmG, &sm.big_full, kb * 64, h, q0, b);
             }
             for (int j = 0; j < n_it; ++j) {
-                const int ks = j % NKS, vs = j % NVS;
+                const int s = j % NST;
                 const int key0 = (nb_lo + j) * BT;
-                uint8_t* kst = ks < 4 ? sm.arena[ks] : sm.ds;
-                if (!mbar_wait_suspend(&sm.a_empty[ks], ((j / NKS) & 1) ^ 1, abort_flag, err, 0x4100 | ks)) break;
-                mbar_expect_tx(&sm.a_full[ks], BT * D * 2);
+                if (!mbar_wait_suspend(&sm.st_empty[s], ((j / NST) & 1) ^ 1, abort_flag, err, 0x4100 | s)) break;
+                mbar_expect_tx(&sm.st_full[s], 2 * BT * D * 2);
 #pragma unroll
-                for (int kb = 0; kb < DK; ++kb) tma_load_4d(kst + kb * 8192, &tmK, &sm.a_full[ks], kb * 64, hk, key0, b);
-                if (!mbar_wait_suspend(&sm.b_empty[vs], ((j / NVS) & 1) ^ 1, abort_flag, err, 0x4180 | vs)) break;
-                mbar_expect_tx(&sm.b_full[vs], BT * D * 2);
-#pragma unroll
-                for (int kb = 0; kb < DK; ++kb) tma_load_4d(sm.arena[4 + vs] + kb * 8192, &tmV, &sm.b_full[vs], kb * 64, hk, key0, b);
+                for (int kb = 0; kb < DK; ++kb) {
+                    tma_load_4d(sm.st0[s] + kb * 8192, &tmK, &sm.st_full[s], kb * 64, hk, key0, b);
+                    tma_load_4d(sm.st1[s] + kb * 8192, &tmV, &sm.st_full[s], kb * 64, hk, key0, b);
+                }
             }
         }
     } else if (warp == 1) {
@@ -502,12 +497,11 @@ fa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             constexpr uint32_t idesc_a = idesc_bf16<true, D>();         // dQ += dS K: B = K tile read MN-major
             bool ok = mbar_wait_suspend(&sm.big_full, 0, abort_flag, err, 0x4200);
             auto issue_sd = [&](int j) -> bool {
-                const int s = j & 1, ks = j % NKS, vs = j % NVS;     // tensor-memory buffer, shared-memory stages
-                if (!mbar_wait_suspend(&sm.a_full[ks], (j / NKS) & 1, abort_flag, err, 0x4300 | ks)) return false;
-                if (!mbar_wait_suspend(&sm.b_full[vs], (j / NVS) & 1, abort_flag, err, 0x4380 | vs)) return false;
+                const int s = j & 1, g = j % NST;                    // tensor-memory buffer, shared-memory stage
+                if (!mbar_wait_suspend(&sm.st_full[g], (j / NST) & 1, abort_flag, err, 0x4300 | g)) return false;
                 tc_fence_after();
                 const uint32_t ql = desc_lo<false>(s32(sm.big0)), gl = desc_lo<false>(s32(sm.big1));
-                const uint32_t kl = desc_lo<false>(s32(ks < 4 ? sm.arena[ks] : sm.ds)), vl = desc_lo<false>(s32(sm.arena[4 + vs]));
+                const uint32_t kl = desc_lo<false>(s32(sm.st0[g])), vl = desc_lo<false>(s32(sm.st1[g]));
 #pragma unroll
                 for (int kk = 0; kk < D / UMMA_K; ++kk) {
                     const uint32_t ao = ((kk / 4) * (BM * 128) + (kk % 4) * 32) >> 4, bo = ((kk / 4) * 8192 + (kk % 4) * 32) >> 4;
@@ -518,21 +512,20 @@ fa_bwd_dq_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     const uint32_t ao = ((kk / 4) * (BM * 128) + (kk % 4) * 32) >> 4, bo = ((kk / 4) * 8192 + (kk % 4) * 32) >> 4;
                     umma_lo(tmem_base + s * 128 + 64, gl + ao, vl + bo, idesc_s, kk > 0 ? 1u : 0u, issue);
                 }
-                umma_commit_if(&sm.b_empty[vs], issue);              // V is not needed again
                 umma_commit_if(&sm.s_full[s], issue);
                 return true;
             };
             if (ok) ok = issue_sd(0);
             for (int j = 0; ok && j < n_it; ++j) {
                 if (j + 1 < n_it) { ok = issue_sd(j + 1); if (!ok) break; }
-                const int ks = j % NKS;
+                const int s = j % NST;
                 if (!mbar_wait_suspend(&sm.p_ready, j & 1, abort_flag, err, 0x4400)) break;
                 tc_fence_after();
-                const uint32_t pl = desc_lo<false>(s32(sm.p)), kl = desc_lo<true>(s32(ks < 4 ? sm.arena[ks] : sm.ds));
+                const uint32_t pl = desc_lo<false>(s32(sm.p)), kl = desc_lo<true>(s32(sm.st0[s]));
 #pragma unroll
                 for (int kk = 0; kk < BT / UMMA_K; ++kk)
                     umma_lo(tmem_base + ACC_COL, pl + kk * 2, kl + kk * 128, idesc_a, (j > 0 || kk > 0) ? 1u : 0u, issue);
-                umma_commit_if(&sm.a_empty[ks], issue);
+                umma_commit_if(&sm.st_empty[s], issue);
                 umma_commit_if(&sm.acc_done, issue);
             }
         }
@@ -633,8 +626,7 @@ fa_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.big_full, 1);
-        for (int s = 0; s < NKS; ++s) { mbar_init(&sm.a_full[s], 1); mbar_init(&sm.a_empty[s], 1); }
-        for (int s = 0; s < NVS; ++s) { mbar_init(&sm.b_full[s], 1); mbar_init(&sm.b_empty[s], 1); }
+        for (int s = 0; s < NST; ++s) { mbar_init(&sm.st_full[s], 1); mbar_init(&sm.st_empty[s], 1); }
         for (int s = 0; s < 2; ++s) mbar_init(&sm.s_full[s], 1);
         mbar_init(&sm.p_ready, 4 * SPLIT);
         mbar_init(&sm.acc_done, 1);
@@ -659,14 +651,14 @@ fa_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
                 tma_load_4d(sm.big1 + kb * BM * 128, &tmV, &sm.big_full, kb * 64, hk, k0, b);
             }
             for (int it = 0; it < n_it; ++it) {
-                const int s = it % NQS;
+                const int s = it % NST;
                 const int h = hk * rep + it / ni, q0 = (i_lo + it % ni) * BT;
-                if (!mbar_wait_suspend(&sm.a_empty[s], ((it / NQS) & 1) ^ 1, abort_flag, err, 0x5100 | s)) break;
-                mbar_expect_tx(&sm.a_full[s], 2 * BT * D * 2);
+                if (!mbar_wait_suspend(&sm.st_empty[s], ((it / NST) & 1) ^ 1, abort_flag, err, 0x5100 | s)) break;
+                mbar_expect_tx(&sm.st_full[s], 2 * BT * D * 2);
 #pragma unroll
                 for (int kb = 0; kb < DK; ++kb) {
-                    tma_load_4d(sm.arena[2 * s] + kb * 8192, &tmQ, &sm.a_full[s], kb * 64, h, q0, b);
-                    tma_load_4d(sm.arena[2 * s + 1] + kb * 8192, &tmG, &sm.a_full[s], kb * 64, h, q0, b);
+                    tma_load_4d(sm.st0[s] + kb * 8192, &tmQ, &sm.st_full[s], kb * 64, h, q0, b);
+                    tma_load_4d(sm.st1[s] + kb * 8192, &tmG, &sm.st_full[s], kb * 64, h, q0, b);
                 }
             }
         }
@@ -677,11 +669,11 @@ fa_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             constexpr uint32_t idesc_a = idesc_bf16<true, D>();         // B = dO / Q tile read MN-major
             bool ok = mbar_wait_suspend(&sm.big_full, 0, abort_flag, err, 0x5200);
             auto issue_sd = [&](int it) -> bool {
-                const int s = it & 1, g = it % NQS;                  // tensor-memory buffer, shared-memory stage
-                if (!mbar_wait_suspend(&sm.a_full[g], (it / NQS) & 1, abort_flag, err, 0x5300 | g)) return false;
+                const int s = it & 1, g = it % NST;                  // tensor-memory buffer, shared-memory stage
+                if (!mbar_wait_suspend(&sm.st_full[g], (it / NST) & 1, abort_flag, err, 0x5300 | g)) return false;
                 tc_fence_after();
                 const uint32_t kl = desc_lo<false>(s32(sm.big0)), vl = desc_lo<false>(s32(sm.big1));
-                const uint32_t ql = desc_lo<false>(s32(sm.arena[2 * g])), gl = desc_lo<false>(s32(sm.arena[2 * g + 1]));
+                const uint32_t ql = desc_lo<false>(s32(sm.st0[g])), gl = desc_lo<false>(s32(sm.st1[g]));
 #pragma unroll
                 for (int kk = 0; kk < D / UMMA_K; ++kk) {
                     const uint32_t ao = ((kk / 4) * (BM * 128) + (kk % 4) * 32) >> 4, bo = ((kk / 4) * 8192 + (kk % 4) * 32) >> 4;
@@ -698,18 +690,18 @@ fa_bwd_dkv_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
             if (ok) ok = issue_sd(0);
             for (int it = 0; ok && it < n_it; ++it) {
                 if (it + 1 < n_it) { ok = issue_sd(it + 1); if (!ok) break; }
-                const int s = it % NQS;
+                const int s = it % NST;
                 if (!mbar_wait_suspend(&sm.p_ready, it & 1, abort_flag, err, 0x5400)) break;
                 tc_fence_after();
                 const uint32_t pl = desc_lo<false>(s32(sm.p)), dl_ = desc_lo<false>(s32(sm.ds));
-                const uint32_t ql = desc_lo<true>(s32(sm.arena[2 * s])), gl = desc_lo<true>(s32(sm.arena[2 * s + 1]));
+                const uint32_t ql = desc_lo<true>(s32(sm.st0[s])), gl = desc_lo<true>(s32(sm.st1[s]));
 #pragma unroll
                 for (int kk = 0; kk < BT / UMMA_K; ++kk)        // dV += P^T dO
                     umma_lo(tmem_base + DV_COL, pl + kk * 2, gl + kk * 128, idesc_a, (it > 0 || kk > 0) ? 1u : 0u, issue);
 #pragma unroll
                 for (int kk = 0; kk < BT / UMMA_K; ++kk)        // dK += dS^T Q
                     umma_lo(tmem_base + DK_COL, dl_ + kk * 2, ql + kk * 128, idesc_a, (it > 0 || kk > 0) ? 1u : 0u, issue);
-                umma_commit_if(&sm.a_empty[s], issue);
+                umma_commit_if(&sm.st_empty[s], issue);
                 umma_commit_if(&sm.acc_done, issue);
             }
         }
