@@ -115,3 +115,32 @@ def test_offload_model_gpu():
         if offl:
             assert m.offload.stats["packed"] > 0
     assert abs(losses[0][0] - losses[1][0]) < 1e-6 and abs(losses[0][1] - losses[1][1]) <= 1e-3 * max(losses[0][1], 1e-6)
+
+
+def test_offload_flags_reach_the_model():
+    """``--cpu-offloading --cpu-offloading-num-layers N`` (the reference's TransformerEngine offload flags) build a model
+    whose first N blocks run under the offload context; training-mode forward + backward on CPU leaves gradients equal
+    to the plain model's."""
+    from linear_moe_b200.config.arguments import build_parser, configs_from_args
+    from linear_moe_b200.models.transformer import CausalLM
+    base = ["--num-layers", "2", "--hidden-size", "64", "--num-attention-heads", "2", "--ffn-hidden-size", "128",
+            "--seq-length", "64", "--max-position-embeddings", "64", "--micro-batch-size", "1", "--global-batch-size", "1",
+            "--la-module", "gla", "--layer-type-list", "LL", "--vocab-size", "128"]
+    grads = []
+    for extra in ([], ["--cpu-offloading", "--cpu-offloading-num-layers", "1"]):
+        args = build_parser().parse_args(base + extra)
+        cfg, _, _ = configs_from_args(args)
+        assert cfg.cpu_offloading == bool(extra)
+        torch.manual_seed(0)
+        m = CausalLM(cfg).float().train()
+        if extra:
+            assert m.offload is not None and m.offload.num_layers == 1
+            m.offload.min_bytes, m.offload.offload_cpu_tensors = 0, True
+        ids = torch.randint(0, 128, (1, 64), generator=torch.Generator().manual_seed(1))
+        m(ids, labels=ids).float().mean().backward()
+        if extra:
+            assert m.offload.stats["packed"] > 0
+        grads.append([p.grad.clone() for p in m.parameters() if p.grad is not None])
+    assert len(grads[0]) == len(grads[1])
+    for a, b in zip(*grads):
+        torch.testing.assert_close(a, b, rtol=0, atol=0)
