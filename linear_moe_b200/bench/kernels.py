@@ -1,6 +1,6 @@
 """Per-kernel timing and roofline harness.
 
-  python -m linear_moe_b200.bench.kernels [--kernel all|gemm|lsm|flash|families|moe|norm|headnorm|swiglu|ce|adam|conv] [--size small|full]
+  python -m linear_moe_b200.bench.kernels [--kernel all|gemm|lsm|flash|families|moe|decode|norm|headnorm|swiglu|ce|adam|conv] [--size small|full]
 
 Each kernel is timed with CUDA events on the launching stream after warm-up, with an L2 flush (a 256 MiB write)
 between iterations; the median is reported together with the algorithmic bytes / FLOPs and the fraction of the
@@ -248,6 +248,35 @@ def bench_moe(size):
     fused_comm.check_status("bench")
 
 
+def bench_decode(size):
+    """One-token decode steps of the LASP-2 Linear-Llama3-1B preset (all layers lightning attention, O(1) state):
+    eager launches against replay of the captured CUDA graph.  The floor is reading the bf16 weights once per token."""
+    from ..config.presets import get_preset
+    from ..infer.generation import GraphedDecodeStep
+    from ..models.transformer import CausalLM
+    dev = torch.device("cuda", 0)
+    cfg = get_preset("bench-lasp2-llama3-1b")
+    if size == "small":
+        cfg.num_layers = 4
+        cfg.layer_type_list = "LLLL"
+    model = CausalLM(cfg, device=dev).to(dev).eval()
+    weight_bytes = sum(p.numel() * p.element_size() for n, p in model.named_parameters() if "word_embeddings" not in n)
+    B = 8
+    with torch.no_grad():
+        caches = model.new_cache()
+        model(torch.randint(0, cfg.vocab_size, (B, 64), device=dev), caches=caches)
+        tok = torch.randint(0, cfg.vocab_size, (B, 1), device=dev)
+        for _ in range(3):
+            model(tok, caches=caches, position_offset=0)
+        t_eager = timeit(lambda: model(tok, caches=caches, position_offset=0))
+        step = GraphedDecodeStep(model, caches, B, dev)
+        step(tok)
+        t_graph = timeit(lambda: step(tok))
+    for name, t in (("eager", t_eager), ("CUDA graph", t_graph)):
+        report(f"decode step, batch {B}, {cfg.num_layers} layers, {name}", t, bytes_=weight_bytes)
+    print(f"  tokens/s: eager {B / t_eager * 1e3:.0f}, graph {B / t_graph * 1e3:.0f}")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--kernel", default="all")
@@ -265,6 +294,8 @@ def main():
         bench_lsm_families(a.size)
     if a.kernel in ("moe", "all"):
         bench_moe(a.size)
+    if a.kernel in ("decode", "all"):
+        bench_decode(a.size)
     if a.kernel in ("norm", "headnorm", "swiglu", "ce", "adam", "conv", "all"):
         bench_elementwise(a.kernel, a.size)
 

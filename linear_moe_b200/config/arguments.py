@@ -231,6 +231,8 @@ def build_parser() -> argparse.ArgumentParser:
     _flag(g, "--recompute-granularity", type=str, default=None, choices=["full", "selective"])
     _flag(g, "--recompute-method", type=str, default=None, choices=["uniform", "block"])
     _flag(g, "--recompute-num-layers", type=int, default=1)
+    _flag(g, "--cuda-graph-decode", action="store_true",
+          help="generation: replay one-token steps from a CUDA graph (models with fixed-size caches)")
     _flag(g, "--cpu-offloading", action="store_true")
     _flag(g, "--cpu-offloading-num-layers", type=int, default=0)
     _flag(g, "--train-mode", type=str, default="pretrain", choices=["pretrain", "finetune"])

@@ -88,13 +88,57 @@ def score_tokens(model, tokens: torch.Tensor) -> torch.Tensor:
     return torch.gather(lp, 2, tokens[:, 1:, None]).squeeze(-1)
 
 
+class GraphedDecodeStep:
+    """One-token decode step replayed from a CUDA graph.
+
+    A decode step of a linear-sequence model is a few hundred small launches (norms, projections of one token, state
+    updates) that the host cannot issue as fast as the GPU runs them.  Models whose every cache entry has a fixed size
+    (all mixers linear sequence models or Mamba2: O(1) recurrent state, no growing KV cache) make the step static, so it
+    is captured once and replayed: the token is copied into a static buffer, the graph runs the whole forward, and the
+    new states are copied back over the state buffers the graph reads.  Softmax-attention layers (KV cache grows by one
+    row per token) are not supported and fall back to eager decoding."""
+
+    def __init__(self, model, caches: List[dict], batch: int, device):
+        self.model, self.caches = model, caches
+        self.tok = torch.zeros(batch, 1, dtype=torch.long, device=device)
+        self.graph: Optional["torch.cuda.CUDAGraph"] = None
+        self.logits: Optional[torch.Tensor] = None
+
+    @staticmethod
+    def supported(model, caches: List[dict], device) -> bool:
+        if device.type != "cuda" or model.mesh.world_size != 1 or not caches:
+            return False
+        if any(s.mixer in ("attn", "mla") for s in model.specs):              # KV caches grow with every token
+            return False
+        return all(all(torch.is_tensor(v) for v in c.values()) for c in caches)   # nested caches (MoM) decode eagerly
+
+    def _capture(self):
+        static = [dict(c) for c in self.caches]                # the state tensors the graph will read and update
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = self.model(self.tok, caches=self.caches, position_offset=0)
+            for c, st in zip(self.caches, static):            # forward rebinds every entry to a new tensor
+                for k, v in st.items():
+                    v.copy_(c[k])
+                    c[k] = v
+
+    def __call__(self, tok: torch.Tensor) -> torch.Tensor:
+        self.tok.copy_(tok)
+        if self.graph is None:
+            self._capture()                                    # capturing records the step without running it
+        self.graph.replay()
+        return self.logits
+
+
 @torch.no_grad()
 def generate_tokens(model, tokens: torch.Tensor, lengths: torch.Tensor, *, eod: Optional[int] = None, top_k: int = 0,
                     top_p: float = 0.0, temperature: float = 1.0, repetition_penalty: float = 1.0,
                     return_log_probs: bool = False, use_eod_for_early_termination: bool = True,
-                    stop_on_double_eol: bool = False, stop_on_eol: bool = False, generator=None
-                    ) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
-    """Fill ``tokens [B, L]`` from the shortest prompt length to L.  Returns (tokens, generated lengths, log-probs)."""
+                    stop_on_double_eol: bool = False, stop_on_eol: bool = False, generator=None,
+                    cuda_graph: bool = False) -> Tuple[torch.Tensor, torch.Tensor, Optional[torch.Tensor]]:
+    """Fill ``tokens [B, L]`` from the shortest prompt length to L.  Returns (tokens, generated lengths, log-probs).
+    ``cuda_graph``: replay the one-token steps from a CUDA graph (``GraphedDecodeStep``) when the model allows it; the
+    prefill and the first two one-token steps run eagerly (they also serve as the warm-up before the capture)."""
     model.eval()
     B, L = tokens.shape
     min_len = int(lengths.min())
@@ -103,8 +147,18 @@ def generate_tokens(model, tokens: torch.Tensor, lengths: torch.Tensor, *, eod: 
     gen_len = torch.full((B,), L, dtype=torch.long, device=tokens.device)
     logps = torch.zeros(B, L - 1, dtype=torch.float32, device=tokens.device) if return_log_probs else None
     prev = 0
+    graphed, single_steps = None, 0
     for ctx in range(min_len, L):
-        logits = model(tokens[:, prev:ctx], caches=caches, position_offset=prev)       # prefill once, then 1 token
+        if ctx - prev == 1:
+            single_steps += 1
+        if cuda_graph and ctx - prev == 1 and single_steps > 2:
+            if graphed is None and GraphedDecodeStep.supported(model, caches, tokens.device):
+                graphed = GraphedDecodeStep(model, caches, B, tokens.device)
+            cuda_graph = graphed is not None
+        if graphed is not None and ctx - prev == 1:
+            logits = graphed(tokens[:, prev:ctx])
+        else:
+            logits = model(tokens[:, prev:ctx], caches=caches, position_offset=prev)   # prefill once, then 1 token
         last = logits[:, -1].float()
         last = apply_repetition_penalty(last, tokens[:, :ctx], repetition_penalty)
         new = sample(last, top_k, top_p, temperature, model.cfg.vocab_size, generator)
@@ -191,7 +245,8 @@ def beam_search(model, prompt: torch.Tensor, beam_size: int, max_new_tokens: int
 def generate_and_post_process(model, tokenizer, prompts: Sequence[str], tokens_to_generate: int = 64, *,
                               return_output_log_probs: bool = False, top_k_sampling: int = 0, top_p_sampling: float = 0.0,
                               temperature: float = 1.0, add_BOS: bool = False, use_eod_token_for_early_termination: bool = True,
-                              repetition_penalty: float = 1.0, random_seed: int = -1, device=None):
+                              repetition_penalty: float = 1.0, random_seed: int = -1, device=None,
+                              cuda_graph: bool = False):
     """Strings in, strings out (api.py:25-111): returns (texts, token lists, log-probs or None)."""
     device = device or next(model.parameters()).device
     gen = None
@@ -204,7 +259,8 @@ def generate_and_post_process(model, tokenizer, prompts: Sequence[str], tokens_t
     tokens, gen_len, lp = generate_tokens(model, tokens, lengths, eod=getattr(tokenizer, "eod", None), top_k=top_k_sampling,
                                           top_p=top_p_sampling, temperature=temperature,
                                           repetition_penalty=repetition_penalty, return_log_probs=return_output_log_probs,
-                                          use_eod_for_early_termination=use_eod_token_for_early_termination, generator=gen)
+                                          use_eod_for_early_termination=use_eod_token_for_early_termination, generator=gen,
+                                          cuda_graph=cuda_graph)
     out_tokens = [tokens[i, : int(gen_len[i])].tolist() for i in range(tokens.shape[0])]
     texts = [tokenizer.decode(t) for t in out_tokens]
     return texts, out_tokens, lp
@@ -232,7 +288,8 @@ class GPTPredictor:
         for p in prompts:
             texts, _, _ = generate_and_post_process(self.model, self.tok, [p], tokens_to_generate=a.out_seq_length,
                                                     top_k_sampling=a.top_k, top_p_sampling=a.top_p,
-                                                    temperature=a.temperature, repetition_penalty=a.repetition_penalty)
+                                                    temperature=a.temperature, repetition_penalty=a.repetition_penalty,
+                                                    cuda_graph=getattr(a, "cuda_graph_decode", False))
             outs.append(texts[0])
         if a.text_generate_output_file:
             with open(a.text_generate_output_file, "a", encoding="utf-8") as f:

@@ -135,3 +135,35 @@ def test_gpu_incremental_decoding_matches_full_forward(name):
     # the argmax (greedy token) agrees almost everywhere
     agree = (full.argmax(-1) == inc.argmax(-1)).float().mean().item()
     assert agree > 0.9, agree
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("la", ["gla", "lightning_attention", "gated_deltanet"])
+def test_cuda_graph_decode_matches_eager(la):
+    """Greedy decoding with the one-token steps replayed from a CUDA graph gives the tokens and log-probs of eager
+    decoding; a model with a softmax-attention layer (growing KV cache) silently decodes eagerly."""
+    from linear_moe_b200.infer.generation import GraphedDecodeStep, generate_tokens
+    torch.manual_seed(0)
+    cfg = ModelConfig(num_layers=2, hidden_size=256, num_attention_heads=2, ffn_hidden_size=512, vocab_size=512,
+                      use_la_module=True, la_module=la, layer_type_list="LL", params_dtype=torch.bfloat16)
+    m = CausalLM(cfg, device="cuda").cuda().eval()
+    B, P, L = 2, 12, 40
+    base = torch.zeros(B, L, dtype=torch.long, device="cuda")
+    base[:, :P] = torch.randint(0, 512, (B, P), device="cuda")
+    lengths = torch.full((B,), P, dtype=torch.long, device="cuda")
+    t0, _, lp0 = generate_tokens(m, base.clone(), lengths, top_k=1, return_log_probs=True)
+    t1, _, lp1 = generate_tokens(m, base.clone(), lengths, top_k=1, return_log_probs=True, cuda_graph=True)
+    assert torch.equal(t0, t1)
+    assert torch.allclose(lp0, lp1, atol=2e-2)
+    caches = m.new_cache()
+    m(base[:, :P], caches=caches)
+    assert GraphedDecodeStep.supported(m, caches, base.device)
+    cfg2 = ModelConfig(num_layers=2, hidden_size=256, num_attention_heads=2, ffn_hidden_size=512, vocab_size=512,
+                       use_la_module=True, la_module=la, layer_type_list="LN", params_dtype=torch.bfloat16)
+    m2 = CausalLM(cfg2, device="cuda").cuda().eval()
+    c2 = m2.new_cache()
+    m2(base[:, :P], caches=c2)
+    assert not GraphedDecodeStep.supported(m2, c2, base.device)
+    a, _, _ = generate_tokens(m2, base.clone(), lengths, top_k=1)
+    b, _, _ = generate_tokens(m2, base.clone(), lengths, top_k=1, cuda_graph=True)
+    assert torch.equal(a, b)

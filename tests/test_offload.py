@@ -104,7 +104,8 @@ def test_offload_model_gpu():
     for offl in (False, True):
         torch.manual_seed(0)
         cfg = ModelConfig(num_layers=2, hidden_size=256, num_attention_heads=2, ffn_hidden_size=512, vocab_size=512,
-                          la_module="gla", layer_type_list="LL", params_dtype=torch.bfloat16, cpu_offloading=offl,
+                          use_la_module=True, la_module="gla", layer_type_list="LL", params_dtype=torch.bfloat16,
+                          cpu_offloading=offl,
                           cpu_offloading_num_layers=1)
         m = CausalLM(cfg, device="cuda").cuda().train()
         ids = torch.randint(0, 512, (2, 2048), device="cuda")
@@ -125,7 +126,7 @@ def test_offload_flags_reach_the_model():
     from linear_moe_b200.models.transformer import CausalLM
     base = ["--num-layers", "2", "--hidden-size", "64", "--num-attention-heads", "2", "--ffn-hidden-size", "128",
             "--seq-length", "64", "--max-position-embeddings", "64", "--micro-batch-size", "1", "--global-batch-size", "1",
-            "--la-module", "gla", "--layer-type-list", "LL", "--vocab-size", "128"]
+            "--use-la-module", "--la-module", "gla", "--layer-type-list", "LL", "--vocab-size", "128"]
     grads = []
     for extra in ([], ["--cpu-offloading", "--cpu-offloading-num-layers", "1"]):
         args = build_parser().parse_args(base + extra)
