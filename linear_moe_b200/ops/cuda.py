@@ -733,10 +733,30 @@ def lsm_scalar(q, k, v, g, scale, initial_state, chunk_size):
     if not ok:
         return LT.chunk_scalar_gated(q, k, v, g, scale, initial_state, chunk_size)
     scale = D ** -0.5 if scale is None else scale
+    if q.shape[1] == 1 and _LASP_CTX is None and not (torch.is_grad_enabled() and
+                                                      any(t.requires_grad for t in (q, k, v) if t is not None)):
+        return _lsm_scalar_step(q, k, v, g, scale, initial_state)
     base = _fused_base(q, k, v)
     if base is not None:
         return _LsmScalarFused.apply(base, g, scale, initial_state)
     return _LsmScalar.apply(q, k, v, g, scale, initial_state)
+
+
+def _lsm_scalar_step(q, k, v, g, scale, initial_state):
+    """Decoding: one token per sequence, S' = e^g S + k^T v, o = scale q S' in one launch (csrc/lsm_step.cu)."""
+    B, _, H, D = q.shape
+    q, k, v = (t if t.stride(-1) == 1 else t.contiguous() for t in (q, k, v))
+    gf = None
+    if g is not None:
+        gf = (g.float().expand(B, H) if g.dim() == 1 else g.float().reshape(B, H)).contiguous()
+    s_in = None if initial_state is None else initial_state.float().contiguous()
+    s_out = torch.empty(B, H, D, D, dtype=torch.float32, device=q.device)
+    o = torch.empty(B, 1, H, D, dtype=q.dtype, device=q.device)
+    ll = ctypes.c_longlong
+    _check(lib().lmoe_lsm_scalar_step(_p(q), _p(k), _p(v), ll(q.stride(0)), ll(q.stride(2)), ll(k.stride(0)), ll(k.stride(2)),
+                                      ll(v.stride(0)), ll(v.stride(2)), _p(gf), _p(s_in), _p(s_out), _p(o), ctypes.c_int(B),
+                                      ctypes.c_int(H), ctypes.c_int(D), ctypes.c_float(scale), _st()), "lsm_scalar_step")
+    return o, s_out
 
 
 class _GlaArgs(ctypes.Structure):

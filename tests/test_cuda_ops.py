@@ -355,3 +355,28 @@ def test_flash_backward_first_node_of_fresh_process():
             "print('ok')\n")
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and "ok" in r.stdout, r.stderr[-2000:]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("gmode", ["none", "per_head", "per_token"])
+@pytest.mark.parametrize("with_state", [False, True])
+def test_lsm_scalar_decode_step(D, gmode, with_state):
+    """One-token step kernel against the recurrence: S' = e^g S + k^T v, o = scale q S'."""
+    from linear_moe_b200.ops import cuda as K
+    from linear_moe_b200.ref.lsm import recurrent_lsm
+    torch.manual_seed(0)
+    B, H = 3, 5
+    dev = "cuda"
+    qkv = (0.5 * torch.randn(B, 1, H, 3 * D, device=dev)).bfloat16()
+    q, k, v = qkv.split(D, dim=-1)                                  # strided views, as the fused projection gives them
+    g = {"none": None, "per_head": -torch.rand(H, device=dev),
+         "per_token": -torch.rand(B, 1, H, device=dev)}[gmode]
+    S0 = torch.randn(B, H, D, D, device=dev) if with_state else None
+    with torch.no_grad():
+        o, S = K.lsm_scalar(q, k, v, g, None, S0, 64)
+    g_ref = None if g is None else (g[None, None, :].expand(B, 1, H) if g.dim() == 1 else g)
+    o_ref, S_ref = recurrent_lsm(q.float(), k.float(), v.float(), g=g_ref, initial_state=S0)
+    assert o.shape == (B, 1, H, D) and S.shape == (B, H, D, D)
+    assert torch.allclose(S, S_ref, atol=1e-4, rtol=1e-4), (S - S_ref).abs().max()
+    assert torch.allclose(o.float(), o_ref, atol=3e-2, rtol=2e-2), (o.float() - o_ref).abs().max()
