@@ -735,26 +735,28 @@ def lsm_scalar(q, k, v, g, scale, initial_state, chunk_size):
     scale = D ** -0.5 if scale is None else scale
     if q.shape[1] == 1 and _LASP_CTX is None and not (torch.is_grad_enabled() and
                                                       any(t.requires_grad for t in (q, k, v) if t is not None)):
-        return _lsm_scalar_step(q, k, v, g, scale, initial_state)
+        return _lsm_step(q, k, v, g, None, scale, initial_state)
     base = _fused_base(q, k, v)
     if base is not None:
         return _LsmScalarFused.apply(base, g, scale, initial_state)
     return _LsmScalar.apply(q, k, v, g, scale, initial_state)
 
 
-def _lsm_scalar_step(q, k, v, g, scale, initial_state):
-    """Decoding: one token per sequence, S' = e^g S + k^T v, o = scale q S' in one launch (csrc/lsm_step.cu)."""
+def _lsm_step(q, k, v, g, gk, scale, initial_state):
+    """Decoding: one token per sequence, S' = e^g diag(e^gk) S + k^T v, o = scale q S' in one launch (csrc/lsm_step.cu).
+    g: None | [H] | [B,1,H]; gk: None | [B,1,H,D]."""
     B, _, H, D = q.shape
     q, k, v = (t if t.stride(-1) == 1 else t.contiguous() for t in (q, k, v))
     gf = None
     if g is not None:
         gf = (g.float().expand(B, H) if g.dim() == 1 else g.float().reshape(B, H)).contiguous()
+    gkf = None if gk is None else gk.float().reshape(B, H, D).contiguous()
     s_in = None if initial_state is None else initial_state.float().contiguous()
     s_out = torch.empty(B, H, D, D, dtype=torch.float32, device=q.device)
     o = torch.empty(B, 1, H, D, dtype=q.dtype, device=q.device)
     ll = ctypes.c_longlong
     _check(lib().lmoe_lsm_scalar_step(_p(q), _p(k), _p(v), ll(q.stride(0)), ll(q.stride(2)), ll(k.stride(0)), ll(k.stride(2)),
-                                      ll(v.stride(0)), ll(v.stride(2)), _p(gf), _p(s_in), _p(s_out), _p(o), ctypes.c_int(B),
+                                      ll(v.stride(0)), ll(v.stride(2)), _p(gf), _p(gkf), _p(s_in), _p(s_out), _p(o), ctypes.c_int(B),
                                       ctypes.c_int(H), ctypes.c_int(D), ctypes.c_float(scale), _st()), "lsm_scalar_step")
     return o, s_out
 
@@ -889,6 +891,8 @@ def lsm_vector(q, k, v, gk, scale, initial_state, bonus, chunk_size):
     if not ok:
         return LT.chunk_vector_gated(q, k, v, gk, scale, initial_state, 16, bonus)
     scale = D ** -0.5 if scale is None else scale
+    if q.shape[1] == 1 and not (torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v, gk))):
+        return _lsm_step(q, k, v, None, gk, scale, initial_state)
     base = _fused_base(q, k, v)
     if base is not None:
         return _LsmVectorFused.apply(base, gk, scale, initial_state)

@@ -380,3 +380,23 @@ def test_lsm_scalar_decode_step(D, gmode, with_state):
     assert o.shape == (B, 1, H, D) and S.shape == (B, H, D, D)
     assert torch.allclose(S, S_ref, atol=1e-4, rtol=1e-4), (S - S_ref).abs().max()
     assert torch.allclose(o.float(), o_ref, atol=3e-2, rtol=2e-2), (o.float() - o_ref).abs().max()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("with_state", [False, True])
+def test_lsm_vector_decode_step(D, with_state):
+    """One-token step with a decay per key channel (GLA / HGRN2) against the recurrence."""
+    from linear_moe_b200.ops import cuda as K
+    from linear_moe_b200.ref.lsm import recurrent_lsm
+    torch.manual_seed(1)
+    B, H = 2, 3
+    dev = "cuda"
+    q, k, v = [(0.5 * torch.randn(B, 1, H, D, device=dev)).bfloat16() for _ in range(3)]
+    gk = -torch.rand(B, 1, H, D, device=dev)
+    S0 = torch.randn(B, H, D, D, device=dev) if with_state else None
+    with torch.no_grad():
+        o, S = K.lsm_vector(q, k, v, gk, None, S0, None, 16)
+    o_ref, S_ref = recurrent_lsm(q.float(), k.float(), v.float(), gk=gk, initial_state=S0)
+    assert torch.allclose(S, S_ref, atol=1e-4, rtol=1e-4), (S - S_ref).abs().max()
+    assert torch.allclose(o.float(), o_ref, atol=3e-2, rtol=2e-2), (o.float() - o_ref).abs().max()
