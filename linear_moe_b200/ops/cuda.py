@@ -942,4 +942,25 @@ class _DeltaRuleScan(torch.autograd.Function):
 
 
 def lsm_delta(q, k, v, beta, g, scale, initial_state, chunk_size):
+    D = q.shape[-1]
+    if (q.shape[1] == 1 and q.is_cuda and q.dtype == torch.bfloat16 and k.dtype == q.dtype and v.dtype == q.dtype
+            and k.shape[-1] == D and v.shape[-1] == D and D in (64, 128)
+            and not (torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, beta, g)))):
+        return _lsm_delta_step(q, k, v, beta, g, D ** -0.5 if scale is None else scale, initial_state)
     return _DeltaRuleScan.apply(q, k, v, beta, g, initial_state, scale, chunk_size)
+
+
+def _lsm_delta_step(q, k, v, beta, g, scale, initial_state):
+    """Decoding: one token of the (gated) delta rule in one launch (csrc/lsm_step.cu).  beta, g: [B,1,H]."""
+    B, _, H, D = q.shape
+    q, k, v = (t if t.stride(-1) == 1 else t.contiguous() for t in (q, k, v))
+    bf = beta.float().reshape(B, H).contiguous()
+    gf = None if g is None else g.float().reshape(B, H).contiguous()
+    s_in = None if initial_state is None else initial_state.float().contiguous()
+    s_out = torch.empty(B, H, D, D, dtype=torch.float32, device=q.device)
+    o = torch.empty(B, 1, H, D, dtype=q.dtype, device=q.device)
+    ll = ctypes.c_longlong
+    _check(lib().lmoe_lsm_delta_step(_p(q), _p(k), _p(v), ll(q.stride(0)), ll(q.stride(2)), ll(k.stride(0)), ll(k.stride(2)),
+                                     ll(v.stride(0)), ll(v.stride(2)), _p(gf), _p(bf), _p(s_in), _p(s_out), _p(o), ctypes.c_int(B),
+                                     ctypes.c_int(H), ctypes.c_int(D), ctypes.c_float(scale), _st()), "lsm_delta_step")
+    return o, s_out

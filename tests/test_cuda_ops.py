@@ -400,3 +400,26 @@ def test_lsm_vector_decode_step(D, with_state):
     o_ref, S_ref = recurrent_lsm(q.float(), k.float(), v.float(), gk=gk, initial_state=S0)
     assert torch.allclose(S, S_ref, atol=1e-4, rtol=1e-4), (S - S_ref).abs().max()
     assert torch.allclose(o.float(), o_ref, atol=3e-2, rtol=2e-2), (o.float() - o_ref).abs().max()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("gated", [False, True])
+@pytest.mark.parametrize("with_state", [False, True])
+def test_lsm_delta_decode_step(D, gated, with_state):
+    """One-token (gated) delta-rule step against the recurrence."""
+    from linear_moe_b200.ops import cuda as K
+    from linear_moe_b200.ref.lsm import recurrent_lsm
+    torch.manual_seed(2)
+    B, H = 2, 3
+    dev = "cuda"
+    q, v = [(0.5 * torch.randn(B, 1, H, D, device=dev)).bfloat16() for _ in range(2)]
+    k = torch.nn.functional.normalize(torch.randn(B, 1, H, D, device=dev), dim=-1).bfloat16()
+    beta = torch.rand(B, 1, H, device=dev)
+    g = -torch.rand(B, 1, H, device=dev) if gated else None
+    S0 = 0.5 * torch.randn(B, H, D, D, device=dev) if with_state else None
+    with torch.no_grad():
+        o, S = K.lsm_delta(q, k, v, beta, g, None, S0, 64)
+    o_ref, S_ref = recurrent_lsm(q.float(), k.float(), v.float(), g=g, beta=beta, initial_state=S0)
+    assert torch.allclose(S, S_ref, atol=2e-4, rtol=1e-4), (S - S_ref).abs().max()
+    assert torch.allclose(o.float(), o_ref, atol=3e-2, rtol=2e-2), (o.float() - o_ref).abs().max()
