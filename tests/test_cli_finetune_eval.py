@@ -32,12 +32,14 @@ def test_reference_flags_are_accepted():
             "--la-mode chunk --base-model qwen2 --la-feature-map elu --la-output-norm rmsnorm --la-gate-fn swish "
             "--layer-type-list LLLN --transformer-impl transformer_engine --use-mcore-models --use-flash-attn "
             "--fp8-hybrid --fp8-amax-history-len 1024 --fp8-amax-compute-algo max --moe-token-dropping "
-            "--moe-train-capacity-factor 1.25 --top-k 5 --temperature 0.7 --out-seq-length 32").split()
+            "--moe-train-capacity-factor 1.25 --top-k 5 --temperature 0.7 --out-seq-length 32 "
+            "--cpu-offloading --cpu-offloading-num-layers 2 --cuda-graph-decode").split()
     args, cfg, par, tc = parse_args(argv)
     assert cfg.la_module == "gated_deltanet" and cfg.layer_type_list == "LLLN" and cfg.num_experts == 8
     assert cfg.vocab_size % (128 * 2) == 0 and not cfg.add_bias_linear and cfg.add_qkv_bias and not cfg.tie_embeddings
     assert par.tp == 2 and par.ep == 2 and par.sequence_parallel and par.use_distributed_optimizer
     assert cfg.recompute_granularity == "selective" and cfg.fp8 == "block" and tc.bf16
+    assert cfg.cpu_offloading and cfg.cpu_offloading_num_layers == 2 and args.cuda_graph_decode
     assert cfg.params_dtype == torch.bfloat16 and cfg.moe_token_dropping and cfg.moe_train_capacity_factor == 1.25
     names = {a.dest for a in build_parser()._actions}
     for flag in ("la_tie_feature_map_qk", "gla_la_gate_low_rank_dim", "rwkv6_la_proj_low_rank_dim", "expand_k", "a_num",
