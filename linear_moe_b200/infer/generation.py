@@ -103,6 +103,7 @@ class GraphedDecodeStep:
         self.tok = torch.zeros(batch, 1, dtype=torch.long, device=device)
         self.graph: Optional["torch.cuda.CUDAGraph"] = None
         self.logits: Optional[torch.Tensor] = None
+        self.failed = False                                    # the step could not be captured: eager from then on
 
     @staticmethod
     def supported(model, caches: List[dict], device) -> bool:
@@ -112,20 +113,35 @@ class GraphedDecodeStep:
             return False
         return all(all(torch.is_tensor(v) for v in c.values()) for c in caches)   # nested caches (MoM) decode eagerly
 
-    def _capture(self):
+    def _capture(self) -> bool:
         static = [dict(c) for c in self.caches]                # the state tensors the graph will read and update
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
-            self.logits = self.model(self.tok, caches=self.caches, position_offset=0)
-            for c, st in zip(self.caches, static):            # forward rebinds every entry to a new tensor
-                for k, v in st.items():
-                    v.copy_(c[k])
-                    c[k] = v
+        graph = torch.cuda.CUDAGraph()
+        try:
+            with torch.cuda.graph(graph):
+                self.logits = self.model(self.tok, caches=self.caches, position_offset=0)
+                for c, st in zip(self.caches, static):        # forward rebinds every entry to a new tensor
+                    for k, v in st.items():
+                        v.copy_(c[k])
+                        c[k] = v
+        except Exception:
+            # a layer that synchronises with the host (e.g. an expert dispatch that reads token counts) cannot be
+            # captured: put the states back as they were and decode eagerly from here on
+            for c, st in zip(self.caches, static):
+                c.clear()
+                c.update(st)
+            torch.cuda.synchronize()
+            self.failed = True
+            return False
+        self.graph = graph
+        return True
 
     def __call__(self, tok: torch.Tensor) -> torch.Tensor:
-        self.tok.copy_(tok)
-        if self.graph is None:
+        if not self.failed and self.graph is None:
+            self.tok.copy_(tok)
             self._capture()                                    # capturing records the step without running it
+        if self.failed:
+            return self.model(tok, caches=self.caches, position_offset=0)
+        self.tok.copy_(tok)
         self.graph.replay()
         return self.logits
 

@@ -167,3 +167,24 @@ def test_cuda_graph_decode_matches_eager(la):
     a, _, _ = generate_tokens(m2, base.clone(), lengths, top_k=1)
     b, _, _ = generate_tokens(m2, base.clone(), lengths, top_k=1, cuda_graph=True)
     assert torch.equal(a, b)
+
+
+@pytest.mark.gpu
+def test_cuda_graph_decode_with_moe_layers():
+    """A linear-attention + MoE model decodes to the same tokens with ``cuda_graph=True``, whether the expert layer can be
+    captured or the step falls back to eager launches."""
+    from linear_moe_b200.infer.generation import generate_tokens
+    torch.manual_seed(0)
+    cfg = ModelConfig(num_layers=2, hidden_size=256, num_attention_heads=2, ffn_hidden_size=512, vocab_size=512,
+                      use_la_module=True, la_module="gla", layer_type_list="LL", num_experts=4, moe_topk=2,
+                      moe_ffn_hidden_size=256, params_dtype=torch.bfloat16)
+    m = CausalLM(cfg, device="cuda").cuda().eval()
+    B, P, L = 2, 12, 32
+    base = torch.zeros(B, L, dtype=torch.long, device="cuda")
+    base[:, :P] = torch.randint(0, 512, (B, P), device="cuda")
+    lengths = torch.full((B,), P, dtype=torch.long, device="cuda")
+    t0, _, _ = generate_tokens(m, base.clone(), lengths, top_k=1)
+    t1, _, _ = generate_tokens(m, base.clone(), lengths, top_k=1, cuda_graph=True)
+    assert torch.equal(t0, t1)
+    from linear_moe_b200.ops import gemm
+    gemm.check_error()
