@@ -131,7 +131,7 @@ class TopKRouter(nn.Module):
         if self.training and cfg.moe_input_jitter_eps:
             eps = cfg.moe_input_jitter_eps
             x = x * torch.empty_like(x).uniform_(1.0 - eps, 1.0 + eps)
-        logits = F.linear(x, self.weight.to(x.dtype)).float()
+        logits = ops.linear(x, self.weight.to(x.dtype)).float()
         if self.training and cfg.moe_z_loss_coeff:
             zl = R.z_loss(logits, cfg.moe_z_loss_coeff / self.mesh.tp)
             logits = MoEAuxLossAutoScaler.apply(logits, zl)

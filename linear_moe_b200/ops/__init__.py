@@ -67,7 +67,7 @@ class _ChunkedLinearCE(torch.autograd.Function):
         lse = torch.empty(T, dtype=torch.float32, device=h.device)
         for s in range(0, T, chunk):
             e = min(s + chunk, T)
-            logits = F.linear(h[s:e], weight.to(h.dtype))
+            logits = _K().mm_nt(h[s:e], weight.to(h.dtype)) if _cuda(h) else F.linear(h[s:e], weight.to(h.dtype))
             if _cuda(h):
                 _K().softmax_ce_fwd(logits, labels[s:e], loss[s:e], lse[s:e], ignore_index)
             else:
@@ -92,7 +92,7 @@ class _ChunkedLinearCE(torch.autograd.Function):
         gl = gl.float().contiguous()
         for s in range(0, T, chunk):
             e = min(s + chunk, T)
-            logits = F.linear(h[s:e], wd)
+            logits = _K().mm_nt(h[s:e], wd) if _cuda(h) else F.linear(h[s:e], wd)
             if _cuda(h):
                 g = _K().softmax_ce_bwd(logits, labels[s:e], lse[s:e], gl[s:e], ctx.ignore_index)
             else:
@@ -101,9 +101,9 @@ class _ChunkedLinearCE(torch.autograd.Function):
                 valid = (lab != ctx.ignore_index).float()
                 p.scatter_add_(-1, lab.clamp(min=0)[:, None], -torch.ones_like(p[:, :1]))
                 g = (p * (gl[s:e] * valid)[:, None]).to(h.dtype)
-            dh[s:e] = g @ wd
+            dh[s:e] = _K().mm_nn(g, wd) if _cuda(h) else g @ wd
             if _cuda(h) and g.dtype != torch.float32:
-                dw += torch.mm(g.t(), h[s:e], out_dtype=torch.float32)     # bf16 operands, fp32 accumulate + output
+                dw += _K().mm_tn(g, h[s:e], out_dtype=torch.float32)       # bf16 operands, fp32 accumulate + output
             else:
                 dw.addmm_(g.t().float(), h[s:e].float())
         return dh, dw.to(weight.dtype), None, None, None
@@ -119,7 +119,7 @@ class _CachedLinearCE(torch.autograd.Function):
     def forward(ctx, h, weight, labels, ignore_index):
         T = h.shape[0]
         wd = weight if weight.dtype == h.dtype else weight.to(h.dtype)
-        Z = torch.mm(h, wd.t())
+        Z = _K().mm_nt(h, wd)
         loss = torch.empty(T, dtype=torch.float32, device=h.device)
         lse = torch.empty(T, dtype=torch.float32, device=h.device)
         K = _K()
@@ -133,10 +133,11 @@ class _CachedLinearCE(torch.autograd.Function):
     def backward(ctx, gl):
         h, wd, Z = ctx.saved_tensors
         g = gl.to(h.dtype)[:, None]
-        dh = torch.mm(Z, wd) * g
-        if _K().wgrad_into_main_grad(ctx.weight, Z.t(), h * g):
+        dh = _K().mm_nn(Z, wd) * g
+        hg = h * g
+        if _K().wgrad_into_main_grad(ctx.weight, Z, hg):
             return dh, None, None, None
-        dw = torch.mm(Z.t(), h * g)
+        dw = _K().mm_tn(Z, hg)
         return dh, dw.to(ctx.wdtype), None, None
 
 

@@ -74,73 +74,132 @@ def _same_dtype(x, *ts):
 
 
 # =====================================================================================
-# GEMM-shaped (cuBLAS for the plain ones; the fused tcgen05 variants live in gemm.py)
+# GEMM-shaped: every dense linear runs the CTA-pair tcgen05 kernel of csrc/gemm_dense.cu
 # =====================================================================================
-_MM_OUT_F32 = None        # does torch.mm(bf16, bf16, out_dtype=fp32, out=...) work in this build?
+def _rows(t: torch.Tensor) -> torch.Tensor:
+    """``[..., n]`` -> a 2-D view (or copy) that satisfies the TMA rules of the dense kernel."""
+    t2 = t.reshape(-1, t.shape[-1])
+    if t2.stride(1) != 1 or t2.stride(0) % 8 or t2.data_ptr() % 16:
+        t2 = t2.contiguous()
+    return t2
 
 
-def wgrad_into_main_grad(weight, a_t: torch.Tensor, b: torch.Tensor) -> bool:
-    """``weight.main_grad (+)= a_t @ b`` straight from the GEMM (fp32 output), skipping the bf16 gradient tensor and
-    the separate accumulation pass (the counterpart of Megatron's gradient-accumulation fusion).  The first write
-    after ``zero_grad`` overwrites, later ones add.  Returns False when the parameter has no fp32 accumulator."""
-    global _MM_OUT_F32
+def wgrad_into_main_grad(weight, dy2: torch.Tensor, x2: torch.Tensor) -> bool:
+    """``weight.main_grad (+)= dy2^T x2`` straight from the GEMM epilogue in fp32 (TMA store for the first write after
+    ``zero_grad``, TMA reduce-add afterwards), skipping the bf16 gradient tensor and the separate accumulation pass
+    (the counterpart of Megatron's gradient-accumulation fusion).  Returns False when the parameter has no fp32
+    accumulator or the operands do not fit the kernel."""
+    from . import gemm
     mg = getattr(weight, "main_grad", None)
     if os.environ.get("LMOE_DIRECT_WGRAD", "1") == "0":
         return False
-    if mg is None or mg.dtype != torch.float32 or a_t.dtype != torch.bfloat16 or not mg.is_contiguous():
+    if mg is None or mg.dtype != torch.float32 or not mg.is_contiguous() or not gemm.dense_ok(dy2, x2):
         return False
-    if _MM_OUT_F32 is None:
-        try:
-            t = torch.zeros(8, 8, dtype=torch.float32, device=a_t.device)
-            torch.mm(torch.ones(8, 16, dtype=torch.bfloat16, device=a_t.device),
-                     torch.ones(16, 8, dtype=torch.bfloat16, device=a_t.device), out_dtype=torch.float32, out=t)
-            _MM_OUT_F32 = bool((t == 16).all())
-        except Exception:
-            _MM_OUT_F32 = False
-    if not _MM_OUT_F32:
-        return False
-    if getattr(weight, "_main_grad_fresh", False):
-        torch.mm(a_t, b, out_dtype=torch.float32, out=mg.view(a_t.shape[0], b.shape[1]))
-        weight._main_grad_fresh = False
-    else:
-        mg.view(a_t.shape[0], b.shape[1]).add_(torch.mm(a_t, b, out_dtype=torch.float32))
+    fresh = getattr(weight, "_main_grad_fresh", False)
+    gemm.dense(dy2, x2, a_mn=True, b_mn=True, out=mg.view(dy2.shape[1], x2.shape[1]), accumulate=not fresh)
+    weight._main_grad_fresh = False
     return True
 
 
-class _LinearMainGrad(torch.autograd.Function):
-    """``x W^T`` whose weight gradient goes directly into ``W.main_grad``."""
+def mm_nt(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``a [M,K] @ b [N,K]^T`` (dense tcgen05 kernel for bf16 operands that fit it, library GEMM otherwise)."""
+    from . import gemm
+    if gemm.dense_ok(a, b) and b.shape[0] % 8 == 0:
+        return gemm.dense(a, b)
+    return torch.mm(a, b.t())
+
+
+def mm_nn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``a [M,N] @ b [N,K]``."""
+    from . import gemm
+    if gemm.dense_ok(a, b):
+        return gemm.dense(a, b, b_mn=True)
+    return torch.mm(a, b)
+
+
+def mm_tn(a: torch.Tensor, b: torch.Tensor, out_dtype=None) -> torch.Tensor:
+    """``a [M,N]^T @ b [M,K]`` -> ``[N,K]`` in ``out_dtype`` (bf16 or fp32 straight from the fp32 accumulators)."""
+    from . import gemm
+    out_dtype = out_dtype or a.dtype
+    if gemm.dense_ok(a, b) and out_dtype in (torch.bfloat16, torch.float32):
+        return gemm.dense(a, b, a_mn=True, b_mn=True, out_dtype=out_dtype)
+    if out_dtype == torch.float32 and a.dtype == torch.bfloat16:
+        return torch.mm(a.t(), b, out_dtype=torch.float32)
+    return torch.mm(a.t(), b).to(out_dtype)
+
+
+class _LinearTc(torch.autograd.Function):
+    """``x W^T`` with forward, data gradient and weight gradient on the dense tcgen05 kernel; the weight gradient goes
+    directly into ``W.main_grad`` when the parameter has one."""
 
     @staticmethod
     def forward(ctx, x, weight):
-        ctx.save_for_backward(x, weight)
-        return F.linear(x, weight)
+        from . import gemm
+        x2 = _rows(x)
+        ctx.save_for_backward(x2, weight)
+        ctx.xshape = x.shape
+        return gemm.dense(x2, weight).view(*x.shape[:-1], weight.shape[0])
 
     @staticmethod
     def backward(ctx, dy):
-        x, weight = ctx.saved_tensors
-        dx = torch.matmul(dy, weight) if ctx.needs_input_grad[0] else None
+        from . import gemm
+        x2, weight = ctx.saved_tensors
+        dy2 = _rows(dy)
+        dx = gemm.dense(dy2, weight, b_mn=True).view(ctx.xshape) if ctx.needs_input_grad[0] else None
         dw = None
-        if ctx.needs_input_grad[1]:
-            dy2, x2 = dy.reshape(-1, dy.shape[-1]), x.reshape(-1, x.shape[-1])
-            if not wgrad_into_main_grad(weight, dy2.t(), x2):
-                dw = torch.mm(dy2.t(), x2)
+        if ctx.needs_input_grad[1] and not wgrad_into_main_grad(weight, dy2, x2):
+            dw = gemm.dense(dy2, x2, a_mn=True, b_mn=True)
         return dx, dw
 
 
 def linear(x, weight, bias=None):
-    from . import fp8
+    from . import fp8, gemm
     if fp8.enabled() and bias is None and fp8.supported(x, weight):
         return fp8.Fp8Linear.apply(x, weight)
-    if (bias is None and weight.dtype == x.dtype == torch.bfloat16 and weight.requires_grad and torch.is_grad_enabled()
-            and getattr(weight, "main_grad", None) is not None):
-        return _LinearMainGrad.apply(x, weight)
+    if (weight.dtype == x.dtype == torch.bfloat16 and weight.dim() == 2 and x.shape[-1] % 8 == 0 and x.numel() > 0
+            and gemm.dense_ok(weight) and weight.shape[0] % 8 == 0):
+        y = _LinearTc.apply(x, weight)
+        return y if bias is None else y + bias.to(y.dtype)
     return F.linear(x, weight if weight.dtype == x.dtype else weight.to(x.dtype),
                     None if bias is None else bias.to(x.dtype))
 
 
+class _LinearSwigluTc(torch.autograd.Function):
+    """fc1 + SwiGLU with the activation in the GEMM epilogue (``gemm.dense_swiglu``): one kernel writes the activation
+    and the pre-activations the backward pass needs; backward = dSwiGLU kernel, then data and weight gradient GEMMs."""
+
+    @staticmethod
+    def forward(ctx, x, weight):
+        from . import gemm
+        x2 = _rows(x)
+        act, pre = gemm.dense_swiglu(x2, weight, want_pre=True)
+        ctx.save_for_backward(x2, weight, pre)
+        ctx.xshape = x.shape
+        return act.view(*x.shape[:-1], act.shape[-1])
+
+    @staticmethod
+    def backward(ctx, dact):
+        from . import gemm
+        x2, weight, pre = ctx.saved_tensors
+        d2 = dact.reshape(-1, dact.shape[-1]).contiguous()
+        dpre = torch.empty_like(pre)
+        rows, Fh = d2.shape
+        _check(lib().lmoe_swiglu_bwd(_p(d2), _p(pre), _p(dpre), _i64(rows), _i32(Fh), _i32(_dt(pre)), _st()), "swiglu_bwd")
+        dx = gemm.dense(dpre, weight, b_mn=True).view(ctx.xshape) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1] and not wgrad_into_main_grad(weight, dpre, x2):
+            dw = gemm.dense(dpre, x2, a_mn=True, b_mn=True)
+        return dx, dw
+
+
 def linear_swiglu(x, weight):
-    """fc1 + SwiGLU.  The GEMM goes through :func:`linear` (fp32 weight-gradient accumulation, fp8 when enabled); the
-    fused-epilogue tcgen05 kernel (``gemm.gemm_nt(..., swiglu=True)``) needs the tiled fc1 layout and is opt-in."""
+    """fc1 + SwiGLU.  bf16 operands that fit the dense tcgen05 kernel take its fused-epilogue form; fp8 and everything
+    else go through :func:`linear` followed by the SwiGLU kernel."""
+    from . import fp8, gemm
+    if (not (fp8.enabled() and fp8.supported(x, weight)) and weight.dtype == x.dtype == torch.bfloat16 and weight.dim() == 2
+            and x.shape[-1] % 8 == 0 and x.numel() > 0 and gemm.dense_ok(weight) and weight.shape[0] % 16 == 0
+            and os.environ.get("LMOE_FUSED_SWIGLU", "1") != "0"):
+        return _LinearSwigluTc.apply(x, weight)
     return swiglu(linear(x, weight))
 
 

@@ -79,6 +79,62 @@ def gemm_nt_2cta(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] =
     return out
 
 
+def dense_ok(*ts: torch.Tensor) -> bool:
+    """Every 2-D bf16 operand fits the TMA rules of the dense kernel (unit inner stride, 16-byte pitches and base)."""
+    if not available():
+        return False
+    for t in ts:
+        if not (t.is_cuda and t.dtype == torch.bfloat16 and t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0
+                and t.shape[1] % 8 == 0 and t.data_ptr() % 16 == 0 and t.shape[0] > 0):
+            return False
+    return True
+
+
+BAND = int(os.environ.get("LMOE_GEMM_BAND", "0"))          # tile rows per band of the tile order (0 = kernel default)
+
+
+def dense(a: torch.Tensor, b: torch.Tensor, a_mn: bool = False, b_mn: bool = False, out: Optional[torch.Tensor] = None,
+          accumulate: bool = False, out_dtype=torch.bfloat16, band: Optional[int] = None) -> torch.Tensor:
+    """``C[M,N] (+)= A B`` on the CTA-pair tcgen05 kernel of ``csrc/gemm_dense.cu``.
+
+    ``a`` is ``[M,K]`` (or ``[K,M]`` with ``a_mn``), ``b`` is ``[N,K]`` (or ``[K,N]`` with ``b_mn``).  ``out`` may be a
+    bf16 or fp32 matrix; ``accumulate`` (fp32 only) adds into it with TMA reduce-adds instead of overwriting.
+    The three GEMMs of a linear layer are ``dense(x, w)`` (forward), ``dense(dy, w, b_mn=True)`` (data gradient) and
+    ``dense(dy, x, a_mn=True, b_mn=True)`` (weight gradient)."""
+    from . import cuda as K
+    M, Kd = (a.shape[1], a.shape[0]) if a_mn else a.shape
+    N = b.shape[1] if b_mn else b.shape[0]
+    assert (b.shape[0] if b_mn else b.shape[1]) == Kd, (a.shape, b.shape, a_mn, b_mn)
+    if out is None:
+        assert not accumulate
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    mode = 0 if out.dtype == torch.bfloat16 else (2 if accumulate else 1)
+    assert out.shape == (M, N) and out.stride(1) == 1 and (mode != 0 or not accumulate)
+    rc = K.lib().lmoe_gemm_dense(K._p(a), ctypes.c_int(a.stride(0)), ctypes.c_int(int(a_mn)), K._p(b), ctypes.c_int(b.stride(0)),
+                                 ctypes.c_int(int(b_mn)), K._p(out), ctypes.c_int(out.stride(0)), ctypes.c_int(mode),
+                                 ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(Kd), ctypes.c_int(BAND if band is None else band),
+                                 K._p(_err(a.device)), ctypes.c_int(K.NUM_SMS), K._st())
+    K._check(rc, "gemm_dense")
+    return out
+
+
+def dense_swiglu(x: torch.Tensor, w: torch.Tensor, want_pre: bool = True, band: Optional[int] = None):
+    """``silu(x Wg^T) * (x Wu^T)`` for ``w = [Wg ; Wu]`` (``[2F, K]``, the ordinary fc1 layout) with the activation in
+    the GEMM epilogue.  Returns ``(act [M,F], pre [M,2F] or None)``; ``pre`` is what the backward pass needs."""
+    from . import cuda as K
+    M, Kd = x.shape
+    F2 = w.shape[0]
+    Fh = F2 // 2
+    act = torch.empty(M, Fh, dtype=torch.bfloat16, device=x.device)
+    pre = torch.empty(M, F2, dtype=torch.bfloat16, device=x.device) if want_pre else None
+    rc = K.lib().lmoe_gemm_dense_swiglu(K._p(x), ctypes.c_int(x.stride(0)), K._p(w), ctypes.c_int(w.stride(0)), K._p(act),
+                                        ctypes.c_int(act.stride(0)), K._p(pre), ctypes.c_int(F2), ctypes.c_int(M),
+                                        ctypes.c_int(Fh), ctypes.c_int(Kd), ctypes.c_int(BAND if band is None else band),
+                                        K._p(_err(x.device)), ctypes.c_int(K.NUM_SMS), K._st())
+    K._check(rc, "gemm_dense_swiglu")
+    return act, pre
+
+
 def tile_swiglu_weight(w: torch.Tensor) -> torch.Tensor:
     """``[2f, h]`` = [gate; up]  ->  per 128 output columns: 128 gate rows followed by the 128 up rows."""
     f = w.shape[0] // 2

@@ -539,6 +539,15 @@ class TpWorkspace:
         return out
 
 
+def _wgrad(w, dy2d, x2d):
+    """``dy^T x`` on the dense tcgen05 kernel: straight into ``w.main_grad`` in fp32 when the parameter has one (returns
+    None then), else a gradient tensor in the weight's dtype."""
+    from ..ops import cuda as K
+    if K.wgrad_into_main_grad(w, dy2d, x2d):
+        return None
+    return K.mm_tn(dy2d, x2d).to(w.dtype)
+
+
 class _AGLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, bias, ws):
@@ -561,7 +570,7 @@ class _AGLinear(torch.autograd.Function):
         wb = w if w.dtype == torch.bfloat16 else w.to(torch.bfloat16)
         dx = ws.gemm_rs(dy2d, T_loc, wb, True)                               # (dy W) reduce-scattered
         xfull = ws.gather(ws.publish(x2d), B * T_loc, T_loc, Kd)             # re-gathered, not saved
-        dw = torch.mm(dy2d.t(), xfull).to(w.dtype)
+        dw = _wgrad(w, dy2d, xfull)
         db = dy2d.sum(0) if ctx.has_bias else None
         return dx.view(B, T_loc, Kd), dw, db, None
 
@@ -589,7 +598,7 @@ class _LinearRS(torch.autograd.Function):
         pub = ws.publish(dy2d)
         dx = ws.ag_gemm(pub, B * T_loc, T_loc, N, wb, True)                  # gather(dy) W
         dyfull = ws.gather(pub, B * T_loc, T_loc, N)
-        dw = torch.mm(dyfull.t(), x2d).to(w.dtype)
+        dw = _wgrad(w, dyfull, x2d)
         return dx.view(B, ws.W * T_loc, Kd), dw, None
 
 

@@ -167,3 +167,97 @@ def test_grouped_wgrad_into_fp32_accumulator():
         assert w.grad is None
         err = (w.main_grad - n * ref).abs().max().item()
         assert err <= 2e-2 * ref.abs().max().item() * n + 1e-3, (n, err)
+
+
+def _dense_case(M, N, K, a_mn, b_mn, seed=0):
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(seed)
+    a = torch.randn(M, K, device=dev).to(torch.bfloat16)
+    b = torch.randn(N, K, device=dev).to(torch.bfloat16)
+    return a, b, (a.t().contiguous() if a_mn else a), (b.t().contiguous() if b_mn else b), a.float() @ b.float().t()
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 320), (1000, 520, 200), (72, 40, 8), (2304, 1280, 1032)])
+def test_gemm_dense_layouts(a_mn, b_mn, M, N, K):
+    """Dense CTA-pair kernel, bf16 output through TMA stores, against the fp32 product (ragged M, N and K included)."""
+    from linear_moe_b200.ops import gemm
+    a, b, aa, bb, ref = _dense_case(M, N, K, a_mn, b_mn)
+    for band in (1, 3, 8):
+        c = gemm.dense(aa, bb, a_mn, b_mn, band=band)
+        torch.cuda.synchronize()
+        gemm.check_error()
+        err = (c.float() - ref).abs().max().item()
+        assert err <= 2e-2 * ref.abs().max().item() + 1e-3, (band, err)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(512, 768, 320), (1000, 264, 4104)])
+def test_gemm_dense_fp32_out_and_accumulate(a_mn, b_mn, M, N, K):
+    """fp32 output (TMA store) and fp32 accumulation (TMA reduce-add) of the dense kernel; relative Frobenius error."""
+    from linear_moe_b200.ops import gemm
+    a, b, aa, bb, ref = _dense_case(M, N, K, a_mn, b_mn, seed=3)
+    c = torch.full((M, N), 7.0, device=a.device)
+    gemm.dense(aa, bb, a_mn, b_mn, out=c)
+    torch.cuda.synchronize()
+    assert ((c - ref).norm() / ref.norm()).item() < 1e-5
+    gemm.dense(aa, bb, a_mn, b_mn, out=c, accumulate=True)
+    gemm.dense(aa, bb, a_mn, b_mn, out=c, accumulate=True)
+    torch.cuda.synchronize()
+    gemm.check_error()
+    assert ((c - 3 * ref).norm() / (3 * ref).norm()).item() < 1e-5
+    # a strided fp32 destination (a slice of a flat gradient buffer)
+    big = torch.zeros(M, N + 12, device=a.device)
+    gemm.dense(aa, bb, a_mn, b_mn, out=big[:, 4:4 + N], accumulate=True)
+    torch.cuda.synchronize()
+    assert ((big[:, 4:4 + N] - ref).norm() / ref.norm()).item() < 1e-5
+    assert big[:, :4].abs().max().item() == 0 and big[:, 4 + N:].abs().max().item() == 0
+
+
+@pytest.mark.parametrize("M,F,K,want_pre", [(520, 512, 256, True), (300, 136, 72, True), (1024, 384, 128, False)])
+def test_gemm_dense_swiglu(M, F, K, want_pre):
+    """fc1 + SwiGLU epilogue on the ordinary [gate; up] weight layout; also returns the pre-activations."""
+    from linear_moe_b200.ops import gemm
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    x = (0.5 * torch.randn(M, K, device=dev)).to(torch.bfloat16)
+    w = (0.1 * torch.randn(2 * F, K, device=dev)).to(torch.bfloat16)
+    act, pre = gemm.dense_swiglu(x, w, want_pre=want_pre)
+    torch.cuda.synchronize()
+    gemm.check_error()
+    z = x.float() @ w.float().t()
+    ref = torch.nn.functional.silu(z[:, :F]) * z[:, F:]
+    assert (act.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item() + 1e-3
+    if want_pre:
+        assert (pre.float() - z).abs().max().item() <= 2e-2 * z.abs().max().item() + 1e-3
+    else:
+        assert pre is None
+
+
+@pytest.mark.parametrize("main_grad", [False, True])
+def test_linear_autograd_on_dense_kernel(main_grad):
+    """ops.linear on bf16 CUDA tensors: y, dx, dW against fp32 autograd; with main_grad two backward passes accumulate."""
+    from linear_moe_b200 import ops
+    from linear_moe_b200.ops import gemm
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(5)
+    x = torch.randn(3, 100, 264, device=dev).to(torch.bfloat16).requires_grad_(True)
+    w = (0.1 * torch.randn(520, 264, device=dev)).to(torch.bfloat16).requires_grad_(True)
+    bias = torch.randn(520, device=dev).to(torch.bfloat16)
+    gy = torch.randn(3, 100, 520, device=dev).to(torch.bfloat16)
+    if main_grad:
+        w.main_grad = torch.empty(520, 264, device=dev)
+        w._main_grad_fresh = True
+    reps = 2 if main_grad else 1
+    for _ in range(reps):
+        y = ops.linear(x, w, bias)
+        y.backward(gy)
+    torch.cuda.synchronize()
+    gemm.check_error()
+    xr, wr = x.detach().float().requires_grad_(True), w.detach().float().requires_grad_(True)
+    yr = torch.nn.functional.linear(xr, wr, bias.float())
+    yr.backward(gy.float())
+    assert (y.float() - yr).abs().max().item() <= 2e-2 * yr.abs().max().item()
+    assert ((x.grad.float() - reps * xr.grad).norm() / (reps * xr.grad).norm()).item() < 1e-2
+    dw = w.main_grad if main_grad else w.grad.float()
+    assert ((dw - reps * wr.grad).norm() / (reps * wr.grad).norm()).item() < (1e-5 if main_grad else 1e-2)
