@@ -84,17 +84,20 @@ def hf_to_mcore(hf: SD, cfg: ModelConfig) -> SD:
             out[m + "mlp.linear_fc1.weight"] = torch.cat([hf[x + "gate_proj.weight"], hf[x + "up_proj.weight"]], 0)
             out[m + "mlp.linear_fc2.weight"] = hf[x + "down_proj.weight"]
             continue
-        if fam == "mixtral":
-            x = p + "block_sparse_moe."
-            out[m + "mlp.router.weight"] = hf[x + "gate.weight"]
+        x = p + ("block_sparse_moe." if (fam == "mixtral" and p + "block_sparse_moe.gate.weight" in hf) else "mlp.")
+        out[m + "mlp.router.weight"] = hf[x + "gate.weight"]
+        if x + "experts.gate_up_proj" in hf:
+            # in-memory layout of transformers >= 5: experts stacked as gate_up_proj [E, 2f, h], down_proj [E, h, f]
+            w1 = list(hf[x + "experts.gate_up_proj"].transpose(1, 2))
+            w2 = list(hf[x + "experts.down_proj"].transpose(1, 2))
+        elif fam == "mixtral":
             w1 = [torch.cat([hf[f"{x}experts.{e}.w1.weight"], hf[f"{x}experts.{e}.w3.weight"]], 0).t() for e in range(cfg.num_experts)]
             w2 = [hf[f"{x}experts.{e}.w2.weight"].t() for e in range(cfg.num_experts)]
         else:
-            x = p + "mlp."
-            out[m + "mlp.router.weight"] = hf[x + "gate.weight"]
             w1 = [torch.cat([hf[f"{x}experts.{e}.gate_proj.weight"], hf[f"{x}experts.{e}.up_proj.weight"]], 0).t()
                   for e in range(cfg.num_experts)]
             w2 = [hf[f"{x}experts.{e}.down_proj.weight"].t() for e in range(cfg.num_experts)]
+        if fam != "mixtral":
             sh = "shared_expert." if fam == "qwen2" else "shared_experts."
             if x + sh + "gate_proj.weight" in hf:
                 out[m + "mlp.shared_expert.linear_fc1.weight"] = torch.cat([hf[x + sh + "gate_proj.weight"],

@@ -14,7 +14,8 @@ reference's per-expert keys ``mlp.experts.local_experts.{e}.linear_fc1/linear_fc
 
 Only data-parallel rank 0 of each model-parallel coordinate writes model weights; under ZeRO-1
 every data-parallel rank writes its optimizer shard next to it.  ``async_save`` hands the CPU copy
-to a writer thread.
+to a writer thread; the tracker file of such a save is published by :func:`finalize_async_saves` once every rank's
+files are on disk.
 """
 from __future__ import annotations
 
@@ -32,6 +33,8 @@ from ..dist.mesh import Mesh
 
 TRACKER = "latest_checkpointed_iteration.txt"
 _WRITERS: List[threading.Thread] = []
+_WRITER_ERRORS: List[BaseException] = []
+_PENDING_TRACKERS: List[Tuple[str, str, bool]] = []      # (root, text, this rank writes it) of async saves not yet finalized
 
 
 def checkpoint_name(root: str, iteration, release: bool, tp_rank: int, pp_rank: int, ep_rank: int,
@@ -83,6 +86,12 @@ def from_reference_keys(sd: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
             (fc1 if tail.startswith("linear_fc1") else fc2).setdefault(base, {})[int(e)] = v
         elif k.endswith("._extra_state"):
             continue
+        elif k.endswith(".linear_qkv.layer_norm_weight") or k.endswith(".linear_q_proj.layer_norm_weight"):
+            # TransformerEngine-style fused norm + linear modules carry the pre-norm weight on the linear
+            # (written by the reference's convertors when use_te): it is this framework's input_layernorm
+            out[k.rsplit(".self_attention.", 1)[0] + ".input_layernorm.weight"] = v
+        elif k.endswith(".mlp.linear_fc1.layer_norm_weight"):
+            out[k[: -len(".mlp.linear_fc1.layer_norm_weight")] + ".pre_mlp_layernorm.weight"] = v
         else:
             out[k] = v
     for base, d in fc1.items():
@@ -128,6 +137,7 @@ def _write(obj, path: str):
 def save_checkpoint(root: str, iteration, models, optimizer, scheduler, cfg, par, tc, mesh: Mesh,
                     consumed_samples: int = 0, release: bool = False):
     """Write this rank's share of the checkpoint and (rank 0, after a barrier) the tracker file."""
+    finalize_async_saves()                                   # an earlier asynchronous save completes first
     os.makedirs(root, exist_ok=True)
     path = checkpoint_name(root, iteration, release, mesh.tp_rank, mesh.pp_rank, mesh.ep_rank, mesh.pp, mesh.ep)
     write_model = mesh.edp_rank == 0          # one writer per (tp, pp, ep) coordinate
@@ -142,31 +152,73 @@ def save_checkpoint(root: str, iteration, models, optimizer, scheduler, cfg, par
             payload["optimizer"] = optimizer.state_dict()
         if scheduler is not None:
             payload["opt_param_scheduler"] = scheduler.state_dict()
-        if not tc.no_save_rng:
-            payload["rng_state"] = [_rng_state()]
+    if not tc.no_save_rng:
+        # one RNG state per expert-data-parallel rank of this model-parallel coordinate (the data-parallel ranks run
+        # with different seeds; restoring rank 0's state everywhere would collapse them)
+        states = [_rng_state()]
+        g = mesh["edp"]
+        if dist.is_initialized() and not g.is_trivial:
+            states = [None] * g.size
+            dist.all_gather_object(states, _rng_state(), group=g.pg)
+        if payload is not None:
+            payload["rng_state"] = states
     jobs = []
     if payload is not None:
         jobs.append((payload, path))
     if optimizer is not None and optimizer.zero1 and not tc.no_save_optim:
         jobs.append((optimizer.state_dict(), path.replace("model_optim_rng.pt", f"distrib_optim_{mesh.dpcp_rank:03d}.pt")))
+    text = "release" if release else str(int(iteration))
     if getattr(tc, "async_save", False):
-        t = threading.Thread(target=lambda: [_write(o, p) for o, p in jobs], daemon=False)
+        # the tracker of this save is written by finalize_async_saves(): at the start of the next save or at the end
+        # of training, after every rank has joined its writers, so it never names files that are still being written
+        def work():
+            try:
+                for o, p in jobs:
+                    _write(o, p)
+            except BaseException as e:                      # surfaced by finalize_async_saves()
+                _WRITER_ERRORS.append(e)
+        t = threading.Thread(target=work, daemon=False)
         t.start()
         _WRITERS.append(t)
-    else:
-        for o, p in jobs:
-            _write(o, p)
+        _PENDING_TRACKERS.append((root, text, mesh.rank == 0))
+        return
+    for o, p in jobs:
+        _write(o, p)
     if dist.is_initialized():
         dist.barrier()
     if mesh.rank == 0:
-        wait_for_async_saves()
         with open(os.path.join(root, TRACKER), "w") as f:
-            f.write("release" if release else str(int(iteration)))
+            f.write(text)
+
+
+def finalize_async_saves():
+    """Collective: join this rank's writer threads, meet the other ranks, then let rank 0 publish the tracker files of
+    the saves that completed.  A writer's failure is raised here (on its rank) before any tracker is written."""
+    while _WRITERS:
+        _WRITERS.pop().join()
+    failed = 1 if _WRITER_ERRORS else 0
+    if dist.is_initialized() and _PENDING_TRACKERS:
+        flags = [None] * dist.get_world_size()
+        dist.all_gather_object(flags, failed)
+        failed_any = any(flags)
+    else:
+        failed_any = bool(failed)
+    pending = list(_PENDING_TRACKERS)
+    _PENDING_TRACKERS.clear()
+    if _WRITER_ERRORS:
+        e = _WRITER_ERRORS[0]
+        _WRITER_ERRORS.clear()
+        raise RuntimeError("asynchronous checkpoint write failed") from e
+    if failed_any:
+        raise RuntimeError("asynchronous checkpoint write failed on another rank; tracker not updated")
+    for root, text, mine in pending:
+        if mine:
+            with open(os.path.join(root, TRACKER), "w") as f:
+                f.write(text)
 
 
 def wait_for_async_saves():
-    while _WRITERS:
-        _WRITERS.pop().join()
+    finalize_async_saves()
 
 
 def load_checkpoint(root: str, models, optimizer, scheduler, mesh: Mesh, load_rng: bool = True,
@@ -187,15 +239,19 @@ def load_checkpoint(root: str, models, optimizer, scheduler, mesh: Mesh, load_rn
         if strict and (missing or unexpected):
             raise KeyError(f"checkpoint mismatch: missing {missing[:5]}, unexpected {unexpected[:5]}")
     if optimizer is not None:
+        optimizer.state_loaded = False                       # read by Trainer.load: restored masters must not be re-derived
         if optimizer.zero1:
             p = path.replace("model_optim_rng.pt", f"distrib_optim_{mesh.dpcp_rank:03d}.pt")
             if os.path.isfile(p):
                 optimizer.load_state_dict(torch.load(p, map_location="cpu", weights_only=False))
+                optimizer.state_loaded = True
         elif "optimizer" in ck:
             optimizer.load_state_dict(ck["optimizer"])
+            optimizer.state_loaded = True
     if scheduler is not None and "opt_param_scheduler" in ck:
         scheduler.load_state_dict(ck["opt_param_scheduler"])
     if load_rng and "rng_state" in ck:
-        _set_rng_state(ck["rng_state"][0])
+        states = ck["rng_state"]
+        _set_rng_state(states[mesh.edp_rank] if mesh.edp_rank < len(states) else states[0])
     consumed = getattr(ck.get("args", Namespace()), "consumed_train_samples", 0)
     return (0 if release else int(ck.get("iteration", it))), int(consumed)

@@ -193,6 +193,7 @@ def build_parser() -> argparse.ArgumentParser:
     _flag(g, "--distributed-backend", type=str, default="nccl", choices=["nccl", "gloo"])
     _flag(g, "--distributed-timeout-minutes", type=int, default=10)
     _flag(g, "--no-fused-comm", action="store_true")
+    _flag(g, "--fused-comm-timeout-s", type=float, default=20.0)
     _flag(g, "--local-rank", "--local_rank", type=int, default=None, dest="local_rank")
 
     g = p.add_argument_group("training")
@@ -428,7 +429,7 @@ def configs_from_args(args: argparse.Namespace) -> Tuple[ModelConfig, ParallelCo
         overlap_grad_reduce=args.overlap_grad_reduce, overlap_param_gather=args.overlap_param_gather,
         distributed_backend=args.distributed_backend,
         distributed_timeout_minutes=args.distributed_timeout_minutes,
-        fused_comm=not args.no_fused_comm,
+        fused_comm=not args.no_fused_comm, fused_comm_timeout_s=args.fused_comm_timeout_s,
     )
     gbs = args.global_batch_size if args.global_batch_size is not None else args.micro_batch_size
     train = TrainConfig(

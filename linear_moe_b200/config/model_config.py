@@ -203,6 +203,7 @@ class ParallelConfig:
     distributed_backend: str = "nccl"
     distributed_timeout_minutes: int = 10
     fused_comm: bool = True                       # P2P/NVLS kernels instead of NCCL where available
+    fused_comm_timeout_s: float = 20.0            # how long a fused kernel waits for a peer before it reports a timeout
 
     @property
     def tp(self): return self.tensor_model_parallel_size

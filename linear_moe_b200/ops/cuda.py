@@ -138,14 +138,21 @@ class _LinearTc(torch.autograd.Function):
         x2 = _rows(x)
         ctx.save_for_backward(x2, weight)
         ctx.xshape = x.shape
-        return gemm.dense(x2, weight).view(*x.shape[:-1], weight.shape[0])
+        # the result is allocated in its final shape: a view returned from forward() would have the 2-D buffer as its
+        # autograd-less `_base`, which code that looks at view chains (fused q|k|v detection) must never see
+        y = torch.empty(*x.shape[:-1], weight.shape[0], dtype=torch.bfloat16, device=x.device)
+        gemm.dense(x2, weight, out=y.view(-1, weight.shape[0]))
+        return y
 
     @staticmethod
     def backward(ctx, dy):
         from . import gemm
         x2, weight = ctx.saved_tensors
         dy2 = _rows(dy)
-        dx = gemm.dense(dy2, weight, b_mn=True).view(ctx.xshape) if ctx.needs_input_grad[0] else None
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty(ctx.xshape, dtype=torch.bfloat16, device=dy.device)
+            gemm.dense(dy2, weight, b_mn=True, out=dx.view(-1, dx.shape[-1]))
         dw = None
         if ctx.needs_input_grad[1] and not wgrad_into_main_grad(weight, dy2, x2):
             dw = gemm.dense(dy2, x2, a_mn=True, b_mn=True)
@@ -172,10 +179,10 @@ class _LinearSwigluTc(torch.autograd.Function):
     def forward(ctx, x, weight):
         from . import gemm
         x2 = _rows(x)
-        act, pre = gemm.dense_swiglu(x2, weight, want_pre=True)
+        act, pre = gemm.dense_swiglu(x2, weight, want_pre=True, out_shape=(*x.shape[:-1], weight.shape[0] // 2))
         ctx.save_for_backward(x2, weight, pre)
         ctx.xshape = x.shape
-        return act.view(*x.shape[:-1], act.shape[-1])
+        return act
 
     @staticmethod
     def backward(ctx, dact):
@@ -185,7 +192,10 @@ class _LinearSwigluTc(torch.autograd.Function):
         dpre = torch.empty_like(pre)
         rows, Fh = d2.shape
         _check(lib().lmoe_swiglu_bwd(_p(d2), _p(pre), _p(dpre), _i64(rows), _i32(Fh), _i32(_dt(pre)), _st()), "swiglu_bwd")
-        dx = gemm.dense(dpre, weight, b_mn=True).view(ctx.xshape) if ctx.needs_input_grad[0] else None
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty(ctx.xshape, dtype=torch.bfloat16, device=dact.device)
+            gemm.dense(dpre, weight, b_mn=True, out=dx.view(-1, dx.shape[-1]))
         dw = None
         if ctx.needs_input_grad[1] and not wgrad_into_main_grad(weight, dpre, x2):
             dw = gemm.dense(dpre, x2, a_mn=True, b_mn=True)
@@ -748,6 +758,8 @@ def _fused_base(q, k, v):
     base = q._base                                   # root of the view chain, e.g. the projection output [B,T,H*3D]
     if base is None or k._base is not base or v._base is not base or not base.is_contiguous():
         return None
+    if base.requires_grad != (q.requires_grad or k.requires_grad or v.requires_grad):
+        return None                                  # a root outside the autograd graph would drop the gradients
     B, T, H, D = q.shape
     if base.numel() != B * T * H * 3 * D:
         return None

@@ -28,9 +28,12 @@ def enable(flag: bool):
 
 
 def _err(device) -> torch.Tensor:
+    """Error word of the tcgen05 kernels: element 1 of the fused-communication status tensor, so the training loop
+    reads both with one copy (``fused_comm.check_status``)."""
     global _ERR
     if _ERR is None or _ERR.device != device:
-        _ERR = torch.zeros(1, dtype=torch.int32, device=device)
+        from ..parallel import fused_comm
+        _ERR = fused_comm.status_word(device)[1:2]
     return _ERR
 
 
@@ -118,17 +121,17 @@ def dense(a: torch.Tensor, b: torch.Tensor, a_mn: bool = False, b_mn: bool = Fal
     return out
 
 
-def dense_swiglu(x: torch.Tensor, w: torch.Tensor, want_pre: bool = True, band: Optional[int] = None):
+def dense_swiglu(x: torch.Tensor, w: torch.Tensor, want_pre: bool = True, band: Optional[int] = None, out_shape=None):
     """``silu(x Wg^T) * (x Wu^T)`` for ``w = [Wg ; Wu]`` (``[2F, K]``, the ordinary fc1 layout) with the activation in
     the GEMM epilogue.  Returns ``(act [M,F], pre [M,2F] or None)``; ``pre`` is what the backward pass needs."""
     from . import cuda as K
     M, Kd = x.shape
     F2 = w.shape[0]
     Fh = F2 // 2
-    act = torch.empty(M, Fh, dtype=torch.bfloat16, device=x.device)
+    act = torch.empty(out_shape or (M, Fh), dtype=torch.bfloat16, device=x.device)
     pre = torch.empty(M, F2, dtype=torch.bfloat16, device=x.device) if want_pre else None
     rc = K.lib().lmoe_gemm_dense_swiglu(K._p(x), ctypes.c_int(x.stride(0)), K._p(w), ctypes.c_int(w.stride(0)), K._p(act),
-                                        ctypes.c_int(act.stride(0)), K._p(pre), ctypes.c_int(F2), ctypes.c_int(M),
+                                        ctypes.c_int(Fh), K._p(pre), ctypes.c_int(F2), ctypes.c_int(M),
                                         ctypes.c_int(Fh), ctypes.c_int(Kd), ctypes.c_int(BAND if band is None else band),
                                         K._p(_err(x.device)), ctypes.c_int(K.NUM_SMS), K._st())
     K._check(rc, "gemm_dense_swiglu")

@@ -66,7 +66,7 @@ class _LaspArgs(ctypes.Structure):
 class LaspWorkspace:
     NSLOT = 64
 
-    def __init__(self, group, max_state_elems: int, device, spin_limit: int = 2_000_000):
+    def __init__(self, group, max_state_elems: int, device, spin_limit: Optional[int] = None):
         """``max_state_elems`` = B*H*D*D of the largest exchange."""
         self.group, self.device = group, device
         W = group.size
@@ -77,7 +77,7 @@ class LaspWorkspace:
         self.flags, self.flag_hdl = _symm_empty(self.NSLOT * W * self.max_ctas, torch.int32, device, group)
         self.flags.zero_()
         self.calls = 0
-        self.spin_limit = spin_limit
+        self.spin_limit = default_spin_limit() if spin_limit is None else spin_limit
         self.peer_data = torch.tensor(list(self.data_hdl.buffer_ptrs), dtype=torch.int64, device=device)
         self.peer_flags = torch.tensor(list(self.flag_hdl.buffer_ptrs), dtype=torch.int64, device=device)
         torch.cuda.synchronize()
@@ -114,14 +114,38 @@ def status_word(device) -> torch.Tensor:
 
 
 def check_status(where: str = ""):
-    """Raise ``CommTimeout`` if any fused kernel gave up on a bounded wait since the last check."""
+    """Raise ``CommTimeout`` if any fused kernel gave up on a bounded wait since the last check, or ``RuntimeError`` if
+    a tcgen05 GEMM did (its error word is the second element of the same status tensor, so one read covers both)."""
     if STATUS is None:
         return
     from ..train.watchdog import raise_on_comm_status
-    vals = STATUS[:1].cpu()
+    vals = STATUS[:2].cpu()
     if int(vals[0]) != 0:
         STATUS.zero_()
-        raise_on_comm_status(vals, where)
+        raise_on_comm_status(vals[:1], where)
+    if int(vals[1]) != 0:
+        STATUS.zero_()
+        raise RuntimeError(f"tcgen05 GEMM: bounded wait expired (code {int(vals[1]):#x}) {where}")
+
+
+# Budget of every bounded wait of the fused kernels.  The default is far above ordinary rank skew (a rank that stalls on
+# the host for a checkpoint copy or a page-in holds the others' kernels in their waits); tests that let a wait run out
+# pass a short limit to the workspace they build.  ``--fused-comm-timeout-s`` / ``LMOE_COMM_TIMEOUT_S`` change it.
+_TIMEOUT_S = float(os.environ.get("LMOE_COMM_TIMEOUT_S", "20"))
+
+
+def set_timeout(seconds: float):
+    """Seconds a fused kernel waits for a peer before it records a timeout (applies to workspaces built afterwards)."""
+    global _TIMEOUT_S
+    _TIMEOUT_S = float(seconds)
+
+
+def default_spin_limit() -> int:
+    return max(1000, int(_TIMEOUT_S * 1_000_000))            # one poll of a remote flag is about a microsecond
+
+
+def default_spin_cycles() -> int:
+    return max(1_000_000, int(_TIMEOUT_S * 2_000_000_000))   # SM clock cycles at ~2 GHz
 
 
 def lasp2_scalar(q, k, v, g, scale, group):
@@ -198,7 +222,7 @@ class ZeroBufferWorkspace:
     """Symmetric parameter (bf16) and gradient (fp32) storage of one flat optimizer buffer plus the flags of its two
     barriers.  ``reduce`` and ``adam_broadcast`` are the two kernel launches of a fused ZeRO-1 step."""
 
-    def __init__(self, group, numel: int, device, spin_limit: int = 4_000_000, use_multicast: bool = True):
+    def __init__(self, group, numel: int, device, spin_limit: Optional[int] = None, use_multicast: bool = True):
         self.group, self.device, self.numel = group, device, numel
         self.W, self.rank = group.size, group.rank
         self.params, self.p_hdl = _symm_empty(numel, torch.bfloat16, device, group)
@@ -214,7 +238,7 @@ class ZeroBufferWorkspace:
         self.sumsq = torch.zeros(1, dtype=torch.float32, device=device)
         self.done_ctr = torch.zeros(1, dtype=torch.int32, device=device)
         self.epoch = 0
-        self.spin_limit = spin_limit
+        self.spin_limit = default_spin_limit() if spin_limit is None else spin_limit
         torch.cuda.synchronize()
         dist.barrier(group=group.pg)
 
@@ -283,7 +307,7 @@ class MoeWorkspace:
     """Receive buffer ``x [cap, h]``, result buffer ``y [cap, h]``, count matrix and flags of one expert-parallel group.
     ``group=None`` builds a one-rank workspace out of ordinary tensors (single-GPU use and tests)."""
 
-    def __init__(self, group, num_experts: int, hidden: int, cap_rows: int, device, spin_limit: int = 4_000_000):
+    def __init__(self, group, num_experts: int, hidden: int, cap_rows: int, device, spin_limit: Optional[int] = None):
         self.group, self.device = group, device
         self.W, self.rank = (group.size, group.rank) if group is not None else (1, 0)
         W = self.W
@@ -310,7 +334,7 @@ class MoeWorkspace:
             torch.tensor(p, dtype=torch.int64, device=device) for p in ptrs]
         self.done_ctr = torch.zeros(1, dtype=torch.int32, device=device)
         self.ep_exchange = self.ep_push = self.ep_pull = 0
-        self.spin_limit = spin_limit
+        self.spin_limit = default_spin_limit() if spin_limit is None else spin_limit
         torch.cuda.synchronize()
         if group is not None:
             dist.barrier(group=group.pg)
@@ -434,7 +458,7 @@ class TpWorkspace:
     ahead of a peer (every call needs data of every rank), so a slot is never overwritten while a peer still reads it."""
     NSLOT = 4
 
-    def __init__(self, group, max_shard_elems: int, device, spin_limit: int = 4_000_000):
+    def __init__(self, group, max_shard_elems: int, device, spin_limit: Optional[int] = None):
         self.group, self.device = group, device
         self.W, self.rank = group.size, group.rank
         assert self.W <= 8
@@ -450,8 +474,8 @@ class TpWorkspace:
         self.peer_flags = torch.tensor(list(hf.buffer_ptrs), dtype=torch.int64, device=device)
         self.done_ctr = torch.zeros(1, dtype=torch.int32, device=device)
         self.ag_calls = self.rs_calls = 0
-        self.spin_limit = spin_limit
-        self.spin_cycles = 4_000_000_000                      # ~2 s of SM clock
+        self.spin_limit = default_spin_limit() if spin_limit is None else spin_limit
+        self.spin_cycles = default_spin_cycles() if spin_limit is None else max(1_000_000, spin_limit * 1000)
         # all-gather -> GEMM: per-slot pointer tables of the published shards, scratch for the gathered matrix, row-block flags
         self.peer_x_slot = [torch.tensor([p + 2 * s * self.max_elems for p in self.x_ptrs], dtype=torch.int64, device=device)
                             for s in range(self.NSLOT)]

@@ -85,6 +85,7 @@ class Trainer:
         set_init_seed(tc.seed)
         if par.fused_comm and self.device.type == "cuda" and self.mesh.world_size > 1:
             from ..parallel import fused_comm
+            fused_comm.set_timeout(par.fused_comm_timeout_s)
             fused_comm.init_workspaces(self.mesh, cfg, tc)
         torch.manual_seed(tc.seed + 100 * self.mesh.pp_rank + 10 * self.mesh.dp_rank + self.mesh.cp_rank)
         sp = par.sequence_parallel and par.tp > 1
@@ -165,6 +166,14 @@ class Trainer:
         return fb(self.forward_step, data_iter, self.model, self.num_microbatches, mesh, shape,
                   self.cfg.params_dtype, opt, forward_only)
 
+    def _check_kernels(self, where: str = ""):
+        """Raise if a fused-communication kernel or a tcgen05 GEMM gave up on a bounded wait since the last check.
+        Called every step between the gradient-norm read (which has synchronised the device) and the parameter
+        update, and before a checkpoint is written, so a timed-out step never reaches the weights or the disk."""
+        if self.device.type == "cuda":
+            from ..parallel import fused_comm
+            fused_comm.check_status(where or f"iteration {self.iteration + 1}")
+
     def train_step(self) -> Dict[str, float]:
         tc, mesh = self.tc, self.mesh
         timers = self.timers
@@ -184,15 +193,12 @@ class Trainer:
         timers("all-grads-sync", 1).stop()
         timers("optimizer").start()
         lr, wd = self.scheduler.get_lr(), self.scheduler.get_wd()
-        ok, grad_norm, _ = self.optimizer.step(lr, wd)
+        ok, grad_norm, _ = self.optimizer.step(lr, wd, pre_update=self._check_kernels)
         timers("optimizer").stop()
         if ok:
             self.scheduler.step(1)
         self.iteration += 1
         self.consumed_samples += tc.global_batch_size
-        if self.device.type == "cuda" and self.iteration % max(tc.log_interval, 1) == 0:
-            from ..parallel import fused_comm
-            fused_comm.check_status(f"iteration {self.iteration}")         # a bounded wait of a fused kernel expired
         out = {"lr": lr, "grad_norm": grad_norm, "skipped": 0 if ok else 1}
         if mesh.is_last_stage and logs:
             keys = logs[0].keys()
@@ -279,6 +285,7 @@ class Trainer:
         t = torch.tensor([total, n], dtype=torch.float64, device=self.device)
         C.all_reduce_(t, self.mesh["world"])
         loss = (t[0] / t[1].clamp(min=1)).item()
+        self._check_kernels("evaluation")
         for m in self.models:
             m.train()
         return {"lm loss": loss, "ppl": math.exp(min(20.0, loss))}
@@ -288,6 +295,9 @@ class Trainer:
         from ..ckpt.legacy import save_checkpoint
         path = path or self.tc.save
         if path:
+            if self.device.type == "cuda":
+                torch.cuda.synchronize()
+            self._check_kernels("before checkpoint save")
             save_checkpoint(path, self.iteration, self.models, self.optimizer, self.scheduler, self.cfg, self.par,
                             self.tc, self.mesh, consumed_samples=self.consumed_samples)
 
@@ -299,7 +309,11 @@ class Trainer:
         if not model_only:
             self.iteration, self.consumed_samples = it, consumed
             self.data_iter.consumed = consumed
-        self.optimizer.reload_model_params()
+        if not getattr(self.optimizer, "state_loaded", False):
+            # weights only (pretrained / --no-load-optim / no optimizer file): derive the fp32 masters from them.
+            # After a full resume the restored masters are kept bit for bit (finetune_utils.py:319-327 reloads only
+            # on the pretrained-checkpoint path).
+            self.optimizer.reload_model_params()
 
     # ------------------------------------------------------------------
     def _should_exit(self) -> Optional[str]:
@@ -391,4 +405,6 @@ def pretrain(argv=None, dataset_provider: Optional[Callable] = None, model_provi
     stats = trainer.train()
     if tc.save:
         trainer.save()
+        from ..ckpt.legacy import finalize_async_saves
+        finalize_async_saves()
     return trainer, stats

@@ -241,9 +241,10 @@ class MixedPrecisionAdam:
         return total, torch.isfinite(total)
 
     @torch.no_grad()
-    def step(self, lr: float, weight_decay: float) -> Tuple[bool, Optional[float], int]:
+    def step(self, lr: float, weight_decay: float, pre_update=None) -> Tuple[bool, Optional[float], int]:
         """Returns (update_successful, grad_norm, num_zeros_in_grad) like Megatron's optimizer.step
-        (training.py:343-351)."""
+        (training.py:343-351).  ``pre_update`` is called after the gradient norm is known (the device is synchronised
+        then) and before any parameter is touched; it may raise to abandon the step."""
         tc = self.tc
         inv_scale = 1.0 if self.loss_scale is None else 1.0 / self.loss_scale
         total_sq, finite = self._grad_sq_and_finite()
@@ -257,6 +258,10 @@ class MixedPrecisionAdam:
         clip = 1.0
         if tc.clip_grad > 0 and grad_norm is not None and math.isfinite(grad_norm):
             clip = min(1.0, tc.clip_grad / (grad_norm + 1e-6))
+        if grad_norm is None and pre_update is not None and total_sq.is_cuda:
+            torch.cuda.synchronize()
+        if pre_update is not None:
+            pre_update()
         if grad_norm is not None and not math.isfinite(grad_norm) and tc.check_for_nan_in_loss_and_grad:
             raise FloatingPointError(f"non-finite gradient norm {grad_norm} on rank {self.mesh.rank}")
         self.step_count += 1

@@ -198,3 +198,59 @@ def test_indexed_dataset_and_index_builder(tmp_path):
         assert np.array_equal(a, b[: len(a)])
     batch = D.make_batch({"text": torch.arange(18)[None]}, eod_token=5, eod_mask_loss=True)
     assert batch["tokens"].shape == (1, 17) and batch["labels"][0, 5] == -100 and batch["loss_mask"][0, 5] == 0
+
+
+def test_resume_keeps_fp32_masters_bitwise(tmp_path):
+    """A full resume of a bf16 model restores the fp32 master weights exactly: re-deriving them from the bf16
+    parameters would drop their low bits (the reference reloads masters only on the pretrained-checkpoint path)."""
+    from linear_moe_b200.train.loop import Trainer
+    cfg = _cfg(use_la_module=True, la_module="retention", layer_type_list="LN", params_dtype=torch.bfloat16)
+    tc = TrainConfig(micro_batch_size=2, global_batch_size=2, seq_length=32, train_iters=3, log_interval=100,
+                     save=str(tmp_path), lr=1e-2, bf16=True)
+    tr = Trainer(cfg, ParallelConfig(), tc, device=torch.device("cpu"))
+    for _ in range(2):
+        tr.train_step()
+    tr.save()
+    masters = [b.master.clone() for b in tr.optimizer.buffers]
+    assert any((m != m.bfloat16().float()).any() for m in masters), "masters must carry bits below bf16 for this test"
+    tc2 = TrainConfig(micro_batch_size=2, global_batch_size=2, seq_length=32, train_iters=3, log_interval=100,
+                      load=str(tmp_path), lr=1e-2, bf16=True)
+    tr2 = Trainer(cfg, ParallelConfig(), tc2, device=torch.device("cpu"))
+    for m, b in zip(masters, tr2.optimizer.buffers):
+        assert torch.equal(m, b.master)
+    # weights only: masters are derived from the parameters
+    tc3 = TrainConfig(micro_batch_size=2, global_batch_size=2, seq_length=32, train_iters=3, log_interval=100,
+                      load=str(tmp_path), lr=1e-2, bf16=True, no_load_optim=True)
+    tr3 = Trainer(cfg, ParallelConfig(), tc3, device=torch.device("cpu"))
+    for b in tr3.optimizer.buffers:
+        assert torch.equal(b.master, b.shard_view(b.params).float())
+
+
+def test_async_save_publishes_tracker_after_writers(tmp_path):
+    """With --async-save the tracker file appears only once the writer threads have been joined (finalize)."""
+    from linear_moe_b200.train.loop import Trainer
+    cfg = _cfg(use_la_module=True, la_module="retention", layer_type_list="LN")
+    tc = TrainConfig(micro_batch_size=2, global_batch_size=2, seq_length=32, train_iters=3, log_interval=100,
+                     save=str(tmp_path), lr=1e-3, async_save=True)
+    tr = Trainer(cfg, ParallelConfig(), tc, device=torch.device("cpu"))
+    tr.train_step()
+    tr.save()
+    assert legacy._PENDING_TRACKERS and not (tmp_path / legacy.TRACKER).exists()
+    legacy.finalize_async_saves()
+    assert open(tmp_path / legacy.TRACKER).read() == "1"
+    assert (tmp_path / "iter_0000001" / "mp_rank_00" / "model_optim_rng.pt").exists()
+    tr.train_step()
+    tr.save()                                    # finalizes nothing pending, defers its own tracker again
+    tr.save()                                    # the second save first publishes the first one's tracker
+    assert open(tmp_path / legacy.TRACKER).read() == "2"
+    legacy.finalize_async_saves()
+
+
+def test_reference_te_style_norm_keys_are_mapped():
+    sd = {"decoder.layers.0.self_attention.linear_qkv.layer_norm_weight": torch.ones(4),
+          "decoder.layers.0.mlp.linear_fc1.layer_norm_weight": torch.zeros(4),
+          "decoder.layers.0.mlp.linear_fc1.weight": torch.zeros(8, 4),
+          "decoder.layers.0.mlp.linear_fc1._extra_state": None}
+    out = legacy.from_reference_keys(sd)
+    assert set(out) == {"decoder.layers.0.input_layernorm.weight", "decoder.layers.0.pre_mlp_layernorm.weight",
+                        "decoder.layers.0.mlp.linear_fc1.weight"}
