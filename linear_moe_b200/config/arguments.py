@@ -275,6 +275,9 @@ def build_parser() -> argparse.ArgumentParser:
     _flag(g, "--no-save-optim", action="store_true")
     _flag(g, "--no-save-rng", action="store_true")
     _flag(g, "--async-save", action="store_true")
+    _flag(g, "--use-dist-ckpt", action="store_true")
+    _flag(g, "--dist-ckpt-format", type=str, default="torch_dist", choices=["torch_dist", "zarr"])
+    _flag(g, "--auto-detect-ckpt-format", action="store_true")
     _flag(g, "--use-checkpoint-args", action="store_true")
     _flag(g, "--convert-checkpoint-from-megatron-to-transformers", action="store_true")
 
@@ -446,7 +449,8 @@ def configs_from_args(args: argparse.Namespace) -> Tuple[ModelConfig, ParallelCo
         eval_interval=args.eval_interval, eval_iters=args.eval_iters, save_interval=args.save_interval,
         save=args.save, load=args.load, pretrained_checkpoint=args.pretrained_checkpoint,
         no_load_optim=args.no_load_optim, no_load_rng=args.no_load_rng, no_save_optim=args.no_save_optim,
-        no_save_rng=args.no_save_rng, async_save=args.async_save, tensorboard_dir=args.tensorboard_dir,
+        no_save_rng=args.no_save_rng, async_save=args.async_save, use_dist_ckpt=args.use_dist_ckpt,
+        auto_detect_ckpt_format=args.auto_detect_ckpt_format, tensorboard_dir=args.tensorboard_dir,
         tensorboard_log_interval=args.tensorboard_log_interval,
         log_timers_to_tensorboard=args.log_timers_to_tensorboard,
         log_memory_to_tensorboard=args.log_memory_to_tensorboard,

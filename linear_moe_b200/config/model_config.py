@@ -255,6 +255,8 @@ class TrainConfig:
     no_save_optim: bool = False
     no_save_rng: bool = False
     async_save: bool = False
+    use_dist_ckpt: bool = False                   # sharded checkpoint format with reshard-on-load (ckpt/sharded.py)
+    auto_detect_ckpt_format: bool = False         # on load, take whichever format the directory holds
     tensorboard_dir: Optional[str] = None
     tensorboard_log_interval: int = 10
     log_timers_to_tensorboard: bool = False

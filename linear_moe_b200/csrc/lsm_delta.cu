@@ -1,0 +1,276 @@
+// (Gated) delta rule: the recurrence over chunks, forward and backward, as hand-written kernels.
+//
+//   S_t = e^{g_t} S_{t-1} + beta_t k_t^T (v_t - k_t e^{g_t} S_{t-1}),      o_t = scale * q_t S_t
+//
+// In the chunked (WY / UT-transform) form every chunk of C = 64 tokens is described by tiles that do not depend on
+// the state (computed chunk-parallel before this kernel):
+//   W  [C,dk]  pseudo keys      T (beta e^{b} K),        T = (I + tril(diag(beta) (K K^T . Gamma), -1))^{-1}
+//   U  [C,dv]  pseudo values    T (beta V)
+//   Qd [C,dk]  scale * e^{b_i} q_i           Kd [C,dk]  e^{b_C - b_j} k_j
+//   A  [C,C]   scale * tril((Q K^T) . Gamma)  (diagonal included),   Gamma_ij = e^{b_i - b_j},   gamma = e^{b_C}
+// and the state-dependent part is, per chunk with entering state S,
+//   Vn = U - W S,        O = Qd S + A Vn,        S' = gamma S + Kd^T Vn.
+// The columns of S are independent, so a (batch, head) sequence is split over dv / 32 CTAs (value slices) to fill the
+// machine; a CTA walks the chunks in order with its [dk x 32] state slice in fp32 registers and a bf16 copy in shared
+// memory as the B operand.  The forward kernel also writes Vn and the entering state of every chunk (bf16): with them
+// the gradients of W, U, Qd, Kd, A and gamma are chunk-parallel products; only the state gradient
+//   dVn = A^T dO + Kd dS',      dS = gamma dS' + Qd^T dO - W^T dVn
+// is a recurrence, walked in reverse by the backward kernel, which writes dVn and the dS' of every chunk.
+//
+// Reference counterpart: fla.ops.gated_delta_rule / delta_rule chunk kernels called by
+// sequence_modeling/gated_deltanet/gated_deltanet.py:99-116 and deltanet/deltanet.py:127-130.
+#include "mma_utils.cuh"
+
+namespace lmoe {
+namespace dr {
+
+constexpr int C = 64;            // chunk length
+constexpr int DVS = 32;          // value columns per CTA
+constexpr int NT = 128;          // threads
+
+struct Args {
+    const bf16 *W, *U, *Qd, *Kd, *A;   // [BH, N, C, dk] / [BH, N, C, dv] / [BH, N, C, C]
+    const float* gamma;                // [BH, N]
+    const float* S0;                   // [BH, dk, dv] or null
+    const bf16* dO;                    // backward: [BH, N, C, dv]
+    const float* dSfinal;              // backward: [BH, dk, dv] or null
+    bf16* O;                           // forward: [BH, N, C, dv]
+    bf16* Vn;                          // forward out / backward in: [BH, N, C, dv]
+    bf16* Sn;                          // forward out: state entering chunk n, [BH, N, dk, dv]
+    float* Sfinal;                     // forward out: [BH, dk, dv]
+    bf16* dVn;                         // backward out: [BH, N, C, dv]
+    bf16* dSn;                         // backward out: gradient of the state leaving chunk n, [BH, N, dk, dv]
+    float* dS0;                        // backward out: [BH, dk, dv]
+    int N, dv;
+};
+
+template <int DK> struct Cfg {
+    static constexpr int LDK = DK + 8;
+    static constexpr int LDC = C + 8;
+    static constexpr int LDV = DVS + 8;
+    static constexpr int RB = DK / 64;              // 16-row blocks of the state per warp (4 warps)
+    // shared memory (bf16 elements): 2 x {W, Qd, Kd: C x LDK; A: C x LDC; X (U or dO): C x LDV} + Sb [DK x LDV] + Vb [C x LDV] (+ Gb)
+    static constexpr int STAGE = 3 * C * LDK + C * LDC + C * LDV;
+    static constexpr size_t SMEM = (size_t)(2 * STAGE + DK * LDV + 2 * C * LDV) * 2;
+};
+
+template <int DK>
+__device__ __forceinline__ void issue_chunk(bf16* st, const Args& a, const bf16* xsrc, long long bh, int n, int col0) {
+    using F = Cfg<DK>;
+    const long long cn = bh * a.N + n;
+    load_tile_async<C, DK, F::LDK>(st, a.W + cn * C * DK, DK, C);
+    load_tile_async<C, DK, F::LDK>(st + C * F::LDK, a.Qd + cn * C * DK, DK, C);
+    load_tile_async<C, DK, F::LDK>(st + 2 * C * F::LDK, a.Kd + cn * C * DK, DK, C);
+    load_tile_async<C, C, F::LDC>(st + 3 * C * F::LDK, a.A + cn * C * C, C, C);
+    load_tile_async<C, DVS, F::LDV>(st + 3 * C * F::LDK + C * F::LDC, xsrc + cn * C * a.dv + col0, a.dv, C);
+}
+
+// write a [rows x DVS] bf16 tile held in shared memory (row stride LDV) to global rows of stride `gld`
+template <int LDV>
+__device__ __forceinline__ void store_rows(const bf16* s, bf16* g, int rows, long long gld) {
+    for (int i = threadIdx.x; i < rows * (DVS / 8); i += NT) {
+        const int r = i / (DVS / 8), c = (i % (DVS / 8)) * 8;
+        *reinterpret_cast<uint4*>(g + (long long)r * gld + c) = *reinterpret_cast<const uint4*>(s + r * LDV + c);
+    }
+}
+
+template <int DK>
+__global__ void __launch_bounds__(NT) delta_scan_fwd_kernel(Args a) {
+    using F = Cfg<DK>;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* stage = reinterpret_cast<bf16*>(smem_raw);
+    bf16* Sb = stage + 2 * F::STAGE;                 // [DK][LDV]
+    bf16* Vb = Sb + DK * F::LDV;                     // [C][LDV]  Vn of the chunk
+    bf16* Ob = Vb + C * F::LDV;                      // [C][LDV]  output staging
+    const int col0 = blockIdx.x * DVS;
+    const long long bh = blockIdx.y;
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+
+    // state slice: warp w owns rows [w*16*RB, +16*RB) x 32 columns
+    float S[F::RB][4][4];
+#pragma unroll
+    for (int rb = 0; rb < F::RB; ++rb) {
+        const int r = (w * F::RB + rb) * 16 + (l >> 2);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            const int c = col0 + nt * 8 + (l & 3) * 2;
+            if (a.S0 != nullptr) {
+                const float* p = a.S0 + (bh * DK + r) * a.dv + c;
+                S[rb][nt][0] = p[0]; S[rb][nt][1] = p[1];
+                S[rb][nt][2] = p[8 * a.dv]; S[rb][nt][3] = p[8 * a.dv + 1];
+            } else {
+                S[rb][nt][0] = S[rb][nt][1] = S[rb][nt][2] = S[rb][nt][3] = 0.f;
+            }
+        }
+        store_acc_bf16<4>(S[rb], Sb, F::LDV, (w * F::RB + rb) * 16, 0);
+    }
+    if (a.N > 0) issue_chunk<DK>(stage, a, a.U, bh, 0, col0);
+    cp_async_commit();
+    for (int n = 0; n < a.N; ++n) {
+        bf16* st = stage + (n & 1) * F::STAGE;
+        if (n + 1 < a.N) issue_chunk<DK>(stage + ((n + 1) & 1) * F::STAGE, a, a.U, bh, n + 1, col0);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();                                           // tiles of chunk n and Sb visible
+        const bf16* Wt = st;
+        const bf16* Qt = st + C * F::LDK;
+        const bf16* Kt = st + 2 * C * F::LDK;
+        const bf16* At = st + 3 * C * F::LDK;
+        const bf16* Ut = At + C * F::LDC;
+        const float gamma = a.gamma[bh * a.N + n];
+        // entering state of this chunk (bf16), for the backward pass
+        store_rows<F::LDV>(Sb, a.Sn + ((bh * a.N + n) * DK) * a.dv + col0, DK, a.dv);
+        // Vn = U - W S   (warp w: rows 16w .. 16w+15)
+        float acc[4][4];
+        zero_acc<4>(acc);
+        warp_gemm<4, DK, false, true>(acc, Wt, F::LDK, 16 * w, Sb, F::LDV, 0);
+        {
+            const int r = 16 * w + (l >> 2);
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const int c = nt * 8 + (l & 3) * 2;
+                const __nv_bfloat162 u0 = *reinterpret_cast<const __nv_bfloat162*>(Ut + r * F::LDV + c);
+                const __nv_bfloat162 u1 = *reinterpret_cast<const __nv_bfloat162*>(Ut + (r + 8) * F::LDV + c);
+                acc[nt][0] = __bfloat162float(u0.x) - acc[nt][0]; acc[nt][1] = __bfloat162float(u0.y) - acc[nt][1];
+                acc[nt][2] = __bfloat162float(u1.x) - acc[nt][2]; acc[nt][3] = __bfloat162float(u1.y) - acc[nt][3];
+            }
+        }
+        store_acc_bf16<4>(acc, Vb, F::LDV, 16 * w, 0);
+        // O = Qd S (needs only Sb) ...
+        float acc_o[4][4];
+        zero_acc<4>(acc_o);
+        warp_gemm<4, DK, false, true>(acc_o, Qt, F::LDK, 16 * w, Sb, F::LDV, 0);
+        __syncthreads();                                           // Vb complete; every read of Sb done
+        // ... + A Vn
+        warp_gemm<4, C, false, true>(acc_o, At, F::LDC, 16 * w, Vb, F::LDV, 0);
+        store_acc_bf16<4>(acc_o, Ob, F::LDV, 16 * w, 0);
+        // S <- gamma S + Kd^T Vn
+#pragma unroll
+        for (int rb = 0; rb < F::RB; ++rb) {
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) S[rb][nt][e] *= gamma;
+            warp_gemm<4, C, true, true>(S[rb], Kt, F::LDK, (w * F::RB + rb) * 16, Vb, F::LDV, 0);
+            store_acc_bf16<4>(S[rb], Sb, F::LDV, (w * F::RB + rb) * 16, 0);
+        }
+        __syncthreads();                                           // Ob, Vb, new Sb complete
+        store_rows<F::LDV>(Ob, a.O + ((bh * a.N + n) * C) * a.dv + col0, C, a.dv);
+        store_rows<F::LDV>(Vb, a.Vn + ((bh * a.N + n) * C) * a.dv + col0, C, a.dv);
+        __syncthreads();                                           // staging drained before the next chunk rewrites it
+    }
+#pragma unroll
+    for (int rb = 0; rb < F::RB; ++rb) {
+        const int r = (w * F::RB + rb) * 16 + (l >> 2);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            const int c = col0 + nt * 8 + (l & 3) * 2;
+            float* p = a.Sfinal + (bh * DK + r) * a.dv + c;
+            p[0] = S[rb][nt][0]; p[1] = S[rb][nt][1];
+            p[8 * a.dv] = S[rb][nt][2]; p[8 * a.dv + 1] = S[rb][nt][3];
+        }
+    }
+}
+
+// Reverse walk: dS' enters from the right (gradient of the state leaving the chunk).
+template <int DK>
+__global__ void __launch_bounds__(NT) delta_scan_bwd_kernel(Args a) {
+    using F = Cfg<DK>;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* stage = reinterpret_cast<bf16*>(smem_raw);
+    bf16* Sb = stage + 2 * F::STAGE;                 // [DK][LDV]  bf16 copy of dS'
+    bf16* Vb = Sb + DK * F::LDV;                     // [C][LDV]   dVn of the chunk
+    const int col0 = blockIdx.x * DVS;
+    const long long bh = blockIdx.y;
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+
+    float S[F::RB][4][4];
+#pragma unroll
+    for (int rb = 0; rb < F::RB; ++rb) {
+        const int r = (w * F::RB + rb) * 16 + (l >> 2);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            const int c = col0 + nt * 8 + (l & 3) * 2;
+            if (a.dSfinal != nullptr) {
+                const float* p = a.dSfinal + (bh * DK + r) * a.dv + c;
+                S[rb][nt][0] = p[0]; S[rb][nt][1] = p[1];
+                S[rb][nt][2] = p[8 * a.dv]; S[rb][nt][3] = p[8 * a.dv + 1];
+            } else {
+                S[rb][nt][0] = S[rb][nt][1] = S[rb][nt][2] = S[rb][nt][3] = 0.f;
+            }
+        }
+        store_acc_bf16<4>(S[rb], Sb, F::LDV, (w * F::RB + rb) * 16, 0);
+    }
+    if (a.N > 0) issue_chunk<DK>(stage, a, a.dO, bh, a.N - 1, col0);
+    cp_async_commit();
+    for (int i = 0; i < a.N; ++i) {
+        const int n = a.N - 1 - i;
+        bf16* st = stage + (i & 1) * F::STAGE;
+        if (n > 0) issue_chunk<DK>(stage + ((i + 1) & 1) * F::STAGE, a, a.dO, bh, n - 1, col0);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const bf16* Wt = st;
+        const bf16* Qt = st + C * F::LDK;
+        const bf16* Kt = st + 2 * C * F::LDK;
+        const bf16* At = st + 3 * C * F::LDK;
+        const bf16* Gt = At + C * F::LDC;             // dO slice
+        const float gamma = a.gamma[bh * a.N + n];
+        store_rows<F::LDV>(Sb, a.dSn + ((bh * a.N + n) * DK) * a.dv + col0, DK, a.dv);
+        // dVn = A^T dO + Kd dS'
+        float acc[4][4];
+        zero_acc<4>(acc);
+        warp_gemm<4, C, true, true>(acc, At, F::LDC, 16 * w, Gt, F::LDV, 0);
+        warp_gemm<4, DK, false, true>(acc, Kt, F::LDK, 16 * w, Sb, F::LDV, 0);
+        store_acc_bf16<4>(acc, Vb, F::LDV, 16 * w, 0);
+        __syncthreads();                                           // Vb complete; reads of Sb done
+        // dS = gamma dS' + Qd^T dO - W^T dVn
+#pragma unroll
+        for (int rb = 0; rb < F::RB; ++rb) {
+            float t[4][4];
+            zero_acc<4>(t);
+            warp_gemm<4, C, true, true>(t, Wt, F::LDK, (w * F::RB + rb) * 16, Vb, F::LDV, 0);
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) S[rb][nt][e] = S[rb][nt][e] * gamma - t[nt][e];
+            warp_gemm<4, C, true, true>(S[rb], Qt, F::LDK, (w * F::RB + rb) * 16, Gt, F::LDV, 0);
+            store_acc_bf16<4>(S[rb], Sb, F::LDV, (w * F::RB + rb) * 16, 0);
+        }
+        store_rows<F::LDV>(Vb, a.dVn + ((bh * a.N + n) * C) * a.dv + col0, C, a.dv);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int rb = 0; rb < F::RB; ++rb) {
+        const int r = (w * F::RB + rb) * 16 + (l >> 2);
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            const int c = col0 + nt * 8 + (l & 3) * 2;
+            float* p = a.dS0 + (bh * DK + r) * a.dv + c;
+            p[0] = S[rb][nt][0]; p[1] = S[rb][nt][1];
+            p[8 * a.dv] = S[rb][nt][2]; p[8 * a.dv + 1] = S[rb][nt][3];
+        }
+    }
+}
+
+}  // namespace dr
+}  // namespace lmoe
+
+using namespace lmoe;
+
+// dir 0: forward, dir 1: backward.  dk in {64, 128}; dv a multiple of 32.  Grid = (dv / 32, B*H).
+LMOE_API int lmoe_delta_scan(int dir, int dk, int BH, const dr::Args* ap, cudaStream_t st) {
+    const dr::Args a = *ap;
+    if (a.dv % dr::DVS || (dk != 64 && dk != 128) || BH <= 0) return -1;
+    dim3 grid(a.dv / dr::DVS, BH);
+#define LMOE_DR_LAUNCH(KERNEL, DK)                                                                                     \
+    do {                                                                                                               \
+        cudaError_t e = cudaFuncSetAttribute(KERNEL<DK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dr::Cfg<DK>::SMEM); \
+        if (e != cudaSuccess) return (int)e;                                                                           \
+        KERNEL<DK><<<grid, dr::NT, dr::Cfg<DK>::SMEM, st>>>(a);                                                        \
+    } while (0)
+    if (dir == 0) { if (dk == 128) LMOE_DR_LAUNCH(dr::delta_scan_fwd_kernel, 128); else LMOE_DR_LAUNCH(dr::delta_scan_fwd_kernel, 64); }
+    else { if (dk == 128) LMOE_DR_LAUNCH(dr::delta_scan_bwd_kernel, 128); else LMOE_DR_LAUNCH(dr::delta_scan_bwd_kernel, 64); }
+#undef LMOE_DR_LAUNCH
+    return (int)cudaGetLastError();
+}

@@ -222,7 +222,8 @@ class LSMCore(nn.Module):
         """Dispatch to LASP-2 when the sequence is split over the cp group, keep the decode cache."""
         g = self.mesh["cp"]
         init = cache.get(name) if cache is not None else None
-        o, S = lasp2(op, q, k, v, group=g, chunk_size=self.cfg.la_chunk_size, initial_state=init, **kw)
+        o, S = lasp2(op, q, k, v, group=g, chunk_size=self.cfg.la_chunk_size, initial_state=init,
+                     mode=self.cfg.la_mode if (init is None or self.cfg.la_mode != "parallel") else "chunk", **kw)
         if cache is not None:
             cache[name] = S.detach()
         return o
@@ -323,8 +324,8 @@ class LSMCore(nn.Module):
             w = self.la_output_norm.weight if self.la_output_norm is not None else None
         o = o.to(gate.dtype)
         if norm == "groupnorm":
-            y = R.group_norm_heads(o, w, self.la_output_norm.bias if self.la_output_norm is not None else None,
-                                   cfg.la_norm_eps).reshape(B, T, -1)
+            y = ops.group_norm_heads(o, w, self.la_output_norm.bias if self.la_output_norm is not None else None,
+                                     cfg.la_norm_eps).reshape(B, T, -1)
             return (y.float() * R.ACT2FN[cfg.la_gate_fn](gate.float())).to(gate.dtype)
         return ops.head_norm_gate(o.contiguous(), w, gate, cfg.la_norm_eps, cfg.la_gate_fn, norm)
 

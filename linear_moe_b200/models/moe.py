@@ -352,13 +352,41 @@ class MoELayer(nn.Module):
             out = C.all_to_all(out, ep, in_splits, out_splits)
         return out
 
+    def _experts_allgather(self, h: torch.Tensor, probs: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+        """All-gather token dispatcher (``--moe-token-dispatcher-type allgather``, token_dispatcher.py:69-291): every
+        rank of the TP x EP group gathers all tokens and their routing, keeps the copies routed to its local experts,
+        runs them, and the weighted outputs are reduce-scattered back to the token owners (which also sums the partial
+        outputs of tensor-parallel expert shards)."""
+        mesh = self.mesh
+        g = mesh["tp_ep"] if not mesh["tp"].is_trivial else mesh["ep"]
+        T = h.shape[0]
+        if g.is_trivial:
+            permuted, order, counts = permute(h, idx, self.E)
+            return unpermute(self.experts(permuted, counts), order, probs, T, self.k)
+        h_all = C.all_gather(h, g, dim=0)                                     # backward: reduce-scatter of the gradients
+        probs_all = C.all_gather(probs, g, dim=0)
+        idx_all = C.all_gather_raw(idx.contiguous(), g, dim=0)
+        lo = mesh.ep_rank * self.El
+        local = (idx_all >= lo) & (idx_all < lo + self.El)
+        idx_loc = torch.where(local, idx_all - lo, torch.full_like(idx_all, -1))
+        permuted, order, counts = permute(h_all, idx_loc, self.El)
+        y = self.experts(permuted, counts)
+        out_all = unpermute(y, order, probs_all, h_all.shape[0], self.k)
+        return C.reduce_scatter(out_all, g, dim=0)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         shape = x.shape
         h = x.reshape(-1, shape[-1])
         T = h.shape[0]
         probs, idx = self.router(h)
-        ws = self._fused_workspace(h)
-        if ws is not None:
+        if self.cfg.moe_token_dispatcher_type == "allgather":
+            out = self._experts_allgather(h, probs, idx).reshape(shape)
+            ws = False
+        else:
+            ws = self._fused_workspace(h)
+        if ws is False:
+            pass
+        elif ws is not None:
             from ..ops.moe_fused import fused_moe
             tp = self.mesh.tp
             if tp > 1:

@@ -56,8 +56,7 @@ class Norm(nn.Module):
         if residual is None:
             return self(x), x
         if self.kind == "LayerNorm":
-            r = x + residual
-            return ops.layer_norm(r, self.weight, self.bias, self.eps), r
+            return ops.add_layer_norm(x, residual, self.weight, self.bias, self.eps)
         return ops.add_rms_norm(x, residual, self.weight, self.eps)
 
 

@@ -169,7 +169,24 @@ def add_rms_norm(x, residual, weight, eps: float = 1e-6):
 
 
 def layer_norm(x, weight, bias, eps: float = 1e-5):
+    if _cuda(x):
+        return _K().layer_norm(x, weight, bias, eps)
     return R.layer_norm(x, weight, bias, eps)
+
+
+def add_layer_norm(x, residual, weight, bias, eps: float = 1e-5):
+    """``r = x + residual; y = layernorm(r)``; returns ``(y, r)`` (the LayerNorm counterpart of :func:`add_rms_norm`)."""
+    if _cuda(x):
+        return _K().add_layer_norm(x, residual, weight, bias, eps)
+    r = x + residual
+    return R.layer_norm(r, weight, bias, eps), r
+
+
+def group_norm_heads(x, weight=None, bias=None, eps: float = 1e-5):
+    """GroupNorm with one group per head over ``[..., H, d]`` = LayerNorm over the head dimension (same kernel on CUDA)."""
+    if _cuda(x):
+        return _K().layer_norm(x, weight, bias, eps)
+    return R.group_norm_heads(x, weight, bias, eps)
 
 
 def gated_rms_norm(x, z, weight, eps: float = 1e-5, group_size: Optional[int] = None):
@@ -187,7 +204,7 @@ def head_norm_gate(o, weight, gate, eps: float = 1e-5, gate_fn: str = "swish", n
     if norm == "rmsnorm":
         y = R.rms_norm(o, weight, eps)
     elif norm == "groupnorm":
-        y = R.group_norm_heads(o, weight, None, eps)
+        y = group_norm_heads(o, weight, None, eps)
     else:
         y = o
     y = y.reshape(B, T, H * dv)

@@ -286,6 +286,63 @@ class _RMSNorm(torch.autograd.Function):
         return dx, (dx if ctx.has_res else None), dw, None, None
 
 
+class _LayerNorm(torch.autograd.Function):
+    """LayerNorm (+ fused residual add) on the kernels of ``csrc/layernorm.cu``."""
+
+    @staticmethod
+    def forward(ctx, x, residual, weight, bias, eps, want_residual):
+        N = x.shape[-1]
+        xc = x.contiguous()
+        rc = None if residual is None else residual.contiguous()
+        w, b = _same_dtype(xc, weight, bias)
+        rows = xc.numel() // N
+        y = torch.empty_like(xc)
+        res_out = torch.empty_like(xc) if rc is not None else None
+        mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        _check(lib().lmoe_layer_norm_fwd(_p(xc), _p(rc), _p(w), _p(b), _p(y), _p(res_out), _p(mean), _p(rstd), _i64(rows),
+                                         _i32(N), _f32(eps), _i32(_dt(xc)), _st()), "layer_norm_fwd")
+        xin = res_out if rc is not None else xc
+        ctx.save_for_backward(xin, w, mean, rstd)
+        ctx.has_res = rc is not None
+        ctx.wdtype = None if weight is None else weight.dtype
+        ctx.bdtype = None if bias is None else bias.dtype
+        if want_residual:
+            return y, xin
+        return y
+
+    @staticmethod
+    def backward(ctx, dy, dres=None):
+        xin, w, mean, rstd = ctx.saved_tensors
+        N = xin.shape[-1]
+        rows = xin.numel() // N
+        dy = dy.contiguous()
+        dres = None if dres is None else dres.contiguous()
+        dx = torch.empty_like(xin)
+        P = min(rows, _PARTIAL_BLOCKS)
+        want = ctx.wdtype is not None or ctx.bdtype is not None
+        partial = torch.empty(P, 2 * N, dtype=torch.float32, device=xin.device) if want else None
+        dwdb = torch.empty(2 * N, dtype=torch.float32, device=xin.device) if want else None
+        _check(lib().lmoe_layer_norm_bwd(_p(dy), _p(xin), _p(w), _p(mean), _p(rstd), _p(dres), _p(dx), _p(partial), _p(dwdb),
+                                         _i64(rows), _i32(N), _i32(P), _i32(_dt(xin)), _st()), "layer_norm_bwd", 2)
+        dw = None if ctx.wdtype is None else dwdb[:N].to(ctx.wdtype)
+        db = None if ctx.bdtype is None else dwdb[N:].to(ctx.bdtype)
+        return dx, (dx if ctx.has_res else None), dw, db, None, None
+
+
+def layer_norm(x, weight=None, bias=None, eps: float = 1e-5):
+    if not _rms_ok(x):
+        return R.layer_norm(x, weight, bias, eps)
+    return _LayerNorm.apply(x, None, weight, bias, eps, False)
+
+
+def add_layer_norm(x, residual, weight, bias, eps: float = 1e-5):
+    if not _rms_ok(x) or residual.dtype != x.dtype:
+        r = x + residual
+        return R.layer_norm(r, weight, bias, eps), r
+    return _LayerNorm.apply(x, residual, weight, bias, eps, True)
+
+
 def _rms_ok(x):
     N = x.shape[-1]
     vn = 8 if x.dtype == torch.bfloat16 else 4
@@ -981,10 +1038,149 @@ class _tf32:
         torch.backends.cuda.matmul.allow_tf32 = self.prev
 
 
+class _DeltaArgs(ctypes.Structure):
+    _fields_ = ([(n, ctypes.c_void_p) for n in ("W", "U", "Qd", "Kd", "A", "gamma", "S0", "dO", "dSfinal", "O", "Vn", "Sn",
+                                                 "Sfinal", "dVn", "dSn", "dS0")] + [("N", ctypes.c_int), ("dv", ctypes.c_int)])
+
+
+def _delta_prepare(q, k, v, beta, g, scale, C=64):
+    """State-independent tiles of the chunked (gated) delta rule (WY / UT transform), chunk-parallel, differentiable:
+    ``W, U, Qd, Kd`` ``[B,H,N,C,d]``, ``A`` ``[B,H,N,C,C]`` in bf16 and ``gamma`` ``[B,H,N]`` fp32 (see csrc/lsm_delta.cu)."""
+    B, T, H, dk = q.shape
+    f = torch.float32
+    N = (T + C - 1) // C
+    pad = N * C - T
+
+    def chunks(x):                                   # [B,T,H,...] -> [B,H,N,C,...]
+        x = x.to(f)
+        if pad:
+            x = F.pad(x, (0, 0) * (x.dim() - 2) + (0, pad))
+        x = x.reshape(B, N, C, *x.shape[2:])
+        return x.permute(0, 3, 1, 2, *range(4, x.dim())).contiguous()
+    qc, kc, vc = chunks(q), chunks(k), chunks(v)
+    bc = chunks(beta)                                                           # [B,H,N,C]
+    if g is None:
+        b = torch.zeros_like(bc)
+    else:
+        b = chunks(g).cumsum(-1)
+    tril = torch.ones(C, C, dtype=torch.bool, device=q.device).tril()
+    L = torch.where(tril, b[..., :, None] - b[..., None, :], torch.full((), float("-inf"), device=q.device)).exp()
+    A_ = ((kc @ kc.transpose(-1, -2)) * L * bc[..., None]).tril(-1)
+    eb = b.exp()
+    rhs = torch.cat([vc * bc[..., None], kc * (bc * eb)[..., None]], dim=-1)
+    eye = torch.eye(C, dtype=f, device=q.device)
+    sol = torch.linalg.solve_triangular(eye + A_, rhs, upper=False, unitriangular=True)
+    dv = v.shape[-1]
+    U, W = sol[..., :dv], sol[..., dv:]
+    qs = qc * scale
+    Aqk = (qs @ kc.transpose(-1, -2)) * L
+    btot = b[..., -1]
+    Qd = qs * eb[..., None]
+    Kd = kc * (btot[..., None] - b).exp()[..., None]
+    bf = torch.bfloat16
+    return W.to(bf), U.to(bf).contiguous(), Qd.to(bf), Kd.to(bf), Aqk.to(bf), btot.exp().contiguous()
+
+
+class _DeltaChunkScan(torch.autograd.Function):
+    """The recurrence over chunks of the (gated) delta rule on the kernels of ``csrc/lsm_delta.cu``:
+    ``Vn = U - W S``, ``O = Qd S + A Vn``, ``S' = gamma S + Kd^T Vn``.  Backward: the reverse state-gradient recurrence is
+    the second kernel; the gradients of the tiles are chunk-parallel products of what the two kernels wrote."""
+
+    @staticmethod
+    def forward(ctx, W, U, Qd, Kd, A, gamma, S0):
+        B, H, N, C, dk = W.shape
+        dv = U.shape[-1]
+        dev = W.device
+        bf = torch.bfloat16
+        O = torch.empty(B, H, N, C, dv, dtype=bf, device=dev)
+        Vn = torch.empty(B, H, N, C, dv, dtype=bf, device=dev)
+        Sn = torch.empty(B, H, N, dk, dv, dtype=bf, device=dev)
+        Sf = torch.empty(B, H, dk, dv, dtype=torch.float32, device=dev)
+        s0 = None if S0 is None else S0.float().contiguous()
+        a = _DeltaArgs()
+        a.W, a.U, a.Qd, a.Kd, a.A, a.gamma = (t.data_ptr() for t in (W, U, Qd, Kd, A, gamma))
+        a.S0 = 0 if s0 is None else s0.data_ptr()
+        a.O, a.Vn, a.Sn, a.Sfinal = O.data_ptr(), Vn.data_ptr(), Sn.data_ptr(), Sf.data_ptr()
+        a.N, a.dv = N, dv
+        _check(lib().lmoe_delta_scan(_i32(0), _i32(dk), _i32(B * H), ctypes.byref(a), _st()), "delta_scan_fwd")
+        ctx.save_for_backward(W, Qd, Kd, A, gamma, Vn, Sn)
+        ctx.has_s0 = S0 is not None
+        return O, Sf
+
+    @staticmethod
+    def backward(ctx, dO, dSf):
+        W, Qd, Kd, A, gamma, Vn, Sn = ctx.saved_tensors
+        B, H, N, C, dk = W.shape
+        dv = Vn.shape[-1]
+        dev = W.device
+        bf = torch.bfloat16
+        dO = dO.to(bf).contiguous()
+        dVn = torch.empty(B, H, N, C, dv, dtype=bf, device=dev)
+        dSn = torch.empty(B, H, N, dk, dv, dtype=bf, device=dev)
+        dS0 = torch.empty(B, H, dk, dv, dtype=torch.float32, device=dev)
+        dsf = None if dSf is None else dSf.float().contiguous()
+        a = _DeltaArgs()
+        a.W, a.Qd, a.Kd, a.A, a.gamma = (t.data_ptr() for t in (W, Qd, Kd, A, gamma))
+        a.U = 0
+        a.dO, a.dSfinal = dO.data_ptr(), 0 if dsf is None else dsf.data_ptr()
+        a.dVn, a.dSn, a.dS0 = dVn.data_ptr(), dSn.data_ptr(), dS0.data_ptr()
+        a.N, a.dv = N, dv
+        _check(lib().lmoe_delta_scan(_i32(1), _i32(dk), _i32(B * H), ctypes.byref(a), _st()), "delta_scan_bwd")
+        SnT = Sn.transpose(-1, -2)
+        dW = -(dVn @ SnT)
+        dQd = dO @ SnT
+        dA = (dO @ Vn.transpose(-1, -2)).tril()
+        dKd = Vn @ dSn.transpose(-1, -2)
+        dgamma = (dSn.float() * Sn.float()).sum((-1, -2))
+        return dW, dVn, dQd, dKd, dA, dgamma, (dS0 if ctx.has_s0 else None)
+
+
 class _DeltaRuleScan(torch.autograd.Function):
-    """(Gated) delta rule as batched tensor-core matmuls: WY/UT transform per chunk, a parallel scan over the chunks'
-    affine state maps, then all chunk outputs at once.  The backward recomputes the forward (nothing but the inputs
-    is kept) and differentiates it."""
+    """(Gated) delta rule.  Forward: chunk-parallel WY/UT tiles (batched tensor-core matmuls + a triangular solve), then
+    the scan kernel.  Only the inputs are kept; the backward rebuilds the tiles with autograd enabled, runs both scan
+    kernels and differentiates the tile construction."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, beta, g, initial_state, scale, chunk_size):
+        B, T, H, dk = q.shape
+        scale = dk ** -0.5 if scale is None else scale
+        with torch.no_grad(), _tf32():
+            tiles = _delta_prepare(q, k, v, beta, g, scale)
+            O, S = _DeltaChunkScan.apply(*tiles, initial_state)
+        ctx.save_for_backward(q, k, v, beta, g, initial_state)
+        ctx.scale = scale
+        o = O.permute(0, 2, 3, 1, 4).reshape(B, -1, H, v.shape[-1])[:, :T]
+        return o.to(q.dtype), S
+
+    @staticmethod
+    def backward(ctx, do, dS):
+        saved = ctx.saved_tensors
+        ins = [None if t is None else t.detach().requires_grad_(t.is_floating_point()) for t in saved]
+        q = ins[0]
+        B, T, H, dk = q.shape
+        with torch.enable_grad(), _tf32():
+            tiles = _delta_prepare(*ins[:5], ctx.scale)
+            O, S = _DeltaChunkScan.apply(*tiles, ins[5])
+            N, C = O.shape[2], O.shape[3]
+            dO = do.to(O.dtype)
+            if N * C != T:
+                dO = F.pad(dO, (0, 0, 0, 0, 0, N * C - T))
+            dO = dO.reshape(B, N, C, H, -1).permute(0, 3, 1, 2, 4)
+            outs, gouts = [O], [dO]
+            if dS is not None:
+                outs.append(S)
+                gouts.append(dS)
+            need = [t for t in ins if t is not None]
+            grads = torch.autograd.grad(outs, need, gouts, allow_unused=True)
+        it = iter(grads)
+        full = [None if t is None else next(it) for t in ins]
+        full = [None if gr is None else gr.to(t.dtype) for gr, t in zip(full, ins)]
+        return (*full, None, None)
+
+
+class _DeltaRuleTorch(torch.autograd.Function):
+    """Eager form of the (gated) delta rule for shapes the scan kernels do not take (head dims other than 64 / 128, value
+    width not a multiple of 32): batched matmuls with a parallel scan over the chunks' affine state maps."""
 
     @staticmethod
     def forward(ctx, q, k, v, beta, g, initial_state, scale, chunk_size):
@@ -1018,7 +1214,9 @@ def lsm_delta(q, k, v, beta, g, scale, initial_state, chunk_size):
             and k.shape[-1] == D and v.shape[-1] == D and D in (64, 128)
             and not (torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, beta, g)))):
         return _lsm_delta_step(q, k, v, beta, g, D ** -0.5 if scale is None else scale, initial_state)
-    return _DeltaRuleScan.apply(q, k, v, beta, g, initial_state, scale, chunk_size)
+    if q.is_cuda and D in (64, 128) and k.shape[-1] == D and v.shape[-1] % 32 == 0 and os.environ.get("LMOE_DELTA_KERNEL", "1") != "0":
+        return _DeltaRuleScan.apply(q, k, v, beta, g, initial_state, scale, chunk_size)
+    return _DeltaRuleTorch.apply(q, k, v, beta, g, initial_state, scale, chunk_size)
 
 
 def _lsm_delta_step(q, k, v, beta, g, scale, initial_state):

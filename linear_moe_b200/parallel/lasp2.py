@@ -62,12 +62,56 @@ def _apply(kind: str, A, P):
     return A @ P
 
 
+def _recurrent(kind, q, k, v, g, gk, beta, scale, init, bonus):
+    """``--la-mode fused_recurrent``: the token-by-token recurrence (exact, O(T) sequential steps)."""
+    from ..ref import lsm as RL
+    if bonus is not None:
+        raise ValueError("--la-mode fused_recurrent is not available for RWKV6's bonus term; use chunk")
+    B, T, H, _ = q.shape
+    gg = g if (g is None or g.dim() == 3) else g[None, None, :].expand(B, T, H)
+    o, S = RL.recurrent_lsm(q, k, v, g=gg, gk=gk, beta=beta, scale=scale, initial_state=init)
+    return o.to(v.dtype), S
+
+
+def _parallel(kind, q, k, v, g, scale, init):
+    """``--la-mode parallel``: the quadratic (attention-like) form ``o = ((Q K^T) . decay mask) V`` of the scalar-decay
+    family; the final state is one extra weighted sum."""
+    if kind != "scalar" or init is not None:
+        raise ValueError("--la-mode parallel exists for the scalar-decay family without an initial state only")
+    B, T, H, dk = q.shape
+    f = torch.float32
+    scale = dk ** -0.5 if scale is None else scale
+    if g is None:
+        b = torch.zeros(B, T, H, dtype=f, device=q.device)
+    elif g.dim() == 1:
+        b = g.to(f)[None, None, :] * torch.arange(1, T + 1, device=q.device, dtype=f)[None, :, None]
+    else:
+        b = g.to(f).cumsum(1)
+    bt = b.permute(0, 2, 1)                                                  # [B,H,T]
+    diff = bt[..., :, None] - bt[..., None, :]
+    mask = torch.ones(T, T, dtype=torch.bool, device=q.device).tril()
+    dec = torch.where(mask, diff, torch.full((), float("-inf"), device=q.device)).exp()
+    s = torch.einsum("bihd,bjhd->bhij", q.to(f) * scale, k.to(f)) * dec
+    o = torch.einsum("bhij,bjhd->bihd", s, v.to(f))
+    kd = k.to(f) * (bt[..., -1:] - bt).exp().permute(0, 2, 1)[..., None]
+    S = torch.einsum("bjhk,bjhv->bhkv", kd, v.to(f))
+    return o.to(v.dtype), S
+
+
 def lasp2(kind: str, q, k, v, *, group: Group, g=None, gk=None, beta=None, scale=None,
-          chunk_size: int = 64, bonus=None, initial_state=None) -> Tuple[torch.Tensor, torch.Tensor]:
+          chunk_size: int = 64, bonus=None, initial_state=None, mode: str = "chunk") -> Tuple[torch.Tensor, torch.Tensor]:
     """Run a linear sequence model whose sequence is split over ``group`` (rank order = sequence
     order).  ``kind``: ``scalar`` | ``vector`` | ``delta``.  Returns the local output and the state
-    after this rank's slice."""
+    after this rank's slice.  ``mode`` (``--la-mode``): ``chunk`` / ``fused_chunk`` = the chunked kernels (one fused
+    implementation serves both names), ``fused_recurrent`` = token recurrence, ``parallel`` = quadratic form."""
+    if mode not in ("chunk", "fused_chunk", "fused_recurrent", "parallel"):
+        raise ValueError(f"unknown --la-mode {mode!r}")
+
     def run(init):
+        if mode == "fused_recurrent":
+            return _recurrent(kind, q, k, v, g, gk, beta, scale, init, bonus)
+        if mode == "parallel":
+            return _parallel(kind, q, k, v, g, scale, init)
         if kind == "scalar":
             return ops.lsm_scalar(q, k, v, g, scale, init, chunk_size)
         if kind == "vector":
@@ -76,7 +120,10 @@ def lasp2(kind: str, q, k, v, *, group: Group, g=None, gk=None, beta=None, scale
 
     if group.is_trivial:
         return run(initial_state)
-    if q.is_cuda and kind == "scalar" and initial_state is None and ops._K().fused_lasp_available(group, q, k, v, g):
+    if mode == "parallel":
+        raise ValueError("--la-mode parallel cannot be combined with sequence parallelism (the quadratic form has no state)")
+    if (q.is_cuda and kind == "scalar" and initial_state is None and mode != "fused_recurrent"
+            and ops._K().fused_lasp_available(group, q, k, v, g)):
         return ops._K().lasp2_scalar(q, k, v, g, scale, group, chunk_size)
 
     M, A = _summaries(kind, q, k, v, g, gk, beta, scale, chunk_size, bonus)

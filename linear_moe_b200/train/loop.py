@@ -298,11 +298,40 @@ class Trainer:
             if self.device.type == "cuda":
                 torch.cuda.synchronize()
             self._check_kernels("before checkpoint save")
+            if self.tc.use_dist_ckpt:
+                from ..ckpt.sharded import save_sharded
+                save_sharded(path, self.iteration, self.models, self.cfg, self.mesh,
+                             None if self.tc.no_save_optim else self.optimizer, layer_offsets=self._layer_offsets(),
+                             extra={"consumed_samples": self.consumed_samples,
+                                    "opt_param_scheduler": self.scheduler.state_dict()})
+                return
             save_checkpoint(path, self.iteration, self.models, self.optimizer, self.scheduler, self.cfg, self.par,
                             self.tc, self.mesh, consumed_samples=self.consumed_samples)
 
+    def _layer_offsets(self):
+        """Global index of the first layer of every model chunk of this pipeline stage."""
+        per = self.cfg.num_layers // (self.mesh.pp * len(self.models))
+        return [(i * self.mesh.pp + self.mesh.pp_rank) * per for i in range(len(self.models))]
+
     def load(self, path: str, model_only: bool = False):
+        from ..ckpt import sharded
         from ..ckpt.legacy import load_checkpoint
+        has_sharded = os.path.isfile(os.path.join(path, sharded.TRACKER))
+        if (self.tc.use_dist_ckpt or (self.tc.auto_detect_ckpt_format and has_sharded)) and has_sharded:
+            opt = None if (model_only or self.tc.no_load_optim) else self.optimizer
+            if opt is not None:
+                opt.state_loaded = False
+            it, extra = sharded.load_sharded(path, self.models, self.cfg, self.mesh, opt, layer_offsets=self._layer_offsets(),
+                                             return_extra=True)
+            if not model_only:
+                self.iteration = it
+                self.consumed_samples = int(extra.get("consumed_samples", 0))
+                self.data_iter.consumed = self.consumed_samples
+                if "opt_param_scheduler" in extra:
+                    self.scheduler.load_state_dict(extra["opt_param_scheduler"])
+            if not getattr(self.optimizer, "state_loaded", False):
+                self.optimizer.reload_model_params()
+            return
         it, consumed = load_checkpoint(path, self.models, None if (model_only or self.tc.no_load_optim) else self.optimizer,
                                        None if model_only else self.scheduler, self.mesh,
                                        load_rng=not (model_only or self.tc.no_load_rng))

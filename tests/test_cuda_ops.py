@@ -195,6 +195,49 @@ def test_fused_adam():
     close(p, w2.to(torch.bfloat16), 0, 0, "bf16 copy")
 
 
+@pytest.mark.parametrize("N,rows", [(2048, 300), (128, 1000), (4096, 64), (1024, 33)])
+@pytest.mark.parametrize("residual", [False, True])
+def test_layer_norm(N, rows, residual):
+    """LayerNorm (+ residual add) kernels against F.layer_norm in fp32: y, dx, dres, dw, db."""
+    torch.manual_seed(0)
+    x = torch.randn(rows, N, device=dev(), dtype=torch.bfloat16)
+    r = torch.randn(rows, N, device=dev(), dtype=torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(N, device=dev())).to(torch.bfloat16)
+    b = (0.1 * torch.randn(N, device=dev())).to(torch.bfloat16)
+    gy = torch.randn(rows, N, device=dev(), dtype=torch.bfloat16)
+    gr = torch.randn(rows, N, device=dev(), dtype=torch.bfloat16)
+    K.reset_launch_count()
+    if residual:
+        f_k = lambda x, r, w, b: ops.add_layer_norm(x, r, w, b, 1e-5)
+        f_r = lambda x, r, w, b: (R.layer_norm(x + r, w, b, 1e-5), x + r)
+        (y, ro), gk = grads(f_k, [x, r, w, b], (gy, gr))
+        (y2, ro2), gr_ = grads(f_r, [x.float(), r.float(), w.float(), b.float()], (gy.float(), gr.float()))
+        close(ro, ro2, 2e-2, 2e-2, "residual out")
+        names = ["dx", "dres", "dw", "db"]
+    else:
+        f_k = lambda x, w, b: ops.layer_norm(x, w, b, 1e-5)
+        f_r = lambda x, w, b: R.layer_norm(x, w, b, 1e-5)
+        (y,), gk = grads(f_k, [x, w, b], gy)
+        (y2,), gr_ = grads(f_r, [x.float(), w.float(), b.float()], gy.float())
+        names = ["dx", "dw", "db"]
+    assert K.reset_launch_count() >= 2, "the LayerNorm kernels did not run"
+    close(y, y2, 2e-2, 2e-2, "y")
+    for name, a_, b_ in zip(names, gk, gr_):
+        rel = ((a_.float() - b_).norm() / b_.norm().clamp_min(1e-6)).item()
+        assert rel < 2e-2, (name, rel)
+
+
+def test_group_norm_heads_uses_layer_norm_kernel():
+    torch.manual_seed(1)
+    o = torch.randn(2, 70, 3, 128, device=dev(), dtype=torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(128, device=dev())).to(torch.bfloat16)
+    b = (0.1 * torch.randn(128, device=dev())).to(torch.bfloat16)
+    K.reset_launch_count()
+    y = ops.group_norm_heads(o, w, b, 1e-5)
+    assert K.reset_launch_count() == 1
+    close(y, R.group_norm_heads(o.float(), w.float(), b.float(), 1e-5), 2e-2, 2e-2, "y")
+
+
 @pytest.mark.parametrize("D", [128, 64])
 @pytest.mark.parametrize("gmode", ["none", "const", "token"])
 @pytest.mark.parametrize("T,with_state", [(1000, False), (256, True), (70, True)])
@@ -307,18 +350,22 @@ def test_ssd_mamba2_on_scalar_kernels():
         close(a, b, 5e-2, 3e-2 * b.abs().max().item(), name)
 
 
-@pytest.mark.parametrize("gated,with_state", [(True, False), (False, True)])
-def test_lsm_delta_rule_scan(gated, with_state):
-    """(Gated) delta rule on the GPU (WY transform + parallel scan over chunk maps, TF32) against the token-by-token
-    fp32 recurrence."""
+@pytest.mark.parametrize("D", [64, 128])
+@pytest.mark.parametrize("T", [70, 256, 1000])
+@pytest.mark.parametrize("gated,with_state", [(True, False), (False, True), (True, True), (False, False)])
+def test_lsm_delta_rule_scan(gated, with_state, T, D):
+    """(Gated) delta rule on the GPU (chunk-parallel WY tiles + the scan kernels of csrc/lsm_delta.cu, forward and
+    backward) against the token-by-token fp32 recurrence: output, final state and every gradient (relative Frobenius
+    error), with and without an initial state / a gradient on the final state."""
     torch.manual_seed(4)
-    B, T, H, D = 2, 300, 2, 64
+    B, H = 2, 2
     q, v = [(0.5 * torch.randn(B, T, H, D, device=dev())).to(torch.bfloat16) for _ in range(2)]
     k = torch.nn.functional.normalize(torch.randn(B, T, H, D, device=dev()), dim=-1).to(torch.bfloat16)
     beta = torch.rand(B, T, H, device=dev())
     g = torch.nn.functional.logsigmoid(torch.randn(B, T, H, device=dev()) + 2.0) if gated else None
     S0 = 0.2 * torch.randn(B, H, D, D, device=dev()) if with_state else None
     go = torch.randn(B, T, H, D, device=dev()).to(torch.bfloat16)
+    gS = 0.05 * torch.randn(B, H, D, D, device=dev()) if with_state else None
     ins = [q, k, v, beta] + ([g] if gated else []) + ([S0] if with_state else [])
 
     def unpack(a):
@@ -327,14 +374,20 @@ def test_lsm_delta_rule_scan(gated, with_state):
         gg = a[4] if gated else None
         s = a[-1] if with_state else None
         return q, k, v, beta, gg, s
-    f_k = lambda *a: ops.lsm_delta(*unpack(a)[:5], None, unpack(a)[5], 64)[0]
+    K.reset_launch_count()
+    f_k = lambda *a: ops.lsm_delta(*unpack(a)[:5], None, unpack(a)[5], 64)
     f_r = lambda *a: RL.recurrent_lsm(unpack(a)[0], unpack(a)[1], unpack(a)[2], beta=unpack(a)[3], g=unpack(a)[4],
-                                      initial_state=unpack(a)[5])[0]
-    (o,), gk = grads(f_k, ins, go)
-    (o2,), gr = grads(f_r, [t.float() for t in ins], go.float())
-    close(o, o2, 3e-2, 2e-2 * o2.abs().max().item(), "o")
+                                      initial_state=unpack(a)[5])
+    (o, S), gk = grads(f_k, ins, (go, gS))
+    assert K.reset_launch_count() >= 2, "the delta-rule scan kernels did not run"
+    (o2, S2), gr = grads(f_r, [t.float() for t in ins], (go.float(), gS))
+
+    def rel(a, b):
+        return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-6)).item()
+    assert rel(o, o2) < 2e-2, ("o", rel(o, o2))
+    assert rel(S, S2) < 2e-2, ("final state", rel(S, S2))
     for name, a, b in zip(["dq", "dk", "dv", "dbeta", "dg/dS0", "dS0"], gk, gr):
-        close(a, b, 5e-2, 3e-2 * b.abs().max().item(), name)
+        assert rel(a, b) < 3e-2, (name, rel(a, b))
 
 
 @pytest.mark.gpu

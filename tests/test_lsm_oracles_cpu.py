@@ -212,3 +212,26 @@ def test_lasp2_matches_one_rank(kind, world):
     _close(outs[-1][1], S_ref, 1e-3)
     for i, x in enumerate(xs):
         _close(torch.cat([o[2][i] for o in outs], 1), x.grad, 2e-3)
+
+
+@pytest.mark.parametrize("la", ["retention", "gla", "deltanet"])
+def test_la_mode_selects_equivalent_forms(la):
+    """``--la-mode``: chunk / fused_chunk (chunked form), fused_recurrent (token recurrence) and, for the scalar-decay
+    family, parallel (quadratic form) compute the same layer output."""
+    from linear_moe_b200.config.model_config import ModelConfig
+    from linear_moe_b200.models.transformer import CausalLM
+    torch.manual_seed(0)
+    ids = torch.randint(0, 512, (2, 96))
+    outs = {}
+    modes = ["chunk", "fused_chunk", "fused_recurrent"] + (["parallel"] if la == "retention" else [])
+    for mode in modes:
+        cfg = ModelConfig(num_layers=2, hidden_size=64, num_attention_heads=2, ffn_hidden_size=128, vocab_size=512,
+                          use_la_module=True, la_module=la, layer_type_list="LL", la_mode=mode)
+        outs[mode] = CausalLM(cfg)(ids)
+    for mode in modes[1:]:
+        assert torch.allclose(outs[mode], outs["chunk"], atol=2e-4, rtol=1e-3), (la, mode, (outs[mode] - outs["chunk"]).abs().max())
+    if la != "retention":
+        with pytest.raises(ValueError):
+            cfg = ModelConfig(num_layers=1, hidden_size=64, num_attention_heads=2, ffn_hidden_size=128, vocab_size=512,
+                              use_la_module=True, la_module=la, layer_type_list="L", la_mode="parallel")
+            CausalLM(cfg)(ids)

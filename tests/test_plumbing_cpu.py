@@ -82,17 +82,20 @@ def test_single_process_loss_decreases(single):
     assert losses[-1] < losses[0] - 0.05, losses
 
 
-@pytest.mark.parametrize("name,par_kw", [
-    ("dp2", dict()),
-    ("dp2_zero1", dict(use_distributed_optimizer=True)),
-    ("tp2_sp", dict(tensor_model_parallel_size=2, sequence_parallel=True)),
-    ("ep2", dict(expert_model_parallel_size=2)),
-    ("cp2_lasp2", dict(context_parallel_size=2)),
-    ("pp2", dict(pipeline_model_parallel_size=2)),
+@pytest.mark.parametrize("name,par_kw,overrides", [
+    ("dp2", dict(), None),
+    ("dp2_zero1", dict(use_distributed_optimizer=True), None),
+    ("tp2_sp", dict(tensor_model_parallel_size=2, sequence_parallel=True), None),
+    ("ep2", dict(expert_model_parallel_size=2), None),
+    ("ep2_allgather_dispatcher", dict(expert_model_parallel_size=2), dict(moe_token_dispatcher_type="allgather")),
+    ("tp2_sp_allgather_dispatcher", dict(tensor_model_parallel_size=2, sequence_parallel=True),
+     dict(moe_token_dispatcher_type="allgather")),
+    ("cp2_lasp2", dict(context_parallel_size=2), None),
+    ("pp2", dict(pipeline_model_parallel_size=2), None),
 ])
-def test_world2_matches_single_process(single, name, par_kw):
+def test_world2_matches_single_process(single, name, par_kw, overrides):
     ref_losses, ref_logits, ref_gn = single
-    outs = run_distributed(_worker, 2, par_kw=par_kw, overrides=None)
+    outs = run_distributed(_worker, 2, par_kw=par_kw, overrides=overrides)
     losses = next(o[0] for o in outs if o[0])
     logits = next(o[1] for o in outs if o[1] is not None)
     gn = outs[0][2]
