@@ -1,25 +1,46 @@
-"""Text generation / evaluation entry: loads a checkpoint (``--load``) and completes the prompts of
-``--text-generate-input-file`` (counterpart of the reference's evaluate_*/generation scripts)."""
+"""Text generation entry: loads a checkpoint (``--load``) and completes the prompts of ``--text-generate-input-file``
+(counterpart of the reference's generation scripts).  Runs in one process, or under ``torchrun`` with
+``--tensor-model-parallel-size`` / ``--pipeline-model-parallel-size``: the stages relay activations, the last stage
+samples and every stage receives the sampled tokens; rank 0 prints the completions.
+
+  python examples/generate.py --load /path/to/ckpt --text-generate-input-file prompts.jsonl <model flags>
+  torchrun --nproc-per-node 2 --master-addr 127.0.0.1 examples/generate.py --pipeline-model-parallel-size 2 ...
+"""
 import os
 import sys
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
-import torch
+import torch                                                                      # noqa: E402
 
-from linear_moe_b200.ckpt.legacy import load_checkpoint
-from linear_moe_b200.config.arguments import parse_args
-from linear_moe_b200.data.tokenizer import build_tokenizer
-from linear_moe_b200.dist.mesh import single_process_mesh
-from linear_moe_b200.infer.generation import GPTPredictor
-from linear_moe_b200.models.transformer import CausalLM
+from linear_moe_b200.ckpt.legacy import load_checkpoint                           # noqa: E402
+from linear_moe_b200.config.arguments import parse_args                           # noqa: E402
+from linear_moe_b200.data.tokenizer import build_tokenizer                        # noqa: E402
+from linear_moe_b200.dist.mesh import init_distributed, single_process_mesh       # noqa: E402
+from linear_moe_b200.infer.generation import GPTPredictor                         # noqa: E402
+from linear_moe_b200.models.transformer import CausalLM                           # noqa: E402
 
 if __name__ == "__main__":
     args, cfg, par, tc = parse_args()
-    dev = torch.device("cuda", 0) if torch.cuda.is_available() else torch.device("cpu")
+    distributed = int(os.environ.get("WORLD_SIZE", "1")) > 1
+    if distributed:
+        if not torch.cuda.is_available():
+            par.distributed_backend = "gloo"
+        par.sequence_parallel = False                     # one-token decode steps cannot be split along the sequence
+        mesh = init_distributed(par)
+    else:
+        mesh = single_process_mesh()
+    dev = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
     tok, _ = build_tokenizer(args.patch_tokenizer_type, args.tokenizer_model, cfg.vocab_size, args.extra_vocab_size)
-    model = CausalLM(cfg, single_process_mesh(), device=dev).to(dev)
+    model = CausalLM(cfg, mesh, pre_process=mesh.is_first_stage, post_process=mesh.is_last_stage, device=dev).to(dev)
     if tc.load:
-        load_checkpoint(tc.load, [model], None, None, single_process_mesh(), load_rng=False)
-    for out in GPTPredictor(model, tok, args).predict():
-        print(out)
+        if tc.use_dist_ckpt:
+            from linear_moe_b200.ckpt.sharded import load_sharded
+            per = cfg.num_layers // mesh.pp
+            load_sharded(tc.load, [model], cfg, mesh, None, layer_offsets=[mesh.pp_rank * per])
+        else:
+            load_checkpoint(tc.load, [model], None, None, mesh, load_rng=False)
+    outs = GPTPredictor(model, tok, args).predict()
+    if mesh.rank == 0:
+        for out in outs:
+            print(out)

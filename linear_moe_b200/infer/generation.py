@@ -21,6 +21,8 @@ from typing import List, Optional, Sequence, Tuple
 import torch
 import torch.nn.functional as F
 
+from . import parallel_forward as PF
+
 
 def modify_logits_for_top_k(logits: torch.Tensor, k: int) -> torch.Tensor:
     kth = torch.topk(logits, k, dim=-1).values[..., -1:]
@@ -82,10 +84,15 @@ def tokenize_prompts(tokenizer, prompts: Sequence[str], tokens_to_generate: int,
 
 @torch.no_grad()
 def score_tokens(model, tokens: torch.Tensor) -> torch.Tensor:
-    """Log-probability of every token given its prefix (``score_and_return_on_first_stage``)."""
-    logits = model(tokens[:, :-1])
-    lp = F.log_softmax(logits.float(), dim=-1)
-    return torch.gather(lp, 2, tokens[:, 1:, None]).squeeze(-1)
+    """Log-probability of every token given its prefix (``score_and_return_on_first_stage``); with pipeline parallelism
+    the last stage computes them and every stage receives them."""
+    logits = PF.stage_forward(model, tokens[:, :-1])
+    out = None
+    if logits is not None:
+        lp = F.log_softmax(logits.float(), dim=-1)
+        out = torch.gather(lp, 2, tokens[:, 1:, None]).squeeze(-1)
+    B, T = tokens.shape
+    return PF.broadcast_from_last_stage(model, out, (B, T - 1), torch.float32, tokens.device)
 
 
 class GraphedDecodeStep:
@@ -107,7 +114,7 @@ class GraphedDecodeStep:
 
     @staticmethod
     def supported(model, caches: List[dict], device) -> bool:
-        if device.type != "cuda" or model.mesh.world_size != 1 or not caches:
+        if device.type != "cuda" or model.mesh.world_size != 1 or not caches:     # graph replay is a one-process path
             return False
         if any(s.mixer in ("attn", "mla") for s in model.specs):              # KV caches grow with every token
             return False
@@ -174,13 +181,18 @@ def generate_tokens(model, tokens: torch.Tensor, lengths: torch.Tensor, *, eod: 
         if graphed is not None and ctx - prev == 1:
             logits = graphed(tokens[:, prev:ctx])
         else:
-            logits = model(tokens[:, prev:ctx], caches=caches, position_offset=prev)   # prefill once, then 1 token
-        last = logits[:, -1].float()
-        last = apply_repetition_penalty(last, tokens[:, :ctx], repetition_penalty)
-        new = sample(last, top_k, top_p, temperature, model.cfg.vocab_size, generator)
+            # prefill once, then 1 token; under pipeline parallelism every stage runs its layers with its own caches
+            logits = PF.stage_forward(model, tokens[:, prev:ctx], caches, prev)
+        new = None
+        if logits is not None:                                # last pipeline stage (or no pipeline): sample here
+            last = logits[:, -1].float()
+            last = apply_repetition_penalty(last, tokens[:, :ctx], repetition_penalty)
+            new = sample(last, top_k, top_p, temperature, model.cfg.vocab_size, generator)
+        # every stage gets the sampled tokens, so token buffers and termination flags stay identical on all of them
+        new = PF.broadcast_from_last_stage(model, new, (B,), torch.long, tokens.device)
         started = lengths <= ctx
         tokens[:, ctx] = torch.where(started, new, tokens[:, ctx])
-        if return_log_probs:                                  # after the write, so position ctx holds its final token
+        if return_log_probs and logits is not None:           # after the write, so position ctx holds its final token
             lp = F.log_softmax(logits.float(), -1)
             tgt = tokens[:, prev + 1:ctx + 1]
             logps[:, prev:ctx] = torch.gather(lp, 2, tgt[..., None]).squeeze(-1)
@@ -192,6 +204,8 @@ def generate_tokens(model, tokens: torch.Tensor, lengths: torch.Tensor, *, eod: 
                 tokens = tokens[:, : ctx + 1]
                 break
         prev = ctx
+    if return_log_probs:
+        logps = PF.broadcast_from_last_stage(model, logps, tuple(logps.shape), torch.float32, tokens.device)
     return tokens, gen_len, logps
 
 
@@ -230,7 +244,7 @@ def beam_search(model, prompt: torch.Tensor, beam_size: int, max_new_tokens: int
     scores[1:] = -1e9                                   # all beams start identical: keep one alive
     hyps = BeamHypotheses(beam_size, length_penalty)
     for step in range(max_new_tokens):
-        logits = model(beams)[:, -1].float()
+        logits = PF.full_logits(model, beams, last_only=True)[:, -1]
         lp = F.log_softmax(logits, -1)
         V = lp.shape[-1]
         cand = (scores[:, None] + lp).reshape(-1)
@@ -307,7 +321,7 @@ class GPTPredictor:
                                                     temperature=a.temperature, repetition_penalty=a.repetition_penalty,
                                                     cuda_graph=getattr(a, "cuda_graph_decode", False))
             outs.append(texts[0])
-        if a.text_generate_output_file:
+        if a.text_generate_output_file and getattr(getattr(self.model, "mesh", None), "rank", 0) == 0:
             with open(a.text_generate_output_file, "a", encoding="utf-8") as f:
                 for p, o in zip(prompts, outs):
                     f.write(json.dumps({"prompt": p, "output": o}, ensure_ascii=False) + "\n")

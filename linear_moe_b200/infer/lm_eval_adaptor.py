@@ -29,7 +29,9 @@ class EvalHarnessAdaptor:
 
     @torch.no_grad()
     def _model_call(self, ids: torch.Tensor) -> torch.Tensor:
-        return self.model(ids.to(self.device)).float()
+        """Logits on every rank: the stages relay the activations, the last stage's (TP-gathered) logits are broadcast."""
+        from .parallel_forward import full_logits
+        return full_logits(self.model, ids.to(self.device))
 
     def _loglikelihood_tokens(self, pairs: Sequence[Tuple[List[int], List[int]]]) -> List[Tuple[float, bool]]:
         out = []

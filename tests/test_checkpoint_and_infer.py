@@ -337,3 +337,54 @@ def test_use_dist_ckpt_flag_resumes_training(tmp_path):
     assert tr2.iteration == 2 and tr2.consumed_samples == tr.consumed_samples
     s1, s2 = tr.train_step(), tr2.train_step()
     assert abs(float(s1["lm loss"]) - float(s2["lm loss"])) < 1e-5
+
+
+def _generate_worker(rank, world, par_kw):
+    from linear_moe_b200.infer import generation as G
+    from linear_moe_b200.infer.lm_eval_adaptor import EvalHarnessAdaptor
+    par = ParallelConfig(distributed_backend="gloo", **par_kw)
+    mesh = Mesh(par) if world > 1 else None
+    return _generate(mesh)
+
+
+def _generate(mesh):
+    from linear_moe_b200.infer import generation as G
+    from linear_moe_b200.infer.lm_eval_adaptor import EvalHarnessAdaptor
+    from linear_moe_b200.models.transformer import CausalLM
+    cfg = _cfg(num_layers=4, use_la_module=True, la_module="gla", layer_type_list="LNLN", num_query_groups=2)
+    if mesh is not None and mesh.pp > 1:
+        model = CausalLM(cfg, mesh, pre_process=mesh.is_first_stage, post_process=mesh.is_last_stage)
+    else:
+        model = CausalLM(cfg, mesh)
+    torch.manual_seed(0)
+    prompts = torch.randint(0, cfg.vocab_size, (2, 24))
+    tokens = torch.cat([prompts[:, :10], torch.zeros(2, 14, dtype=torch.long)], 1)
+    toks, _, lp = G.generate_tokens(model, tokens.clone(), torch.tensor([6, 10]), top_k=1, return_log_probs=True)
+    scores = G.score_tokens(model, prompts)
+
+    class Tok:
+        eod = 0
+
+        def encode(self, s):
+            return [int(x) for x in s.split()]
+
+        def decode(self, t):
+            return " ".join(str(x) for x in t)
+    ad = EvalHarnessAdaptor(model, Tok(), max_length=64)
+    ll = ad.loglikelihood([("1 2 3 4 5", "6 7 8"), ("9 8 7", "6 5")])
+    return toks, lp, scores, ll
+
+
+@pytest.mark.parametrize("par_kw", [dict(pipeline_model_parallel_size=2), dict(tensor_model_parallel_size=2)])
+def test_generation_and_eval_across_pipeline_and_tensor_parallel_ranks(par_kw):
+    """Greedy generation, token scoring and the evaluation adaptor give the same result on two pipeline stages or two
+    tensor-parallel ranks as in one process, on EVERY rank (sampled tokens / log-probs are handed back by the last
+    stage; vocabulary-parallel logits are gathered)."""
+    from dist_utils import run_distributed
+    ref_toks, ref_lp, ref_scores, ref_ll = _generate(None)
+    outs = run_distributed(_generate_worker, 2, par_kw=par_kw)
+    for toks, lp, scores, ll in outs:
+        assert torch.equal(toks, ref_toks)
+        assert torch.allclose(lp, ref_lp, atol=1e-4)
+        assert torch.allclose(scores, ref_scores, atol=1e-4)
+        assert all(abs(a[0] - b[0]) < 1e-3 and a[1] == b[1] for a, b in zip(ll, ref_ll))
