@@ -1,6 +1,6 @@
 """Per-kernel yardsticks: this repository's kernels next to the engines the reference calls for the same operator.
 
-  python -m linear_moe_b200.bench.comparators [--only lightning,gla,gdn,delta,flash,gemm] [--iters 10]
+  python -m linear_moe_b200.bench.comparators [--only lightning,gla,gdn,delta,flash4k,flash16k,gemm] [--iters 10]
 
 The reference reaches its sequence-mixing kernels through ``flash-linear-attention`` (``fla.ops.simple_gla`` for
 lightning attention / retention, ``fla.ops.gla``, ``fla.ops.gated_delta_rule``, ``fla.ops.delta_rule``;
@@ -8,7 +8,8 @@ gla/gla.py:94, gated_deltanet.py:112, retention.py:91) and softmax attention thr
 Both packages are Triton / CUDA libraries; they are imported here only as comparators and never by the framework.
 Shapes are the per-GPU shapes of the benchmark configurations.  Every row is timed the same way: CUDA events on the
 launching stream, 3 warm-up calls, an L2 flush (256 MiB write) before every timed call, median of ``--iters``.
-Forward and forward+backward are reported; a comparator that is missing or fails prints the reason in its cell.
+Forward and forward+backward are reported.  Every measurement runs in a process of its own, so a comparator that is
+missing or fails prints the reason in its cell and the table goes on.
 """
 from __future__ import annotations
 
@@ -55,49 +56,39 @@ def _fwd_bwd(op, inputs, iters):
     return _time(fwd, iters), _time(both, iters)
 
 
-def _cell(fn):
-    try:
-        f, fb = fn()
-        return f"{f:8.0f} / {fb:8.0f}"
-    except Exception as e:                                   # noqa: BLE001 - a comparator may be absent or refuse a shape
-        return f"n/a ({type(e).__name__}: {str(e)[:60]})"
-
-
-def bench_lightning(iters):
-    """Config LASP-2 Linear-Llama3-1B: lightning attention, T=16384, 16 heads x 128, constant decay per head."""
-    from .. import ops
+def _inputs_lightning():
     from ..ref import lsm as RL
     B, T, H, D = 1, 16384, 16, 128
     dev = torch.device("cuda", 0)
     qkv = (0.5 * torch.randn(B, T, H, 3 * D, device=dev)).bfloat16()
     q, k, v = (t.contiguous() for t in qkv.split(D, dim=-1))
-    g = -RL.lightning_slopes(H).to(dev)
-    ours = lambda q, k, v: ops.lsm_scalar(q, k, v, g, 1.0, None, 64)
-
-    def fla_op(q, k, v):
-        from fla.ops.simple_gla import chunk_simple_gla
-        return chunk_simple_gla(q, k, v, g_gamma=g, scale=1.0)
-    return [("lightning attention T=16384 H=16 D=128", _cell(lambda: _fwd_bwd(ours, [q, k, v], iters)),
-             "fla chunk_simple_gla", _cell(lambda: _fwd_bwd(fla_op, [q, k, v], iters)))]
+    return [q, k, v], -RL.lightning_slopes(H).to(dev)
 
 
-def bench_gla(iters):
+def cell_lightning(impl, iters):
+    """Config LASP-2 Linear-Llama3-1B: lightning attention, T=16384, 16 heads x 128, constant decay per head."""
+    from .. import ops
+    ins, g = _inputs_lightning()
+    if impl == "ours":
+        return _fwd_bwd(lambda q, k, v: ops.lsm_scalar(q, k, v, g, 1.0, None, 64), ins, iters)
+    from fla.ops.simple_gla import chunk_simple_gla
+    return _fwd_bwd(lambda q, k, v: chunk_simple_gla(q, k, v, g_gamma=g, scale=1.0), ins, iters)
+
+
+def cell_gla(impl, iters):
     """Config A0.3B-2B: GLA, 8 sequences of 2048, 8 heads x 128."""
     from .. import ops
     B, T, H, D = 8, 2048, 8, 128
     dev = torch.device("cuda", 0)
     q, k, v = [(0.5 * torch.randn(B, T, H, D, device=dev)).bfloat16() for _ in range(3)]
     gk = (torch.nn.functional.logsigmoid(torch.randn(B, T, H, D, device=dev)) / 16).bfloat16()
-    ours = lambda q, k, v, gk: ops.lsm_vector(q, k, v, gk.float(), None, None, None, 64)
-
-    def fla_op(q, k, v, gk):
-        from fla.ops.gla import chunk_gla
-        return chunk_gla(q, k, v, gk)
-    return [("GLA B=8 T=2048 H=8 D=128", _cell(lambda: _fwd_bwd(ours, [q, k, v, gk], iters)),
-             "fla chunk_gla", _cell(lambda: _fwd_bwd(fla_op, [q, k, v, gk], iters)))]
+    if impl == "ours":
+        return _fwd_bwd(lambda q, k, v, gk: ops.lsm_vector(q, k, v, gk.float(), None, None, None, 64), [q, k, v, gk], iters)
+    from fla.ops.gla import chunk_gla
+    return _fwd_bwd(lambda q, k, v, gk: chunk_gla(q, k, v, gk), [q, k, v, gk], iters)
 
 
-def bench_gdn(iters, gated=True):
+def _cell_delta(impl, iters, gated):
     """Config A1B-7B hybrid: (gated) delta rule, 2 sequences of 4096, 8 heads x 128 (16 heads under TP2)."""
     from .. import ops
     B, T, H, D = 2, 4096, 8, 128
@@ -106,47 +97,73 @@ def bench_gdn(iters, gated=True):
     k = torch.nn.functional.normalize(torch.randn(B, T, H, D, device=dev), dim=-1).bfloat16()
     beta = torch.rand(B, T, H, device=dev).bfloat16()
     g = torch.nn.functional.logsigmoid(torch.randn(B, T, H, device=dev) + 2.0)
+    if impl == "ours":
+        if gated:
+            return _fwd_bwd(lambda q, k, v, beta, g: ops.lsm_delta(q, k, v, beta.float(), g, None, None, 64), [q, k, v, beta, g], iters)
+        return _fwd_bwd(lambda q, k, v, beta: ops.lsm_delta(q, k, v, beta.float(), None, None, None, 64), [q, k, v, beta], iters)
+    if impl == "eager":                                          # the batched-matmul + parallel-scan form this kernel replaced
+        import os
+        os.environ["LMOE_DELTA_KERNEL"] = "0"
+        if gated:
+            return _fwd_bwd(lambda q, k, v, beta, g: ops.lsm_delta(q, k, v, beta.float(), g, None, None, 64), [q, k, v, beta, g], iters)
+        return _fwd_bwd(lambda q, k, v, beta: ops.lsm_delta(q, k, v, beta.float(), None, None, None, 64), [q, k, v, beta], iters)
     if gated:
-        ours = lambda q, k, v, beta, g: ops.lsm_delta(q, k, v, beta.float(), g, None, None, 64)
-
-        def fla_op(q, k, v, beta, g):
-            from fla.ops.gated_delta_rule import chunk_gated_delta_rule
-            return chunk_gated_delta_rule(q, k, v, g, beta)
-        ins, name, fname = [q, k, v, beta, g], "gated delta rule", "fla chunk_gated_delta_rule"
-    else:
-        ours = lambda q, k, v, beta: ops.lsm_delta(q, k, v, beta.float(), None, None, None, 64)
-
-        def fla_op(q, k, v, beta):
-            from fla.ops.delta_rule import chunk_delta_rule
-            return chunk_delta_rule(q, k, v, beta)
-        ins, name, fname = [q, k, v, beta], "delta rule", "fla chunk_delta_rule"
-    return [(f"{name} B=2 T=4096 H=8 D=128", _cell(lambda: _fwd_bwd(ours, ins, iters)), fname,
-             _cell(lambda: _fwd_bwd(fla_op, ins, iters)))]
+        from fla.ops.gated_delta_rule import chunk_gated_delta_rule
+        return _fwd_bwd(lambda q, k, v, beta, g: chunk_gated_delta_rule(q, k, v, g, beta), [q, k, v, beta, g], iters)
+    from fla.ops.delta_rule import chunk_delta_rule
+    return _fwd_bwd(lambda q, k, v, beta: chunk_delta_rule(q, k, v, beta), [q, k, v, beta], iters)
 
 
-def bench_flash(iters):
-    """Softmax attention layers of the hybrid configs: causal GQA, head dim 128."""
+def cell_gdn(impl, iters):
+    return _cell_delta(impl, iters, True)
+
+
+def cell_delta(impl, iters):
+    return _cell_delta(impl, iters, False)
+
+
+def _cell_flash(impl, iters, shape):
     from ..ops import attention
-    rows = []
-    for B, T, Hq, Hkv in ((2, 4096, 8, 2), (1, 16384, 16, 4)):
-        dev = torch.device("cuda", 0)
-        q = (0.5 * torch.randn(B, T, Hq, 128, device=dev)).bfloat16()
-        k = (0.5 * torch.randn(B, T, Hkv, 128, device=dev)).bfloat16()
-        v = (0.5 * torch.randn(B, T, Hkv, 128, device=dev)).bfloat16()
-        ours = lambda q, k, v: attention.flash_attention(q, k, v, 128 ** -0.5, True, 0, None)
+    B, T, Hq, Hkv = shape
+    dev = torch.device("cuda", 0)
+    q = (0.5 * torch.randn(B, T, Hq, 128, device=dev)).bfloat16()
+    k = (0.5 * torch.randn(B, T, Hkv, 128, device=dev)).bfloat16()
+    v = (0.5 * torch.randn(B, T, Hkv, 128, device=dev)).bfloat16()
+    if impl == "ours":
+        return _fwd_bwd(lambda q, k, v: attention.flash_attention(q, k, v, 128 ** -0.5, True, 0, None), [q, k, v], iters)
+    if impl == "flash_attn":
+        from flash_attn import flash_attn_func
+        return _fwd_bwd(lambda q, k, v: flash_attn_func(q, k, v, causal=True), [q, k, v], iters)
 
-        def fa(q, k, v):
-            from flash_attn import flash_attn_func
-            return flash_attn_func(q, k, v, causal=True)
+    def sdpa(q, k, v):
+        o = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
+                                                             is_causal=True, enable_gqa=True)
+        return o.transpose(1, 2)
+    return _fwd_bwd(sdpa, [q, k, v], iters)
 
-        def sdpa(q, k, v):
-            o = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2),
-                                                                 is_causal=True, enable_gqa=True)
-            return o.transpose(1, 2)
-        rows.append((f"flash attention B={B} T={T} {Hq}q/{Hkv}kv D=128", _cell(lambda: _fwd_bwd(ours, [q, k, v], iters)),
-                     "flash_attn 2.8 | torch SDPA",
-                     _cell(lambda: _fwd_bwd(fa, [q, k, v], iters)) + " | " + _cell(lambda: _fwd_bwd(sdpa, [q, k, v], iters))))
-    return rows
+
+def cell_flash4k(impl, iters):
+    return _cell_flash(impl, iters, (2, 4096, 8, 2))
+
+
+def cell_flash16k(impl, iters):
+    return _cell_flash(impl, iters, (1, 16384, 16, 4))
+
+
+# operator -> (row title, cell function, implementations; "ours" first).  A comparator that faulted the GPU in an
+# earlier run is listed in SKIP with the record of that run and is not started again.
+TABLE = {
+    "lightning": ("lightning attention T=16384 H=16 D=128", cell_lightning, ["ours", "fla"]),
+    "gla": ("GLA B=8 T=2048 H=8 D=128", cell_gla, ["ours", "fla"]),
+    "gdn": ("gated delta rule B=2 T=4096 H=8 D=128", cell_gdn, ["ours", "eager", "fla"]),
+    "delta": ("delta rule B=2 T=4096 H=8 D=128", cell_delta, ["ours", "eager", "fla"]),
+    "flash4k": ("flash attention B=2 T=4096 8q/2kv D=128", cell_flash4k, ["ours", "flash_attn", "sdpa"]),
+    "flash16k": ("flash attention B=1 T=16384 16q/4kv D=128", cell_flash16k, ["ours", "flash_attn", "sdpa"]),
+}
+SKIP = {
+    ("gdn", "fla"): "not run: a run that included fla.ops.gated_delta_rule.chunk_gated_delta_rule at this shape ended in "
+                    "'CUDA error: misaligned address' (Triton 3.6 on sm_100a); it is not started again",
+}
 
 
 def bench_gemm(iters):
@@ -172,28 +189,42 @@ def bench_gemm(iters):
 
 
 def main():
+    import subprocess
+    import sys
     ap = argparse.ArgumentParser()
-    ap.add_argument("--only", type=str, default="lightning,gla,gdn,delta,flash,gemm")
+    ap.add_argument("--only", type=str, default="lightning,gla,gdn,delta,flash4k,flash16k,gemm")
     ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--cell", type=str, default=None, help="internal: run one <operator>:<implementation> measurement")
     args = ap.parse_args()
-    only = set(args.only.split(","))
-    rows = []
-    if "lightning" in only:
-        rows += bench_lightning(args.iters)
-    if "gla" in only:
-        rows += bench_gla(args.iters)
-    if "gdn" in only:
-        rows += bench_gdn(args.iters, True)
-    if "delta" in only:
-        rows += bench_gdn(args.iters, False)
-    if "flash" in only:
-        rows += bench_flash(args.iters)
-    if "gemm" in only:
-        rows += bench_gemm(args.iters)
-    print("| operator (per-GPU shape) | this repository: fwd / fwd+bwd (us) | comparator | comparator: fwd / fwd+bwd (us) |")
+    if args.cell:
+        op, impl = args.cell.split(":")
+        f, fb = TABLE[op][1](impl, args.iters)
+        print(f"RESULT {f:.1f} {fb:.1f}", flush=True)
+        return
+    print("| operator (per-GPU shape) | implementation | forward (us) | forward + backward (us) |")
     print("|---|---|---|---|")
-    for r in rows:
-        print("| " + " | ".join(r) + " |", flush=True)
+    for op in args.only.split(","):
+        if op == "gemm":
+            for r in bench_gemm(args.iters):
+                print(f"| {r[0]} | this repository | {r[1]} | |")
+                print(f"| {r[0]} | {r[2]} | {r[3]} | |", flush=True)
+            continue
+        title, _, impls = TABLE[op]
+        for impl in impls:
+            name = "this repository" if impl == "ours" else impl
+            if (op, impl) in SKIP:
+                print(f"| {title} | {name} | {SKIP[(op, impl)]} | |", flush=True)
+                continue
+            # one process per measurement: a comparator that fails cannot take the rest of the table with it
+            r = subprocess.run([sys.executable, "-m", "linear_moe_b200.bench.comparators", "--cell", f"{op}:{impl}",
+                                "--iters", str(args.iters)], capture_output=True, text=True)
+            line = [l for l in r.stdout.splitlines() if l.startswith("RESULT")]
+            if r.returncode == 0 and line:
+                _, f, fb = line[-1].split()
+                print(f"| {title} | {name} | {float(f):.0f} | {float(fb):.0f} |", flush=True)
+            else:
+                err = (r.stderr.strip().splitlines() or ["failed"])[-1][:120]
+                print(f"| {title} | {name} | n/a ({err}) | |", flush=True)
 
 
 if __name__ == "__main__":

@@ -412,7 +412,7 @@ def configs_from_args(args: argparse.Namespace) -> Tuple[ModelConfig, ParallelCo
         q_lora_rank=args.q_lora_rank, kv_lora_rank=args.kv_lora_rank,
         qk_nope_head_dim=args.qk_nope_head_dim, qk_rope_head_dim=args.qk_rope_head_dim,
         v_head_dim=args.v_head_dim, params_dtype=dtype,
-        fp8="block" if (args.fp8_hybrid or args.fp8_format) else None,
+        fp8="rowwise" if (args.fp8_hybrid or args.fp8_format) else None,
         recompute_granularity=recompute, recompute_method=args.recompute_method,
         recompute_num_layers=args.recompute_num_layers, test_mode=args.test_mode,
         cpu_offloading=args.cpu_offloading, cpu_offloading_num_layers=args.cpu_offloading_num_layers,

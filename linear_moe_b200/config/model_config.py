@@ -134,7 +134,7 @@ class ModelConfig:
     v_head_dim: int = 128
     # ---- precision / memory --------------------------------------------
     params_dtype: torch.dtype = torch.float32
-    fp8: Optional[str] = None                     # None | any recipe name: e4m3 GEMMs with per-row scales (ops/fp8.py)
+    fp8: Optional[str] = None                     # None | "rowwise": e4m3 GEMMs, one current-amax scale per operand row (ops/fp8.py)
     recompute_granularity: Optional[str] = None   # None | selective | full
     recompute_method: Optional[str] = None        # uniform | block
     recompute_num_layers: int = 1

@@ -90,12 +90,12 @@ PRESETS: Dict[str, dict] = {
                                   la_module="lightning_attention", layer_type_list="L" * 16,
                                   init_method_std=0.02, max_position_embeddings=131072,
                                   params_dtype=torch.bfloat16),
-    # 5: Mixtral-style Mamba2 hybrid, block-scaled fp8, TP=2 EP=4 + ZeRO-1
+    # 5: Mixtral-style Mamba2 hybrid, e4m3 GEMMs (one scale per operand row, not 1x128 / 128x128 blocks), TP=2 EP=4 + ZeRO-1
     "bench-mixtral-mamba2-fp8": dict(_MIXTRAL, num_layers=32, hidden_size=4096, num_attention_heads=32,
                                      num_query_groups=8, ffn_hidden_size=14336, num_experts=8, moe_topk=2,
                                      vocab_size=32000, use_la_module=True, la_module="mamba2",
                                      hybrid_override_pattern=("M" * 7 + "*") * 4, mamba_d_state=128,
-                                     mamba_head_dim=64, mamba_chunk_size=256, fp8="block",
+                                     mamba_head_dim=64, mamba_chunk_size=256, fp8="rowwise",
                                      init_method_std=0.02, params_dtype=torch.bfloat16, sliding_window=None),
 }
 

@@ -52,6 +52,8 @@ struct ZeroArgs {
     float grad_scale;
     float lr, b1, b2, eps, wd, bc1, bc2, gscale;
     long long spin_limit;
+    int slot;                   // flag slot of this reduce launch (0 for the whole-shard reduce; one per bucket when the
+                                // reduction is split into buckets that overlap the backward pass)
 };
 
 __device__ __forceinline__ bool wait_all(const ZeroArgs& a, int phase, int code) {
@@ -74,14 +76,17 @@ __device__ __forceinline__ bool wait_all(const ZeroArgs& a, int phase, int code)
 
 __global__ void zero_reduce_kernel(ZeroArgs a) {
     __shared__ float red[32];
+    // slot 0 = flags [0, W); slot 1 is the parameter barrier of zero_adam_bcast_kernel; bucket slots follow
+    const int phase = a.slot == 0 ? 0 : a.slot + 1;
     if (blockIdx.x == 0 && (int)threadIdx.x < a.world) {
         __threadfence_system();
-        st_rel_sys(a.peer_flags[threadIdx.x] + 0 * a.world + a.rank, a.epoch);      // "my gradients are complete"
+        st_rel_sys(a.peer_flags[threadIdx.x] + phase * a.world + a.rank, a.epoch);  // "my gradients (of this bucket) are complete"
     }
-    wait_all(a, 0, 1);
+    const long long n4 = (a.hi - a.lo) / 4;
+    if (n4 <= 0) return;                                   // nothing of this bucket in this rank's shard: signal only
+    wait_all(a, phase, 1);
     __syncthreads();
     float ss = 0.f;
-    const long long n4 = (a.hi - a.lo) / 4;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
         const long long e = a.lo + i * 4;
         float4 v;

@@ -81,8 +81,10 @@ class MambaMixer(nn.Module):
         g = dt * A[None, None, :]
         vv = (xh.float() * dt[..., None]).to(xh.dtype)
         init = cache.get("ssm") if cache is not None else None
-        y, S = lasp2("scalar", qq, kk, vv, group=self.mesh["cp"], g=g, scale=1.0,
-                     chunk_size=min(cfg.mamba_chunk_size, 64) if x.is_cuda else cfg.mamba_chunk_size,
+        # --mamba-chunk-size is the tile length of the chunked scan.  It does not change the result (the scan is exact
+        # for any tiling); the eager form tiles by it, the CUDA kernel always tiles by 64 tokens (its register /
+        # shared-memory budget), so the value is passed through unchanged and only the eager form reads it.
+        y, S = lasp2("scalar", qq, kk, vv, group=self.mesh["cp"], g=g, scale=1.0, chunk_size=cfg.mamba_chunk_size,
                      initial_state=init)
         if cache is not None:
             cache["ssm"] = S.detach()

@@ -175,9 +175,14 @@ class CausalLM(nn.Module):
         if hasattr(self, "lower_bounds"):
             lb = self.lower_bounds.float().softmax(0)
             lbs = lb.cumsum(0) - lb[0]
+        ready = getattr(self, "grad_ready_hook", None)
         for i, blk in enumerate(layers):
             cache = None if caches is None else caches[i]
             lb_i = None if lbs is None else lbs[blk.spec.index]
+            if ready is not None and caches is None and torch.is_grad_enabled() and x.requires_grad:
+                # fires when the gradient with respect to this block's input exists, i.e. after the block's whole
+                # backward: its parameter gradients are final and their reduction may start
+                x.register_hook(lambda g, i=i: ready(i))
             if full_recompute and self._should_recompute(i):
                 x, residual = ckpt.checkpoint(blk, x, residual, None, position_offset, lb_i, use_reentrant=False)
             elif self.offload is not None and self.training and caches is None and torch.is_grad_enabled():

@@ -1077,8 +1077,11 @@ def _delta_prepare(q, k, v, beta, g, scale, C=64):
     btot = b[..., -1]
     Qd = qs * eb[..., None]
     Kd = kc * (btot[..., None] - b).exp()[..., None]
+    # row-major tiles for the kernels: the triangular solve may return its result in column-major order, and a dtype
+    # conversion keeps whatever dense layout it is given
     bf = torch.bfloat16
-    return W.to(bf), U.to(bf).contiguous(), Qd.to(bf), Kd.to(bf), Aqk.to(bf), btot.exp().contiguous()
+    return (W.to(bf).contiguous(), U.to(bf).contiguous(), Qd.to(bf).contiguous(), Kd.to(bf).contiguous(),
+            Aqk.to(bf).contiguous(), btot.exp().contiguous())
 
 
 class _DeltaChunkScan(torch.autograd.Function):
@@ -1097,6 +1100,7 @@ class _DeltaChunkScan(torch.autograd.Function):
         Sn = torch.empty(B, H, N, dk, dv, dtype=bf, device=dev)
         Sf = torch.empty(B, H, dk, dv, dtype=torch.float32, device=dev)
         s0 = None if S0 is None else S0.float().contiguous()
+        W, U, Qd, Kd, A, gamma = (t.contiguous() for t in (W, U, Qd, Kd, A, gamma))
         a = _DeltaArgs()
         a.W, a.U, a.Qd, a.Kd, a.A, a.gamma = (t.data_ptr() for t in (W, U, Qd, Kd, A, gamma))
         a.S0 = 0 if s0 is None else s0.data_ptr()

@@ -215,19 +215,21 @@ class _ZeroArgs(ctypes.Structure):
                 ("rank", ctypes.c_int), ("world", ctypes.c_int), ("epoch", ctypes.c_int), ("grad_scale", ctypes.c_float),
                 ("lr", ctypes.c_float), ("b1", ctypes.c_float), ("b2", ctypes.c_float), ("eps", ctypes.c_float),
                 ("wd", ctypes.c_float), ("bc1", ctypes.c_float), ("bc2", ctypes.c_float), ("gscale", ctypes.c_float),
-                ("spin_limit", ctypes.c_longlong)]
+                ("spin_limit", ctypes.c_longlong), ("slot", ctypes.c_int)]
 
 
 class ZeroBufferWorkspace:
     """Symmetric parameter (bf16) and gradient (fp32) storage of one flat optimizer buffer plus the flags of its two
     barriers.  ``reduce`` and ``adam_broadcast`` are the two kernel launches of a fused ZeRO-1 step."""
 
+    MAX_BUCKETS = 510            # flag slots for bucketed reduces (one per bucket and step)
+
     def __init__(self, group, numel: int, device, spin_limit: Optional[int] = None, use_multicast: bool = True):
         self.group, self.device, self.numel = group, device, numel
         self.W, self.rank = group.size, group.rank
         self.params, self.p_hdl = _symm_empty(numel, torch.bfloat16, device, group)
         self.grads, self.g_hdl = _symm_empty(numel, torch.float32, device, group)
-        self.flags, self.f_hdl = _symm_empty(2 * self.W + 64, torch.int32, device, group)
+        self.flags, self.f_hdl = _symm_empty((2 + self.MAX_BUCKETS) * self.W + 64, torch.int32, device, group)
         self.flags.zero_()
         mc_p = int(getattr(self.p_hdl, "multicast_ptr", 0) or 0)
         mc_g = int(getattr(self.g_hdl, "multicast_ptr", 0) or 0)
@@ -259,7 +261,27 @@ class ZeroBufferWorkspace:
         self.sumsq.zero_()
         a = self._args(shard)
         a.grad_scale = grad_scale
+        a.slot = 0
         K._check(K.lib().lmoe_zero_reduce(ctypes.byref(a), ctypes.c_int(K.NUM_SMS * 4), K._st()), "zero_reduce")
+
+    # -- bucketed form: the reduction of a step is split into ranges that are launched as soon as their gradients exist
+    def begin_step(self):
+        """Start the bucketed reduction of one optimizer step (every rank calls it at the same point)."""
+        self.epoch += 1
+        self.sumsq.zero_()
+        self._next_slot = 1
+
+    def reduce_range(self, lo: int, hi: int, shard, grad_scale: float, blocks: Optional[int] = None):
+        """Reduce-scatter ``[lo, hi)`` of the flat buffer: this rank sums the part of the range that lies in its shard over
+        all ranks (NVLS ``multimem.ld_reduce``); a rank that owns none of it only signals that its gradients of the range
+        are complete.  Every rank must issue the same sequence of ranges per step.  Runs on the current stream."""
+        from ..ops import cuda as K
+        assert self._next_slot <= self.MAX_BUCKETS, "too many gradient buckets in one step"
+        a = self._args((max(lo, shard[0]), max(min(hi, shard[1]), max(lo, shard[0]))))
+        a.grad_scale = grad_scale
+        a.slot = self._next_slot
+        self._next_slot += 1
+        K._check(K.lib().lmoe_zero_reduce(ctypes.byref(a), ctypes.c_int(blocks or K.NUM_SMS * 2), K._st()), "zero_reduce")
 
     def adam_broadcast(self, shard, master, exp_avg, exp_avg_sq, lr, b1, b2, eps, wd, bc1, bc2, gscale):
         from ..ops import cuda as K

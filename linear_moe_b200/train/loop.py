@@ -94,7 +94,12 @@ class Trainer:
         self.model = self.models[0]
         wrapper = nn.ModuleList(self.models)
         self.optimizer = MixedPrecisionAdam(wrapper, self.mesh, tc, zero1=par.use_distributed_optimizer,
-                                            sequence_parallel=sp, fused_comm=par.fused_comm)
+                                            sequence_parallel=sp, fused_comm=par.fused_comm,
+                                            overlap_grad_reduce=par.overlap_grad_reduce)
+        if par.overlap_grad_reduce and self.mesh.pp == 1 and len(self.models) == 1 and \
+                any(b.fused is not None for b in self.optimizer.buffers):
+            # a block's gradients are reduced while the backward pass of the blocks before it is still running
+            getattr(self.model, "module", self.model).grad_ready_hook = self.optimizer.bucket_ready
         self.scheduler = OptimizerParamScheduler(tc)
         self.timers = Timers(tc.timing_log_level, cuda=self.device.type == "cuda")
         self.iteration, self.consumed_samples = 0, 0

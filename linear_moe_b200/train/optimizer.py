@@ -109,8 +109,12 @@ class MixedPrecisionAdam:
     and optional ZeRO-1 sharding over the data-parallel group."""
 
     def __init__(self, model: nn.Module, mesh: Mesh, tc: TrainConfig, *, zero1: bool = False,
-                 sequence_parallel: bool = False, fused_comm: bool = True):
+                 sequence_parallel: bool = False, fused_comm: bool = True, overlap_grad_reduce: bool = False):
         self.mesh, self.tc, self.zero1 = mesh, tc, zero1 and (mesh.dp * mesh.cp) > 1
+        self.overlap_grad_reduce = overlap_grad_reduce
+        self.overlap_active = False            # set by the schedule while the LAST micro-batch's backward runs
+        self._side_stream = None
+        self._bucket_state = None              # per fused buffer: list of [lo, hi) ranges already reduced this step
         self.sequence_parallel = sequence_parallel and mesh.tp > 1
         self.fused_comm = fused_comm
         self.step_count = 0
@@ -189,11 +193,67 @@ class MixedPrecisionAdam:
                 t.copy_(flat[off:off + t.numel()].view_as(t))
                 off += t.numel()
 
+    # ---- gradient reduction overlapped with the backward pass (--overlap-grad-reduce) -------------------------------
+    def _layer_range(self, b: "FlatBuffer", layer: int):
+        """``[lo, hi)`` of the flat buffer holding the parameters of ``decoder.layers.<layer>`` (contiguous: slots are in
+        model order), or None."""
+        cache = b.__dict__.setdefault("_layer_ranges", {})
+        if layer not in cache:
+            pre = f"decoder.layers.{layer}."
+            sl = [s for s in b.slots if s.name.startswith(pre)]
+            cache[layer] = None if not sl else (min(s.start for s in sl), max(s.start + s.numel for s in sl))
+        return cache[layer]
+
+    def bucket_ready(self, layer: int):
+        """Called from the backward pass when every gradient of block ``layer`` has been written (a hook on the block's
+        input): the reduce-scatter of that block's range starts at once on a side stream, overlapping the backward of the
+        blocks before it (Megatron's ``overlap_grad_reduce``, training.py:278-298).  Only the fused NVLS buffers and only
+        the last micro-batch of a step take part; everything else is reduced by :meth:`reduce_grads`."""
+        if not (self.overlap_grad_reduce and self.overlap_active) or self.sequence_parallel:
+            return
+        fused = [b for b in self.buffers if b.fused is not None]
+        if not fused:
+            return
+        if self._side_stream is None:
+            self._side_stream = torch.cuda.Stream()
+        main = torch.cuda.current_stream()
+        if self._bucket_state is None:
+            self._bucket_state = {}
+            for b in fused:
+                b.fused.begin_step()
+                self._bucket_state[id(b)] = []
+        ev = torch.cuda.Event()
+        ev.record(main)
+        self._side_stream.wait_event(ev)
+        with torch.cuda.stream(self._side_stream):
+            for b in fused:
+                r = self._layer_range(b, layer)
+                if r is None:
+                    continue
+                b.fused.reduce_range(r[0], r[1], b.shard, b.grad_scale)
+                self._bucket_state[id(b)].append(r)
+
+    def _finish_bucketed_with(self, b: "FlatBuffer", state):
+        """Reduce what the hooks did not cover (embedding, final norm, LM head, padding) after the backward pass."""
+        done = sorted(state[id(b)])
+        pos = 0
+        for lo, hi in done + [(b.numel, b.numel)]:
+            if lo > pos:
+                b.fused.reduce_range(pos, lo, b.shard, b.grad_scale, blocks=None)
+            pos = max(pos, hi)
+
     def reduce_grads(self):
         """Data-parallel reduction of every buffer: all-reduce, or reduce-scatter into this rank's
         shard under ZeRO-1 (the rest of the buffer is then stale until the next zero_grad)."""
         self._reduce_sequence_parallel_grads()
+        bucketed = self._bucket_state
+        self._bucket_state = None
+        if bucketed is not None:
+            torch.cuda.current_stream().wait_stream(self._side_stream)
         for b in self.buffers:
+            if b.fused is not None and bucketed is not None:
+                self._finish_bucketed_with(b, bucketed)
+                continue
             if b.fused is not None:
                 # barrier + in-switch reduce-scatter + scale + partial sum of squares, one kernel, no NCCL
                 b.fused.reduce(b.shard, b.grad_scale)

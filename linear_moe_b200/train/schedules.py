@@ -44,13 +44,17 @@ def _recv(shape, dtype, device, src: int, mesh: Mesh) -> torch.Tensor:
 def forward_backward_no_pipelining(forward_step: Callable, data_iter: Iterator, model, num_microbatches: int,
                                    optimizer=None, forward_only: bool = False) -> List[dict]:
     logs = []
-    for _ in range(num_microbatches):
+    for i in range(num_microbatches):
         batch = next(data_iter)
         out, loss_fn = forward_step(batch, model, None)
         loss, log = loss_fn(out)
         if not forward_only:
             loss = loss / num_microbatches
+            if optimizer is not None and hasattr(optimizer, "overlap_active"):
+                optimizer.overlap_active = i == num_microbatches - 1      # gradients are final after this backward
             (optimizer.scale_loss(loss) if optimizer is not None else loss).backward()
+            if optimizer is not None and hasattr(optimizer, "overlap_active"):
+                optimizer.overlap_active = False
         logs.append(log)
     return logs
 

@@ -38,7 +38,7 @@ def test_reference_flags_are_accepted():
     assert cfg.la_module == "gated_deltanet" and cfg.layer_type_list == "LLLN" and cfg.num_experts == 8
     assert cfg.vocab_size % (128 * 2) == 0 and not cfg.add_bias_linear and cfg.add_qkv_bias and not cfg.tie_embeddings
     assert par.tp == 2 and par.ep == 2 and par.sequence_parallel and par.use_distributed_optimizer
-    assert cfg.recompute_granularity == "selective" and cfg.fp8 == "block" and tc.bf16
+    assert cfg.recompute_granularity == "selective" and cfg.fp8 == "rowwise" and tc.bf16
     assert cfg.cpu_offloading and cfg.cpu_offloading_num_layers == 2 and args.cuda_graph_decode
     assert cfg.params_dtype == torch.bfloat16 and cfg.moe_token_dropping and cfg.moe_train_capacity_factor == 1.25
     names = {a.dest for a in build_parser()._actions}
