@@ -253,6 +253,167 @@ __global__ void __launch_bounds__(NT) delta_scan_bwd_kernel(Args a) {
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// Chunk-parallel construction of the tiles (forward): one CTA per (batch, head, chunk).
+//   b_i = inclusive cumulative log decay inside the chunk,  Gamma_ij = e^{b_i - b_j}
+//   A   = strictly-lower(diag(beta) (K K^T . Gamma)),   T = (I + A)^{-1}   (column c of T lives in the registers of
+//         thread c: row i needs only rows < i of the same column, so the substitution runs without any barrier)
+//   W = T (beta e^{b} K),  U = T (beta V),  Aqk = scale tril((Q K^T) . Gamma),  Qd = scale e^{b} Q,  Kd = e^{b_C - b} K
+// ---------------------------------------------------------------------------------------------------------------
+struct PrepArgs {
+    const bf16 *q, *k, *v;             // [B,T,H,D] with the strides below (elements)
+    long long qs_b, qs_t, qs_h, ks_b, ks_t, ks_h, vs_b, vs_t, vs_h;
+    const float* beta;                 // [B,T,H]
+    const float* g;                    // [B,T,H] log decay, or null
+    bf16 *W, *U, *Qd, *Kd, *A;         // outputs, [BH, N, C, D] / [BH, N, C, C]
+    float* gamma;                      // [BH, N]
+    int B, T, H, N;
+    float scale;
+};
+
+template <int D>
+__global__ void __launch_bounds__(NT) delta_prep_fwd_kernel(PrepArgs a) {
+    constexpr int LD = D + 8, LDC = C + 8, LDA = C + 1;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Ks = reinterpret_cast<bf16*>(smem_raw);            // [C][LD]
+    bf16* Vs = Ks + C * LD;                                  // [C][LD]  V, then beta V
+    bf16* Qs = Vs + C * LD;                                  // [C][LD]
+    bf16* Kb = Qs + C * LD;                                  // [C][LD]  beta e^b K
+    bf16* Tb = Kb + C * LD;                                  // [C][LDC] T in bf16
+    float* A32 = reinterpret_cast<float*>(Tb + C * LDC);     // [C][LDA] strictly lower A
+    float* bcum = A32 + C * LDA;                             // [C]
+    float* bet = bcum + C;                                   // [C]
+    const int n = blockIdx.x, bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    const int t0 = n * C;
+    const int valid = min(C, a.T - t0);
+    const long long cn = (long long)bh * a.N + n;
+
+    load_tile_async<C, D, LD>(Ks, a.k + b * a.ks_b + h * a.ks_h + (long long)t0 * a.ks_t, a.ks_t, valid);
+    load_tile_async<C, D, LD>(Vs, a.v + b * a.vs_b + h * a.vs_h + (long long)t0 * a.vs_t, a.vs_t, valid);
+    load_tile_async<C, D, LD>(Qs, a.q + b * a.qs_b + h * a.qs_h + (long long)t0 * a.qs_t, a.qs_t, valid);
+    cp_async_commit();
+    if (w == 0) {                                            // decay table: two tokens per lane, warp scan
+        const int i0 = 2 * l, i1 = 2 * l + 1;
+        float g0 = 0.f, g1 = 0.f, be0 = 0.f, be1 = 0.f;
+        if (i0 < valid) {
+            const long long o = ((long long)b * a.T + t0 + i0) * a.H + h;
+            be0 = a.beta[o];
+            if (a.g != nullptr) g0 = a.g[o];
+        }
+        if (i1 < valid) {
+            const long long o = ((long long)b * a.T + t0 + i1) * a.H + h;
+            be1 = a.beta[o];
+            if (a.g != nullptr) g1 = a.g[o];
+        }
+        float s = g0 + g1;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const float x = __shfl_up_sync(0xffffffffu, s, o);
+            if (l >= o) s += x;
+        }
+        bcum[i1] = s;
+        bcum[i0] = s - g1;
+        bet[i0] = be0;
+        bet[i1] = be1;
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+    const float btot = bcum[C - 1];
+    // ---- K K^T -> A (fp32, strictly lower) and Q K^T -> Aqk (bf16, to global); warp w owns rows 16w .. 16w+15
+    {
+        float kk[8][4], qk[8][4];
+        zero_acc<8>(kk);
+        zero_acc<8>(qk);
+        warp_gemm<8, D, false, false>(kk, Ks, LD, 16 * w, Ks, LD, 0);
+        warp_gemm<8, D, false, false>(qk, Qs, LD, 16 * w, Ks, LD, 0);
+        bf16* Ag = a.A + cn * C * C;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int i = 16 * w + (l >> 2) + 8 * hh;
+                const int j = nt * 8 + (l & 3) * 2;
+                const float bi = bcum[i], be = bet[i];
+                const float d0 = __expf(bi - bcum[j]), d1 = __expf(bi - bcum[j + 1]);
+                A32[i * LDA + j] = i > j ? be * d0 * kk[nt][2 * hh] : 0.f;
+                A32[i * LDA + j + 1] = i > j + 1 ? be * d1 * kk[nt][2 * hh + 1] : 0.f;
+                const float a0 = i >= j ? a.scale * d0 * qk[nt][2 * hh] : 0.f;
+                const float a1 = i >= j + 1 ? a.scale * d1 * qk[nt][2 * hh + 1] : 0.f;
+                *reinterpret_cast<__nv_bfloat162*>(Ag + i * C + j) = __floats2bfloat162_rn(a0, a1);
+            }
+    }
+    __syncthreads();
+    // ---- threads 0..63: column c of T = (I + A)^{-1} by forward substitution, entirely in registers;
+    //      threads 64..127: the elementwise tiles (beta e^b K -> Kb, beta V in place, Qd and Kd to global)
+    if (threadIdx.x < C) {
+        const int c = threadIdx.x;
+        float t[C];
+#pragma unroll
+        for (int i = 0; i < C; ++i) {
+            float acc = (i == c) ? 1.f : 0.f;
+#pragma unroll
+            for (int j = 0; j < i; ++j) acc -= A32[i * LDA + j] * t[j];
+            t[i] = acc;
+        }
+#pragma unroll
+        for (int i = 0; i < C; ++i) Tb[i * LDC + c] = __float2bfloat16(t[i]);
+    } else {
+        const int tid = threadIdx.x - C;                      // 0..63: one row each
+        const int i = tid;
+        const float bi = bcum[i], be = bet[i];
+        const float fk = be * __expf(bi), fq = a.scale * __expf(bi), fd = __expf(btot - bi);
+        bf16* Qg = a.Qd + (cn * C + i) * D;
+        bf16* Kg = a.Kd + (cn * C + i) * D;
+#pragma unroll 4
+        for (int c = 0; c < D; c += 8) {
+            Vec<bf16> kx, vx, qx, o1, o2, o3, o4;
+            kx.load(Ks + i * LD + c);
+            vx.load(Vs + i * LD + c);
+            qx.load(Qs + i * LD + c);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                o1.set(e, kx.get(e) * fk);
+                o2.set(e, vx.get(e) * be);
+                o3.set(e, qx.get(e) * fq);
+                o4.set(e, kx.get(e) * fd);
+            }
+            o1.store(Kb + i * LD + c);
+            o2.store(Vs + i * LD + c);
+            o3.store(Qg + c);
+            o4.store(Kg + c);
+        }
+        if (tid == 0) a.gamma[cn] = __expf(btot);
+    }
+    __syncthreads();
+    // ---- W = T Kb, U = T (beta V): warp w -> rows 16w .. 16w+15, all D columns
+    {
+        float acc[D / 8][4];
+        zero_acc<D / 8>(acc);
+        warp_gemm<D / 8, C, false, true>(acc, Tb, LDC, 16 * w, Kb, LD, 0);
+        bf16* Wg = a.W + cn * C * D;
+        const int r = 16 * w + (l >> 2), cc = (l & 3) * 2;
+#pragma unroll
+        for (int nt = 0; nt < D / 8; ++nt) {
+            *reinterpret_cast<__nv_bfloat162*>(Wg + r * D + cc + nt * 8) = __floats2bfloat162_rn(acc[nt][0], acc[nt][1]);
+            *reinterpret_cast<__nv_bfloat162*>(Wg + (r + 8) * D + cc + nt * 8) = __floats2bfloat162_rn(acc[nt][2], acc[nt][3]);
+        }
+        zero_acc<D / 8>(acc);
+        warp_gemm<D / 8, C, false, true>(acc, Tb, LDC, 16 * w, Vs, LD, 0);
+        bf16* Ug = a.U + cn * C * D;
+#pragma unroll
+        for (int nt = 0; nt < D / 8; ++nt) {
+            *reinterpret_cast<__nv_bfloat162*>(Ug + r * D + cc + nt * 8) = __floats2bfloat162_rn(acc[nt][0], acc[nt][1]);
+            *reinterpret_cast<__nv_bfloat162*>(Ug + (r + 8) * D + cc + nt * 8) = __floats2bfloat162_rn(acc[nt][2], acc[nt][3]);
+        }
+    }
+}
+
+template <int D> constexpr size_t prep_smem() {
+    return (size_t)(4 * C * (D + 8) + C * (C + 8)) * 2 + (size_t)(C * (C + 1) + 2 * C) * 4;
+}
+
 }  // namespace dr
 }  // namespace lmoe
 
@@ -272,5 +433,22 @@ LMOE_API int lmoe_delta_scan(int dir, int dk, int BH, const dr::Args* ap, cudaSt
     if (dir == 0) { if (dk == 128) LMOE_DR_LAUNCH(dr::delta_scan_fwd_kernel, 128); else LMOE_DR_LAUNCH(dr::delta_scan_fwd_kernel, 64); }
     else { if (dk == 128) LMOE_DR_LAUNCH(dr::delta_scan_bwd_kernel, 128); else LMOE_DR_LAUNCH(dr::delta_scan_bwd_kernel, 64); }
 #undef LMOE_DR_LAUNCH
+    return (int)cudaGetLastError();
+}
+
+// Tiles of the chunked (gated) delta rule for every chunk of every (batch, head): grid (N, B*H).  dk = dv = D in {64, 128}.
+LMOE_API int lmoe_delta_prepare(int D, const dr::PrepArgs* ap, cudaStream_t st) {
+    const dr::PrepArgs a = *ap;
+    if (a.N <= 0 || a.B * a.H <= 0) return -1;
+    dim3 grid(a.N, a.B * a.H);
+    if (D == 128) {
+        cudaError_t e = cudaFuncSetAttribute(dr::delta_prep_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dr::prep_smem<128>());
+        if (e != cudaSuccess) return (int)e;
+        dr::delta_prep_fwd_kernel<128><<<grid, dr::NT, dr::prep_smem<128>(), st>>>(a);
+    } else if (D == 64) {
+        cudaError_t e = cudaFuncSetAttribute(dr::delta_prep_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dr::prep_smem<64>());
+        if (e != cudaSuccess) return (int)e;
+        dr::delta_prep_fwd_kernel<64><<<grid, dr::NT, dr::prep_smem<64>(), st>>>(a);
+    } else return -2;
     return (int)cudaGetLastError();
 }

@@ -1084,6 +1084,38 @@ def _delta_prepare(q, k, v, beta, g, scale, C=64):
             Aqk.to(bf).contiguous(), btot.exp().contiguous())
 
 
+class _DeltaPrepArgs(ctypes.Structure):
+    _fields_ = ([(n, ctypes.c_void_p) for n in ("q", "k", "v")] +
+                [(n, ctypes.c_longlong) for n in ("qs_b", "qs_t", "qs_h", "ks_b", "ks_t", "ks_h", "vs_b", "vs_t", "vs_h")] +
+                [(n, ctypes.c_void_p) for n in ("beta", "g", "W", "U", "Qd", "Kd", "A", "gamma")] +
+                [(n, ctypes.c_int) for n in ("B", "T", "H", "N")] + [("scale", ctypes.c_float)])
+
+
+def _delta_prepare_kernel(q, k, v, beta, g, scale, C=64):
+    """The tiles of :func:`_delta_prepare` from one chunk-parallel kernel (``delta_prep_fwd_kernel``, csrc/lsm_delta.cu):
+    K K^T, the triangular inverse (forward substitution in registers), W, U, Q K^T and the decay-scaled copies of Q, K.
+    No autograd: used by the forward pass, which keeps only the inputs."""
+    B, T, H, D = q.shape
+    N = (T + C - 1) // C
+    q, k, v = _inner_contig(q), _inner_contig(k), _inner_contig(v)
+    bf, dev = torch.bfloat16, q.device
+    W, U, Qd, Kd = (torch.empty(B, H, N, C, D, dtype=bf, device=dev) for _ in range(4))
+    A = torch.empty(B, H, N, C, C, dtype=bf, device=dev)
+    gamma = torch.empty(B, H, N, dtype=torch.float32, device=dev)
+    bt = beta.float().contiguous()
+    gt = None if g is None else g.float().contiguous()
+    a = _DeltaPrepArgs()
+    a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    a.qs_b, a.qs_t, a.qs_h = q.stride(0), q.stride(1), q.stride(2)
+    a.ks_b, a.ks_t, a.ks_h = k.stride(0), k.stride(1), k.stride(2)
+    a.vs_b, a.vs_t, a.vs_h = v.stride(0), v.stride(1), v.stride(2)
+    a.beta, a.g = bt.data_ptr(), 0 if gt is None else gt.data_ptr()
+    a.W, a.U, a.Qd, a.Kd, a.A, a.gamma = (t.data_ptr() for t in (W, U, Qd, Kd, A, gamma))
+    a.B, a.T, a.H, a.N, a.scale = B, T, H, N, float(scale)
+    _check(lib().lmoe_delta_prepare(_i32(D), ctypes.byref(a), _st()), "delta_prepare")
+    return W, U, Qd, Kd, A, gamma
+
+
 class _DeltaChunkScan(torch.autograd.Function):
     """The recurrence over chunks of the (gated) delta rule on the kernels of ``csrc/lsm_delta.cu``:
     ``Vn = U - W S``, ``O = Qd S + A Vn``, ``S' = gamma S + Kd^T Vn``.  Backward: the reverse state-gradient recurrence is
@@ -1149,7 +1181,10 @@ class _DeltaRuleScan(torch.autograd.Function):
         B, T, H, dk = q.shape
         scale = dk ** -0.5 if scale is None else scale
         with torch.no_grad(), _tf32():
-            tiles = _delta_prepare(q, k, v, beta, g, scale)
+            if q.dtype == k.dtype == v.dtype == torch.bfloat16 and v.shape[-1] == dk and os.environ.get("LMOE_DELTA_PREP_KERNEL", "1") != "0":
+                tiles = _delta_prepare_kernel(q, k, v, beta, g, scale)
+            else:
+                tiles = _delta_prepare(q, k, v, beta, g, scale)
             O, S = _DeltaChunkScan.apply(*tiles, initial_state)
         ctx.save_for_backward(q, k, v, beta, g, initial_state)
         ctx.scale = scale

@@ -476,3 +476,22 @@ def test_lsm_delta_decode_step(D, gated, with_state):
     o_ref, S_ref = recurrent_lsm(q.float(), k.float(), v.float(), g=g, beta=beta, initial_state=S0)
     assert torch.allclose(S, S_ref, atol=2e-4, rtol=1e-4), (S - S_ref).abs().max()
     assert torch.allclose(o.float(), o_ref, atol=3e-2, rtol=2e-2), (o.float() - o_ref).abs().max()
+
+
+@pytest.mark.parametrize("D,T,gated", [(64, 70, True), (128, 300, True), (128, 256, False)])
+def test_delta_prepare_kernel_matches_torch_tiles(D, T, gated):
+    """The chunk-parallel tile kernel (K K^T, triangular inverse by substitution, W, U, Q K^T, scaled Q / K) against the
+    same tiles built with torch ops in fp32."""
+    torch.manual_seed(3)
+    B, H = 2, 3
+    qkv = (0.5 * torch.randn(B, T, H, 3 * D, device=dev())).to(torch.bfloat16)
+    q, k, v = qkv.split(D, dim=-1)                                   # strided views
+    k = torch.nn.functional.normalize(k.float(), dim=-1).to(torch.bfloat16)
+    beta = torch.rand(B, T, H, device=dev())
+    g = torch.nn.functional.logsigmoid(torch.randn(B, T, H, device=dev()) + 1.0) if gated else None
+    got = K._delta_prepare_kernel(q, k, v, beta, g, D ** -0.5)
+    ref = K._delta_prepare(q, k, v, beta, g, D ** -0.5)
+    torch.cuda.synchronize()
+    for name, a, b in zip(["W", "U", "Qd", "Kd", "A", "gamma"], got, ref):
+        rel = ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-6)).item()
+        assert rel < 1e-2, (name, rel)

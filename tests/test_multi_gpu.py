@@ -77,18 +77,22 @@ def _zero_worker(rank, world, multicast):
     cfg = get_preset("bench-lasp2-llama3-1b", num_layers=2, layer_type_list="LL", vocab_size=2048, hidden_size=256,
                      num_attention_heads=2, ffn_hidden_size=512)
     outs = {}
-    for fused in (True, False):
-        par = ParallelConfig(use_distributed_optimizer=True, fused_comm=fused)
+    for fused in (True, False, "no_overlap"):
+        par = ParallelConfig(use_distributed_optimizer=True, fused_comm=bool(fused), overlap_grad_reduce=fused is True)
         mesh = Mesh(par)
         tc = TrainConfig(micro_batch_size=1, global_batch_size=world, seq_length=256, train_iters=4, bf16=True,
                          log_interval=1000, lr=1e-3, min_lr=1e-3, lr_decay_style="constant", seed=7)
         tr = Trainer(cfg, par, tc, mesh, device=dev)
-        assert (tr.optimizer.buffers[0].fused is not None) == fused
+        assert (tr.optimizer.buffers[0].fused is not None) == bool(fused)
+        if fused is True:
+            assert getattr(tr.model, "grad_ready_hook", None) is not None, "the bucketed reduce is not wired"
         losses = [float(tr.train_step()["lm loss"]) for _ in range(4)]
         torch.cuda.synchronize()
         fused_comm.check_status("zero test")
         outs[fused] = (losses, torch.cat([b.params.float().cpu() for b in tr.optimizer.buffers]))
-    mc = tr.optimizer.buffers[0].fused is None and None
+    # the bucketed reduce-scatter that overlaps the backward pass sums the same values in the same order as the single
+    # launch after it: parameters must agree bit for bit
+    assert torch.equal(outs[True][1], outs["no_overlap"][1]), "overlapped and non-overlapped fused ZeRO-1 differ"
     return outs[True][0], outs[False][0], (outs[True][1] - outs[False][1]).abs().max().item(), outs[False][1].abs().max().item()
 
 
