@@ -29,9 +29,14 @@ def main():
     ap.add_argument("--microbatches", type=int, default=1)
     ap.add_argument("--layers", type=int, default=None)
     ap.add_argument("--zero1", action="store_true")
+    ap.add_argument("--baseline-eager", action="store_true",
+                    help="stand-in for the reference's NCCL + cuBLAS build: NCCL collectives instead of the fused peer-memory "
+                         "kernels and library GEMMs instead of the tcgen05 dense kernel (same model, same step)")
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
+    if a.baseline_eager:
+        os.environ["LMOE_TCGEN05_GEMM"] = "0"
     from ..config.model_config import ParallelConfig, TrainConfig
     from ..config.presets import get_preset
     from ..dist.mesh import init_distributed
@@ -41,7 +46,8 @@ def main():
     from ..train.loop import Trainer
     world = int(os.environ.get("WORLD_SIZE", "1"))
     par = ParallelConfig(tensor_model_parallel_size=a.tp, sequence_parallel=a.tp > 1, expert_model_parallel_size=a.ep,
-                         context_parallel_size=a.cp, use_distributed_optimizer=a.zero1, distributed_backend="nccl")
+                         context_parallel_size=a.cp, use_distributed_optimizer=a.zero1, distributed_backend="nccl",
+                         fused_comm=not a.baseline_eager, overlap_grad_reduce=not a.baseline_eager)
     mesh = init_distributed(par)
     dev = torch.device("cuda", torch.cuda.current_device())
     over = {}
@@ -69,6 +75,8 @@ def main():
         last = trainer.train_step()
     sync()
     K.reset_launch_count()
+    from .clocks import ClockSampler
+    sampler = ClockSampler(torch.cuda.current_device()) if mesh.rank == 0 else None
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(a.steps):
@@ -78,6 +86,7 @@ def main():
     ms = torch.tensor([e0.elapsed_time(e1) / a.steps], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    clocks = sampler.stop() if sampler is not None else None
     launches = K.reset_launch_count() // a.steps
     fused_comm.check_status("bench configs")
     gemm.check_error()
@@ -88,7 +97,9 @@ def main():
                           (" zero1" if a.zero1 else ""), "tokens_per_step": tokens, "ms_per_step": float(ms),
                           "tokens_per_s": tokens / (float(ms) / 1e3), "params_this_rank": n_params, "layers": cfg.num_layers,
                           "loss": float(last["lm loss"]) if last and "lm loss" in last else None, "own_kernel_launches": launches,
-                          "peak_mem_gib": round(mem, 1), "fp8": bool(cfg.fp8), "valid": a.layers is None}))
+                          "peak_mem_gib": round(mem, 1), "fp8": bool(cfg.fp8), "valid": a.layers is None,
+                          "impl": "baseline-eager (NCCL + cuBLAS)" if a.baseline_eager else "ours", "clocks": clocks,
+                          "global_batch": gbs, "seq_len": a.seq}))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()

@@ -1192,7 +1192,7 @@ LMOE_API const char* lmoe_noalloc_strerror(int code) {
         case 0: return "ok";
         case LMOE_NOALLOC_ERR_SIZE:
             return "lmoe_rms_norm_bwd_noalloc: N exceeds LMOE_NOALLOC_MAX_N (4096) or is not a multiple of the "
-                   "vector width (8 for bf16, 4 for fp32)";
+                   "vector width (8 for bf16, 4 for fp32), or rows exceeds 2^31 - 1";
         case LMOE_NOALLOC_ERR_SETUP:
             return "lmoe_rms_norm_bwd_noalloc: could not obtain the device address of the built-in scratch array";
         default: return "lmoe_rms_norm_bwd_noalloc: CUDA launch error (code is a cudaError_t)";
@@ -1204,10 +1204,13 @@ LMOE_API int lmoe_rms_norm_bwd_noalloc(const void* dy, const void* xin, const vo
                                        cudaStream_t st) {
     const int vn = dtype == 1 ? 8 : 4;
     if (N <= 0 || N > LMOE_NOALLOC_MAX_N || N % vn != 0) return LMOE_NOALLOC_ERR_SIZE;
+    if (rows < 0 || rows > 2147483647LL) return LMOE_NOALLOC_ERR_SIZE;      // the kernels take the row count as an int
+    if (rows == 0) return 0;
     float* scratch = nullptr;
     int rc = noalloc_scratch(&scratch);
     if (rc != 0) return rc;
     // same kernels as lmoe_rms_norm_bwd, with the built-in array as the partials buffer
-    return lmoe_rms_norm_bwd(dy, xin, w, rstd, dres, dx, w != nullptr ? scratch : nullptr, dw, rows, N,
-                             LMOE_NOALLOC_MAX_BLOCKS, dtype, st);
+    rc = lmoe_rms_norm_bwd(dy, xin, w, rstd, dres, dx, w != nullptr ? scratch : nullptr, dw, rows, N,
+                           LMOE_NOALLOC_MAX_BLOCKS, dtype, st);
+    return rc < 0 ? LMOE_NOALLOC_ERR_SIZE : rc;        // the launcher's own size refusals (-1, -2) are size errors too
 }

@@ -12,7 +12,8 @@
 //   * The array is LMOE_NOALLOC_MAX_BLOCKS x LMOE_NOALLOC_MAX_N floats (4.6 MiB).  Every GPU that loads the
 //     library holds it from load until the process exits.
 //   * N (the normalised width) must be <= LMOE_NOALLOC_MAX_N and a multiple of 8 (bf16) or 4 (fp32);
-//     otherwise the call returns LMOE_NOALLOC_ERR_SIZE and launches nothing.  rows is unlimited.
+//     otherwise the call returns LMOE_NOALLOC_ERR_SIZE and launches nothing.  rows may be anything from 0 up to
+//     2^31 - 1 (the kernels index rows with a 32-bit integer); more is refused with LMOE_NOALLOC_ERR_SIZE too.
 //   * The first call on each device looks up the array's device address (cudaGetSymbolAddress) with that
 //     device current.  Make that first call before any stream capture begins.
 //   * The function calls no cudaMalloc / cudaFree and no allocating library routine.
@@ -28,7 +29,7 @@
 
 #define LMOE_NOALLOC_MAX_BLOCKS 296
 #define LMOE_NOALLOC_MAX_N 4096
-#define LMOE_NOALLOC_ERR_SIZE (-100)     /* N too large or not a multiple of the vector width */
+#define LMOE_NOALLOC_ERR_SIZE (-100)     /* N too large / not a multiple of the vector width, or rows >= 2^31 */
 #define LMOE_NOALLOC_ERR_SETUP (-101)    /* the device address of the scratch array could not be obtained */
 
 #ifdef __cplusplus

@@ -199,8 +199,9 @@ class MixedPrecisionAdam:
         model order), or None."""
         cache = b.__dict__.setdefault("_layer_ranges", {})
         if layer not in cache:
+            # slot names carry the position of the model chunk in the optimizer's module list ("0.decoder.layers.3...")
             pre = f"decoder.layers.{layer}."
-            sl = [s for s in b.slots if s.name.startswith(pre)]
+            sl = [s for s in b.slots if s.name.startswith(pre) or f".{pre}" in s.name]
             cache[layer] = None if not sl else (min(s.start for s in sl), max(s.start + s.numel for s in sl))
         return cache[layer]
 

@@ -87,6 +87,10 @@ def _zero_worker(rank, world, multicast):
         if fused is True:
             assert getattr(tr.model, "grad_ready_hook", None) is not None, "the bucketed reduce is not wired"
         losses = [float(tr.train_step()["lm loss"]) for _ in range(4)]
+        if fused is True:
+            fb = [b for b in tr.optimizer.buffers if b.fused is not None]
+            assert any(tr.optimizer._layer_range(b, 0) is not None for b in fb), "no block maps to a gradient bucket"
+            assert max(b.fused._next_slot for b in fb) > 2, "the reduce-scatter was not split into buckets"
         torch.cuda.synchronize()
         fused_comm.check_status("zero test")
         outs[fused] = (losses, torch.cat([b.params.float().cpu() for b in tr.optimizer.buffers]))
