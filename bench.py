@@ -38,6 +38,8 @@ def parse():
     p.add_argument("--tokens-per-gpu", type=int, default=TOKENS_PER_GPU)
     p.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (marks the result invalid)")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--overlap-grad-reduce", action=argparse.BooleanOptionalAction, default=True,
+                   help="reduce-scatter the gradients of a block while the backward pass of the blocks before it runs")
     p.add_argument("--zero1", action=argparse.BooleanOptionalAction, default=True,
                    help="distributed optimizer (ZeRO-1) through the fused NVLS kernels when N > 1 (the reference launchers default to DO=true)")
     return p.parse_args()
@@ -68,7 +70,8 @@ def main():
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
-    par = ParallelConfig(context_parallel_size=world, use_distributed_optimizer=args.zero1, distributed_backend="nccl")
+    par = ParallelConfig(context_parallel_size=world, use_distributed_optimizer=args.zero1, distributed_backend="nccl",
+                         overlap_grad_reduce=args.overlap_grad_reduce)
     mesh = init_distributed(par)
     dev = torch.device("cuda", torch.cuda.current_device())
     overrides = {} if args.layers is None else {"num_layers": args.layers, "layer_type_list": "L" * args.layers}
@@ -148,7 +151,8 @@ def main():
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
             "impl": "ours",
             "config": {"model": args.config, "global_batch": 1, "seq_len": seq, "tokens_per_gpu": args.tokens_per_gpu,
-                       "parallelism": f"sp{world} (LASP-2)" + (" zero1" if args.zero1 else ""), "params": n_params,
+                       "parallelism": f"sp{world} (LASP-2)" + (" zero1" if args.zero1 else "") +
+                       (" overlap-grad-reduce" if (args.zero1 and args.overlap_grad_reduce and world > 1) else ""), "params": n_params,
                        "layers": cfg.num_layers, "l2": "inputs larger than L2 (16384x2048 bf16 activations, 3.3 GB weights)",
                        "optimizer": "AdamW fp32 masters, clip 1.0", "valid": args.layers is None},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,

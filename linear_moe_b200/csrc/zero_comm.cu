@@ -87,21 +87,36 @@ __global__ void zero_reduce_kernel(ZeroArgs a) {
     wait_all(a, phase, 1);
     __syncthreads();
     float ss = 0.f;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
-        const long long e = a.lo + i * 4;
-        float4 v;
-        if (a.grads_mc != nullptr) {
-            v = mc_ld_reduce_f32x4(a.grads_mc + e);
-        } else {
-            v = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int j = 0; j < a.world; ++j) {
-                float4 p = __ldcg(reinterpret_cast<const float4*>(a.peer_grads[j] + e));
-                v.x += p.x; v.y += p.y; v.z += p.z; v.w += p.w;
+    // four independent 16-byte reductions in flight per thread: a bucket launched next to the backward pass runs on a
+    // few dozen CTAs only, and the in-switch reduction has microseconds of latency
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (long long i0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; i0 < n4; i0 += 4 * stride) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const long long i = i0 + u * stride;
+            if (i >= n4) { v[u] = make_float4(0.f, 0.f, 0.f, 0.f); continue; }
+            const long long e = a.lo + i * 4;
+            if (a.grads_mc != nullptr) {
+                v[u] = mc_ld_reduce_f32x4(a.grads_mc + e);
+            } else {
+                v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int j = 0; j < a.world; ++j) {
+                    float4 p = __ldcg(reinterpret_cast<const float4*>(a.peer_grads[j] + e));
+                    v[u].x += p.x; v[u].y += p.y; v[u].z += p.z; v[u].w += p.w;
+                }
             }
         }
-        v.x *= a.grad_scale; v.y *= a.grad_scale; v.z *= a.grad_scale; v.w *= a.grad_scale;
-        *reinterpret_cast<float4*>(a.grads + e) = v;
-        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const long long i = i0 + u * stride;
+            if (i >= n4) continue;
+            const long long e = a.lo + i * 4;
+            float4 x = v[u];
+            x.x *= a.grad_scale; x.y *= a.grad_scale; x.z *= a.grad_scale; x.w *= a.grad_scale;
+            *reinterpret_cast<float4*>(a.grads + e) = x;
+            ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+        }
     }
     ss = block_sum(ss, red);
     if (threadIdx.x == 0) atomicAdd(a.sumsq, ss);

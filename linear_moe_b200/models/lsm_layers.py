@@ -345,7 +345,9 @@ class LerpLinear(nn.Module):
     def forward(self, x, delta=None):
         if delta is None:
             delta = F.pad(x, (0, 0, 1, -1)) - x
-        return self.linear(x + delta * self.mu)
+        inp = x + delta * self.mu
+        tp_in = getattr(self, "tp_in", None)
+        return self.linear(inp if tp_in is None else tp_in(inp))
 
 
 class DDLerpLinear(nn.Module):
@@ -361,7 +363,9 @@ class DDLerpLinear(nn.Module):
     def forward(self, x, mu, delta=None):
         if delta is None:
             delta = F.pad(x, (0, 0, 1, -1)) - x
-        return self.linear(x + delta * mu)
+        inp = x + delta * mu
+        tp_in = getattr(self, "tp_in", None)
+        return self.linear(inp if tp_in is None else tp_in(inp))
 
 
 class LoRA(nn.Module):
@@ -375,18 +379,48 @@ class LoRA(nn.Module):
                                   nn.Linear(low_rank, out, bias=bias, dtype=dtype, device=device))
 
     def forward(self, x):
-        return self.lora(x)
+        tp_in = getattr(self, "tp_in", None)
+        if tp_in is None:
+            return self.lora(x)
+        return self.lora[2](tp_in(self.lora[1](self.lora[0](x))))      # head-sharded up-projection under TP
+
+
+class _HeadShardedInput(nn.Module):
+    """Marks the input of a head-sharded projection under tensor parallelism: identity in the forward pass, all-reduce of
+    the gradient over the TP group in the backward pass, so that everything upstream (the block input, the token-shift
+    mixing coefficients, the replicated low-rank factors) receives the complete gradient on every rank."""
+
+    def __init__(self, mesh: Mesh, enabled: bool):
+        super().__init__()
+        self.mesh, self.enabled = mesh, enabled
+
+    def forward(self, x):
+        return C.copy_to_region(x, self.mesh["tp"]) if self.enabled else x
+
+
+def _shard_rows(linear: nn.Linear, mesh: Mesh):
+    """Keep this TP rank's block of output rows (= its heads) of a projection that was initialised at full size."""
+    linear.weight = nn.Parameter(_tp_slice(linear.weight.data, mesh, 0))
+    linear.weight.tensor_parallel, linear.weight.partition_dim, linear.weight.partition_stride = True, 0, 1
+    if linear.bias is not None:
+        linear.bias = nn.Parameter(_tp_slice(linear.bias.data, mesh, 0))
+        linear.bias.tensor_parallel, linear.bias.partition_dim, linear.bias.partition_stride = True, 0, 1
+    linear.out_features = linear.weight.shape[0]
 
 
 class LinearRNN(nn.Module):
-    """HGRN2 / RWKV6 / RWKV7 token mixers.  These run with replicated projections (no TP sharding of
-    the low-rank mixers, as in the reference) and are built for tp == 1."""
+    """HGRN2 / RWKV6 / RWKV7 token mixers.  Under tensor parallelism the heads are split over the TP ranks: every
+    projection into key / value space keeps its ranks' rows, the per-head vectors are sliced, the low-rank mixers in
+    front of them stay replicated (their gradients are completed by an all-reduce at the sharded projections' inputs)
+    and ``o_proj`` is row-parallel.  (The reference builds these mixers without TP support.)"""
 
     def __init__(self, cfg: ModelConfig, mesh: Optional[Mesh] = None, layer_number: int = 1, key: str = "",
                  sequence_parallel: bool = False, device=None):
         super().__init__()
         self.cfg, self.mesh = cfg, mesh or single_process_mesh()
-        assert self.mesh.tp == 1, "LinearRNN mixers (hgrn2/rwkv6/rwkv7) support tensor parallel size 1 only"
+        tp = self.mesh.tp
+        assert not (sequence_parallel and tp > 1), "LinearRNN mixers: tensor parallelism without sequence parallelism only"
+        assert cfg.num_attention_heads % tp == 0, "heads must divide over the tensor-parallel ranks"
         self.kind = cfg.la_module
         H, hid = cfg.num_attention_heads, cfg.hidden_size
         self.H = H
@@ -430,6 +464,34 @@ class LinearRNN(nn.Module):
         self.o_proj = RowParallelLinear(self.value_dim, hid, mesh=self.mesh, std=out_std, key=key + ".o_proj",
                                         dtype=dt, device=device)
         self.norm_weight = nn.Parameter(torch.ones(self.dv, **kw)) if cfg.la_output_norm != "identity" else None
+        self.tp_in = _HeadShardedInput(self.mesh, tp > 1)
+        if tp > 1:
+            self._shard_for_tp()
+
+    def _shard_for_tp(self):
+        """Cut the full-size, seed-initialised parameters down to this rank's heads (same values as the tp = 1 model)."""
+        mesh = self.mesh
+        self.H = self.H // mesh.tp
+        projs = {"rwkv6": ["r_proj", "w_proj", "k_proj", "v_proj", "g_proj"],
+                 "rwkv7": ["r_proj", "k_proj", "v_proj", "w_proj", "a_proj", "g_proj"],
+                 "hgrn2": ["q_proj", "f_proj", "i_proj"]}[self.kind]
+        for name in projs:
+            m = getattr(self, name)
+            if isinstance(m, nn.Linear):
+                _shard_rows(m, mesh)
+                continue
+            inner = m.linear if hasattr(m, "linear") else m          # DDLerpLinear -> Linear | LoRA; or a bare LoRA
+            if isinstance(inner, nn.Linear):
+                _shard_rows(inner, mesh)
+                m.tp_in = _HeadShardedInput(mesh, True)
+            else:
+                _shard_rows(inner.lora[2], mesh)                      # LoRA: the up-projection carries the heads
+                inner.tp_in = _HeadShardedInput(mesh, True)
+        for name in ("bonus", "booster", "removal"):
+            if hasattr(self, name):
+                p = nn.Parameter(_tp_slice(getattr(self, name).data, mesh, 0))
+                p.tensor_parallel, p.partition_dim, p.partition_stride = True, 0, 1
+                setattr(self, name, p)
 
     def _shift(self, x, cache, name="shift"):
         """Token shift ``x_{t-1}`` with sequence-parallel halo and decode cache."""
@@ -474,9 +536,9 @@ class LinearRNN(nn.Module):
             assert self.mesh["cp"].is_trivial, "rwkv7: sequence parallelism not available"
             delta = self._shift(x, cache) - x
             xr, xw, xk, xv, xa, xg = torch.addcmul(x[None], delta[None], self.x.view(6, 1, 1, -1)).unbind(0)
-            r = self.r_proj(xr)
+            r = self.r_proj(self.tp_in(xr))
             w = -math.exp(-0.5) * self.w_proj(xw).float().sigmoid()
-            k, v = self.k_proj(xk), self.v_proj(xv)
+            k, v = self.k_proj(self.tp_in(xk)), self.v_proj(self.tp_in(xv))
             a = self.a_proj(xa).sigmoid()
             g = self.g_proj(xg)
             kk = ops.l2_norm(hv(k * self.removal, self.dk)).reshape(B, T, -1)
@@ -490,7 +552,12 @@ class LinearRNN(nn.Module):
             o = o + ((hv(r, self.dk) * hv(k, self.dk) * self.bonus).sum(-1, keepdim=True) * hv(v, self.dv))
             o = o.reshape(B, T, -1) * act(g)
         else:  # hgrn2
-            q, f, i = F.silu(self.q_proj(x)), self.f_proj(x).float(), self.i_proj(x)
+            xs = self.tp_in(x)
+            q, f, i = F.silu(self.q_proj(xs)), self.f_proj(xs).float(), self.i_proj(xs)
+            if lower_bound is not None and self.mesh.tp > 1:
+                # the bounds are a replicated parameter indexed by key channel: take this rank's heads, complete its
+                # gradient over the TP ranks
+                lower_bound = _tp_slice(C.copy_to_region(lower_bound, self.mesh["tp"]), self.mesh, -1)
             if lower_bound is None or not self.cfg.hgrn2_lower_bound:
                 k, g = 1 - f.sigmoid(), F.logsigmoid(f)
             else:
@@ -504,4 +571,6 @@ class LinearRNN(nn.Module):
     def _out_norm(self, o):
         if self.norm_weight is None:
             return o
-        return ops.rms_norm(o.to(self.norm_weight.dtype).contiguous(), self.norm_weight, self.cfg.la_norm_eps)
+        # the per-head norm weight is shared by all heads: under TP its gradient is summed over the ranks' heads
+        w = C.copy_to_region(self.norm_weight, self.mesh["tp"])
+        return ops.rms_norm(o.to(self.norm_weight.dtype).contiguous(), w, self.cfg.la_norm_eps)

@@ -152,6 +152,18 @@ def linear_cross_entropy(h, weight, labels, ignore_index: int = -100, chunk: int
     return _ChunkedLinearCE.apply(h, weight, labels, ignore_index, chunk)
 
 
+def embedding(ids, weight, id_offset: int = 0, sharded: bool = False):
+    """Rows ``ids - id_offset`` of ``weight``; with ``sharded`` (vocabulary split over tensor-parallel ranks) ids outside
+    this shard give zero rows."""
+    if _cuda(weight):
+        return _K().embedding(ids, weight, id_offset, sharded)
+    if not sharded:
+        return F.embedding(ids, weight)
+    local = ids - id_offset
+    oob = (local < 0) | (local >= weight.shape[0])
+    return F.embedding(local.masked_fill(oob, 0), weight).masked_fill(oob[..., None], 0.0)
+
+
 # ---- norms / activations / rotary -----------------------------------------
 def rms_norm(x, weight=None, eps: float = 1e-6):
     if _cuda(x):

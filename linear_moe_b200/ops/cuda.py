@@ -286,6 +286,51 @@ class _RMSNorm(torch.autograd.Function):
         return dx, (dx if ctx.has_res else None), dw, None, None
 
 
+def _embedding_lookup(ids, weight, id_offset, sharded):
+    if not sharded:
+        return F.embedding(ids, weight)
+    local = ids - id_offset
+    oob = (local < 0) | (local >= weight.shape[0])
+    return F.embedding(local.masked_fill(oob, 0), weight).masked_fill(oob[..., None], 0.0)
+
+
+class _Embedding(torch.autograd.Function):
+    """Embedding lookup whose backward scatters the gradient rows straight into the table's fp32 accumulator
+    (``csrc/embedding.cu``), without the dense ``[vocab, hidden]`` gradient tensor and the pass that adds it."""
+
+    @staticmethod
+    def forward(ctx, ids, weight, id_offset, sharded):
+        ctx.save_for_backward(ids)
+        ctx.weight, ctx.id_offset = weight, int(id_offset)
+        return _embedding_lookup(ids, weight, id_offset, sharded)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (ids,) = ctx.saved_tensors
+        w = ctx.weight
+        V, h = w.shape
+        dy2 = dy.reshape(-1, h).contiguous()
+        idf = ids.reshape(-1).to(torch.int64).contiguous()
+        mg = getattr(w, "main_grad", None)
+        direct = mg is not None and mg.dtype == torch.float32 and mg.is_contiguous()
+        dst = mg if direct else torch.zeros(V, h, dtype=torch.float32, device=dy.device)
+        _check(lib().lmoe_embedding_bwd(_p(dy2), _p(idf), _p(dst), _i64(dy2.shape[0]), _i32(h), _i64(V), _i64(ctx.id_offset),
+                                        _i32(_dt(dy2)), _st()), "embedding_bwd")
+        if direct:
+            w._main_grad_fresh = False
+            return None, None, None, None
+        return None, dst.to(w.dtype), None, None
+
+
+def embedding(ids, weight, id_offset: int = 0, sharded: bool = False):
+    """``weight[ids - id_offset]``; with ``sharded`` ids outside this vocabulary shard give zero rows.  See
+    :class:`_Embedding` for the backward."""
+    if (weight.dtype not in (torch.bfloat16, torch.float32) or weight.shape[1] % 8
+            or not (weight.requires_grad and torch.is_grad_enabled())):
+        return _embedding_lookup(ids, weight, id_offset, sharded)
+    return _Embedding.apply(ids, weight, id_offset, sharded)
+
+
 class _LayerNorm(torch.autograd.Function):
     """LayerNorm (+ fused residual add) on the kernels of ``csrc/layernorm.cu``."""
 

@@ -167,11 +167,8 @@ class VocabParallelEmbedding(nn.Module):
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
         g = self.mesh["tp"]
         if g.is_trivial:
-            return F.embedding(ids, self.weight)
-        local = ids - self.start
-        oob = (local < 0) | (local >= self.per_rank)
-        e = F.embedding(local.masked_fill(oob, 0), self.weight)
-        e = e.masked_fill(oob[..., None], 0.0)
+            return ops.embedding(ids, self.weight)
+        e = ops.embedding(ids, self.weight, self.start, sharded=True)
         if self.sequence_parallel:
             return C.reduce_scatter(e, g, dim=1)
         return C.all_reduce(e, g)

@@ -24,6 +24,7 @@ weights, router, shared-expert gate) are additionally summed over TP under seque
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import Dict, Iterable, List, Optional, Tuple
 
@@ -113,6 +114,8 @@ class MixedPrecisionAdam:
         self.mesh, self.tc, self.zero1 = mesh, tc, zero1 and (mesh.dp * mesh.cp) > 1
         self.overlap_grad_reduce = overlap_grad_reduce
         self.overlap_active = False            # set by the schedule while the LAST micro-batch's backward runs
+        # CTAs of a bucket reduce launched next to the backward pass: few, so that the GEMMs keep their SMs
+        self.bucket_blocks = int(os.environ.get("LMOE_ZERO_BUCKET_BLOCKS", "48"))
         self._side_stream = None
         self._bucket_state = None              # per fused buffer: list of [lo, hi) ranges already reduced this step
         self.sequence_parallel = sequence_parallel and mesh.tp > 1
@@ -231,7 +234,7 @@ class MixedPrecisionAdam:
                 r = self._layer_range(b, layer)
                 if r is None:
                     continue
-                b.fused.reduce_range(r[0], r[1], b.shard, b.grad_scale)
+                b.fused.reduce_range(r[0], r[1], b.shard, b.grad_scale, blocks=self.bucket_blocks)
                 self._bucket_state[id(b)].append(r)
 
     def _finish_bucketed_with(self, b: "FlatBuffer", state):

@@ -495,3 +495,29 @@ def test_delta_prepare_kernel_matches_torch_tiles(D, T, gated):
     for name, a, b in zip(["W", "U", "Qd", "Kd", "A", "gamma"], got, ref):
         rel = ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-6)).item()
         assert rel < 1e-2, (name, rel)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("main_grad", [False, True])
+def test_embedding_backward_scatter(dtype, main_grad):
+    """Embedding backward kernel (atomic scatter-add of gradient rows, repeated and out-of-shard ids included) against
+    F.embedding's gradient in fp32."""
+    torch.manual_seed(0)
+    V, h, T = 500, 256, 3000                           # many repeated ids
+    w = torch.randn(V, h, device=dev()).to(dtype).requires_grad_(True)
+    ids = torch.randint(0, 2 * V, (3, T // 3), device=dev())          # half of them fall outside the shard [0, V)
+    gy = torch.randn(3, T // 3, h, device=dev()).to(dtype)
+    if main_grad:
+        w.main_grad = torch.zeros(V, h, device=dev())
+    K.reset_launch_count()
+    y = ops.embedding(ids, w, 0, sharded=True)
+    y.backward(gy)
+    assert K.reset_launch_count() == 1
+    wr = w.detach().float().requires_grad_(True)
+    inside = ids < V
+    yr = torch.nn.functional.embedding(ids.clamp(max=V - 1), wr) * inside[..., None]
+    yr.backward(gy.float())
+    assert torch.equal(y.float(), yr.detach().to(dtype).float())
+    got = w.main_grad if main_grad else w.grad.float()
+    rel = ((got - wr.grad).norm() / wr.grad.norm()).item()
+    assert rel < (1e-5 if main_grad or dtype == torch.float32 else 5e-3), rel
