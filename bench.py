@@ -144,6 +144,23 @@ def main():
         e2e = {"value": seq / (ms_e2e / 1000.0), "unit": "tokens/s", "ms_per_step": ms_e2e,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "last_loss": last.get("loss")}
 
+    # ---- on-stream time of the fused LASP-2 exchange (push + wait for the other ranks + fold), one extra step ----
+    lasp = None
+    ws = fused_comm.lasp_workspace(mesh["cp"]) if world > 1 else None
+    if ws is not None:
+        trainer.data_iter = Cycle(resident)
+        ws.timing = []
+        trainer.train_step()
+        torch.cuda.synchronize()
+        us = [a.elapsed_time(b) * 1e3 for a, b in ws.timing]
+        ws.timing = None
+        t = torch.tensor([sum(us), float(len(us))], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        lasp = {"exchanges_per_step": int(t[1]), "us_per_exchange_max_over_ranks": float(t[0]) / max(float(t[1]), 1.0),
+                "share_of_step": float(t[0]) / 1e3 / ms_dev,
+                "note": "duration on the compute stream of the fused kernel that pushes the rank's state summary to every peer, "
+                        "waits for theirs and folds them; it includes the skew between ranks and nothing of it is hidden"}
+
     if mesh.rank == 0:
         out = {
             "metric": METRIC, "value": seq / (ms_dev / 1000.0), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
@@ -157,6 +174,10 @@ def main():
                        "optimizer": "AdamW fp32 masters, clip 1.0", "valid": args.layers is None},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         }
+        if lasp is not None:
+            out["lasp_exchange"] = lasp
+        if clocks and clocks.get("sm_mhz"):
+            out["ms_x_ghz"] = ms_dev * clocks["sm_mhz"] / 1e3      # clock-normalised step time, to compare runs
         print(json.dumps(out))
     if world > 1:
         dist.barrier()

@@ -1,6 +1,6 @@
 """Per-kernel timing and roofline harness.
 
-  python -m linear_moe_b200.bench.kernels [--kernel all|gemm|lsm|flash|families|moe|decode|norm|headnorm|swiglu|ce|adam|conv] [--size small|full]
+  python -m linear_moe_b200.bench.kernels [--kernel all|gemm|gemm_dense|lsm|flash|families|moe|decode|norm|headnorm|swiglu|ce|adam|conv] [--size small|full]
 
 Each kernel is timed with CUDA events on the launching stream after warm-up, with an L2 flush (a 256 MiB write)
 between iterations; the median is reported together with the algorithmic bytes / FLOPs and the fraction of the
@@ -77,6 +77,42 @@ def bench_gemm(size):
         report(f"gemm fp8 tcgen05 2-CTA {M}x{N}x{K}", timeit(lambda: fp8.gemm_nt(aq, sa, bq, sb, pairs=True)), flops=2.0 * M * N * K)
         report(f"fp8 quant rows {M}x{K}", timeit(lambda: fp8.quant_rows(a)), bytes_=3.0 * M * K)
         report(f"fp8 quant cols^T {M}x{K}", timeit(lambda: fp8.quant_cols_t(a)), bytes_=5.0 * M * K)
+    gemm.check_error()
+
+
+def bench_gemm_dense(size):
+    """The dense CTA-pair kernel under every plain linear (``csrc/gemm_dense.cu``) in its three operand layouts, next to
+    the library GEMM on the same operands.  ``small``: one 4096 x 4096 x 2048 problem per layout (what ``ncu`` captures)."""
+    from ..ops import gemm
+    dev = torch.device("cuda", 0)
+    if size == "small":
+        shapes = [("fwd  x W^T", 4096, 4096, 2048, 0, 0, 0), ("dgrad dy W", 4096, 2048, 4096, 0, 1, 0),
+                  ("wgrad dy^T x (fp32)", 4096, 2048, 4096, 1, 1, 1)]
+    else:
+        shapes = [("fc1 fwd", 16384, 16384, 2048, 0, 0, 0), ("fc2 fwd", 16384, 2048, 8192, 0, 0, 0),
+                  ("qkv fwd", 16384, 6144, 2048, 0, 0, 0), ("fc1 dgrad", 16384, 2048, 16384, 0, 1, 0),
+                  ("fc2 dgrad", 16384, 8192, 2048, 0, 1, 0), ("fc1 wgrad (fp32)", 16384, 2048, 16384, 1, 1, 1),
+                  ("fc2 wgrad (fp32)", 2048, 8192, 16384, 1, 1, 1), ("LM head fwd", 16384, 128256, 2048, 0, 0, 0)]
+    for name, M, N, K, amn, bmn, f32 in shapes:
+        a = torch.randn(M, K, device=dev).bfloat16()
+        b = torch.randn(N, K, device=dev).bfloat16()
+        aa, bb = (a.t().contiguous() if amn else a), (b.t().contiguous() if bmn else b)
+        del a, b
+        c = torch.empty(M, N, device=dev, dtype=torch.float32 if f32 else torch.bfloat16)
+        at, bt = (aa.t() if amn else aa), (bb if bmn else bb.t())
+        fl = 2.0 * M * N * K
+        report(f"gemm_dense {name} {M}x{N}x{K}", timeit(lambda: gemm.dense(aa, bb, bool(amn), bool(bmn), out=c)), flops=fl)
+        lib = (lambda: torch.mm(at, bt, out_dtype=torch.float32, out=c)) if f32 else (lambda: torch.mm(at, bt, out=c))
+        report(f"cuBLAS     {name} {M}x{N}x{K}", timeit(lib), flops=fl)
+        del aa, bb, c, at, bt
+    if size != "small":
+        M, F_, K = 16384, 8192, 2048
+        x = torch.randn(M, K, device=dev).bfloat16()
+        w = (0.1 * torch.randn(2 * F_, K, device=dev)).bfloat16()
+        from .. import ops
+        report("fc1 + SwiGLU, fused epilogue (writes act + pre)", timeit(lambda: gemm.dense_swiglu(x, w, want_pre=True)),
+               flops=2.0 * M * 2 * F_ * K)
+        report("fc1 cuBLAS + SwiGLU kernel", timeit(lambda: ops.swiglu(torch.mm(x, w.t()))), flops=2.0 * M * 2 * F_ * K)
     gemm.check_error()
 
 
@@ -286,6 +322,8 @@ def main():
     print(f"peaks: {peaks()}")
     if a.kernel in ("gemm", "all"):
         bench_gemm(a.size)
+    if a.kernel in ("gemm_dense", "all"):
+        bench_gemm_dense(a.size)
     if a.kernel in ("lsm", "all"):
         bench_lsm(a.size)
     if a.kernel in ("flash", "all"):

@@ -10,6 +10,9 @@
 //          stages 128 gate rows, CTA 1 the matching 128 up rows, so accumulator columns [0,128) / [128,256) are gate / up
 //          of the same 128 outputs; the epilogue writes silu(gate) * up to C [M,F] and, if Y != null, the
 //          pre-activations to Y [M,2F] (what the backward pass needs).  No re-tiling of the weight.
+//   epi 2 (A K-major, B MN-major, bf16 out): the data-gradient GEMM of fc2, dAct = dY W2, with the SwiGLU backward in
+//          the epilogue: the tile of dAct never leaves the SM; the matching gate / up pre-activations are fetched by TMA
+//          from Y [M,2F] into shared memory and C [M,2F] receives dGate = dAct * up * silu'(gate), dUp = dAct * silu(gate).
 //
 // Tile order: tiles are numbered band by band (a band = `band` consecutive tile rows of C), column by column inside a
 // band, so the ~74 tiles in flight cover about band x (74 / band) tiles: both operands' working sets stay a few MB and
@@ -36,6 +39,7 @@ struct __align__(1024) Smem {
     uint8_t tiles[STAGES][STAGE_BYTES];
     uint8_t out[4][2][OUT_BYTES];
     uint64_t full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2];
+    uint64_t epi_bar[4];                         // epi 2: arrival of a warp's gate / up slabs
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -91,6 +95,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     const uint32_t rank = cluster_rank();
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
     constexpr int TILE_N = EPI == 1 ? 128 : 256;                        // output columns per tile
+    constexpr int NS = EPI == 2 ? STAGES - 1 : STAGES;                  // epi 2 uses the last ring slot for its input slabs
     const int tiles_m = (p.M + 255) / 256, tiles_n = (p.N + TILE_N - 1) / TILE_N;
     const int num_tiles = tiles_m * tiles_n;
     const int kblocks = (p.K + BK - 1) / BK;
@@ -100,6 +105,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(&sm.tmem_full[b], 1); mbar_init(&sm.tmem_empty[b], 8); }   // 4 warps x 2 CTAs
+        for (int b = 0; b < 4; ++b) mbar_init(&sm.epi_bar[b], 1);
         sm.abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -123,8 +129,8 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 const int a0 = tm * 256 + half;
                 const int b0 = EPI == 1 ? (int)rank * p.f_half + tn * 128 : tn * 256 + half;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
+                    const int s = it % NS;
+                    const uint32_t ph = (it / NS) & 1;
                     if (!mbar_wait(&sm.empty[s], ph ^ 1, abort_flag, err, 0x7100 | s)) goto producer_done;
                     if (rank == 0) mbar_expect_tx(&sm.full[s], 2 * STAGE_BYTES);      // both CTAs' loads land on the leader's barrier
                     const uint32_t fl = map_to_cta(&sm.full[s], 0);
@@ -157,8 +163,8 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                 const uint32_t d_tmem = tmem_base + buf * 256;
                 bool dead = false;
                 for (int kb = 0; kb < kblocks; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
+                    const int s = it % NS;
+                    const uint32_t ph = (it / NS) & 1;
                     if (!mbar_wait(&sm.full[s], ph, abort_flag, err, 0x7300 | s)) { dead = true; break; }
                     tc_fence_after();
                     const uint32_t a_addr = s32(sm.tiles[s]), b_addr = a_addr + HALF_BYTES;
@@ -178,6 +184,7 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const int q = warp & 3;                                   // TMEM lane quadrant this warp may read
         uint8_t* stg0 = sm.out[warp - 2][0];
         int lt = 0, nst = 0;                                      // nst: staging slabs used so far (ring of 2)
+        int nload = 0, nepi = 0;                                  // epi 2: input-slab loads completed by this warp
         for (int tile = pair; tile < num_tiles; tile += num_pairs, ++lt) {
             int tm, tn;
             decode(p, tile, tiles_m, tiles_n, tm, tn);
@@ -228,6 +235,75 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     fence_async_smem();
                     __syncwarp();
                     if (lane == 0) { if (live && col_base + c < p.f_half) tma_store_2d(&tmC, s, col_base + c, row0); bulk_commit(); }
+                    ++nst;
+                }
+            } else if (EPI == 2) {
+                const int col_base = tn * 256;
+                uint8_t* gin = sm.tiles[STAGES - 1] + (warp - 2) * 2 * OUT_BYTES;      // gate slab, then up slab
+                uint64_t* ebar = &sm.epi_bar[warp - 2];
+#pragma unroll 1
+                for (int c = 0; c < 256; c += 64, ++nepi) {
+                    const bool cols_live = col_base + c < p.N;
+                    if (lane == 0 && live && cols_live) {
+                        fence_async_smem();                                // the lanes' reads of the previous slabs are done
+                        mbar_expect_tx(ebar, 2 * OUT_BYTES);
+                        tma_load_2d(gin, &tmY, ebar, col_base + c, row0);
+                        tma_load_2d(gin + OUT_BYTES, &tmY, ebar, p.N + col_base + c, row0);
+                    }
+                    uint32_t v0[32], v1[32];
+                    tmem_ld32(taddr + c, v0);
+                    tmem_ld32(taddr + c + 32, v1);
+                    tmem_ld_wait();
+                    bool ok = true;
+                    if (live && cols_live) ok = mbar_wait(ebar, nload & 1, abort_flag, err, 0x7500 | (warp - 2));
+                    if (live && cols_live) ++nload;
+                    if (!ok) break;
+                    // this lane's row of the gate / up slabs (16-byte chunks are xor-swizzled by the row)
+                    uint32_t dg[32], du[32];
+#pragma unroll
+                    for (int ch = 0; ch < 8; ++ch) {
+                        uint4 g4 = make_uint4(0, 0, 0, 0), u4 = make_uint4(0, 0, 0, 0);
+                        if (live && cols_live) {
+                            g4 = *reinterpret_cast<const uint4*>(gin + lane * 128 + ((ch ^ (lane & 7)) << 4));
+                            u4 = *reinterpret_cast<const uint4*>(gin + OUT_BYTES + lane * 128 + ((ch ^ (lane & 7)) << 4));
+                        }
+                        const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, uw[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int col = ch * 8 + e * 2;                               // columns col, col + 1 of the slab
+                            const __nv_bfloat162 gb = *reinterpret_cast<const __nv_bfloat162*>(&gw[e]);
+                            const __nv_bfloat162 ub = *reinterpret_cast<const __nv_bfloat162*>(&uw[e]);
+                            const float g0 = __bfloat162float(gb.x), g1 = __bfloat162float(gb.y);
+                            const float u0 = __bfloat162float(ub.x), u1 = __bfloat162float(ub.y);
+                            const float d0 = __uint_as_float(col < 32 ? v0[col & 31] : v1[col & 31]);
+                            const float d1 = __uint_as_float(col + 1 < 32 ? v0[(col + 1) & 31] : v1[(col + 1) & 31]);
+                            const float s0 = sigmoid_f(g0), s1 = sigmoid_f(g1);
+                            dg[ch * 4 + e] = pack_bf16(d0 * u0 * s0 * (1.f + g0 * (1.f - s0)), d1 * u1 * s1 * (1.f + g1 * (1.f - s1)));
+                            du[ch * 4 + e] = pack_bf16(d0 * g0 * s0, d1 * g1 * s1);
+                        }
+                    }
+                    __syncwarp();                                          // every lane has read its input row
+                    uint8_t* s = stg0 + (nst & 1) * OUT_BYTES;
+                    if (lane == 0) bulk_wait_read<1>();
+                    __syncwarp();
+#pragma unroll
+                    for (int ch = 0; ch < 8; ++ch)
+                        *reinterpret_cast<uint4*>(s + lane * 128 + ((ch ^ (lane & 7)) << 4)) =
+                            make_uint4(dg[ch * 4], dg[ch * 4 + 1], dg[ch * 4 + 2], dg[ch * 4 + 3]);
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) { if (live && cols_live) tma_store_2d(&tmC, s, col_base + c, row0); bulk_commit(); }
+                    ++nst;
+                    s = stg0 + (nst & 1) * OUT_BYTES;
+                    if (lane == 0) bulk_wait_read<1>();
+                    __syncwarp();
+#pragma unroll
+                    for (int ch = 0; ch < 8; ++ch)
+                        *reinterpret_cast<uint4*>(s + lane * 128 + ((ch ^ (lane & 7)) << 4)) =
+                            make_uint4(du[ch * 4], du[ch * 4 + 1], du[ch * 4 + 2], du[ch * 4 + 3]);
+                    fence_async_smem();
+                    __syncwarp();
+                    if (lane == 0) { if (live && cols_live) tma_store_2d(&tmC, s, p.N + col_base + c, row0); bulk_commit(); }
                     ++nst;
                 }
             } else if (OUT == 0) {
@@ -380,4 +456,25 @@ LMOE_API int lmoe_gemm_dense_swiglu(const void* X, int ldx, const void* W, int l
     Params p;
     p.M = M; p.N = F; p.K = K; p.band = band > 0 ? band : 8; p.f_half = F; p.err = err;
     return launch<false, false, 0, 1>(ma, mb, mc, my, Y != nullptr ? 1 : 0, p, num_sms, st);
+}
+
+// dPre[M,2F] = SwiGLU'(Pre[M,2F]) applied to dAct = dY[M,H] * W2[H,F] (W2 as stored: [H, F] row-major, pitch ldw), with the
+// activation gradient in the GEMM epilogue (dAct is never written).  F % 64 == 0, H % 8 == 0.
+LMOE_API int lmoe_gemm_dense_dswiglu(const void* dY, int lddy, const void* W2, int ldw, const void* pre, int ldpre, void* dpre,
+                                     int lddpre, int M, int F, int H, int band, int* err, int num_sms, cudaStream_t st) {
+    if (M <= 0 || F <= 0 || H <= 0) return -1;
+    if (lddy % 8 || ldw % 8 || H % 8 || F % 64 || ldpre % 8 || lddpre % 8) return -1;   // 64-column slabs must not straddle F
+    if (((uintptr_t)dY | (uintptr_t)W2 | (uintptr_t)pre | (uintptr_t)dpre) & 15) return -2;
+    CUtensorMap ma, mb, mc, my;
+    int rc = make_map(&ma, dY, (uint64_t)M, (uint64_t)H, (uint64_t)lddy, 128);
+    if (rc) return rc;
+    rc = make_map(&mb, W2, (uint64_t)H, (uint64_t)F, (uint64_t)ldw, 64);                      // MN-major B: [K = H rows, N = F cols]
+    if (rc) return rc;
+    rc = make_map_any(&mc, dpre, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, 2 * F, lddpre, 64, 32);
+    if (rc) return rc;
+    rc = make_map_any(&my, pre, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, 2 * F, ldpre, 64, 32);
+    if (rc) return rc;
+    Params p;
+    p.M = M; p.N = F; p.K = H; p.band = band > 0 ? band : 8; p.f_half = F; p.err = err;
+    return launch<false, true, 0, 2>(ma, mb, mc, my, 1, p, num_sms, st);
 }

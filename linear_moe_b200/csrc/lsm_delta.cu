@@ -410,6 +410,345 @@ __global__ void __launch_bounds__(NT) delta_prep_fwd_kernel(PrepArgs a) {
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// Chunk-parallel backward of everything that is not the state recurrence: one CTA per (batch, head, chunk).
+// Inputs: q, k, v, beta, g (to rebuild the tiles), the entering state S_n and the gradient dS'_n of the leaving state,
+// Vn, dVn (= dU) and dO of the chunk (written by the two scan kernels), and dgamma_n = <dS'_n, S_n> (gated case).
+//
+//   through the scan equations      dW = -dVn S^T,  dQd = dO S^T,  dKd = Vn dS'^T,  dAqk = tril(dO Vn^T)
+//   through W = T Kb, U = T Vb      dKb = T^T dW,  dVb = T^T dU,  dT = dW Kb^T + dU Vb^T,  dA = -strict_lower(T^T dT T^T)
+//   through the tiles               dq = s e^b dQd + P K                         P = s Gamma . dAqk
+//                                   dk = e^{b_C-b} dKd + P^T Q + beta e^b dKb + M K + M^T K          M = beta_i Gamma . dA
+//                                   dv = beta dVb
+//                                   dbeta_i = e^{b_i} <dKb_i, k_i> + <dVb_i, v_i> + sum_j dA_ij Gamma_ij (k_i.k_j)
+//                                   db_i (gradient of the cumulative log decay) from every e^{b}: rows minus columns of
+//                                   dAqk . Aqk and dA . A, +<dQd_i, Qd_i>, -<dKd_j, Kd_j> (and their sum on b_C),
+//                                   +beta_i e^{b_i} <dKb_i, k_i>, + dgamma gamma on b_C;   dg_s = sum_{i >= s} db_i
+// The products are mma.sync tiles on bf16 copies in shared memory with fp32 accumulation; dk accumulates in registers
+// across the phases, every other output is finished inside one phase.
+// ---------------------------------------------------------------------------------------------------------------
+struct PrepBwdArgs {
+    const bf16 *q, *k, *v;
+    long long qs_b, qs_t, qs_h, ks_b, ks_t, ks_h, vs_b, vs_t, vs_h;
+    const float* beta;
+    const float* g;                    // or null
+    const bf16 *Sn, *dSn;              // [BH, N, D, D]
+    const bf16 *Vn, *dVn, *dO;         // [BH, N, C, D]
+    const float* dgamma;               // [BH, N] or null
+    bf16 *dq, *dk, *dv;                // contiguous [B, T, H, D]
+    float *dbeta, *dg;                 // [B, T, H]
+    int B, T, H, N;
+    float scale;
+};
+
+// sum over the thread's columns of acc[row][col] * tile[row][col] for its two rows (r, r + 8), reduced over the quad
+template <int NTL>
+__device__ __forceinline__ void row_dot(const float (&acc)[NTL][4], const bf16* tile, int ld, int m0, float& lo, float& hi) {
+    const int l = threadIdx.x & 31;
+    const int r = m0 + (l >> 2), c = (l & 3) * 2;
+    lo = 0.f; hi = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < NTL; ++nt) {
+        const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(tile + r * ld + c + nt * 8);
+        const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(tile + (r + 8) * ld + c + nt * 8);
+        lo += acc[nt][0] * __bfloat162float(a.x) + acc[nt][1] * __bfloat162float(a.y);
+        hi += acc[nt][2] * __bfloat162float(b.x) + acc[nt][3] * __bfloat162float(b.y);
+    }
+    lo += __shfl_xor_sync(0xffffffffu, lo, 1); lo += __shfl_xor_sync(0xffffffffu, lo, 2);
+    hi += __shfl_xor_sync(0xffffffffu, hi, 1); hi += __shfl_xor_sync(0xffffffffu, hi, 2);
+}
+
+// write a warp's [16 x 8 NTL] accumulator rows to global rows (bf16), rows >= valid skipped
+template <int NTL>
+__device__ __forceinline__ void store_rows_global(const float (&acc)[NTL][4], bf16* g, long long row_stride, int m0, int valid) {
+    const int l = threadIdx.x & 31;
+    const int r = m0 + (l >> 2), c = (l & 3) * 2;
+#pragma unroll
+    for (int nt = 0; nt < NTL; ++nt) {
+        if (r < valid) *reinterpret_cast<__nv_bfloat162*>(g + r * row_stride + c + nt * 8) = __floats2bfloat162_rn(acc[nt][0], acc[nt][1]);
+        if (r + 8 < valid) *reinterpret_cast<__nv_bfloat162*>(g + (r + 8) * row_stride + c + nt * 8) = __floats2bfloat162_rn(acc[nt][2], acc[nt][3]);
+    }
+}
+
+template <int D>
+__global__ void __launch_bounds__(NT) delta_prep_bwd_kernel(PrepBwdArgs a) {
+    constexpr int LD = D + 8, LDC = C + 8, LDA = C + 1, NTD = D / 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    bf16* Ks = reinterpret_cast<bf16*>(smem_raw);            // [C][LD]
+    bf16* Qs = Ks + C * LD;                                  // [C][LD]
+    bf16* Vs = Qs + C * LD;                                  // [C][LD]  V, later beta V
+    bf16* Gs = Vs + C * LD;                                  // [C][LD]  dO, later dW
+    bf16* Ns = Gs + C * LD;                                  // [C][LD]  Vn
+    bf16* Us = Ns + C * LD;                                  // [C][LD]  dVn = dU
+    bf16* Sb = Us + C * LD;                                  // [D][LD]  S_n, then dS'_n, then Kb (first C rows)
+    bf16* Tb = Sb + D * LD;                                  // [C][LDC] T
+    bf16* Ps = Tb + C * LDC;                                 // [C][LDC] P, later M
+    bf16* X1 = Ps + C * LDC;                                 // [C][LDC] dT
+    bf16* X2 = X1 + C * LDC;                                 // [C][LDC] T^T dT
+    float* GK = reinterpret_cast<float*>(X2 + C * LDC);      // [C][LDA] Gamma_ij (k_i.k_j), strictly lower
+    float* bcum = GK + C * LDA;                              // [C]
+    float* bet = bcum + C;                                   // [C]
+    float* db = bet + C;                                     // [C] gradient of the cumulative log decay
+    float* dbe = db + C;                                     // [C] gradient of beta
+    const int n = blockIdx.x, bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+    const int t0 = n * C;
+    const int valid = min(C, a.T - t0);
+    const long long cn = (long long)bh * a.N + n;
+    const int m0 = 16 * w, r0 = m0 + (l >> 2), c0 = (l & 3) * 2;
+
+    load_tile_async<C, D, LD>(Ks, a.k + b * a.ks_b + h * a.ks_h + (long long)t0 * a.ks_t, a.ks_t, valid);
+    load_tile_async<C, D, LD>(Qs, a.q + b * a.qs_b + h * a.qs_h + (long long)t0 * a.qs_t, a.qs_t, valid);
+    load_tile_async<C, D, LD>(Vs, a.v + b * a.vs_b + h * a.vs_h + (long long)t0 * a.vs_t, a.vs_t, valid);
+    load_tile_async<C, D, LD>(Gs, a.dO + cn * C * D, D, C);
+    load_tile_async<C, D, LD>(Ns, a.Vn + cn * C * D, D, C);
+    load_tile_async<C, D, LD>(Us, a.dVn + cn * C * D, D, C);
+    load_tile_async<D, D, LD>(Sb, a.Sn + cn * D * D, D, D);
+    cp_async_commit();
+    if (w == 0) {
+        const int i0 = 2 * l, i1 = 2 * l + 1;
+        float g0 = 0.f, g1 = 0.f, be0 = 0.f, be1 = 0.f;
+        if (i0 < valid) { const long long o = ((long long)b * a.T + t0 + i0) * a.H + h; be0 = a.beta[o]; if (a.g != nullptr) g0 = a.g[o]; }
+        if (i1 < valid) { const long long o = ((long long)b * a.T + t0 + i1) * a.H + h; be1 = a.beta[o]; if (a.g != nullptr) g1 = a.g[o]; }
+        float s = g0 + g1;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const float x = __shfl_up_sync(0xffffffffu, s, o); if (l >= o) s += x; }
+        bcum[i1] = s; bcum[i0] = s - g1; bet[i0] = be0; bet[i1] = be1;
+        db[i0] = db[i1] = 0.f; dbe[i0] = dbe[i1] = 0.f;
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+    const float btot = bcum[C - 1];
+    const float b_lo = bcum[r0], b_hi = bcum[r0 + 8], be_lo = bet[r0], be_hi = bet[r0 + 8];
+
+    // ---- (1) K K^T -> GK (fp32), T by substitution (threads 0..63) ---------------------------------------------
+    {
+        float kk[8][4];
+        zero_acc<8>(kk);
+        warp_gemm<8, D, false, false>(kk, Ks, LD, m0, Ks, LD, 0);
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int i = r0 + 8 * hh, j = nt * 8 + c0;
+                const float bi = hh ? b_hi : b_lo;
+                GK[i * LDA + j] = i > j ? __expf(bi - bcum[j]) * kk[nt][2 * hh] : 0.f;
+                GK[i * LDA + j + 1] = i > j + 1 ? __expf(bi - bcum[j + 1]) * kk[nt][2 * hh + 1] : 0.f;
+            }
+    }
+    __syncthreads();
+    if (threadIdx.x < C) {
+        const int c = threadIdx.x;
+        float t[C];
+#pragma unroll
+        for (int i = 0; i < C; ++i) {
+            float acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < i; ++j) acc += GK[i * LDA + j] * t[j];
+            t[i] = ((i == c) ? 1.f : 0.f) - bet[i] * acc;
+        }
+#pragma unroll
+        for (int i = 0; i < C; ++i) Tb[i * LDC + c] = __float2bfloat16(t[i]);
+    }
+    // ---- (2) dAqk = tril(dO Vn^T), Q K^T again for Aqk; P = scale Gamma . dAqk; decay gradients of Aqk ---------------
+    {
+        float da[8][4], qk[8][4];
+        zero_acc<8>(da);
+        zero_acc<8>(qk);
+        warp_gemm<8, D, false, false>(da, Gs, LD, m0, Ns, LD, 0);
+        warp_gemm<8, D, false, false>(qk, Qs, LD, m0, Ks, LD, 0);
+        float rs_lo = 0.f, rs_hi = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            float pv[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = r0 + 8 * (e >> 1), j = nt * 8 + c0 + (e & 1);
+                const float gam = i >= j ? a.scale * __expf((e >> 1 ? b_hi : b_lo) - bcum[j]) : 0.f;
+                pv[e] = gam * da[nt][e];                              // P_ij
+                const float t_ = pv[e] * qk[nt][e];                   // dAqk_ij Aqk_ij
+                if (e >> 1) rs_hi += t_; else rs_lo += t_;
+                if (i >= j) atomicAdd(&db[j], -t_);
+            }
+            *reinterpret_cast<__nv_bfloat162*>(Ps + r0 * LDC + nt * 8 + c0) = __floats2bfloat162_rn(pv[0], pv[1]);
+            *reinterpret_cast<__nv_bfloat162*>(Ps + (r0 + 8) * LDC + nt * 8 + c0) = __floats2bfloat162_rn(pv[2], pv[3]);
+        }
+        rs_lo += __shfl_xor_sync(0xffffffffu, rs_lo, 1); rs_lo += __shfl_xor_sync(0xffffffffu, rs_lo, 2);
+        rs_hi += __shfl_xor_sync(0xffffffffu, rs_hi, 1); rs_hi += __shfl_xor_sync(0xffffffffu, rs_hi, 2);
+        if ((l & 3) == 0) { atomicAdd(&db[r0], rs_lo); atomicAdd(&db[r0 + 8], rs_hi); }
+    }
+    __syncthreads();                                                   // Ps, Tb complete
+    // ---- (3) dq = scale e^b (dO S^T) + P K; its decay gradient <dQd_i, Qd_i> ----------------------------------------
+    float acc_dk[NTD][4];
+    zero_acc<NTD>(acc_dk);
+    {
+        float acc[NTD][4];
+        zero_acc<NTD>(acc);
+        warp_gemm<NTD, D, false, false>(acc, Gs, LD, m0, Sb, LD, 0);  // dQd = dO S^T  (S stored [dk][dv] = [n][k])
+        const float f_lo = a.scale * __expf(b_lo), f_hi = a.scale * __expf(b_hi);
+#pragma unroll
+        for (int nt = 0; nt < NTD; ++nt) { acc[nt][0] *= f_lo; acc[nt][1] *= f_lo; acc[nt][2] *= f_hi; acc[nt][3] *= f_hi; }
+        float d_lo, d_hi;
+        row_dot<NTD>(acc, Qs, LD, m0, d_lo, d_hi);                    // = <dQd_i, Qd_i> since acc already carries s e^b
+        if ((l & 3) == 0) { atomicAdd(&db[r0], d_lo); atomicAdd(&db[r0 + 8], d_hi); }
+        warp_gemm<NTD, C, false, true>(acc, Ps, LDC, m0, Ks, LD, 0);  // + P K
+        store_rows_global<NTD>(acc, a.dq + (((long long)b * a.T + t0) * a.H + h) * D, (long long)a.H * D, m0, valid);
+        // dk += P^T Q
+        warp_gemm<NTD, C, true, true>(acc_dk, Ps, LDC, m0, Qs, LD, 0);
+    }
+    // ---- (4) dW = -dVn S^T -> shared (in dO's buffer once every warp is done with dO) --------------------------------
+    {
+        float acc[NTD][4];
+        zero_acc<NTD>(acc);
+        warp_gemm<NTD, D, false, false>(acc, Us, LD, m0, Sb, LD, 0);
+#pragma unroll
+        for (int nt = 0; nt < NTD; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[nt][e] = -acc[nt][e];
+        __syncthreads();                                               // all reads of dO (Gs) and S_n (Sb) are done
+        store_acc_bf16<NTD>(acc, Gs, LD, m0, 0);                       // Gs now holds dW
+    }
+    // ---- (5) dS'_n into the state buffer; dKd = Vn dS'^T ------------------------------------------------------------
+    load_tile_async<D, D, LD>(Sb, a.dSn + cn * D * D, D, D);
+    cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+    {
+        float acc[NTD][4];
+        zero_acc<NTD>(acc);
+        warp_gemm<NTD, D, false, false>(acc, Ns, LD, m0, Sb, LD, 0);  // dKd_j = Vn_j dS'^T
+        const float f_lo = __expf(btot - b_lo), f_hi = __expf(btot - b_hi);
+#pragma unroll
+        for (int nt = 0; nt < NTD; ++nt) { acc[nt][0] *= f_lo; acc[nt][1] *= f_lo; acc[nt][2] *= f_hi; acc[nt][3] *= f_hi; }
+        float d_lo, d_hi;
+        row_dot<NTD>(acc, Ks, LD, m0, d_lo, d_hi);                    // <dKd_j, Kd_j>
+        if ((l & 3) == 0) {
+            atomicAdd(&db[r0], -d_lo); atomicAdd(&db[r0 + 8], -d_hi);
+            atomicAdd(&db[C - 1], d_lo + d_hi);
+        }
+#pragma unroll
+        for (int nt = 0; nt < NTD; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc_dk[nt][e] += acc[nt][e];
+    }
+    __syncthreads();                                                   // dS'_n no longer needed: Sb becomes Kb
+    // ---- (6) dVb = T^T dU: dv, dbeta; then Kb = beta e^b K and Vb = beta V in shared -------------------------------
+    {
+        float acc[NTD][4];
+        zero_acc<NTD>(acc);
+        warp_gemm<NTD, C, true, true>(acc, Tb, LDC, m0, Us, LD, 0);
+        float d_lo, d_hi;
+        row_dot<NTD>(acc, Vs, LD, m0, d_lo, d_hi);                    // <dVb_i, v_i>
+        if ((l & 3) == 0) { atomicAdd(&dbe[r0], d_lo); atomicAdd(&dbe[r0 + 8], d_hi); }
+#pragma unroll
+        for (int nt = 0; nt < NTD; ++nt) { acc[nt][0] *= be_lo; acc[nt][1] *= be_lo; acc[nt][2] *= be_hi; acc[nt][3] *= be_hi; }
+        store_rows_global<NTD>(acc, a.dv + (((long long)b * a.T + t0) * a.H + h) * D, (long long)a.H * D, m0, valid);
+    }
+    __syncthreads();                                                   // every warp has read raw V
+    for (int i = threadIdx.x; i < C * (D / 8); i += NT) {
+        const int r = i / (D / 8), c = (i % (D / 8)) * 8;
+        const float be = bet[r], fk = be * __expf(bcum[r]);
+        Vec<bf16> kx, vx, o1, o2;
+        kx.load(Ks + r * LD + c);
+        vx.load(Vs + r * LD + c);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { o1.set(e, kx.get(e) * fk); o2.set(e, vx.get(e) * be); }
+        o1.store(Sb + r * LD + c);                                     // Kb
+        o2.store(Vs + r * LD + c);                                     // Vb
+    }
+    __syncthreads();
+    // ---- (7) dKb = T^T dW: its part of dk, dbeta and db -------------------------------------------------------------
+    {
+        float acc[NTD][4];
+        zero_acc<NTD>(acc);
+        warp_gemm<NTD, C, true, true>(acc, Tb, LDC, m0, Gs, LD, 0);
+        float d_lo, d_hi;
+        row_dot<NTD>(acc, Ks, LD, m0, d_lo, d_hi);                    // <dKb_i, k_i>
+        const float e_lo = __expf(b_lo), e_hi = __expf(b_hi);
+        if ((l & 3) == 0) {
+            atomicAdd(&dbe[r0], e_lo * d_lo); atomicAdd(&dbe[r0 + 8], e_hi * d_hi);
+            atomicAdd(&db[r0], be_lo * e_lo * d_lo); atomicAdd(&db[r0 + 8], be_hi * e_hi * d_hi);
+        }
+#pragma unroll
+        for (int nt = 0; nt < NTD; ++nt) {
+            acc_dk[nt][0] += be_lo * e_lo * acc[nt][0]; acc_dk[nt][1] += be_lo * e_lo * acc[nt][1];
+            acc_dk[nt][2] += be_hi * e_hi * acc[nt][2]; acc_dk[nt][3] += be_hi * e_hi * acc[nt][3];
+        }
+    }
+    // ---- (8) dT = dW Kb^T + dU Vb^T -> X1;  X2 = T^T dT;  dA = -(X2 T^T), strictly lower ------------------------------
+    {
+        float acc[8][4];
+        zero_acc<8>(acc);
+        warp_gemm<8, D, false, false>(acc, Gs, LD, m0, Sb, LD, 0);
+        warp_gemm<8, D, false, false>(acc, Us, LD, m0, Vs, LD, 0);
+        store_acc_bf16<8>(acc, X1, LDC, m0, 0);
+    }
+    __syncthreads();
+    {
+        float acc[8][4];
+        zero_acc<8>(acc);
+        warp_gemm<8, C, true, true>(acc, Tb, LDC, m0, X1, LDC, 0);
+        store_acc_bf16<8>(acc, X2, LDC, m0, 0);
+    }
+    __syncthreads();
+    {
+        float acc[8][4];
+        zero_acc<8>(acc);
+        warp_gemm<8, C, false, false>(acc, X2, LDC, m0, Tb, LDC, 0);  // (X2 T^T)_ij = sum_k X2_ik T_jk
+        float rb_lo = 0.f, rb_hi = 0.f, rd_lo = 0.f, rd_hi = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            float mv[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = r0 + 8 * (e >> 1), j = nt * 8 + c0 + (e & 1);
+                const float dA = i > j ? -acc[nt][e] : 0.f;
+                const float gk = GK[i * LDA + j];                      // Gamma_ij (k_i.k_j), zero on and above the diagonal
+                const float be = (e >> 1) ? be_hi : be_lo;
+                const float t1 = dA * gk;                              // -> dbeta_i
+                const float t2 = t1 * be;                              // dA_ij A_ij -> db_i, -db_j
+                if (e >> 1) { rb_hi += t1; rd_hi += t2; } else { rb_lo += t1; rd_lo += t2; }
+                if (i > j) atomicAdd(&db[j], -t2);
+                mv[e] = i > j ? dA * be * __expf(((e >> 1) ? b_hi : b_lo) - bcum[j]) : 0.f;      // M_ij
+            }
+            *reinterpret_cast<__nv_bfloat162*>(Ps + r0 * LDC + nt * 8 + c0) = __floats2bfloat162_rn(mv[0], mv[1]);
+            *reinterpret_cast<__nv_bfloat162*>(Ps + (r0 + 8) * LDC + nt * 8 + c0) = __floats2bfloat162_rn(mv[2], mv[3]);
+        }
+#pragma unroll
+        for (int o = 1; o <= 2; o <<= 1) {
+            rb_lo += __shfl_xor_sync(0xffffffffu, rb_lo, o); rb_hi += __shfl_xor_sync(0xffffffffu, rb_hi, o);
+            rd_lo += __shfl_xor_sync(0xffffffffu, rd_lo, o); rd_hi += __shfl_xor_sync(0xffffffffu, rd_hi, o);
+        }
+        if ((l & 3) == 0) {
+            atomicAdd(&dbe[r0], rb_lo); atomicAdd(&dbe[r0 + 8], rb_hi);
+            atomicAdd(&db[r0], rd_lo); atomicAdd(&db[r0 + 8], rd_hi);
+        }
+    }
+    __syncthreads();                                                   // Ps holds M
+    // ---- (9) dk += M K + M^T K; store ---------------------------------------------------------------------------------
+    warp_gemm<NTD, C, false, true>(acc_dk, Ps, LDC, m0, Ks, LD, 0);
+    warp_gemm<NTD, C, true, true>(acc_dk, Ps, LDC, m0, Ks, LD, 0);
+    store_rows_global<NTD>(acc_dk, a.dk + (((long long)b * a.T + t0) * a.H + h) * D, (long long)a.H * D, m0, valid);
+    __syncthreads();                                                   // all contributions to db / dbeta are in
+    // ---- (10) dbeta; dg_s = sum_{i >= s} db_i (+ dgamma gamma on the last position) -----------------------------------
+    if (w == 0) {
+        const int i0 = 2 * l, i1 = 2 * l + 1;
+        float x0 = db[i0], x1 = db[i1];
+        if (a.dgamma != nullptr && l == 31) x1 += a.dgamma[cn] * __expf(btot);
+        float s = x0 + x1;                                             // suffix sums over lane pairs
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const float y = __shfl_down_sync(0xffffffffu, s, o); if (l + o < 32) s += y; }
+        const long long o0 = ((long long)b * a.T + t0 + i0) * a.H + h, o1 = o0 + a.H;
+        if (i0 < valid) { a.dbeta[o0] = dbe[i0]; if (a.dg != nullptr) a.dg[o0] = s; }
+        if (i1 < valid) { a.dbeta[o1] = dbe[i1]; if (a.dg != nullptr) a.dg[o1] = s - x0; }
+    }
+}
+
+template <int D> constexpr size_t prep_bwd_smem() {
+    return (size_t)(6 * C * (D + 8) + D * (D + 8) + 4 * C * (C + 8)) * 2 + (size_t)(C * (C + 1) + 4 * C) * 4;
+}
+
 template <int D> constexpr size_t prep_smem() {
     return (size_t)(4 * C * (D + 8) + C * (C + 8)) * 2 + (size_t)(C * (C + 1) + 2 * C) * 4;
 }
@@ -449,6 +788,23 @@ LMOE_API int lmoe_delta_prepare(int D, const dr::PrepArgs* ap, cudaStream_t st) 
         cudaError_t e = cudaFuncSetAttribute(dr::delta_prep_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dr::prep_smem<64>());
         if (e != cudaSuccess) return (int)e;
         dr::delta_prep_fwd_kernel<64><<<grid, dr::NT, dr::prep_smem<64>(), st>>>(a);
+    } else return -2;
+    return (int)cudaGetLastError();
+}
+
+// Chunk-parallel backward of the tile construction and of the chunk-local scan equations: grid (N, B*H).
+LMOE_API int lmoe_delta_prepare_bwd(int D, const dr::PrepBwdArgs* ap, cudaStream_t st) {
+    const dr::PrepBwdArgs a = *ap;
+    if (a.N <= 0 || a.B * a.H <= 0) return -1;
+    dim3 grid(a.N, a.B * a.H);
+    if (D == 128) {
+        cudaError_t e = cudaFuncSetAttribute(dr::delta_prep_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dr::prep_bwd_smem<128>());
+        if (e != cudaSuccess) return (int)e;
+        dr::delta_prep_bwd_kernel<128><<<grid, dr::NT, dr::prep_bwd_smem<128>(), st>>>(a);
+    } else if (D == 64) {
+        cudaError_t e = cudaFuncSetAttribute(dr::delta_prep_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dr::prep_bwd_smem<64>());
+        if (e != cudaSuccess) return (int)e;
+        dr::delta_prep_bwd_kernel<64><<<grid, dr::NT, dr::prep_bwd_smem<64>(), st>>>(a);
     } else return -2;
     return (int)cudaGetLastError();
 }

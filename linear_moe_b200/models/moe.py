@@ -56,7 +56,13 @@ class MLP(nn.Module):
                                             sequence_parallel=sequence_parallel, dtype=dt, device=device)
 
     def forward(self, x):
-        fc1 = self.linear_fc1
+        fc1, fc2 = self.linear_fc1, self.linear_fc2
+        if (self.glu and fc1.bias is None and fc2.bias is None and not fc1.sequence_parallel and not fc1.gather_output
+                and not fc2.sequence_parallel and fc2.input_is_parallel and x.is_cuda):
+            # both linears and the activation in one autograd node: SwiGLU forward and backward live in GEMM epilogues;
+            # the row-parallel reduction of fc2 follows outside
+            g = self.mesh["tp"]
+            return C.all_reduce(ops.mlp_swiglu(C.copy_to_region(x, g), fc1.weight, fc2.weight), g)
         if self.glu and fc1.bias is None and not fc1.sequence_parallel and not fc1.gather_output:
             h = ops.linear_swiglu(C.copy_to_region(x, self.mesh["tp"]), fc1.weight)
         else:

@@ -40,6 +40,13 @@ def linear_swiglu(x, weight, bias=None):
     return swiglu(linear(x, weight, bias))
 
 
+def mlp_swiglu(x, w1, w2):
+    """``fc2(swiglu(fc1(x)))`` without biases (``w1 [2f, h]`` = [gate; up], ``w2 [h, f]``)."""
+    if _cuda(x):
+        return _K().mlp_swiglu(x, w1, w2)
+    return linear(linear_swiglu(x, w1), w2)
+
+
 def allgather_linear(x, weight, bias, group, dim: int = 1):
     """All-gather ``x`` along ``dim`` over ``group`` then ``linear`` (sequence-parallel column layer)."""
     from ..dist import collectives as C

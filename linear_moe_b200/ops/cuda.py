@@ -19,7 +19,22 @@ from ..ref import ops as R
 from . import lsm_torch as LT
 
 _LIB: Optional[ctypes.CDLL] = None
-NUM_SMS = 148
+_NUM_SMS = None
+
+
+def num_sms() -> int:
+    """SM count of the current device (148 on a B200); persistent kernels size their grids from it."""
+    global _NUM_SMS
+    if _NUM_SMS is None:
+        _NUM_SMS = (torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+                    if torch.cuda.is_available() else 148)
+    return _NUM_SMS
+
+
+def __getattr__(name):                       # ``K.NUM_SMS`` for the callers in other modules
+    if name == "NUM_SMS":
+        return num_sms()
+    raise AttributeError(name)
 launch_count = 0          # kernels of this library launched since the last reset (bench.py reports it)
 
 
@@ -98,6 +113,7 @@ def wgrad_into_main_grad(weight, dy2: torch.Tensor, x2: torch.Tensor) -> bool:
     fresh = getattr(weight, "_main_grad_fresh", False)
     gemm.dense(dy2, x2, a_mn=True, b_mn=True, out=mg.view(dy2.shape[1], x2.shape[1]), accumulate=not fresh)
     weight._main_grad_fresh = False
+    weight._direct_wgrad = True            # the optimizer may skip clearing this accumulator (first write overwrites)
     return True
 
 
@@ -202,6 +218,51 @@ class _LinearSwigluTc(torch.autograd.Function):
         return dx, dw
 
 
+class _MlpSwigluTc(torch.autograd.Function):
+    """``(silu(x Wg^T) * (x Wu^T)) W2^T`` as four GEMMs with both halves of the activation inside GEMM epilogues: the
+    forward fc1 writes the activation and the pre-activations; in the backward pass the fc2 data gradient goes through
+    the SwiGLU backward in its epilogue and is never written."""
+
+    @staticmethod
+    def forward(ctx, x, w1, w2):
+        from . import gemm
+        x2 = _rows(x)
+        act, pre = gemm.dense_swiglu(x2, w1, want_pre=True)
+        y = torch.empty(*x.shape[:-1], w2.shape[0], dtype=torch.bfloat16, device=x.device)
+        gemm.dense(act, w2, out=y.view(-1, w2.shape[0]))
+        ctx.save_for_backward(x2, w1, w2, pre, act)
+        ctx.xshape = x.shape
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import gemm
+        x2, w1, w2, pre, act = ctx.saved_tensors
+        dy2 = _rows(dy)
+        dw2 = None
+        if ctx.needs_input_grad[2] and not wgrad_into_main_grad(w2, dy2, act):
+            dw2 = gemm.dense(dy2, act, a_mn=True, b_mn=True)
+        dpre = gemm.dense_dswiglu(dy2, w2, pre)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty(ctx.xshape, dtype=torch.bfloat16, device=dy.device)
+            gemm.dense(dpre, w1, b_mn=True, out=dx.view(-1, dx.shape[-1]))
+        dw1 = None
+        if ctx.needs_input_grad[1] and not wgrad_into_main_grad(w1, dpre, x2):
+            dw1 = gemm.dense(dpre, x2, a_mn=True, b_mn=True)
+        return dx, dw1, dw2
+
+
+def mlp_swiglu(x, w1, w2):
+    """SwiGLU MLP ``fc2(swiglu(fc1(x)))`` without biases; the fully fused form when the shapes allow it."""
+    from . import fp8, gemm
+    if (not fp8.enabled() and x.dtype == w1.dtype == w2.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and x.numel() > 0
+            and gemm.dense_ok(w1, w2) and w1.shape[0] % 128 == 0 and w2.shape[0] % 8 == 0 and w2.shape[1] * 2 == w1.shape[0]
+            and os.environ.get("LMOE_FUSED_MLP", "1") != "0"):
+        return _MlpSwigluTc.apply(x, w1, w2)
+    return linear(linear_swiglu(x, w1), w2)
+
+
 def linear_swiglu(x, weight):
     """fc1 + SwiGLU.  bf16 operands that fit the dense tcgen05 kernel take its fused-epilogue form; fp8 and everything
     else go through :func:`linear` followed by the SwiGLU kernel."""
@@ -245,7 +306,8 @@ def linear_reducescatter(x, weight, group, dim):
 # =====================================================================================
 # RMSNorm (+ residual add)
 # =====================================================================================
-_PARTIAL_BLOCKS = NUM_SMS * 4
+def _partial_blocks() -> int:
+    return num_sms() * 4
 
 
 class _RMSNorm(torch.autograd.Function):
@@ -276,7 +338,7 @@ class _RMSNorm(torch.autograd.Function):
         dy = dy.contiguous()
         dres = None if dres is None else dres.contiguous()
         dx = torch.empty_like(xin)
-        P = min(rows, _PARTIAL_BLOCKS)
+        P = min(rows, _partial_blocks())
         partial = torch.empty(P, N, dtype=torch.float32, device=xin.device) if w is not None else None
         dw = torch.empty(N, dtype=xin.dtype, device=xin.device) if w is not None else None
         _check(lib().lmoe_rms_norm_bwd(_p(dy), _p(xin), _p(w), _p(rstd), _p(dres), _p(dx), _p(partial), _p(dw),
@@ -364,7 +426,7 @@ class _LayerNorm(torch.autograd.Function):
         dy = dy.contiguous()
         dres = None if dres is None else dres.contiguous()
         dx = torch.empty_like(xin)
-        P = min(rows, _PARTIAL_BLOCKS)
+        P = min(rows, _partial_blocks())
         want = ctx.wdtype is not None or ctx.bdtype is not None
         partial = torch.empty(P, 2 * N, dtype=torch.float32, device=xin.device) if want else None
         dwdb = torch.empty(2 * N, dtype=torch.float32, device=xin.device) if want else None
@@ -433,7 +495,7 @@ class _HeadNormGate(torch.autograd.Function):
         dy = dy.contiguous()
         d_o, dgate = torch.empty_like(oc), torch.empty_like(gc)
         need_dw = w is not None and ctx.do_norm
-        P = min((rows + 7) // 8, NUM_SMS * 8)
+        P = min((rows + 7) // 8, num_sms() * 8)
         partial = torch.empty(P, D, dtype=torch.float32, device=oc.device) if need_dw else None
         dw = torch.empty(D, dtype=oc.dtype, device=oc.device) if need_dw else None
         _check(lib().lmoe_head_norm_gate_bwd(_p(dy), _p(oc), _p(w), _p(gc), _p(rstd), _p(d_o), _p(dgate), _p(partial),
@@ -744,7 +806,7 @@ def _inner_contig(t):
 
 def lsm_groups(B, H, T):
     nchunks = (T + 63) // 64
-    G = max(1, min(nchunks, NUM_SMS // max(B * H, 1)))
+    G = max(1, min(nchunks, num_sms() // max(B * H, 1)))
     cpg = (nchunks + G - 1) // G
     G = (nchunks + cpg - 1) // cpg
     return G, cpg
@@ -1161,29 +1223,59 @@ def _delta_prepare_kernel(q, k, v, beta, g, scale, C=64):
     return W, U, Qd, Kd, A, gamma
 
 
+def _delta_scan_fwd(W, U, Qd, Kd, A, gamma, S0):
+    """``delta_scan_fwd_kernel``: ``Vn = U - W S``, ``O = Qd S + A Vn``, ``S' = gamma S + Kd^T Vn`` over the chunks.
+    Returns ``O, Vn`` ``[B,H,N,C,dv]`` bf16, the state entering every chunk ``Sn`` ``[B,H,N,dk,dv]`` bf16 and the final
+    state in fp32."""
+    B, H, N, C, dk = W.shape
+    dv = U.shape[-1]
+    dev = W.device
+    bf = torch.bfloat16
+    O = torch.empty(B, H, N, C, dv, dtype=bf, device=dev)
+    Vn = torch.empty(B, H, N, C, dv, dtype=bf, device=dev)
+    Sn = torch.empty(B, H, N, dk, dv, dtype=bf, device=dev)
+    Sf = torch.empty(B, H, dk, dv, dtype=torch.float32, device=dev)
+    s0 = None if S0 is None else S0.float().contiguous()
+    a = _DeltaArgs()
+    a.W, a.U, a.Qd, a.Kd, a.A, a.gamma = (t.data_ptr() for t in (W, U, Qd, Kd, A, gamma))
+    a.S0 = 0 if s0 is None else s0.data_ptr()
+    a.O, a.Vn, a.Sn, a.Sfinal = O.data_ptr(), Vn.data_ptr(), Sn.data_ptr(), Sf.data_ptr()
+    a.N, a.dv = N, dv
+    _check(lib().lmoe_delta_scan(_i32(0), _i32(dk), _i32(B * H), ctypes.byref(a), _st()), "delta_scan_fwd")
+    return O, Vn, Sn, Sf
+
+
+def _delta_scan_bwd(W, Qd, Kd, A, gamma, dO, dSf):
+    """``delta_scan_bwd_kernel``: the reverse recurrence ``dVn = A^T dO + Kd dS'``, ``dS = gamma dS' + Qd^T dO - W^T dVn``.
+    Returns ``dVn`` ``[B,H,N,C,dv]``, the gradient of the state leaving every chunk ``dSn`` ``[B,H,N,dk,dv]`` (bf16) and the
+    gradient of the initial state (fp32)."""
+    B, H, N, C, dk = W.shape
+    dv = dO.shape[-1]
+    dev = W.device
+    bf = torch.bfloat16
+    dVn = torch.empty(B, H, N, C, dv, dtype=bf, device=dev)
+    dSn = torch.empty(B, H, N, dk, dv, dtype=bf, device=dev)
+    dS0 = torch.empty(B, H, dk, dv, dtype=torch.float32, device=dev)
+    dsf = None if dSf is None else dSf.float().contiguous()
+    a = _DeltaArgs()
+    a.W, a.Qd, a.Kd, a.A, a.gamma = (t.data_ptr() for t in (W, Qd, Kd, A, gamma))
+    a.U = 0
+    a.dO, a.dSfinal = dO.data_ptr(), 0 if dsf is None else dsf.data_ptr()
+    a.dVn, a.dSn, a.dS0 = dVn.data_ptr(), dSn.data_ptr(), dS0.data_ptr()
+    a.N, a.dv = N, dv
+    _check(lib().lmoe_delta_scan(_i32(1), _i32(dk), _i32(B * H), ctypes.byref(a), _st()), "delta_scan_bwd")
+    return dVn, dSn, dS0
+
+
 class _DeltaChunkScan(torch.autograd.Function):
-    """The recurrence over chunks of the (gated) delta rule on the kernels of ``csrc/lsm_delta.cu``:
-    ``Vn = U - W S``, ``O = Qd S + A Vn``, ``S' = gamma S + Kd^T Vn``.  Backward: the reverse state-gradient recurrence is
-    the second kernel; the gradients of the tiles are chunk-parallel products of what the two kernels wrote."""
+    """The recurrence over chunks of the (gated) delta rule on the kernels of ``csrc/lsm_delta.cu`` as an autograd node over
+    the tiles.  Backward: the reverse state-gradient recurrence is the second kernel; the gradients of the tiles are
+    chunk-parallel products of what the two kernels wrote."""
 
     @staticmethod
     def forward(ctx, W, U, Qd, Kd, A, gamma, S0):
-        B, H, N, C, dk = W.shape
-        dv = U.shape[-1]
-        dev = W.device
-        bf = torch.bfloat16
-        O = torch.empty(B, H, N, C, dv, dtype=bf, device=dev)
-        Vn = torch.empty(B, H, N, C, dv, dtype=bf, device=dev)
-        Sn = torch.empty(B, H, N, dk, dv, dtype=bf, device=dev)
-        Sf = torch.empty(B, H, dk, dv, dtype=torch.float32, device=dev)
-        s0 = None if S0 is None else S0.float().contiguous()
         W, U, Qd, Kd, A, gamma = (t.contiguous() for t in (W, U, Qd, Kd, A, gamma))
-        a = _DeltaArgs()
-        a.W, a.U, a.Qd, a.Kd, a.A, a.gamma = (t.data_ptr() for t in (W, U, Qd, Kd, A, gamma))
-        a.S0 = 0 if s0 is None else s0.data_ptr()
-        a.O, a.Vn, a.Sn, a.Sfinal = O.data_ptr(), Vn.data_ptr(), Sn.data_ptr(), Sf.data_ptr()
-        a.N, a.dv = N, dv
-        _check(lib().lmoe_delta_scan(_i32(0), _i32(dk), _i32(B * H), ctypes.byref(a), _st()), "delta_scan_fwd")
+        O, Vn, Sn, Sf = _delta_scan_fwd(W, U, Qd, Kd, A, gamma, S0)
         ctx.save_for_backward(W, Qd, Kd, A, gamma, Vn, Sn)
         ctx.has_s0 = S0 is not None
         return O, Sf
@@ -1191,22 +1283,8 @@ class _DeltaChunkScan(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dO, dSf):
         W, Qd, Kd, A, gamma, Vn, Sn = ctx.saved_tensors
-        B, H, N, C, dk = W.shape
-        dv = Vn.shape[-1]
-        dev = W.device
-        bf = torch.bfloat16
-        dO = dO.to(bf).contiguous()
-        dVn = torch.empty(B, H, N, C, dv, dtype=bf, device=dev)
-        dSn = torch.empty(B, H, N, dk, dv, dtype=bf, device=dev)
-        dS0 = torch.empty(B, H, dk, dv, dtype=torch.float32, device=dev)
-        dsf = None if dSf is None else dSf.float().contiguous()
-        a = _DeltaArgs()
-        a.W, a.Qd, a.Kd, a.A, a.gamma = (t.data_ptr() for t in (W, Qd, Kd, A, gamma))
-        a.U = 0
-        a.dO, a.dSfinal = dO.data_ptr(), 0 if dsf is None else dsf.data_ptr()
-        a.dVn, a.dSn, a.dS0 = dVn.data_ptr(), dSn.data_ptr(), dS0.data_ptr()
-        a.N, a.dv = N, dv
-        _check(lib().lmoe_delta_scan(_i32(1), _i32(dk), _i32(B * H), ctypes.byref(a), _st()), "delta_scan_bwd")
+        dO = dO.to(torch.bfloat16).contiguous()
+        dVn, dSn, dS0 = _delta_scan_bwd(W, Qd, Kd, A, gamma, dO, dSf)
         SnT = Sn.transpose(-1, -2)
         dW = -(dVn @ SnT)
         dQd = dO @ SnT
@@ -1214,6 +1292,42 @@ class _DeltaChunkScan(torch.autograd.Function):
         dKd = Vn @ dSn.transpose(-1, -2)
         dgamma = (dSn.float() * Sn.float()).sum((-1, -2))
         return dW, dVn, dQd, dKd, dA, dgamma, (dS0 if ctx.has_s0 else None)
+
+
+class _DeltaPrepBwdArgs(ctypes.Structure):
+    _fields_ = ([(n, ctypes.c_void_p) for n in ("q", "k", "v")] +
+                [(n, ctypes.c_longlong) for n in ("qs_b", "qs_t", "qs_h", "ks_b", "ks_t", "ks_h", "vs_b", "vs_t", "vs_h")] +
+                [(n, ctypes.c_void_p) for n in ("beta", "g", "Sn", "dSn", "Vn", "dVn", "dO", "dgamma", "dq", "dk", "dv", "dbeta",
+                                                "dg")] +
+                [(n, ctypes.c_int) for n in ("B", "T", "H", "N")] + [("scale", ctypes.c_float)])
+
+
+def _delta_prepare_bwd_kernel(q, k, v, beta, g, scale, Sn, dSn, Vn, dVn, dO, dgamma):
+    """Gradients of ``q, k, v, beta, g`` from what the two scan kernels wrote, one chunk-parallel kernel
+    (``delta_prep_bwd_kernel``, csrc/lsm_delta.cu): the chunk-local scan equations, ``W = T Kb`` / ``U = T Vb``, the
+    triangular inverse and the decay factors are differentiated in shared memory on the tensor cores."""
+    B, T, H, D = q.shape
+    N = Sn.shape[2]
+    q, k, v = _inner_contig(q), _inner_contig(k), _inner_contig(v)
+    dev = q.device
+    dq, dk, dv = (torch.empty(B, T, H, D, dtype=torch.bfloat16, device=dev) for _ in range(3))
+    dbeta = torch.empty(B, T, H, dtype=torch.float32, device=dev)
+    dg = None if g is None else torch.empty(B, T, H, dtype=torch.float32, device=dev)
+    bt = beta.float().contiguous()
+    gt = None if g is None else g.float().contiguous()
+    a = _DeltaPrepBwdArgs()
+    a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
+    a.qs_b, a.qs_t, a.qs_h = q.stride(0), q.stride(1), q.stride(2)
+    a.ks_b, a.ks_t, a.ks_h = k.stride(0), k.stride(1), k.stride(2)
+    a.vs_b, a.vs_t, a.vs_h = v.stride(0), v.stride(1), v.stride(2)
+    a.beta, a.g = bt.data_ptr(), 0 if gt is None else gt.data_ptr()
+    a.Sn, a.dSn, a.Vn, a.dVn, a.dO = (t.data_ptr() for t in (Sn, dSn, Vn, dVn, dO))
+    a.dgamma = 0 if dgamma is None else dgamma.data_ptr()
+    a.dq, a.dk, a.dv, a.dbeta = dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dbeta.data_ptr()
+    a.dg = 0 if dg is None else dg.data_ptr()
+    a.B, a.T, a.H, a.N, a.scale = B, T, H, N, float(scale)
+    _check(lib().lmoe_delta_prepare_bwd(_i32(D), ctypes.byref(a), _st()), "delta_prepare_bwd")
+    return dq, dk, dv, dbeta, dg
 
 
 class _DeltaRuleScan(torch.autograd.Function):
@@ -1226,7 +1340,9 @@ class _DeltaRuleScan(torch.autograd.Function):
         B, T, H, dk = q.shape
         scale = dk ** -0.5 if scale is None else scale
         with torch.no_grad(), _tf32():
-            if q.dtype == k.dtype == v.dtype == torch.bfloat16 and v.shape[-1] == dk and os.environ.get("LMOE_DELTA_PREP_KERNEL", "1") != "0":
+            ctx.kernel_tiles = (q.dtype == k.dtype == v.dtype == torch.bfloat16 and v.shape[-1] == dk
+                                and os.environ.get("LMOE_DELTA_PREP_KERNEL", "1") != "0")
+            if ctx.kernel_tiles:
                 tiles = _delta_prepare_kernel(q, k, v, beta, g, scale)
             else:
                 tiles = _delta_prepare(q, k, v, beta, g, scale)
@@ -1239,6 +1355,8 @@ class _DeltaRuleScan(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do, dS):
         saved = ctx.saved_tensors
+        if ctx.kernel_tiles and os.environ.get("LMOE_DELTA_PREP_BWD_KERNEL", "1") != "0":
+            return _DeltaRuleScan._backward_kernels(ctx, do, dS)
         ins = [None if t is None else t.detach().requires_grad_(t.is_floating_point()) for t in saved]
         q = ins[0]
         B, T, H, dk = q.shape
@@ -1260,6 +1378,31 @@ class _DeltaRuleScan(torch.autograd.Function):
         full = [None if t is None else next(it) for t in ins]
         full = [None if gr is None else gr.to(t.dtype) for gr, t in zip(full, ins)]
         return (*full, None, None)
+
+
+def _delta_backward_kernels(ctx, do, dS):
+    """Backward of the (gated) delta rule on kernels only: rebuild the tiles, rerun the forward scan for ``Vn`` and the
+    entering states, run the reverse scan, then one chunk-parallel kernel for every input gradient."""
+    q, k, v, beta, g, s0 = ctx.saved_tensors
+    B, T, H, D = q.shape
+    with torch.no_grad():
+        W, U, Qd, Kd, A, gamma = _delta_prepare_kernel(q, k, v, beta, g, ctx.scale)
+        N, C = W.shape[2], W.shape[3]
+        _, Vn, Sn, _ = _delta_scan_fwd(W, U, Qd, Kd, A, gamma, s0)
+        dO = do.to(torch.bfloat16)
+        if N * C != T:
+            dO = F.pad(dO, (0, 0, 0, 0, 0, N * C - T))
+        dO = dO.reshape(B, N, C, H, D).permute(0, 3, 1, 2, 4).contiguous()
+        dVn, dSn, dS0 = _delta_scan_bwd(W, Qd, Kd, A, gamma, dO, dS)
+        dgamma = None if g is None else (dSn.float() * Sn.float()).sum((-1, -2)).contiguous()
+        dq, dk, dv, dbeta, dg = _delta_prepare_bwd_kernel(q, k, v, beta, g, ctx.scale, Sn, dSn, Vn, dVn, dO, dgamma)
+    need = ctx.needs_input_grad
+    return (dq.to(q.dtype) if need[0] else None, dk.to(k.dtype) if need[1] else None, dv.to(v.dtype) if need[2] else None,
+            dbeta.to(beta.dtype) if need[3] else None, (dg.to(g.dtype) if (g is not None and need[4]) else None),
+            (dS0.to(s0.dtype) if (s0 is not None and need[5]) else None), None, None)
+
+
+_DeltaRuleScan._backward_kernels = staticmethod(_delta_backward_kernels)
 
 
 class _DeltaRuleTorch(torch.autograd.Function):

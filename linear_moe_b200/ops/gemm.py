@@ -138,6 +138,21 @@ def dense_swiglu(x: torch.Tensor, w: torch.Tensor, want_pre: bool = True, band: 
     return act, pre
 
 
+def dense_dswiglu(dy: torch.Tensor, w2: torch.Tensor, pre: torch.Tensor, band: Optional[int] = None) -> torch.Tensor:
+    """``dPre = SwiGLU'(pre) applied to (dy @ w2)`` for ``w2 [H, F]`` (the fc2 weight as stored) and ``pre [M, 2F]``: the
+    data-gradient GEMM of fc2 with the activation backward in its epilogue.  ``F`` must be a multiple of 64."""
+    from . import cuda as K
+    M, H = dy.shape
+    Fh = w2.shape[1]
+    dpre = torch.empty(M, 2 * Fh, dtype=torch.bfloat16, device=dy.device)
+    rc = K.lib().lmoe_gemm_dense_dswiglu(K._p(dy), ctypes.c_int(dy.stride(0)), K._p(w2), ctypes.c_int(w2.stride(0)), K._p(pre),
+                                         ctypes.c_int(pre.stride(0)), K._p(dpre), ctypes.c_int(2 * Fh), ctypes.c_int(M),
+                                         ctypes.c_int(Fh), ctypes.c_int(H), ctypes.c_int(BAND if band is None else band),
+                                         K._p(_err(dy.device)), ctypes.c_int(K.NUM_SMS), K._st())
+    K._check(rc, "gemm_dense_dswiglu")
+    return dpre
+
+
 def tile_swiglu_weight(w: torch.Tensor) -> torch.Tensor:
     """``[2f, h]`` = [gate; up]  ->  per 128 output columns: 128 gate rows followed by the 128 up rows."""
     f = w.shape[0] // 2
@@ -210,6 +225,7 @@ class GroupedLinear(torch.autograd.Function):
             fresh = getattr(w, "_main_grad_fresh", False)
             _gg(x, True, dy, True, mg, 2, Kd, N, 0, E, offs, Kd * N, accumulate=not fresh)
             w._main_grad_fresh = False
+            w._direct_wgrad = True
             return dx, None, None
         dw = torch.empty_like(w)
         _gg(x, True, dy, True, dw, 2, Kd, N, 0, E, offs, Kd * N)                           # x_e^T @ dy_e

@@ -10,9 +10,14 @@ LASP workspace protocol
 -----------------------
 ``data``   fp32 ``[NSLOT][W(src)][BH*D*D]`` — slot ``s`` of rank ``j`` receives the summary of every source rank.
 ``flags``  int32 ``[NSLOT][W(src)][nctas]``  — epoch numbers, written with release stores by the source.
-Call ``i`` of a rank uses slot ``i % NSLOT`` with epoch ``i // NSLOT + 1``.  A rank can run ahead of a peer by
-at most one direction of one step (forward waits on lower ranks, backward on higher ranks, and every optimizer
-step synchronises all ranks), i.e. by ``2 x layers`` calls, which NSLOT must exceed.
+Call ``i`` of a rank uses slot ``i % NSLOT`` with epoch ``i // NSLOT + 1``.  The exchange itself does not bound how
+far a rank runs ahead of a peer: in the forward direction rank 0 waits for nobody, in the backward direction the last
+rank waits for nobody, so within one pass a rank can lead by every LSM layer of its stage, and a forward-only loop has no
+other cross-rank dependency at all.  Slot reuse is therefore guarded on the host: ``NSLOT`` is sized from the layer count
+(two passes of every layer), the trainer calls :func:`mark_step_sync` after each optimizer step (whose gradient
+reduction waits for every rank), and a workspace that has issued ``NSLOT - 1`` exchanges since the last such point
+enqueues a one-element all-reduce on the group first: it completes on a rank's stream only when every rank's stream
+has reached it, i.e. when every earlier exchange of every rank has finished and all slots are free.
 """
 from __future__ import annotations
 
@@ -64,11 +69,14 @@ class _LaspArgs(ctypes.Structure):
 
 
 class LaspWorkspace:
-    NSLOT = 64
-
-    def __init__(self, group, max_state_elems: int, device, spin_limit: Optional[int] = None):
-        """``max_state_elems`` = B*H*D*D of the largest exchange."""
+    def __init__(self, group, max_state_elems: int, device, spin_limit: Optional[int] = None, nslot: int = 64):
+        """``max_state_elems`` = B*H*D*D of the largest exchange; ``nslot`` = exchanges that may be in flight between two
+        points at which all ranks are known to have caught up."""
         self.group, self.device = group, device
+        self.NSLOT = max(int(nslot), 4)
+        self.since_sync = 0
+        self.timing = None                           # a list: every exchange appends its (start, end) CUDA events
+        self._sync_token = torch.zeros(1, dtype=torch.float32, device=device)
         W = group.size
         self.W, self.rank = W, group.rank
         self.max_elems = max_state_elems
@@ -89,6 +97,10 @@ class LaspWorkspace:
         assert BH * DD <= self.max_elems, "LASP workspace too small for this state"
         nctas = ((DD + 255) // 256) * BH
         assert nctas <= self.max_ctas
+        if self.since_sync >= self.NSLOT - 1:
+            dist.all_reduce(self._sync_token, group=self.group.pg)      # stream-ordered: all earlier exchanges are over
+            self.since_sync = 0
+        self.since_sync += 1
         slot, epoch = self.calls % self.NSLOT, self.calls // self.NSLOT + 1
         self.calls += 1
         a = _LaspArgs()
@@ -103,7 +115,20 @@ class LaspWorkspace:
         a.H, a.G, a.cpg, a.T, a.DD, a.BH = H, G, cpg, T, DD, BH
         a.spin_limit = self.spin_limit
         # slot layout inside the kernel is [W(src)][BH*DD] / [W(src)][nctas] with the *actual* BH*DD and nctas
+        if self.timing is not None:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
         K._check(K.lib().lmoe_lasp_combine(ctypes.c_int(rev), ctypes.byref(a), K._st()), "lasp_combine")
+        if self.timing is not None:
+            e1.record()
+            self.timing.append((e0, e1))
+
+
+def mark_step_sync():
+    """Called at a point of the step at which every rank has finished its earlier sequence-parallel exchanges (after the
+    gradient reduction): the slot counters of the LASP workspaces start again."""
+    for ws in _LASP.values():
+        ws.since_sync = 0
 
 
 def status_word(device) -> torch.Tensor:
@@ -175,7 +200,7 @@ def init_workspaces(mesh, cfg=None, tc=None):
         H = cfg.num_attention_heads // mesh.tp
         dk, dv = cfg.key_dim // cfg.num_attention_heads, cfg.value_dim // cfg.num_attention_heads
         mb = tc.micro_batch_size if tc is not None else 1
-        _LASP[cp.name] = LaspWorkspace(cp, mb * H * dk * dv, device)
+        _LASP[cp.name] = LaspWorkspace(cp, mb * H * dk * dv, device, nslot=max(64, 2 * cfg.num_layers + 2))
     tpg = mesh["tp"]
     if (not tpg.is_trivial and tpg.size <= 8 and cfg is not None and tpg.name not in _TP
             and os.environ.get("LMOE_FUSED_TP", "1") != "0"):

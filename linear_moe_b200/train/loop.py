@@ -195,6 +195,9 @@ class Trainer:
                 inner.offload.step_done()
         timers("all-grads-sync", 1).start()
         self.optimizer.reduce_grads()
+        if self.device.type == "cuda":
+            from ..parallel import fused_comm
+            fused_comm.mark_step_sync()              # the reduction waits for every rank: all LASP slots are free again
         timers("all-grads-sync", 1).stop()
         timers("optimizer").start()
         lr, wd = self.scheduler.get_lr(), self.scheduler.get_wd()

@@ -164,6 +164,8 @@ class MixedPrecisionAdam:
     @staticmethod
     def _accumulate(p: nn.Parameter):
         if p.grad is not None:
+            if getattr(p, "_direct_wgrad", False) and getattr(p, "_main_grad_fresh", False):
+                p.main_grad.zero_()            # its accumulator is not cleared by zero_grad (direct weights): clear it now
             if p.grad.is_cuda and p.grad.dtype in (torch.bfloat16, torch.float32) and p.grad.is_contiguous():
                 from ..ops import cuda as K
                 K.accumulate_grad(p.main_grad, p.grad)      # one pass: fp32 accumulator += bf16 gradient
@@ -173,8 +175,29 @@ class MixedPrecisionAdam:
             p._main_grad_fresh = False
 
     def zero_grad(self):
+        """Clear the fp32 accumulators.  A weight whose gradient GEMM stores straight into its accumulator (the first
+        write after this call overwrites, ``_main_grad_fresh``) needs no clearing, so once such weights are known only the
+        remaining ranges (norm weights, biases, the embedding table, padding) are zeroed: for the 1.7 B-parameter
+        benchmark model that is 1 GB instead of 6.7 GB per step.  ``reduce_grads`` clears a direct weight that was not
+        written in a step."""
         for b in self.buffers:
-            b.grads.zero_()
+            direct = [bool(getattr(s.param, "_direct_wgrad", False)) for s in b.slots]
+            if not any(direct) or os.environ.get("LMOE_SKIP_ZERO", "1") == "0":
+                b.grads.zero_()
+                continue
+            key = tuple(direct)
+            if getattr(b, "_zero_key", None) != key:
+                ranges, pos = [], 0
+                for s, d in zip(b.slots, direct):
+                    if d:
+                        if s.start > pos:
+                            ranges.append((pos, s.start))
+                        pos = s.start + s.numel
+                if pos < b.numel:
+                    ranges.append((pos, b.numel))
+                b._zero_key, b._zero_ranges = key, ranges
+            for lo, hi in b._zero_ranges:
+                b.grads[lo:hi].zero_()
         for _, p in self.named:
             p.grad = None
             p._main_grad_fresh = True          # the next direct weight-gradient GEMM may overwrite instead of add
@@ -249,6 +272,9 @@ class MixedPrecisionAdam:
     def reduce_grads(self):
         """Data-parallel reduction of every buffer: all-reduce, or reduce-scatter into this rank's
         shard under ZeRO-1 (the rest of the buffer is then stale until the next zero_grad)."""
+        for _, p in self.named:                 # a direct weight that saw no gradient this step still holds the last one
+            if getattr(p, "_direct_wgrad", False) and getattr(p, "_main_grad_fresh", False):
+                p.main_grad.zero_()
         self._reduce_sequence_parallel_grads()
         bucketed = self._bucket_state
         self._bucket_state = None

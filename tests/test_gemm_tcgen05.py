@@ -261,3 +261,45 @@ def test_linear_autograd_on_dense_kernel(main_grad):
     assert ((x.grad.float() - reps * xr.grad).norm() / (reps * xr.grad).norm()).item() < 1e-2
     dw = w.main_grad if main_grad else w.grad.float()
     assert ((dw - reps * wr.grad).norm() / (reps * wr.grad).norm()).item() < (1e-5 if main_grad else 1e-2)
+
+
+@pytest.mark.parametrize("M,F,H", [(520, 512, 256), (300, 192, 136), (2048, 1024, 512)])
+def test_gemm_dense_dswiglu(M, F, H):
+    """fc2 data-gradient GEMM with the SwiGLU backward in its epilogue against fp32 autograd of swiglu(pre) @ W2^T."""
+    from linear_moe_b200.ops import gemm
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    dy = (0.5 * torch.randn(M, H, device=dev)).to(torch.bfloat16)
+    w2 = (0.1 * torch.randn(H, F, device=dev)).to(torch.bfloat16)
+    pre = torch.randn(M, 2 * F, device=dev).to(torch.bfloat16)
+    dpre = gemm.dense_dswiglu(dy, w2, pre)
+    torch.cuda.synchronize()
+    gemm.check_error()
+    p = pre.float().requires_grad_(True)
+    act = torch.nn.functional.silu(p[:, :F]) * p[:, F:]
+    (act @ w2.float().t()).backward(dy.float())
+    rel = ((dpre.float() - p.grad).norm() / p.grad.norm()).item()
+    assert rel < 1e-2, rel
+
+
+def test_mlp_swiglu_autograd():
+    """The fused SwiGLU MLP node (fc1 + SwiGLU epilogue, fc2, dSwiGLU epilogue) against fp32 autograd: y, dx, dW1, dW2."""
+    from linear_moe_b200 import ops
+    from linear_moe_b200.ops import gemm
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(1)
+    h, f = 256, 384
+    x = torch.randn(2, 150, h, device=dev).to(torch.bfloat16).requires_grad_(True)
+    w1 = (0.08 * torch.randn(2 * f, h, device=dev)).to(torch.bfloat16).requires_grad_(True)
+    w2 = (0.08 * torch.randn(h, f, device=dev)).to(torch.bfloat16).requires_grad_(True)
+    gy = torch.randn(2, 150, h, device=dev).to(torch.bfloat16)
+    y = ops.mlp_swiglu(x, w1, w2)
+    y.backward(gy)
+    torch.cuda.synchronize()
+    gemm.check_error()
+    xr, w1r, w2r = (t.detach().float().requires_grad_(True) for t in (x, w1, w2))
+    z = xr @ w1r.t()
+    yr = (torch.nn.functional.silu(z[..., :f]) * z[..., f:]) @ w2r.t()
+    yr.backward(gy.float())
+    rel = lambda a, b: ((a.float() - b).norm() / b.norm()).item()
+    assert rel(y, yr) < 1e-2 and rel(x.grad, xr.grad) < 2e-2 and rel(w1.grad, w1r.grad) < 2e-2 and rel(w2.grad, w2r.grad) < 2e-2
