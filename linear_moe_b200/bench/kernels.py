@@ -225,9 +225,11 @@ def bench_flash(size):
 
 
 def bench_lsm_families(size):
+    """GLA and the gated delta rule, forward and backward.  ``--size small`` runs every operator once (one forward, one
+    backward, 4 x 4096 tokens so that the inputs exceed L2) and is the case to put under a profiler; ``full`` times them."""
     from .. import ops
     dev = torch.device("cuda", 0)
-    B, H, D = 1, 8, 128
+    B, H, D = 4, 8, 128
     T = 4096
     q, k, v = [(0.5 * torch.randn(B, T, H, D, device=dev)).bfloat16().requires_grad_(True) for _ in range(3)]
     gk = (torch.nn.functional.logsigmoid(torch.randn(B, T, H, D, device=dev)) / 16).requires_grad_(True)
@@ -237,18 +239,23 @@ def bench_lsm_families(size):
     kn = torch.nn.functional.normalize(k.detach().float(), dim=-1).bfloat16().requires_grad_(True)
     cases = {
         "gla (lsm_vector.cu)": lambda: ops.lsm_vector(q, k, v, gk, None, None, None, 64)[0],
-        "gated delta rule (torch WY)": lambda: ops.lsm_delta(q, kn, v, beta, g, None, None, 64)[0],
+        "gated delta rule (lsm_delta.cu)": lambda: ops.lsm_delta(q, kn, v, beta, g, None, None, 64)[0],
     }
     for name, fn in cases.items():
+        if size == "small":
+            fn().backward(go)
+            torch.cuda.synchronize()
+            print(f"{name}: one forward + backward, B={B} T={T} H={H} D={D}")
+            continue
         with torch.no_grad():
-            report(f"{name} fwd T={T} H={H} D={D}", timeit(fn, iters=5))
+            report(f"{name} fwd B={B} T={T} H={H} D={D}", timeit(fn, iters=5))
         o = fn()
 
         def bwd():
             for t in (q, k, v, gk, g, beta, kn):
                 t.grad = None
             o.backward(go, retain_graph=True)
-        report(f"{name} bwd T={T} H={H} D={D}", timeit(bwd, iters=5))
+        report(f"{name} bwd B={B} T={T} H={H} D={D}", timeit(bwd, iters=5))
 
 
 def bench_moe(size):

@@ -170,18 +170,35 @@ __global__ void combine_kernel(float* __restrict__ states, const float* __restri
     const int e = blockIdx.x * blockDim.x + threadIdx.x;
     if (e >= DD) return;
     float carry = seed != nullptr ? seed[(int64_t)bh * DD + e] : 0.f;
-    for (int i = 0; i < G; ++i) {
-        const int g = REV ? G - 1 - i : i;
-        float a;
-        if (gdecay != nullptr) a = gdecay[(int64_t)bh * G + g];
-        else if (gconst != nullptr) {
-            int t_lo = g * cpg * CH, t_hi = min(T, (g + 1) * cpg * CH);
-            a = gconst[h] * (float)max(t_hi - t_lo, 0);
-        } else a = 0.f;
-        float* p = states + ((int64_t)bh * G + g) * DD + e;
-        float m = *p;
-        *p = carry;
-        carry = __expf(a) * carry + m;
+    // the summaries of a batch of groups are loaded before any of them is overwritten, so that the loads of a thread are
+    // in flight together (one dependent load per group would leave the kernel bound by memory latency)
+    constexpr int NB = 8;
+    for (int i0 = 0; i0 < G; i0 += NB) {
+        float m[NB], dec[NB];
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            const int i = i0 + j;
+            if (i < G) {
+                const int g = REV ? G - 1 - i : i;
+                m[j] = __ldcg(states + ((int64_t)bh * G + g) * DD + e);
+                float a;
+                if (gdecay != nullptr) a = gdecay[(int64_t)bh * G + g];
+                else if (gconst != nullptr) {
+                    int t_lo = g * cpg * CH, t_hi = min(T, (g + 1) * cpg * CH);
+                    a = gconst[h] * (float)max(t_hi - t_lo, 0);
+                } else a = 0.f;
+                dec[j] = __expf(a);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            const int i = i0 + j;
+            if (i < G) {
+                const int g = REV ? G - 1 - i : i;
+                states[((int64_t)bh * G + g) * DD + e] = carry;
+                carry = dec[j] * carry + m[j];
+            }
+        }
     }
     if (final_out != nullptr) final_out[(int64_t)bh * DD + e] = carry;
 }

@@ -173,13 +173,24 @@ __global__ void gla_combine_kernel(float* __restrict__ states, const float* __re
     if (e >= DD) return;
     const int row = e / D;
     float carry = seed != nullptr ? seed[(int64_t)bh * DD + e] : 0.f;
-    for (int i = 0; i < G; ++i) {
-        const int g = REV ? G - 1 - i : i;
-        float a = gdecay[((int64_t)bh * G + g) * D + row];
-        float* p = states + ((int64_t)bh * G + g) * DD + e;
-        float m = *p;
-        *p = carry;
-        carry = __expf(a) * carry + m;
+    // batches of loads in flight together (a load per group that waits for the previous store is bound by memory latency)
+    constexpr int NB = 8;
+    for (int i0 = 0; i0 < G; i0 += NB) {
+        float m[NB], dec[NB];
+#pragma unroll
+        for (int j = 0; j < NB; ++j)
+            if (i0 + j < G) {
+                const int g = REV ? G - 1 - (i0 + j) : i0 + j;
+                m[j] = __ldcg(states + ((int64_t)bh * G + g) * DD + e);
+                dec[j] = __expf(gdecay[((int64_t)bh * G + g) * D + row]);
+            }
+#pragma unroll
+        for (int j = 0; j < NB; ++j)
+            if (i0 + j < G) {
+                const int g = REV ? G - 1 - (i0 + j) : i0 + j;
+                states[((int64_t)bh * G + g) * DD + e] = carry;
+                carry = dec[j] * carry + m[j];
+            }
     }
     if (final_out != nullptr) final_out[(int64_t)bh * DD + e] = carry;
 }

@@ -252,6 +252,40 @@ def apply_rope(x, cos, sin, interleaved: bool = False):
     return R.apply_rope(x, cos, sin, interleaved)
 
 
+def rope_positions(T: int, batch: int, device, seqlen_offsets=None, cu_seqlens=None):
+    """Token positions for rotary embeddings of sequences that do not all start at 0.
+
+    ``seqlen_offsets``: an int or an int tensor ``[batch]`` -- sequence ``b`` starts at position ``offsets[b]`` (decoding
+    with caches of different lengths).  ``cu_seqlens``: int tensor ``[n + 1]`` of a packed batch (``batch == 1``, ``T`` =
+    total tokens) -- positions restart at every boundary.  The two can be combined (one offset per packed sequence).
+    Same contract as the ``seqlen_offsets`` / ``cu_seqlens`` arguments of the reference's rotary kernel
+    (common_modules/rotary.py:40-134).  Returns an int64 tensor ``[batch, T]``."""
+    ar = torch.arange(T, device=device, dtype=torch.int64)
+    if cu_seqlens is not None:
+        cu = cu_seqlens.to(device=device, dtype=torch.int64)
+        seq_id = torch.searchsorted(cu[1:].contiguous(), ar, right=True)            # packed sequence of every token
+        pos = ar - cu[seq_id]
+        if seqlen_offsets is not None:
+            off = torch.as_tensor(seqlen_offsets, device=device, dtype=torch.int64)
+            pos = pos + (off[seq_id] if off.dim() else off)
+        return pos[None, :].expand(batch, T)
+    pos = ar[None, :].expand(batch, T)
+    if seqlen_offsets is not None:
+        off = torch.as_tensor(seqlen_offsets, device=device, dtype=torch.int64)
+        pos = pos + (off[:, None] if off.dim() else off)
+    return pos
+
+
+def apply_rope_at(x, cos_table, sin_table, positions, interleaved: bool = False):
+    """Rotary embedding with an explicit position per token: ``x`` ``[B,T,H,D]``, tables ``[P, R/2]`` covering every
+    position, ``positions`` int ``[B,T]`` (see :func:`rope_positions`).  The per-token rows of the tables are gathered
+    once and the ordinary kernel runs on the batch flattened into one sequence."""
+    B, T, H, D = x.shape
+    idx = positions.reshape(-1)
+    cos, sin = cos_table.index_select(0, idx), sin_table.index_select(0, idx)
+    return apply_rope(x.reshape(1, B * T, H, D), cos, sin, interleaved).reshape(B, T, H, D)
+
+
 def causal_conv1d(x, weight, bias=None, activation="silu", initial_state=None):
     if _cuda(x):
         return _K().causal_conv1d(x, weight, bias, activation, initial_state)

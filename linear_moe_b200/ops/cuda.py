@@ -283,14 +283,20 @@ def fused_lasp_available(group, q, k, v, g) -> bool:
     from ..parallel import fused_comm
     if fused_comm.lasp_workspace(group) is None:
         return False
-    D = q.shape[-1]
-    return (q.dtype == torch.bfloat16 and D == v.shape[-1] and D in (64, 128)
-            and (g is None or g.dim() == 1))
+    ws = fused_comm.lasp_workspace(group)
+    B, _, H, D = q.shape
+    return (q.dtype == torch.bfloat16 and k.dtype == q.dtype and v.dtype == q.dtype and D == v.shape[-1]
+            and D == k.shape[-1] and D in (64, 128) and B * H * D * D <= ws.max_elems)
 
 
 def lasp2_scalar(q, k, v, g, scale, group, chunk_size):
     from ..parallel import fused_comm
     return fused_comm.lasp2_scalar(q, k, v, g, scale, group)
+
+
+def lasp2_vector(q, k, v, gk, scale, group, chunk_size):
+    from ..parallel import fused_comm
+    return fused_comm.lasp2_vector(q, k, v, gk, scale, group)
 
 
 def allgather_linear(x, weight, bias, group, dim):
@@ -861,9 +867,10 @@ class _LsmScalar(torch.autograd.Function):
         seed = None if init is None else init.float().contiguous()
         a = _lsm_args(q, k, v, gf, gmode, scale, B, T, H, G, cpg, states, gdecay, o=o)
         _lsm_launch(0, D, a)
-        lasp = _LASP_CTX if (gmode != 2 and init is None) else None
+        lasp = _LASP_CTX if init is None else None
         if lasp is not None:       # sequence split over ranks: exchange fused into the combine kernel
-            lasp.combine(0, states, gf if gmode == 1 else None, final, B * H, H, G, cpg, T, D)
+            lasp.combine(0, states, gf if gmode == 1 else None, final, B * H, H, G, cpg, T, D,
+                         gdecay=gdecay, dmode=1 if gmode == 2 else 0)
         else:
             _lsm_combine(0, states, gdecay, gf if gmode == 1 else None, seed, final, B * H, H, G, cpg, T, D)
         _lsm_launch(2, D, a)
@@ -895,7 +902,12 @@ class _LsmScalar(torch.autograd.Function):
         _lsm_launch(1, D, a2)
         seed = None if dfinal is None else dfinal.float().contiguous()
         if ctx.lasp is not None:
-            ctx.lasp.combine(1, dstates, gf if ctx.gmode == 1 else None, None, B * H, H, G, cpg, T, D)
+            # the gradient of the state that leaves this rank arrives from the ranks after it; the decay gradient needs it
+            need_r = ctx.gmode == 2 or (ctx.gmode == 1 and len(ctx.needs_input_grad) > 3 and ctx.needs_input_grad[3])
+            r_out = torch.empty(B, H, D, D, dtype=torch.float32, device=q.device) if need_r else None
+            ctx.lasp.combine(1, dstates, gf if ctx.gmode == 1 else None, None, B * H, H, G, cpg, T, D,
+                             gdecay=gdecay, dmode=1 if ctx.gmode == 2 else 0, r_out=r_out)
+            dfinal = r_out
         else:
             _lsm_combine(1, dstates, gdecay, gf if ctx.gmode == 1 else None, seed, dinit, B * H, H, G, cpg, T, D)
         _lsm_launch(4, D, a2)
@@ -1050,8 +1062,13 @@ class _LsmVector(torch.autograd.Function):
         seed = None if init is None else init.float().contiguous()
         a = _gla_args(q, k, v, gf, scale, B, T, H, G, cpg, states, gdecay, o=o)
         _gla_launch(0, D, a)
-        _gla_combine(0, states, gdecay, seed, final, B * H, G, D)
+        lasp = _LASP_CTX if init is None else None
+        if lasp is not None:       # sequence split over ranks: exchange fused into the combine kernel
+            lasp.combine(0, states, None, final, B * H, H, G, cpg, T, D, gdecay=gdecay, dmode=2)
+        else:
+            _gla_combine(0, states, gdecay, seed, final, B * H, G, D)
         _gla_launch(2, D, a)
+        ctx.lasp = lasp
         ctx.save_for_backward(q, k, v, gf, states, gdecay, final)
         ctx.scale, ctx.grid, ctx.has_init, ctx.g_dtype = scale, (G, cpg), init is not None, gk.dtype
         return o, final
@@ -1071,7 +1088,12 @@ class _LsmVector(torch.autograd.Function):
         a2 = _gla_args(q, k, v, gf, ctx.scale, B, T, H, G, cpg, dstates, None, d_o=d_o, dk=dk, dv=dv)
         _gla_launch(1, D, a2)
         seed = None if dfinal is None else dfinal.float().contiguous()
-        _gla_combine(1, dstates, gdecay, seed, dinit, B * H, G, D)
+        if ctx.lasp is not None:
+            r_out = torch.empty(B, H, D, D, dtype=torch.float32, device=q.device)
+            ctx.lasp.combine(1, dstates, None, None, B * H, H, G, cpg, T, D, gdecay=gdecay, dmode=2, r_out=r_out)
+            dfinal = r_out         # gradient of the state leaving this rank, folded from the ranks after it
+        else:
+            _gla_combine(1, dstates, gdecay, seed, dinit, B * H, G, D)
         _gla_launch(4, D, a2)
         # d gk_t = sum_{i>=t} q_i . dq_i - sum_{j>=t} k_j . dk_j per channel (+ <S_T, dS_T> rows with a final-state gradient)
         # (the scan runs along the innermost dimension of a [B,H,D,T] copy: a scan over an outer dimension is ~10x slower)

@@ -61,11 +61,12 @@ def _symm_empty(numel: int, dtype, device, group):
 
 class _LaspArgs(ctypes.Structure):
     _fields_ = [("states", ctypes.c_void_p), ("final_out", ctypes.c_void_p), ("gconst", ctypes.c_void_p),
+                ("gdecay", ctypes.c_void_p), ("r_out", ctypes.c_void_p),
                 ("peer_data", ctypes.c_void_p), ("peer_flags", ctypes.c_void_p), ("status", ctypes.c_void_p),
-                ("data_off", ctypes.c_longlong), ("flag_off", ctypes.c_longlong), ("epoch", ctypes.c_int),
-                ("rank", ctypes.c_int), ("world", ctypes.c_int), ("H", ctypes.c_int), ("G", ctypes.c_int),
-                ("cpg", ctypes.c_int), ("T", ctypes.c_int), ("DD", ctypes.c_int), ("BH", ctypes.c_int),
-                ("spin_limit", ctypes.c_longlong)]
+                ("data_off", ctypes.c_longlong), ("dec_off", ctypes.c_longlong), ("flag_off", ctypes.c_longlong),
+                ("epoch", ctypes.c_int), ("rank", ctypes.c_int), ("world", ctypes.c_int), ("H", ctypes.c_int),
+                ("G", ctypes.c_int), ("cpg", ctypes.c_int), ("T", ctypes.c_int), ("DD", ctypes.c_int), ("BH", ctypes.c_int),
+                ("dmode", ctypes.c_int), ("D", ctypes.c_int), ("spin_limit", ctypes.c_longlong)]
 
 
 class LaspWorkspace:
@@ -81,7 +82,8 @@ class LaspWorkspace:
         self.W, self.rank = W, group.rank
         self.max_elems = max_state_elems
         self.max_ctas = (max_state_elems + 255) // 256 + 4096
-        self.data, self.data_hdl = _symm_empty(self.NSLOT * W * max_state_elems, torch.float32, device, group)
+        self.max_dec = max(max_state_elems // 64, 1)             # summed log decay per state row (rows are >= 64 wide)
+        self.data, self.data_hdl = _symm_empty(self.NSLOT * W * (max_state_elems + self.max_dec), torch.float32, device, group)
         self.flags, self.flag_hdl = _symm_empty(self.NSLOT * W * self.max_ctas, torch.int32, device, group)
         self.flags.zero_()
         self.calls = 0
@@ -91,8 +93,12 @@ class LaspWorkspace:
         torch.cuda.synchronize()
         dist.barrier(group=group.pg)                 # every rank's flags are zero before anyone pushes
 
-    def combine(self, rev: int, states, gconst, final_out, BH, H, G, cpg, T, D):
+    def combine(self, rev: int, states, gconst, final_out, BH, H, G, cpg, T, D, gdecay=None, dmode: int = 0, r_out=None):
+        """One exchange.  ``dmode`` 0: no decay or the constant per-head log decay ``gconst``; 1: ``gdecay`` ``[BH, G]``
+        summed log decay per group (data-dependent scalar decay); 2: ``gdecay`` ``[BH, G, D]`` (per key channel).
+        ``r_out`` ``[BH, D*D]`` receives the folded remote state."""
         from ..ops import cuda as K
+        assert (dmode == 0) == (gdecay is None)
         DD = D * D
         assert BH * DD <= self.max_elems, "LASP workspace too small for this state"
         nctas = ((DD + 255) // 256) * BH
@@ -107,6 +113,10 @@ class LaspWorkspace:
         a.states = states.data_ptr()
         a.final_out = 0 if final_out is None else final_out.data_ptr()
         a.gconst = 0 if gconst is None else gconst.data_ptr()
+        a.gdecay = 0 if gdecay is None else gdecay.data_ptr()
+        a.r_out = 0 if r_out is None else r_out.data_ptr()
+        a.dmode, a.D = dmode, D
+        a.dec_off = self.NSLOT * self.W * self.max_elems + slot * self.W * self.max_dec
         a.peer_data, a.peer_flags = self.peer_data.data_ptr(), self.peer_flags.data_ptr()
         a.status = status_word(self.device).data_ptr()
         a.data_off = slot * self.W * self.max_elems
@@ -186,6 +196,23 @@ def lasp2_scalar(q, k, v, g, scale, group):
         if base is not None:
             return K._LsmScalarFused.apply(base, g, scale, None)
         return K._LsmScalar.apply(q, k, v, g, scale, None)
+    finally:
+        K._LASP_CTX = None
+
+
+def lasp2_vector(q, k, v, gk, scale, group):
+    """Key-channel-gated linear attention (GLA, HGRN2, RWKV6 without bonus) over a sequence split across ``group``, the
+    exchange (state summaries and per-channel slice decays) fused into the combine kernel."""
+    from ..ops import cuda as K
+    ws = lasp_workspace(group)
+    D = q.shape[-1]
+    scale = D ** -0.5 if scale is None else scale
+    K._LASP_CTX = ws
+    try:
+        base = K._fused_base(q, k, v)
+        if base is not None:
+            return K._LsmVectorFused.apply(base, gk, scale, None)
+        return K._LsmVector.apply(q, k, v, gk, scale, None)
     finally:
         K._LASP_CTX = None
 

@@ -13,9 +13,10 @@ The reference implements this only for undecayed linear attention, drops the int
 term and uses NCCL ``all_gather_into_tensor`` (lasp2_without_mask_triton_op.py:673-750,
 lasp2.py:62-79).  This module is the general algorithm, written on differentiable
 collectives so that autograd produces the mirrored backward (gather of state gradients,
-suffix combine).  On CUDA the scalar-decay family takes the fused path of
-``ops.cuda.lasp2_scalar`` instead, where the exchange happens inside the scan kernels
-through peer memory.
+suffix combine).  On CUDA the scalar-decay family (constant or data-dependent decay) and the
+key-channel-gated family take the fused paths ``ops.cuda.lasp2_scalar`` / ``lasp2_vector`` instead,
+where the exchange happens inside the combine kernel through peer memory; the delta-rule
+families (whose transition is a ``dk x dk`` matrix) use the form below.
 """
 from __future__ import annotations
 
@@ -125,6 +126,9 @@ def lasp2(kind: str, q, k, v, *, group: Group, g=None, gk=None, beta=None, scale
     if (q.is_cuda and kind == "scalar" and initial_state is None and mode != "fused_recurrent"
             and ops._K().fused_lasp_available(group, q, k, v, g)):
         return ops._K().lasp2_scalar(q, k, v, g, scale, group, chunk_size)
+    if (q.is_cuda and kind == "vector" and bonus is None and initial_state is None and mode != "fused_recurrent"
+            and ops._K().fused_lasp_available(group, q, k, v, None)):
+        return ops._K().lasp2_vector(q, k, v, gk, scale, group, chunk_size)
 
     M, A = _summaries(kind, q, k, v, g, gk, beta, scale, chunk_size, bonus)
     W, r = group.size, group.rank

@@ -61,6 +61,58 @@ def _lasp_worker(rank, world, D, decay, T):
     return errs, scale_o, scale_g
 
 
+def _lasp_gated_worker(rank, world, kind, D, T):
+    """Data-dependent decays through the fused exchange: per-token scalar gates (``scalar``: Mamba2 SSD, simple GLA) and
+    per-key-channel gates (``vector``: GLA, HGRN2, RWKV6)."""
+    from linear_moe_b200 import ops
+    from linear_moe_b200.config.model_config import ParallelConfig
+    from linear_moe_b200.dist.mesh import Mesh
+    from linear_moe_b200.ops import cuda as K
+    from linear_moe_b200.parallel import fused_comm
+    from linear_moe_b200.parallel.lasp2 import lasp2
+    dev = torch.device("cuda", rank)
+    mesh = Mesh(ParallelConfig(context_parallel_size=world))
+    B, H = 2, 3
+    fused_comm._LASP[mesh["cp"].name] = fused_comm.LaspWorkspace(mesh["cp"], B * H * D * D, dev, spin_limit=2_000_000)
+    torch.manual_seed(1)
+    Tt = T * world
+    qkv = (0.5 * torch.randn(B, Tt, H, 3 * D, device=dev)).to(torch.bfloat16)
+    go = torch.randn(B, Tt, H, D, device=dev).to(torch.bfloat16)
+    if kind == "scalar":
+        gate = torch.nn.functional.logsigmoid(torch.randn(B, Tt, H, device=dev) + 3.0)
+    else:
+        gate = torch.nn.functional.logsigmoid(torch.randn(B, Tt, H, D, device=dev) + 3.0) / 4
+    sl = slice(rank * T, (rank + 1) * T)
+
+    def run(x, gt, group):
+        q, k, v = x.split(D, dim=-1)
+        if group is None:
+            return (ops.lsm_scalar(q, k, v, gt, None, None, 64) if kind == "scalar"
+                    else ops.lsm_vector(q, k, v, gt, None, None, None, 64))[0]
+        return lasp2(kind, q, k, v, group=group, g=gt if kind == "scalar" else None, gk=gt if kind == "vector" else None)[0]
+    full, gfull = qkv.clone().requires_grad_(True), gate.clone().requires_grad_(True)
+    o_ref = run(full, gfull, None)
+    o_ref.backward(go)
+    K.reset_launch_count()
+    loc, gloc = qkv[:, sl].clone().requires_grad_(True), gate[:, sl].clone().requires_grad_(True)
+    calls0 = fused_comm.lasp_workspace(mesh["cp"]).calls
+    o = run(loc, gloc, mesh["cp"])
+    o.backward(go[:, sl])
+    torch.cuda.synchronize()
+    fused_comm.check_status("lasp gated test")
+    assert fused_comm.lasp_workspace(mesh["cp"]).calls == calls0 + 2, "the fused exchange was not used"
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-6)).item()
+    return rel(o, o_ref[:, sl]), rel(loc.grad, full.grad[:, sl]), rel(gloc.grad, gfull.grad[:, sl])
+
+
+@pytest.mark.parametrize("kind,D,T", [("scalar", 128, 512), ("vector", 128, 512), ("vector", 64, 200)])
+def test_lasp2_fused_data_dependent_decay(kind, D, T):
+    _need_gpus(2)
+    outs = run_distributed(_lasp_gated_worker, 2, backend="nccl", kind=kind, D=D, T=T)
+    for eo, eg, edecay in outs:
+        assert eo < 2e-2 and eg < 3e-2 and edecay < 3e-2, (kind, eo, eg, edecay)
+
+
 @pytest.mark.parametrize("D,decay,T", [(128, True, 1024), (64, False, 300)])
 def test_lasp2_fused_matches_single_gpu(D, decay, T):
     _need_gpus(2)

@@ -136,3 +136,34 @@ def test_hybrid_layer_allocator():
         layout.allocate_mamba_pattern(4, 0.0, 0.0, override="MxMM")
     with pytest.raises(ValueError):
         layout.allocate_mamba_pattern(4, 0.5, 0.0, override="MMMM")
+
+
+def test_rope_with_sequence_offsets_and_packed_sequences():
+    """Rotary embedding with per-sequence start offsets and with packed sequences (positions restart at cu_seqlens
+    boundaries) equals the plain op applied to each sequence with its own table slice."""
+    import torch
+    from linear_moe_b200 import ops
+    from linear_moe_b200.ref import ops as R
+    torch.manual_seed(0)
+    B, T, H, D = 3, 10, 2, 16
+    cos, sin = R.rope_freqs(64, D, 10000.0, 0, torch.device("cpu"), None)
+    x = torch.randn(B, T, H, D)
+    offs = torch.tensor([0, 5, 17])
+    pos = ops.rope_positions(T, B, x.device, seqlen_offsets=offs)
+    got = ops.apply_rope_at(x, cos, sin, pos)
+    for b in range(B):
+        o = int(offs[b])
+        want = ops.apply_rope(x[b:b + 1], cos[o:o + T], sin[o:o + T])
+        assert torch.allclose(got[b:b + 1], want, atol=1e-6)
+    assert torch.equal(ops.rope_positions(T, B, x.device, seqlen_offsets=4), torch.arange(4, 4 + T).expand(B, T))
+    # packed: three sequences of 4, 1 and 7 tokens in one row of 12
+    cu = torch.tensor([0, 4, 5, 12])
+    xp = torch.randn(1, 12, H, D)
+    pos = ops.rope_positions(12, 1, xp.device, cu_seqlens=cu)
+    assert pos.tolist() == [[0, 1, 2, 3, 0, 0, 1, 2, 3, 4, 5, 6]]
+    got = ops.apply_rope_at(xp, cos, sin, pos, interleaved=True)
+    for s, e in zip(cu[:-1].tolist(), cu[1:].tolist()):
+        want = ops.apply_rope(xp[:, s:e], cos[: e - s], sin[: e - s], interleaved=True)
+        assert torch.allclose(got[:, s:e], want, atol=1e-6)
+    pos = ops.rope_positions(12, 1, xp.device, cu_seqlens=cu, seqlen_offsets=torch.tensor([2, 0, 9]))
+    assert pos.tolist() == [[2, 3, 4, 5, 0, 9, 10, 11, 12, 13, 14, 15]]
