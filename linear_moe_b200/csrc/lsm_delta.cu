@@ -414,7 +414,9 @@ __global__ void __launch_bounds__(NT) delta_prep_fwd_kernel(PrepArgs a) {
 // ---------------------------------------------------------------------------------------------------------------
 // Chunk-parallel backward of everything that is not the state recurrence: one CTA per (batch, head, chunk).
 // Inputs: q, k, v, beta, g (to rebuild the tiles), the entering state S_n and the gradient dS'_n of the leaving state,
-// Vn, dVn (= dU) and dO of the chunk (written by the two scan kernels), and dgamma_n = <dS'_n, S_n> (gated case).
+// Vn, dVn (= dU) and dO of the chunk (written by the two scan kernels).  The gradient of the chunk's total decay,
+// dgamma_n = <dS'_n, S_n> (gated case), is formed here too: every thread keeps its share of S_n in registers while the
+// state buffer is refilled with dS'_n.
 //
 //   through the scan equations      dW = -dVn S^T,  dQd = dO S^T,  dKd = Vn dS'^T,  dAqk = tril(dO Vn^T)
 //   through W = T Kb, U = T Vb      dKb = T^T dW,  dVb = T^T dU,  dT = dW Kb^T + dU Vb^T,  dA = -strict_lower(T^T dT T^T)
@@ -435,7 +437,6 @@ struct PrepBwdArgs {
     const float* g;                    // or null
     const bf16 *Sn, *dSn;              // [BH, N, D, D]
     const bf16 *Vn, *dVn, *dO;         // [BH, N, C, D]
-    const float* dgamma;               // [BH, N] or null
     bf16 *dq, *dk, *dv;                // contiguous [B, T, H, D]
     float *dbeta, *dg;                 // [B, T, H]
     int B, T, H, N;
@@ -471,9 +472,13 @@ __device__ __forceinline__ void store_rows_global(const float (&acc)[NTL][4], bf
     }
 }
 
+// 256 threads: warp w works on rows 16 (w & 3) .. +15 and on column half (w >> 2) of every product, so that eight
+// warps per SM hide each other's shared-memory and tensor-pipe latencies (the tiles allow one CTA per SM only).
+constexpr int NTB = 256;
+
 template <int D>
-__global__ void __launch_bounds__(NT) delta_prep_bwd_kernel(PrepBwdArgs a) {
-    constexpr int LD = D + 8, LDC = C + 8, LDA = C + 1, NTD = D / 8;
+__global__ void __launch_bounds__(NTB) delta_prep_bwd_kernel(PrepBwdArgs a) {
+    constexpr int LD = D + 8, LDC = C + 8, LDA = C + 1, NTH = D / 16, HD = D / 2;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Ks = reinterpret_cast<bf16*>(smem_raw);            // [C][LD]
     bf16* Qs = Ks + C * LD;                                  // [C][LD]
@@ -491,12 +496,16 @@ __global__ void __launch_bounds__(NT) delta_prep_bwd_kernel(PrepBwdArgs a) {
     float* bet = bcum + C;                                   // [C]
     float* db = bet + C;                                     // [C] gradient of the cumulative log decay
     float* dbe = db + C;                                     // [C] gradient of beta
+    float* dgam = dbe + C;                                   // [1] <dS'_n, S_n>
     const int n = blockIdx.x, bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
     const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
     const int t0 = n * C;
     const int valid = min(C, a.T - t0);
     const long long cn = (long long)bh * a.N + n;
-    const int m0 = 16 * w, r0 = m0 + (l >> 2), c0 = (l & 3) * 2;
+    const int m0 = 16 * (w & 3), r0 = m0 + (l >> 2), c0 = (l & 3) * 2;
+    const bool gated = a.g != nullptr;
+    const int nd = (w >> 2) * HD;                            // first column of this warp's half of a D-wide product
+    const int nc = (w >> 2) * (C / 2);                       // ... of a C-wide product
 
     load_tile_async<C, D, LD>(Ks, a.k + b * a.ks_b + h * a.ks_h + (long long)t0 * a.ks_t, a.ks_t, valid);
     load_tile_async<C, D, LD>(Qs, a.q + b * a.qs_b + h * a.qs_h + (long long)t0 * a.qs_t, a.qs_t, valid);
@@ -516,6 +525,7 @@ __global__ void __launch_bounds__(NT) delta_prep_bwd_kernel(PrepBwdArgs a) {
         for (int o = 1; o < 32; o <<= 1) { const float x = __shfl_up_sync(0xffffffffu, s, o); if (l >= o) s += x; }
         bcum[i1] = s; bcum[i0] = s - g1; bet[i0] = be0; bet[i1] = be1;
         db[i0] = db[i1] = 0.f; dbe[i0] = dbe[i1] = 0.f;
+        if (l == 0) dgam[0] = 0.f;
     }
     cp_async_wait<0>();
     __syncthreads();
@@ -524,14 +534,14 @@ __global__ void __launch_bounds__(NT) delta_prep_bwd_kernel(PrepBwdArgs a) {
 
     // ---- (1) K K^T -> GK (fp32), T by substitution (threads 0..63) ---------------------------------------------
     {
-        float kk[8][4];
-        zero_acc<8>(kk);
-        warp_gemm<8, D, false, false>(kk, Ks, LD, m0, Ks, LD, 0);
+        float kk[4][4];
+        zero_acc<4>(kk);
+        warp_gemm<4, D, false, false>(kk, Ks, LD, m0, Ks, LD, nc);
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
+        for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
-                const int i = r0 + 8 * hh, j = nt * 8 + c0;
+                const int i = r0 + 8 * hh, j = nc + nt * 8 + c0;
                 const float bi = hh ? b_hi : b_lo;
                 GK[i * LDA + j] = i > j ? __expf(bi - bcum[j]) * kk[nt][2 * hh] : 0.f;
                 GK[i * LDA + j + 1] = i > j + 1 ? __expf(bi - bcum[j + 1]) * kk[nt][2 * hh + 1] : 0.f;
@@ -553,26 +563,26 @@ __global__ void __launch_bounds__(NT) delta_prep_bwd_kernel(PrepBwdArgs a) {
     }
     // ---- (2) dAqk = tril(dO Vn^T), Q K^T again for Aqk; P = scale Gamma . dAqk; decay gradients of Aqk ---------------
     {
-        float da[8][4], qk[8][4];
-        zero_acc<8>(da);
-        zero_acc<8>(qk);
-        warp_gemm<8, D, false, false>(da, Gs, LD, m0, Ns, LD, 0);
-        warp_gemm<8, D, false, false>(qk, Qs, LD, m0, Ks, LD, 0);
+        float da[4][4], qk[4][4];
+        zero_acc<4>(da);
+        zero_acc<4>(qk);
+        warp_gemm<4, D, false, false>(da, Gs, LD, m0, Ns, LD, nc);
+        warp_gemm<4, D, false, false>(qk, Qs, LD, m0, Ks, LD, nc);
         float rs_lo = 0.f, rs_hi = 0.f;
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
+        for (int nt = 0; nt < 4; ++nt) {
             float pv[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int i = r0 + 8 * (e >> 1), j = nt * 8 + c0 + (e & 1);
+                const int i = r0 + 8 * (e >> 1), j = nc + nt * 8 + c0 + (e & 1);
                 const float gam = i >= j ? a.scale * __expf((e >> 1 ? b_hi : b_lo) - bcum[j]) : 0.f;
                 pv[e] = gam * da[nt][e];                              // P_ij
                 const float t_ = pv[e] * qk[nt][e];                   // dAqk_ij Aqk_ij
                 if (e >> 1) rs_hi += t_; else rs_lo += t_;
                 if (i >= j) atomicAdd(&db[j], -t_);
             }
-            *reinterpret_cast<__nv_bfloat162*>(Ps + r0 * LDC + nt * 8 + c0) = __floats2bfloat162_rn(pv[0], pv[1]);
-            *reinterpret_cast<__nv_bfloat162*>(Ps + (r0 + 8) * LDC + nt * 8 + c0) = __floats2bfloat162_rn(pv[2], pv[3]);
+            *reinterpret_cast<__nv_bfloat162*>(Ps + r0 * LDC + nc + nt * 8 + c0) = __floats2bfloat162_rn(pv[0], pv[1]);
+            *reinterpret_cast<__nv_bfloat162*>(Ps + (r0 + 8) * LDC + nc + nt * 8 + c0) = __floats2bfloat162_rn(pv[2], pv[3]);
         }
         rs_lo += __shfl_xor_sync(0xffffffffu, rs_lo, 1); rs_lo += __shfl_xor_sync(0xffffffffu, rs_lo, 2);
         rs_hi += __shfl_xor_sync(0xffffffffu, rs_hi, 1); rs_hi += __shfl_xor_sync(0xffffffffu, rs_hi, 2);
@@ -580,73 +590,101 @@ __global__ void __launch_bounds__(NT) delta_prep_bwd_kernel(PrepBwdArgs a) {
     }
     __syncthreads();                                                   // Ps, Tb complete
     // ---- (3) dq = scale e^b (dO S^T) + P K; its decay gradient <dQd_i, Qd_i> ----------------------------------------
-    float acc_dk[NTD][4];
-    zero_acc<NTD>(acc_dk);
+    float acc_dk[NTH][4];
+    zero_acc<NTH>(acc_dk);
     {
-        float acc[NTD][4];
-        zero_acc<NTD>(acc);
-        warp_gemm<NTD, D, false, false>(acc, Gs, LD, m0, Sb, LD, 0);  // dQd = dO S^T  (S stored [dk][dv] = [n][k])
+        float acc[NTH][4];
+        zero_acc<NTH>(acc);
+        warp_gemm<NTH, D, false, false>(acc, Gs, LD, m0, Sb, LD, nd); // dQd = dO S^T  (S stored [dk][dv] = [n][k])
         const float f_lo = a.scale * __expf(b_lo), f_hi = a.scale * __expf(b_hi);
 #pragma unroll
-        for (int nt = 0; nt < NTD; ++nt) { acc[nt][0] *= f_lo; acc[nt][1] *= f_lo; acc[nt][2] *= f_hi; acc[nt][3] *= f_hi; }
+        for (int nt = 0; nt < NTH; ++nt) { acc[nt][0] *= f_lo; acc[nt][1] *= f_lo; acc[nt][2] *= f_hi; acc[nt][3] *= f_hi; }
         float d_lo, d_hi;
-        row_dot<NTD>(acc, Qs, LD, m0, d_lo, d_hi);                    // = <dQd_i, Qd_i> since acc already carries s e^b
+        row_dot<NTH>(acc, Qs + nd, LD, m0, d_lo, d_hi);               // = <dQd_i, Qd_i> over this warp's columns
         if ((l & 3) == 0) { atomicAdd(&db[r0], d_lo); atomicAdd(&db[r0 + 8], d_hi); }
-        warp_gemm<NTD, C, false, true>(acc, Ps, LDC, m0, Ks, LD, 0);  // + P K
-        store_rows_global<NTD>(acc, a.dq + (((long long)b * a.T + t0) * a.H + h) * D, (long long)a.H * D, m0, valid);
+        warp_gemm<NTH, C, false, true>(acc, Ps, LDC, m0, Ks, LD, nd); // + P K
+        store_rows_global<NTH>(acc, a.dq + (((long long)b * a.T + t0) * a.H + h) * D + nd, (long long)a.H * D, m0, valid);
         // dk += P^T Q
-        warp_gemm<NTD, C, true, true>(acc_dk, Ps, LDC, m0, Qs, LD, 0);
+        warp_gemm<NTH, C, true, true>(acc_dk, Ps, LDC, m0, Qs, LD, nd);
     }
     // ---- (4) dW = -dVn S^T -> shared (in dO's buffer once every warp is done with dO) --------------------------------
     {
-        float acc[NTD][4];
-        zero_acc<NTD>(acc);
-        warp_gemm<NTD, D, false, false>(acc, Us, LD, m0, Sb, LD, 0);
+        float acc[NTH][4];
+        zero_acc<NTH>(acc);
+        warp_gemm<NTH, D, false, false>(acc, Us, LD, m0, Sb, LD, nd);
 #pragma unroll
-        for (int nt = 0; nt < NTD; ++nt)
+        for (int nt = 0; nt < NTH; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[nt][e] = -acc[nt][e];
         __syncthreads();                                               // all reads of dO (Gs) and S_n (Sb) are done
-        store_acc_bf16<NTD>(acc, Gs, LD, m0, 0);                       // Gs now holds dW
+        store_acc_bf16<NTH>(acc, Gs, LD, m0, nd);                      // Gs now holds dW
     }
-    // ---- (5) dS'_n into the state buffer; dKd = Vn dS'^T ------------------------------------------------------------
+    // ---- (5) dS'_n into the state buffer; dgamma = <dS'_n, S_n>; dKd = Vn dS'^T --------------------------------------
+    constexpr int SPT = D * D / 8 / NTB;                               // 16-byte pieces of the state per thread
+    uint4 keep[SPT];
+    if (gated) {
+#pragma unroll
+        for (int i = 0; i < SPT; ++i) {
+            const int idx = threadIdx.x + i * NTB;
+            keep[i] = *reinterpret_cast<const uint4*>(Sb + (idx / (D / 8)) * LD + (idx % (D / 8)) * 8);
+        }
+        __syncthreads();                                               // every thread has its share before the refill
+    }
     load_tile_async<D, D, LD>(Sb, a.dSn + cn * D * D, D, D);
     cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
+    if (gated) {
+        float dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < SPT; ++i) {
+            const int idx = threadIdx.x + i * NTB;
+            const uint4 d = *reinterpret_cast<const uint4*>(Sb + (idx / (D / 8)) * LD + (idx % (D / 8)) * 8);
+            const __nv_bfloat162* x = reinterpret_cast<const __nv_bfloat162*>(&keep[i]);
+            const __nv_bfloat162* y = reinterpret_cast<const __nv_bfloat162*>(&d);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 fx = __bfloat1622float2(x[e]), fy = __bfloat1622float2(y[e]);
+                dot += fx.x * fy.x + fx.y * fy.y;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        if (l == 0) atomicAdd(dgam, dot);
+    }
     {
-        float acc[NTD][4];
-        zero_acc<NTD>(acc);
-        warp_gemm<NTD, D, false, false>(acc, Ns, LD, m0, Sb, LD, 0);  // dKd_j = Vn_j dS'^T
+        float acc[NTH][4];
+        zero_acc<NTH>(acc);
+        warp_gemm<NTH, D, false, false>(acc, Ns, LD, m0, Sb, LD, nd); // dKd_j = Vn_j dS'^T
         const float f_lo = __expf(btot - b_lo), f_hi = __expf(btot - b_hi);
 #pragma unroll
-        for (int nt = 0; nt < NTD; ++nt) { acc[nt][0] *= f_lo; acc[nt][1] *= f_lo; acc[nt][2] *= f_hi; acc[nt][3] *= f_hi; }
+        for (int nt = 0; nt < NTH; ++nt) { acc[nt][0] *= f_lo; acc[nt][1] *= f_lo; acc[nt][2] *= f_hi; acc[nt][3] *= f_hi; }
         float d_lo, d_hi;
-        row_dot<NTD>(acc, Ks, LD, m0, d_lo, d_hi);                    // <dKd_j, Kd_j>
+        row_dot<NTH>(acc, Ks + nd, LD, m0, d_lo, d_hi);               // <dKd_j, Kd_j>
         if ((l & 3) == 0) {
             atomicAdd(&db[r0], -d_lo); atomicAdd(&db[r0 + 8], -d_hi);
             atomicAdd(&db[C - 1], d_lo + d_hi);
         }
 #pragma unroll
-        for (int nt = 0; nt < NTD; ++nt)
+        for (int nt = 0; nt < NTH; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc_dk[nt][e] += acc[nt][e];
     }
     __syncthreads();                                                   // dS'_n no longer needed: Sb becomes Kb
     // ---- (6) dVb = T^T dU: dv, dbeta; then Kb = beta e^b K and Vb = beta V in shared -------------------------------
     {
-        float acc[NTD][4];
-        zero_acc<NTD>(acc);
-        warp_gemm<NTD, C, true, true>(acc, Tb, LDC, m0, Us, LD, 0);
+        float acc[NTH][4];
+        zero_acc<NTH>(acc);
+        warp_gemm<NTH, C, true, true>(acc, Tb, LDC, m0, Us, LD, nd);
         float d_lo, d_hi;
-        row_dot<NTD>(acc, Vs, LD, m0, d_lo, d_hi);                    // <dVb_i, v_i>
+        row_dot<NTH>(acc, Vs + nd, LD, m0, d_lo, d_hi);               // <dVb_i, v_i>
         if ((l & 3) == 0) { atomicAdd(&dbe[r0], d_lo); atomicAdd(&dbe[r0 + 8], d_hi); }
 #pragma unroll
-        for (int nt = 0; nt < NTD; ++nt) { acc[nt][0] *= be_lo; acc[nt][1] *= be_lo; acc[nt][2] *= be_hi; acc[nt][3] *= be_hi; }
-        store_rows_global<NTD>(acc, a.dv + (((long long)b * a.T + t0) * a.H + h) * D, (long long)a.H * D, m0, valid);
+        for (int nt = 0; nt < NTH; ++nt) { acc[nt][0] *= be_lo; acc[nt][1] *= be_lo; acc[nt][2] *= be_hi; acc[nt][3] *= be_hi; }
+        store_rows_global<NTH>(acc, a.dv + (((long long)b * a.T + t0) * a.H + h) * D + nd, (long long)a.H * D, m0, valid);
     }
     __syncthreads();                                                   // every warp has read raw V
-    for (int i = threadIdx.x; i < C * (D / 8); i += NT) {
+    for (int i = threadIdx.x; i < C * (D / 8); i += NTB) {
         const int r = i / (D / 8), c = (i % (D / 8)) * 8;
         const float be = bet[r], fk = be * __expf(bcum[r]);
         Vec<bf16> kx, vx, o1, o2;
@@ -660,49 +698,49 @@ __global__ void __launch_bounds__(NT) delta_prep_bwd_kernel(PrepBwdArgs a) {
     __syncthreads();
     // ---- (7) dKb = T^T dW: its part of dk, dbeta and db -------------------------------------------------------------
     {
-        float acc[NTD][4];
-        zero_acc<NTD>(acc);
-        warp_gemm<NTD, C, true, true>(acc, Tb, LDC, m0, Gs, LD, 0);
+        float acc[NTH][4];
+        zero_acc<NTH>(acc);
+        warp_gemm<NTH, C, true, true>(acc, Tb, LDC, m0, Gs, LD, nd);
         float d_lo, d_hi;
-        row_dot<NTD>(acc, Ks, LD, m0, d_lo, d_hi);                    // <dKb_i, k_i>
+        row_dot<NTH>(acc, Ks + nd, LD, m0, d_lo, d_hi);               // <dKb_i, k_i>
         const float e_lo = __expf(b_lo), e_hi = __expf(b_hi);
         if ((l & 3) == 0) {
             atomicAdd(&dbe[r0], e_lo * d_lo); atomicAdd(&dbe[r0 + 8], e_hi * d_hi);
             atomicAdd(&db[r0], be_lo * e_lo * d_lo); atomicAdd(&db[r0 + 8], be_hi * e_hi * d_hi);
         }
 #pragma unroll
-        for (int nt = 0; nt < NTD; ++nt) {
+        for (int nt = 0; nt < NTH; ++nt) {
             acc_dk[nt][0] += be_lo * e_lo * acc[nt][0]; acc_dk[nt][1] += be_lo * e_lo * acc[nt][1];
             acc_dk[nt][2] += be_hi * e_hi * acc[nt][2]; acc_dk[nt][3] += be_hi * e_hi * acc[nt][3];
         }
     }
     // ---- (8) dT = dW Kb^T + dU Vb^T -> X1;  X2 = T^T dT;  dA = -(X2 T^T), strictly lower ------------------------------
     {
-        float acc[8][4];
-        zero_acc<8>(acc);
-        warp_gemm<8, D, false, false>(acc, Gs, LD, m0, Sb, LD, 0);
-        warp_gemm<8, D, false, false>(acc, Us, LD, m0, Vs, LD, 0);
-        store_acc_bf16<8>(acc, X1, LDC, m0, 0);
+        float acc[4][4];
+        zero_acc<4>(acc);
+        warp_gemm<4, D, false, false>(acc, Gs, LD, m0, Sb, LD, nc);
+        warp_gemm<4, D, false, false>(acc, Us, LD, m0, Vs, LD, nc);
+        store_acc_bf16<4>(acc, X1, LDC, m0, nc);
     }
     __syncthreads();
     {
-        float acc[8][4];
-        zero_acc<8>(acc);
-        warp_gemm<8, C, true, true>(acc, Tb, LDC, m0, X1, LDC, 0);
-        store_acc_bf16<8>(acc, X2, LDC, m0, 0);
+        float acc[4][4];
+        zero_acc<4>(acc);
+        warp_gemm<4, C, true, true>(acc, Tb, LDC, m0, X1, LDC, nc);
+        store_acc_bf16<4>(acc, X2, LDC, m0, nc);
     }
     __syncthreads();
     {
-        float acc[8][4];
-        zero_acc<8>(acc);
-        warp_gemm<8, C, false, false>(acc, X2, LDC, m0, Tb, LDC, 0);  // (X2 T^T)_ij = sum_k X2_ik T_jk
+        float acc[4][4];
+        zero_acc<4>(acc);
+        warp_gemm<4, C, false, false>(acc, X2, LDC, m0, Tb, LDC, nc); // (X2 T^T)_ij = sum_k X2_ik T_jk
         float rb_lo = 0.f, rb_hi = 0.f, rd_lo = 0.f, rd_hi = 0.f;
 #pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
+        for (int nt = 0; nt < 4; ++nt) {
             float mv[4];
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int i = r0 + 8 * (e >> 1), j = nt * 8 + c0 + (e & 1);
+                const int i = r0 + 8 * (e >> 1), j = nc + nt * 8 + c0 + (e & 1);
                 const float dA = i > j ? -acc[nt][e] : 0.f;
                 const float gk = GK[i * LDA + j];                      // Gamma_ij (k_i.k_j), zero on and above the diagonal
                 const float be = (e >> 1) ? be_hi : be_lo;
@@ -712,8 +750,8 @@ __global__ void __launch_bounds__(NT) delta_prep_bwd_kernel(PrepBwdArgs a) {
                 if (i > j) atomicAdd(&db[j], -t2);
                 mv[e] = i > j ? dA * be * __expf(((e >> 1) ? b_hi : b_lo) - bcum[j]) : 0.f;      // M_ij
             }
-            *reinterpret_cast<__nv_bfloat162*>(Ps + r0 * LDC + nt * 8 + c0) = __floats2bfloat162_rn(mv[0], mv[1]);
-            *reinterpret_cast<__nv_bfloat162*>(Ps + (r0 + 8) * LDC + nt * 8 + c0) = __floats2bfloat162_rn(mv[2], mv[3]);
+            *reinterpret_cast<__nv_bfloat162*>(Ps + r0 * LDC + nc + nt * 8 + c0) = __floats2bfloat162_rn(mv[0], mv[1]);
+            *reinterpret_cast<__nv_bfloat162*>(Ps + (r0 + 8) * LDC + nc + nt * 8 + c0) = __floats2bfloat162_rn(mv[2], mv[3]);
         }
 #pragma unroll
         for (int o = 1; o <= 2; o <<= 1) {
@@ -727,15 +765,15 @@ __global__ void __launch_bounds__(NT) delta_prep_bwd_kernel(PrepBwdArgs a) {
     }
     __syncthreads();                                                   // Ps holds M
     // ---- (9) dk += M K + M^T K; store ---------------------------------------------------------------------------------
-    warp_gemm<NTD, C, false, true>(acc_dk, Ps, LDC, m0, Ks, LD, 0);
-    warp_gemm<NTD, C, true, true>(acc_dk, Ps, LDC, m0, Ks, LD, 0);
-    store_rows_global<NTD>(acc_dk, a.dk + (((long long)b * a.T + t0) * a.H + h) * D, (long long)a.H * D, m0, valid);
+    warp_gemm<NTH, C, false, true>(acc_dk, Ps, LDC, m0, Ks, LD, nd);
+    warp_gemm<NTH, C, true, true>(acc_dk, Ps, LDC, m0, Ks, LD, nd);
+    store_rows_global<NTH>(acc_dk, a.dk + (((long long)b * a.T + t0) * a.H + h) * D + nd, (long long)a.H * D, m0, valid);
     __syncthreads();                                                   // all contributions to db / dbeta are in
     // ---- (10) dbeta; dg_s = sum_{i >= s} db_i (+ dgamma gamma on the last position) -----------------------------------
     if (w == 0) {
         const int i0 = 2 * l, i1 = 2 * l + 1;
         float x0 = db[i0], x1 = db[i1];
-        if (a.dgamma != nullptr && l == 31) x1 += a.dgamma[cn] * __expf(btot);
+        if (gated && l == 31) x1 += dgam[0] * __expf(btot);             // gamma = e^{b_C}: d b_C += dgamma gamma
         float s = x0 + x1;                                             // suffix sums over lane pairs
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) { const float y = __shfl_down_sync(0xffffffffu, s, o); if (l + o < 32) s += y; }
@@ -746,7 +784,7 @@ __global__ void __launch_bounds__(NT) delta_prep_bwd_kernel(PrepBwdArgs a) {
 }
 
 template <int D> constexpr size_t prep_bwd_smem() {
-    return (size_t)(6 * C * (D + 8) + D * (D + 8) + 4 * C * (C + 8)) * 2 + (size_t)(C * (C + 1) + 4 * C) * 4;
+    return (size_t)(6 * C * (D + 8) + D * (D + 8) + 4 * C * (C + 8)) * 2 + (size_t)(C * (C + 1) + 4 * C + 4) * 4;
 }
 
 template <int D> constexpr size_t prep_smem() {
@@ -800,11 +838,11 @@ LMOE_API int lmoe_delta_prepare_bwd(int D, const dr::PrepBwdArgs* ap, cudaStream
     if (D == 128) {
         cudaError_t e = cudaFuncSetAttribute(dr::delta_prep_bwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dr::prep_bwd_smem<128>());
         if (e != cudaSuccess) return (int)e;
-        dr::delta_prep_bwd_kernel<128><<<grid, dr::NT, dr::prep_bwd_smem<128>(), st>>>(a);
+        dr::delta_prep_bwd_kernel<128><<<grid, dr::NTB, dr::prep_bwd_smem<128>(), st>>>(a);
     } else if (D == 64) {
         cudaError_t e = cudaFuncSetAttribute(dr::delta_prep_bwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dr::prep_bwd_smem<64>());
         if (e != cudaSuccess) return (int)e;
-        dr::delta_prep_bwd_kernel<64><<<grid, dr::NT, dr::prep_bwd_smem<64>(), st>>>(a);
+        dr::delta_prep_bwd_kernel<64><<<grid, dr::NTB, dr::prep_bwd_smem<64>(), st>>>(a);
     } else return -2;
     return (int)cudaGetLastError();
 }

@@ -25,6 +25,14 @@ def close(a, b, rtol, atol, name=""):
     assert torch.allclose(a, b, rtol=rtol, atol=atol), f"{name}: max abs err {err:.4e} (ref max {ref:.4e})"
 
 
+def rel_close(a, b, tol, name=""):
+    """Relative Frobenius error: a reduced gradient (a sum over rows) that lost one block of partial sums fails this
+    even where an absolute tolerance sized for bf16 sums would let it through."""
+    a, b = a.float(), b.float()
+    rel = ((a - b).norm() / b.norm().clamp_min(1e-12)).item()
+    assert rel < tol, f"{name}: relative error {rel:.3e} (limit {tol:.1e})"
+
+
 def grads(fn, inputs, gout):
     ins = [t.detach().clone().requires_grad_(True) for t in inputs]
     out = fn(*ins)
@@ -56,7 +64,7 @@ def test_rms_norm(N, rows, residual):
         (y2,), gr_ = grads(f_r, [x.float(), w.float()], gy.float())
     close(y, y2, 2e-2, 2e-2, "y")
     close(gk[0], gr_[0], 3e-2, 3e-2, "dx")
-    close(gk[-1], gr_[-1], 3e-2, 0.02 * math.sqrt(rows), "dw")
+    rel_close(gk[-1], gr_[-1], 1e-2, "dw")
 
 
 @pytest.mark.parametrize("D", [64, 128])
@@ -79,7 +87,7 @@ def test_head_norm_gate(D, norm):
     close(gk[0], gr[0], 3e-2, 3e-2, "do")
     close(gk[2], gr[2], 3e-2, 3e-2, "dgate")
     if norm:
-        close(gk[1], gr[1], 3e-2, 0.5, "dw")
+        rel_close(gk[1], gr[1], 1e-2, "dw")
 
 
 def test_gated_rms_norm():
@@ -94,7 +102,7 @@ def test_gated_rms_norm():
     close(y, y2, 2e-2, 2e-2, "y")
     close(gk[0], gr[0], 3e-2, 3e-2, "dx")
     close(gk[1], gr[1], 3e-2, 3e-2, "dz")
-    close(gk[2], gr[2], 3e-2, 0.3, "dw")
+    rel_close(gk[2], gr[2], 1e-2, "dw")
 
 
 def test_swiglu_l2norm_rope():
@@ -153,8 +161,8 @@ def test_causal_conv1d(init):
     (y2,), gr = grads(f_r, [t.float() for t in ins], gy.float())
     close(y, y2, 2e-2, 2e-2, "y")
     close(gk[0], gr[0], 3e-2, 3e-2, "dx")
-    close(gk[1], gr[1], 3e-2, 0.5, "dw")
-    close(gk[2], gr[2], 3e-2, 0.5, "db")
+    rel_close(gk[1], gr[1], 1e-2, "dw")
+    rel_close(gk[2], gr[2], 1e-2, "db")
     if init:
         close(gk[3], gr[3], 3e-2, 3e-2, "dinit")
         close(ops.causal_conv1d(x, w, b, "silu", s)[1], R.causal_conv1d(x, w, b, "silu", s)[1], 0, 0, "tail")

@@ -303,3 +303,28 @@ def test_mlp_swiglu_autograd():
     yr.backward(gy.float())
     rel = lambda a, b: ((a.float() - b).norm() / b.norm()).item()
     assert rel(y, yr) < 1e-2 and rel(x.grad, xr.grad) < 2e-2 and rel(w1.grad, w1r.grad) < 2e-2 and rel(w2.grad, w2r.grad) < 2e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 2048, 2048), (8, 6144, 2048), (5, 2056, 8192), (16, 128256, 2048), (11, 40, 64)])
+def test_skinny_gemm_for_decode_rows(M, N, K):
+    """The weight-streaming GEMM of one-token decode steps (up to 16 rows) against fp32 matmul; also through
+    ``ops.linear`` without autograd, which must route to it."""
+    from linear_moe_b200 import ops
+    from linear_moe_b200.ops import cuda as K_
+    torch.manual_seed(M + N)
+    dev = torch.device("cuda", 0)
+    x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=dev) / K ** 0.5).to(torch.bfloat16)
+    ref = x.float() @ w.float().t()
+    y = K_.linear_skinny(x, w)
+    torch.cuda.synchronize()
+    rel = ((y.float() - ref).norm() / ref.norm()).item()
+    assert rel < 5e-3, rel
+    K_.reset_launch_count()
+    with torch.no_grad():
+        y2 = ops.linear(x.view(1, M, K), w)
+    assert K_.reset_launch_count() == 1 and y2.shape == (1, M, N)
+    assert torch.equal(y2.view(M, N), y)                       # deterministic: no atomics
+    # with autograd on a parameter the regular (differentiable) path runs instead
+    wp = w.clone().requires_grad_(True)
+    assert not K_._skinny_ok(x, wp)
