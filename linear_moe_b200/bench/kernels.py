@@ -116,6 +116,32 @@ def bench_gemm_dense(size):
     gemm.check_error()
 
 
+def bench_skinny(size):
+    """Linears of a one-token decode step (batch 8): the weight-streaming kernel against the library call.  Each
+    measurement loops once over enough copies of the weight (>= 512 MB) that no call finds its weight in L2, inside one
+    pair of events, so launch gaps of a few microseconds do not dominate kernels of a few microseconds."""
+    from ..ops import cuda as K
+    dev = torch.device("cuda", 0)
+    M = 8
+    shapes = [("qkv", 6144, 2048), ("gate / out proj", 2048, 2048), ("fc1", 16384, 2048), ("fc2", 2048, 8192),
+              ("LM head", 128256, 2048)]
+    for name, N, Kd in shapes:
+        x = torch.randn(M, Kd, device=dev).bfloat16()
+        n = max(2, (512 << 20) // (N * Kd * 2) + 1)
+        ws = [(torch.randn(N, Kd, device=dev) / Kd ** 0.5).bfloat16() for _ in range(n)]
+
+        def loop(fn):
+            def run():
+                for w_ in ws:
+                    fn(x, w_)
+            return run
+        with torch.no_grad():
+            for label, fn in (("gemm_skinny", K.linear_skinny), ("cuBLAS     ", torch.nn.functional.linear)):
+                ms = timeit(loop(fn), iters=5) / n
+                report(f"{label} {name} {M}x{N}x{Kd}", ms, bytes_=N * Kd * 2)
+        del ws
+
+
 def bench_lsm(size):
     from .. import ops
     dev = torch.device("cuda", 0)
@@ -331,6 +357,8 @@ def main():
         bench_gemm(a.size)
     if a.kernel in ("gemm_dense", "all"):
         bench_gemm_dense(a.size)
+    if a.kernel in ("skinny", "all"):
+        bench_skinny(a.size)
     if a.kernel in ("lsm", "all"):
         bench_lsm(a.size)
     if a.kernel in ("flash", "all"):

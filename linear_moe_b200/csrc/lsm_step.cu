@@ -33,9 +33,15 @@ lsm_scalar_step_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     const float* si = s_in == nullptr ? nullptr : s_in + (long long)bh * D * D;
     float* so = s_out + (long long)bh * D * D;
     float acc = 0.f;
-#pragma unroll 8
-    for (int i = r; i < D; i += 4) {
-        const float s = (si == nullptr ? 0.f : si[i * D + j] * dec[i]) + ks[i] * vj;
+    // all D/4 loads of a thread are issued before the first use: the step is one pass over the state, and with a few
+    // loads in flight per thread it is bound by memory latency instead of bandwidth
+    float st[D / 4];
+#pragma unroll
+    for (int t = 0; t < D / 4; ++t) st[t] = si == nullptr ? 0.f : __ldcs(si + (r + 4 * t) * D + j);
+#pragma unroll
+    for (int t = 0; t < D / 4; ++t) {
+        const int i = r + 4 * t;
+        const float s = st[t] * dec[i] + ks[i] * vj;
         so[i * D + j] = s;
         acc = fmaf(qs[i], s, acc);
     }
