@@ -49,6 +49,7 @@ struct Params {
     int band;          // tile rows per band of the tile order
     int f_half;        // epi 1: F (rows of the gate block of B)
     int* err;
+    const bf16* bias;  // out mode 0 without epilogue function: [N] added to every row, or null
 };
 
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int c0, int c1) {
@@ -70,6 +71,23 @@ __device__ __forceinline__ void decode(const Params& p, int t, int tiles_m, int 
     const int gm = min(p.band, tiles_m - b * p.band);
     tm = b * p.band + r % gm;
     tn = r / gm;
+}
+
+// v[i] += bias[i] for 32 consecutive columns (the same 64 bytes for every lane: broadcast loads); columns >= n_left skipped
+__device__ __forceinline__ void add_bias32(uint32_t (&v)[32], const bf16* bias, int n_left) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        if (g * 8 < n_left) {                                           // N is a multiple of 8
+            const uint4 b = __ldg(reinterpret_cast<const uint4*>(bias) + g);
+            const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(b2[i]);
+                v[g * 8 + 2 * i] = __float_as_uint(__uint_as_float(v[g * 8 + 2 * i]) + f.x);
+                v[g * 8 + 2 * i + 1] = __float_as_uint(__uint_as_float(v[g * 8 + 2 * i + 1]) + f.y);
+            }
+        }
+    }
 }
 
 // one lane's 32 fp32 values -> 64 bytes (bf16) of its row in a swizzled staging slab; `part` = which half of the 128-byte row
@@ -317,6 +335,10 @@ gemm_dense_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
                     if (lane == 0) bulk_wait_read<1>();           // the store that last used this slab has read it
                     __syncwarp();
                     tmem_ld_wait();
+                    if (p.bias != nullptr) {
+                        add_bias32(v0, p.bias + col_base + c, p.N - (col_base + c));
+                        add_bias32(v1, p.bias + col_base + c + 32, p.N - (col_base + c + 32));
+                    }
                     stage_bf16(s, lane, 0, v0); stage_bf16(s, lane, 1, v1);
                     fence_async_smem();
                     __syncwarp();
@@ -407,9 +429,10 @@ using namespace lmoe::gd;
 //   out_mode 0: C bf16;  1: C fp32 (overwrite);  2: C fp32 += (reduce-add performed by the memory system).
 //   band: tile rows per band of the tile order (0 = default).
 // Every pitch and the contiguous extent of every matrix must be a multiple of 8 elements (16-byte TMA rule).
-LMOE_API int lmoe_gemm_dense(const void* A, int lda, int a_mn, const void* B, int ldb, int b_mn, void* C, int ldc, int out_mode,
-                             int M, int N, int K, int band, int* err, int num_sms, cudaStream_t st) {
+static int gemm_dense_impl(const void* A, int lda, int a_mn, const void* B, int ldb, int b_mn, void* C, int ldc, int out_mode,
+                           int M, int N, int K, int band, int* err, int num_sms, cudaStream_t st, const void* bias) {
     if (M <= 0 || N <= 0 || K <= 0) return -1;
+    if (bias != nullptr && (out_mode != 0 || ((uintptr_t)bias & 15))) return -1;
     if (lda % 8 || ldb % 8 || (a_mn ? M : K) % 8 || (b_mn ? N : K) % 8) return -1;
     if (out_mode == 0 ? (ldc % 8 || N % 8) : (ldc % 4 || N % 4)) return -1;
     if (((uintptr_t)A | (uintptr_t)B | (uintptr_t)C) & 15) return -2;
@@ -422,7 +445,7 @@ LMOE_API int lmoe_gemm_dense(const void* A, int lda, int a_mn, const void* B, in
                        : make_map_any(&mc, C, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, M, N, ldc, 32, 32);
     if (rc) return rc;
     Params p;
-    p.M = M; p.N = N; p.K = K; p.band = band > 0 ? band : 8; p.f_half = 0; p.err = err;
+    p.M = M; p.N = N; p.K = K; p.band = band > 0 ? band : 8; p.f_half = 0; p.err = err; p.bias = (const bf16*)bias;
 #define LMOE_GD_OUT(AMN, BMN)                                                                          \
     (out_mode == 0 ? launch<AMN, BMN, 0, 0>(ma, mb, mc, mc, 0, p, num_sms, st)                         \
    : out_mode == 1 ? launch<AMN, BMN, 1, 0>(ma, mb, mc, mc, 0, p, num_sms, st)                         \
@@ -432,6 +455,17 @@ LMOE_API int lmoe_gemm_dense(const void* A, int lda, int a_mn, const void* B, in
     if (a_mn && b_mn) return LMOE_GD_OUT(true, true);
     return LMOE_GD_OUT(true, false);
 #undef LMOE_GD_OUT
+}
+
+LMOE_API int lmoe_gemm_dense(const void* A, int lda, int a_mn, const void* B, int ldb, int b_mn, void* C, int ldc, int out_mode,
+                             int M, int N, int K, int band, int* err, int num_sms, cudaStream_t st) {
+    return gemm_dense_impl(A, lda, a_mn, B, ldb, b_mn, C, ldc, out_mode, M, N, K, band, err, num_sms, st, nullptr);
+}
+
+// C[M,N] (bf16) = A * B + bias[N] (bf16, 16-byte aligned), the bias added to the fp32 accumulator in the epilogue.
+LMOE_API int lmoe_gemm_dense_bias(const void* A, int lda, int a_mn, const void* B, int ldb, int b_mn, void* C, int ldc,
+                                  const void* bias, int M, int N, int K, int band, int* err, int num_sms, cudaStream_t st) {
+    return gemm_dense_impl(A, lda, a_mn, B, ldb, b_mn, C, ldc, 0, M, N, K, band, err, num_sms, st, bias);
 }
 
 // act[M,F] = silu(x Wg^T) * (x Wu^T) with W = [Wg ; Wu] of shape [2F, K] (pitch ldw); if Y != null the pre-activations
@@ -454,7 +488,7 @@ LMOE_API int lmoe_gemm_dense_swiglu(const void* X, int ldx, const void* W, int l
         if (rc) return rc;
     }
     Params p;
-    p.M = M; p.N = F; p.K = K; p.band = band > 0 ? band : 8; p.f_half = F; p.err = err;
+    p.M = M; p.N = F; p.K = K; p.band = band > 0 ? band : 8; p.f_half = F; p.err = err; p.bias = nullptr;
     return launch<false, false, 0, 1>(ma, mb, mc, my, Y != nullptr ? 1 : 0, p, num_sms, st);
 }
 
@@ -475,6 +509,6 @@ LMOE_API int lmoe_gemm_dense_dswiglu(const void* dY, int lddy, const void* W2, i
     rc = make_map_any(&my, pre, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, 2 * F, ldpre, 64, 32);
     if (rc) return rc;
     Params p;
-    p.M = M; p.N = F; p.K = H; p.band = band > 0 ? band : 8; p.f_half = F; p.err = err;
+    p.M = M; p.N = F; p.K = H; p.band = band > 0 ? band : 8; p.f_half = F; p.err = err; p.bias = nullptr;
     return launch<false, true, 0, 2>(ma, mb, mc, my, 1, p, num_sms, st);
 }

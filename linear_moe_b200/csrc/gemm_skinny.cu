@@ -15,13 +15,32 @@ namespace sk {
 
 __device__ __forceinline__ uint4 ld_stream(const bf16* p) { return __ldcs(reinterpret_cast<const uint4*>(p)); }
 
-template <int NTILES>   // 1: M <= 8, 2: M <= 16
+__device__ __forceinline__ uint32_t sk_cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void sk_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// store a float into the shared memory of CTA `rank` of the cluster, at the address `p` has in this CTA
+__device__ __forceinline__ void st_cluster_f32(float* p, uint32_t rank, float v) {
+    uint32_t local = (uint32_t)__cvta_generic_to_shared(p), remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" :: "r"(remote), "f"(v) : "memory");
+}
+
+// NTILES 1: M <= 8, 2: M <= 16.  KS: CTAs of a cluster that split K between them (for matrices with few rows, so that
+// every SM streams a piece of W); their partial tiles meet in the shared memory of the cluster's first CTA.
+template <int NTILES, int KS>
 __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict__ x, long long ldx, const bf16* __restrict__ W,
                                                           long long ldw, bf16* __restrict__ y, long long ldy, int M, int N, int K) {
     __shared__ float red[8][NTILES][32][4];
+    __shared__ float cred[KS][NTILES][32][4];
     const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
     const int g = l >> 2, q = l & 3;
-    const int row_lo = blockIdx.x * 16 + g, row_hi = row_lo + 8;
+    const uint32_t crank = KS > 1 ? sk_cluster_rank() : 0;
+    const int row_lo = (blockIdx.x / KS) * 16 + g, row_hi = row_lo + 8;
     const bool lo_ok = row_lo < N, hi_ok = row_hi < N;
     const bf16* w_lo = W + (long long)(lo_ok ? row_lo : 0) * ldw + q * 8;
     const bf16* w_hi = W + (long long)(hi_ok ? row_hi : 0) * ldw + q * 8;
@@ -36,8 +55,10 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
 #pragma unroll
     for (int t = 0; t < NTILES; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
     const uint4 zero = make_uint4(0, 0, 0, 0);
-#pragma unroll 4
-    for (int k0 = w * 32; k0 < K; k0 += 256) {
+    const int kslice = K / KS;                                           // a multiple of 32 (checked by the launcher)
+    const int k_end = (int)(crank + 1) * kslice;
+#pragma unroll 8
+    for (int k0 = (int)crank * kslice + w * 32; k0 < k_end; k0 += 256) {
         const uint4 a_lo = lo_ok ? ld_stream(w_lo + k0) : zero;
         const uint4 a_hi = hi_ok ? ld_stream(w_hi + k0) : zero;
         const uint32_t f1[4] = {a_lo.x, a_hi.x, a_lo.y, a_hi.y};
@@ -54,14 +75,32 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
 #pragma unroll
         for (int e = 0; e < 4; ++e) red[w][t][l][e] = acc[t][e];
     __syncthreads();
+    float s[4] = {0.f, 0.f, 0.f, 0.f};
     if (w < NTILES) {
-        const int t = w;
-        float s[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int i = 0; i < 8; ++i)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) s[e] += red[i][t][l][e];
-        const int n0 = 8 * t + 2 * q;                                   // batch rows n0, n0 + 1
+            for (int e = 0; e < 4; ++e) s[e] += red[i][w][l][e];
+    }
+    if (KS > 1) {
+        // the CTA's partial tile goes to slot `crank` of the first CTA; it adds the slots in rank order (deterministic)
+        if (w < NTILES) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) st_cluster_f32(&cred[crank][w][l][e], 0, s[e]);
+        }
+        sk_cluster_sync();
+        if (crank != 0) return;
+        if (w < NTILES) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                s[e] = 0.f;
+#pragma unroll
+                for (int i = 0; i < KS; ++i) s[e] += cred[i][w][l][e];
+            }
+        }
+    }
+    if (w < NTILES) {
+        const int n0 = 8 * w + 2 * q;                                   // batch rows n0, n0 + 1
         if (n0 < M) {
             if (lo_ok) y[(long long)n0 * ldy + row_lo] = __float2bfloat16(s[0]);
             if (hi_ok) y[(long long)n0 * ldy + row_hi] = __float2bfloat16(s[2]);
@@ -71,6 +110,28 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
             if (hi_ok) y[(long long)(n0 + 1) * ldy + row_hi] = __float2bfloat16(s[3]);
         }
     }
+}
+
+template <int NTILES, int KS>
+static int launch_skinny(const bf16* x, long long ldx, const bf16* W, long long ldw, bf16* y, long long ldy, int M, int N, int K,
+                         cudaStream_t st) {
+    const int blocks = ((N + 15) / 16) * KS;
+    if (KS == 1) {
+        gemm_skinny_kernel<NTILES, 1><<<blocks, 256, 0, st>>>(x, ldx, W, ldw, y, ldy, M, N, K);
+        return (int)cudaGetLastError();
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(blocks);
+    cfg.blockDim = dim3(256);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = KS;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<NTILES, KS>, x, ldx, W, ldw, y, ldy, M, N, K);
 }
 
 }  // namespace sk
@@ -83,10 +144,17 @@ LMOE_API int lmoe_gemm_skinny(const void* x, long long ldx, const void* W, long 
     using namespace lmoe;
     if (M <= 0 || M > 16 || N <= 0 || K <= 0 || K % 32 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return -1;
     if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(W)) & 15) return -1;
-    const int grid = (N + 15) / 16;
-    if (M <= 8)
-        sk::gemm_skinny_kernel<1><<<grid, 256, 0, st>>>((const bf16*)x, ldx, (const bf16*)W, ldw, (bf16*)y, ldy, M, N, K);
-    else
-        sk::gemm_skinny_kernel<2><<<grid, 256, 0, st>>>((const bf16*)x, ldx, (const bf16*)W, ldw, (bf16*)y, ldy, M, N, K);
-    return (int)cudaGetLastError();
+    const bf16 *xb = (const bf16*)x, *Wb = (const bf16*)W;
+    bf16* yb = (bf16*)y;
+    // few row blocks: four CTAs of a cluster split K so that the whole GPU streams W
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) sms = 148;
+    }
+    const bool split = (N + 15) / 16 < 2 * sms && K % 128 == 0;
+    if (M <= 8) return split ? sk::launch_skinny<1, 4>(xb, ldx, Wb, ldw, yb, ldy, M, N, K, st)
+                             : sk::launch_skinny<1, 1>(xb, ldx, Wb, ldw, yb, ldy, M, N, K, st);
+    return split ? sk::launch_skinny<2, 4>(xb, ldx, Wb, ldw, yb, ldy, M, N, K, st)
+                 : sk::launch_skinny<2, 1>(xb, ldx, Wb, ldw, yb, ldy, M, N, K, st);
 }

@@ -444,39 +444,98 @@ struct DgArgs {
     float* segsum;        // [B*H, nseg, D]
     int B, T, H, D, nseg;
 };
-__device__ __forceinline__ float dg_term(const DgArgs& a, int b, int t, int h, int d) {
-    const float q = __bfloat162float(a.q[b * a.qs_b + (int64_t)t * a.qs_t + h * a.qs_h + d]);
-    const float k = __bfloat162float(a.k[b * a.ks_b + (int64_t)t * a.ks_t + h * a.ks_h + d]);
-    const float dq = __bfloat162float(a.dq[b * a.dqs_b + (int64_t)t * a.dqs_t + h * a.dqs_h + d]);
-    const float dk = __bfloat162float(a.dk[b * a.dks_b + (int64_t)t * a.dks_t + h * a.dks_h + d]);
-    return q * dq - k * dk;
+// q*dq - k*dk for eight consecutive channels of one token (16-byte loads; the pitches are multiples of 8 elements)
+__device__ __forceinline__ void dg_term8(const DgArgs& a, int b, int t, int h, int d, float (&o)[8]) {
+    const uint4 q4 = __ldg(reinterpret_cast<const uint4*>(a.q + b * a.qs_b + (int64_t)t * a.qs_t + h * a.qs_h + d));
+    const uint4 k4 = __ldg(reinterpret_cast<const uint4*>(a.k + b * a.ks_b + (int64_t)t * a.ks_t + h * a.ks_h + d));
+    const uint4 dq4 = __ldg(reinterpret_cast<const uint4*>(a.dq + b * a.dqs_b + (int64_t)t * a.dqs_t + h * a.dqs_h + d));
+    const uint4 dk4 = __ldg(reinterpret_cast<const uint4*>(a.dk + b * a.dks_b + (int64_t)t * a.dks_t + h * a.dks_h + d));
+    const __nv_bfloat162* q2 = reinterpret_cast<const __nv_bfloat162*>(&q4);
+    const __nv_bfloat162* k2 = reinterpret_cast<const __nv_bfloat162*>(&k4);
+    const __nv_bfloat162* dq2 = reinterpret_cast<const __nv_bfloat162*>(&dq4);
+    const __nv_bfloat162* dk2 = reinterpret_cast<const __nv_bfloat162*>(&dk4);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 fq = __bfloat1622float2(q2[i]), fk = __bfloat1622float2(k2[i]);
+        const float2 fdq = __bfloat1622float2(dq2[i]), fdk = __bfloat1622float2(dk2[i]);
+        o[2 * i] = fq.x * fdq.x - fk.x * fdk.x;
+        o[2 * i + 1] = fq.y * fdq.y - fk.y * fdk.y;
+    }
 }
-// grid (nseg, B*H), D threads
-__global__ void gla_dg_segsum_kernel(DgArgs a) {
-    const int seg = blockIdx.x, bh = blockIdx.y, b = bh / a.H, h = bh % a.H, d = threadIdx.x;
-    const int t0 = seg * DG_SEG, t1 = min(a.T, t0 + DG_SEG);
-    float s = 0.f;
-    for (int t = t0; t < t1; ++t) s += dg_term(a, b, t, h, d);
-    a.segsum[((int64_t)bh * a.nseg + seg) * a.D + d] = s;
+
+// Both kernels: grid (nseg, B*H), 256 threads.  D / 8 threads cover the channels of one token with 16-byte accesses;
+// the 256 / (D / 8) thread groups each own a contiguous run of DG_SEG / groups tokens of the segment.
+// 1. per-segment sums of the terms
+__global__ void __launch_bounds__(256) gla_dg_segsum_kernel(DgArgs a) {
+    __shared__ float part[32][129];                                    // [group][channel], D <= 128
+    const int seg = blockIdx.x, bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
+    const int tpr = a.D / 8, groups = 256 / tpr, L = DG_SEG / groups;
+    const int grp = threadIdx.x / tpr, d = (threadIdx.x % tpr) * 8;
+    const int t0 = seg * DG_SEG + grp * L, t1 = min(a.T, t0 + L);
+    float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+    for (int t = t0; t < t1; ++t) {
+        float o[8];
+        dg_term8(a, b, t, h, d, o);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s[i] += o[i];
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) part[grp][d + i] = s[i];
+    __syncthreads();
+    if (threadIdx.x < a.D) {
+        float tot = 0.f;
+        for (int g2 = 0; g2 < groups; ++g2) tot += part[g2][threadIdx.x];
+        a.segsum[((int64_t)bh * a.nseg + seg) * a.D + threadIdx.x] = tot;
+    }
 }
-__global__ void gla_dg_scan_kernel(DgArgs a) {
-    const int seg = blockIdx.x, bh = blockIdx.y, b = bh / a.H, h = bh % a.H, d = threadIdx.x;
-    float run = 0.f;
-    for (int s2 = a.nseg - 1; s2 > seg; --s2) run += a.segsum[((int64_t)bh * a.nseg + s2) * a.D + d];
-    const int t0 = seg * DG_SEG, t1 = min(a.T, t0 + DG_SEG);
+// 2. running suffix sums: later segments from the table, later token runs of this segment through shared memory, then
+//    the run's own tokens from last to first (re-read; they are in L2 from the first pass of this CTA)
+__global__ void __launch_bounds__(256) gla_dg_scan_kernel(DgArgs a) {
+    __shared__ float part[32][129];
+    const int seg = blockIdx.x, bh = blockIdx.y, b = bh / a.H, h = bh % a.H;
+    const int tpr = a.D / 8, groups = 256 / tpr, L = DG_SEG / groups;
+    const int grp = threadIdx.x / tpr, d = (threadIdx.x % tpr) * 8;
+    const int t0 = seg * DG_SEG + grp * L, t1 = min(a.T, t0 + L);
+    float s[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+    for (int t = t0; t < t1; ++t) {
+        float o[8];
+        dg_term8(a, b, t, h, d, o);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s[i] += o[i];
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) part[grp][d + i] = s[i];
+    __syncthreads();
+    float run[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float r = 0.f;
+        for (int s2 = a.nseg - 1; s2 > seg; --s2) r += a.segsum[((int64_t)bh * a.nseg + s2) * a.D + d + i];
+        for (int g2 = groups - 1; g2 > grp; --g2) r += part[g2][d + i];
+        run[i] = r;
+    }
     for (int t = t1 - 1; t >= t0; --t) {
-        run += dg_term(a, b, t, h, d);
-        a.dg[(((int64_t)b * a.T + t) * a.H + h) * a.D + d] = run;
+        float o[8];
+        dg_term8(a, b, t, h, d, o);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) run[i] += o[i];
+        float4* dst = reinterpret_cast<float4*>(a.dg + (((int64_t)b * a.T + t) * a.H + h) * a.D + d);
+        dst[0] = make_float4(run[0], run[1], run[2], run[3]);
+        dst[1] = make_float4(run[4], run[5], run[6], run[7]);
     }
 }
 }  // namespace lmoe
 
 LMOE_API int lmoe_gla_dg(const lmoe::DgArgs* ap, cudaStream_t st) {
     lmoe::DgArgs a = *ap;
-    if (a.D > 1024 || a.T <= 0) return -1;
+    if ((a.D != 64 && a.D != 128) || a.T <= 0) return -1;
+    if ((a.qs_t | a.qs_h | a.qs_b | a.ks_t | a.ks_h | a.ks_b | a.dqs_t | a.dqs_h | a.dqs_b | a.dks_t | a.dks_h | a.dks_b) % 8) return -1;
+    if (((uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.dq | (uintptr_t)a.dk) & 15) return -1;
     a.nseg = (a.T + lmoe::DG_SEG - 1) / lmoe::DG_SEG;
     dim3 grid(a.nseg, a.B * a.H);
-    lmoe::gla_dg_segsum_kernel<<<grid, a.D, 0, st>>>(a);
-    lmoe::gla_dg_scan_kernel<<<grid, a.D, 0, st>>>(a);
+    lmoe::gla_dg_segsum_kernel<<<grid, 256, 0, st>>>(a);
+    lmoe::gla_dg_scan_kernel<<<grid, 256, 0, st>>>(a);
     return (int)cudaGetLastError();
 }

@@ -307,6 +307,50 @@ __global__ void moe_pull_kernel(MoeArgs a) {
     }
 }
 
+// Gradient of the routing probabilities in the combine: d_probs[t, j] = <rows[t * k + j, :], d_out[t, :]> (zero for a
+// dropped assignment).  One warp per token: the token's output gradient is read once per 256-element piece and reused
+// for its k gathered rows.  (A batched matrix product with one output column per batch runs this at a fraction of the
+// memory bandwidth.)
+template <int KMAX>
+__global__ void moe_dprobs_kernel(const bf16* __restrict__ rows, const bf16* __restrict__ d_out, const int* __restrict__ dest_rank,
+                                  float* __restrict__ d_probs, int T, int k, int h) {
+    const int wpb = blockDim.x >> 5, l = threadIdx.x & 31;
+    for (long long t = (long long)blockIdx.x * wpb + (threadIdx.x >> 5); t < T; t += (long long)gridDim.x * wpb) {
+        float acc[KMAX];
+#pragma unroll
+        for (int j = 0; j < KMAX; ++j) acc[j] = 0.f;
+        const uint4* dp = reinterpret_cast<const uint4*>(d_out + t * h);
+        for (int c = l; c < h / 8; c += 32) {
+            const uint4 dv = __ldg(dp + c);
+            const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&dv);
+            float2 df[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) df[i] = __bfloat1622float2(d2[i]);
+#pragma unroll
+            for (int j = 0; j < KMAX; ++j) {
+                if (j < k) {
+                    const uint4 rv = __ldcs(reinterpret_cast<const uint4*>(rows + (t * k + j) * h) + c);
+                    const __nv_bfloat162* r2 = reinterpret_cast<const __nv_bfloat162*>(&rv);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 rf = __bfloat1622float2(r2[i]);
+                        acc[j] += rf.x * df[i].x + rf.y * df[i].y;
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < KMAX; ++j) {
+            if (j < k) {
+                float v = acc[j];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+                if (l == 0) d_probs[t * k + j] = dest_rank[t * k + j] >= 0 ? v : 0.f;
+            }
+        }
+    }
+}
+
 }  // namespace lmoe
 
 using namespace lmoe;
@@ -354,5 +398,21 @@ LMOE_API int lmoe_moe_comm(int which, const MoeArgs* ap, int num_sms, cudaStream
     default:
         return -1;
     }
+    return (int)cudaGetLastError();
+}
+
+// d_probs [T, k] fp32 from the gathered expert outputs rows [T * k, h] (bf16) and the combine's output gradient
+// d_out [T, h] (bf16); h a multiple of 8, k <= 16.
+LMOE_API int lmoe_moe_dprobs(const void* rows, const void* d_out, const int* dest_rank, float* d_probs, int T, int k, int h,
+                             int num_sms, cudaStream_t st) {
+    if (T <= 0) return 0;
+    if (h % 8 != 0 || k <= 0 || k > 16) return -1;
+    const int grid = (int)std::min<long long>(((long long)T + 7) / 8, (long long)num_sms * 8);
+    const bf16* r = (const bf16*)rows;
+    const bf16* d = (const bf16*)d_out;
+    if (k <= 2) moe_dprobs_kernel<2><<<grid, 256, 0, st>>>(r, d, dest_rank, d_probs, T, k, h);
+    else if (k <= 4) moe_dprobs_kernel<4><<<grid, 256, 0, st>>>(r, d, dest_rank, d_probs, T, k, h);
+    else if (k <= 8) moe_dprobs_kernel<8><<<grid, 256, 0, st>>>(r, d, dest_rank, d_probs, T, k, h);
+    else moe_dprobs_kernel<16><<<grid, 256, 0, st>>>(r, d, dest_rank, d_probs, T, k, h);
     return (int)cudaGetLastError();
 }

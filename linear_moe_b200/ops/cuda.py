@@ -145,19 +145,21 @@ def mm_tn(a: torch.Tensor, b: torch.Tensor, out_dtype=None) -> torch.Tensor:
 
 
 class _LinearTc(torch.autograd.Function):
-    """``x W^T`` with forward, data gradient and weight gradient on the dense tcgen05 kernel; the weight gradient goes
-    directly into ``W.main_grad`` when the parameter has one."""
+    """``x W^T (+ bias)`` with forward, data gradient and weight gradient on the dense tcgen05 kernel; the bias is added to
+    the fp32 accumulator in the GEMM epilogue; the weight gradient goes directly into ``W.main_grad`` when the parameter
+    has one."""
 
     @staticmethod
-    def forward(ctx, x, weight):
+    def forward(ctx, x, weight, bias=None):
         from . import gemm
         x2 = _rows(x)
         ctx.save_for_backward(x2, weight)
         ctx.xshape = x.shape
+        ctx.bias_dtype = None if bias is None else bias.dtype
         # the result is allocated in its final shape: a view returned from forward() would have the 2-D buffer as its
         # autograd-less `_base`, which code that looks at view chains (fused q|k|v detection) must never see
         y = torch.empty(*x.shape[:-1], weight.shape[0], dtype=torch.bfloat16, device=x.device)
-        gemm.dense(x2, weight, out=y.view(-1, weight.shape[0]))
+        gemm.dense(x2, weight, out=y.view(-1, weight.shape[0]), bias=bias)
         return y
 
     @staticmethod
@@ -172,7 +174,10 @@ class _LinearTc(torch.autograd.Function):
         dw = None
         if ctx.needs_input_grad[1] and not wgrad_into_main_grad(weight, dy2, x2):
             dw = gemm.dense(dy2, x2, a_mn=True, b_mn=True)
-        return dx, dw
+        db = None
+        if ctx.bias_dtype is not None and ctx.needs_input_grad[2]:
+            db = dy2.sum(0, dtype=torch.float32).to(ctx.bias_dtype)
+        return dx, dw, db
 
 
 def _skinny_ok(x, weight) -> bool:
@@ -206,6 +211,8 @@ def linear(x, weight, bias=None):
         return fp8.Fp8Linear.apply(x, weight)
     if (weight.dtype == x.dtype == torch.bfloat16 and weight.dim() == 2 and x.shape[-1] % 8 == 0 and x.numel() > 0
             and gemm.dense_ok(weight) and weight.shape[0] % 8 == 0):
+        if bias is not None and bias.dtype == torch.bfloat16 and bias.is_contiguous() and bias.data_ptr() % 16 == 0:
+            return _LinearTc.apply(x, weight, bias)
         y = _LinearTc.apply(x, weight)
         return y if bias is None else y + bias.to(y.dtype)
     return F.linear(x, weight if weight.dtype == x.dtype else weight.to(x.dtype),
@@ -783,6 +790,17 @@ def router_topk(logits, k, order="softmax_topk"):
     if logits.shape[-1] > 256 or k > 16:
         return R.router_topk(logits, k, order)
     return _RouterTopK.apply(logits, k, order)
+
+
+def moe_dprobs(rows, d_out, dest_rank, T, k):
+    """Gradient of the routing probabilities in the MoE combine: ``d_probs[t, j] = <rows[t*k+j], d_out[t]>``, zero for
+    dropped assignments (``moe_dprobs_kernel``, csrc/moe_comm.cu)."""
+    h = d_out.shape[-1]
+    rows, d_out = rows.contiguous(), d_out.contiguous()
+    out = torch.empty(T, k, dtype=torch.float32, device=d_out.device)
+    _check(lib().lmoe_moe_dprobs(_p(rows), _p(d_out), _p(dest_rank), _p(out), _i32(T), _i32(k), _i32(h), _i32(num_sms()),
+                                 _st()), "moe_dprobs")
+    return out
 
 
 def grouped_mlp(x_sorted, tokens_per_expert, w1, w2):

@@ -97,8 +97,10 @@ BAND = int(os.environ.get("LMOE_GEMM_BAND", "0"))          # tile rows per band 
 
 
 def dense(a: torch.Tensor, b: torch.Tensor, a_mn: bool = False, b_mn: bool = False, out: Optional[torch.Tensor] = None,
-          accumulate: bool = False, out_dtype=torch.bfloat16, band: Optional[int] = None) -> torch.Tensor:
-    """``C[M,N] (+)= A B`` on the CTA-pair tcgen05 kernel of ``csrc/gemm_dense.cu``.
+          accumulate: bool = False, out_dtype=torch.bfloat16, band: Optional[int] = None,
+          bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``C[M,N] (+)= A B`` on the CTA-pair tcgen05 kernel of ``csrc/gemm_dense.cu`` (``bias`` ``[N]`` bf16: added in the
+    epilogue of the bf16-output form).
 
     ``a`` is ``[M,K]`` (or ``[K,M]`` with ``a_mn``), ``b`` is ``[N,K]`` (or ``[K,N]`` with ``b_mn``).  ``out`` may be a
     bf16 or fp32 matrix; ``accumulate`` (fp32 only) adds into it with TMA reduce-adds instead of overwriting.
@@ -113,6 +115,15 @@ def dense(a: torch.Tensor, b: torch.Tensor, a_mn: bool = False, b_mn: bool = Fal
         out = torch.empty(M, N, dtype=out_dtype, device=a.device)
     mode = 0 if out.dtype == torch.bfloat16 else (2 if accumulate else 1)
     assert out.shape == (M, N) and out.stride(1) == 1 and (mode != 0 or not accumulate)
+    if bias is not None:
+        assert mode == 0 and bias.dtype == torch.bfloat16 and bias.numel() == N and bias.is_contiguous()
+        rc = K.lib().lmoe_gemm_dense_bias(K._p(a), ctypes.c_int(a.stride(0)), ctypes.c_int(int(a_mn)), K._p(b),
+                                          ctypes.c_int(b.stride(0)), ctypes.c_int(int(b_mn)), K._p(out), ctypes.c_int(out.stride(0)),
+                                          K._p(bias), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(Kd),
+                                          ctypes.c_int(BAND if band is None else band), K._p(_err(a.device)),
+                                          ctypes.c_int(K.NUM_SMS), K._st())
+        K._check(rc, "gemm_dense_bias")
+        return out
     rc = K.lib().lmoe_gemm_dense(K._p(a), ctypes.c_int(a.stride(0)), ctypes.c_int(int(a_mn)), K._p(b), ctypes.c_int(b.stride(0)),
                                  ctypes.c_int(int(b_mn)), K._p(out), ctypes.c_int(out.stride(0)), ctypes.c_int(mode),
                                  ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(Kd), ctypes.c_int(BAND if band is None else band),

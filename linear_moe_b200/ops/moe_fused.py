@@ -45,8 +45,8 @@ class _Combine(torch.autograd.Function):
         route = ctx.route
         d_out = d_out.contiguous()
         T, k = route.T, route.k
-        d_probs = torch.bmm(rows.view(T, k, -1), d_out.unsqueeze(-1)).squeeze(-1).float()
-        d_probs = torch.where(route.dest_rank.view(T, k) >= 0, d_probs, torch.zeros_like(d_probs))
+        from . import cuda as K
+        d_probs = K.moe_dprobs(rows, d_out, route.dest_rank, T, k)
         d_y = ctx.ws.push(d_out, route, w.reshape(-1))
         return d_y, d_probs.to(ctx.pdtype), None, None
 

@@ -328,3 +328,26 @@ def test_skinny_gemm_for_decode_rows(M, N, K):
     # with autograd on a parameter the regular (differentiable) path runs instead
     wp = w.clone().requires_grad_(True)
     assert not K_._skinny_ok(x, wp)
+
+
+def test_linear_with_bias_in_the_gemm_epilogue():
+    """``ops.linear`` with a bf16 bias: the bias is added in the GEMM epilogue (one launch forward); output and all three
+    gradients against fp32 PyTorch."""
+    from linear_moe_b200 import ops
+    from linear_moe_b200.ops import cuda as K_
+    torch.manual_seed(5)
+    dev = torch.device("cuda", 0)
+    x = torch.randn(3, 700, 512, device=dev).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(1032, 512, device=dev) / 512 ** 0.5).to(torch.bfloat16).requires_grad_(True)
+    b = torch.randn(1032, device=dev).to(torch.bfloat16).requires_grad_(True)
+    gy = torch.randn(3, 700, 1032, device=dev).to(torch.bfloat16)
+    K_.reset_launch_count()
+    y = ops.linear(x, w, b)
+    assert K_.reset_launch_count() == 1, "the bias add is a separate launch"
+    y.backward(gy)
+    xf, wf, bf = [t.detach().float().requires_grad_(True) for t in (x, w, b)]
+    yr = torch.nn.functional.linear(xf, wf, bf)
+    yr.backward(gy.float())
+    rel = lambda a, r: ((a.float() - r).norm() / r.norm()).item()
+    assert rel(y, yr) < 5e-3, rel(y, yr)
+    assert rel(x.grad, xf.grad) < 5e-3 and rel(w.grad, wf.grad) < 5e-3 and rel(b.grad, bf.grad) < 5e-3
