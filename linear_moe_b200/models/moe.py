@@ -413,6 +413,7 @@ class MoELayer(nn.Module):
         if self.shared_expert is not None:
             s = self.shared_expert(x)
             if self.shared_expert_gate is not None:
-                s = s * torch.sigmoid(F.linear(x, self.shared_expert_gate.weight.to(x.dtype)))
-            out = out + s
+                out = ops.gated_add(out, s, F.linear(x, self.shared_expert_gate.weight.to(x.dtype)))
+            else:
+                out = out + s
         return out

@@ -286,6 +286,14 @@ def apply_rope_at(x, cos_table, sin_table, positions, interleaved: bool = False)
     return apply_rope(x.reshape(1, B * T, H, D), cos, sin, interleaved).reshape(B, T, H, D)
 
 
+def gated_add(a, s, g):
+    """``a + s * sigmoid(g)``; ``a``, ``s`` ``[..., N]``, ``g`` ``[..., 1]`` gate logits (the shared expert of a Qwen2-MoE
+    layer joining the routed experts' output)."""
+    if _cuda(a):
+        return _K().gated_add(a, s, g)
+    return a + s * torch.sigmoid(g)
+
+
 def causal_conv1d(x, weight, bias=None, activation="silu", initial_state=None):
     if _cuda(x):
         return _K().causal_conv1d(x, weight, bias, activation, initial_state)

@@ -792,6 +792,39 @@ def router_topk(logits, k, order="softmax_topk"):
     return _RouterTopK.apply(logits, k, order)
 
 
+class _GatedAdd(torch.autograd.Function):
+    """``a + s * sigmoid(g)`` with one gate logit per row (``csrc/gated_add.cu``)."""
+
+    @staticmethod
+    def forward(ctx, a, s, g):
+        N = a.shape[-1]
+        a2, s2 = a.reshape(-1, N).contiguous(), s.reshape(-1, N).contiguous()
+        g2 = g.reshape(-1).contiguous()
+        out = torch.empty_like(a2)
+        _check(lib().lmoe_gated_add_fwd(_p(a2), _p(s2), _p(g2), _p(out), _i64(a2.shape[0]), _i32(N), _i32(_dt(a2)), _st()),
+               "gated_add_fwd")
+        ctx.save_for_backward(s2, g2)
+        ctx.shapes = (a.shape, g.shape)
+        return out.view(a.shape)
+
+    @staticmethod
+    def backward(ctx, d_out):
+        s2, g2 = ctx.saved_tensors
+        N = s2.shape[-1]
+        d2 = d_out.reshape(-1, N).contiguous()
+        ds = torch.empty_like(s2)
+        dg = torch.empty_like(g2)
+        _check(lib().lmoe_gated_add_bwd(_p(d2), _p(s2), _p(g2), _p(ds), _p(dg), _i64(d2.shape[0]), _i32(N), _i32(_dt(d2)), _st()),
+               "gated_add_bwd")
+        return d_out, ds.view(ctx.shapes[0]), dg.view(ctx.shapes[1])
+
+
+def gated_add(a, s, g):
+    if a.dtype != s.dtype or g.dtype != a.dtype or a.dtype not in (torch.bfloat16, torch.float32) or a.shape[-1] % 8:
+        return a + s * torch.sigmoid(g)
+    return _GatedAdd.apply(a, s, g)
+
+
 def moe_dprobs(rows, d_out, dest_rank, T, k):
     """Gradient of the routing probabilities in the MoE combine: ``d_probs[t, j] = <rows[t*k+j], d_out[t]>``, zero for
     dropped assignments (``moe_dprobs_kernel``, csrc/moe_comm.cu)."""

@@ -529,3 +529,21 @@ def test_embedding_backward_scatter(dtype, main_grad):
     got = w.main_grad if main_grad else w.grad.float()
     rel = ((got - wr.grad).norm() / wr.grad.norm()).item()
     assert rel < (1e-5 if main_grad or dtype == torch.float32 else 5e-3), rel
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_gated_add(dtype):
+    """``a + s * sigmoid(g)`` (one gate logit per row), forward and the three gradients, against fp32 PyTorch."""
+    torch.manual_seed(6)
+    a = torch.randn(3, 70, 256, device=dev()).to(dtype)
+    s = torch.randn(3, 70, 256, device=dev()).to(dtype)
+    g = torch.randn(3, 70, 1, device=dev()).to(dtype)
+    go = torch.randn(3, 70, 256, device=dev()).to(dtype)
+    K.reset_launch_count()
+    (y,), gk = grads(ops.gated_add, [a, s, g], go)
+    assert K.reset_launch_count() == 2
+    (y2,), gr = grads(lambda a, s, g: a + s * torch.sigmoid(g), [a.float(), s.float(), g.float()], go.float())
+    tol = 1e-2 if dtype == torch.bfloat16 else 1e-5
+    rel_close(y, y2, tol, "out")
+    for name, x_, r_ in zip(["da", "ds", "dg"], gk, gr):
+        rel_close(x_, r_, tol, name)
