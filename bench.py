@@ -11,6 +11,9 @@ reduction over the sequence-parallel ranks + clip + Adam on fp32 masters.
   python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
       bench.py --gpus N --steps K --warmup W
 
+``--config`` selects another benchmark configuration together with its parallel layout (``LAYOUTS`` below); the default
+is the configuration the headline number is quoted on.
+
 Rank 0 prints ONE JSON line.  ``value`` is device-timed (CUDA events, max over ranks) with the batch already
 on the device; ``e2e`` repeats the measurement through ``Trainer.train_step`` with, every step, the host->device
 copy of that step's tokens/labels/mask from pinned memory and a device->host read of the loss.
@@ -27,6 +30,21 @@ import time
 TOKENS_PER_GPU = 16384
 METRIC = "train tokens/s per 8xB200 box (LASP-2 Linear-Llama3-1B, lightning attention, 16384 tokens per GPU, seq 131072 at 8 GPUs)"
 
+# Parallel layout, batch and metric of every benchmark configuration that ``--config`` accepts.  The default (and the
+# configuration the headline number is quoted on) is the LASP-2 Linear-Llama3-1B one; the others weak-scale the number of
+# sequences with the data-parallel size.  ``tp`` is capped by the number of GPUs.
+LAYOUTS = {
+    "bench-lasp2-llama3-1b": dict(kind="cp", metric=METRIC),
+    "bench-a0.3b-2b-gla": dict(kind="ep", tp=1, mbs=8, seq=2048,
+                               metric="train tokens/s (A0.3B-2B: 16 x GLA + 64-expert top-8 MoE, EP = N, 8 x 2048 tokens per GPU)"),
+    "bench-a1b-7b-hybrid": dict(kind="ep", tp=2, mbs=2, seq=4096,
+                                metric="train tokens/s (A1B-7B hybrid LLLN x 6: Gated DeltaNet + attention, 64-expert top-8 MoE, "
+                                       "TP2 x EP N/2, 2 x 4096 tokens per data-parallel rank)"),
+    "bench-mixtral-mamba2-fp8": dict(kind="ep", tp=2, mbs=1, seq=4096,
+                                     metric="train tokens/s (Mixtral-shaped Mamba2 + attention hybrid, 8-expert top-2 MoE, e4m3 "
+                                            "projections, TP2 x EP N/2, 4096 tokens per data-parallel rank)"),
+}
+
 
 def parse():
     p = argparse.ArgumentParser()
@@ -34,7 +52,8 @@ def parse():
     p.add_argument("--steps", type=int, default=8)
     p.add_argument("--warmup", type=int, default=3)
     p.add_argument("--impl", type=str, default="ours", choices=["ours", "reference"])
-    p.add_argument("--config", type=str, default="bench-lasp2-llama3-1b")
+    p.add_argument("--config", type=str, default="bench-lasp2-llama3-1b",
+                   help="benchmark configuration: " + ", ".join(LAYOUTS) + " (preset, parallel layout and batch switch together)")
     p.add_argument("--tokens-per-gpu", type=int, default=TOKENS_PER_GPU)
     p.add_argument("--layers", type=int, default=None, help="debug only: fewer layers (marks the result invalid)")
     p.add_argument("--no-e2e", action="store_true")
@@ -72,14 +91,33 @@ def main():
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
-    par = ParallelConfig(context_parallel_size=world, use_distributed_optimizer=args.zero1, distributed_backend="nccl",
-                         overlap_grad_reduce=args.overlap_grad_reduce)
+    layout = LAYOUTS.get(args.config, LAYOUTS["bench-lasp2-llama3-1b"])
+    if layout["kind"] == "cp":                       # one sequence split over all GPUs (LASP-2)
+        par = ParallelConfig(context_parallel_size=world, use_distributed_optimizer=args.zero1, distributed_backend="nccl",
+                             overlap_grad_reduce=args.overlap_grad_reduce)
+        seq, mbs, gbs = args.tokens_per_gpu * world, 1, 1
+        layout_name = f"sp{world} (LASP-2)"
+    else:                                            # tensor x expert parallel, sequences scale with the data-parallel size
+        tp = min(layout["tp"], world)
+        par = ParallelConfig(tensor_model_parallel_size=tp, sequence_parallel=tp > 1, expert_model_parallel_size=world // tp,
+                             use_distributed_optimizer=args.zero1 and world > tp, distributed_backend="nccl",
+                             overlap_grad_reduce=args.overlap_grad_reduce)
+        seq, mbs = layout["seq"], layout["mbs"]
+        gbs = mbs * (world // tp)
+        layout_name = f"tp{tp} ep{world // tp} dp{world // tp}"
     mesh = init_distributed(par)
     dev = torch.device("cuda", torch.cuda.current_device())
-    overrides = {} if args.layers is None else {"num_layers": args.layers, "layer_type_list": "L" * args.layers}
+    overrides = {}
+    if args.layers is not None:
+        base = get_preset(args.config)
+        overrides["num_layers"] = args.layers
+        if base.layer_type_list:
+            overrides["layer_type_list"] = (base.layer_type_list * args.layers)[: args.layers]
+        if base.hybrid_override_pattern:
+            overrides["hybrid_override_pattern"] = (base.hybrid_override_pattern * args.layers)[: args.layers]
     cfg = get_preset(args.config, **overrides)
-    seq = args.tokens_per_gpu * world
-    tc = TrainConfig(micro_batch_size=1, global_batch_size=1, seq_length=seq, train_iters=10 ** 9, lr=1e-4, min_lr=1e-5,
+    tokens_per_step = gbs * seq
+    tc = TrainConfig(micro_batch_size=mbs, global_batch_size=gbs, seq_length=seq, train_iters=10 ** 9, lr=1e-4, min_lr=1e-5,
                      lr_decay_style="cosine", lr_decay_iters=100000, lr_warmup_iters=100, weight_decay=0.1,
                      adam_beta1=0.9, adam_beta2=0.95, clip_grad=1.0, bf16=True, log_interval=10 ** 9, seed=1234,
                      check_for_nan_in_loss_and_grad=False)
@@ -143,7 +181,7 @@ def main():
         for _ in range(2):
             e2e_step()
         ms_e2e, _ = timed(e2e_step, args.steps)
-        e2e = {"value": seq / (ms_e2e / 1000.0), "unit": "tokens/s", "ms_per_step": ms_e2e,
+        e2e = {"value": tokens_per_step / (ms_e2e / 1000.0), "unit": "tokens/s", "ms_per_step": ms_e2e,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4, "last_loss": last.get("loss")}
 
     # ---- on-stream time of the fused LASP-2 exchange (push + wait for the other ranks + fold), one extra step ----
@@ -165,14 +203,15 @@ def main():
 
     if mesh.rank == 0:
         out = {
-            "metric": METRIC, "value": seq / (ms_dev / 1000.0), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "metric": layout["metric"], "value": tokens_per_step / (ms_dev / 1000.0), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_dev, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic uniform token ids, random-init N(0,0.02) weights",
             "impl": "ours",
-            "config": {"model": args.config, "global_batch": 1, "seq_len": seq, "tokens_per_gpu": args.tokens_per_gpu,
-                       "parallelism": f"sp{world} (LASP-2)" + (" zero1" if args.zero1 else "") +
+            "config": {"model": args.config, "global_batch": gbs, "seq_len": seq, "tokens_per_gpu": tokens_per_step // world,
+                       "parallelism": layout_name + (" zero1" if par.use_distributed_optimizer else "") +
                        (" overlap-grad-reduce" if (args.zero1 and args.overlap_grad_reduce and world > 1) else ""), "params": n_params,
-                       "layers": cfg.num_layers, "l2": "inputs larger than L2 (16384x2048 bf16 activations, 3.3 GB weights)",
+                       "layers": cfg.num_layers, "l2": "inputs larger than L2 (>= 16384 tokens x hidden bf16 activations and GBs of weights per GPU)",
                        "optimizer": "AdamW fp32 masters, clip 1.0", "valid": args.layers is None},
             "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
         }

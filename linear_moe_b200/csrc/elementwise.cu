@@ -606,23 +606,33 @@ __global__ void causal_conv1d_fwd_vec_kernel(const T* __restrict__ x, const T* _
 #pragma unroll
         for (int e = 0; e < VN; ++e) hist[j][e] = have ? v.get(e) : 0.f;
     }
-    for (int t = t0; t < t1; ++t) {
-        Vec<T> cur, out;
-        cur.load(x + ((int64_t)b * Tlen + t) * D + d0);
+    // eight rows per pass, their loads issued together before the first use
+    constexpr int U = 8;
+    for (int tb = t0; tb < t1; tb += U) {
+        Vec<T> curv[U];
 #pragma unroll
-        for (int e = 0; e < VN; ++e) {
-            float acc = bv[e] + cur.get(e) * wk[e][K - 1];
+        for (int u = 0; u < U; ++u)
+            if (tb + u < t1) curv[u].load(x + ((int64_t)b * Tlen + tb + u) * D + d0);
 #pragma unroll
-            for (int j = 0; j < K - 1; ++j) acc += hist[j][e] * wk[e][j];
-            out.set(e, act ? silu_f(acc) : acc);
+        for (int u = 0; u < U; ++u) {
+            const int t = tb + u;
+            if (t >= t1) break;
+            Vec<T> out;
+#pragma unroll
+            for (int e = 0; e < VN; ++e) {
+                float acc = bv[e] + curv[u].get(e) * wk[e][K - 1];
+#pragma unroll
+                for (int j = 0; j < K - 1; ++j) acc += hist[j][e] * wk[e][j];
+                out.set(e, act ? silu_f(acc) : acc);
+            }
+            out.store(y + ((int64_t)b * Tlen + t) * D + d0);
+#pragma unroll
+            for (int j = 0; j + 1 < K - 1; ++j)
+#pragma unroll
+                for (int e = 0; e < VN; ++e) hist[j][e] = hist[j + 1][e];
+#pragma unroll
+            for (int e = 0; e < VN; ++e) hist[K - 2][e] = curv[u].get(e);
         }
-        out.store(y + ((int64_t)b * Tlen + t) * D + d0);
-#pragma unroll
-        for (int j = 0; j + 1 < K - 1; ++j)
-#pragma unroll
-            for (int e = 0; e < VN; ++e) hist[j][e] = hist[j + 1][e];
-#pragma unroll
-        for (int e = 0; e < VN; ++e) hist[K - 2][e] = cur.get(e);
     }
 }
 
@@ -735,55 +745,69 @@ __global__ void causal_conv1d_bwd_vec_kernel(const T* __restrict__ dy, const T* 
     for (int j = 0; j < K - 1; ++j)
 #pragma unroll
         for (int e = 0; e < VN; ++e) first_dp[j][e] = 0.f;
-    for (int t = t0; t < t1 + K - 1; ++t) {
-        // shift windows
+    // four time steps per pass: their loads are issued together (one dependent load per step left the kernel bound by
+    // memory latency), then the steps run in order on the register windows
+    constexpr int U = 4;
+    for (int tb = t0; tb < t1 + K - 1; tb += U) {
+        Vec<T> curv[U], gvec[U];
 #pragma unroll
-        for (int k = 0; k + 1 < K; ++k)
-#pragma unroll
-            for (int e = 0; e < VN; ++e) { xw[k][e] = xw[k + 1][e]; dp[k][e] = dp[k + 1][e]; }
-        if (t < Tlen) {
-            Vec<T> cur, g;
-            cur.load(x + ((int64_t)b * Tlen + t) * D + d0);
-            g.load(dy + ((int64_t)b * Tlen + t) * D + d0);
-#pragma unroll
-            for (int e = 0; e < VN; ++e) {
-                xw[K - 1][e] = cur.get(e);
-                float gv = g.get(e);
-                if (act) {
-                    float pre = bv[e];
-#pragma unroll
-                    for (int k = 0; k < K; ++k) pre += xw[k][e] * wk[e][k];
-                    gv *= dsilu_f(pre);
-                }
-                dp[K - 1][e] = gv;
-                if (t < t1) {
-                    dbacc[e] += gv;
-#pragma unroll
-                    for (int k = 0; k < K; ++k) dwacc[e][k] += gv * xw[k][e];
-                }
+        for (int u = 0; u < U; ++u) {
+            const int t = tb + u;
+            if (t < t1 + K - 1 && t < Tlen) {
+                curv[u].load(x + ((int64_t)b * Tlen + t) * D + d0);
+                gvec[u].load(dy + ((int64_t)b * Tlen + t) * D + d0);
             }
-        } else {
-#pragma unroll
-            for (int e = 0; e < VN; ++e) { xw[K - 1][e] = 0.f; dp[K - 1][e] = 0.f; }
         }
-        if (t0 == 0 && t < K - 1) {
 #pragma unroll
-            for (int j = 0; j < K - 1; ++j)
-                if (j == t)
+        for (int u = 0; u < U; ++u) {
+            const int t = tb + u;
+            if (t >= t1 + K - 1) break;
+            // shift windows
 #pragma unroll
-                    for (int e = 0; e < VN; ++e) first_dp[j][e] = dp[K - 1][e];
-        }
-        const int tout = t - (K - 1);
-        if (tout >= t0 && tout < t1) {
-            Vec<T> o;
+            for (int k = 0; k + 1 < K; ++k)
 #pragma unroll
-            for (int e = 0; e < VN; ++e) {
-                float acc = 0.f;
+                for (int e = 0; e < VN; ++e) { xw[k][e] = xw[k + 1][e]; dp[k][e] = dp[k + 1][e]; }
+            if (t < Tlen) {
 #pragma unroll
-                for (int k = 0; k < K; ++k) acc += dp[K - 1 - k][e] * wk[e][k];       // dpre[tout + K-1-k] * w[k]
-                o.set(e, acc);
+                for (int e = 0; e < VN; ++e) {
+                    xw[K - 1][e] = curv[u].get(e);
+                    float gv = gvec[u].get(e);
+                    if (act) {
+                        float pre = bv[e];
+#pragma unroll
+                        for (int k = 0; k < K; ++k) pre += xw[k][e] * wk[e][k];
+                        gv *= dsilu_f(pre);
+                    }
+                    dp[K - 1][e] = gv;
+                    if (t < t1) {
+                        dbacc[e] += gv;
+#pragma unroll
+                        for (int k = 0; k < K; ++k) dwacc[e][k] += gv * xw[k][e];
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int e = 0; e < VN; ++e) { xw[K - 1][e] = 0.f; dp[K - 1][e] = 0.f; }
             }
-            o.store(dx + ((int64_t)b * Tlen + tout) * D + d0);
+            if (t0 == 0 && t < K - 1) {
+#pragma unroll
+                for (int j = 0; j < K - 1; ++j)
+                    if (j == t)
+#pragma unroll
+                        for (int e = 0; e < VN; ++e) first_dp[j][e] = dp[K - 1][e];
+            }
+            const int tout = t - (K - 1);
+            if (tout >= t0 && tout < t1) {
+                Vec<T> o;
+#pragma unroll
+                for (int e = 0; e < VN; ++e) {
+                    float acc = 0.f;
+#pragma unroll
+                    for (int k = 0; k < K; ++k) acc += dp[K - 1 - k][e] * wk[e][k];       // dpre[tout + K-1-k] * w[k]
+                    o.set(e, acc);
+                }
+                o.store(dx + ((int64_t)b * Tlen + tout) * D + d0);
+            }
         }
     }
     if (dinit != nullptr && t0 == 0) {
