@@ -1230,13 +1230,34 @@ def _gla_dg(q, k, dq, dk):
     return dg
 
 
+def _lsm_vector_bonus(q, k, v, gk, scale, initial_state, bonus, chunk_size):
+    """RWKV6 on the key-channel-gated kernels: ``o_t = r_t (S_{t-1} + diag(u) k_t^T v_t)``.
+
+    The kernels compute ``q_t S_t`` with ``S_t`` including token ``t``.  ``r_t S_{t-1}`` is what they return at position
+    ``t - 1`` when the query there is ``r_t``, so the queries are shifted one position to the left, the outputs one to the
+    right (position 0 reads the initial state), and the bonus term is a per-token dot product.  Nothing is subtracted,
+    so strong decays lose no precision; autograd differentiates the shifts."""
+    B, T, H, D = q.shape
+    q_shift = torch.cat([q[:, 1:], q.new_zeros(B, 1, H, D)], 1)
+    out_s, S = lsm_vector(q_shift, k, v, gk, scale, initial_state, None, chunk_size)
+    if initial_state is None:
+        first = out_s.new_zeros(B, 1, H, v.shape[-1])
+    else:
+        first = (scale * torch.einsum("bhk,bhkv->bhv", q[:, 0].float(), initial_state.float())).to(out_s.dtype)[:, None]
+    o_state = torch.cat([first, out_s[:, :-1]], 1)
+    diag = (q.float() * k.float() * bonus.float()[None, None]).sum(-1, keepdim=True) * scale
+    return o_state + (diag * v.float()).to(o_state.dtype), S
+
+
 def lsm_vector(q, k, v, gk, scale, initial_state, bonus, chunk_size):
     D = q.shape[-1]
-    ok = (bonus is None and q.dtype == torch.bfloat16 and k.dtype == q.dtype and v.dtype == q.dtype
+    ok = (q.dtype == torch.bfloat16 and k.dtype == q.dtype and v.dtype == q.dtype
           and v.shape[-1] == D and k.shape[-1] == D and D in (64, 128))
     if not ok:
         return LT.chunk_vector_gated(q, k, v, gk, scale, initial_state, 16, bonus)
     scale = D ** -0.5 if scale is None else scale
+    if bonus is not None:
+        return _lsm_vector_bonus(q, k, v, gk, scale, initial_state, bonus, chunk_size)
     if q.shape[1] == 1 and not (torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v, gk))):
         return _lsm_step(q, k, v, None, gk, scale, initial_state)
     base = _fused_base(q, k, v)

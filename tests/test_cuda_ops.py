@@ -547,3 +547,28 @@ def test_gated_add(dtype):
     rel_close(y, y2, tol, "out")
     for name, x_, r_ in zip(["da", "ds", "dg"], gk, gr):
         rel_close(x_, r_, tol, name)
+
+
+@pytest.mark.parametrize("D,T,with_state", [(64, 130, False), (128, 200, True), (64, 1, True)])
+def test_lsm_vector_rwkv6_bonus_on_kernels(D, T, with_state):
+    """RWKV6 (``o_t = r_t (S_{t-1} + diag(u) k_t^T v_t)``) through the key-channel-gated kernels with shifted queries,
+    against the token-by-token fp32 recurrence: output, final state and every gradient incl. the bonus."""
+    torch.manual_seed(12)
+    B, H = 2, 3
+    r, k, v = [(0.5 * torch.randn(B, T, H, D, device=dev())).to(torch.bfloat16) for _ in range(3)]
+    w = -torch.exp(torch.randn(B, T, H, D, device=dev()) - 1.0)                # RWKV6 log decays, some of them strong
+    u = 0.5 * torch.randn(H, D, device=dev())
+    S0 = 0.3 * torch.randn(B, H, D, D, device=dev()) if with_state else None
+    go = torch.randn(B, T, H, D, device=dev(), dtype=torch.bfloat16)
+    gS = 0.1 * torch.randn(B, H, D, D, device=dev()) if with_state else None
+    ins = [r, k, v, w, u] + ([S0] if with_state else [])
+    K.reset_launch_count()
+    f_k = lambda r, k, v, w, u, s=None: ops.lsm_vector(r, k, v, w, 1.0, s, u, 64)
+    f_r = lambda r, k, v, w, u, s=None: RL.recurrent_rwkv6(r, k, v, w, u, scale=1.0, initial_state=s)
+    (o, S), gk_ = grads(f_k, ins, (go, gS))
+    assert K.reset_launch_count() >= 1, "the RWKV6 path did not reach the kernels"
+    (o2, S2), gr = grads(f_r, [t.float() for t in ins], (go.float(), gS))
+    rel_close(o, o2, 2e-2, "o")
+    rel_close(S, S2, 2e-2, "final state")
+    for name, a_, b_ in zip(["dr", "dk", "dv", "dw", "du", "dS0"], gk_, gr):
+        rel_close(a_, b_, 4e-2, name)
