@@ -32,6 +32,9 @@ def main():
     ap.add_argument("--baseline-eager", action="store_true",
                     help="stand-in for the reference's NCCL + cuBLAS build: NCCL collectives instead of the fused peer-memory "
                          "kernels and library GEMMs instead of the tcgen05 dense kernel (same model, same step)")
+    ap.add_argument("--torch-profile", type=str, default=None,
+                    help="after the timed steps, run one more step under torch.profiler and write the per-operator CUDA-time "
+                         "table (grouped by input shape) of rank 0 to this file")
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     a = ap.parse_args()
@@ -100,6 +103,15 @@ def main():
                           "peak_mem_gib": round(mem, 1), "fp8": bool(cfg.fp8), "valid": a.layers is None,
                           "impl": "baseline-eager (NCCL + cuBLAS)" if a.baseline_eager else "ours", "clocks": clocks,
                           "global_batch": gbs, "seq_len": a.seq}))
+    if a.torch_profile:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA], record_shapes=True) as prof:
+            trainer.train_step()
+            torch.cuda.synchronize()
+        if mesh.rank == 0:
+            with open(a.torch_profile, "w") as f:
+                f.write(prof.key_averages(group_by_input_shape=True).table(sort_by="self_cuda_time_total", row_limit=80,
+                                                                            max_name_column_width=48, max_shapes_column_width=100))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
