@@ -1230,6 +1230,22 @@ def _gla_dg(q, k, dq, dk):
     return dg
 
 
+_HALF_CHUNK_DECAY_LIMIT = -80.0     # the gated-scan kernels rescale bf16 operands by e^{+-(decay over half a chunk)}
+
+
+def _note_strong_decay(gk):
+    """Record (without a host synchronisation) whether some key channel decays by more than ``e^-80`` inside one half
+    chunk of 32 tokens: beyond that the rescaled bf16 operands of ``csrc/lsm_vector.cu`` overflow.  The flag is the
+    third element of the status word that the trainer reads every step; ``check_status`` raises on it."""
+    from ..parallel import fused_comm
+    B, T, H, D = gk.shape
+    g = gk.detach().float()
+    if T % 32:
+        g = F.pad(g, (0, 0, 0, 0, 0, 32 - T % 32))
+    worst = g.view(B, -1, 32, H, D).sum(2).amin()
+    fused_comm.status_word(gk.device)[2:3] += (worst < _HALF_CHUNK_DECAY_LIMIT).to(torch.int32)
+
+
 def _lsm_vector_bonus(q, k, v, gk, scale, initial_state, bonus, chunk_size):
     """RWKV6 on the key-channel-gated kernels: ``o_t = r_t (S_{t-1} + diag(u) k_t^T v_t)``.
 
@@ -1238,6 +1254,8 @@ def _lsm_vector_bonus(q, k, v, gk, scale, initial_state, bonus, chunk_size):
     right (position 0 reads the initial state), and the bonus term is a per-token dot product.  Nothing is subtracted,
     so strong decays lose no precision; autograd differentiates the shifts."""
     B, T, H, D = q.shape
+    if T > 1:
+        _note_strong_decay(gk)            # RWKV6 decays -exp(.) are not bounded the way GLA's normalised log-sigmoids are
     q_shift = torch.cat([q[:, 1:], q.new_zeros(B, 1, H, D)], 1)
     out_s, S = lsm_vector(q_shift, k, v, gk, scale, initial_state, None, chunk_size)
     if initial_state is None:
@@ -1257,6 +1275,8 @@ def lsm_vector(q, k, v, gk, scale, initial_state, bonus, chunk_size):
         return LT.chunk_vector_gated(q, k, v, gk, scale, initial_state, 16, bonus)
     scale = D ** -0.5 if scale is None else scale
     if bonus is not None:
+        if os.environ.get("LMOE_RWKV6_KERNEL", "1") == "0":
+            return LT.chunk_vector_gated(q, k, v, gk, scale, initial_state, 16, bonus)
         return _lsm_vector_bonus(q, k, v, gk, scale, initial_state, bonus, chunk_size)
     if q.shape[1] == 1 and not (torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v, gk))):
         return _lsm_step(q, k, v, None, gk, scale, initial_state)

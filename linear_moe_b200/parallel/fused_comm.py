@@ -150,11 +150,17 @@ def status_word(device) -> torch.Tensor:
 
 def check_status(where: str = ""):
     """Raise ``CommTimeout`` if any fused kernel gave up on a bounded wait since the last check, or ``RuntimeError`` if
-    a tcgen05 GEMM did (its error word is the second element of the same status tensor, so one read covers both)."""
+    a tcgen05 GEMM did (its error word is the second element of the same status tensor, so one read covers both), or if
+    a decay too strong for the gated-scan kernels was seen (third element)."""
     if STATUS is None:
         return
     from ..train.watchdog import raise_on_comm_status
-    vals = STATUS[:2].cpu()
+    vals = STATUS[:3].cpu()
+    if int(vals[2]) != 0:
+        STATUS.zero_()
+        raise RuntimeError("a key-channel log decay below -80 over half a chunk (32 tokens) reached the chunked gated-scan "
+                           f"kernels, whose bf16 operand rescaling overflows there {where}; LMOE_RWKV6_KERNEL=0 selects the "
+                           "16-token torch form for RWKV6")
     if int(vals[0]) != 0:
         STATUS.zero_()
         raise_on_comm_status(vals[:1], where)

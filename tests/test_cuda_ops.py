@@ -570,5 +570,6 @@ def test_lsm_vector_rwkv6_bonus_on_kernels(D, T, with_state):
     (o2, S2), gr = grads(f_r, [t.float() for t in ins], (go.float(), gS))
     rel_close(o, o2, 2e-2, "o")
     rel_close(S, S2, 2e-2, "final state")
+    # the decay gradient is a reverse cumulative sum of q.dq - k.dk over bf16 dq / dk: a few per cent, the rest is bf16 rounding
     for name, a_, b_ in zip(["dr", "dk", "dv", "dw", "du", "dS0"], gk_, gr):
-        rel_close(a_, b_, 4e-2, name)
+        rel_close(a_, b_, 8e-2 if name == "dw" else 1e-2, name)
