@@ -1275,7 +1275,14 @@ def lsm_vector(q, k, v, gk, scale, initial_state, bonus, chunk_size):
         return LT.chunk_vector_gated(q, k, v, gk, scale, initial_state, 16, bonus)
     scale = D ** -0.5 if scale is None else scale
     if bonus is not None:
-        if os.environ.get("LMOE_RWKV6_KERNEL", "1") == "0":
+        # RWKV6.  Forward-only calls (evaluation, prefill, generation) run on the kernels.  With gradients the default is
+        # the fp32 16-token torch form: the kernels' decay gradient is a reverse cumulative sum of q.dq - k.dk over bf16
+        # dq / dk, accurate to a few per cent per element, which is not enough for RWKV6's slowly decaying channels (the
+        # gradient of the decay projection came out with a cosine of 0.7 against the fp32 form on a small model).
+        # LMOE_RWKV6_KERNEL=1 forces the kernels for training too, =0 forces the torch form everywhere.
+        mode = os.environ.get("LMOE_RWKV6_KERNEL", "auto")
+        needs_grad = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, gk, bonus, initial_state))
+        if mode == "0" or (mode != "1" and needs_grad):
             return LT.chunk_vector_gated(q, k, v, gk, scale, initial_state, 16, bonus)
         return _lsm_vector_bonus(q, k, v, gk, scale, initial_state, bonus, chunk_size)
     if q.shape[1] == 1 and not (torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v, gk))):

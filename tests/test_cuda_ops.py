@@ -550,9 +550,10 @@ def test_gated_add(dtype):
 
 
 @pytest.mark.parametrize("D,T,with_state", [(64, 130, False), (128, 200, True), (64, 1, True)])
-def test_lsm_vector_rwkv6_bonus_on_kernels(D, T, with_state):
+def test_lsm_vector_rwkv6_bonus_on_kernels(D, T, with_state, monkeypatch):
     """RWKV6 (``o_t = r_t (S_{t-1} + diag(u) k_t^T v_t)``) through the key-channel-gated kernels with shifted queries,
     against the token-by-token fp32 recurrence: output, final state and every gradient incl. the bonus."""
+    monkeypatch.setenv("LMOE_RWKV6_KERNEL", "1")                               # the kernels also under autograd
     torch.manual_seed(12)
     B, H = 2, 3
     r, k, v = [(0.5 * torch.randn(B, T, H, D, device=dev())).to(torch.bfloat16) for _ in range(3)]
@@ -573,3 +574,9 @@ def test_lsm_vector_rwkv6_bonus_on_kernels(D, T, with_state):
     # the decay gradient is a reverse cumulative sum of q.dq - k.dk over bf16 dq / dk: a few per cent, the rest is bf16 rounding
     for name, a_, b_ in zip(["dr", "dk", "dv", "dw", "du", "dS0"], gk_, gr):
         rel_close(a_, b_, 8e-2 if name == "dw" else 1e-2, name)
+    # forward-only calls take the kernels by default
+    monkeypatch.delenv("LMOE_RWKV6_KERNEL")
+    K.reset_launch_count()
+    with torch.no_grad():
+        o3, _ = ops.lsm_vector(r, k, v, w, 1.0, S0, u, 64)
+    assert K.reset_launch_count() >= 1 and torch.equal(o3, o)
