@@ -82,6 +82,11 @@ template <> struct Vec<float> {
     __device__ __forceinline__ void set(int i, float v) { reinterpret_cast<float*>(&raw)[i] = v; }
 };
 
+// Lets a kernel that was launched with programmatic stream serialization (the decode GEMM, csrc/gemm_skinny.cu) start while
+// this one is still running; that kernel waits for this one's completion before it reads anything this one writes.
+// Without such a dependent in the stream the instruction does nothing.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + __expf(-x)); }
 // d/dx [x * sigmoid(x)]

@@ -29,6 +29,7 @@ __global__ void rms_norm_fwd_kernel(const T* __restrict__ x, const T* __restrict
     constexpr int VN = Vec<T>::N;
     const int64_t row = blockIdx.x;
     const int nvec = N / VN;
+    pdl_trigger();
     const T* xr = x + row * N;
     Vec<T> v[MAXV];
     float ss = 0.f;
@@ -184,6 +185,7 @@ template <typename T, int DMAX>
 __global__ void head_norm_gate_fwd_kernel(const T* __restrict__ o, const T* __restrict__ w, const T* __restrict__ gate,
                                           T* __restrict__ y, float* __restrict__ rstd_out, int64_t rows, int D,
                                           float eps, int do_norm) {
+    pdl_trigger();
     const int lane = threadIdx.x & 31;
     constexpr int PER = DMAX / 128;
     const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
@@ -360,6 +362,7 @@ __global__ void gated_rms_norm_bwd_kernel(const T* __restrict__ dy, const T* __r
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void swiglu_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, int64_t rows, int F) {
+    pdl_trigger();
     constexpr int VN = Vec<T>::N;
     const int64_t nvec = rows * (F / VN);
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {

@@ -6,7 +6,9 @@
 // over k does not care about the order of k, so the eight consecutive elements a lane loads are used as the k slots
 // that lane owns in two MMA steps (the same assignment for the W and the x fragment), and no shared-memory staging or
 // transposition is needed.  The eight partial tiles are added through shared memory.  No atomics: results are
-// deterministic.
+// deterministic.  The kernel is launched with programmatic stream serialization: its first eight steps of W are in
+// flight before it waits for the kernel that produces x, so consecutive linears of a decode step keep HBM busy across
+// the kernel boundaries (the small kernels in between call griddepcontrol.launch_dependents at their start).
 #include "common.cuh"
 #include "mma_utils.cuh"
 
@@ -56,16 +58,42 @@ __global__ void __launch_bounds__(256) gemm_skinny_kernel(const bf16* __restrict
     for (int t = 0; t < NTILES; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
     const uint4 zero = make_uint4(0, 0, 0, 0);
     const int kslice = K / KS;                                           // a multiple of 32 (checked by the launcher)
-    const int k_end = (int)(crank + 1) * kslice;
-#pragma unroll 8
-    for (int k0 = (int)crank * kslice + w * 32; k0 < k_end; k0 += 256) {
+    const int k_beg = (int)crank * kslice + w * 32, k_end = (int)(crank + 1) * kslice;
+    // The weights do not depend on the kernel before this one: the first PF steps of W are requested before waiting for
+    // it (programmatic dependent launch), so the weight stream of one linear overlaps the tail of whatever produced x.
+    constexpr int PF = 8;
+    uint4 pa_lo[PF], pa_hi[PF];
+#pragma unroll
+    for (int i = 0; i < PF; ++i) {
+        const int k0 = k_beg + i * 256;
+        pa_lo[i] = (lo_ok && k0 < k_end) ? ld_stream(w_lo + k0) : zero;
+        pa_hi[i] = (hi_ok && k0 < k_end) ? ld_stream(w_hi + k0) : zero;
+    }
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");     // the next kernel may start its own prefetch
+    asm volatile("griddepcontrol.wait;" ::: "memory");                  // x is complete and visible from here on
+#pragma unroll
+    for (int i = 0; i < PF; ++i) {
+        const int k0 = k_beg + i * 256;
+        if (k0 < k_end) {
+            const uint32_t f1[4] = {pa_lo[i].x, pa_hi[i].x, pa_lo[i].y, pa_hi[i].y};
+            const uint32_t f2[4] = {pa_lo[i].z, pa_hi[i].z, pa_lo[i].w, pa_hi[i].w};
+#pragma unroll
+            for (int t = 0; t < NTILES; ++t) {
+                const uint4 b = x_ok[t] ? *reinterpret_cast<const uint4*>(xr[t] + k0) : zero;
+                mma16816(acc[t], f1, b.x, b.y);
+                mma16816(acc[t], f2, b.z, b.w);
+            }
+        }
+    }
+#pragma unroll 4
+    for (int k0 = k_beg + PF * 256; k0 < k_end; k0 += 256) {
         const uint4 a_lo = lo_ok ? ld_stream(w_lo + k0) : zero;
         const uint4 a_hi = hi_ok ? ld_stream(w_hi + k0) : zero;
         const uint32_t f1[4] = {a_lo.x, a_hi.x, a_lo.y, a_hi.y};
         const uint32_t f2[4] = {a_lo.z, a_hi.z, a_lo.w, a_hi.w};
 #pragma unroll
         for (int t = 0; t < NTILES; ++t) {
-            const uint4 b = x_ok[t] ? __ldg(reinterpret_cast<const uint4*>(xr[t] + k0)) : zero;
+            const uint4 b = x_ok[t] ? *reinterpret_cast<const uint4*>(xr[t] + k0) : zero;
             mma16816(acc[t], f1, b.x, b.y);
             mma16816(acc[t], f2, b.z, b.w);
         }
@@ -116,21 +144,26 @@ template <int NTILES, int KS>
 static int launch_skinny(const bf16* x, long long ldx, const bf16* W, long long ldw, bf16* y, long long ldy, int M, int N, int K,
                          cudaStream_t st) {
     const int blocks = ((N + 15) / 16) * KS;
-    if (KS == 1) {
-        gemm_skinny_kernel<NTILES, 1><<<blocks, 256, 0, st>>>(x, ldx, W, ldw, y, ldy, M, N, K);
-        return (int)cudaGetLastError();
-    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(blocks);
     cfg.blockDim = dim3(256);
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = KS;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    // the kernel may start while its predecessor in the stream is still running; it waits (griddepcontrol.wait) before it
+    // reads x
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+    if (KS > 1) {
+        attr[na].id = cudaLaunchAttributeClusterDimension;
+        attr[na].val.clusterDim.x = KS;
+        attr[na].val.clusterDim.y = 1;
+        attr[na].val.clusterDim.z = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = na;
     return (int)cudaLaunchKernelEx(&cfg, gemm_skinny_kernel<NTILES, KS>, x, ldx, W, ldw, y, ldy, M, N, K);
 }
 

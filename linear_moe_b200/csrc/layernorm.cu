@@ -20,6 +20,7 @@ __global__ void layer_norm_fwd_kernel(const T* __restrict__ x, const T* __restri
     constexpr int VN = Vec<T>::N;
     const int64_t row = blockIdx.x;
     const int nvec = N / VN;
+    pdl_trigger();
     Vec<T> v[MAXV];
     float s = 0.f;
 #pragma unroll
