@@ -9,6 +9,8 @@
 // deterministic.  The kernel is launched with programmatic stream serialization: its first eight steps of W are in
 // flight before it waits for the kernel that produces x, so consecutive linears of a decode step keep HBM busy across
 // the kernel boundaries (the small kernels in between call griddepcontrol.launch_dependents at their start).
+#include <cstdlib>
+
 #include "common.cuh"
 #include "mma_utils.cuh"
 
@@ -152,9 +154,12 @@ static int launch_skinny(const bf16* x, long long ldx, const bf16* W, long long 
     int na = 0;
     // the kernel may start while its predecessor in the stream is still running; it waits (griddepcontrol.wait) before it
     // reads x
-    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[na].val.programmaticStreamSerializationAllowed = 1;
-    ++na;
+    static const bool pdl = [] { const char* e = getenv("LMOE_SKINNY_PDL"); return e == nullptr || e[0] != '0'; }();
+    if (pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
     if (KS > 1) {
         attr[na].id = cudaLaunchAttributeClusterDimension;
         attr[na].val.clusterDim.x = KS;
