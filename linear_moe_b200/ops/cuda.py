@@ -1488,9 +1488,10 @@ def _delta_prepare_bwd_kernel(q, k, v, beta, g, scale, Sn, dSn, Vn, dVn, dO):
 
 
 class _DeltaRuleScan(torch.autograd.Function):
-    """(Gated) delta rule.  Forward: chunk-parallel WY/UT tiles (batched tensor-core matmuls + a triangular solve), then
-    the scan kernel.  Only the inputs are kept; the backward rebuilds the tiles with autograd enabled, runs both scan
-    kernels and differentiates the tile construction."""
+    """(Gated) delta rule on the kernels of ``csrc/lsm_delta.cu``.  Forward: the chunk-parallel WY / UT tile kernel, then the
+    scan kernel.  Only the inputs are kept.  Backward (bf16, equal key / value widths): tiles and forward scan again, the
+    reverse scan, then the chunk-parallel tile-gradient kernel (``_delta_backward_kernels``).  Other dtypes / widths build
+    the tiles with torch ops and differentiate that construction with autograd around the two scan kernels."""
 
     @staticmethod
     def forward(ctx, q, k, v, beta, g, initial_state, scale, chunk_size):
