@@ -17,6 +17,8 @@ single-process model with the same seed.
 """
 from __future__ import annotations
 
+import os
+
 import hashlib
 import math
 from typing import Optional
@@ -174,12 +176,58 @@ class VocabParallelEmbedding(nn.Module):
         return C.all_reduce(e, g)
 
 
+def _ce_kernel_labels(labels, vocab_start, width, ignore_index):
+    """Labels as the per-shard kernels want them: the local column for targets inside this shard, ``ignore_index`` for
+    ignored rows, and for rows whose target lives in another shard a value that matches no column (the row still gets
+    the softmax part of its gradient)."""
+    local = labels - vocab_start
+    inshard = (local >= 0) & (local < width) & (labels != ignore_index)
+    nowhere = -1 if ignore_index != -1 else -2
+    fwd = torch.where(inshard, local, torch.full_like(local, ignore_index))
+    bwd = torch.where(labels != ignore_index, torch.where(inshard, local, torch.full_like(local, nowhere)),
+                      torch.full_like(local, ignore_index))
+    return inshard, fwd, bwd
+
+
+def vocab_shard_stats(logits2d, labels1d, vocab_start, ignore_index):
+    """Per-shard statistics of the vocabulary-parallel cross entropy on the softmax kernels: the log-sum-exp over this
+    shard's columns and the target logit where the target is in the shard (0 elsewhere).  No ``[tokens, vocab]``
+    temporary is made."""
+    K = ops._K()
+    T = logits2d.shape[0]
+    inshard, lab_fwd, lab_bwd = _ce_kernel_labels(labels1d, vocab_start, logits2d.shape[1], ignore_index)
+    loss = torch.empty(T, dtype=torch.float32, device=logits2d.device)
+    lse = torch.empty(T, dtype=torch.float32, device=logits2d.device)
+    K.softmax_ce_fwd(logits2d, lab_fwd, loss, lse, ignore_index)
+    tgt = torch.where(inshard, lse - loss, torch.zeros_like(lse))
+    return lse, tgt, lab_bwd
+
+
 class _VocabParallelCE(torch.autograd.Function):
-    """Cross entropy over logits split along the vocabulary: three small all-reduces
-    (max, sum-exp, target logit), as ``vocab_parallel_cross_entropy`` does for the reference."""
+    """Cross entropy over logits split along the vocabulary (``vocab_parallel_cross_entropy`` of the reference's engine).
+
+    CUDA: every rank runs the softmax kernels on its shard (log-sum-exp and target logit per token), ONE all-gather
+    exchanges the two numbers per token, and the backward kernel turns the shard's logits into its gradient in place with
+    the global log-sum-exp; nothing of size ``[tokens, vocab]`` is allocated.  CPU (gloo tests): the eager form with three
+    all-reduces (max, sum-exp, target logit)."""
 
     @staticmethod
     def forward(ctx, logits, labels, g, vocab_start, ignore_index):
+        if logits.is_cuda and os.environ.get("LMOE_TP_CE_KERNEL", "0") != "0":
+            l2 = logits.reshape(-1, logits.shape[-1])
+            if not l2.is_contiguous():
+                l2 = l2.contiguous()
+            lab = labels.reshape(-1)
+            lse_loc, tgt_loc, lab_bwd = vocab_shard_stats(l2, lab, vocab_start, ignore_index)
+            both = C.all_gather_raw(torch.stack([lse_loc, tgt_loc])[None].contiguous(), g, dim=0)     # [tp, 2, T]
+            lse = torch.logsumexp(both[:, 0], dim=0)
+            tgt = both[:, 1].sum(0)
+            valid = lab != ignore_index
+            loss = torch.where(valid, lse - tgt, torch.zeros_like(lse))
+            ctx.save_for_backward(l2, lab_bwd, lse)
+            ctx.kernel, ctx.ignore, ctx.shape = True, ignore_index, logits.shape
+            return loss.reshape(labels.shape)
+        ctx.kernel = False
         lf = logits.float()
         m = lf.max(-1).values
         C.all_reduce_(m, g, op=torch.distributed.ReduceOp.MAX)
@@ -199,6 +247,11 @@ class _VocabParallelCE(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, gl):
+        if ctx.kernel:
+            l2, lab_bwd, lse = ctx.saved_tensors
+            # the logits are this node's alone (the LM head's output): they are overwritten with their gradient
+            grad = ops._K().softmax_ce_bwd(l2, lab_bwd, lse, gl.reshape(-1).float().contiguous(), ctx.ignore)
+            return grad.view(ctx.shape), None, None, None, None
         p, local, inshard, valid = ctx.saved_tensors
         grad = p.clone()
         idx = local.clamp(0, p.shape[-1] - 1)[..., None]

@@ -580,3 +580,28 @@ def test_lsm_vector_rwkv6_bonus_on_kernels(D, T, with_state, monkeypatch):
     with torch.no_grad():
         o3, _ = ops.lsm_vector(r, k, v, w, 1.0, S0, u, 64)
     assert K.reset_launch_count() >= 1 and torch.equal(o3, o)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_vocab_parallel_ce_shard_kernels(dtype):
+    """The per-shard pieces of the vocabulary-parallel cross entropy (softmax kernels on each shard, log-sum-exp and target
+    logit combined across shards, gradient with the global log-sum-exp) on two emulated shards against
+    ``F.cross_entropy`` on the whole vocabulary."""
+    from linear_moe_b200.parallel.tensor_parallel import vocab_shard_stats
+    torch.manual_seed(7)
+    T, V, shards = 300, 4096, 2
+    full = (2.0 * torch.randn(T, V, device=dev())).to(dtype)
+    labels = torch.randint(0, V, (T,), device=dev())
+    labels[::9] = -100
+    gl = torch.rand(T, device=dev())
+    w = V // shards
+    stats = [vocab_shard_stats(full[:, s * w:(s + 1) * w].contiguous(), labels, s * w, -100) for s in range(shards)]
+    lse = torch.logsumexp(torch.stack([st[0] for st in stats]), dim=0)
+    tgt = torch.stack([st[1] for st in stats]).sum(0)
+    loss = torch.where(labels != -100, lse - tgt, torch.zeros_like(lse))
+    ref_in = full.float().requires_grad_(True)
+    ref = F.cross_entropy(ref_in, labels, ignore_index=-100, reduction="none")
+    (ref * gl).sum().backward()
+    assert torch.allclose(loss, ref.detach(), atol=2e-3 if dtype == torch.bfloat16 else 1e-4, rtol=1e-3)
+    grad = torch.cat([K.softmax_ce_bwd(full[:, s * w:(s + 1) * w].contiguous(), stats[s][2], lse, gl, -100) for s in range(shards)], 1)
+    rel_close(grad, ref_in.grad, 1e-2 if dtype == torch.bfloat16 else 1e-5, "dlogits")
