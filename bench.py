@@ -213,7 +213,7 @@ def main():
                        (" overlap-grad-reduce" if (args.zero1 and args.overlap_grad_reduce and world > 1) else ""), "params": n_params,
                        "layers": cfg.num_layers, "l2": "inputs larger than L2 (>= 16384 tokens x hidden bf16 activations and GBs of weights per GPU)",
                        "optimizer": "AdamW fp32 masters, clip 1.0", "valid": args.layers is None},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches * args.steps, "gpu_launches_per_step": launches,
         }
         if lasp is not None:
             out["lasp_exchange"] = lasp
