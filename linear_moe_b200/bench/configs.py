@@ -50,7 +50,7 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     par = ParallelConfig(tensor_model_parallel_size=a.tp, sequence_parallel=a.tp > 1, expert_model_parallel_size=a.ep,
                          context_parallel_size=a.cp, use_distributed_optimizer=a.zero1, distributed_backend="nccl",
-                         fused_comm=not a.baseline_eager, overlap_grad_reduce=not a.baseline_eager)
+                         fused_comm=not a.baseline_eager, overlap_grad_reduce=False)
     mesh = init_distributed(par)
     dev = torch.device("cuda", torch.cuda.current_device())
     over = {}

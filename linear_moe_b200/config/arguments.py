@@ -188,8 +188,8 @@ def build_parser() -> argparse.ArgumentParser:
           dest="expert_model_parallel_size")
     _flag(g, "--sequence-parallel", action="store_true")
     _flag(g, "--use-distributed-optimizer", action="store_true")
-    _flag(g, "--overlap-grad-reduce", action=argparse.BooleanOptionalAction, default=True)
-    _flag(g, "--overlap-param-gather", action=argparse.BooleanOptionalAction, default=True)
+    _flag(g, "--overlap-grad-reduce", action=argparse.BooleanOptionalAction, default=False)
+    _flag(g, "--overlap-param-gather", action=argparse.BooleanOptionalAction, default=False)
     _flag(g, "--distributed-backend", type=str, default="nccl", choices=["nccl", "gloo"])
     _flag(g, "--distributed-timeout-minutes", type=int, default=10)
     _flag(g, "--no-fused-comm", action="store_true")

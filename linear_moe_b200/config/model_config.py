@@ -198,8 +198,8 @@ class ParallelConfig:
     expert_model_parallel_size: int = 1
     sequence_parallel: bool = False               # Megatron-style SP inside TP regions
     use_distributed_optimizer: bool = False
-    overlap_grad_reduce: bool = True
-    overlap_param_gather: bool = True
+    overlap_grad_reduce: bool = False             # bucketed gradient reduce-scatter during backward (bitwise equal; off as in Megatron)
+    overlap_param_gather: bool = False            # accepted; the parameter all-gather is part of the fused Adam + broadcast kernel
     distributed_backend: str = "nccl"
     distributed_timeout_minutes: int = 10
     fused_comm: bool = True                       # P2P/NVLS kernels instead of NCCL where available

@@ -100,6 +100,10 @@ class Trainer:
                 any(b.fused is not None for b in self.optimizer.buffers):
             # a block's gradients are reduced while the backward pass of the blocks before it is still running
             getattr(self.model, "module", self.model).grad_ready_hook = self.optimizer.bucket_ready
+        if par.overlap_param_gather and self.mesh.rank == 0:
+            print("note: --overlap-param-gather has nothing to move: with the distributed optimizer the updated parameters are "
+                  "broadcast by the fused Adam kernel itself (multimem stores), without it there is no parameter gather",
+                  flush=True)
         self.scheduler = OptimizerParamScheduler(tc)
         self.timers = Timers(tc.timing_log_level, cuda=self.device.type == "cuda")
         self.iteration, self.consumed_samples = 0, 0
