@@ -213,7 +213,7 @@ class _VocabParallelCE(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, logits, labels, g, vocab_start, ignore_index):
-        if logits.is_cuda and os.environ.get("LMOE_TP_CE_KERNEL", "0") != "0":
+        if logits.is_cuda and os.environ.get("LMOE_TP_CE_KERNEL", "1") != "0":
             l2 = logits.reshape(-1, logits.shape[-1])
             if not l2.is_contiguous():
                 l2 = l2.contiguous()
