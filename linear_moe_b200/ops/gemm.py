@@ -216,11 +216,16 @@ class GroupedLinear(torch.autograd.Function):
     Every offset must be a multiple of :data:`ROW_ALIGN`."""
 
     @staticmethod
-    def forward(ctx, x, w, offs):
+    def forward(ctx, x, w, offs, out=None, dx_out=None):
+        """``out`` / ``dx_out``: holders (objects with a ``buf`` tensor ``[rows, N]`` / ``[rows, K]``, not tensors, so that
+        autograd does not track the workspace) into which the result / the input gradient is written instead of a fresh
+        tensor: the expert-parallel exchange lets the GEMM write straight into the buffer its peers read."""
         E, Kd, N = w.shape
-        y = torch.empty(x.shape[0], N, dtype=torch.bfloat16, device=x.device)
+        y = torch.empty(x.shape[0], N, dtype=torch.bfloat16, device=x.device) if out is None else out.buf[: x.shape[0]]
+        assert y.shape == (x.shape[0], N) and y.is_contiguous()
         _gg(x, False, w.view(E * Kd, N), True, y, 1, 0, N, Kd, E, offs, 0)
         ctx.save_for_backward(x, w, offs)
+        ctx.dx_out = dx_out
         return y
 
     @staticmethod
@@ -228,7 +233,8 @@ class GroupedLinear(torch.autograd.Function):
         x, w, offs = ctx.saved_tensors
         E, Kd, N = w.shape
         dy = dy.contiguous()
-        dx = torch.empty_like(x)
+        dx = torch.empty_like(x) if ctx.dx_out is None else ctx.dx_out.buf[: x.shape[0]]
+        assert dx.shape == x.shape and dx.is_contiguous()
         _gg(dy, False, w.view(E * Kd, N), False, dx, 1, 0, Kd, N, E, offs, 0)              # dy @ w[e]^T
         mg = getattr(w, "main_grad", None)
         if PAIRS and mg is not None and mg.dtype == torch.float32 and mg.is_contiguous() and mg.shape == w.shape:
@@ -237,10 +243,10 @@ class GroupedLinear(torch.autograd.Function):
             _gg(x, True, dy, True, mg, 2, Kd, N, 0, E, offs, Kd * N, accumulate=not fresh)
             w._main_grad_fresh = False
             w._direct_wgrad = True
-            return dx, None, None
+            return dx, None, None, None, None
         dw = torch.empty_like(w)
         _gg(x, True, dy, True, dw, 2, Kd, N, 0, E, offs, Kd * N)                           # x_e^T @ dy_e
-        return dx, dw, None
+        return dx, dw, None, None, None
 
 
 def supports_grouped(x, w1, w2) -> bool:

@@ -47,7 +47,7 @@ class _Combine(torch.autograd.Function):
         T, k = route.T, route.k
         from . import cuda as K
         d_probs = K.moe_dprobs(rows, d_out, route.dest_rank, T, k)
-        d_y = ctx.ws.push(d_out, route, w.reshape(-1))
+        d_y = ctx.ws.push(d_out, route, w.reshape(-1), keep=False)
         return d_y, d_probs.to(ctx.pdtype), None, None
 
 
@@ -56,7 +56,10 @@ def fused_moe(h: torch.Tensor, probs: torch.Tensor, idx: torch.Tensor, w1: torch
     from . import cuda as K
     route = ws.route(idx)
     xr = _Dispatch.apply(h, ws, route)
-    y1 = gemm.GroupedLinear.apply(xr, w1, route.offs)
+    # between ranks, the second GEMM writes its result, and the first GEMM's backward its input gradient, straight into
+    # the buffer the peers pull from (no copy into it)
+    res = ws.result_holder()
+    y1 = gemm.GroupedLinear.apply(xr, w1, route.offs, None, res)
     act = K.swiglu(y1)
-    y2 = gemm.GroupedLinear.apply(act, w2, route.offs)
+    y2 = gemm.GroupedLinear.apply(act, w2, route.offs, res, None)
     return _Combine.apply(y2, probs, ws, route)

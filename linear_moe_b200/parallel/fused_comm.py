@@ -464,9 +464,16 @@ class MoeWorkspace:
         self._run(1, a, "moe_assign")
         return MoeRoute(T, k, dest_rank, dest_row, offs, real)
 
-    def push(self, src: torch.Tensor, route: "MoeRoute", weights: Optional[torch.Tensor]) -> torch.Tensor:
-        """Send every (token, slot) row of ``src [T, h]`` (times ``weights [T*k]``) to its expert's rank; returns a copy
-        of this rank's receive buffer ``[cap, h]`` with zeroed padding rows."""
+    def result_holder(self):
+        """The buffer the peers pull from, for a producer that writes into it directly (``None`` on one rank, where results
+        are read where they are)."""
+        return None if self.group is None else _BufHolder(self.y)
+
+    def push(self, src: torch.Tensor, route: "MoeRoute", weights: Optional[torch.Tensor], keep: bool = True) -> torch.Tensor:
+        """Send every (token, slot) row of ``src [T, h]`` (times ``weights [T*k]``) to its expert's rank; returns this
+        rank's receive buffer ``[cap, h]`` with zeroed padding rows: a copy with ``keep`` (the forward pass saves it for the
+        weight gradient), the shared buffer itself without (the backward pass consumes it before this rank signals its
+        results, and no peer pushes again before it has pulled those)."""
         assert src.is_contiguous() and src.dtype == torch.bfloat16 and src.shape == (route.T, self.h)
         self.ep_push += 1
         a = self._args()
@@ -485,7 +492,7 @@ class MoeWorkspace:
             return x
         self._run(2, a, "moe_push")
         self._run(3, a, "moe_zero_pads")
-        return self.x.clone()
+        return self.x.clone() if keep else self.x
 
     def pull(self, y_local: torch.Tensor, route: "MoeRoute", weights: Optional[torch.Tensor], save_rows: bool):
         """Publish this rank's expert results ``[cap, h]`` and gather, weight and sum every token's ``k`` rows from their
@@ -494,8 +501,8 @@ class MoeWorkspace:
         if self.group is None:
             y_local = y_local.contiguous()
             self.peer_y.fill_(y_local.data_ptr())                # one rank: read the results where they are
-        else:
-            self.y.copy_(y_local)
+        elif y_local.data_ptr() != self.y.data_ptr():
+            self.y.copy_(y_local)                                # (the grouped GEMM normally writes into self.y itself)
         a = self._args()
         a.epoch = self.ep_pull
         out = torch.empty(route.T, self.h, dtype=torch.bfloat16, device=self.device)
@@ -507,6 +514,13 @@ class MoeWorkspace:
         self._run(4, a, "moe_signal")
         self._run(5, a, "moe_pull")
         return out, rows
+
+
+class _BufHolder:
+    """A tensor behind a plain attribute, so that it can be handed to an autograd function without being tracked."""
+
+    def __init__(self, buf):
+        self.buf = buf
 
 
 class MoeRoute:
