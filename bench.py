@@ -120,7 +120,8 @@ def main():
     tc = TrainConfig(micro_batch_size=mbs, global_batch_size=gbs, seq_length=seq, train_iters=10 ** 9, lr=1e-4, min_lr=1e-5,
                      lr_decay_style="cosine", lr_decay_iters=100000, lr_warmup_iters=100, weight_decay=0.1,
                      adam_beta1=0.9, adam_beta2=0.95, clip_grad=1.0, bf16=True, log_interval=10 ** 9, seed=1234,
-                     check_for_nan_in_loss_and_grad=False)
+                     check_for_nan_in_loss_and_grad=False,
+                     manual_gc=os.environ.get("LMOE_BENCH_MANUAL_GC", "1") != "0")
     if world > 1:
         fused_comm.init_workspaces(mesh, cfg, tc)
     trainer = Trainer(cfg, par, tc, mesh, device=dev)

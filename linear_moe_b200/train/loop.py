@@ -183,9 +183,24 @@ class Trainer:
             from ..parallel import fused_comm
             fused_comm.check_status(where or f"iteration {self.iteration + 1}")
 
+    def _manual_gc(self):
+        """``--manual-gc``: the cyclic collector is switched off and run by hand at the same step on every rank, so that a
+        collection pause on one rank does not show up as waiting time in the other ranks' collectives."""
+        import gc
+        tc = self.tc
+        if not tc.manual_gc:
+            return
+        if not getattr(self, "_gc_off", False):
+            gc.collect()
+            gc.disable()
+            self._gc_off = True
+        elif tc.manual_gc_interval and self.iteration % tc.manual_gc_interval == 0:
+            gc.collect()
+
     def train_step(self) -> Dict[str, float]:
         tc, mesh = self.tc, self.mesh
         timers = self.timers
+        self._manual_gc()
         for m in self.models:
             m.train()
         self.optimizer.zero_grad()
