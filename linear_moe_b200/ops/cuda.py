@@ -62,7 +62,14 @@ def _p(t: Optional[torch.Tensor]):
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _st():
+    """The current CUDA stream as the launchers take it.  ``torch.cuda.current_stream()`` builds a Python stream object
+    through several layers of device-index checks (~15 us, once per kernel launch); the raw query is a single C call."""
+    if _RAW_STREAM is not None:
+        return ctypes.c_void_p(_RAW_STREAM(torch.cuda.current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 

@@ -18,8 +18,14 @@ _ENABLED = os.environ.get("LMOE_TCGEN05_GEMM", "1") != "0"
 _ERR: Optional[torch.Tensor] = None
 
 
+_CUDA_OK: Optional[bool] = None
+
+
 def available() -> bool:
-    return _ENABLED and torch.cuda.is_available()
+    global _CUDA_OK
+    if _CUDA_OK is None:
+        _CUDA_OK = torch.cuda.is_available()          # asked on every linear: cache the answer
+    return _ENABLED and _CUDA_OK
 
 
 def enable(flag: bool):
