@@ -24,6 +24,8 @@ if __name__ == "__main__":
     p = build_parser()
     p.add_argument("--lm-eval-tasks", type=str, default=None, help="comma-separated lm-evaluation-harness task names")
     args = p.parse_args()
+    import logging
+    logging.basicConfig(level=getattr(logging, str(args.verbosity).upper(), logging.INFO))      # --verbosity (lm_evaluate.py)
     cfg, par, tc = configs_from_args(args)
     mesh = init_distributed(par)
     dev = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
@@ -39,7 +41,8 @@ if __name__ == "__main__":
         from linear_moe_b200.infer.lm_eval_adaptor import get_lm_eval_model
         tok, _ = build_tokenizer(args.patch_tokenizer_type, args.tokenizer_model, cfg.vocab_size, args.extra_vocab_size)
         lm = get_lm_eval_model(trainer.model, tok)
-        res = lm_eval.simple_evaluate(model=lm, tasks=args.lm_eval_tasks.split(","))
+        tasks = args.lm_eval_tasks.split(",") if args.lm_eval_tasks != "all" else args.task_list.split(",")
+        res = lm_eval.simple_evaluate(model=lm, tasks=tasks, num_fewshot=args.num_fewshot)
         if mesh.rank == 0:
             print(res["results"])
     else:

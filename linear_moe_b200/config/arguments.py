@@ -307,7 +307,8 @@ def build_parser() -> argparse.ArgumentParser:
     _flag(g, "--temperature", type=float, default=1.0)
     _flag(g, "--out-seq-length", type=int, default=1024)
     _flag(g, "--generation-length", type=int, default=None)
-    _flag(g, "--repetition-penalty", type=float, default=1.0)
+    _flag(g, "--repetition-penalty", "--repetition_penalty", type=float, default=1.0, dest="repetition_penalty")
+    _flag(g, "--verbosity", type=str, default="INFO", help="logging verbosity of the evaluation harness adaptor")
     _flag(g, "--text-generate-input-file", type=str, default="")
     _flag(g, "--text-generate-output-file", type=str, default="")
     _flag(g, "--text-generate-gt-file", type=str, default="")
