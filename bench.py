@@ -46,6 +46,20 @@ LAYOUTS = {
 }
 
 
+def resolve_layout(config: str, world: int, zero1: bool = True, overlap: bool = False, tokens_per_gpu: int = TOKENS_PER_GPU):
+    """Parallel layout and batch of a benchmark configuration on ``world`` GPUs: ``(layout entry, ParallelConfig keyword
+    arguments, sequence length, micro batch, global batch, layout name)``."""
+    layout = LAYOUTS.get(config, LAYOUTS["bench-lasp2-llama3-1b"])
+    if layout["kind"] == "cp":                       # one sequence split over all GPUs (LASP-2)
+        pkw = dict(context_parallel_size=world, use_distributed_optimizer=zero1, overlap_grad_reduce=overlap)
+        return layout, pkw, tokens_per_gpu * world, 1, 1, f"sp{world} (LASP-2)"
+    # tensor x expert parallel; the number of sequences scales with the data-parallel size
+    tp = min(layout["tp"], world)
+    pkw = dict(tensor_model_parallel_size=tp, sequence_parallel=tp > 1, expert_model_parallel_size=world // tp,
+               use_distributed_optimizer=zero1 and world > tp, overlap_grad_reduce=overlap)
+    return layout, pkw, layout["seq"], layout["mbs"], layout["mbs"] * (world // tp), f"tp{tp} ep{world // tp} dp{world // tp}"
+
+
 def parse():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
@@ -91,20 +105,9 @@ def main():
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run"
-    layout = LAYOUTS.get(args.config, LAYOUTS["bench-lasp2-llama3-1b"])
-    if layout["kind"] == "cp":                       # one sequence split over all GPUs (LASP-2)
-        par = ParallelConfig(context_parallel_size=world, use_distributed_optimizer=args.zero1, distributed_backend="nccl",
-                             overlap_grad_reduce=args.overlap_grad_reduce)
-        seq, mbs, gbs = args.tokens_per_gpu * world, 1, 1
-        layout_name = f"sp{world} (LASP-2)"
-    else:                                            # tensor x expert parallel, sequences scale with the data-parallel size
-        tp = min(layout["tp"], world)
-        par = ParallelConfig(tensor_model_parallel_size=tp, sequence_parallel=tp > 1, expert_model_parallel_size=world // tp,
-                             use_distributed_optimizer=args.zero1 and world > tp, distributed_backend="nccl",
-                             overlap_grad_reduce=args.overlap_grad_reduce)
-        seq, mbs = layout["seq"], layout["mbs"]
-        gbs = mbs * (world // tp)
-        layout_name = f"tp{tp} ep{world // tp} dp{world // tp}"
+    layout, pkw, seq, mbs, gbs, layout_name = resolve_layout(args.config, world, args.zero1, args.overlap_grad_reduce,
+                                                             args.tokens_per_gpu)
+    par = ParallelConfig(distributed_backend="nccl", **pkw)
     mesh = init_distributed(par)
     dev = torch.device("cuda", torch.cuda.current_device())
     overrides = {}

@@ -167,3 +167,17 @@ def test_rope_with_sequence_offsets_and_packed_sequences():
         assert torch.allclose(got[:, s:e], want, atol=1e-6)
     pos = ops.rope_positions(12, 1, xp.device, cu_seqlens=cu, seqlen_offsets=torch.tensor([2, 0, 9]))
     assert pos.tolist() == [[2, 3, 4, 5, 0, 9, 10, 11, 12, 13, 14, 15]]
+
+
+def test_vocab_parallel_ce_label_mapping():
+    """Label tensors handed to the per-shard softmax kernels of the vocabulary-parallel cross entropy: the local column
+    inside the shard, the ignore value for ignored rows, and a value that matches no column for targets in other shards."""
+    import torch
+    from linear_moe_b200.parallel.tensor_parallel import _ce_kernel_labels
+    labels = torch.tensor([0, 5, 9, 10, 19, 20, -100, 15])
+    inshard, fwd, bwd = _ce_kernel_labels(labels, vocab_start=10, width=10, ignore_index=-100)
+    assert inshard.tolist() == [False, False, False, True, True, False, False, True]
+    assert fwd.tolist() == [-100, -100, -100, 0, 9, -100, -100, 5]           # the forward kernel reads logit[label]: in-shard only
+    assert bwd.tolist() == [-1, -1, -1, 0, 9, -1, -100, 5]                   # -1: softmax part only; -100: no gradient
+    _, _, bwd2 = _ce_kernel_labels(torch.tensor([3, -1]), 0, 2, ignore_index=-1)
+    assert bwd2.tolist() == [-2, -1]                                          # the "nowhere" value never equals the ignore value

@@ -171,3 +171,29 @@ def test_linear_rnn_mixers_under_tensor_parallelism(la):
     # the first step pins the gradients (fp32 reduction order only); Adam's first updates then amplify rounding noise
     assert abs(gn[0] - ref_gn[0]) < 5e-4 * ref_gn[0], (gn, ref_gn)
     assert torch.allclose(torch.tensor(gn), torch.tensor(ref_gn), rtol=2e-2), (gn, ref_gn)
+
+
+def test_bench_config_layouts():
+    """``bench.py --config`` maps every benchmark configuration to a parallel layout that exists on 1, 2, 4 and 8 GPUs, and
+    the headline configuration keeps 16384 tokens per GPU."""
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location("lmoe_bench", os.path.join(os.path.dirname(os.path.dirname(__file__)), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    from linear_moe_b200.config.model_config import ParallelConfig
+    from linear_moe_b200.config.presets import get_preset
+    for name in bench.LAYOUTS:
+        cfg = get_preset(name)
+        for world in (1, 2, 4, 8):
+            layout, pkw, seq, mbs, gbs, label = bench.resolve_layout(name, world)
+            par = ParallelConfig(distributed_backend="gloo", **pkw)
+            tp, ep, cp = par.tensor_model_parallel_size, par.expert_model_parallel_size, par.context_parallel_size
+            assert world % (tp * cp) == 0 and (world // tp) % ep == 0, (name, world, label)
+            dp = world // (tp * cp)
+            assert gbs == mbs * dp and gbs * seq > 0
+            if cfg.num_experts:
+                assert cfg.num_experts % ep == 0
+            if name == "bench-lasp2-llama3-1b":
+                assert seq == 16384 * world and gbs == 1 and cp == world
+    assert bench.resolve_layout("bench-a1b-7b-hybrid", 8)[5] == "tp2 ep4 dp4"
