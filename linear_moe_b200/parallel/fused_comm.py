@@ -54,9 +54,25 @@ def _symm_empty(numel: int, dtype, device, group):
             symm.enable_symm_mem_for_group(name)
         except Exception:
             pass                                   # newer torch enables every group implicitly
-    t = symm.empty(numel, dtype=dtype, device=device)
+    # every peer-writable buffer ends in a guard region with a fixed byte pattern: a peer (or a local kernel) that writes
+    # past the logical end of a workspace lands there, and `verify_canaries` (run from `check_status` with LMOE_CANARY=1)
+    # reports which buffer was overrun
+    t = symm.empty(numel + _CANARY_ELEMS, dtype=dtype, device=device)
     hdl = symm.rendezvous(t, name if name is not None else group.pg)
-    return t, hdl
+    t[numel:].view(torch.uint8).fill_(_CANARY_BYTE)
+    _CANARIES.append((f"{group.name}:{dtype}:{numel}", t, numel))
+    return t[:numel], hdl
+
+
+_CANARY_ELEMS, _CANARY_BYTE = 256, 0xA5
+_CANARIES: list = []
+
+
+def verify_canaries():
+    """Raise if the guard region behind any symmetric workspace of this rank no longer holds its pattern."""
+    bad = [name for name, t, numel in _CANARIES if bool((t[numel:].view(torch.uint8) != _CANARY_BYTE).any())]
+    if bad:
+        raise RuntimeError(f"workspace overrun: the guard region of {bad} was overwritten")
 
 
 class _LaspArgs(ctypes.Structure):
@@ -152,6 +168,8 @@ def check_status(where: str = ""):
     """Raise ``CommTimeout`` if any fused kernel gave up on a bounded wait since the last check, or ``RuntimeError`` if
     a tcgen05 GEMM did (its error word is the second element of the same status tensor, so one read covers both), or if
     a decay too strong for the gated-scan kernels was seen (third element)."""
+    if os.environ.get("LMOE_CANARY", "0") != "0":
+        verify_canaries()
     if STATUS is None:
         return
     from ..train.watchdog import raise_on_comm_status
