@@ -197,3 +197,25 @@ def test_bench_config_layouts():
             if name == "bench-lasp2-llama3-1b":
                 assert seq == 16384 * world and gbs == 1 and cp == world
     assert bench.resolve_layout("bench-a1b-7b-hybrid", 8)[5] == "tp2 ep4 dp4"
+
+
+def test_workspace_guard_region_check():
+    """``verify_canaries`` reports a workspace whose guard region lost its byte pattern (an overrun by a peer or a kernel)."""
+    import pytest
+    import torch
+    from linear_moe_b200.parallel import fused_comm as fc
+    saved = list(fc._CANARIES)
+    try:
+        fc._CANARIES.clear()
+        numel = 100
+        t = torch.zeros(numel + fc._CANARY_ELEMS, dtype=torch.float32)
+        t[numel:].view(torch.uint8).fill_(fc._CANARY_BYTE)
+        fc._CANARIES.append(("test:float32:100", t, numel))
+        fc.verify_canaries()                                  # intact
+        t[:numel].fill_(7.0)                                  # writes inside the workspace are fine
+        fc.verify_canaries()
+        t[numel + 3] = 1.0                                    # one element past the logical end
+        with pytest.raises(RuntimeError, match="test:float32:100"):
+            fc.verify_canaries()
+    finally:
+        fc._CANARIES[:] = saved
