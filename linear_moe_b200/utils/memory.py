@@ -41,14 +41,21 @@ def compute_weight_and_optimizer_memory(cfg: ModelConfig, par: ParallelConfig, w
     c = analytic_parameter_counts(cfg)
     tp, pp, ep = par.tp, par.pp, par.ep
     dense_layers = c["transformer"] - c["experts"]
-    shard = ((dense_layers + c["experts"] / ep) / pp + c["embedding_one"]) / tp
+    dense_shard = (dense_layers / pp + c["embedding_one"]) / tp
     if not cfg.tie_embeddings and pp == 1:
-        shard += c["embedding_one"] / tp
+        dense_shard += c["embedding_one"] / tp
+    expert_shard = c["experts"] / ep / pp / tp
+    shard = dense_shard + expert_shard
     dp = 1
     if world_size:
-        dp = max(world_size // (tp * pp * par.cp), 1)
-    bytes_per = 18.0 if not par.use_distributed_optimizer else 6.0 + 12.0 / dp
-    mem = shard * bytes_per
+        dp = max(world_size // (tp * pp), 1)              # data x context parallel ranks: dense gradients are reduced over them
+    edp = max(dp // ep, 1)                                # expert-data-parallel ranks: the only ones that share an expert shard
+    # 2 (bf16 weight) + 4 (fp32 gradient) + 12 (fp32 master, two Adam moments); the distributed optimizer shards the 12
+    # bytes over the ranks that hold the same parameters: dp for dense parameters, edp for experts
+    if par.use_distributed_optimizer:
+        mem = dense_shard * (6.0 + 12.0 / dp) + expert_shard * (6.0 + 12.0 / edp)
+    else:
+        mem = shard * 18.0
     if verbose:
         print(f"Number of parameters in transformer layers in billions: {c['transformer'] / 1e9:.2f}")
         print(f"Number of parameters in embedding layers in billions: {c['embedding'] / 1e9:.2f}")

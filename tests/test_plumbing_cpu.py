@@ -219,3 +219,21 @@ def test_workspace_guard_region_check():
             fc.verify_canaries()
     finally:
         fc._CANARIES[:] = saved
+
+
+def test_memory_estimate_knows_the_expert_data_parallel_size():
+    """Weights + optimizer estimate: the distributed optimizer shards dense state over the data-parallel ranks but expert
+    state only over the expert-data-parallel ranks (none when EP uses up the data-parallel size)."""
+    from linear_moe_b200.config.model_config import ParallelConfig
+    from linear_moe_b200.config.presets import get_preset
+    from linear_moe_b200.utils.memory import analytic_parameter_counts, compute_weight_and_optimizer_memory as est
+    cfg = get_preset("bench-mixtral-mamba2-fp8")
+    c = analytic_parameter_counts(cfg)
+    par = ParallelConfig(tensor_model_parallel_size=2, expert_model_parallel_size=4, use_distributed_optimizer=True)
+    got = est(cfg, par, world_size=8)                        # dp = 4, ep = 4 -> every expert shard lives on one rank only
+    experts = c["experts"] / 4 / 2
+    assert got > experts * 18.0                              # expert state is not sharded at all
+    par16 = ParallelConfig(tensor_model_parallel_size=2, expert_model_parallel_size=4, use_distributed_optimizer=True)
+    assert est(cfg, par16, world_size=16) < got              # twice the data-parallel size: expert state halves
+    no_zero = ParallelConfig(tensor_model_parallel_size=2, expert_model_parallel_size=4)
+    assert est(cfg, no_zero, world_size=8) > got
