@@ -235,3 +235,38 @@ def test_la_mode_selects_equivalent_forms(la):
             cfg = ModelConfig(num_layers=1, hidden_size=64, num_attention_heads=2, ffn_hidden_size=128, vocab_size=512,
                               use_la_module=True, la_module=la, layer_type_list="L", la_mode="parallel")
             CausalLM(cfg)(ids)
+
+
+@pytest.mark.parametrize("T,with_state", [(50, True), (37, False), (1, True)])
+def test_rwkv6_shifted_query_identity(T, with_state, monkeypatch):
+    """RWKV6 through the gated-scan operator with queries shifted one position to the left (what the CUDA path does around
+    its kernels): output, final state and all gradients equal the token-by-token recurrence.  The kernels are stood in
+    for by the chunked torch form of the same operator."""
+    from linear_moe_b200.ops import cuda as K
+    from linear_moe_b200.ops import lsm_torch as LT
+    from linear_moe_b200.ref import lsm as RL
+
+    def inner(q, k, v, gk, scale, init, bonus, chunk):
+        assert bonus is None
+        return LT.chunk_vector_gated(q, k, v, gk, scale, init, 16, None)
+    monkeypatch.setattr(K, "lsm_vector", inner)
+    monkeypatch.setattr(K, "_note_strong_decay", lambda gk: None)
+    torch.manual_seed(12)
+    B, H, D = 2, 3, 16
+    f64 = torch.float64
+    r, k, v = [0.5 * torch.randn(B, T, H, D, dtype=f64) for _ in range(3)]
+    w = -torch.exp(torch.randn(B, T, H, D, dtype=f64) - 1.0)
+    u = 0.5 * torch.randn(H, D, dtype=f64)
+    S0 = 0.3 * torch.randn(B, H, D, D, dtype=f64) if with_state else None
+    ins = [t.clone().requires_grad_(True) for t in ([r, k, v, w, u] + ([S0] if with_state else []))]
+    o, S = K._lsm_vector_bonus(ins[0], ins[1], ins[2], ins[3], 1.0, ins[5] if with_state else None, ins[4], 64)
+    go, gS = torch.randn_like(o), 0.1 * torch.randn_like(S)
+    ((o * go).sum() + (S * gS).sum()).backward()
+    ref_in = [t.detach().clone().float().requires_grad_(True) for t in ins]
+    o2, S2 = RL.recurrent_rwkv6(ref_in[0], ref_in[1], ref_in[2], ref_in[3], ref_in[4], scale=1.0,
+                                initial_state=ref_in[5] if with_state else None)
+    ((o2 * go.float()).sum() + (S2 * gS.float()).sum()).backward()
+    rel = lambda a, b: ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-12)).item()
+    assert rel(o, o2) < 1e-5 and rel(S, S2) < 1e-5
+    for a, b in zip(ins, ref_in):
+        assert rel(a.grad, b.grad) < 1e-4
