@@ -81,6 +81,8 @@ def parse():
 
 
 def reference_arm():
+    if int(os.environ.get("RANK", "0")) != 0:          # launched as N ranks: one line, from rank 0
+        return 0
     print(json.dumps({
         "impl": "reference",
         "unavailable": "the reference is not installable offline: its source tree has no setup.py/pyproject.toml and its "
