@@ -237,3 +237,40 @@ def test_memory_estimate_knows_the_expert_data_parallel_size():
     assert est(cfg, par16, world_size=16) < got              # twice the data-parallel size: expert state halves
     no_zero = ParallelConfig(tensor_model_parallel_size=2, expert_model_parallel_size=4)
     assert est(cfg, no_zero, world_size=8) > got
+
+
+def test_direct_weight_gradient_accumulators_skip_the_zero_fill():
+    """Weights whose gradient GEMM writes its fp32 accumulator directly are not cleared by ``zero_grad``; the three guards
+    around that: (1) other accumulators are still cleared, (2) an ordinary autograd gradient arriving for such a weight
+    clears the stale accumulator before adding, (3) a direct weight that saw no gradient in a step is cleared before the
+    reduction."""
+    import torch
+    import torch.nn as nn
+    from linear_moe_b200.config.model_config import TrainConfig
+    from linear_moe_b200.dist.mesh import single_process_mesh
+    from linear_moe_b200.train.optimizer import MixedPrecisionAdam
+    torch.manual_seed(0)
+    model = nn.ModuleList([nn.Sequential(nn.Linear(8, 16, bias=False), nn.Linear(16, 8, bias=False))])
+    tc = TrainConfig(micro_batch_size=1, global_batch_size=1, seq_length=8, train_iters=4, lr=1e-2, min_lr=1e-2,
+                     lr_decay_style="constant", clip_grad=0.0, weight_decay=0.0)
+    opt = MixedPrecisionAdam(model, single_process_mesh(), tc)
+    w0, w1 = model[0][0].weight, model[0][1].weight
+    opt.zero_grad()
+    # step 1: w0's gradient is written directly (what the weight-gradient GEMM does), w1's arrives through autograd
+    assert w0._main_grad_fresh
+    w0.main_grad.copy_(torch.full_like(w0.main_grad, 3.0))
+    w0._main_grad_fresh, w0._direct_wgrad = False, True
+    w1.grad = torch.ones_like(w1)
+    opt._accumulate(w1)
+    assert torch.all(w1.main_grad == 1.0)
+    opt.zero_grad()
+    assert torch.all(w0.main_grad == 3.0), "a direct weight's accumulator is cleared lazily"           # (skipped)
+    assert torch.all(w1.main_grad == 0.0)                                                               # (1)
+    # step 2: this time w0's gradient comes through autograd: the stale 3.0 must not be added to
+    w0.grad = torch.full_like(w0, 2.0)
+    opt._accumulate(w0)
+    assert torch.all(w0.main_grad == 2.0)                                                               # (2)
+    opt.zero_grad()
+    # step 3: w0 gets no gradient at all: the reduction must not see step 2's values
+    opt.reduce_grads()
+    assert torch.all(w0.main_grad == 0.0)                                                               # (3)
