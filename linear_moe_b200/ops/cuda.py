@@ -1073,6 +1073,12 @@ def lsm_scalar(q, k, v, g, scale, initial_state, chunk_size):
         s0 = None if initial_state is None else F.pad(initial_state, (0, D - Dv))
         o, S = lsm_scalar(q, k, F.pad(v, (0, D - Dv)), g, scale, s0, chunk_size)
         return o[..., :Dv], (None if S is None else S[..., :Dv])
+    if (not ok and q.dtype == torch.bfloat16 and k.dtype == q.dtype and v.dtype == q.dtype and k.shape[-1] == D
+            and q.shape[1] > 1 and os.environ.get("LMOE_LSM_BLOCKED", "1") != "0"):
+        # any other feature / value width (Based and Rebased feature maps, the normaliser's column of ones): the sum of
+        # the kernel over 128-wide key blocks, one call per value block
+        from .lsm_blocked import blocked_scalar
+        return blocked_scalar(lsm_scalar, q, k, v, g, scale, initial_state, chunk_size)
     if not ok:
         return LT.chunk_scalar_gated(q, k, v, g, scale, initial_state, chunk_size)
     scale = D ** -0.5 if scale is None else scale
