@@ -67,12 +67,17 @@ def build_cuda(verbose: bool = False, extra_flags=()) -> str:
     return so
 
 
-def build_host(verbose: bool = False) -> str:
-    os.makedirs(LIB, exist_ok=True)
+def build_host(verbose: bool = False, sanitize: bool = False, out_dir: str = None) -> str:
+    """``sanitize``: an AddressSanitizer + UndefinedBehaviorSanitizer build (``liblmoe_host_asan.so``) for the tests that
+    run the host helpers under the sanitizers; it is loaded into a process that preloads the ASan runtime."""
+    out_dir = out_dir or LIB
+    os.makedirs(out_dir, exist_ok=True)
     srcs = sorted(glob.glob(os.path.join(CSRC, "host", "*.cpp")))
-    so = os.path.join(LIB, "liblmoe_host.so")
+    so = os.path.join(out_dir, "liblmoe_host_asan.so" if sanitize else "liblmoe_host.so")
     if srcs and _newer(so, srcs):
-        _run(["g++", "-O3", "-std=c++17", "-fPIC", "-shared", "-o", so, *srcs])
+        flags = ["-O1", "-g", "-fsanitize=address,undefined", "-fno-sanitize-recover=all", "-fno-omit-frame-pointer"] \
+            if sanitize else ["-O3"]
+        _run(["g++", *flags, "-std=c++17", "-fPIC", "-shared", "-pthread", "-o", so, *srcs])
     return so
 
 

@@ -66,6 +66,7 @@ class IndexedDataset:
         self.doc_idx = np.frombuffer(idx, dtype=np.int64, count=n_doc,
                                      offset=offset + self.sizes.nbytes + self.pointers.nbytes)
         self.data = np.memmap(prefix + ".bin", mode="r", order="C")
+        self.dtype_code = code
 
     def __len__(self):
         return len(self.sizes)
@@ -136,6 +137,10 @@ class GPTDataset(torch.utils.data.Dataset):
         self.doc_idx = np.concatenate([rng.permutation(docs) for _ in range(epochs)]).astype(np.int64)
         self.sample_idx = build_sample_idx(np.asarray(indexed.sizes), self.doc_idx, seq_length, epochs, tokens_per_epoch)
         self.shuffle_idx = rng.permutation(len(self.sample_idx) - 1)
+        # aligned in-memory copies of the two per-document tables for the native gather (they sit at unaligned offsets
+        # of the memory-mapped .idx file)
+        self._sizes = np.require(indexed.sizes, dtype=np.int32, requirements=["C", "A"])
+        self._pointers = np.require(indexed.pointers, dtype=np.int64, requirements=["C", "A"])
 
     def __len__(self):
         return len(self.shuffle_idx)
@@ -152,6 +157,20 @@ class GPTDataset(torch.utils.data.Dataset):
             toks = np.concatenate(parts)
         return {"text": torch.from_numpy(toks.astype(np.int64))}
 
+    def __getitems__(self, indices):
+        """Batched fetch (``torch.utils.data`` calls this with a whole batch of indices): one native call assembles all
+        samples from the memory-mapped file on several host threads; without the host library, one by one."""
+        from ..utils import hostlib
+        lib = hostlib.load()
+        if lib is None or np.dtype(self.ds.dtype).kind not in "iu":
+            return [self[i] for i in indices]
+        n = len(self.shuffle_idx)
+        rows = self.shuffle_idx[np.asarray(indices, dtype=np.int64) % n]
+        toks = hostlib.gather_gpt_samples(lib, self.ds.data, self.ds.dtype_code, self._sizes, self._pointers,
+                                          self.doc_idx, self.sample_idx, rows, self.seq)
+        batch = torch.from_numpy(toks)
+        return [{"text": batch[i]} for i in range(len(rows))]
+
 
 class BlendedDataset(torch.utils.data.Dataset):
     """Weighted mixture of datasets: sample i comes from the dataset whose running share is furthest
@@ -161,6 +180,13 @@ class BlendedDataset(torch.utils.data.Dataset):
         w = np.asarray(weights, dtype=np.float64)
         w = w / w.sum()
         self.datasets = datasets
+        if not 1 <= len(datasets) <= 256:
+            raise ValueError(f"a blend takes 1 to 256 datasets, got {len(datasets)}")
+        from ..utils import hostlib
+        lib = hostlib.load()
+        if lib is not None:
+            self.ds_index, self.ds_sample = hostlib.build_blending_indices(lib, w, size)
+            return
         self.ds_index = np.zeros(size, dtype=np.uint8)
         self.ds_sample = np.zeros(size, dtype=np.int64)
         counts = np.zeros(len(datasets), dtype=np.int64)
