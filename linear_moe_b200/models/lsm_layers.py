@@ -412,14 +412,17 @@ class LinearRNN(nn.Module):
     """HGRN2 / RWKV6 / RWKV7 token mixers.  Under tensor parallelism the heads are split over the TP ranks: every
     projection into key / value space keeps its ranks' rows, the per-head vectors are sliced, the low-rank mixers in
     front of them stay replicated (their gradients are completed by an all-reduce at the sharded projections' inputs)
-    and ``o_proj`` is row-parallel.  (The reference builds these mixers without TP support.)"""
+    and ``o_proj`` is row-parallel (reduce-scattering along T under sequence parallelism).  (The reference builds these
+    mixers without TP support.)"""
 
     def __init__(self, cfg: ModelConfig, mesh: Optional[Mesh] = None, layer_number: int = 1, key: str = "",
                  sequence_parallel: bool = False, device=None):
         super().__init__()
         self.cfg, self.mesh = cfg, mesh or single_process_mesh()
         tp = self.mesh.tp
-        assert not (sequence_parallel and tp > 1), "LinearRNN mixers: tensor parallelism without sequence parallelism only"
+        # sequence parallelism: the block's input arrives split along T over the TP ranks; it is gathered at the entry
+        # (every rank then holds the complete input gradient, so the backward is a slice) and o_proj reduce-scatters
+        self.sp = sequence_parallel and tp > 1
         assert cfg.num_attention_heads % tp == 0, "heads must divide over the tensor-parallel ranks"
         self.kind = cfg.la_module
         H, hid = cfg.num_attention_heads, cfg.hidden_size
@@ -462,7 +465,7 @@ class LinearRNN(nn.Module):
                     m.weight.copy_(init_normal(tuple(m.weight.shape), cfg.init_method_std, f"{key}.{name}.weight", device))
         out_std = cfg.init_method_std / math.sqrt(2.0 * cfg.num_layers)
         self.o_proj = RowParallelLinear(self.value_dim, hid, mesh=self.mesh, std=out_std, key=key + ".o_proj",
-                                        dtype=dt, device=device)
+                                        sequence_parallel=self.sp, dtype=dt, device=device)
         self.norm_weight = nn.Parameter(torch.ones(self.dv, **kw)) if cfg.la_output_norm != "identity" else None
         self.tp_in = _HeadShardedInput(self.mesh, tp > 1)
         if tp > 1:
@@ -517,6 +520,8 @@ class LinearRNN(nn.Module):
         return o
 
     def forward(self, x, cache: Optional[dict] = None, lower_bound: Optional[torch.Tensor] = None, **_):
+        if self.sp:
+            x = C.gather_no_reduce(x, self.mesh["tp"], dim=1)
         B, T, hid = x.shape
         H, act = self.H, R.ACT2FN[self.cfg.la_gate_fn]
         hv = lambda t, d: t.reshape(B, T, H, d)

@@ -155,17 +155,19 @@ def _train_rnn(mesh, par, la, steps=3, seq=64):
     return [float(o["lm loss"]) for o in out], [o["grad_norm"] for o in out]
 
 
-def _worker_rnn(rank, world, la):
-    par = ParallelConfig(distributed_backend="gloo", tensor_model_parallel_size=2)
+def _worker_rnn(rank, world, la, sp=False):
+    par = ParallelConfig(distributed_backend="gloo", tensor_model_parallel_size=2, sequence_parallel=sp)
     return _train_rnn(Mesh(par), par, la)
 
 
-@pytest.mark.parametrize("la", ["hgrn2", "rwkv6", "rwkv7"])
-def test_linear_rnn_mixers_under_tensor_parallelism(la):
+@pytest.mark.parametrize("la,sp", [("hgrn2", False), ("rwkv6", False), ("rwkv7", False),
+                                   ("hgrn2", True), ("rwkv6", True), ("rwkv7", True)])
+def test_linear_rnn_mixers_under_tensor_parallelism(la, sp):
     """HGRN2 / RWKV6 / RWKV7 with their heads split over two tensor-parallel ranks train like the single-process model
-    (sharded projections, sliced per-head vectors, replicated low-rank mixers with completed gradients)."""
+    (sharded projections, sliced per-head vectors, replicated low-rank mixers with completed gradients), with and without
+    sequence parallelism (input gathered along T at the mixer's entry, output reduce-scattered)."""
     ref_losses, ref_gn = _train_rnn(single_process_mesh(), ParallelConfig(), la)
-    outs = run_distributed(_worker_rnn, 2, la=la)
+    outs = run_distributed(_worker_rnn, 2, la=la, sp=sp)
     losses, gn = outs[0]
     assert torch.allclose(torch.tensor(losses), torch.tensor(ref_losses), atol=2e-4), (losses, ref_losses)
     # the first step pins the gradients (fp32 reduction order only); Adam's first updates then amplify rounding noise
