@@ -89,6 +89,8 @@ class SelfAttention(nn.Module):
             self.q_layernorm.weight = nn.Parameter(torch.ones(D, dtype=dt, device=device))
             self.k_layernorm = nn.Module()
             self.k_layernorm.weight = nn.Parameter(torch.ones(D, dtype=dt, device=device))
+            # shared by all heads, applied to this rank's heads: the optimizer sums the partial gradients over TP
+            self.q_layernorm.weight.tp_partial_grad = self.k_layernorm.weight.tp_partial_grad = True
         self.rope = RotaryCache(cfg, D) if cfg.position_embedding_type == "rope" else None
 
     def forward(self, x, cache: Optional[dict] = None, position_offset: int = 0, **_):
@@ -179,8 +181,12 @@ class MLASelfAttention(nn.Module):
 
     def forward(self, x, cache: Optional[dict] = None, position_offset: int = 0, **_):
         cfg = self.cfg
+        tp = self.mesh["tp"]
         if self.sp:
-            x = C.all_gather(x, self.mesh["tp"], dim=1)
+            # every path from x into head-sharded work passes a point that all-reduces its gradient (the column-parallel
+            # up-projections, the shared rope key below), so each rank ends up with the complete gradient of the
+            # gathered input and the backward of the gather is a slice
+            x = C.gather_no_reduce(x, tp, dim=1)
         B, T, _ = x.shape
         if cfg.q_lora_rank is None:
             q = self.linear_q_proj(x)
@@ -202,6 +208,8 @@ class MLASelfAttention(nn.Module):
         # before rotating (yarn_rotary_pos_embedding.py:198-202): same as rotating interleaved pairs.
         q_pe = ops.apply_rope(q_pe.contiguous(), cos, sin, True)
         k_pe = ops.apply_rope(k_pe.reshape(B, T, 1, self.dr).contiguous(), cos, sin, True)
+        if not tp.is_trivial:
+            k_pe = C.copy_to_region(k_pe, tp)       # one rope key for all heads: its gradient is the sum over every rank's heads
         qf = torch.cat([q_nope, q_pe], dim=-1)
         kf = torch.cat([k_nope, k_pe.expand(B, T, self.Hl, self.dr)], dim=-1)
         kf, v, q_off = _kv_cache_update(cache, kf, v)

@@ -153,7 +153,28 @@ def elu_p1(x):
     return F.elu(x) + 1.0
 
 
-def build_feature_map(name: Optional[str], head_dim: int) -> Optional[nn.Module]:
+def keyed_init(module: nn.Module, key: str, device=None) -> nn.Module:
+    """Re-draw every ``nn.Linear`` inside a learnable feature map from a generator seeded by ``(init seed, key)``, with
+    ``nn.Linear``'s own bound ``1 / sqrt(fan_in)``: the constructor drew them from the process-global generator, which is
+    seeded differently on every data- and context-parallel rank, so replicas would start from different weights.
+    Hedgehog's identity initialisation is left alone."""
+    from ..parallel.tensor_parallel import init_uniform
+    if module is None or isinstance(module, Hedgehog):
+        return module
+    with torch.no_grad():
+        for name, m in module.named_modules():
+            if isinstance(m, nn.Linear):
+                bound = 1.0 / math.sqrt(m.in_features)
+                m.weight.copy_(init_uniform(tuple(m.weight.shape), -bound, bound, f"{key}.{name}.weight", device))
+                if m.bias is not None:
+                    m.bias.copy_(init_uniform(tuple(m.bias.shape), -bound, bound, f"{key}.{name}.bias", device))
+    return module
+
+
+def build_feature_map(name: Optional[str], head_dim: int, key: Optional[str] = None) -> Optional[nn.Module]:
+    """``key``: parameter-name prefix that seeds the learnable maps' initial weights (same on every rank)."""
+    if key is not None:
+        return keyed_init(build_feature_map(name, head_dim), key)
     if name is None:
         return None
     simple = {

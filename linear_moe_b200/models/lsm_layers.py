@@ -198,9 +198,9 @@ class LSMCore(nn.Module):
         elif kind == "rebased":
             self.feature_map_q = self.feature_map_k = RebasedMap(dk)
         elif kind in ("linear_attention", "lightning_attention", "retention", "gla", "gsa"):
-            self.feature_map_q = build_feature_map(fm, dk)
+            self.feature_map_q = build_feature_map(fm, dk, key + ".feature_map_q")
             self.feature_map_k = self.feature_map_q if (cfg.la_tie_feature_map_qk or fm is None) else \
-                build_feature_map(fm, dk)
+                build_feature_map(fm, dk, key + ".feature_map_k")
         else:
             self.feature_map_q = self.feature_map_k = None
         if kind == "lightning_attention":
@@ -216,6 +216,12 @@ class LSMCore(nn.Module):
                 self.la_output_norm.bias = nn.Parameter(torch.zeros(dv, dtype=dt, device=device))
         else:
             self.la_output_norm = None
+        # replicated over the tensor-parallel ranks but applied to the rank's own heads only: every rank holds a partial
+        # gradient, which the optimizer sums over the TP group
+        shared = [self.la_output_norm, self.feature_map_q, self.feature_map_k]
+        for mod in shared:
+            for p in (mod.parameters() if mod is not None else ()):
+                p.tp_partial_grad = True
 
     # -- helpers --------------------------------------------------------
     def _run(self, op: str, q, k, v, cache, name="state", **kw):
@@ -463,6 +469,8 @@ class LinearRNN(nn.Module):
             if isinstance(m, nn.Linear):
                 with torch.no_grad():
                     m.weight.copy_(init_normal(tuple(m.weight.shape), cfg.init_method_std, f"{key}.{name}.weight", device))
+                    if m.bias is not None:
+                        m.bias.zero_()       # nn.Linear drew it from the process-global generator: not the same on every rank
         out_std = cfg.init_method_std / math.sqrt(2.0 * cfg.num_layers)
         self.o_proj = RowParallelLinear(self.value_dim, hid, mesh=self.mesh, std=out_std, key=key + ".o_proj",
                                         sequence_parallel=self.sp, dtype=dt, device=device)
@@ -538,7 +546,6 @@ class LinearRNN(nn.Module):
                           scale=1.0, bonus=self.bonus)
             o = self._out_norm(o).reshape(B, T, -1) * act(g)
         elif self.kind == "rwkv7":
-            assert self.mesh["cp"].is_trivial, "rwkv7: sequence parallelism not available"
             delta = self._shift(x, cache) - x
             xr, xw, xk, xv, xa, xg = torch.addcmul(x[None], delta[None], self.x.view(6, 1, 1, -1)).unbind(0)
             r = self.r_proj(self.tp_in(xr))
@@ -548,11 +555,8 @@ class LinearRNN(nn.Module):
             g = self.g_proj(xg)
             kk = ops.l2_norm(hv(k * self.removal, self.dk)).reshape(B, T, -1)
             k = torch.addcmul(k, k * (a - 1), self.booster)
-            init = cache.get("state") if cache is not None else None
-            o, S = ops.lsm_dplr(hv(r, self.dk), hv(w, self.dk), hv(k, self.dk), hv(v, self.dv), hv(-kk, self.dk),
-                                hv(kk * a, self.dk), 1.0, init)
-            if cache is not None:
-                cache["state"] = S.detach()
+            o = self._run("dplr", hv(r, self.dk), hv(k, self.dk), hv(v, self.dv), cache, gk=hv(w, self.dk), scale=1.0,
+                          dplr=(hv(-kk, self.dk), hv(kk * a, self.dk)))
             o = self._out_norm(o.to(x.dtype))
             o = o + ((hv(r, self.dk) * hv(k, self.dk) * self.bonus).sum(-1, keepdim=True) * hv(v, self.dv))
             o = o.reshape(B, T, -1) * act(g)

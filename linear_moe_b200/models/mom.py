@@ -23,6 +23,7 @@ import torch.nn.functional as F
 
 from .. import ops
 from ..config.model_config import ModelConfig
+from ..dist import collectives as C
 from ..dist.mesh import Mesh, single_process_mesh
 from ..parallel.tensor_parallel import ColumnParallelLinear, RowParallelLinear, init_normal, init_uniform
 from .lsm_layers import GLAGate, LSMCore, _tp_slice
@@ -83,8 +84,9 @@ class MomLinearAttention(nn.Module):
         self.dk, self.dv = cfg.key_dim // H, cfg.value_dim // H
         self.M, self.topk, self.capacity, self.shared_mem = cfg.mom_num_memories, cfg.mom_topk, cfg.mom_capacity, cfg.mom_shared_mem
         dt, std = cfg.params_dtype, cfg.init_method_std
-        sp = sequence_parallel
-        assert not sp, "MoM: Megatron sequence parallelism is not available"
+        # sequence parallelism: gather the input along T at the entry (every path below completes its input gradient over
+        # the TP ranks, so the backward of the gather is a slice), reduce-scatter at o_proj
+        self.sp = sequence_parallel and mesh.tp > 1
         qkv_bias = (cfg.add_bias_linear or cfg.add_qkv_bias) if cfg.base_model == "qwen2" else cfg.add_bias_linear
         self.gate = nn.Linear(cfg.hidden_size, self.M, bias=False, dtype=dt, device=device)
         with torch.no_grad():
@@ -116,11 +118,12 @@ class MomLinearAttention(nn.Module):
             self.dt_bias = nn.Parameter(_tp_slice(dtv + torch.log(-torch.expm1(-dtv)), mesh))
             for p in (self.A_log, self.D, self.dt_bias):
                 p._no_weight_decay = True
+                p.tensor_parallel, p.partition_dim, p.partition_stride = mesh.tp > 1, 0, 1
         self.core_linear_attention = LSMCore(core_cfg, mesh, self.Hl, self.dk, self.dv,
                                              key + ".core_linear_attention", device)
         self.o_proj = RowParallelLinear(cfg.value_dim, cfg.hidden_size, mesh=mesh, bias=cfg.add_bias_linear,
-                                        std=std / math.sqrt(2.0 * cfg.num_layers), key=key + ".o_proj", dtype=dt,
-                                        device=device)
+                                        std=std / math.sqrt(2.0 * cfg.num_layers), key=key + ".o_proj",
+                                        sequence_parallel=self.sp, dtype=dt, device=device)
 
     def _extras(self, x, gk_proj, beta_proj, a_proj):
         B, T = x.shape[:2]
@@ -138,12 +141,17 @@ class MomLinearAttention(nn.Module):
 
     def forward(self, x, cache: Optional[dict] = None, **_):
         assert cache is None or x.shape[1] >= 1
+        tp = self.mesh["tp"]
+        if self.sp:
+            x = C.gather_no_reduce(x, tp, dim=1)
         B, T, _ = x.shape
         M, k = self.M, self.topk
         gate = self.o_gate_proj(x)
         scores = F.softmax(self.gate(x).float(), dim=-1)
         w, sel = torch.topk(scores, k, dim=-1)
         w = (w / w.sum(-1, keepdim=True)).to(x.dtype)
+        if not tp.is_trivial:
+            w = C.copy_to_region(w, tp)     # the routing weights scale this rank's heads only: sum their gradient over TP
         L = math.ceil(T / k * self.capacity)
         slot, gidx = mom_plan(sel, M, L)
         xm = mom_transform(x, gidx)                                           # [M,B,L,h]

@@ -16,7 +16,7 @@ collectives so that autograd produces the mirrored backward (gather of state gra
 suffix combine).  On CUDA the scalar-decay family (constant or data-dependent decay) and the
 key-channel-gated family take the fused paths ``ops.cuda.lasp2_scalar`` / ``lasp2_vector`` instead,
 where the exchange happens inside the combine kernel through peer memory; the delta-rule
-families (whose transition is a ``dk x dk`` matrix) use the form below.
+families and RWKV7's diagonal-plus-low-rank transition (``dk x dk`` matrices) use the form below.
 """
 from __future__ import annotations
 
@@ -29,9 +29,19 @@ from ..dist import collectives as C
 from ..dist.mesh import Group
 
 
-def _summaries(kind: str, q, k, v, g, gk, beta, scale, chunk_size, bonus):
+def _summaries(kind: str, q, k, v, g, gk, beta, scale, chunk_size, bonus, dplr=None):
     """Local state from zero ``M`` and transition ``A`` of this rank's slice."""
     B, T, H, dk = k.shape
+    if kind == "dplr":
+        # RWKV7: S_t = (diag(e^{w_t}) + b_t a_t^T) S_{t-1} + k_t v_t^T; the slice's transition is the product of the
+        # per-token matrices, read off by sending the identity through the recurrence with zero values
+        a, b = dplr
+        sc = 1.0 if scale is None else scale
+        _, M = ops.lsm_dplr(q, gk, k, v, a, b, sc, None)
+        eye = torch.eye(dk, dtype=torch.float32, device=k.device).expand(B, H, dk, dk)
+        zeros = torch.zeros(B, T, H, dk, dtype=v.dtype, device=v.device)
+        _, A = ops.lsm_dplr(q, gk, k, zeros, a, b, sc, eye)
+        return M, A
     if kind == "scalar":
         _, M = ops.lsm_scalar(q, k, v, g, scale, None, chunk_size)
         if g is None:
@@ -60,7 +70,7 @@ def _apply(kind: str, A, P):
         return P * A[..., None, None]
     if kind == "vector":
         return P * A[..., None]
-    return A @ P
+    return A @ P                       # delta rule and DPLR: a dk x dk matrix per head
 
 
 def _recurrent(kind, q, k, v, g, gk, beta, scale, init, bonus):
@@ -100,15 +110,19 @@ def _parallel(kind, q, k, v, g, scale, init):
 
 
 def lasp2(kind: str, q, k, v, *, group: Group, g=None, gk=None, beta=None, scale=None,
-          chunk_size: int = 64, bonus=None, initial_state=None, mode: str = "chunk") -> Tuple[torch.Tensor, torch.Tensor]:
+          chunk_size: int = 64, bonus=None, initial_state=None, mode: str = "chunk",
+          dplr=None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Run a linear sequence model whose sequence is split over ``group`` (rank order = sequence
-    order).  ``kind``: ``scalar`` | ``vector`` | ``delta``.  Returns the local output and the state
+    order).  ``kind``: ``scalar`` | ``vector`` | ``delta`` | ``dplr`` (RWKV7: ``q`` = receptance, ``gk`` = log decay,
+    ``dplr = (a, b)`` the low-rank factors of the transition).  Returns the local output and the state
     after this rank's slice.  ``mode`` (``--la-mode``): ``chunk`` / ``fused_chunk`` = the chunked kernels (one fused
     implementation serves both names), ``fused_recurrent`` = token recurrence, ``parallel`` = quadratic form."""
     if mode not in ("chunk", "fused_chunk", "fused_recurrent", "parallel"):
         raise ValueError(f"unknown --la-mode {mode!r}")
 
     def run(init):
+        if kind == "dplr":
+            return ops.lsm_dplr(q, gk, k, v, dplr[0], dplr[1], 1.0 if scale is None else scale, init)
         if mode == "fused_recurrent":
             return _recurrent(kind, q, k, v, g, gk, beta, scale, init, bonus)
         if mode == "parallel":
@@ -130,7 +144,7 @@ def lasp2(kind: str, q, k, v, *, group: Group, g=None, gk=None, beta=None, scale
             and ops._K().fused_lasp_available(group, q, k, v, None)):
         return ops._K().lasp2_vector(q, k, v, gk, scale, group, chunk_size)
 
-    M, A = _summaries(kind, q, k, v, g, gk, beta, scale, chunk_size, bonus)
+    M, A = _summaries(kind, q, k, v, g, gk, beta, scale, chunk_size, bonus, dplr)
     W, r = group.size, group.rank
     allM = C.all_gather(M[None].contiguous(), group, dim=0)                 # [W, B, H, dk, dv]
     allA = None if A is None else C.all_gather(A[None].contiguous(), group, dim=0)

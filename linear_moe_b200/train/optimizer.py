@@ -128,6 +128,7 @@ class MixedPrecisionAdam:
                 seen.add(id(p))
                 uniq.append((n, p))
         self.named = uniq
+        self._tp_partial = mesh.tp > 1 and any(getattr(p, "tp_partial_grad", False) for _, p in uniq)
         groups: Dict[Tuple[bool, bool], List[Tuple[str, nn.Parameter]]] = {}
         for n, p in uniq:
             key = (bool(getattr(p, "expert_parallel", False)), not _no_weight_decay(n, p))
@@ -207,10 +208,15 @@ class MixedPrecisionAdam:
 
     # ------------------------------------------------------------------
     def _reduce_sequence_parallel_grads(self):
-        if not self.sequence_parallel:
+        """Complete, over the tensor-parallel group, the gradients of replicated parameters that every rank computes
+        from only part of the data: those applied to the sequence-sharded stream under sequence parallelism
+        (``sequence_parallel_grad``: norm weights, router) and those applied per head to the rank's own heads
+        (``tp_partial_grad``: per-head output norms, q / k layer norms, learnable feature maps).  One all-reduce."""
+        if self.mesh.tp <= 1:
             return
         g = self.mesh["tp"]
-        ts = [p.main_grad for _, p in self.named if getattr(p, "sequence_parallel_grad", False)]
+        ts = [p.main_grad for _, p in self.named
+              if getattr(p, "tp_partial_grad", False) or (self.sequence_parallel and getattr(p, "sequence_parallel_grad", False))]
         if ts:
             flat = torch.cat([t.reshape(-1) for t in ts])
             C.all_reduce_(flat, g)
@@ -236,8 +242,8 @@ class MixedPrecisionAdam:
         input): the reduce-scatter of that block's range starts at once on a side stream, overlapping the backward of the
         blocks before it (Megatron's ``overlap_grad_reduce``, training.py:278-298).  Only the fused NVLS buffers and only
         the last micro-batch of a step take part; everything else is reduced by :meth:`reduce_grads`."""
-        if not (self.overlap_grad_reduce and self.overlap_active) or self.sequence_parallel:
-            return
+        if not (self.overlap_grad_reduce and self.overlap_active) or self.sequence_parallel or self._tp_partial:
+            return                    # gradients that still need the tensor-parallel all-reduce must not be reduced early
         fused = [b for b in self.buffers if b.fused is not None]
         if not fused:
             return

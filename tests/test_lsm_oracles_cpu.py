@@ -214,6 +214,46 @@ def test_lasp2_matches_one_rank(kind, world):
         _close(torch.cat([o[2][i] for o in outs], 1), x.grad, 2e-3)
 
 
+def _dplr_inputs(B, T, H, dk, dv):
+    gen = torch.Generator().manual_seed(5)
+    rn = lambda *s: torch.randn(*s, generator=gen)
+    r, k, v = rn(B, T, H, dk), rn(B, T, H, dk) * 0.5, rn(B, T, H, dv)
+    w = -0.6 * torch.sigmoid(rn(B, T, H, dk))                                   # RWKV7's bounded log decay
+    kk = torch.nn.functional.normalize(rn(B, T, H, dk), dim=-1)
+    a = torch.sigmoid(rn(B, T, H, dk))
+    return r, w, k, v, -kk, kk * a, rn(B, T, H, dv)
+
+
+def _dplr_worker(rank, world):
+    from linear_moe_b200.config.model_config import ParallelConfig
+    from linear_moe_b200.dist.mesh import Mesh
+    from linear_moe_b200.parallel.lasp2 import lasp2
+    mesh = Mesh(ParallelConfig(context_parallel_size=world))
+    B, T, H, dk, dv = 1, 24 * world, 2, 8, 12
+    r, w, k, v, a, b, go = _dplr_inputs(B, T, H, dk, dv)
+    sl = slice(rank * (T // world), (rank + 1) * (T // world))
+    loc = [t[:, sl].clone().requires_grad_(True) for t in (r, w, k, v, a, b)]
+    o, S = lasp2("dplr", loc[0], loc[2], loc[3], group=mesh["cp"], gk=loc[1], scale=1.0, dplr=(loc[4], loc[5]))
+    (o * go[:, sl]).sum().backward()
+    return o.detach(), S.detach(), [t.grad for t in loc]
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_lasp2_dplr_matches_one_rank(world):
+    """RWKV7's diagonal-plus-low-rank recurrence with the sequence split over ranks: outputs, final state and every input
+    gradient equal the unsplit recurrence."""
+    outs = run_distributed(_dplr_worker, world)
+    B, T, H, dk, dv = 1, 24 * world, 2, 8, 12
+    *xs, go = _dplr_inputs(B, T, H, dk, dv)
+    xs = [t.clone().requires_grad_(True) for t in xs]
+    o_ref, S_ref = L.recurrent_dplr(*xs, 1.0, None)
+    (o_ref * go).sum().backward()
+    _close(torch.cat([o[0] for o in outs], 1), o_ref, 1e-4)
+    _close(outs[-1][1], S_ref, 1e-4)
+    for i, x in enumerate(xs):
+        _close(torch.cat([o[2][i] for o in outs], 1), x.grad, 5e-4)
+
+
 @pytest.mark.parametrize("la", ["retention", "gla", "deltanet"])
 def test_la_mode_selects_equivalent_forms(la):
     """``--la-mode``: chunk / fused_chunk (chunked form), fused_recurrent (token recurrence) and, for the scalar-decay

@@ -175,6 +175,81 @@ def test_linear_rnn_mixers_under_tensor_parallelism(la, sp):
     assert torch.allclose(torch.tensor(gn), torch.tensor(ref_gn), rtol=2e-2), (gn, ref_gn)
 
 
+def _worker_rnn_cp(rank, world, la):
+    par = ParallelConfig(distributed_backend="gloo", context_parallel_size=2)
+    return _train_rnn(Mesh(par), par, la)
+
+
+@pytest.mark.parametrize("la", ["hgrn2", "rwkv6", "rwkv7"])
+def test_linear_rnn_mixers_under_context_parallelism(la):
+    """The same mixers with the sequence split over two ranks (token-shift halo from the rank before, LASP-2 exchange of
+    the state summaries; RWKV7's transition is a matrix per head) train like the single-process model."""
+    ref_losses, ref_gn = _train_rnn(single_process_mesh(), ParallelConfig(), la)
+    outs = run_distributed(_worker_rnn_cp, 2, la=la)
+    losses, gn = outs[0]
+    assert torch.allclose(torch.tensor(losses), torch.tensor(ref_losses), atol=3e-4), (losses, ref_losses)
+    assert abs(gn[0] - ref_gn[0]) < 1e-3 * ref_gn[0], (gn, ref_gn)
+
+
+def _reduced_grads(mesh, par, kw):
+    cfg = get_preset("bench-cpu-plumbing", **kw)
+    tc = TrainConfig(micro_batch_size=2, global_batch_size=2, seq_length=64, train_iters=1, lr=1e-3, min_lr=1e-3,
+                     lr_decay_style="constant", weight_decay=0.0, clip_grad=0.0, log_interval=1000, seed=0)
+    ds = SyntheticTokenDataset(cfg.vocab_size, 64, num_samples=2, seed=0)
+    tr = Trainer(cfg, par, tc, mesh, device=torch.device("cpu"), dataset=ds)
+    for m in tr.models:
+        m.train()
+    tr.optimizer.zero_grad()
+    tr._run_schedule()
+    tr.optimizer.reduce_grads()
+    return {n: (p.main_grad.clone().float(), bool(getattr(p, "tensor_parallel", False))) for n, p in tr.optimizer.named}
+
+
+def _worker_reduced_grads(rank, world, kw, sp):
+    par = ParallelConfig(distributed_backend="gloo", tensor_model_parallel_size=2, sequence_parallel=sp)
+    return _reduced_grads(Mesh(par), par, kw)
+
+
+_TP_GRAD_CASES = {
+    "lightning": (dict(la_module="lightning_attention"), True),
+    "retention_t2r": (dict(la_module="retention", la_feature_map="t2r"), True),
+    "gla_groupnorm": (dict(la_module="gla", la_feature_map=None, la_output_norm="groupnorm"), True),
+    "rebased": (dict(la_module="rebased", la_feature_map=None, kv_channels=16), True),
+    "mom_gla": (dict(la_module="mom_gla", la_feature_map=None), True),
+    "mom_gdn_nosp": (dict(la_module="mom_gated_deltanet", la_feature_map=None, num_experts=None, ffn_hidden_size=256), False),
+    "attn_qk_layernorm": (dict(layer_type_list="NN", qk_layernorm=True), True),
+    "mla": (dict(base_model="deepseek_v2", kv_lora_rank=32, q_lora_rank=32, qk_nope_head_dim=16, qk_rope_head_dim=8,
+                 v_head_dim=16, layer_type_list="NN", use_la_module=False), True),
+    "mla_nosp": (dict(base_model="deepseek_v2", kv_lora_rank=32, q_lora_rank=None, qk_nope_head_dim=16, qk_rope_head_dim=8,
+                      v_head_dim=16, layer_type_list="NN", use_la_module=False, num_experts=None, ffn_hidden_size=256), False),
+}
+
+
+@pytest.mark.parametrize("case", list(_TP_GRAD_CASES))
+def test_replicated_parameter_gradients_under_tensor_parallelism(case):
+    """After the gradient reduction, every parameter that is replicated over the tensor-parallel ranks holds, on both
+    ranks, the gradient of the single-process model: parameters shared by all heads but applied to the rank's own heads
+    (per-head output norms, q / k layer norms, learnable feature maps, MoM routing weights, MLA's shared rope key and
+    replicated down-projections) get their partial gradients summed, and nothing is summed twice."""
+    kw, sp = _TP_GRAD_CASES[case]
+    ref = _reduced_grads(single_process_mesh(), ParallelConfig(), kw)
+    outs = run_distributed(_worker_reduced_grads, 2, kw=kw, sp=sp)
+    checked, bad = 0, []
+    for n, (g0, sharded) in outs[0].items():
+        g1, r = outs[1][n][0], ref[n][0]
+        if sharded:
+            assert g0.numel() * 2 == r.numel() or g0.shape != r.shape or r.dim() == 0, n
+            continue
+        assert g0.shape == r.shape, (n, g0.shape, r.shape)          # a sliced parameter that is not marked tensor_parallel
+        if r.norm() < 1e-9:
+            continue
+        checked += 1
+        e = max(((g - r).norm() / r.norm()).item() for g in (g0, g1))
+        if e > 5e-3:
+            bad.append((n, round(e, 4)))
+    assert checked > 3 and not bad, bad
+
+
 def test_bench_config_layouts():
     """``bench.py --config`` maps every benchmark configuration to a parallel layout that exists on 1, 2, 4 and 8 GPUs, and
     the headline configuration keeps 16384 tokens per GPU."""
