@@ -250,6 +250,28 @@ def test_replicated_parameter_gradients_under_tensor_parallelism(case):
     assert checked > 3 and not bad, bad
 
 
+@pytest.mark.parametrize("kw", [
+    dict(la_module="rwkv6", la_feature_map=None), dict(la_module="rwkv7", la_feature_map=None),
+    dict(la_module="retention", la_feature_map="t2r"), dict(la_module="linear_attention", la_feature_map="elementwise_product"),
+    dict(la_module="linear_attention", la_feature_map="polysketch"), dict(la_module="gla", la_feature_map="learnable_outer_product"),
+    dict(la_module="mom_gla", la_feature_map=None), dict(la_module="gsa", la_feature_map=None),
+    dict(la_module="mamba2", la_feature_map=None, hybrid_override_pattern="M-", num_layers=2, mamba_head_dim=16, mamba_d_state=16),
+    dict(base_model="deepseek_v2", kv_lora_rank=32, q_lora_rank=32, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+         layer_type_list="NN", use_la_module=False),
+], ids=lambda kw: kw.get("la_module", "mla") + "-" + str(kw.get("la_feature_map")))
+def test_initial_weights_do_not_depend_on_the_global_generator(kw):
+    """The trainer seeds the process-global generator differently on every data- and context-parallel rank (dropout), so
+    a parameter drawn from it would differ between replicas: two builds under different global seeds must be equal."""
+    from linear_moe_b200.models.transformer import CausalLM
+    cfg = get_preset("bench-cpu-plumbing", **kw)
+    torch.manual_seed(1)
+    a = CausalLM(cfg).state_dict()
+    torch.manual_seed(2)
+    b = CausalLM(cfg).state_dict()
+    diff = [n for n in a if not torch.equal(a[n], b[n])]
+    assert not diff, diff
+
+
 def test_bench_config_layouts():
     """``bench.py --config`` maps every benchmark configuration to a parallel layout that exists on 1, 2, 4 and 8 GPUs, and
     the headline configuration keeps 16384 tokens per GPU."""
