@@ -26,9 +26,13 @@ SD = Dict[str, torch.Tensor]
 _LAYER = re.compile(r"^decoder\.layers\.(\d+)\.(.*)$")
 
 _COL = ("linear_qkv.", "qkv_proj.", "o_gate_proj.", "beta_proj.", "a_proj.", "linear_q_proj.", "linear_q_b_proj.",
-        "linear_kv_b_proj.", "gk_proj.1.", "f_proj.", "shared_qkv_proj.", "shared_beta_proj.", "shared_a_proj.")
+        "linear_kv_b_proj.", "f_proj.", "shared_qkv_proj.", "shared_beta_proj.", "shared_a_proj.")
 _ROW = ("linear_proj.weight", "o_proj.weight", "linear_fc2.weight", "out_proj.weight")
-_HEADVEC = ("A_log", "D", "dt_bias", "bonus")
+_HEADVEC = ("A_log", "D", "dt_bias", "bonus", "booster", "removal")
+_GLA_GATE = re.compile(r"gk_proj\.([01])\.(?:weight|bias)$")
+_RNN_ANY = re.compile(r"\.[a-z]_proj\.")
+_RNN_ROWS = re.compile(r"\.(?:[qfirkv]_proj\.(?:weight|bias)|[rwkvg]_proj\.linear\.(?:weight|bias)"
+                       r"|[rwkvag]_proj\.(?:linear\.)?lora\.2\.(?:weight|bias))$")
 
 
 def _mamba_parts(cfg: ModelConfig):
@@ -57,6 +61,13 @@ def _rule(name: str, cfg: ModelConfig):
         return "dim0", None
     if any(name.endswith(r) for r in _ROW):
         return "dim1", None
+    if cfg.la_module in ("hgrn2", "rwkv6", "rwkv7") and ".self_attention." in name and _RNN_ANY.search(name):
+        # HGRN2 / RWKV6 / RWKV7 mixers: projections into key / value space keep the rank's heads (rows); of a low-rank
+        # pair only the up-projection does; token-shift mixers (x_proj, mu, x) stay whole
+        return ("dim0", None) if _RNN_ROWS.search(name) else ("rep", None)
+    m = _GLA_GATE.search(name)
+    if m:                                   # low-rank GLA gate (also one per MoM memory): only the up-projection is sharded
+        return ("dim0", None) if m.group(1) == "1" else ("rep", None)
     if any(c in name for c in _COL) and "linear_q_a_proj" not in name and "kv_a_proj" not in name:
         return "dim0", None
     last = name.rsplit(".", 1)[-1]

@@ -27,6 +27,14 @@ CASES = {
     "deepseek_mla": dict(base_model="deepseek_v2", num_experts=4, moe_topk=2, moe_ffn_hidden_size=32,
                          enable_shared_expert=True, shared_moe_ffn_hidden_size=64, kv_lora_rank=32, qk_nope_head_dim=16,
                          qk_rope_head_dim=8, v_head_dim=16, q_lora_rank=24, moe_layer_freq=1),
+    "rwkv6": dict(use_la_module=True, la_module="rwkv6", layer_type_list="LN"),
+    "rwkv7": dict(use_la_module=True, la_module="rwkv7", layer_type_list="LL"),
+    "hgrn2": dict(use_la_module=True, la_module="hgrn2", layer_type_list="LL", hgrn2_lower_bound=True),
+    "gsa": dict(use_la_module=True, la_module="gsa", layer_type_list="LL"),
+    "mom_gla": dict(use_la_module=True, la_module="mom_gla", layer_type_list="LL"),
+    "mom_gdn": dict(use_la_module=True, la_module="mom_gated_deltanet", layer_type_list="LL"),
+    "retention_t2r": dict(use_la_module=True, la_module="retention", la_feature_map="t2r", layer_type_list="LL"),
+    "rebased": dict(use_la_module=True, la_module="rebased", layer_type_list="LL", kv_channels=16),
 }
 
 
