@@ -135,7 +135,9 @@ def test_zero1_optimizer_reshard():
     assert torch.equal(torch.cat([s["buffers"][0]["master"] for s in new]), torch.arange(512, dtype=torch.float32))
 
 
-@pytest.mark.parametrize("la", [None, "lightning_attention", "gla", "gated_deltanet", "hgrn2", "rwkv6", "mamba2"])
+@pytest.mark.parametrize("la", [None, "lightning_attention", "gla", "gated_deltanet", "hgrn2", "rwkv6", "mamba2",
+                                "retention", "deltanet", "rwkv7", "gsa", "based", "rebased", "linear_attention_norm",
+                                "mom_gla", "mom_gated_deltanet", "mla"])
 def test_incremental_decoding_matches_full_forward(la):
     """Prefill + token-by-token decoding with the recurrent / KV caches gives the logits of one full forward."""
     torch.manual_seed(0)
@@ -143,8 +145,17 @@ def test_incremental_decoding_matches_full_forward(la):
     if la == "mamba2":
         kw.update(use_la_module=True, la_module=la, hybrid_override_pattern="M*", mamba_head_dim=16, mamba_d_state=16,
                   mamba_ngroups=2)
+    elif la == "mla":
+        kw.update(base_model="deepseek_v2", kv_lora_rank=32, q_lora_rank=24, qk_nope_head_dim=16, qk_rope_head_dim=8,
+                  v_head_dim=16)
+    elif la == "linear_attention_norm":
+        kw.update(use_la_module=True, la_module="linear_attention", layer_type_list="LN", la_do_feature_map_norm=True)
+    elif la in ("based", "rebased"):
+        kw.update(use_la_module=True, la_module=la, layer_type_list="LN", kv_channels=8)
     elif la is not None:
         kw.update(use_la_module=True, la_module=la, layer_type_list="LN", use_short_conv=la == "gated_deltanet")
+        if la.startswith("mom_"):
+            kw.update(mom_capacity=float(kw.get("mom_num_memories", 4)))    # no token is dropped in the full forward either
     model = CausalLM(ModelConfig(**kw)).eval()
     ids = torch.randint(0, 128, (2, 12))
     with torch.no_grad():
