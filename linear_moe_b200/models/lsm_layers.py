@@ -309,9 +309,7 @@ class LSMCore(nn.Module):
         logf = F.logsigmoid(f.float()) / cfg.gla_la_gate_logit_normalizer            # [B,T,H,m]
         s = 1.0 - logf.exp()
         init1 = cache.get("gsa_k") if cache is not None else None
-        assert self.mesh["cp"].is_trivial, "gsa: sequence parallelism is not available for the slot pass"
-        from ..ops import lsm_torch as LT
-        ok, S1 = LT.chunk_value_gated(q, k, s, logf, scale=None, initial_state=init1)
+        ok, S1 = lasp2("value", q, k, s, group=self.mesh["cp"], gk=logf, scale=None, initial_state=init1)
         p = torch.softmax(ok, dim=-1).to(v.dtype)
         o = self._run("vector", p, s.to(v.dtype), v, cache, name="gsa_v", gk=logf, scale=1.0)
         if cache is not None:

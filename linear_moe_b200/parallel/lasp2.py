@@ -27,11 +27,16 @@ import torch
 from .. import ops
 from ..dist import collectives as C
 from ..dist.mesh import Group
+from ..ops import lsm_torch as LT
 
 
 def _summaries(kind: str, q, k, v, g, gk, beta, scale, chunk_size, bonus, dplr=None):
     """Local state from zero ``M`` and transition ``A`` of this rank's slice."""
     B, T, H, dk = k.shape
+    if kind == "value":
+        # decay per value channel (first pass of gated slot attention): S_t = S_{t-1} diag(e^{gv_t}) + k_t^T v_t
+        _, M = LT.chunk_value_gated(q, k, v, gk, scale, None)
+        return M, gk.float().sum(1).exp()
     if kind == "dplr":
         # RWKV7: S_t = (diag(e^{w_t}) + b_t a_t^T) S_{t-1} + k_t v_t^T; the slice's transition is the product of the
         # per-token matrices, read off by sending the identity through the recurrence with zero values
@@ -70,6 +75,8 @@ def _apply(kind: str, A, P):
         return P * A[..., None, None]
     if kind == "vector":
         return P * A[..., None]
+    if kind == "value":
+        return P * A[..., None, :]
     return A @ P                       # delta rule and DPLR: a dk x dk matrix per head
 
 
@@ -113,7 +120,7 @@ def lasp2(kind: str, q, k, v, *, group: Group, g=None, gk=None, beta=None, scale
           chunk_size: int = 64, bonus=None, initial_state=None, mode: str = "chunk",
           dplr=None) -> Tuple[torch.Tensor, torch.Tensor]:
     """Run a linear sequence model whose sequence is split over ``group`` (rank order = sequence
-    order).  ``kind``: ``scalar`` | ``vector`` | ``delta`` | ``dplr`` (RWKV7: ``q`` = receptance, ``gk`` = log decay,
+    order).  ``kind``: ``scalar`` | ``vector`` | ``value`` (``gk`` = log decay per value channel) | ``delta`` | ``dplr`` (RWKV7: ``q`` = receptance, ``gk`` = log decay,
     ``dplr = (a, b)`` the low-rank factors of the transition).  Returns the local output and the state
     after this rank's slice.  ``mode`` (``--la-mode``): ``chunk`` / ``fused_chunk`` = the chunked kernels (one fused
     implementation serves both names), ``fused_recurrent`` = token recurrence, ``parallel`` = quadratic form."""
@@ -121,6 +128,8 @@ def lasp2(kind: str, q, k, v, *, group: Group, g=None, gk=None, beta=None, scale
         raise ValueError(f"unknown --la-mode {mode!r}")
 
     def run(init):
+        if kind == "value":
+            return LT.chunk_value_gated(q, k, v, gk, scale, init)
         if kind == "dplr":
             return ops.lsm_dplr(q, gk, k, v, dplr[0], dplr[1], 1.0 if scale is None else scale, init)
         if mode == "fused_recurrent":

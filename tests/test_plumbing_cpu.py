@@ -250,6 +250,39 @@ def test_replicated_parameter_gradients_under_tensor_parallelism(case):
     assert checked > 3 and not bad, bad
 
 
+def _worker_cp_grads(rank, world, kw):
+    par = ParallelConfig(distributed_backend="gloo", context_parallel_size=2)
+    return _reduced_grads(Mesh(par), par, kw)
+
+
+@pytest.mark.parametrize("case", ["gsa", "rwkv7", "mla", "based", "linear_attention_norm", "deltanet_conv"])
+def test_gradients_under_context_parallelism(case):
+    """Every parameter's reduced gradient with the sequence split over two ranks equals the single-process gradient:
+    gated slot attention (value-gated first pass + key-gated second pass through LASP-2), RWKV7 (matrix transition),
+    MLA (gathered keys / values with rope offsets), Based and normalised linear attention (feature maps, normaliser
+    column), DeltaNet with the short convolution's halo."""
+    kw = {
+        "gsa": dict(la_module="gsa", la_feature_map=None),
+        "rwkv7": dict(la_module="rwkv7", la_feature_map=None),
+        "mla": _TP_GRAD_CASES["mla"][0],
+        "based": dict(la_module="based", la_feature_map=None, kv_channels=16),
+        "linear_attention_norm": dict(la_module="linear_attention", la_feature_map="elu", la_do_feature_map_norm=True),
+        "deltanet_conv": dict(la_module="deltanet", la_feature_map=None, use_short_conv=True),
+    }[case]
+    ref = _reduced_grads(single_process_mesh(), ParallelConfig(), kw)
+    outs = run_distributed(_worker_cp_grads, 2, kw=kw)
+    bad = []
+    for n, (g0, _) in outs[0].items():
+        r = ref[n][0]
+        assert g0.shape == r.shape, n
+        if r.norm() < 1e-9:
+            continue
+        e = max(((o[n][0] - r).norm() / r.norm()).item() for o in outs)
+        if e > 5e-3:
+            bad.append((n, round(e, 4)))
+    assert not bad, bad
+
+
 @pytest.mark.parametrize("kw", [
     dict(la_module="rwkv6", la_feature_map=None), dict(la_module="rwkv7", la_feature_map=None),
     dict(la_module="retention", la_feature_map="t2r"), dict(la_module="linear_attention", la_feature_map="elementwise_product"),
