@@ -11,6 +11,11 @@ summed.  An optional shared memory sees every token.  Cores: GLA, Gated DeltaNet
 
 The routing plan is built with vectorised index arithmetic (no sort): a token routed to memory m
 lands in slot ``L - count(b,m) + rank(b,t,m)`` of that memory's padded row.
+
+Parallel layouts: heads split over the tensor-parallel ranks (the routing weights' gradient is summed over them);
+under sequence parallelism the input is gathered along T at the entry and ``o_proj`` reduce-scatters; under context
+parallelism every memory's subsequence continues across the ranks through the LASP-2 state exchange of the core
+(padding slots neither decay nor write the state), with the capacity applied per rank slice.
 """
 from __future__ import annotations
 
@@ -75,7 +80,6 @@ class MomLinearAttention(nn.Module):
         super().__init__()
         self.cfg, self.mesh = cfg, mesh or single_process_mesh()
         mesh = self.mesh
-        assert mesh["cp"].is_trivial, "MoM: sequence parallelism is not available"
         self.core_kind = {"mom_gla": "gla", "mom_gated_deltanet": "gated_deltanet",
                           "mom_linear_attention": "linear_attention"}[cfg.la_module]
         core_cfg = cfg.replace(la_module=self.core_kind)

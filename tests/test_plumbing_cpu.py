@@ -255,7 +255,8 @@ def _worker_cp_grads(rank, world, kw):
     return _reduced_grads(Mesh(par), par, kw)
 
 
-@pytest.mark.parametrize("case", ["gsa", "rwkv7", "mla", "based", "linear_attention_norm", "deltanet_conv"])
+@pytest.mark.parametrize("case", ["gsa", "rwkv7", "mla", "based", "linear_attention_norm", "deltanet_conv", "mom_gla",
+                                  "mom_gated_deltanet"])
 def test_gradients_under_context_parallelism(case):
     """Every parameter's reduced gradient with the sequence split over two ranks equals the single-process gradient:
     gated slot attention (value-gated first pass + key-gated second pass through LASP-2), RWKV7 (matrix transition),
@@ -268,6 +269,10 @@ def test_gradients_under_context_parallelism(case):
         "based": dict(la_module="based", la_feature_map=None, kv_channels=16),
         "linear_attention_norm": dict(la_module="linear_attention", la_feature_map="elu", la_do_feature_map_norm=True),
         "deltanet_conv": dict(la_module="deltanet", la_feature_map=None, use_short_conv=True),
+        # mixture of memories: every memory's sub-sequence is carried across the ranks by LASP-2; the capacity is per
+        # rank slice, so the comparison uses one that drops no token
+        "mom_gla": dict(la_module="mom_gla", la_feature_map=None, mom_capacity=4.0),
+        "mom_gated_deltanet": dict(la_module="mom_gated_deltanet", la_feature_map=None, mom_capacity=4.0),
     }[case]
     ref = _reduced_grads(single_process_mesh(), ParallelConfig(), kw)
     outs = run_distributed(_worker_cp_grads, 2, kw=kw)
