@@ -520,7 +520,8 @@ class LinearRNN(nn.Module):
 
     def _run(self, op, q, k, v, cache, **kw):
         init = cache.get("state") if cache is not None else None
-        o, S = lasp2(op, q, k, v, group=self.mesh["cp"], chunk_size=self.cfg.la_chunk_size, initial_state=init, **kw)
+        o, S = lasp2(op, q, k, v, group=self.mesh["cp"], chunk_size=self.cfg.la_chunk_size, initial_state=init,
+                     mode=self.cfg.la_mode, **kw)
         if cache is not None:
             cache["state"] = S.detach()
         return o

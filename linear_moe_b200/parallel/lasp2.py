@@ -83,9 +83,20 @@ def _apply(kind: str, A, P):
 def _recurrent(kind, q, k, v, g, gk, beta, scale, init, bonus):
     """``--la-mode fused_recurrent``: the token-by-token recurrence (exact, O(T) sequential steps)."""
     from ..ref import lsm as RL
-    if bonus is not None:
-        raise ValueError("--la-mode fused_recurrent is not available for RWKV6's bonus term; use chunk")
     B, T, H, _ = q.shape
+    if bonus is not None:
+        # RWKV6: the output reads the state BEFORE the current token is written and adds the token's own contribution
+        # weighted by the bonus u: o_t = q_t S_{t-1} + (q_t . (u * k_t)) v_t
+        f = torch.float32
+        sc = q.shape[-1] ** -0.5 if scale is None else scale
+        qf, kf, vf, w = q.to(f) * sc, k.to(f), v.to(f), gk.to(f).exp()
+        S = torch.zeros(B, H, q.shape[-1], v.shape[-1], dtype=f, device=q.device) if init is None else init.to(f)
+        own = (qf * bonus.to(f)[None, None] * kf).sum(-1, keepdim=True) * vf
+        outs = []
+        for t in range(T):
+            outs.append(torch.einsum("bhk,bhkv->bhv", qf[:, t], S) + own[:, t])
+            S = S * w[:, t][..., None] + kf[:, t][..., None] * vf[:, t][..., None, :]
+        return torch.stack(outs, 1).to(v.dtype), S
     gg = g if (g is None or g.dim() == 3) else g[None, None, :].expand(B, T, H)
     o, S = RL.recurrent_lsm(q, k, v, g=gg, gk=gk, beta=beta, scale=scale, initial_state=init)
     return o.to(v.dtype), S

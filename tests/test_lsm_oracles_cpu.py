@@ -254,7 +254,7 @@ def test_lasp2_dplr_matches_one_rank(world):
         _close(torch.cat([o[2][i] for o in outs], 1), x.grad, 5e-4)
 
 
-@pytest.mark.parametrize("la", ["retention", "gla", "deltanet"])
+@pytest.mark.parametrize("la", ["retention", "gla", "deltanet", "rwkv6", "hgrn2"])
 def test_la_mode_selects_equivalent_forms(la):
     """``--la-mode``: chunk / fused_chunk (chunked form), fused_recurrent (token recurrence) and, for the scalar-decay
     family, parallel (quadratic form) compute the same layer output."""
