@@ -153,14 +153,26 @@ class CausalLM(nn.Module):
         if post_process:
             self.decoder.final_layernorm = Norm(cfg, device)
             tied = self.embedding.word_embeddings.weight if (cfg.tie_embeddings and pre_process) else None
+            # tied weights with the embedding on another pipeline stage: this stage holds a copy drawn from the same key
+            # (equal values); the optimizer sums the two copies' gradients, so both receive the same update
+            split_tie = cfg.tie_embeddings and not pre_process
             self.output_layer = LMHead(cfg.hidden_size, cfg.vocab_size, mesh=mesh, std=cfg.init_method_std, tied=tied,
+                                       key="embedding.word_embeddings" if split_tie else "output_layer",
                                        chunk=cfg.cross_entropy_chunk, sequence_parallel=sp, dtype=dt, device=device)
+            if split_tie:
+                self.output_layer.weight.pp_shared_grad = "embedding"
+        if pre_process and not post_process and cfg.tie_embeddings and mesh.pp > 1:
+            self.embedding.word_embeddings.weight.pp_shared_grad = "embedding"
         self.offload = None
         if cfg.cpu_offloading and cfg.cpu_offloading_num_layers > 0:
             from ..parallel.offload import ActivationOffload
             self.offload = ActivationOffload(cfg.cpu_offloading_num_layers)
         if cfg.la_module == "hgrn2" and cfg.hgrn2_lower_bound:
             self.lower_bounds = nn.Parameter(torch.zeros(len(all_specs), cfg.key_dim, dtype=dt, device=device))
+            if mesh.pp > 1 or vpp:
+                # every layer's bound is a cumulative softmax over ALL layers' rows: each pipeline stage (and model chunk)
+                # holds the whole table and contributes the gradient of its own layers
+                self.lower_bounds.pp_shared_grad = "all"
 
     # ------------------------------------------------------------------
     def new_cache(self) -> List[dict]:

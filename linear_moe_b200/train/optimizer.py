@@ -129,6 +129,7 @@ class MixedPrecisionAdam:
                 uniq.append((n, p))
         self.named = uniq
         self._tp_partial = mesh.tp > 1 and any(getattr(p, "tp_partial_grad", False) for _, p in uniq)
+        self._pp_shared = any(getattr(p, "pp_shared_grad", None) is not None for _, p in uniq)
         groups: Dict[Tuple[bool, bool], List[Tuple[str, nn.Parameter]]] = {}
         for n, p in uniq:
             key = (bool(getattr(p, "expert_parallel", False)), not _no_weight_decay(n, p))
@@ -225,6 +226,54 @@ class MixedPrecisionAdam:
                 t.copy_(flat[off:off + t.numel()].view_as(t))
                 off += t.numel()
 
+    def _reduce_pipeline_shared_grads(self):
+        """Sum the gradients of parameters that live on more than one pipeline stage (or model chunk of a stage):
+        ``pp_shared_grad == "all"``: a copy on every stage and chunk (HGRN2's lower-bound table), summed over the local
+        chunks and all-reduced over the pipeline group; ``"embedding"``: the tied word embedding on the first stage and
+        its copy under the LM head on the last (Megatron's embedding group), exchanged point to point.  Every copy then
+        holds the full gradient and receives the same update."""
+        import torch.distributed as dist
+        g = self.mesh["pp"]
+        every = [p for _, p in self.named if getattr(p, "pp_shared_grad", None) == "all"]
+        if every:
+            by_shape: Dict[Tuple[int, ...], List[nn.Parameter]] = {}
+            for p in every:
+                by_shape.setdefault(tuple(p.shape), []).append(p)
+            for ps in by_shape.values():                     # one table per model chunk on this stage: same shape
+                total = ps[0].main_grad.clone()
+                for p in ps[1:]:
+                    total += p.main_grad
+                if not g.is_trivial:
+                    C.all_reduce_(total, g)
+                for p in ps:
+                    p.main_grad.copy_(total)
+        tied = [p for _, p in self.named if getattr(p, "pp_shared_grad", None) == "embedding"]
+        if tied and not g.is_trivial:
+            first, last = g.ranks[0], g.ranks[-1]
+            for p in tied:
+                grad = p.main_grad
+                if self.mesh.rank == last:
+                    dist.send(grad, dst=first, group=g.pg)
+                    dist.recv(grad, src=first, group=g.pg)
+                elif self.mesh.rank == first:
+                    other = torch.empty_like(grad)
+                    dist.recv(other, src=last, group=g.pg)
+                    grad += other
+                    dist.send(grad, dst=last, group=g.pg)
+
+    def _is_shared_copy(self, p) -> bool:
+        """A parameter whose gradient was summed into an identical copy elsewhere and must be counted once in the
+        gradient norm: the owner is the first pipeline stage (first model chunk)."""
+        tag = getattr(p, "pp_shared_grad", None)
+        if tag is None:
+            return False
+        if self.mesh.pp_rank != 0:
+            return True
+        if tag == "all":
+            first = next(q for _, q in self.named if getattr(q, "pp_shared_grad", None) == "all" and q.shape == p.shape)
+            return first is not p
+        return False
+
     # ---- gradient reduction overlapped with the backward pass (--overlap-grad-reduce) -------------------------------
     def _layer_range(self, b: "FlatBuffer", layer: int):
         """``[lo, hi)`` of the flat buffer holding the parameters of ``decoder.layers.<layer>`` (contiguous: slots are in
@@ -242,7 +291,8 @@ class MixedPrecisionAdam:
         input): the reduce-scatter of that block's range starts at once on a side stream, overlapping the backward of the
         blocks before it (Megatron's ``overlap_grad_reduce``, training.py:278-298).  Only the fused NVLS buffers and only
         the last micro-batch of a step take part; everything else is reduced by :meth:`reduce_grads`."""
-        if not (self.overlap_grad_reduce and self.overlap_active) or self.sequence_parallel or self._tp_partial:
+        if not (self.overlap_grad_reduce and self.overlap_active) or self.sequence_parallel or self._tp_partial \
+                or self._pp_shared:
             return                    # gradients that still need the tensor-parallel all-reduce must not be reduced early
         fused = [b for b in self.buffers if b.fused is not None]
         if not fused:
@@ -282,6 +332,7 @@ class MixedPrecisionAdam:
             if getattr(p, "_direct_wgrad", False) and getattr(p, "_main_grad_fresh", False):
                 p.main_grad.zero_()
         self._reduce_sequence_parallel_grads()
+        self._reduce_pipeline_shared_grads()
         bucketed = self._bucket_state
         self._bucket_state = None
         if bucketed is not None:
@@ -324,6 +375,11 @@ class MixedPrecisionAdam:
                         sq = sq + torch.linalg.vector_norm(b.grads[a:e]).square()
             else:
                 sq = torch.linalg.vector_norm(b.grads[lo:hi]).square()
+            for s, dup in zip(b.slots, b.tp_dup):            # copies of pipeline-shared parameters count once
+                if self._is_shared_copy(s.param) and not (dup and mesh.tp > 1 and mesh.tp_rank != 0):
+                    a, e = max(s.start, lo), min(s.start + s.numel, hi)
+                    if e > a:
+                        sq = sq - torch.linalg.vector_norm(b.grads[a:e]).square()
             if b.expert:
                 expert = expert + sq
             else:

@@ -144,6 +144,59 @@ def test_pipeline_schedules_match_single_process(par_kw):
     assert torch.allclose(torch.tensor(gn), torch.tensor(ref_gn), rtol=2e-3), (gn, ref_gn)
 
 
+def _train_shared(mesh, par, kw, steps=3, seq=64, gbs=4):
+    cfg = get_preset("bench-cpu-plumbing", num_layers=4, num_experts=None, ffn_hidden_size=256, **kw)
+    tc = TrainConfig(micro_batch_size=1, global_batch_size=gbs, seq_length=seq, train_iters=steps, lr=3e-4, min_lr=3e-4,
+                     lr_decay_style="constant", weight_decay=0.01, clip_grad=1.0, log_interval=1000, seed=0)
+    ds = SyntheticTokenDataset(cfg.vocab_size, seq, num_samples=gbs, seed=0)
+    tr = Trainer(cfg, par, tc, mesh, device=torch.device("cpu"), dataset=ds)
+    losses, gnorms = [], []
+    for _ in range(steps):
+        st = tr.train_step()
+        gnorms.append(st["grad_norm"])
+        if "lm loss" in st:
+            losses.append(float(st["lm loss"]))
+    shared = {n: p.detach().clone() for m in tr.models for n, p in m.named_parameters()
+              if getattr(p, "pp_shared_grad", None) is not None or "word_embeddings" in n or "lower_bounds" in n}
+    return losses, gnorms, shared
+
+
+def _worker_shared(rank, world, kw, par_kw):
+    par = ParallelConfig(distributed_backend="gloo", **par_kw)
+    return _train_shared(Mesh(par), par, kw)
+
+
+@pytest.mark.parametrize("kw,par_kw", [
+    (dict(tie_embeddings=True, layer_type_list="LLLL"), dict(pipeline_model_parallel_size=2)),
+    (dict(la_module="hgrn2", la_feature_map=None, hgrn2_lower_bound=True, layer_type_list="LLLL"),
+     dict(pipeline_model_parallel_size=2)),
+    (dict(la_module="hgrn2", la_feature_map=None, hgrn2_lower_bound=True, layer_type_list="LLLL", tie_embeddings=True),
+     dict(pipeline_model_parallel_size=2, virtual_pipeline_model_parallel_size=2)),
+], ids=["tied_embeddings_pp2", "hgrn2_lower_bounds_pp2", "both_pp2_vpp2"])
+def test_parameters_shared_across_pipeline_stages(kw, par_kw):
+    """Tied input / output embeddings whose two uses sit on different pipeline stages, and HGRN2's lower-bound table that
+    every stage (and interleaved model chunk) needs in full: the copies' gradients are summed, counted once in the
+    gradient norm, and the copies stay equal while training matches the single-process run with clipping active."""
+    ref_losses, ref_gn, ref_shared = _train_shared(single_process_mesh(), ParallelConfig(), kw)
+    outs = run_distributed(_worker_shared, 2, kw=kw, par_kw=par_kw)
+    losses = next(o[0] for o in outs if o[0])
+    assert torch.allclose(torch.tensor(losses), torch.tensor(ref_losses), atol=3e-4), (losses, ref_losses)
+    # the first step pins the gradients (fp32 accumulation order only); Adam's first updates then amplify rounding noise
+    assert abs(outs[0][1][0] - ref_gn[0]) < 5e-4 * ref_gn[0], (outs[0][1], ref_gn)
+    assert torch.allclose(torch.tensor(outs[0][1]), torch.tensor(ref_gn), rtol=2e-2), (outs[0][1], ref_gn)
+    assert outs[1][1] == outs[0][1]
+    if kw.get("tie_embeddings"):
+        emb = next(v for n, v in outs[0][2].items() if "word_embeddings" in n)
+        head = next(v for n, v in outs[1][2].items() if "output_layer" in n)
+        assert torch.equal(emb, head)
+        assert torch.allclose(emb, next(v for n, v in ref_shared.items() if "word_embeddings" in n), atol=2e-4)
+    if kw.get("hgrn2_lower_bound"):
+        tables = [v for o in outs for n, v in o[2].items() if "lower_bounds" in n]
+        assert len(tables) >= 2 and all(torch.equal(t, tables[0]) for t in tables)
+        assert tables[0].abs().max() > 0
+        assert torch.allclose(tables[0], next(v for n, v in ref_shared.items() if "lower_bounds" in n), atol=2e-4)
+
+
 def _train_rnn(mesh, par, la, steps=3, seq=64):
     cfg = get_preset("bench-cpu-plumbing", la_module=la, la_feature_map=None, num_experts=None, ffn_hidden_size=256,
                      hgrn2_lower_bound=la == "hgrn2")
