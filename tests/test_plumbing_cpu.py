@@ -244,9 +244,9 @@ def test_linear_rnn_mixers_under_context_parallelism(la):
     assert abs(gn[0] - ref_gn[0]) < 1e-3 * ref_gn[0], (gn, ref_gn)
 
 
-def _reduced_grads(mesh, par, kw):
+def _reduced_grads(mesh, par, kw, mbs=2):
     cfg = get_preset("bench-cpu-plumbing", **kw)
-    tc = TrainConfig(micro_batch_size=2, global_batch_size=2, seq_length=64, train_iters=1, lr=1e-3, min_lr=1e-3,
+    tc = TrainConfig(micro_batch_size=mbs, global_batch_size=2, seq_length=64, train_iters=1, lr=1e-3, min_lr=1e-3,
                      lr_decay_style="constant", weight_decay=0.0, clip_grad=0.0, log_interval=1000, seed=0)
     ds = SyntheticTokenDataset(cfg.vocab_size, 64, num_samples=2, seed=0)
     tr = Trainer(cfg, par, tc, mesh, device=torch.device("cpu"), dataset=ds)
