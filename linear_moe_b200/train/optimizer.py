@@ -232,6 +232,8 @@ class MixedPrecisionAdam:
         chunks and all-reduced over the pipeline group; ``"embedding"``: the tied word embedding on the first stage and
         its copy under the LM head on the last (Megatron's embedding group), exchanged point to point.  Every copy then
         holds the full gradient and receives the same update."""
+        if not self._pp_shared:
+            return
         import torch.distributed as dist
         g = self.mesh["pp"]
         every = [p for _, p in self.named if getattr(p, "pp_shared_grad", None) == "all"]
@@ -375,7 +377,7 @@ class MixedPrecisionAdam:
                         sq = sq + torch.linalg.vector_norm(b.grads[a:e]).square()
             else:
                 sq = torch.linalg.vector_norm(b.grads[lo:hi]).square()
-            for s, dup in zip(b.slots, b.tp_dup):            # copies of pipeline-shared parameters count once
+            for s, dup in (zip(b.slots, b.tp_dup) if self._pp_shared else ()):   # copies of pipeline-shared parameters count once
                 if self._is_shared_copy(s.param) and not (dup and mesh.tp > 1 and mesh.tp_rank != 0):
                     a, e = max(s.start, lo), min(s.start + s.numel, hi)
                     if e > a:
