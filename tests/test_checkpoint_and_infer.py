@@ -275,7 +275,7 @@ def test_reference_te_style_norm_keys_are_mapped():
                         "decoder.layers.0.mlp.linear_fc1.weight"}
 
 
-@pytest.mark.parametrize("name", ["qwen2_moe_gqa", "mamba2"])
+@pytest.mark.parametrize("name", ["qwen2_moe_gqa", "mamba2", "rwkv6", "rwkv7", "mom_gla"])
 def test_sharded_checkpoint_reshard_on_load(tmp_path, name):
     """Sharded format: shards written under one (TP, PP, EP) layout are read under other layouts, every reader getting
     exactly its part of every tensor (no full merge)."""
