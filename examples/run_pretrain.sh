@@ -26,6 +26,14 @@ case "${BASE_MODEL}-${MODEL_SIZE}" in
   deepseek_v2-A21B)  M="--num-layers 60 --hidden-size 5120 --num-attention-heads 128 --ffn-hidden-size 12288 --num-experts 160 --moe-router-topk 6 --moe-ffn-hidden-size 1536 --enable-shared-expert --num-shared-experts 2 --shared-moe-ffn-hidden-size 3072 --q-lora-rank 1536 --moe-layer-freq 1 --kv-lora-rank 512 --extra-vocab-size 2400";;
   *) echo "unknown ${BASE_MODEL}-${MODEL_SIZE}"; exit 1;;
 esac
+# per-family switches of the reference launchers (run_pretrain_qwen.sh:430-445, run_pretrain_mcore_llama.sh:321-332,
+# run_pretrain_mistral.sh:313-322, run_pretrain_deepseek.sh:349-361): tokenizer vocabulary, QKV bias, norm kind and epsilon
+case "${BASE_MODEL}" in
+  qwen2)       F="--add-qkv-bias --normalization RMSNorm --norm-epsilon 1e-6 --vocab-size 151643";;
+  llama3)      F="--normalization RMSNorm --vocab-size 128000";;
+  mixtral)     F="--normalization LayerNorm --vocab-size 32000 --moe-router-load-balancing-type aux_loss";;
+  deepseek_v2) F="--normalization RMSNorm --norm-epsilon 1e-6 --rotary-base 10000 --vocab-size 100000 --moe-router-load-balancing-type aux_loss";;
+esac
 [ "$LA_MODULE" = "none" ] && LA="" || LA="--use-la-module --la-module ${LA_MODULE} --la-mode chunk --la-output-norm rmsnorm --la-gate-fn swish"
 if [ "$LA_MODULE" = "mamba2" ]; then LA="$LA --hybrid-override-pattern ${LAYER_TYPE_LIST}"; elif [ -n "$LA" ]; then LA="$LA --layer-type-list ${LAYER_TYPE_LIST}"; fi
 [ "$PR" = "fp16" ] && P="--fp16"; [ "$PR" = "bf16" ] && P="--bf16"; [ "$PR" = "fp8" ] && P="--bf16 --fp8-hybrid --fp8-amax-history-len 1024 --fp8-amax-compute-algo max"
@@ -33,15 +41,17 @@ if [ "$LA_MODULE" = "mamba2" ]; then LA="$LA --hybrid-override-pattern ${LAYER_T
 [ "$DO" = "true" ] && D="--use-distributed-optimizer" || D=""
 [ "$SP" = "true" ] && S="--sequence-parallel" || S=""
 [ -n "$DATA_PATH" ] && DP="--data-path ${DATA_PATH}" || DP=""
-mkdir -p ${OUT}/log ${OUT}/checkpoint
-torchrun --nnodes 1 --nproc-per-node ${GPUS} --master-addr 127.0.0.1 --master-port ${MASTER_PORT:-29500} \
-  $(dirname $0)/pretrain.py --base-model ${BASE_MODEL} ${M} ${LA} ${P} ${A} ${D} ${S} ${DP} \
+ARGS="--base-model ${BASE_MODEL} ${M} ${F} ${LA} ${P} ${A} ${D} ${S} ${DP} \
   --save ${OUT}/checkpoint --split 99,1,0 --lr ${LR} --min-lr ${MIN_LR} --lr-decay-style cosine --weight-decay 0.1 \
   --adam-beta1 0.9 --adam-beta2 0.95 --clip-grad 1.0 --init-method-std 0.008 --attention-dropout 0.0 --hidden-dropout 0.0 \
   --lr-decay-iters ${TRAIN_ITERS} --lr-warmup-iters ${WARMUP} --train-iters ${TRAIN_ITERS} \
   --micro-batch-size ${BATCH_SIZE} --global-batch-size ${GLOBAL_BATCH_SIZE} --seq-length ${SEQ_LEN} \
   --max-position-embeddings ${SEQ_LEN} --log-interval 10 --eval-interval 100000 --eval-iters 10 --save-interval 1000 \
   --tensorboard-dir ${OUT}/tensorboard --tensor-model-parallel-size ${TP} --pipeline-model-parallel-size ${PP} \
-  --context-parallel-size ${CP} --expert-model-parallel-size ${EP} --dataset ${DATASET} --swiglu --normalization RMSNorm \
+  --context-parallel-size ${CP} --expert-model-parallel-size ${EP} --dataset ${DATASET} --swiglu \
   --use-rotary-position-embeddings --position-embedding-type rope --untie-embeddings-and-output-weights \
-  --disable-bias-linear --add-qkv-bias --rotary-percent 1.0 --vocab-size 151643 2>&1 | tee ${OUT}/log/$(date +%Y.%m.%d-%H.%M.%S).log
+  --disable-bias-linear --rotary-percent 1.0"
+if [ -n "${DRY_RUN}" ]; then echo ${ARGS}; exit 0; fi      # print the training flags only (used by the tests)
+mkdir -p ${OUT}/log ${OUT}/checkpoint
+torchrun --nnodes 1 --nproc-per-node ${GPUS} --master-addr 127.0.0.1 --master-port ${MASTER_PORT:-29500} \
+  $(dirname $0)/pretrain.py ${ARGS} 2>&1 | tee ${OUT}/log/$(date +%Y.%m.%d-%H.%M.%S).log

@@ -164,3 +164,37 @@ def test_convert_checkpoint_cli_roundtrip(tmp_path):
     assert set(out) == set(hf)
     for k in hf:
         assert torch.equal(out[k], hf[k]), k
+
+
+@pytest.mark.parametrize("base,size,la,pattern", [
+    ("qwen2", "A0.3B", "gla", "LLLLLLLLLLLL"), ("qwen2", "A1B", "gated_deltanet", "LLLNLLLNLLLNLLLN"), ("qwen2", "7B", "none", ""),
+    ("llama3", "1B", "lasp2", "LLLLLLLLLLLLLLLL"), ("llama3", "8B", "retention", "LLLN" * 8),
+    ("mixtral", "Small", "rwkv6", "LLLLLLLL"), ("mixtral", "8x7B", "mamba2", "M-" * 16),
+    ("deepseek_v2", "A2.4B", "hgrn2", "L" * 27), ("deepseek_v2", "A21B", "none", ""),
+])
+def test_launcher_flags_parse_into_the_model(base, size, la, pattern):
+    """``examples/run_pretrain.sh`` in dry-run mode prints the flags it would pass; every model-size block of every
+    backbone parses and yields the architecture the block names (the reference has one launcher per backbone)."""
+    import os
+    import subprocess
+    from linear_moe_b200.config.arguments import parse_args
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, DRY_RUN="1", BASE_MODEL=base, MODEL_SIZE=size, LA_MODULE=la, LAYER_TYPE_LIST=pattern or "L",
+               TP="2", EP="2", SP="true", PR="bf16")
+    out = subprocess.run(["bash", os.path.join(root, "examples", "run_pretrain.sh")], env=env, capture_output=True, text=True)
+    assert out.returncode == 0, out.stderr
+    _, cfg, par, tc = parse_args(out.stdout.split())
+    assert cfg.base_model == base and par.tp == 2 and par.ep == 2 and par.sequence_parallel
+    assert cfg.vocab_size % (128 * 2) == 0
+    assert cfg.normalization == ("LayerNorm" if base == "mixtral" else "RMSNorm")
+    assert cfg.add_qkv_bias == (base == "qwen2") and not cfg.add_bias_linear and not cfg.tie_embeddings
+    kinds = cfg.layer_types()
+    if la == "none":
+        assert not cfg.use_la_module and all(s.symbol == "N" and s.mixer in ("attn", "mla") for s in kinds)
+    elif la == "mamba2":
+        # without --megatron-hybrid-mamba-method every mixer block is followed by its own MLP block (the reference's default)
+        assert [s.symbol for s in kinds if s.symbol != "-"] == [c for c in pattern if c != "-"]
+    else:
+        assert cfg.la_module == la and len(kinds) == cfg.num_layers
+    if base == "deepseek_v2":
+        assert cfg.kv_lora_rank == 512 and all(s.mixer == "mla" for s in kinds if s.symbol == "N")
