@@ -1,6 +1,6 @@
 #!/bin/bash
 # Launcher with the reference's switch blocks (examples/linear_moe_qwen2/run_pretrain_qwen.sh:17-62,126-365):
-#   MODEL_SIZE  qwen2: 0.5B 1.5B 7B A0.3B A1B A14B | llama3: 0.3B 1B 8B | mixtral: Small 8x7B | deepseek_v2: A2.4B A21B
+#   MODEL_SIZE  qwen2: 0.5B 0.5Boriginal 1.5B 7B 72B A0.3B A1B A14B | llama3: 0.3B 1B 8B | mixtral: Small 8x7B | deepseek_v2: A2.4B A21B
 #   LA_MODULE   any --la-module value or "none" (pure softmax attention); LAYER_TYPE_LIST  L/N pattern (M/*/- for mamba2)
 #   PR fp16|bf16|fp8, AC full|sel|none, DO true|false, SP true|false, TP PP CP EP sizes
 set -e
@@ -11,12 +11,14 @@ BATCH_SIZE=${BATCH_SIZE:-4}; GLOBAL_BATCH_SIZE=${GLOBAL_BATCH_SIZE:-64}; SEQ_LEN
 LR=${LR:-1e-4}; MIN_LR=${MIN_LR:-1e-5}; TRAIN_ITERS=${TRAIN_ITERS:-1000}; WARMUP=${WARMUP:-100}
 DATASET=${DATASET:-Synthetic}; DATA_PATH=${DATA_PATH:-}; OUT=${OUT:-./output}
 case "${BASE_MODEL}-${MODEL_SIZE}" in
-  qwen2-0.5B)  M="--num-layers 24 --hidden-size 512 --num-attention-heads 16 --ffn-hidden-size 4864 --extra-vocab-size 293";;
-  qwen2-1.5B)  M="--num-layers 28 --hidden-size 1536 --num-attention-heads 12 --group-query-attention --num-query-groups 2 --ffn-hidden-size 8960 --extra-vocab-size 293";;
-  qwen2-7B)    M="--num-layers 28 --hidden-size 3584 --num-attention-heads 28 --group-query-attention --num-query-groups 4 --ffn-hidden-size 18944 --extra-vocab-size 421";;
+  qwen2-0.5B)  M="--num-layers 24 --hidden-size 512 --num-attention-heads 16 --ffn-hidden-size 4864 --rotary-base 1000000 --extra-vocab-size 293";;
+  qwen2-0.5Boriginal) M="--num-layers 24 --hidden-size 896 --num-attention-heads 14 --group-query-attention --num-query-groups 2 --ffn-hidden-size 4864 --rotary-base 1000000 --extra-vocab-size 293";;
+  qwen2-72B)   M="--num-layers 80 --hidden-size 8192 --num-attention-heads 64 --group-query-attention --num-query-groups 8 --ffn-hidden-size 29568 --rotary-base 1000000 --extra-vocab-size 421";;
+  qwen2-1.5B)  M="--num-layers 28 --hidden-size 1536 --num-attention-heads 12 --group-query-attention --num-query-groups 2 --ffn-hidden-size 8960 --rotary-base 1000000 --extra-vocab-size 293";;
+  qwen2-7B)    M="--num-layers 28 --hidden-size 3584 --num-attention-heads 28 --group-query-attention --num-query-groups 4 --ffn-hidden-size 18944 --rotary-base 1000000 --extra-vocab-size 421";;
   qwen2-A0.3B) M="--num-layers 12 --hidden-size 1024 --num-attention-heads 8 --ffn-hidden-size 896 --num-experts 64 --moe-router-topk 8 --moe-ffn-hidden-size 896 --rotary-base 10000 --extra-vocab-size 293";;
   qwen2-A1B)   M="--num-layers 16 --hidden-size 2048 --num-attention-heads 16 --ffn-hidden-size 1024 --num-experts 64 --moe-router-topk 8 --moe-ffn-hidden-size 1024 --extra-vocab-size 293";;
-  qwen2-A14B)  M="--num-layers 28 --hidden-size 3584 --num-attention-heads 28 --group-query-attention --num-query-groups 4 --ffn-hidden-size 18944 --num-experts 64 --moe-router-topk 8 --moe-ffn-hidden-size 2560 --shared-moe-ffn-hidden-size 20480 --enable-shared-expert --extra-vocab-size 421";;
+  qwen2-A14B)  M="--num-layers 28 --hidden-size 3584 --num-attention-heads 28 --group-query-attention --num-query-groups 4 --ffn-hidden-size 18944 --num-experts 64 --moe-router-topk 8 --moe-ffn-hidden-size 2560 --shared-moe-ffn-hidden-size 20480 --enable-shared-expert --rotary-base 1000000 --extra-vocab-size 293";;
   llama3-0.3B) M="--num-layers 12 --hidden-size 1024 --num-attention-heads 32 --group-query-attention --num-query-groups 8 --ffn-hidden-size 4096 --rotary-base 500000 --norm-epsilon 1e-5 --extra-vocab-size 256";;
   llama3-1B)   M="--num-layers 16 --hidden-size 2048 --num-attention-heads 32 --group-query-attention --num-query-groups 8 --ffn-hidden-size 8192 --rotary-base 500000 --norm-epsilon 1e-5 --extra-vocab-size 256";;
   llama3-8B)   M="--num-layers 32 --hidden-size 4096 --num-attention-heads 32 --group-query-attention --num-query-groups 8 --ffn-hidden-size 14336 --rotary-base 500000 --norm-epsilon 1e-5 --extra-vocab-size 256";;

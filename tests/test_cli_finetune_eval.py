@@ -168,6 +168,7 @@ def test_convert_checkpoint_cli_roundtrip(tmp_path):
 
 @pytest.mark.parametrize("base,size,la,pattern", [
     ("qwen2", "A0.3B", "gla", "LLLLLLLLLLLL"), ("qwen2", "A1B", "gated_deltanet", "LLLNLLLNLLLNLLLN"), ("qwen2", "7B", "none", ""),
+    ("qwen2", "0.5Boriginal", "none", ""), ("qwen2", "72B", "linear_attention", "L" * 80),
     ("llama3", "1B", "lasp2", "LLLLLLLLLLLLLLLL"), ("llama3", "8B", "retention", "LLLN" * 8),
     ("mixtral", "Small", "rwkv6", "LLLLLLLL"), ("mixtral", "8x7B", "mamba2", "M-" * 16),
     ("deepseek_v2", "A2.4B", "hgrn2", "L" * 27), ("deepseek_v2", "A21B", "none", ""),
@@ -198,3 +199,21 @@ def test_launcher_flags_parse_into_the_model(base, size, la, pattern):
         assert cfg.la_module == la and len(kinds) == cfg.num_layers
     if base == "deepseek_v2":
         assert cfg.kv_lora_rank == 512 and all(s.mixer == "mla" for s in kinds if s.symbol == "N")
+
+
+def test_evaluation_launcher_builds_on_the_training_blocks():
+    import os
+    import subprocess
+    from linear_moe_b200.config.arguments import build_parser, configs_from_args
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, DRY_RUN_EVAL="1", CKPT="/ckpt", VALID_DATA="/data/valid.json", BASE_MODEL="llama3",
+               MODEL_SIZE="0.3B", LA_MODULE="lasp2", LAYER_TYPE_LIST="L" * 12, GPUS="2", TP="2", BATCH_SIZE="4")
+    out = subprocess.run(["bash", os.path.join(root, "examples", "run_evaluate.sh")], env=env, capture_output=True, text=True)
+    assert out.returncode == 0, out.stderr
+    words = out.stdout.split()
+    assert words[0].endswith("evaluate.py")
+    p = build_parser()
+    p.add_argument("--lm-eval-tasks", type=str, default=None)
+    cfg, par, tc = configs_from_args(p.parse_args(words[1:]))
+    assert cfg.la_module == "lasp2" and par.tp == 2 and tc.load == "/ckpt" and tc.no_load_optim and tc.eval_iters == 10
+    assert tc.valid_data == ["/data/valid.json"] and tc.dataset == "LLama-Pretrain-Raw" and tc.global_batch_size == 4
