@@ -79,7 +79,8 @@ def clean_dir(input_dir: str, output_dir: str, target_key: Optional[str] = None,
         return 0
     if (processes or 1) <= 1 or len(jobs) == 1:
         return sum(clean_file(*j) for j in jobs)
-    with ProcessPoolExecutor(max_workers=processes) as ex:
+    import multiprocessing
+    with ProcessPoolExecutor(max_workers=processes, mp_context=multiprocessing.get_context("spawn")) as ex:
         return sum(ex.map(_clean_job, jobs))
 
 
