@@ -239,6 +239,9 @@ def build_parser() -> argparse.ArgumentParser:
     _flag(g, "--train-mode", type=str, default="pretrain", choices=["pretrain", "finetune"])
     _flag(g, "--check-for-nan-in-loss-and-grad", action=argparse.BooleanOptionalAction, default=True)
     _flag(g, "--exit-interval", type=int, default=None)
+    _flag(g, "--adlr-autoresume", action="store_true",
+          help="checkpoint and exit when the cluster's auto-resume service (or the file named by LMOE_AUTORESUME_FILE) asks")
+    _flag(g, "--adlr-autoresume-interval", type=int, default=1000)
     _flag(g, "--manual-gc", action="store_true")
     _flag(g, "--manual-gc-interval", type=int, default=0)
     _flag(g, "--exit-duration-in-mins", type=float, default=None)
@@ -460,6 +463,7 @@ def configs_from_args(args: argparse.Namespace) -> Tuple[ModelConfig, ParallelCo
         log_validation_ppl_to_tensorboard=args.log_validation_ppl_to_tensorboard,
         timing_log_level=args.timing_log_level, barrier_with_L1_time=args.barrier_with_L1_time,
         exit_interval=args.exit_interval, exit_duration_in_mins=args.exit_duration_in_mins,
+        adlr_autoresume=args.adlr_autoresume, adlr_autoresume_interval=args.adlr_autoresume_interval,
         manual_gc=args.manual_gc, manual_gc_interval=args.manual_gc_interval,
         exit_signal_handler=args.exit_signal_handler,
         check_for_nan_in_loss_and_grad=args.check_for_nan_in_loss_and_grad, profile=args.profile,

@@ -266,6 +266,8 @@ class TrainConfig:
     barrier_with_L1_time: bool = True
     exit_interval: Optional[int] = None
     exit_duration_in_mins: Optional[float] = None
+    adlr_autoresume: bool = False                 # --adlr-autoresume: ask the scheduler's auto-resume service every interval
+    adlr_autoresume_interval: int = 1000
     manual_gc: bool = False                       # --manual-gc: Python's collector off, collected by hand every manual_gc_interval steps
     manual_gc_interval: int = 0                   # 0 = only at evaluation / checkpoint time
     exit_signal_handler: bool = False

@@ -387,6 +387,13 @@ class Trainer:
                 return "duration"
         if tc.exit_interval and self.iteration % tc.exit_interval == 0:
             return "interval"
+        if tc.adlr_autoresume and self.iteration % max(tc.adlr_autoresume_interval, 1) == 0:
+            from .watchdog import autoresume_termination_requested
+            flag = torch.tensor([1 if (self.mesh.rank == 0 and autoresume_termination_requested()) else 0],
+                                device=self.device)
+            C.all_reduce_(flag, self.mesh["world"], op=dist.ReduceOp.MAX)
+            if int(flag) > 0:
+                return "autoresume"
         return None
 
     def train(self) -> Dict[str, float]:
@@ -437,6 +444,9 @@ class Trainer:
                 if tc.save:
                     self.save()
                 print_rank_0(f"exiting program at iteration {self.iteration} ({why})")
+                if why == "autoresume" and self.mesh.rank == 0:
+                    from .watchdog import autoresume_request_resume
+                    autoresume_request_resume()          # after the checkpoint is on disk
                 break
         if self.heartbeat is not None:
             self.heartbeat.stop()

@@ -86,3 +86,33 @@ def raise_on_comm_status(status_words, where: str = ""):
         w = bad[0]
         raise CommTimeout(f"{where}: bounded wait expired (kernel {w >> 24}, peer {(w >> 16) & 0xFF}, "
                           f"phase {w & 0xFFFF})")
+
+
+# ---- scheduler-driven checkpoint-and-exit (``--adlr-autoresume``) ------------------------------------------------------
+def _autoresume_service():
+    """The cluster's auto-resume client (``userlib.auto_resume.AutoResume``, the library Megatron's
+    ``check_adlr_autoresume_termination`` talks to; training.py:639-642), or None where it is not installed."""
+    try:
+        from userlib.auto_resume import AutoResume
+    except ImportError:
+        return None
+    return AutoResume
+
+
+def autoresume_termination_requested() -> bool:
+    """True when the job should checkpoint and exit: the auto-resume service says so, or the file named by
+    ``LMOE_AUTORESUME_FILE`` exists (a plain-file stand-in for clusters without the service: ``touch`` it to stop the job
+    at its next check)."""
+    import os
+    svc = _autoresume_service()
+    if svc is not None and svc.termination_requested():
+        return True
+    path = os.environ.get("LMOE_AUTORESUME_FILE")
+    return bool(path) and os.path.exists(path)
+
+
+def autoresume_request_resume():
+    """Tell the service to queue the job again (called by rank 0 once the checkpoint is written)."""
+    svc = _autoresume_service()
+    if svc is not None:
+        svc.request_resume()

@@ -217,3 +217,44 @@ def test_evaluation_launcher_builds_on_the_training_blocks():
     cfg, par, tc = configs_from_args(p.parse_args(words[1:]))
     assert cfg.la_module == "lasp2" and par.tp == 2 and tc.load == "/ckpt" and tc.no_load_optim and tc.eval_iters == 10
     assert tc.valid_data == ["/data/valid.json"] and tc.dataset == "LLama-Pretrain-Raw" and tc.global_batch_size == 4
+
+
+def test_autoresume_checkpoints_and_exits(tmp_path, monkeypatch):
+    """``--adlr-autoresume``: at the next check after the scheduler's auto-resume service (a fake ``userlib.auto_resume``
+    here) or the stand-in file asks for termination, the run writes a checkpoint, asks to be queued again and stops."""
+    import sys
+    import types
+    from linear_moe_b200.config.model_config import ModelConfig, ParallelConfig, TrainConfig
+    from linear_moe_b200.train.loop import Trainer
+    calls = {"asked": 0, "resume": 0}
+
+    class AutoResume:
+        @staticmethod
+        def termination_requested():
+            calls["asked"] += 1
+            return calls["asked"] >= 2
+
+        @staticmethod
+        def request_resume():
+            calls["resume"] += 1
+    pkg, mod = types.ModuleType("userlib"), types.ModuleType("userlib.auto_resume")
+    mod.AutoResume = AutoResume
+    pkg.auto_resume = mod
+    monkeypatch.setitem(sys.modules, "userlib", pkg)
+    monkeypatch.setitem(sys.modules, "userlib.auto_resume", mod)
+    cfg = ModelConfig(num_layers=1, hidden_size=32, num_attention_heads=2, ffn_hidden_size=64, vocab_size=64)
+    kw = dict(micro_batch_size=1, global_batch_size=1, seq_length=16, train_iters=20, log_interval=100, lr=1e-3,
+              adlr_autoresume=True, adlr_autoresume_interval=3)
+    tr = Trainer(cfg, ParallelConfig(), TrainConfig(save=str(tmp_path / "a"), **kw), device=torch.device("cpu"))
+    tr.train()
+    assert tr.iteration == 6 and calls == {"asked": 2, "resume": 1}
+    assert (tmp_path / "a" / "latest_checkpointed_iteration.txt").read_text().strip() == "6"
+    # without the service: the file named by LMOE_AUTORESUME_FILE
+    monkeypatch.delitem(sys.modules, "userlib")
+    monkeypatch.delitem(sys.modules, "userlib.auto_resume")
+    stop = tmp_path / "stop"
+    monkeypatch.setenv("LMOE_AUTORESUME_FILE", str(stop))
+    tr2 = Trainer(cfg, ParallelConfig(), TrainConfig(save=str(tmp_path / "b"), **kw), device=torch.device("cpu"))
+    stop.write_text("")
+    tr2.train()
+    assert tr2.iteration == 3
