@@ -464,3 +464,44 @@ def test_direct_weight_gradient_accumulators_skip_the_zero_fill():
     # step 3: w0 gets no gradient at all: the reduction must not see step 2's values
     opt.reduce_grads()
     assert torch.all(w0.main_grad == 0.0)                                                               # (3)
+
+
+def test_fp16_dynamic_loss_scale_skips_and_recovers():
+    """fp16 training with the dynamic scaler: a scale that overflows the gradients skips the update (parameters and
+    Adam state untouched, the step counted as skipped), halves after ``hysteresis`` overflows, and doubles again after
+    ``loss_scale_window`` clean steps (training.py:390-417 semantics of skipped iterations)."""
+    cfg = get_preset("bench-cpu-plumbing", num_experts=None, ffn_hidden_size=128, num_layers=1, layer_type_list="L",
+                     params_dtype=torch.float16)
+    tc = TrainConfig(micro_batch_size=1, global_batch_size=1, seq_length=32, train_iters=50, lr=1e-3, min_lr=1e-3,
+                     lr_decay_style="constant", weight_decay=0.0, clip_grad=1.0, log_interval=1000, seed=0, fp16=True,
+                     initial_loss_scale=2.0 ** 28, loss_scale_window=3, hysteresis=2, min_loss_scale=1.0)
+    ds = SyntheticTokenDataset(cfg.vocab_size, 32, num_samples=4, seed=0)
+    tr = Trainer(cfg, ParallelConfig(), tc, single_process_mesh(), device=torch.device("cpu"), dataset=ds)
+    opt = tr.optimizer
+    assert opt.dynamic_scale and opt.loss_scale == 2.0 ** 28
+    scales, skipped = [], []
+    for _ in range(30):
+        before = [p.detach().clone() for _, p in opt.named]
+        steps_before = opt.step_count
+        st = tr.train_step()
+        scales.append(opt.loss_scale)
+        skipped.append(st["skipped"])
+        moved = any(not torch.equal(a, p.detach()) for a, (_, p) in zip(before, opt.named))
+        assert moved == (not st["skipped"]), "a skipped step must leave the weights alone, a clean step must move them"
+        assert opt.step_count == steps_before + (0 if st["skipped"] else 1)
+    assert skipped[0] == 1 and skipped[1] == 1                 # 2^28 overflows fp16 gradients
+    # the scaler's rule, replayed on the observed overflow pattern
+    scale, hyst, clean, want = 2.0 ** 28, 2, 0, []
+    for sk in skipped:
+        if sk:
+            clean, hyst = 0, hyst - 1
+            if hyst <= 0:
+                scale = max(scale / 2.0, 1.0)
+        else:
+            clean += 1
+            if clean >= 3:
+                clean, hyst, scale = 0, 2, scale * 2.0
+        want.append(scale)
+    assert scales == want, (scales, want)
+    assert 0 in skipped and any(b > a for a, b in zip(scales, scales[1:])), "the scale never recovered"
+    assert opt.skipped_iters == sum(skipped) and tr.iteration == 30
