@@ -207,6 +207,13 @@ def build_parser() -> argparse.ArgumentParser:
           choices=["constant", "linear", "cosine", "inverse-square-root"])
     _flag(g, "--lr-decay-iters", type=int, default=None)
     _flag(g, "--lr-warmup-iters", type=int, default=0)
+    _flag(g, "--lr-warmup-fraction", type=float, default=None, help="warm-up as a fraction of the decay span")
+    _flag(g, "--train-samples", type=int, default=None, help="sample-based run length (with a constant global batch)")
+    _flag(g, "--lr-decay-samples", type=int, default=None)
+    _flag(g, "--lr-warmup-samples", type=int, default=0)
+    _flag(g, "--skip-train", action="store_true", help="evaluate only")
+    _flag(g, "--empty-unused-memory-level", type=int, default=0, choices=[0, 1, 2],
+          help="release the caching allocator's free blocks every step (1: after the step, 2: also after backward)")
     _flag(g, "--lr-warmup-init", type=float, default=0.0)
     _flag(g, "--weight-decay", type=float, default=0.1)
     _flag(g, "--start-weight-decay", type=float, default=None)
@@ -276,6 +283,16 @@ def build_parser() -> argparse.ArgumentParser:
     _flag(g, "--save-interval", type=int, default=None)
     _flag(g, "--pretrained-checkpoint", type=str, default=None)
     _flag(g, "--no-load-optim", action="store_true")
+    _flag(g, "--finetune", action="store_true",
+          help="load the weights only and start from iteration 0 (no optimizer state, no random state)")
+    _flag(g, "--exit-on-missing-checkpoint", action="store_true", help="stop when --load names no checkpoint")
+    _flag(g, "--ckpt-format", type=str, default=None, choices=["torch", "torch_dist"],
+          help="torch = the legacy mp_rank layout, torch_dist = the sharded format (same as --use-dist-ckpt)")
+    # accepted for launcher compatibility; what they ask for is always on here
+    _flag(g, "--accumulate-allreduce-grads-in-fp32", action="store_true", help="gradients are accumulated and reduced in fp32")
+    _flag(g, "--tp-comm-overlap", action="store_true", help="the fused all-gather / reduce-scatter GEMMs overlap by construction")
+    _flag(g, "--log-throughput", action="store_true", help="tokens/s and model FLOP/s utilisation are always in the log line")
+    _flag(g, "--mock-data", action="store_true", help="same as --dataset Synthetic")
     _flag(g, "--no-load-rng", action="store_true")
     _flag(g, "--no-save-optim", action="store_true")
     _flag(g, "--no-save-rng", action="store_true")
@@ -441,6 +458,21 @@ def configs_from_args(args: argparse.Namespace) -> Tuple[ModelConfig, ParallelCo
         fused_comm=not args.no_fused_comm, fused_comm_timeout_s=args.fused_comm_timeout_s,
     )
     gbs = args.global_batch_size if args.global_batch_size is not None else args.micro_batch_size
+    if args.train_samples is not None:              # sample-based schedule: the global batch is constant, so iterations
+        args.train_iters = args.train_samples // gbs
+        if args.lr_decay_samples is not None:
+            args.lr_decay_iters = args.lr_decay_samples // gbs
+        if args.lr_warmup_samples:
+            args.lr_warmup_iters = args.lr_warmup_samples // gbs
+    if args.lr_warmup_fraction is not None:
+        span = args.lr_decay_iters if args.lr_decay_iters is not None else args.train_iters
+        args.lr_warmup_iters = int(args.lr_warmup_fraction * span)
+    if args.finetune:
+        args.no_load_optim = args.no_load_rng = True
+    if args.ckpt_format == "torch_dist":
+        args.use_dist_ckpt = True
+    if args.mock_data:
+        args.dataset = "Synthetic"
     train = TrainConfig(
         micro_batch_size=args.micro_batch_size, global_batch_size=gbs, seq_length=args.seq_length,
         train_iters=args.train_iters, lr=args.lr, min_lr=args.min_lr, lr_decay_style=args.lr_decay_style,
@@ -463,6 +495,8 @@ def configs_from_args(args: argparse.Namespace) -> Tuple[ModelConfig, ParallelCo
         log_validation_ppl_to_tensorboard=args.log_validation_ppl_to_tensorboard,
         timing_log_level=args.timing_log_level, barrier_with_L1_time=args.barrier_with_L1_time,
         exit_interval=args.exit_interval, exit_duration_in_mins=args.exit_duration_in_mins,
+        finetune=args.finetune, exit_on_missing_checkpoint=args.exit_on_missing_checkpoint, skip_train=args.skip_train,
+        empty_unused_memory_level=args.empty_unused_memory_level,
         adlr_autoresume=args.adlr_autoresume, adlr_autoresume_interval=args.adlr_autoresume_interval,
         manual_gc=args.manual_gc, manual_gc_interval=args.manual_gc_interval,
         exit_signal_handler=args.exit_signal_handler,

@@ -266,6 +266,10 @@ class TrainConfig:
     barrier_with_L1_time: bool = True
     exit_interval: Optional[int] = None
     exit_duration_in_mins: Optional[float] = None
+    finetune: bool = False                        # --finetune: weights only, iteration and sample counters start at 0
+    exit_on_missing_checkpoint: bool = False
+    skip_train: bool = False
+    empty_unused_memory_level: int = 0
     adlr_autoresume: bool = False                 # --adlr-autoresume: ask the scheduler's auto-resume service every interval
     adlr_autoresume_interval: int = 1000
     manual_gc: bool = False                       # --manual-gc: Python's collector off, collected by hand every manual_gc_interval steps

@@ -133,8 +133,12 @@ class Trainer:
         self.heartbeat = Heartbeat(self.mesh, tc.heartbeat_interval_s, tc.heartbeat_timeout_s) \
             if tc.heartbeat_interval_s > 0 else None
         self.flops_per_token = model_flops_per_token(cfg, tc.seq_length)
-        if tc.load:
-            self.load(tc.load)
+        if tc.load and not self._has_checkpoint(tc.load):
+            if tc.exit_on_missing_checkpoint:
+                raise SystemExit(f"--exit-on-missing-checkpoint: no checkpoint under {tc.load}")
+            print_rank_0(f"> no checkpoint under {tc.load}: starting from the initial weights")
+        elif tc.load:
+            self.load(tc.load, model_only=tc.finetune)
         elif tc.pretrained_checkpoint:
             self.load(tc.pretrained_checkpoint, model_only=True)
             self.optimizer.reload_model_params()
@@ -212,6 +216,8 @@ class Trainer:
             inner = getattr(m, "module", m)
             if getattr(inner, "offload", None) is not None:
                 inner.offload.step_done()
+        if tc.empty_unused_memory_level >= 2 and self.device.type == "cuda":
+            torch.cuda.empty_cache()
         timers("all-grads-sync", 1).start()
         self.optimizer.reduce_grads()
         if self.device.type == "cuda":
@@ -222,6 +228,8 @@ class Trainer:
         lr, wd = self.scheduler.get_lr(), self.scheduler.get_wd()
         ok, grad_norm, _ = self.optimizer.step(lr, wd, pre_update=self._check_kernels)
         timers("optimizer").stop()
+        if tc.empty_unused_memory_level >= 1 and self.device.type == "cuda":
+            torch.cuda.empty_cache()
         if ok:
             self.scheduler.step(1)
         self.iteration += 1
@@ -339,6 +347,11 @@ class Trainer:
         """Global index of the first layer of every model chunk of this pipeline stage."""
         per = self.cfg.num_layers // (self.mesh.pp * len(self.models))
         return [(i * self.mesh.pp + self.mesh.pp_rank) * per for i in range(len(self.models))]
+
+    @staticmethod
+    def _has_checkpoint(path: str) -> bool:
+        from ..ckpt import sharded
+        return any(os.path.isfile(os.path.join(path, f)) for f in (sharded.TRACKER, "latest_checkpointed_iteration.txt"))
 
     def load(self, path: str, model_only: bool = False):
         from ..ckpt import sharded
@@ -468,6 +481,11 @@ def pretrain(argv=None, dataset_provider: Optional[Callable] = None, model_provi
     trainer = Trainer(cfg, par, tc, mesh, dataset=train_ds, valid_dataset=valid_ds, model_provider=model_provider,
                       forward_step=forward_step)
     print_rank_0(f"> parameters on this rank: {count_parameters(trainer.models):,}")
+    if tc.skip_train:
+        stats = trainer.evaluate(tc.eval_iters) or {}
+        if mesh.rank == 0 and stats:
+            print_rank_0("validation: " + " | ".join(f"{k} {float(v):.6E}" for k, v in stats.items()))
+        return trainer, stats
     stats = trainer.train()
     if tc.save:
         trainer.save()

@@ -258,3 +258,39 @@ def test_autoresume_checkpoints_and_exits(tmp_path, monkeypatch):
     stop.write_text("")
     tr2.train()
     assert tr2.iteration == 3
+
+
+def test_sample_based_schedule_and_checkpoint_flags(tmp_path):
+    """Megatron's general training flags beyond the reference's launchers: sample-based run length and warm-up, warm-up
+    as a fraction, --finetune (weights only, counters at 0), --exit-on-missing-checkpoint, --ckpt-format, --mock-data."""
+    from linear_moe_b200.config.arguments import parse_args
+    from linear_moe_b200.config.model_config import ParallelConfig
+    from linear_moe_b200.train.loop import Trainer
+    base = ["--num-layers", "1", "--hidden-size", "32", "--num-attention-heads", "2", "--ffn-hidden-size", "64",
+            "--vocab-size", "64", "--seq-length", "16", "--micro-batch-size", "2", "--global-batch-size", "4", "--lr", "1e-3"]
+    _, _, _, tc = parse_args(base + ["--train-samples", "400", "--lr-decay-samples", "320", "--lr-warmup-samples", "40"])
+    assert (tc.train_iters, tc.lr_decay_iters, tc.lr_warmup_iters) == (100, 80, 10)
+    _, _, _, tc = parse_args(base + ["--train-iters", "200", "--lr-warmup-fraction", "0.05", "--ckpt-format", "torch_dist",
+                                     "--mock-data", "--tp-comm-overlap", "--log-throughput",
+                                     "--accumulate-allreduce-grads-in-fp32"])
+    assert tc.lr_warmup_iters == 10 and tc.use_dist_ckpt and tc.dataset == "Synthetic"
+    # a run to fine-tune from
+    _, cfg, _, tc = parse_args(base + ["--train-iters", "3", "--save", str(tmp_path / "ck"), "--log-interval", "100"])
+    tr = Trainer(cfg, ParallelConfig(), tc, device=torch.device("cpu"))
+    for _ in range(3):
+        tr.train_step()
+    tr.save()
+    _, cfg, _, tc = parse_args(base + ["--train-iters", "3", "--load", str(tmp_path / "ck"), "--finetune"])
+    assert tc.no_load_optim and tc.no_load_rng
+    ft = Trainer(cfg, ParallelConfig(), tc, device=torch.device("cpu"))
+    assert ft.iteration == 0 and ft.consumed_samples == 0 and ft.optimizer.step_count == 0
+    a, b = tr.models[0].state_dict(), ft.models[0].state_dict()
+    assert all(torch.equal(a[k], b[k]) for k in a)
+    _, cfg, _, tc = parse_args(base + ["--load", str(tmp_path / "ck")])
+    assert Trainer(cfg, ParallelConfig(), tc, device=torch.device("cpu")).iteration == 3
+    # nothing to load
+    _, cfg, _, tc = parse_args(base + ["--load", str(tmp_path / "nothing")])
+    assert Trainer(cfg, ParallelConfig(), tc, device=torch.device("cpu")).iteration == 0
+    _, cfg, _, tc = parse_args(base + ["--load", str(tmp_path / "nothing"), "--exit-on-missing-checkpoint"])
+    with pytest.raises(SystemExit):
+        Trainer(cfg, ParallelConfig(), tc, device=torch.device("cpu"))
