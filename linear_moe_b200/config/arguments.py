@@ -283,6 +283,10 @@ def build_parser() -> argparse.ArgumentParser:
     _flag(g, "--save-interval", type=int, default=None)
     _flag(g, "--pretrained-checkpoint", type=str, default=None)
     _flag(g, "--no-load-optim", action="store_true")
+    _flag(g, "--override-opt_param-scheduler", action="store_true", dest="override_opt_param_scheduler",
+          help="on resume take the learning-rate schedule from the command line (the default), without the note")
+    _flag(g, "--use-checkpoint-opt_param-scheduler", action="store_true", dest="use_checkpoint_opt_param_scheduler",
+          help="on resume take the learning-rate schedule stored in the checkpoint")
     _flag(g, "--finetune", action="store_true",
           help="load the weights only and start from iteration 0 (no optimizer state, no random state)")
     _flag(g, "--exit-on-missing-checkpoint", action="store_true", help="stop when --load names no checkpoint")
@@ -495,6 +499,8 @@ def configs_from_args(args: argparse.Namespace) -> Tuple[ModelConfig, ParallelCo
         log_validation_ppl_to_tensorboard=args.log_validation_ppl_to_tensorboard,
         timing_log_level=args.timing_log_level, barrier_with_L1_time=args.barrier_with_L1_time,
         exit_interval=args.exit_interval, exit_duration_in_mins=args.exit_duration_in_mins,
+        override_opt_param_scheduler=args.override_opt_param_scheduler,
+        use_checkpoint_opt_param_scheduler=args.use_checkpoint_opt_param_scheduler,
         finetune=args.finetune, exit_on_missing_checkpoint=args.exit_on_missing_checkpoint, skip_train=args.skip_train,
         empty_unused_memory_level=args.empty_unused_memory_level,
         adlr_autoresume=args.adlr_autoresume, adlr_autoresume_interval=args.adlr_autoresume_interval,

@@ -266,6 +266,8 @@ class TrainConfig:
     barrier_with_L1_time: bool = True
     exit_interval: Optional[int] = None
     exit_duration_in_mins: Optional[float] = None
+    override_opt_param_scheduler: bool = False
+    use_checkpoint_opt_param_scheduler: bool = False
     finetune: bool = False                        # --finetune: weights only, iteration and sample counters start at 0
     exit_on_missing_checkpoint: bool = False
     skip_train: bool = False

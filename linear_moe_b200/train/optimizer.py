@@ -547,8 +547,30 @@ class OptimizerParamScheduler:
     def step(self, increment: int = 1):
         self.num_steps += increment
 
+    _SAVED = ("lr", "min_lr", "lr_decay_style", "lr_warmup_init", "weight_decay_incr_style")
+
     def state_dict(self):
-        return {"num_steps": self.num_steps}
+        sd = {"num_steps": self.num_steps, "decay_steps": self.decay_steps, "warmup": self.warmup,
+              "start_wd": self.start_wd, "end_wd": self.end_wd}
+        sd.update({k: getattr(self.tc, k) for k in self._SAVED})
+        return sd
 
     def load_state_dict(self, sd):
+        """The step count always comes from the checkpoint.  The schedule's shape comes from the command line
+        (``--override-opt_param-scheduler``, also the default here, with a note when the two differ) or from the checkpoint
+        (``--use-checkpoint-opt_param-scheduler``)."""
         self.num_steps = sd["num_steps"]
+        mine = self.state_dict()
+        differ = sorted(k for k in sd if k != "num_steps" and k in mine and sd[k] != mine[k])
+        if not differ:
+            return
+        if getattr(self.tc, "use_checkpoint_opt_param_scheduler", False):
+            for k in ("decay_steps", "warmup", "start_wd", "end_wd"):
+                if k in sd:
+                    setattr(self, k, sd[k])
+            for k in self._SAVED:
+                if k in sd:
+                    setattr(self.tc, k, sd[k])
+        elif not getattr(self.tc, "override_opt_param_scheduler", False):
+            print(f"> learning-rate schedule: the command line differs from the checkpoint in {differ}; using the command "
+                  "line (--use-checkpoint-opt_param-scheduler keeps the checkpoint's)", flush=True)

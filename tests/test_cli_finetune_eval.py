@@ -294,3 +294,25 @@ def test_sample_based_schedule_and_checkpoint_flags(tmp_path):
     _, cfg, _, tc = parse_args(base + ["--load", str(tmp_path / "nothing"), "--exit-on-missing-checkpoint"])
     with pytest.raises(SystemExit):
         Trainer(cfg, ParallelConfig(), tc, device=torch.device("cpu"))
+
+
+def test_resume_takes_the_schedule_from_the_command_line_or_the_checkpoint(tmp_path):
+    from linear_moe_b200.config.arguments import parse_args
+    from linear_moe_b200.config.model_config import ParallelConfig
+    from linear_moe_b200.train.loop import Trainer
+    base = ["--num-layers", "1", "--hidden-size", "32", "--num-attention-heads", "2", "--ffn-hidden-size", "64",
+            "--vocab-size", "64", "--seq-length", "16", "--micro-batch-size", "1", "--train-iters", "40",
+            "--lr-decay-style", "cosine", "--lr-warmup-iters", "2", "--log-interval", "100"]
+    _, cfg, _, tc = parse_args(base + ["--lr", "1e-3", "--min-lr", "1e-4", "--save", str(tmp_path)])
+    tr = Trainer(cfg, ParallelConfig(), tc, device=torch.device("cpu"))
+    for _ in range(5):
+        tr.train_step()
+    tr.save()
+    want_ckpt = tr.scheduler.get_lr()
+    _, cfg, _, tc = parse_args(base + ["--lr", "5e-4", "--min-lr", "5e-5", "--load", str(tmp_path)])
+    cli = Trainer(cfg, ParallelConfig(), tc, device=torch.device("cpu"))
+    assert cli.scheduler.num_steps == 5 and abs(cli.scheduler.get_lr() - want_ckpt / 2) < 1e-9
+    _, cfg, _, tc = parse_args(base + ["--lr", "5e-4", "--min-lr", "5e-5", "--load", str(tmp_path),
+                                      "--use-checkpoint-opt_param-scheduler"])
+    kept = Trainer(cfg, ParallelConfig(), tc, device=torch.device("cpu"))
+    assert abs(kept.scheduler.get_lr() - want_ckpt) < 1e-12
