@@ -5,6 +5,7 @@ samples and every stage receives the sampled tokens; rank 0 prints the completio
 
   python examples/generate.py --load /path/to/ckpt --text-generate-input-file prompts.jsonl <model flags>
   torchrun --nproc-per-node 2 --master-addr 127.0.0.1 examples/generate.py --pipeline-model-parallel-size 2 ...
+  LMOE_SERVE_PORT=5000 python examples/generate.py --load /path/to/ckpt <model flags>     # serve PUT /api instead
 """
 import os
 import sys
@@ -40,6 +41,19 @@ if __name__ == "__main__":
             load_sharded(tc.load, [model], cfg, mesh, None, layer_offsets=[mesh.pp_rank * per])
         else:
             load_checkpoint(tc.load, [model], None, None, mesh, load_rng=False)
+    port = int(os.environ.get("LMOE_SERVE_PORT", "0"))
+    if port:
+        # HTTP endpoint (PUT /api, the request fields of Megatron's text-generation server): rank 0 serves, the other
+        # ranks of a parallel replica join every generation call
+        from linear_moe_b200.infer.server import build_app, serve_followers
+        graph = getattr(args, "cuda_graph_decode", False)
+        if mesh.rank == 0:
+            import uvicorn
+            uvicorn.run(build_app(model.eval(), tok, cuda_graph=graph), host=os.environ.get("LMOE_SERVE_HOST", "127.0.0.1"),
+                        port=port, log_level="warning")
+        else:
+            serve_followers(model.eval(), tok, cuda_graph=graph)
+        sys.exit(0)
     outs = GPTPredictor(model, tok, args).predict()
     if mesh.rank == 0:
         for out in outs:
