@@ -60,3 +60,39 @@ def test_bad_requests_are_refused_with_a_message(client, body, needle):
     r = c.put("/api", json=body)
     assert r.status_code == 400 and needle in r.json()["message"]
     assert c.put("/api", content=b"not json").status_code == 400
+
+
+def _parallel_worker(rank, world):
+    from linear_moe_b200.config.model_config import ParallelConfig
+    from linear_moe_b200.dist.mesh import Mesh
+    from linear_moe_b200.infer import server as S
+    mesh = Mesh(ParallelConfig(distributed_backend="gloo", tensor_model_parallel_size=2))
+    cfg = ModelConfig(num_layers=2, hidden_size=64, num_attention_heads=4, ffn_hidden_size=128, vocab_size=128,
+                      use_la_module=True, la_module="gla", layer_type_list="LN", init_method_std=0.1)
+    model, tok = CausalLM(cfg, mesh).eval(), NullTokenizer(128)
+    if rank != 0:
+        S.serve_followers(model, tok)
+        return None
+    outs = []
+    with torch.no_grad():
+        for req in ({"prompts": ["1 2 3 4"], "tokens_to_generate": 4, "top_k": 1},
+                    {"prompts": ["7 7 7", "3 2 1 0 9"], "tokens_to_generate": 3, "top_k": 1, "logprobs": True}):
+            S._broadcast_request(req, None)
+            outs.append(S.run_request(model, tok, req))
+    S._broadcast_request(None, None)
+    return outs
+
+
+def test_follower_ranks_join_every_request(client):
+    """A tensor-parallel replica: rank 0 hands each request to the follower loop of rank 1 and both generate together;
+    the tokens equal those of the single-process model."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from dist_utils import run_distributed
+    c, _, _ = client
+    outs = run_distributed(_parallel_worker, 2)[0]
+    one = c.put("/api", json={"prompts": ["1 2 3 4"], "tokens_to_generate": 4, "top_k": 1}).json()
+    two = c.put("/api", json={"prompts": ["7 7 7", "3 2 1 0 9"], "tokens_to_generate": 3, "top_k": 1, "logprobs": True}).json()
+    assert outs[0]["tokens"] == one["tokens"] and outs[1]["tokens"] == two["tokens"]
+    assert abs(outs[1]["logprobs"][1][3] - two["logprobs"][1][3]) < 1e-4
