@@ -212,6 +212,8 @@ def build_parser() -> argparse.ArgumentParser:
     _flag(g, "--lr-decay-samples", type=int, default=None)
     _flag(g, "--lr-warmup-samples", type=int, default=0)
     _flag(g, "--skip-train", action="store_true", help="evaluate only")
+    _flag(g, "--rampup-batch-size", type=int, nargs=3, default=None, metavar=("START", "INCREMENT", "SAMPLES"),
+          help="grow the global batch from START by INCREMENT to --global-batch-size over the first SAMPLES samples")
     _flag(g, "--empty-unused-memory-level", type=int, default=0, choices=[0, 1, 2],
           help="release the caching allocator's free blocks every step (1: after the step, 2: also after backward)")
     _flag(g, "--lr-warmup-init", type=float, default=0.0)
@@ -499,6 +501,7 @@ def configs_from_args(args: argparse.Namespace) -> Tuple[ModelConfig, ParallelCo
         log_validation_ppl_to_tensorboard=args.log_validation_ppl_to_tensorboard,
         timing_log_level=args.timing_log_level, barrier_with_L1_time=args.barrier_with_L1_time,
         exit_interval=args.exit_interval, exit_duration_in_mins=args.exit_duration_in_mins,
+        rampup_batch_size=tuple(args.rampup_batch_size) if args.rampup_batch_size else None,
         override_opt_param_scheduler=args.override_opt_param_scheduler,
         use_checkpoint_opt_param_scheduler=args.use_checkpoint_opt_param_scheduler,
         finetune=args.finetune, exit_on_missing_checkpoint=args.exit_on_missing_checkpoint, skip_train=args.skip_train,

@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import dataclasses
 from dataclasses import dataclass, field
-from typing import List, Optional
+from typing import List, Optional, Tuple
 
 import torch
 
@@ -266,6 +266,7 @@ class TrainConfig:
     barrier_with_L1_time: bool = True
     exit_interval: Optional[int] = None
     exit_duration_in_mins: Optional[float] = None
+    rampup_batch_size: Optional[Tuple[int, int, int]] = None     # --rampup-batch-size start increment ramp-up-samples
     override_opt_param_scheduler: bool = False
     use_checkpoint_opt_param_scheduler: bool = False
     finetune: bool = False                        # --finetune: weights only, iteration and sample counters start at 0

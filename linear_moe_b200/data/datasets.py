@@ -303,7 +303,9 @@ class BatchIterator:
         mesh = self.mesh
         base = self.consumed + mesh.dp_rank * self.mbs
         self.consumed += self.mbs * mesh.dp
-        rows = [self.ds[(base + i) % len(self.ds)] for i in range(self.mbs)]
+        idx = [(base + i) % len(self.ds) for i in range(self.mbs)]
+        batched = getattr(self.ds, "__getitems__", None)        # one native call for the whole micro-batch where there is one
+        rows = batched(idx) if batched is not None else [self.ds[j] for j in idx]
         sample = {k: torch.stack([r[k] for r in rows]) for k in rows[0]}
         batch = make_batch(sample, **self.kw)
         batch = slice_for_context_parallel(batch, mesh)

@@ -112,6 +112,13 @@ class Trainer:
         assert tc.global_batch_size % (tc.micro_batch_size * dp) == 0, \
             f"global batch {tc.global_batch_size} not divisible by micro batch {tc.micro_batch_size} x dp {dp}"
         self.num_microbatches = tc.global_batch_size // (tc.micro_batch_size * dp)
+        self.global_batch_now = tc.global_batch_size
+        if tc.rampup_batch_size:
+            start, incr, _ = tc.rampup_batch_size
+            unit = tc.micro_batch_size * dp
+            assert start % unit == 0 and incr % unit == 0 and (tc.global_batch_size - start) % incr == 0 and incr > 0, \
+                f"--rampup-batch-size {tc.rampup_batch_size}: start and increment must be multiples of micro batch x dp = " \
+                f"{unit} and the increments must reach the global batch {tc.global_batch_size}"
         if dataset is None:
             dataset = SyntheticTokenDataset(cfg.vocab_size, tc.seq_length, seed=tc.seed)
         self.dataset, self.valid_dataset = dataset, valid_dataset
@@ -201,10 +208,24 @@ class Trainer:
         elif tc.manual_gc_interval and self.iteration % tc.manual_gc_interval == 0:
             gc.collect()
 
+    def _ramped_global_batch(self, consumed: int) -> int:
+        """``--rampup-batch-size start increment samples``: the global batch grows from ``start`` to the configured size
+        in equal increments spread over the first ``samples`` samples (Megatron's ramp-up micro-batch calculator)."""
+        tc = self.tc
+        if not tc.rampup_batch_size:
+            return tc.global_batch_size
+        start, incr, ramp = tc.rampup_batch_size
+        steps = (tc.global_batch_size - start) // incr
+        if steps <= 0 or consumed >= ramp:
+            return tc.global_batch_size
+        return min(start + int(consumed / (ramp / steps)) * incr, tc.global_batch_size)
+
     def train_step(self) -> Dict[str, float]:
         tc, mesh = self.tc, self.mesh
         timers = self.timers
         self._manual_gc()
+        self.global_batch_now = self._ramped_global_batch(self.consumed_samples)
+        self.num_microbatches = self.global_batch_now // (tc.micro_batch_size * mesh.dp)
         for m in self.models:
             m.train()
         self.optimizer.zero_grad()
@@ -233,7 +254,7 @@ class Trainer:
         if ok:
             self.scheduler.step(1)
         self.iteration += 1
-        self.consumed_samples += tc.global_batch_size
+        self.consumed_samples += self.global_batch_now
         out = {"lr": lr, "grad_norm": grad_norm, "skipped": 0 if ok else 1}
         if mesh.is_last_stage and logs:
             keys = logs[0].keys()
@@ -255,7 +276,7 @@ class Trainer:
         if self.iteration % tc.log_interval != 0:
             return
         per_iter = elapsed_s / max(self._log_n, 1)
-        tokens = tc.global_batch_size * tc.seq_length
+        tokens = self.global_batch_now * tc.seq_length
         tps = tokens / per_iter
         gpus = mesh.world_size
         mfu = None
@@ -264,7 +285,7 @@ class Trainer:
         line = (f" iteration {self.iteration:8d}/{tc.train_iters:8d} | consumed samples: {self.consumed_samples:12d} |"
                 f" elapsed time per iteration (ms): {per_iter * 1000:.1f} | tokens/s: {tps:.0f} |"
                 f" tokens/s/gpu: {tps / gpus:.0f} | learning rate: {stats['lr']:.3E} |"
-                f" global batch size: {tc.global_batch_size:5d} |")
+                f" global batch size: {self.global_batch_now:5d} |")
         for k, v in self._log_acc.items():
             if k != "skipped":
                 line += f" {k}: {v / max(self._log_n, 1):.6E} |"
@@ -288,7 +309,7 @@ class Trainer:
         if self.writer is not None:
             it = self.iteration
             self.writer.add_scalar("learning-rate", stats["lr"], it)
-            self.writer.add_scalar("batch-size", tc.global_batch_size, it)
+            self.writer.add_scalar("batch-size", self.global_batch_now, it)
             self.writer.add_scalar("tokens-per-second", tps, it)
             for k, v in self._log_acc.items():
                 self.writer.add_scalar(k, v / max(self._log_n, 1), it)

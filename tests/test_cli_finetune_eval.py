@@ -316,3 +316,31 @@ def test_resume_takes_the_schedule_from_the_command_line_or_the_checkpoint(tmp_p
                                       "--use-checkpoint-opt_param-scheduler"])
     kept = Trainer(cfg, ParallelConfig(), tc, device=torch.device("cpu"))
     assert abs(kept.scheduler.get_lr() - want_ckpt) < 1e-12
+
+
+def test_batch_size_rampup(tmp_path):
+    """--rampup-batch-size 2 2 12 with a global batch of 6: batches 2 (samples 0-5), 4 (6-11), then 6; the sample
+    counter, the number of micro-batches and the data position follow, also across a resume."""
+    from linear_moe_b200.config.arguments import parse_args
+    from linear_moe_b200.config.model_config import ParallelConfig
+    from linear_moe_b200.train.loop import Trainer
+    base = ["--num-layers", "1", "--hidden-size", "32", "--num-attention-heads", "2", "--ffn-hidden-size", "64",
+            "--vocab-size", "64", "--seq-length", "16", "--micro-batch-size", "1", "--global-batch-size", "6", "--lr", "1e-3",
+            "--train-iters", "9", "--log-interval", "100", "--rampup-batch-size", "2", "2", "12", "--save", str(tmp_path)]
+    _, cfg, _, tc = parse_args(base)
+    assert tc.rampup_batch_size == (2, 2, 12)
+    tr = Trainer(cfg, ParallelConfig(), tc, device=torch.device("cpu"))
+    seen = []
+    for _ in range(7):
+        tr.train_step()
+        seen.append((tr.global_batch_now, tr.num_microbatches, tr.consumed_samples))
+    assert [s[0] for s in seen] == [2, 2, 2, 4, 4, 6, 6]
+    assert [s[1] for s in seen] == [2, 2, 2, 4, 4, 6, 6] and seen[-1][2] == 26 and tr.data_iter.consumed == 26
+    tr.save()
+    _, cfg, _, tc = parse_args(base + ["--load", str(tmp_path)])
+    again = Trainer(cfg, ParallelConfig(), tc, device=torch.device("cpu"))
+    a, b = tr.train_step(), again.train_step()
+    assert again.consumed_samples == 32 and abs(float(a["lm loss"]) - float(b["lm loss"])) < 1e-6
+    with pytest.raises(AssertionError):
+        _, cfg, _, tc = parse_args(base[:-6] + ["--rampup-batch-size", "2", "3", "12"])
+        Trainer(cfg, ParallelConfig(), tc, device=torch.device("cpu"))
