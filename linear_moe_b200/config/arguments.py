@@ -157,6 +157,11 @@ def build_parser() -> argparse.ArgumentParser:
     _flag(g, "--moe-z-loss-coeff", "--z-loss-weight", type=float, default=0.0, dest="moe_z_loss_coeff")
     _flag(g, "--moe-input-jitter-eps", type=float, default=None)
     _flag(g, "--moe-token-dropping", action="store_true")
+    _flag(g, "--moe-expert-capacity-factor", type=float, default=None,
+          help="Megatron's spelling (the reference's router reads config.moe_expert_capacity_factor, router.py:238): sets "
+               "the training and evaluation capacity factors and switches token dropping on")
+    _flag(g, "--moe-router-pre-softmax", action="store_true", help="softmax over all experts before the top-k selection")
+    _flag(g, "--moe-per-layer-logging", action="store_true", help="log the auxiliary losses of every MoE layer")
     _flag(g, "--moe-train-capacity-factor", type=float, default=None)
     _flag(g, "--moe-eval-capacity-factor", type=float, default=None)
     _flag(g, "--moe-min-capacity", type=int, default=4)
@@ -374,6 +379,12 @@ def pad_vocab(vocab: int, divisible_by: int, tp: int) -> int:
 
 
 def configs_from_args(args: argparse.Namespace) -> Tuple[ModelConfig, ParallelConfig, TrainConfig]:
+    if args.moe_expert_capacity_factor is not None:
+        args.moe_token_dropping = True
+        if args.moe_train_capacity_factor is None:
+            args.moe_train_capacity_factor = args.moe_expert_capacity_factor
+        if args.moe_eval_capacity_factor is None:
+            args.moe_eval_capacity_factor = args.moe_expert_capacity_factor
     dtype = torch.bfloat16 if args.bf16 else torch.float16 if args.fp16 else torch.float32
     vocab = args.vocab_size if args.vocab_size is not None else 32000
     vocab = pad_vocab(vocab + args.extra_vocab_size, args.make_vocab_size_divisible_by,
@@ -430,6 +441,7 @@ def configs_from_args(args: argparse.Namespace) -> Tuple[ModelConfig, ParallelCo
         enable_shared_expert=args.enable_shared_expert, num_shared_experts=args.num_shared_experts,
         moe_layer_freq=args.moe_layer_freq, expert_interval=args.expert_interval,
         moe_router_load_balancing_type=args.moe_router_load_balancing_type,
+        moe_router_order="softmax_topk" if args.moe_router_pre_softmax else None,
         moe_aux_loss_coeff=args.moe_aux_loss_coeff, moe_z_loss_coeff=args.moe_z_loss_coeff,
         moe_input_jitter_eps=args.moe_input_jitter_eps, moe_token_dropping=args.moe_token_dropping,
         moe_train_capacity_factor=args.moe_train_capacity_factor,
@@ -501,6 +513,7 @@ def configs_from_args(args: argparse.Namespace) -> Tuple[ModelConfig, ParallelCo
         log_validation_ppl_to_tensorboard=args.log_validation_ppl_to_tensorboard,
         timing_log_level=args.timing_log_level, barrier_with_L1_time=args.barrier_with_L1_time,
         exit_interval=args.exit_interval, exit_duration_in_mins=args.exit_duration_in_mins,
+        moe_per_layer_logging=args.moe_per_layer_logging,
         rampup_batch_size=tuple(args.rampup_batch_size) if args.rampup_batch_size else None,
         override_opt_param_scheduler=args.override_opt_param_scheduler,
         use_checkpoint_opt_param_scheduler=args.use_checkpoint_opt_param_scheduler,

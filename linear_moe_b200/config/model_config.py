@@ -266,6 +266,7 @@ class TrainConfig:
     barrier_with_L1_time: bool = True
     exit_interval: Optional[int] = None
     exit_duration_in_mins: Optional[float] = None
+    moe_per_layer_logging: bool = False           # the auxiliary losses of every MoE layer in the log line and TensorBoard
     rampup_batch_size: Optional[Tuple[int, int, int]] = None     # --rampup-batch-size start increment ramp-up-samples
     override_opt_param_scheduler: bool = False
     use_checkpoint_opt_param_scheduler: bool = False

@@ -300,6 +300,13 @@ class Trainer:
         aux = AuxLossTracker.pop()
         for k, v in aux.items():
             line += f" {k}: {float(v.sum()) / max(self.cfg.num_layers, 1) / max(self._log_n, 1):.4E} |"
+            if tc.moe_per_layer_logging:
+                per = (v / max(self._log_n, 1)).tolist()
+                line += "".join(f" moe/{k}_layer_{i}: {x:.4E} |" for i, x in enumerate(per) if x != 0.0)
+                if self.writer is not None:
+                    for i, x in enumerate(per):
+                        if x != 0.0:
+                            self.writer.add_scalar(f"moe/{k}_layer_{i}", x, self.iteration)
         if mesh.rank == mesh.world_size - 1 or mesh.world_size == 1:
             print(line, flush=True)
         if tc.timing_log_level >= 0:

@@ -344,3 +344,21 @@ def test_batch_size_rampup(tmp_path):
     with pytest.raises(AssertionError):
         _, cfg, _, tc = parse_args(base[:-6] + ["--rampup-batch-size", "2", "3", "12"])
         Trainer(cfg, ParallelConfig(), tc, device=torch.device("cpu"))
+
+
+def test_megatron_moe_flag_spellings(capsys):
+    from linear_moe_b200.config.arguments import parse_args
+    from linear_moe_b200.config.model_config import ParallelConfig
+    from linear_moe_b200.train.loop import Trainer
+    base = ["--num-layers", "2", "--hidden-size", "32", "--num-attention-heads", "2", "--ffn-hidden-size", "64",
+            "--vocab-size", "64", "--seq-length", "16", "--micro-batch-size", "2", "--num-experts", "4", "--moe-router-topk", "2",
+            "--moe-ffn-hidden-size", "32", "--moe-aux-loss-coeff", "0.01", "--base-model", "mixtral"]
+    _, cfg, _, tc = parse_args(base + ["--moe-expert-capacity-factor", "1.5", "--moe-router-pre-softmax",
+                                       "--moe-per-layer-logging", "--train-iters", "2", "--log-interval", "1"])
+    assert cfg.moe_token_dropping and cfg.moe_train_capacity_factor == 1.5 and cfg.moe_eval_capacity_factor == 1.5
+    assert cfg.moe_router_order == "softmax_topk" and tc.moe_per_layer_logging
+    _, plain, _, _ = parse_args(base)
+    assert plain.moe_router_order == "topk_softmax" and not plain.moe_token_dropping
+    Trainer(cfg, ParallelConfig(), tc, device=torch.device("cpu")).train()
+    out = capsys.readouterr().out
+    assert "moe/load_balancing_loss_layer_0:" in out and "moe/load_balancing_loss_layer_1:" in out
