@@ -304,6 +304,9 @@ def build_parser() -> argparse.ArgumentParser:
     _flag(g, "--tp-comm-overlap", action="store_true", help="the fused all-gather / reduce-scatter GEMMs overlap by construction")
     _flag(g, "--log-throughput", action="store_true", help="tokens/s and model FLOP/s utilisation are always in the log line")
     _flag(g, "--mock-data", action="store_true", help="same as --dataset Synthetic")
+    _flag(g, "--attention-softmax-in-fp32", action="store_true", help="the attention kernels always take the softmax in fp32")
+    _flag(g, "--use-cpu-initialization", action="store_true",
+          help="initial weights depend on (seed, parameter name) only, so every parallel layout starts from the same model")
     _flag(g, "--no-load-rng", action="store_true")
     _flag(g, "--no-save-optim", action="store_true")
     _flag(g, "--no-save-rng", action="store_true")
