@@ -12,6 +12,8 @@ from linear_moe_b200.models.transformer import CausalLM
 @pytest.fixture(scope="module")
 def client():
     from fastapi.testclient import TestClient
+    from linear_moe_b200.parallel.tensor_parallel import set_init_seed
+    set_init_seed(1234)             # earlier tests in the same process may have trained with another seed
     torch.manual_seed(0)
     cfg = ModelConfig(num_layers=2, hidden_size=64, num_attention_heads=4, ffn_hidden_size=128, vocab_size=128,
                       use_la_module=True, la_module="gla", layer_type_list="LN", init_method_std=0.1)
@@ -66,6 +68,8 @@ def _parallel_worker(rank, world):
     from linear_moe_b200.config.model_config import ParallelConfig
     from linear_moe_b200.dist.mesh import Mesh
     from linear_moe_b200.infer import server as S
+    from linear_moe_b200.parallel.tensor_parallel import set_init_seed
+    set_init_seed(1234)
     mesh = Mesh(ParallelConfig(distributed_backend="gloo", tensor_model_parallel_size=2))
     cfg = ModelConfig(num_layers=2, hidden_size=64, num_attention_heads=4, ffn_hidden_size=128, vocab_size=128,
                       use_la_module=True, la_module="gla", layer_type_list="LN", init_method_std=0.1)
