@@ -120,3 +120,35 @@ def test_deepseek_v2_parity():
                       kv_lora_rank=32, q_lora_rank=None, qk_rope_head_dim=8, qk_nope_head_dim=16, v_head_dim=16,
                       max_position_embeddings=128)
     _check(cfg, hf, 320)
+
+
+def test_qwen2_dense_parity():
+    """Dense Qwen2 / Qwen1.5 (QKV bias, GQA): the dense branch of the Qwen convertor."""
+    hc = transformers.Qwen2Config(vocab_size=320, hidden_size=64, intermediate_size=112, num_hidden_layers=2,
+                                  num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=128,
+                                  rms_norm_eps=1e-6, rope_theta=10000.0, tie_word_embeddings=False, use_sliding_window=False)
+    torch.manual_seed(0)
+    hf = transformers.Qwen2ForCausalLM(hc)
+    with torch.no_grad():                                   # biases are zero at init: make them count
+        for n, p in hf.named_parameters():
+            if n.endswith("_proj.bias"):
+                p.normal_(0, 0.05)
+    cfg = ModelConfig(base_model="qwen2", num_layers=2, hidden_size=64, num_attention_heads=4, num_query_groups=2,
+                      ffn_hidden_size=112, vocab_size=320, norm_eps=1e-6, rotary_base=10000.0, add_qkv_bias=True,
+                      max_position_embeddings=128)
+    _check(cfg, hf, 320)
+
+
+def test_mistral_dense_parity_with_sliding_window():
+    """Dense Mistral (the reference's mistral convertor): Llama layout plus a sliding attention window shorter than the
+    test sequence."""
+    hc = transformers.MistralConfig(vocab_size=320, hidden_size=64, intermediate_size=112, num_hidden_layers=2,
+                                    num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=128,
+                                    rms_norm_eps=1e-5, rope_theta=10000.0, sliding_window=8, tie_word_embeddings=False)
+    hc._attn_implementation = "eager"
+    torch.manual_seed(0)
+    hf = transformers.MistralForCausalLM(hc)
+    cfg = ModelConfig(base_model="mixtral", num_layers=2, hidden_size=64, num_attention_heads=4, num_query_groups=2,
+                      ffn_hidden_size=112, vocab_size=320, norm_eps=1e-5, rotary_base=10000.0, sliding_window=8,
+                      max_position_embeddings=128)
+    _check(cfg, hf, 320)
