@@ -202,6 +202,22 @@ class BlendedDataset(torch.utils.data.Dataset):
     def __getitem__(self, i):
         return self.datasets[self.ds_index[i]][int(self.ds_sample[i])]
 
+    def __getitems__(self, indices):
+        """Batched fetch: the indices are grouped by component dataset and every component that has a batched fetch of
+        its own (the native gather of ``GPTDataset``) is asked once."""
+        idx = np.asarray(indices, dtype=np.int64) % len(self.ds_index)
+        out = [None] * len(idx)
+        which = self.ds_index[idx]
+        for d in np.unique(which):
+            pos = np.nonzero(which == d)[0]
+            ds = self.datasets[int(d)]
+            local = [int(self.ds_sample[idx[p]]) % len(ds) for p in pos]
+            batched = getattr(ds, "__getitems__", None)
+            rows = batched(local) if batched is not None else [ds[j] for j in local]
+            for p, r in zip(pos, rows):
+                out[int(p)] = r
+        return out
+
 
 class RawJsonDataset(torch.utils.data.Dataset):
     """json / jsonl samples with ``instruction``/``input``/``output`` (SFT) or ``text``/``content`` (pretrain).

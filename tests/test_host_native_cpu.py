@@ -117,3 +117,18 @@ def test_host_helpers_under_asan_ubsan(tmp_path):
     env["PYTHONPATH"] = root + os.pathsep + env.get("PYTHONPATH", "")
     r = subprocess.run([sys.executable, "-c", _CHILD, str(tmp_path)], env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "SANITIZED_OK" in r.stdout, (r.stdout[-2000:], r.stderr[-4000:])
+
+
+def test_blended_dataset_batched_fetch(tmp_path):
+    a = D.GPTDataset(D.IndexedDataset(_corpus(tmp_path, np.uint16, seed=1)), seq_length=16, num_samples=60, seed=3)
+    b = D.GPTDataset(D.IndexedDataset(_corpus(tmp_path, np.int32, seed=2)), seq_length=16, num_samples=60, seed=4)
+    blend = D.BlendedDataset([a, b], [0.7, 0.3], 50)
+    idx = [0, 7, 3, 49, 12, 12, 51]
+    got = blend.__getitems__(idx)
+    for i, g in zip(idx, got):
+        assert torch.equal(g["text"], blend[i % 50]["text"])
+    from linear_moe_b200.dist.mesh import single_process_mesh
+    it = D.BatchIterator(blend, 4, single_process_mesh(), torch.device("cpu"))
+    first = next(it)
+    assert first["tokens"].shape == (4, 16)
+    assert torch.equal(first["tokens"], torch.stack([blend[i]["text"][:-1] for i in range(4)]))
