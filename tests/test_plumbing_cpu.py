@@ -505,3 +505,30 @@ def test_fp16_dynamic_loss_scale_skips_and_recovers():
     assert scales == want, (scales, want)
     assert 0 in skipped and any(b > a for a, b in zip(scales, scales[1:])), "the scale never recovered"
     assert opt.skipped_iters == sum(skipped) and tr.iteration == 30
+
+
+@pytest.mark.parametrize("kw", [
+    dict(recompute_granularity="full", recompute_method="uniform", recompute_num_layers=1),
+    dict(recompute_granularity="full", recompute_method="block", recompute_num_layers=1),
+    dict(recompute_granularity="selective"),
+    dict(moe_layer_recompute=True),
+], ids=["full_uniform", "full_block", "selective", "moe_layer"])
+def test_activation_recompute_keeps_loss_and_gradients(kw):
+    """Every activation-recompute mode (hybrid_transformer_block.py:262-300, --moe-layer-recompute) is a memory trade
+    only: same loss, same gradient for every parameter, with the router's jitter and auxiliary losses in play."""
+    from linear_moe_b200.models.transformer import CausalLM
+    base = dict(la_module="gla", la_feature_map=None, layer_type_list="LN", moe_aux_loss_coeff=0.01, moe_z_loss_coeff=1e-3)
+
+    def run(extra):
+        torch.manual_seed(0)
+        m = CausalLM(get_preset("bench-cpu-plumbing", **base, **extra)).train()
+        ids = torch.randint(0, 512, (2, 48), generator=torch.Generator().manual_seed(1))
+        loss = m(ids, torch.roll(ids, -1, 1)).mean()
+        loss.backward()
+        return loss.item(), {n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None}
+
+    l0, g0 = run({})
+    l1, g1 = run(kw)
+    assert abs(l0 - l1) < 1e-6 and set(g0) == set(g1)
+    for n in g0:
+        assert torch.allclose(g0[n], g1[n], rtol=1e-4, atol=1e-6), n
