@@ -98,6 +98,8 @@ class AuxLossTracker:
 
     @classmethod
     def save(cls, name: str, loss: torch.Tensor, layer_number: int, num_layers: int):
+        if torch._C._current_graph_task_id() != -1:
+            return      # a forward pass replayed inside backward (activation recompute): already recorded once
         if name not in cls.values:
             cls.values[name] = torch.zeros(num_layers, device=loss.device)
         if cls.values[name].device != loss.device or cls.values[name].numel() != num_layers:

@@ -519,16 +519,21 @@ def test_activation_recompute_keeps_loss_and_gradients(kw):
     from linear_moe_b200.models.transformer import CausalLM
     base = dict(la_module="gla", la_feature_map=None, layer_type_list="LN", moe_aux_loss_coeff=0.01, moe_z_loss_coeff=1e-3)
 
+    from linear_moe_b200.models.moe import AuxLossTracker
+
     def run(extra):
         torch.manual_seed(0)
+        AuxLossTracker.values = {}
         m = CausalLM(get_preset("bench-cpu-plumbing", **base, **extra)).train()
         ids = torch.randint(0, 512, (2, 48), generator=torch.Generator().manual_seed(1))
         loss = m(ids, torch.roll(ids, -1, 1)).mean()
         loss.backward()
-        return loss.item(), {n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None}
+        logged = {k: v.tolist() for k, v in AuxLossTracker.pop().items()}
+        return loss.item(), {n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None}, logged
 
-    l0, g0 = run({})
-    l1, g1 = run(kw)
+    l0, g0, a0 = run({})
+    l1, g1, a1 = run(kw)
     assert abs(l0 - l1) < 1e-6 and set(g0) == set(g1)
+    assert a0 == a1 and a0["load_balancing_loss"][0] > 0, "the replayed forward pass must not be logged twice"
     for n in g0:
         assert torch.allclose(g0[n], g1[n], rtol=1e-4, atol=1e-6), n
