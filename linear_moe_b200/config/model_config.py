@@ -152,6 +152,9 @@ class ModelConfig:
             raise ValueError(f"unknown base model {self.base_model!r}")
         if self.la_module is not None and self.la_module not in LA_MODULES:
             raise ValueError(f"unknown --la-module {self.la_module!r}")
+        if self.attention_dropout and self.attention_dropout > 0.0:
+            raise ValueError("--attention-dropout > 0 is not available: the attention kernels never materialise the "
+                             "probabilities it would act on (the reference's launchers train with 0.0); use --hidden-dropout")
         if self.moe_router_order is None:
             # Qwen2/DeepSeek: softmax then top-k (qwen2/moe/router.py:70-71);
             # Mixtral/Llama3: top-k then softmax (mixtral/moe/router.py:159-160).

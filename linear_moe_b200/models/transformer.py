@@ -22,6 +22,7 @@ from typing import Dict, List, Optional
 
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 import torch.utils.checkpoint as ckpt
 
 from .. import ops
@@ -111,14 +112,21 @@ class Block(nn.Module):
         if mixer is not None:
             h, residual = self._mixer_norm().add_norm(x, residual)
             kw = {"lower_bound": lower_bound} if lower_bound is not None else {}
-            x = mixer(h, cache=cache, position_offset=position_offset, **kw)
+            x = self._drop(mixer(h, cache=cache, position_offset=position_offset, **kw))
         if self.spec.ffn is not None:
             h, residual = self.pre_mlp_layernorm.add_norm(x, residual)
             if self.cfg.moe_layer_recompute and self.spec.ffn == "moe" and self.training:
                 x = ckpt.checkpoint(self.mlp, h, use_reentrant=False)
             else:
                 x = self.mlp(h)
+            x = self._drop(x)
         return x, residual
+
+    def _drop(self, x):
+        """``--hidden-dropout``: on every sub-layer's output before it joins the residual stream (Megatron's
+        bias-dropout-add; the add itself is fused into the next norm)."""
+        p = self.cfg.hidden_dropout
+        return F.dropout(x, p, True) if (p > 0.0 and self.training) else x
 
 
 class CausalLM(nn.Module):

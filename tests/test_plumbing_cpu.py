@@ -537,3 +537,33 @@ def test_activation_recompute_keeps_loss_and_gradients(kw):
     assert a0 == a1 and a0["load_balancing_loss"][0] > 0, "the replayed forward pass must not be logged twice"
     for n in g0:
         assert torch.allclose(g0[n], g1[n], rtol=1e-4, atol=1e-6), n
+
+
+def test_hidden_dropout_acts_in_training_only_and_attention_dropout_is_refused():
+    from linear_moe_b200.config.model_config import ModelConfig
+    from linear_moe_b200.models.transformer import CausalLM
+    kw = dict(num_layers=2, hidden_size=64, num_attention_heads=4, ffn_hidden_size=128, vocab_size=256)
+    ids = torch.randint(0, 256, (2, 32), generator=torch.Generator().manual_seed(0))
+    plain, drop = CausalLM(ModelConfig(**kw)), CausalLM(ModelConfig(hidden_dropout=0.2, **kw))
+    drop.load_state_dict(plain.state_dict())
+    with torch.no_grad():
+        assert torch.equal(plain.eval()(ids), drop.eval()(ids))                  # evaluation: no dropout
+        torch.manual_seed(1)
+        a = drop.train()(ids)
+        torch.manual_seed(1)
+        b = drop(ids)
+        torch.manual_seed(2)
+        c = drop(ids)
+    assert torch.equal(a, b) and not torch.equal(a, c) and not torch.allclose(a, plain.train()(ids), atol=1e-3)
+    # full recompute replays the same masks: gradients equal those without recompute
+    re = CausalLM(ModelConfig(hidden_dropout=0.2, recompute_granularity="full", recompute_method="uniform", **kw)).train()
+    re.load_state_dict(plain.state_dict())
+    grads = []
+    for m in (drop.train(), re):
+        m.zero_grad()
+        torch.manual_seed(3)
+        m(ids, torch.roll(ids, -1, 1)).mean().backward()
+        grads.append([p.grad.clone() for p in m.parameters()])
+    assert all(torch.allclose(x, y, rtol=1e-4, atol=1e-7) for x, y in zip(*grads))
+    with pytest.raises(ValueError, match="attention-dropout"):
+        ModelConfig(attention_dropout=0.1, **kw)
