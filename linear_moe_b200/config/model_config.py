@@ -152,6 +152,10 @@ class ModelConfig:
             raise ValueError(f"unknown base model {self.base_model!r}")
         if self.la_module is not None and self.la_module not in LA_MODULES:
             raise ValueError(f"unknown --la-module {self.la_module!r}")
+        if (self.enable_shared_expert and self.shared_moe_ffn_hidden_size is None and self.num_shared_experts
+                and self.moe_ffn_hidden_size):
+            # DeepSeek-V2 counts shared experts: their fused width is the count times the routed experts' width
+            self.shared_moe_ffn_hidden_size = self.num_shared_experts * self.moe_ffn_hidden_size
         if self.attention_dropout and self.attention_dropout > 0.0:
             raise ValueError("--attention-dropout > 0 is not available: the attention kernels never materialise the "
                              "probabilities it would act on (the reference's launchers train with 0.0); use --hidden-dropout")
@@ -269,6 +273,7 @@ class TrainConfig:
     barrier_with_L1_time: bool = True
     exit_interval: Optional[int] = None
     exit_duration_in_mins: Optional[float] = None
+    eod_token: Optional[int] = None               # the tokenizer's end-of-document id, for --eod-mask-loss
     moe_per_layer_logging: bool = False           # the auxiliary losses of every MoE layer in the log line and TensorBoard
     rampup_batch_size: Optional[Tuple[int, int, int]] = None     # --rampup-batch-size start increment ramp-up-samples
     override_opt_param_scheduler: bool = False

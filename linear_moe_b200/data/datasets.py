@@ -17,7 +17,9 @@ from __future__ import annotations
 
 import json
 import os
+import queue
 import struct
+import threading
 from typing import Dict, Iterator, List, Optional, Sequence
 
 import numpy as np
@@ -306,19 +308,32 @@ class BatchIterator:
     same global batch as a single process that reads W micro-batches."""
 
     def __init__(self, dataset, micro_batch_size: int, mesh: Mesh, device, *, consumed_samples: int = 0,
-                 eod_token=None, eod_mask_loss=False, pad_token=None, pin: bool = True):
+                 eod_token=None, eod_mask_loss=False, pad_token=None, pin: bool = True, prefetch: int = 0):
+        """``prefetch`` (``--num-workers``) > 0: a host thread reads, assembles and pins up to ``2 * prefetch``
+        micro-batches ahead of the training loop; the order of the batches is the same as without it."""
         self.ds, self.mbs, self.mesh, self.device = dataset, micro_batch_size, mesh, device
-        self.consumed = consumed_samples
+        self._consumed = consumed_samples
         self.kw = dict(eod_token=eod_token, eod_mask_loss=eod_mask_loss, pad_token=pad_token)
         self.pin = pin and torch.cuda.is_available()
+        self.prefetch = max(int(prefetch or 0), 0)
+        self._queue, self._thread, self._stop, self._ahead = None, None, None, consumed_samples
+
+    # position in the global sample stream; assigning it (a resume) discards what was read ahead
+    @property
+    def consumed(self) -> int:
+        return self._consumed
+
+    @consumed.setter
+    def consumed(self, value: int):
+        self._shutdown()
+        self._consumed = self._ahead = int(value)
 
     def __iter__(self):
         return self
 
-    def __next__(self):
+    def _host_batch(self, start: int):
         mesh = self.mesh
-        base = self.consumed + mesh.dp_rank * self.mbs
-        self.consumed += self.mbs * mesh.dp
+        base = start + mesh.dp_rank * self.mbs
         idx = [(base + i) % len(self.ds) for i in range(self.mbs)]
         batched = getattr(self.ds, "__getitems__", None)        # one native call for the whole micro-batch where there is one
         rows = batched(idx) if batched is not None else [self.ds[j] for j in idx]
@@ -327,4 +342,50 @@ class BatchIterator:
         batch = slice_for_context_parallel(batch, mesh)
         if self.pin:
             batch = {k: v.contiguous().pin_memory() for k, v in batch.items()}
+        return batch
+
+    def _worker(self, q, stop):
+        step = self.mbs * self.mesh.dp
+        if self.pin and getattr(self.device, "type", None) == "cuda":
+            torch.cuda.set_device(self.device)             # pinning allocates through this thread's current device
+        try:
+            while not stop.is_set():
+                item = (self._ahead, self._host_batch(self._ahead))
+                self._ahead += step
+                while not stop.is_set():
+                    try:
+                        q.put(item, timeout=0.1)
+                        break
+                    except queue.Full:
+                        continue
+        except BaseException as e:                         # hand the error to the training thread
+            q.put((None, e))
+
+    def _shutdown(self):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join(timeout=10.0)
+        self._queue, self._thread, self._stop = None, None, None
+
+    def __next__(self):
+        step = self.mbs * self.mesh.dp
+        if self.prefetch == 0:
+            batch = self._host_batch(self._consumed)
+        else:
+            if self._thread is None:
+                self._queue, self._stop, self._ahead = queue.Queue(maxsize=2 * self.prefetch), threading.Event(), self._consumed
+                self._thread = threading.Thread(target=self._worker, args=(self._queue, self._stop), daemon=True)
+                self._thread.start()
+            start, batch = self._queue.get()
+            if start is None:
+                self._shutdown()
+                raise batch
+            assert start == self._consumed, (start, self._consumed)
+        self._consumed += step
         return {k: v.to(self.device, non_blocking=True) for k, v in batch.items()}
+
+    def __del__(self):
+        try:
+            self._shutdown()
+        except Exception:
+            pass

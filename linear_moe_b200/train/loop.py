@@ -122,7 +122,8 @@ class Trainer:
         if dataset is None:
             dataset = SyntheticTokenDataset(cfg.vocab_size, tc.seq_length, seed=tc.seed)
         self.dataset, self.valid_dataset = dataset, valid_dataset
-        self.data_iter = BatchIterator(dataset, tc.micro_batch_size, self.mesh, self.device)
+        self.data_iter = BatchIterator(dataset, tc.micro_batch_size, self.mesh, self.device, eod_token=tc.eod_token,
+                                       eod_mask_loss=tc.eod_mask_loss, prefetch=tc.num_workers)
         self.writer = None
         if tc.tensorboard_dir and self.mesh.rank == self.mesh.world_size - 1:
             try:
@@ -253,6 +254,15 @@ class Trainer:
             torch.cuda.empty_cache()
         if ok:
             self.scheduler.step(1)
+        if self.cfg.test_mode:
+            # --test-mode (attention.py:400-467, run every step there): replicated q / k norm weights must still agree
+            # across the data- and tensor-parallel ranks
+            for m in self.models:
+                for mod in m.modules():
+                    check = getattr(mod, "run_realtime_tests", None)
+                    if check is not None and not check():
+                        raise RuntimeError(f"--test-mode: replicated weights of {type(mod).__name__} differ between ranks "
+                                           f"at iteration {self.iteration + 1}")
         self.iteration += 1
         self.consumed_samples += self.global_batch_now
         out = {"lr": lr, "grad_norm": grad_norm, "skipped": 0 if ok else 1}
@@ -273,6 +283,13 @@ class Trainer:
             self._log_acc[k] = self._log_acc.get(k, 0.0) + float(v)
         self._log_n += 1
         self._log_acc["skipped"] = self._log_acc.get("skipped", 0.0) + stats.get("skipped", 0)
+        if (self.writer is not None and tc.tensorboard_log_interval and self.iteration % tc.tensorboard_log_interval == 0
+                and self.iteration % tc.log_interval != 0):
+            # --tensorboard-log-interval: this step's values between two console lines (the console line writes averages)
+            self.writer.add_scalar("learning-rate", stats["lr"], self.iteration)
+            for k, v in stats.items():
+                if k not in ("lr", "skipped") and v is not None:
+                    self.writer.add_scalar("grad-norm" if k == "grad_norm" else k, float(v), self.iteration)
         if self.iteration % tc.log_interval != 0:
             return
         per_iter = elapsed_s / max(self._log_n, 1)
@@ -310,9 +327,13 @@ class Trainer:
         if mesh.rank == mesh.world_size - 1 or mesh.world_size == 1:
             print(line, flush=True)
         if tc.timing_log_level >= 0:
-            s = self.timers.log_string(normalizer=max(self._log_n, 1))
-            if s:
-                print_rank_0("    timers (ms/iter): " + s)
+            tv = self.timers.collect()
+            if tv:
+                n = max(self._log_n, 1)
+                print_rank_0("    timers (ms/iter): " + " | ".join(f"{k}: {v * 1000.0 / n:.2f}" for k, v in tv.items()))
+                if tc.log_timers_to_tensorboard and self.writer is not None:
+                    for k, v in tv.items():
+                        self.writer.add_scalar(k + "-time", v / n, self.iteration)
         if self.writer is not None:
             it = self.iteration
             self.writer.add_scalar("learning-rate", stats["lr"], it)
@@ -506,6 +527,11 @@ def pretrain(argv=None, dataset_provider: Optional[Callable] = None, model_provi
     print_rank_0(f"> mesh: {mesh.describe()}")
     mem = compute_weight_and_optimizer_memory(cfg, par, verbose=mesh.rank == 0)
     train_ds, valid_ds = (dataset_provider or build_datasets)(args, cfg, tc)
+    if tc.eod_mask_loss and tc.eod_token is None:
+        # --eod-mask-loss: no loss on the token that follows an end-of-document token; the id comes from the tokenizer
+        from ..data.tokenizer import build_tokenizer
+        tok, _ = build_tokenizer(args.patch_tokenizer_type, args.tokenizer_model, cfg.vocab_size, args.extra_vocab_size)
+        tc.eod_token = getattr(tok, "eod", None)
     trainer = Trainer(cfg, par, tc, mesh, dataset=train_ds, valid_dataset=valid_ds, model_provider=model_provider,
                       forward_step=forward_step)
     print_rank_0(f"> parameters on this rank: {count_parameters(trainer.models):,}")

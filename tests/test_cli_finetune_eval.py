@@ -362,3 +362,46 @@ def test_megatron_moe_flag_spellings(capsys):
     Trainer(cfg, ParallelConfig(), tc, device=torch.device("cpu")).train()
     out = capsys.readouterr().out
     assert "moe/load_balancing_loss_layer_0:" in out and "moe/load_balancing_loss_layer_1:" in out
+
+
+def test_logging_and_loader_flags_have_readers(tmp_path, monkeypatch):
+    """--tensorboard-log-interval, --log-timers-to-tensorboard, --num-workers, --test-mode and --num-shared-experts all
+    change behaviour (none is accepted and ignored)."""
+    from linear_moe_b200.config.arguments import parse_args
+    from linear_moe_b200.config.model_config import ParallelConfig
+    from linear_moe_b200.train import loop as L
+    written = []
+
+    class Writer:
+        def __init__(self, *a, **k):
+            pass
+
+        def add_scalar(self, name, value, step):
+            written.append((name, step))
+
+        def flush(self):
+            pass
+
+        def close(self):
+            pass
+    import torch.utils.tensorboard as tb
+    monkeypatch.setattr(tb, "SummaryWriter", Writer)
+    base = ["--num-layers", "2", "--hidden-size", "32", "--num-attention-heads", "2", "--ffn-hidden-size", "64",
+            "--vocab-size", "64", "--seq-length", "16", "--micro-batch-size", "2", "--train-iters", "6", "--lr", "1e-3",
+            "--qk-layernorm", "--test-mode", "--num-workers", "2", "--log-interval", "4", "--tensorboard-dir", str(tmp_path),
+            "--tensorboard-log-interval", "2", "--log-timers-to-tensorboard", "--timing-log-level", "1"]
+    _, cfg, par, tc = parse_args(base)
+    assert cfg.test_mode and tc.num_workers == 2 and tc.tensorboard_log_interval == 2
+    tr = L.Trainer(cfg, ParallelConfig(), tc, device=torch.device("cpu"))
+    assert tr.data_iter.prefetch == 2
+    tr.train()
+    steps = sorted({s for n, s in written if n == "learning-rate"})
+    assert steps == [2, 4, 6], steps                           # every 2nd step, the console step 4 included once
+    assert any(n.endswith("-time") for n, _ in written)
+    # --test-mode notices replicated weights that drifted apart (here: a check that is made to fail)
+    monkeypatch.setattr(type(tr.models[0].decoder.layers[0].self_attention), "run_realtime_tests", lambda self: False)
+    with pytest.raises(RuntimeError, match="test-mode"):
+        tr.train_step()
+    _, ds, _, _ = parse_args(["--num-layers", "1", "--hidden-size", "32", "--num-attention-heads", "2", "--num-experts", "4",
+                              "--moe-ffn-hidden-size", "24", "--enable-shared-expert", "--num-shared-experts", "2"])
+    assert ds.shared_moe_ffn_hidden_size == 48

@@ -132,3 +132,35 @@ def test_blended_dataset_batched_fetch(tmp_path):
     first = next(it)
     assert first["tokens"].shape == (4, 16)
     assert torch.equal(first["tokens"], torch.stack([blend[i]["text"][:-1] for i in range(4)]))
+
+
+def test_prefetching_iterator_keeps_the_order_and_masks_after_eod(tmp_path):
+    """--num-workers: the read-ahead thread delivers the same micro-batches in the same order, a resume position discards
+    what was read ahead; --eod-mask-loss removes the loss where the input token is the end-of-document id."""
+    from linear_moe_b200.dist.mesh import single_process_mesh
+    ds = D.GPTDataset(D.IndexedDataset(_corpus(tmp_path, np.uint16, seed=5)), seq_length=16, num_samples=80, seed=9)
+    mesh, dev = single_process_mesh(), torch.device("cpu")
+    plain = D.BatchIterator(ds, 3, mesh, dev)
+    ahead = D.BatchIterator(ds, 3, mesh, dev, prefetch=2)
+    for _ in range(7):
+        a, b = next(plain), next(ahead)
+        assert all(torch.equal(a[k], b[k]) for k in a)
+    assert ahead.consumed == plain.consumed == 21
+    ahead.consumed = plain.consumed = 6                       # resume elsewhere
+    a, b = next(plain), next(ahead)
+    assert torch.equal(a["tokens"], b["tokens"]) and torch.equal(a["tokens"][0], ds[6]["text"][:-1])
+    ahead._shutdown()
+    eod = int(a["tokens"][0, 3])
+    masked = next(D.BatchIterator(ds, 3, mesh, dev, consumed_samples=6, eod_token=eod, eod_mask_loss=True))
+    assert torch.equal(masked["tokens"], a["tokens"])
+    assert bool((masked["loss_mask"][a["tokens"] == eod] == 0).all()) and masked["loss_mask"][0, 3] == 0
+    assert bool((masked["loss_mask"][a["tokens"] != eod] == 1).all())
+
+    class Broken(torch.utils.data.Dataset):
+        def __len__(self):
+            return 4
+
+        def __getitem__(self, i):
+            raise OSError("disk gone")
+    with pytest.raises(OSError, match="disk gone"):
+        next(D.BatchIterator(Broken(), 2, mesh, dev, prefetch=1))
