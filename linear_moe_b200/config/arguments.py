@@ -14,6 +14,7 @@ and recorded but select nothing: there is one code path.
 from __future__ import annotations
 
 import argparse
+import os
 from typing import Optional, Sequence, Tuple
 
 import torch
@@ -510,7 +511,7 @@ def configs_from_args(args: argparse.Namespace) -> Tuple[ModelConfig, ParallelCo
         no_load_optim=args.no_load_optim, no_load_rng=args.no_load_rng, no_save_optim=args.no_save_optim,
         no_save_rng=args.no_save_rng, async_save=args.async_save, use_dist_ckpt=args.use_dist_ckpt,
         auto_detect_ckpt_format=args.auto_detect_ckpt_format, tensorboard_dir=args.tensorboard_dir,
-        tensorboard_log_interval=args.tensorboard_log_interval,
+        tensorboard_log_interval=args.tensorboard_log_interval, tensorboard_queue_size=args.tensorboard_queue_size,
         log_timers_to_tensorboard=args.log_timers_to_tensorboard,
         log_memory_to_tensorboard=args.log_memory_to_tensorboard,
         log_validation_ppl_to_tensorboard=args.log_validation_ppl_to_tensorboard,
@@ -540,8 +541,38 @@ def configs_from_args(args: argparse.Namespace) -> Tuple[ModelConfig, ParallelCo
     return model, par, train
 
 
+# Flags of the reference's launchers that select something this framework has one form of (a fused kernel that is always
+# used, a Megatron code path that does not exist here) or that the reference itself never reads (its multimodal and
+# vestigial model switches).  They parse, and a run that sets one says so once instead of silently ignoring it.
+NO_EFFECT = frozenset("""
+use_rotary_position_embeddings apply_query_key_layer_scaling transformer_type transformer_impl use_mcore_models
+use_flash_attn no_rope_fusion no_bias_swiglu_fusion no_masked_softmax_fusion no_create_attention_mask_in_dataloader
+disable_parallel_output attention_head_type use_alibi_mask use_normhead embed_layernorm position_encoding_2d
+use_llama2_rotary_position_embeddings use_mistral_rotary_position_embeddings use_cache mix_type a_pooling a_num
+moe_grouped_gemm moe_megablocks moe use_tutel router_type moe_input_feature_slicing expert_tensor_parallelism
+fp8_amax_history_len fp8_amax_compute_algo train_mode max_tokens_to_oom log_batch_size_to_tensorboard transformer_timers
+dist_ckpt_format use_checkpoint_args tokenizer_type source_seq_len target_seq_len generation_length text_generate_gt_file
+time input_len eval_dev eval_fp32 adaptive_seq_len mm_use_im_start_end mm_use_im_patch_token tune_mm_mlp_adapter
+freeze_clip_vision_tower freeze_llm cvcuda_image_processing image_folder vision_tower image_aspect_ratio version
+mm_projector_type mm_vision_select_layer image_size patch_size la_checkpointing moe_pad_expert_input_to_capacity
+""".split())
+
+
+def flags_without_effect(parser: argparse.ArgumentParser, args: argparse.Namespace):
+    """Option strings of the ``NO_EFFECT`` flags that the command line set to something other than their default."""
+    out = []
+    for a in parser._actions:
+        if a.dest in NO_EFFECT and a.option_strings and getattr(args, a.dest, a.default) != a.default:
+            out.append(a.option_strings[0])
+    return sorted(out)
+
+
 def parse_args(argv: Optional[Sequence[str]] = None):
     """Parse ``argv`` → ``(namespace, ModelConfig, ParallelConfig, TrainConfig)``."""
-    args = build_parser().parse_args(argv)
+    parser = build_parser()
+    args = parser.parse_args(argv)
+    ignored = flags_without_effect(parser, args)
+    if ignored and int(os.environ.get("RANK", "0")) == 0:
+        print("> accepted for launcher compatibility, without effect here: " + " ".join(ignored), flush=True)
     model, par, train = configs_from_args(args)
     return args, model, par, train

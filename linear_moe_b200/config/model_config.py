@@ -266,6 +266,7 @@ class TrainConfig:
     auto_detect_ckpt_format: bool = False         # on load, take whichever format the directory holds
     tensorboard_dir: Optional[str] = None
     tensorboard_log_interval: int = 10
+    tensorboard_queue_size: int = 1000
     log_timers_to_tensorboard: bool = False
     log_memory_to_tensorboard: bool = False
     log_validation_ppl_to_tensorboard: bool = False

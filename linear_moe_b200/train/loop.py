@@ -128,7 +128,7 @@ class Trainer:
         if tc.tensorboard_dir and self.mesh.rank == self.mesh.world_size - 1:
             try:
                 from torch.utils.tensorboard import SummaryWriter
-                self.writer = SummaryWriter(tc.tensorboard_dir, max_queue=1000)
+                self.writer = SummaryWriter(tc.tensorboard_dir, max_queue=tc.tensorboard_queue_size)
             except Exception as e:                      # tensorboard is optional
                 print_rank_0(f"tensorboard disabled: {e}")
         self._exit_signal = False

@@ -405,3 +405,16 @@ def test_logging_and_loader_flags_have_readers(tmp_path, monkeypatch):
     _, ds, _, _ = parse_args(["--num-layers", "1", "--hidden-size", "32", "--num-attention-heads", "2", "--num-experts", "4",
                               "--moe-ffn-hidden-size", "24", "--enable-shared-expert", "--num-shared-experts", "2"])
     assert ds.shared_moe_ffn_hidden_size == 48
+
+
+def test_compatibility_only_flags_are_named_once(capsys):
+    from linear_moe_b200.config.arguments import NO_EFFECT, build_parser, parse_args
+    base = ["--num-layers", "1", "--hidden-size", "32", "--num-attention-heads", "2"]
+    parse_args(base)
+    assert "without effect" not in capsys.readouterr().out
+    parse_args(base + ["--use-flash-attn", "--transformer-impl", "transformer_engine", "--vision-tower", "clip"])
+    out = capsys.readouterr().out
+    assert out.count("without effect here") == 1
+    assert all(f in out for f in ("--use-flash-attn", "--transformer-impl", "--vision-tower"))
+    dests = {a.dest for a in build_parser()._actions}
+    assert NO_EFFECT <= dests, sorted(NO_EFFECT - dests)
