@@ -58,6 +58,21 @@ def read_tracker(root: str) -> Tuple[Optional[int], bool]:
     return int(s), False
 
 
+def read_checkpoint_args(root: str) -> Optional[Namespace]:
+    """The ``args`` namespace stored in the latest checkpoint under ``root`` (``--use-checkpoint-args``), read from the
+    first model-parallel file; None when there is no checkpoint."""
+    import glob
+    it, release = read_tracker(root)
+    if it is None:
+        return None
+    directory = os.path.join(root, "release" if release else f"iter_{int(it):07d}")
+    files = sorted(glob.glob(os.path.join(directory, "mp_rank_*", "model_optim_rng.pt")))
+    if not files:
+        return None
+    ck = torch.load(files[0], map_location="cpu", weights_only=False)
+    return ck.get("args")
+
+
 # ---- expert key translation ------------------------------------------------
 def to_reference_keys(sd: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
     """``...experts.weight1 [E,h,2f]`` / ``weight2 [E,f,h]`` -> per-expert ``linear_fc1 [2f,h]`` /

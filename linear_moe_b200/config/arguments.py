@@ -551,7 +551,7 @@ disable_parallel_output attention_head_type use_alibi_mask use_normhead embed_la
 use_llama2_rotary_position_embeddings use_mistral_rotary_position_embeddings use_cache mix_type a_pooling a_num
 moe_grouped_gemm moe_megablocks moe use_tutel router_type moe_input_feature_slicing expert_tensor_parallelism
 fp8_amax_history_len fp8_amax_compute_algo train_mode max_tokens_to_oom log_batch_size_to_tensorboard transformer_timers
-dist_ckpt_format use_checkpoint_args tokenizer_type source_seq_len target_seq_len generation_length text_generate_gt_file
+dist_ckpt_format tokenizer_type source_seq_len target_seq_len generation_length text_generate_gt_file
 time input_len eval_dev eval_fp32 adaptive_seq_len mm_use_im_start_end mm_use_im_patch_token tune_mm_mlp_adapter
 freeze_clip_vision_tower freeze_llm cvcuda_image_processing image_folder vision_tower image_aspect_ratio version
 mm_projector_type mm_vision_select_layer image_size patch_size la_checkpointing moe_pad_expert_input_to_capacity
@@ -567,6 +567,33 @@ def flags_without_effect(parser: argparse.ArgumentParser, args: argparse.Namespa
     return sorted(out)
 
 
+# what --use-checkpoint-args does NOT take from the checkpoint: how the model is run, not what it is
+_RUNTIME_FIELDS = frozenset("""params_dtype recompute_granularity recompute_method recompute_num_layers moe_layer_recompute
+cpu_offloading cpu_offloading_num_layers cross_entropy_chunk test_mode fp8 la_mode hidden_dropout attention_dropout
+moe_token_dispatcher_type""".split())
+
+
+def apply_checkpoint_args(model: ModelConfig, load: str) -> ModelConfig:
+    """``--use-checkpoint-args``: the architecture (every model field a checkpoint stores, except the run-time switches)
+    comes from the checkpoint under ``load`` instead of the command line."""
+    import dataclasses
+    from ..ckpt.legacy import read_checkpoint_args
+    stored = read_checkpoint_args(load)
+    if stored is None:
+        return model
+    take = {}
+    for f in dataclasses.fields(ModelConfig):
+        if f.name in _RUNTIME_FIELDS or not hasattr(stored, f.name):
+            continue
+        v = getattr(stored, f.name)
+        if v != getattr(model, f.name):
+            take[f.name] = v
+    if take and int(os.environ.get("RANK", "0")) == 0:
+        print("> --use-checkpoint-args: from the checkpoint: " + ", ".join(f"{k}={v}" for k, v in sorted(take.items())),
+              flush=True)
+    return model.replace(**take) if take else model
+
+
 def parse_args(argv: Optional[Sequence[str]] = None):
     """Parse ``argv`` → ``(namespace, ModelConfig, ParallelConfig, TrainConfig)``."""
     parser = build_parser()
@@ -575,4 +602,6 @@ def parse_args(argv: Optional[Sequence[str]] = None):
     if ignored and int(os.environ.get("RANK", "0")) == 0:
         print("> accepted for launcher compatibility, without effect here: " + " ".join(ignored), flush=True)
     model, par, train = configs_from_args(args)
+    if args.use_checkpoint_args and args.load:
+        model = apply_checkpoint_args(model, args.load)
     return args, model, par, train

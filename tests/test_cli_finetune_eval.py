@@ -418,3 +418,31 @@ def test_compatibility_only_flags_are_named_once(capsys):
     assert all(f in out for f in ("--use-flash-attn", "--transformer-impl", "--vision-tower"))
     dests = {a.dest for a in build_parser()._actions}
     assert NO_EFFECT <= dests, sorted(NO_EFFECT - dests)
+
+
+def test_use_checkpoint_args_restores_the_architecture(tmp_path, capsys):
+    from linear_moe_b200.config.arguments import parse_args
+    from linear_moe_b200.config.model_config import ParallelConfig
+    from linear_moe_b200.train.loop import Trainer
+    arch = ["--num-layers", "2", "--hidden-size", "48", "--num-attention-heads", "4", "--ffn-hidden-size", "96",
+            "--vocab-size", "128", "--use-la-module", "--la-module", "retention", "--layer-type-list", "LN",
+            "--group-query-attention", "--num-query-groups", "2"]
+    run = ["--seq-length", "16", "--micro-batch-size", "1", "--train-iters", "1", "--log-interval", "100"]
+    _, cfg, _, tc = parse_args(arch + run + ["--save", str(tmp_path)])
+    tr = Trainer(cfg, ParallelConfig(), tc, device=torch.device("cpu"))
+    tr.train_step()
+    tr.save()
+    # a command line with another architecture, and a run-time switch of its own
+    other = ["--num-layers", "1", "--hidden-size", "32", "--num-attention-heads", "2", "--recompute-granularity", "full",
+             "--recompute-method", "uniform"]
+    _, got, _, tc2 = parse_args(other + run + ["--load", str(tmp_path), "--use-checkpoint-args"])
+    assert "--use-checkpoint-args: from the checkpoint" in capsys.readouterr().out
+    for k in ("num_layers", "hidden_size", "num_attention_heads", "num_query_groups", "ffn_hidden_size", "vocab_size",
+              "la_module", "layer_type_list"):
+        assert getattr(got, k) == getattr(cfg, k), k
+    assert got.recompute_granularity == "full"                       # how it runs stays with the command line
+    again = Trainer(got, ParallelConfig(), tc2, device=torch.device("cpu"))
+    a, b = tr.models[0].state_dict(), again.models[0].state_dict()
+    assert again.iteration == 1 and all(torch.equal(a[k], b[k]) for k in a)
+    _, plain, _, _ = parse_args(other + run + ["--load", str(tmp_path)])
+    assert plain.hidden_size == 32
