@@ -62,8 +62,15 @@ def read_checkpoint_args(root: str) -> Optional[Namespace]:
     """The ``args`` namespace stored in the latest checkpoint under ``root`` (``--use-checkpoint-args``), read from the
     first model-parallel file; None when there is no checkpoint."""
     import glob
+    import json
     it, release = read_tracker(root)
     if it is None:
+        # the sharded format keeps the model fields in its metadata file
+        tracker = os.path.join(root, "latest_sharded_iteration.txt")
+        if os.path.isfile(tracker):
+            meta = os.path.join(root, f"iter_{int(open(tracker).read().strip()):07d}", "metadata.json")
+            stored = json.load(open(meta)).get("extra", {}).get("model_args")
+            return None if stored is None else Namespace(**stored)
         return None
     directory = os.path.join(root, "release" if release else f"iter_{int(it):07d}")
     files = sorted(glob.glob(os.path.join(directory, "mp_rank_*", "model_optim_rng.pt")))

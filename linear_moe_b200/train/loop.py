@@ -387,7 +387,9 @@ class Trainer:
                 save_sharded(path, self.iteration, self.models, self.cfg, self.mesh,
                              None if self.tc.no_save_optim else self.optimizer, layer_offsets=self._layer_offsets(),
                              extra={"consumed_samples": self.consumed_samples,
-                                    "opt_param_scheduler": self.scheduler.state_dict()})
+                                    "opt_param_scheduler": self.scheduler.state_dict(),
+                                    "model_args": {k: (v if not isinstance(v, torch.dtype) else str(v))
+                                                   for k, v in vars(self.cfg).items()}})
                 return
             save_checkpoint(path, self.iteration, self.models, self.optimizer, self.scheduler, self.cfg, self.par,
                             self.tc, self.mesh, consumed_samples=self.consumed_samples)

@@ -446,3 +446,19 @@ def test_use_checkpoint_args_restores_the_architecture(tmp_path, capsys):
     assert again.iteration == 1 and all(torch.equal(a[k], b[k]) for k in a)
     _, plain, _, _ = parse_args(other + run + ["--load", str(tmp_path)])
     assert plain.hidden_size == 32
+
+
+def test_use_checkpoint_args_reads_the_sharded_format_too(tmp_path):
+    from linear_moe_b200.config.arguments import parse_args
+    from linear_moe_b200.config.model_config import ParallelConfig
+    from linear_moe_b200.train.loop import Trainer
+    arch = ["--num-layers", "2", "--hidden-size", "48", "--num-attention-heads", "4", "--ffn-hidden-size", "96", "--vocab-size", "128"]
+    run = ["--seq-length", "16", "--micro-batch-size", "1", "--train-iters", "1", "--log-interval", "100", "--use-dist-ckpt"]
+    _, cfg, _, tc = parse_args(arch + run + ["--save", str(tmp_path)])
+    tr = Trainer(cfg, ParallelConfig(), tc, device=torch.device("cpu"))
+    tr.train_step()
+    tr.save()
+    _, got, _, tc2 = parse_args(["--num-layers", "1", "--hidden-size", "32", "--num-attention-heads", "2"] + run +
+                                ["--load", str(tmp_path), "--use-checkpoint-args"])
+    assert (got.num_layers, got.hidden_size, got.ffn_hidden_size, got.vocab_size) == (2, 48, 96, cfg.vocab_size)
+    assert Trainer(got, ParallelConfig(), tc2, device=torch.device("cpu")).iteration == 1
