@@ -327,6 +327,7 @@ def build_parser() -> argparse.ArgumentParser:
     _flag(g, "--split", type=str, default="99,1,0")
     _flag(g, "--max-padding-length", type=int, default=None)
     _flag(g, "--num-workers", type=int, default=0)
+    _flag(g, "--data-cache-path", type=str, default=None, help="folder for the dataset index arrays (built once, then memory-mapped)")
     _flag(g, "--epochs", type=int, default=None)
     _flag(g, "--keep-last", action="store_true")
     _flag(g, "--eod-mask-loss", action="store_true")

@@ -16,7 +16,7 @@ def _split_documents(n_docs: int, split: str):
     return [np.arange(bounds[i], bounds[i + 1], dtype=np.int64) for i in range(3)]
 
 
-def build_pretrain_dataset_from_idxmap(paths, seq_length, num_samples, seed, split):
+def build_pretrain_dataset_from_idxmap(paths, seq_length, num_samples, seed, split, cache_dir=None):
     """``paths`` is either one prefix or ``w1 prefix1 w2 prefix2 ...`` (Megatron blend syntax)."""
     if len(paths) == 1:
         weights, prefixes = [1.0], list(paths)
@@ -26,9 +26,9 @@ def build_pretrain_dataset_from_idxmap(paths, seq_length, num_samples, seed, spl
     for p in prefixes:
         ds = IndexedDataset(p)
         tr, va, _ = _split_documents(len(ds), split)
-        trains.append(GPTDataset(ds, seq_length, num_samples, seed, tr))
+        trains.append(GPTDataset(ds, seq_length, num_samples, seed, tr, cache_dir=cache_dir))
         if len(va):
-            valids.append(GPTDataset(ds, seq_length, max(num_samples // 100, 1), seed, va))
+            valids.append(GPTDataset(ds, seq_length, max(num_samples // 100, 1), seed, va, cache_dir=cache_dir))
     if len(trains) == 1:
         return trains[0], (valids[0] if valids else None)
     train = BlendedDataset(trains, weights, num_samples)
@@ -42,7 +42,8 @@ def build_datasets(args, cfg, tc):
         return SyntheticTokenDataset(cfg.vocab_size, tc.seq_length, seed=tc.seed), \
             SyntheticTokenDataset(cfg.vocab_size, tc.seq_length, seed=tc.seed + (1 << 24))
     if tc.dataset == "LLama-Pretrain-Idxmap":
-        return build_pretrain_dataset_from_idxmap(tc.data_path, tc.seq_length, n, tc.seed, tc.split)
+        return build_pretrain_dataset_from_idxmap(tc.data_path, tc.seq_length, n, tc.seed, tc.split,
+                                                  cache_dir=getattr(args, "data_cache_path", None))
     tok, _ = build_tokenizer(args.patch_tokenizer_type, args.tokenizer_model, cfg.vocab_size, args.extra_vocab_size)
     L = tc.max_padding_length or tc.seq_length
     sft = tc.dataset == "LLama-SFT"

@@ -69,6 +69,7 @@ class IndexedDataset:
                                      offset=offset + self.sizes.nbytes + self.pointers.nbytes)
         self.data = np.memmap(prefix + ".bin", mode="r", order="C")
         self.dtype_code = code
+        self.prefix = prefix
 
     def __len__(self):
         return len(self.sizes)
@@ -130,19 +131,44 @@ class GPTDataset(torch.utils.data.Dataset):
     """Fixed-length samples drawn across document boundaries of an ``IndexedDataset``."""
 
     def __init__(self, indexed: IndexedDataset, seq_length: int, num_samples: int, seed: int = 1234,
-                 documents: Optional[np.ndarray] = None):
+                 documents: Optional[np.ndarray] = None, cache_dir: Optional[str] = None):
+        """``cache_dir`` (``--data-cache-path``): the three index arrays are stored there under a name derived from
+        everything they depend on and memory-mapped by later runs (and by the other ranks) instead of being rebuilt."""
         self.ds, self.seq = indexed, seq_length
         docs = np.arange(len(indexed), dtype=np.int64) if documents is None else documents
-        tokens_per_epoch = int(np.sum(indexed.sizes[docs]))
-        epochs = max(1, -(-(num_samples * seq_length + 1) // max(tokens_per_epoch, 1)))
-        rng = np.random.RandomState(seed)
-        self.doc_idx = np.concatenate([rng.permutation(docs) for _ in range(epochs)]).astype(np.int64)
-        self.sample_idx = build_sample_idx(np.asarray(indexed.sizes), self.doc_idx, seq_length, epochs, tokens_per_epoch)
-        self.shuffle_idx = rng.permutation(len(self.sample_idx) - 1)
+        cached = self._cache_files(cache_dir, indexed, seq_length, num_samples, seed, docs)
+        if cached is not None and all(os.path.isfile(f) for f in cached):
+            self.doc_idx, self.sample_idx, self.shuffle_idx = (np.load(f, mmap_mode="r") for f in cached)
+            self.doc_idx, self.sample_idx = np.ascontiguousarray(self.doc_idx), np.ascontiguousarray(self.sample_idx)
+        else:
+            tokens_per_epoch = int(np.sum(indexed.sizes[docs]))
+            epochs = max(1, -(-(num_samples * seq_length + 1) // max(tokens_per_epoch, 1)))
+            rng = np.random.RandomState(seed)
+            self.doc_idx = np.concatenate([rng.permutation(docs) for _ in range(epochs)]).astype(np.int64)
+            self.sample_idx = build_sample_idx(np.asarray(indexed.sizes), self.doc_idx, seq_length, epochs, tokens_per_epoch)
+            self.shuffle_idx = rng.permutation(len(self.sample_idx) - 1)
+            if cached is not None and int(os.environ.get("RANK", "0")) == 0:
+                os.makedirs(cache_dir, exist_ok=True)
+                for f, a in zip(cached, (self.doc_idx, self.sample_idx, self.shuffle_idx)):
+                    tmp = f + f".tmp{os.getpid()}.npy"
+                    np.save(tmp, a)
+                    os.replace(tmp, f)                    # a reader never sees a half-written file
         # aligned in-memory copies of the two per-document tables for the native gather (they sit at unaligned offsets
         # of the memory-mapped .idx file)
         self._sizes = np.require(indexed.sizes, dtype=np.int32, requirements=["C", "A"])
         self._pointers = np.require(indexed.pointers, dtype=np.int64, requirements=["C", "A"])
+
+    @staticmethod
+    def _cache_files(cache_dir, indexed, seq_length, num_samples, seed, docs):
+        if not cache_dir:
+            return None
+        import hashlib
+        h = hashlib.sha256()
+        h.update(repr((os.path.abspath(getattr(indexed, "prefix", "")), len(indexed), int(np.sum(indexed.sizes[docs])),
+                       seq_length, num_samples, seed, len(docs), int(docs[0]) if len(docs) else -1,
+                       int(docs[-1]) if len(docs) else -1)).encode())
+        key = h.hexdigest()[:24]
+        return [os.path.join(cache_dir, f"{key}_{part}.npy") for part in ("doc_idx", "sample_idx", "shuffle_idx")]
 
     def __len__(self):
         return len(self.shuffle_idx)

@@ -164,3 +164,17 @@ def test_prefetching_iterator_keeps_the_order_and_masks_after_eod(tmp_path):
             raise OSError("disk gone")
     with pytest.raises(OSError, match="disk gone"):
         next(D.BatchIterator(Broken(), 2, mesh, dev, prefetch=1))
+
+
+def test_index_cache_is_written_once_and_reused(tmp_path, monkeypatch):
+    prefix = _corpus(tmp_path, np.uint16, seed=8)
+    cache = tmp_path / "cache"
+    a = D.GPTDataset(D.IndexedDataset(prefix), seq_length=16, num_samples=70, seed=2, cache_dir=str(cache))
+    files = sorted(os.listdir(cache))
+    assert len(files) == 3 and all(f.endswith(".npy") for f in files)
+    monkeypatch.setattr(D, "build_sample_idx", lambda *a, **k: (_ for _ in ()).throw(AssertionError("rebuilt")))
+    b = D.GPTDataset(D.IndexedDataset(prefix), seq_length=16, num_samples=70, seed=2, cache_dir=str(cache))
+    assert all(torch.equal(a[i]["text"], b[i]["text"]) for i in range(0, len(a), 7))
+    assert torch.equal(a.__getitems__([1, 2, 3])[2]["text"], b.__getitems__([1, 2, 3])[2]["text"])
+    with pytest.raises(AssertionError, match="rebuilt"):          # another seed is another index
+        D.GPTDataset(D.IndexedDataset(prefix), seq_length=16, num_samples=70, seed=3, cache_dir=str(cache))
