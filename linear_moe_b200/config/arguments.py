@@ -218,6 +218,8 @@ def build_parser() -> argparse.ArgumentParser:
     _flag(g, "--lr-decay-samples", type=int, default=None)
     _flag(g, "--lr-warmup-samples", type=int, default=0)
     _flag(g, "--skip-train", action="store_true", help="evaluate only")
+    _flag(g, "--optimizer", type=str, default="adam", choices=["adam", "sgd"])
+    _flag(g, "--sgd-momentum", type=float, default=0.9)
     _flag(g, "--rampup-batch-size", type=int, nargs=3, default=None, metavar=("START", "INCREMENT", "SAMPLES"),
           help="grow the global batch from START by INCREMENT to --global-batch-size over the first SAMPLES samples")
     _flag(g, "--empty-unused-memory-level", type=int, default=0, choices=[0, 1, 2],
@@ -518,7 +520,7 @@ def configs_from_args(args: argparse.Namespace) -> Tuple[ModelConfig, ParallelCo
         log_validation_ppl_to_tensorboard=args.log_validation_ppl_to_tensorboard,
         timing_log_level=args.timing_log_level, barrier_with_L1_time=args.barrier_with_L1_time,
         exit_interval=args.exit_interval, exit_duration_in_mins=args.exit_duration_in_mins,
-        moe_per_layer_logging=args.moe_per_layer_logging,
+        optimizer=args.optimizer, sgd_momentum=args.sgd_momentum, moe_per_layer_logging=args.moe_per_layer_logging,
         rampup_batch_size=tuple(args.rampup_batch_size) if args.rampup_batch_size else None,
         override_opt_param_scheduler=args.override_opt_param_scheduler,
         use_checkpoint_opt_param_scheduler=args.use_checkpoint_opt_param_scheduler,

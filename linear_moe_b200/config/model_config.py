@@ -274,6 +274,8 @@ class TrainConfig:
     barrier_with_L1_time: bool = True
     exit_interval: Optional[int] = None
     exit_duration_in_mins: Optional[float] = None
+    optimizer: str = "adam"                       # adam | sgd
+    sgd_momentum: float = 0.9
     eod_token: Optional[int] = None               # the tokenizer's end-of-document id, for --eod-mask-loss
     moe_per_layer_logging: bool = False           # the auxiliary losses of every MoE layer in the log line and TensorBoard
     rampup_batch_size: Optional[Tuple[int, int, int]] = None     # --rampup-batch-size start increment ramp-up-samples

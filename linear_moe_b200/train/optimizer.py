@@ -158,6 +158,8 @@ class MixedPrecisionAdam:
 
     def _want_fused(self, group: Group, dtype) -> bool:
         """Symmetric-memory buffers + fused NVLS kernels: ZeRO-1 on a multi-GPU NCCL group with bf16 parameters."""
+        if self.tc.optimizer != "adam":
+            return False                         # the fused update kernel is Adam
         if not (self.zero1 and self.fused_comm and not group.is_trivial and dtype == torch.bfloat16):
             return False
         return torch.cuda.is_available() and dist.is_initialized() and dist.get_backend() == "nccl"
@@ -427,6 +429,21 @@ class MixedPrecisionAdam:
             wd = weight_decay if b.weight_decay else 0.0
             g = b.grads[lo:hi]
             pshard = b.params[lo:hi]
+            if tc.optimizer == "sgd":
+                # --optimizer sgd: torch.optim.SGD's rule (L2 weight decay added to the gradient, momentum buffer in the
+                # first-moment slot, no dampening / Nesterov), in eager tensor ops on the flat shard
+                w = b.master if b.master is not None else pshard
+                gg = g.float() * gscale
+                if wd:
+                    gg = gg.add(w.float(), alpha=wd)
+                if tc.sgd_momentum:
+                    gg = b.exp_avg.mul_(tc.sgd_momentum).add_(gg)
+                w.add_(gg.to(w.dtype), alpha=-lr)
+                if b.master is not None:
+                    pshard.copy_(w)
+                if self.zero1 and not b.group.is_trivial:
+                    b.params.copy_(C.all_gather_raw(pshard.clone(), b.group, dim=0))
+                continue
             if b.fused is not None:
                 # Adam on the shard + multicast store of the bf16 parameters to every rank + barrier, one kernel
                 b.fused.adam_broadcast(b.shard, b.master, b.exp_avg, b.exp_avg_sq, lr, b1, b2, eps, wd, bc1, bc2, gscale)

@@ -567,3 +567,32 @@ def test_hidden_dropout_acts_in_training_only_and_attention_dropout_is_refused()
     assert all(torch.allclose(x, y, rtol=1e-4, atol=1e-7) for x, y in zip(*grads))
     with pytest.raises(ValueError, match="attention-dropout"):
         ModelConfig(attention_dropout=0.1, **kw)
+
+
+def test_sgd_matches_torch_sgd():
+    """--optimizer sgd --sgd-momentum 0.9 with weight decay and clipping off: the flat-buffer update equals
+    torch.optim.SGD on the same model and data, step for step."""
+    from linear_moe_b200.config.model_config import ModelConfig
+    from linear_moe_b200.models.transformer import CausalLM
+    cfg = ModelConfig(num_layers=2, hidden_size=32, num_attention_heads=2, ffn_hidden_size=64, vocab_size=64)
+    tc = TrainConfig(micro_batch_size=2, global_batch_size=2, seq_length=16, train_iters=4, lr=0.05, min_lr=0.05,
+                     lr_decay_style="constant", weight_decay=0.01, clip_grad=0.0, log_interval=1000, seed=0,
+                     optimizer="sgd", sgd_momentum=0.9)
+    ds = SyntheticTokenDataset(cfg.vocab_size, 16, num_samples=8, seed=0)
+    tr = Trainer(cfg, ParallelConfig(), tc, single_process_mesh(), device=torch.device("cpu"), dataset=ds)
+    ref = CausalLM(cfg)
+    ref.load_state_dict(tr.models[0].state_dict())
+    decay = [p for n, p in ref.named_parameters() if p.dim() >= 2]
+    plain = [p for n, p in ref.named_parameters() if p.dim() < 2]
+    opt = torch.optim.SGD([{"params": decay, "weight_decay": 0.01}, {"params": plain, "weight_decay": 0.0}], lr=0.05, momentum=0.9)
+    it = D_iter = iter(ds[i]["text"] for i in range(8))
+    for step in range(4):
+        st = tr.train_step()
+        text = torch.stack([next(it), next(it)])
+        opt.zero_grad()
+        loss = ref.train()(text[:, :-1], text[:, 1:]).mean()
+        loss.backward()
+        opt.step()
+        assert abs(float(st["lm loss"]) - loss.item()) < 1e-5, (step, float(st["lm loss"]), loss.item())
+    a, b = tr.models[0].state_dict(), ref.state_dict()
+    assert all(torch.allclose(a[k], b[k], rtol=1e-5, atol=1e-6) for k in a)
