@@ -462,3 +462,13 @@ def test_use_checkpoint_args_reads_the_sharded_format_too(tmp_path):
                                 ["--load", str(tmp_path), "--use-checkpoint-args"])
     assert (got.num_layers, got.hidden_size, got.ffn_hidden_size, got.vocab_size) == (2, 48, 96, cfg.vocab_size)
     assert Trainer(got, ParallelConfig(), tc2, device=torch.device("cpu")).iteration == 1
+
+
+def test_skip_train_only_evaluates(capsys):
+    from linear_moe_b200.train.loop import pretrain
+    argv = ["--num-layers", "1", "--hidden-size", "32", "--num-attention-heads", "2", "--ffn-hidden-size", "64",
+            "--vocab-size", "64", "--seq-length", "16", "--micro-batch-size", "2", "--train-iters", "5", "--eval-iters", "2",
+            "--skip-train", "--log-interval", "100"]
+    trainer, stats = pretrain(argv)
+    assert trainer.iteration == 0 and "lm loss" in stats and float(stats["lm loss"]) > 0
+    assert "validation:" in capsys.readouterr().out
