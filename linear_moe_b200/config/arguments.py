@@ -70,6 +70,9 @@ def build_parser() -> argparse.ArgumentParser:
     _flag(g, "--hidden-dropout", type=float, default=0.0)
     _flag(g, "--qk-layernorm", action="store_true")
     _flag(g, "--sliding-window", type=int, default=None)
+    _flag(g, "--window-size", type=str, default=None, metavar="LEFT,RIGHT",
+          help="Megatron's spelling of the attention window: LEFT earlier tokens plus the current one (RIGHT must be 0 for "
+               "causal attention); the same as --sliding-window LEFT+1")
     _flag(g, "--apply-query-key-layer-scaling", action="store_true")
     _flag(g, "--vocab-size", type=int, default=None)
     _flag(g, "--extra-vocab-size", type=int, default=0)
@@ -386,6 +389,11 @@ def pad_vocab(vocab: int, divisible_by: int, tp: int) -> int:
 
 
 def configs_from_args(args: argparse.Namespace) -> Tuple[ModelConfig, ParallelConfig, TrainConfig]:
+    if getattr(args, "window_size", None) and args.sliding_window is None:
+        left, _, right = args.window_size.partition(",")
+        if int(right or 0) != 0:
+            raise ValueError("--window-size: causal attention takes RIGHT = 0")
+        args.sliding_window = None if int(left) < 0 else int(left) + 1
     if args.moe_expert_capacity_factor is not None:
         args.moe_token_dropping = True
         if args.moe_train_capacity_factor is None:
