@@ -472,3 +472,13 @@ def test_skip_train_only_evaluates(capsys):
     trainer, stats = pretrain(argv)
     assert trainer.iteration == 0 and "lm loss" in stats and float(stats["lm loss"]) > 0
     assert "validation:" in capsys.readouterr().out
+
+
+def test_window_size_spelling():
+    from linear_moe_b200.config.arguments import parse_args
+    b = ["--num-layers", "1", "--hidden-size", "32", "--num-attention-heads", "2"]
+    assert parse_args(b + ["--window-size", "7,0"])[1].sliding_window == 8          # 7 earlier tokens + the current one
+    assert parse_args(b + ["--window-size=-1,0"])[1].sliding_window is None         # no window
+    assert parse_args(b + ["--sliding-window", "16", "--window-size", "3,0"])[1].sliding_window == 16
+    with pytest.raises(ValueError, match="RIGHT = 0"):
+        parse_args(b + ["--window-size", "7,3"])
