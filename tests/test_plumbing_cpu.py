@@ -596,3 +596,29 @@ def test_sgd_matches_torch_sgd():
         assert abs(float(st["lm loss"]) - loss.item()) < 1e-5, (step, float(st["lm loss"]), loss.item())
     a, b = tr.models[0].state_dict(), ref.state_dict()
     assert all(torch.allclose(a[k], b[k], rtol=1e-5, atol=1e-6) for k in a)
+
+
+def _train_sgd(mesh, par, steps=3):
+    cfg = get_preset("bench-cpu-plumbing", num_experts=None, ffn_hidden_size=128, num_layers=2, layer_type_list="LN")
+    tc = TrainConfig(micro_batch_size=1, global_batch_size=2, seq_length=32, train_iters=steps, lr=0.02, min_lr=0.02,
+                     lr_decay_style="constant", weight_decay=0.01, clip_grad=1.0, log_interval=1000, seed=0,
+                     optimizer="sgd", sgd_momentum=0.9)
+    ds = SyntheticTokenDataset(cfg.vocab_size, 32, num_samples=2, seed=0)
+    tr = Trainer(cfg, par, tc, mesh, device=torch.device("cpu"), dataset=ds)
+    out = [tr.train_step() for _ in range(steps)]
+    return [float(o["lm loss"]) for o in out], [o["grad_norm"] for o in out]
+
+
+def _worker_sgd(rank, world):
+    par = ParallelConfig(distributed_backend="gloo", use_distributed_optimizer=True)
+    return _train_sgd(Mesh(par), par)
+
+
+def test_sgd_with_sharded_optimizer_state_matches_single_process():
+    """SGD under ZeRO-1 on two data-parallel ranks (momentum buffers sharded, updated shards gathered) follows the
+    single-process run with gradient accumulation."""
+    ref_losses, ref_gn = _train_sgd(single_process_mesh(), ParallelConfig())
+    losses, gn = run_distributed(_worker_sgd, 2)[0]
+    assert torch.allclose(torch.tensor(losses), torch.tensor(ref_losses), atol=2e-4), (losses, ref_losses)
+    assert torch.allclose(torch.tensor(gn), torch.tensor(ref_gn), rtol=2e-3), (gn, ref_gn)
+    assert ref_losses[-1] < ref_losses[0]
