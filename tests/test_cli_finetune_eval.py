@@ -482,3 +482,31 @@ def test_window_size_spelling():
     assert parse_args(b + ["--sliding-window", "16", "--window-size", "3,0"])[1].sliding_window == 16
     with pytest.raises(ValueError, match="RIGHT = 0"):
         parse_args(b + ["--window-size", "7,3"])
+
+
+def test_pretrain_cli_on_an_indexed_corpus_with_cache_and_read_ahead(tmp_path):
+    """The whole data path through the command line: json lines -> tokenised .bin / .idx -> training with the index cache,
+    the read-ahead thread, the native gather and --eod-mask-loss."""
+    import json
+    import os
+    from linear_moe_b200.data import preprocess
+    from linear_moe_b200.train.loop import pretrain
+    rng = torch.Generator().manual_seed(0)
+    src = tmp_path / "docs.jsonl"
+    with open(src, "w") as f:
+        for _ in range(40):
+            n = int(torch.randint(5, 60, (1,), generator=rng))
+            f.write(json.dumps({"text": " ".join(str(int(t)) for t in torch.randint(0, 100, (n,), generator=rng))}) + "\n")
+    preprocess.main(["--input", str(src), "--output-prefix", str(tmp_path / "corpus"), "--patch-tokenizer-type", "NullTokenizer",
+                     "--vocab-size", "128", "--append-eod"])
+    prefix = next(str(tmp_path / p[:-4]) for p in os.listdir(tmp_path) if p.endswith(".idx"))
+    argv = ["--num-layers", "1", "--hidden-size", "32", "--num-attention-heads", "2", "--ffn-hidden-size", "64",
+            "--vocab-size", "128", "--patch-tokenizer-type", "NullTokenizer", "--seq-length", "16", "--micro-batch-size", "2",
+            "--global-batch-size", "4", "--train-iters", "4", "--lr", "1e-3", "--log-interval", "100", "--eval-interval", "1000",
+            "--dataset", "LLama-Pretrain-Idxmap", "--data-path", prefix, "--split", "90,10,0",
+            "--data-cache-path", str(tmp_path / "cache"), "--num-workers", "2", "--eod-mask-loss"]
+    trainer, stats = pretrain(argv)
+    assert trainer.iteration == 4 and trainer.consumed_samples == 16 and float(stats["lm loss"]) > 0
+    assert trainer.tc.eod_token == 127 and trainer.data_iter.prefetch == 2
+    assert len(os.listdir(tmp_path / "cache")) >= 3
+    trainer.data_iter._shutdown()
